@@ -1,0 +1,142 @@
+/* joshua_b200 - C ABI of the B200 (sm_100a) quantized-matmul library.
+ *
+ * A drop-in for one path of the joshua inference engine: the fused
+ * dequantise-and-dot matmuls over raw GGUF blocks (Q8_0, Q2_K, Q4_K, IQ2_XXS,
+ * MXFP4) and the routed-expert gather / grouped matmul / scatter of its MoE
+ * loaders.  Every entry point names the reference interface it stands in for
+ * (file:line in the reference tree).
+ *
+ * Conventions (those of the reference's one C ABI, src/npu/mod.rs:32-50):
+ * int32 status, 0 = success, negative = failure; opaque handles; `*_free`
+ * releases; nothing throws or aborts across the boundary.  After a failure,
+ * `jq_last_error()` returns a message for the calling thread.  Handles are
+ * immutable after creation and may be used from several threads at once; each
+ * host-buffer call takes a private stream and workspace from the context.
+ *
+ * Matmul contract (src/quant_matmul.rs:105-118): weights are n rows of k
+ * columns stored row-major as n*k/B raw blocks in GGUF byte order; `lhs` is
+ * f32 [m, k] row-major; `dst` is f32 [m, n] row-major and is ASSIGNED,
+ * dst[i*n + j] = sum_c lhs[i*k + c] * W[j, c] (src/mxfp4.rs:185-189).
+ *
+ * There is no CPU fallback: every compute entry fails with JQ_E_CUDA when no
+ * device is usable.
+ */
+#ifndef JOSHUA_B200_H
+#define JOSHUA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct jq_ctx jq_ctx;       /* one device, its streams and workspaces */
+typedef struct jq_weight jq_weight; /* raw blocks resident in device memory */
+typedef struct jq_moe jq_moe;       /* one MoE layer: router + expert banks */
+
+/* status codes */
+#define JQ_OK 0
+#define JQ_E_INVALID (-1)      /* shape / length / alignment / NULL argument */
+#define JQ_E_TYPE (-2)         /* GGUF type id without a kernel here */
+#define JQ_E_CUDA (-3)         /* a CUDA runtime call failed (incl. no device) */
+#define JQ_E_NOMEM (-4)        /* device or pinned-host allocation failed */
+#define JQ_E_EXPERT_RANGE (-5) /* router produced an expert id >= n_expert */
+#define JQ_E_TOO_LARGE (-6)    /* request exceeds a fixed capacity */
+
+/* GGUF tensor type ids (src/gguf_ext.rs:483-512, src/iq2xxs.rs:23, src/mxfp4.rs:39) */
+#define JQ_TYPE_Q8_0 8u
+#define JQ_TYPE_Q2_K 10u
+#define JQ_TYPE_Q4_K 12u
+#define JQ_TYPE_IQ2_XXS 16u
+#define JQ_TYPE_MXFP4 39u
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* jq_last_error(void);
+
+/* Elements and bytes of one block of `type` (src/kquant_dot.rs:95-104,
+ * src/iq2xxs.rs:25-27, src/mxfp4.rs:36,59). */
+int32_t jq_block_size(uint32_t type, uint64_t* elems, uint64_t* bytes);
+
+/* ── context ─────────────────────────────────────────────────────────────
+ * Stands in for the reference's device selection (src/engine.rs:764-834).
+ * Binds to CUDA device `device`, uploads the decode tables. */
+int32_t jq_init(int32_t device, jq_ctx** out);
+void jq_free(jq_ctx* ctx);
+
+/* ── weights ─────────────────────────────────────────────────────────────
+ * jq_weight_upload replaces the zero-copy borrow of a tensor's byte range
+ * from the model mapping (`borrowed_range*` / `borrowed_qtensor*`,
+ * src/mmap_tensor.rs:520-655): `bytes` are the tensor's raw GGUF bytes,
+ * copied to device memory unmodified.  Fails like `blocks_from_bytes`
+ * (src/iq2xxs.rs:422-435, src/mxfp4.rs:265-279, src/kquant_dot.rs:217-220)
+ * when `nbytes` is not a whole number of blocks. */
+int32_t jq_weight_upload(jq_ctx* ctx, uint32_t type, const void* bytes, uint64_t nbytes, jq_weight** out);
+
+/* Adopt blocks that already sit in device memory (not copied, not freed). */
+int32_t jq_weight_from_device(jq_ctx* ctx, uint32_t type, const void* device_bytes, uint64_t nbytes,
+                              jq_weight** out);
+
+/* A run of whole blocks [block0, block0 + n_blocks) of `parent`, sharing its
+ * memory: the per-expert slicing of a [n_expert, out, in] tensor
+ * (`split_experts`, src/quantized_qwen3_moe.rs:556-651,
+ * src/quantized_deepseek4.rs:2193-2379).  The parent must outlive the slice. */
+int32_t jq_weight_slice(const jq_weight* parent, uint64_t block0, uint64_t n_blocks, jq_weight** out);
+
+void jq_weight_free(jq_weight* w);
+
+/* QuantizedType::{dtype, storage_size_in_bytes, block_size, as_ptr}
+ * (src/mmap_tensor.rs:127-188). */
+uint32_t jq_weight_type(const jq_weight* w);
+uint64_t jq_weight_storage_size(const jq_weight* w);
+uint64_t jq_weight_block_elems(const jq_weight* w);
+const void* jq_weight_device_ptr(const jq_weight* w);
+
+/* ── the operator: QuantizedType::matmul_t ───────────────────────────────
+ * Replaces `impl QuantizedType for MmapBlocks<T>` / MmapBlocksIq2Xxs /
+ * MmapBlocksMxfp4 :: matmul_t (src/mmap_tensor.rs:132-134,374-376,447-449),
+ * i.e. matmul_kquant (src/quant_matmul.rs:110-118), iq2xxs::matmul_t
+ * (src/iq2xxs.rs:103-111), mxfp4::matmul_t (src/mxfp4.rs:120-128).
+ * HOST buffers; `lhs_len` / `dst_len` are the slice lengths in elements and
+ * are validated as the reference validates them (src/quant_matmul.rs:133-165):
+ * k not a block multiple, block count != n*k/B, lhs_len != m*k or
+ * dst_len != m*n fail with JQ_E_INVALID; m == 0 or n == 0 is a no-op. */
+int32_t jq_matmul_t(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const float* lhs, uint64_t lhs_len,
+                    float* dst, uint64_t dst_len);
+
+/* QuantizedType::matmul_t_f16 (src/iq2xxs.rs:396-412, src/mxfp4.rs:242-258):
+ * IEEE binary16 in and out (as uint16 bit patterns), widened to f32, the f32
+ * product, rounded back to nearest-even. */
+int32_t jq_matmul_t_f16(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const uint16_t* lhs,
+                        uint64_t lhs_len, uint16_t* dst, uint64_t dst_len);
+
+/* Same product with DEVICE buffers on a caller stream (cudaStream_t passed as
+ * void*), no synchronisation: the device-resident insertion point that
+ * `Weight::Zc` / ZcWeight::forward occupies in the reference
+ * (src/quantized_qwen3_moe.rs:215-227, src/zero_copy_metal.rs:374-408). */
+int32_t jq_matmul_t_dev(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const float* lhs_dev,
+                        float* dst_dev, void* stream);
+
+/* QuantizedType::dequantize (src/mmap_tensor.rs:169-174) and
+ * decode_raw_to_f32 (src/quant_matmul.rs:36-103): all blocks to f32.
+ * `two_step` != 0 gives the separately rounded k-quant form fl(fl(d*sc*)q)-m
+ * of a plain `d1 * q - m1` (what `to_float` returns); 0 gives the single fused
+ * multiply-subtract the matmul kernels form (src/kquant_dot.rs:256-260).  The
+ * two differ by at most one ulp; other types have one form. */
+int32_t jq_dequantize(const jq_weight* w, float* out, uint64_t elem_count, int32_t two_step);
+int32_t jq_dequantize_dev(const jq_weight* w, float* out_dev, uint64_t elem_count, int32_t two_step, void* stream);
+
+/* QuantizedType::embedding (src/mmap_tensor.rs:140-167): out[i, :] = row
+ * ids[i] of a [rows, hidden] tensor, decoded.  Fails with JQ_E_INVALID when
+ * hidden is not a block multiple, the block count is not rows*hidden/B, or an
+ * id is >= rows. */
+int32_t jq_embedding(const jq_weight* w, const uint32_t* ids, uint64_t n_ids, uint64_t rows, uint64_t hidden,
+                     float* out);
+
+/* QuantizedType::from_float / from_float_imatrix (src/mmap_tensor.rs:190-203):
+ * borrowed tensors are read-only; always fails with JQ_E_INVALID. */
+int32_t jq_weight_from_float(jq_weight* w, const float* xs, uint64_t len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JOSHUA_B200_H */

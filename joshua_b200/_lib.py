@@ -1,0 +1,72 @@
+"""Loads `libjoshua_b200.so` (built in-tree by `joshua_b200.build`) through ctypes.
+
+There is no fallback: if the library is missing or cannot be loaded, importing
+any compute entry point raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libjoshua_b200.so"
+
+OK, E_INVALID, E_TYPE, E_CUDA, E_NOMEM, E_EXPERT_RANGE, E_TOO_LARGE = 0, -1, -2, -3, -4, -5, -6
+
+
+class JoshuaB200Error(RuntimeError):
+    """A C-ABI call returned a negative status; `.code` holds it."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+
+
+_lib = None
+
+u64, i32, u32, vp = ctypes.c_uint64, ctypes.c_int32, ctypes.c_uint32, ctypes.c_void_p
+pp = ctypes.POINTER(ctypes.c_void_p)
+
+_SIGNATURES = {
+    "jq_last_error": (ctypes.c_char_p, []),
+    "jq_block_size": (i32, [u32, ctypes.POINTER(u64), ctypes.POINTER(u64)]),
+    "jq_init": (i32, [i32, pp]),
+    "jq_free": (None, [vp]),
+    "jq_weight_upload": (i32, [vp, u32, vp, u64, pp]),
+    "jq_weight_from_device": (i32, [vp, u32, vp, u64, pp]),
+    "jq_weight_slice": (i32, [vp, u64, u64, pp]),
+    "jq_weight_free": (None, [vp]),
+    "jq_weight_type": (u32, [vp]),
+    "jq_weight_storage_size": (u64, [vp]),
+    "jq_weight_block_elems": (u64, [vp]),
+    "jq_weight_device_ptr": (vp, [vp]),
+    "jq_matmul_t": (i32, [vp, u64, u64, u64, vp, u64, vp, u64]),
+    "jq_matmul_t_f16": (i32, [vp, u64, u64, u64, vp, u64, vp, u64]),
+    "jq_matmul_t_dev": (i32, [vp, u64, u64, u64, vp, vp, vp]),
+    "jq_dequantize": (i32, [vp, vp, u64, i32]),
+    "jq_dequantize_dev": (i32, [vp, vp, u64, i32, vp]),
+    "jq_embedding": (i32, [vp, vp, u64, u64, u64, vp]),
+    "jq_weight_from_float": (i32, [vp, vp, u64]),
+}
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(
+                f"{LIB_PATH} is missing: build the CUDA library first (python -m joshua_b200.build); "
+                "joshua_b200 has no CPU fallback"
+            )
+        handle = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise JoshuaB200Error(rc, lib().jq_last_error().decode())

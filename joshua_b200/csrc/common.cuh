@@ -1,0 +1,37 @@
+// Shared declarations of the library's translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "formats.cuh"
+
+namespace jq {
+
+// Status codes of the C ABI (0 = success, negative = failure), following the
+// int32 status / opaque handle convention of the reference's only C ABI
+// (src/npu/mod.rs:32-50).
+enum : int32_t {
+    OK = 0,
+    E_INVALID = -1,      // shape / length / alignment / NULL argument
+    E_TYPE = -2,         // GGUF type id without a kernel here
+    E_CUDA = -3,         // a CUDA runtime call failed
+    E_NOMEM = -4,        // device or pinned host allocation failed
+    E_EXPERT_RANGE = -5, // router produced an expert id >= n_expert
+    E_TOO_LARGE = -6,    // request exceeds a fixed capacity
+};
+
+// dequant.cu
+cudaError_t tables_dequant();
+cudaError_t launch_dequant(uint32_t type, const uint8_t* w, uint64_t n_blocks, float* out, bool two_step,
+                           cudaStream_t s);
+// rows of `hidden` values gathered by id; ids >= rows set *bad_id (device flag) and write nothing
+cudaError_t launch_embedding(uint32_t type, const uint8_t* w, uint64_t rows, uint64_t hidden, const uint32_t* ids,
+                             uint64_t n_ids, float* out, int* bad_id, cudaStream_t s);
+
+// gemv_f32.cu: exact-decode float path, any m
+cudaError_t tables_gemv_f32();
+cudaError_t launch_matmul_f32(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
+                              float* dst, cudaStream_t s);
+
+}  // namespace jq

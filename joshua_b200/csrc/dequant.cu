@@ -1,0 +1,98 @@
+// Standalone block decode: raw GGUF blocks -> f32, one 8-value unit per thread.
+//
+// Serves QuantizedType::dequantize and QuantizedType::embedding of the
+// reference's borrowed tensors (src/mmap_tensor.rs:140-174,379-440,452-513)
+// and the raw decode of the streamed loader (src/quant_matmul.rs:36-103), and
+// is what the bit-exactness check of the block decode runs against.
+// HBM-bound: reads the block bytes once, writes 4 bytes per weight.
+#include "common.cuh"
+
+namespace jq {
+
+cudaError_t tables_dequant() { return upload_tables(); }
+
+namespace {
+
+template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES>
+__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict__ w, uint64_t n_units,
+                                                      float* __restrict__ out, bool two_step) {
+    constexpr uint32_t UPB = ELEMS / 8;  // units per block
+    for (uint64_t u = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; u < n_units;
+         u += (uint64_t)gridDim.x * blockDim.x) {
+        float v[8];
+        decode_unit<TYPE>(w + (u / UPB) * BYTES, (uint32_t)(u % UPB), v, two_step);
+        float4* o = reinterpret_cast<float4*>(out + u * 8);
+        o[0] = make_float4(v[0], v[1], v[2], v[3]);
+        o[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+}
+
+// out[i, :] = decode(row ids[i]); ids out of range raise the flag and leave the row untouched
+// (the reference bails with "embedding id .. is out of range", src/mmap_tensor.rs:158-160).
+template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES>
+__global__ void __launch_bounds__(256) embedding_kernel(const uint8_t* __restrict__ w, uint64_t rows, uint64_t hidden,
+                                                        const uint32_t* __restrict__ ids, uint64_t n_ids,
+                                                        float* __restrict__ out, int* bad_id) {
+    constexpr uint32_t UPB = ELEMS / 8;
+    const uint64_t units_per_row = hidden / 8;
+    const uint64_t row_bytes = hidden / ELEMS * BYTES;
+    const uint64_t total = n_ids * units_per_row;
+    for (uint64_t t = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; t < total;
+         t += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t i = t / units_per_row, u = t % units_per_row;
+        uint32_t id = ids[i];
+        if (id >= rows) {
+            if (u == 0) atomicExch(bad_id, 1);
+            continue;
+        }
+        float v[8];
+        decode_unit<TYPE>(w + id * row_bytes + (u / UPB) * BYTES, (uint32_t)(u % UPB), v, true);
+        float4* o = reinterpret_cast<float4*>(out + i * hidden + u * 8);
+        o[0] = make_float4(v[0], v[1], v[2], v[3]);
+        o[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+}
+
+inline unsigned grid_for(uint64_t work) {
+    uint64_t blocks = (work + 255) / 256;
+    return (unsigned)(blocks < 148ull * 64 ? (blocks ? blocks : 1) : 148ull * 64);
+}
+
+}  // namespace
+
+cudaError_t launch_dequant(uint32_t type, const uint8_t* w, uint64_t n_blocks, float* out, bool two_step,
+                           cudaStream_t s) {
+    Format f;
+    if (!format_of(type, &f)) return cudaErrorInvalidValue;
+    if (n_blocks == 0) return cudaSuccess;
+    uint64_t n_units = n_blocks * (f.elems / 8);
+    unsigned g = grid_for(n_units);
+    switch (type) {
+        case T_Q8_0: dequant_kernel<T_Q8_0, 32, 34><<<g, 256, 0, s>>>(w, n_units, out, two_step); break;
+        case T_Q2_K: dequant_kernel<T_Q2_K, 256, 84><<<g, 256, 0, s>>>(w, n_units, out, two_step); break;
+        case T_Q4_K: dequant_kernel<T_Q4_K, 256, 144><<<g, 256, 0, s>>>(w, n_units, out, two_step); break;
+        case T_IQ2_XXS: dequant_kernel<T_IQ2_XXS, 256, 66><<<g, 256, 0, s>>>(w, n_units, out, two_step); break;
+        case T_MXFP4: dequant_kernel<T_MXFP4, 32, 17><<<g, 256, 0, s>>>(w, n_units, out, two_step); break;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_embedding(uint32_t type, const uint8_t* w, uint64_t rows, uint64_t hidden, const uint32_t* ids,
+                             uint64_t n_ids, float* out, int* bad_id, cudaStream_t s) {
+    Format f;
+    if (!format_of(type, &f)) return cudaErrorInvalidValue;
+    if (n_ids == 0) return cudaSuccess;
+    unsigned g = grid_for(n_ids * (hidden / 8));
+#define JQ_EMB(T, E, B) embedding_kernel<T, E, B><<<g, 256, 0, s>>>(w, rows, hidden, ids, n_ids, out, bad_id)
+    switch (type) {
+        case T_Q8_0: JQ_EMB(T_Q8_0, 32, 34); break;
+        case T_Q2_K: JQ_EMB(T_Q2_K, 256, 84); break;
+        case T_Q4_K: JQ_EMB(T_Q4_K, 256, 144); break;
+        case T_IQ2_XXS: JQ_EMB(T_IQ2_XXS, 256, 66); break;
+        case T_MXFP4: JQ_EMB(T_MXFP4, 32, 17); break;
+    }
+#undef JQ_EMB
+    return cudaGetLastError();
+}
+
+}  // namespace jq
