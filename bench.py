@@ -1,0 +1,254 @@
+"""Benchmark of the quantized-matmul path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workloads
+  llama8b  (default) decode of a Llama-8B-shaped model, every linear Q4_K, batch 1:
+           one step = one token through all 32 layers' quantized linears and the
+           output head (4.22 GB of raw Q4_K blocks read once per token).
+  gemv     one quantized matmul shape, rotated over a working set larger than L2
+           (--type, --n, --k, --m, --rotate-gb): the kernel-level roofline probe
+           and the command used for ncu captures.
+
+One JSON line is printed by rank 0.  `value` is tokens/s with inputs resident
+in HBM; `e2e` is the same metric through the host-buffer C ABI (`jq_matmul_t`,
+host->device and device->host copies inside the timed region); `roofline` is the
+dominant kernel's algorithmic bytes over its CUDA-event time against the
+measured HBM copy bandwidth; `cpu_baseline` is the CPU oracle (a C++/AVX2
+restatement of the reference's kernels) timed on this host's cores on a bounded
+sample of the same workload.  `--impl reference` times that CPU path alone.
+All data are synthetic (seeded random raw blocks, N(0,1) activations).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import numpy as np  # noqa: E402
+
+from joshua_b200 import synth  # noqa: E402
+
+FALLBACK_HBM_GBS = 6650.0
+TYPE_BY_NAME = {v: k for k, v in synth.NAMES.items()}
+
+# Llama-8B-class shape of the benchmark configuration
+LLAMA = dict(layers=32, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=14336, vocab=128256)
+
+
+def llama_linears():
+    """(name, n, k) of the quantized linears one decoded token passes through, in order."""
+    c = LLAMA
+    h, kv = c["hidden"], c["kv_heads"] * c["head_dim"]
+    per_layer = [("wq", h, h), ("wk", kv, h), ("wv", kv, h), ("wo", h, h),
+                 ("w_gate", c["ffn"], h), ("w_up", c["ffn"], h), ("w_down", h, c["ffn"])]
+    out = []
+    for layer in range(c["layers"]):
+        out += [(f"l{layer}.{nm}", n, k) for nm, n, k in per_layer]
+    out.append(("output", c["vocab"], h))
+    return out
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index),
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) == 6:
+                self.rows.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(float(r[0]) for r in self.rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(self.rows[0][1]), "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+# ───────────────────────────── CPU baseline ───────────────────────────────
+
+def cpu_llama_sample(seconds_budget: float = 15.0):
+    """Times the oracle on layer-0's seven linears + nothing else, scaled to a token.
+
+    The sample is a fixed fraction of the token's weight bytes; tokens/s is
+    extrapolated by bytes (every linear is the same Q4_K kernel at m = 1).
+    """
+    import oracle
+
+    c = LLAMA
+    h, kv = c["hidden"], c["kv_heads"] * c["head_dim"]
+    shapes = [(h, h), (kv, h), (kv, h), (h, h), (c["ffn"], h), (c["ffn"], h), (h, c["ffn"])]
+    weights = [synth.random_weight(synth.Q4_K, n, k, seed=i) for i, (n, k) in enumerate(shapes)]
+    acts = {k: synth.random_activations(1, k, seed=k) for k in {s[1] for s in shapes}}
+    sample_bytes = sum(w.size for w in weights)
+    token_bytes = sum(synth.tensor_bytes(synth.Q4_K, n, k) for _, n, k in llama_linears())
+
+    def one_pass():
+        for w, (n, k) in zip(weights, shapes):
+            oracle.matmul_t(synth.Q4_K, (1, k, n), acts[k], w)
+
+    one_pass()
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        one_pass()
+        reps += 1
+        if time.perf_counter() - t0 > seconds_budget or reps >= 200:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    tok_s = 1.0 / (dt * token_bytes / sample_bytes)
+    return {"value": tok_s, "unit": "tok/s", "cores": oracle.threads(), "kind": "port",
+            "sample": f"layer-0 linears (7 Q4_K matmuls, {sample_bytes / 1e6:.0f} MB of {token_bytes / 1e9:.2f} GB "
+                      f"per token), {reps} passes, scaled by bytes",
+            "gbs": sample_bytes / dt / 1e9}
+
+
+def run_reference(args):
+    """`--impl reference`: the reference's CPU kernels (C++ oracle port) on this host, all cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    t0 = time.perf_counter()
+    base = cpu_llama_sample(seconds_budget=max(5.0, min(60.0, 2.0 * (args.steps + args.warmup))))
+    line = {
+        "impl": "reference", "metric": "decode_tok_s", "value": base["value"], "unit": "tok/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 / base["value"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "llama8b_q4k_decode_b1", **LLAMA},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(line))
+
+
+# ───────────────────────────── GPU workloads ──────────────────────────────
+
+def cuda_time(fn, steps, warmup, barrier=None):
+    """Runs fn() warmup + steps times; returns seconds per step from CUDA events on the current stream."""
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(steps):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return s.elapsed_time(e) * 1e-3 / steps
+
+
+def run_gemv(args):
+    import torch
+
+    from joshua_b200.qtensor import QTensor
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    t = TYPE_BY_NAME[args.type]
+    n, k, m = args.n, args.k, args.m
+    wbytes = synth.tensor_bytes(t, n, k)
+    nmat = max(2, int(args.rotate_gb * 1e9 // wbytes))
+    bank = synth.random_weight_torch(t, n * nmat, k, 1, dev)
+    bank = torch.cat([bank, torch.zeros(16, dtype=torch.uint8, device=dev)])
+    ws = [QTensor.from_device(t, bank[i * wbytes:(i + 1) * wbytes]) for i in range(nmat)]
+    x = torch.randn(m, k, device=dev)
+    y = torch.empty(m, n, device=dev)
+
+    def step():
+        for w in ws:
+            w.matmul_t_dev((m, k, n), x, y)
+
+    with ClockSampler(dev.index or 0) as clocks:
+        dt = cuda_time(step, args.steps, args.warmup) / nmat
+    peak, which = measured_peaks()
+    alg = wbytes + 4 * m * (k + n)
+    line = {
+        "metric": "quant_matmul_gbs", "value": alg / dt / 1e9, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "i8xi8->i32, f32 scales", "data": "synthetic",
+        "config": {"workload": f"gemv {args.type} n={n} k={k} m={m}", "rotating_set_gb": nmat * wbytes / 1e9,
+                   "l2": "inputs larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": alg / dt / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": alg / dt / 1e9 / peak, "traffic": None, "peak_source": which,
+                     "note": "time per matmul includes the activation-plane kernel that precedes it"},
+        "gpu_launches": 2 * nmat * args.steps, "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="llama8b", choices=["llama8b", "gemv"])
+    ap.add_argument("--type", default="q4_k", choices=sorted(TYPE_BY_NAME))
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--rotate-gb", type=float, default=1.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.workload == "gemv":
+        return run_gemv(args)
+    from joshua_b200 import bench_llama
+
+    return bench_llama.run(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -42,6 +42,7 @@ typedef struct jq_moe jq_moe;       /* one MoE layer: router + expert banks */
 #define JQ_E_NOMEM (-4)        /* device or pinned-host allocation failed */
 #define JQ_E_EXPERT_RANGE (-5) /* router produced an expert id >= n_expert */
 #define JQ_E_TOO_LARGE (-6)    /* request exceeds a fixed capacity */
+#define JQ_E_TIMEOUT (-7)      /* a bounded wait inside a kernel gave up */
 
 /* GGUF tensor type ids (src/gguf_ext.rs:483-512, src/iq2xxs.rs:23, src/mxfp4.rs:39) */
 #define JQ_TYPE_Q8_0 8u
@@ -62,6 +63,13 @@ int32_t jq_block_size(uint32_t type, uint64_t* elems, uint64_t* bytes);
  * Binds to CUDA device `device`, uploads the decode tables. */
 int32_t jq_init(int32_t device, jq_ctx** out);
 void jq_free(jq_ctx* ctx);
+
+/* Every wait inside a kernel (on a copy in flight) is bounded; a kernel whose
+ * wait runs out sets a device-visible flag and returns.  Host-buffer entries
+ * check the flag themselves; callers of the *_dev entries poll it here after
+ * synchronising their stream.  JQ_OK or JQ_E_TIMEOUT.  (The reference's
+ * counterpart is the deadline handling of its plugin shim, src/npu/shim.rs:1-8.) */
+int32_t jq_device_status(const jq_ctx* ctx);
 
 /* ── weights ─────────────────────────────────────────────────────────────
  * jq_weight_upload replaces the zero-copy borrow of a tensor's byte range

@@ -11,7 +11,7 @@ from pathlib import Path
 _HERE = Path(__file__).resolve().parent
 LIB_PATH = _HERE / "libjoshua_b200.so"
 
-OK, E_INVALID, E_TYPE, E_CUDA, E_NOMEM, E_EXPERT_RANGE, E_TOO_LARGE = 0, -1, -2, -3, -4, -5, -6
+OK, E_INVALID, E_TYPE, E_CUDA, E_NOMEM, E_EXPERT_RANGE, E_TOO_LARGE, E_TIMEOUT = 0, -1, -2, -3, -4, -5, -6, -7
 
 
 class JoshuaB200Error(RuntimeError):
@@ -32,6 +32,7 @@ _SIGNATURES = {
     "jq_block_size": (i32, [u32, ctypes.POINTER(u64), ctypes.POINTER(u64)]),
     "jq_init": (i32, [i32, pp]),
     "jq_free": (None, [vp]),
+    "jq_device_status": (i32, [vp]),
     "jq_weight_upload": (i32, [vp, u32, vp, u64, pp]),
     "jq_weight_from_device": (i32, [vp, u32, vp, u64, pp]),
     "jq_weight_slice": (i32, [vp, u64, u64, pp]),

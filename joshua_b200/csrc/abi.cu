@@ -3,6 +3,8 @@
 // they replace are in include/joshua_b200.h.
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+#include <map>
 #include <mutex>
 #include <new>
 #include <string>
@@ -61,10 +63,38 @@ struct Workspace {
 
 }  // namespace
 
+// Scratch of the decode kernels (activation planes), one per caller stream.
+struct StreamScratch {
+    void* dev = nullptr;
+    size_t cap = 0;
+};
+
 struct jq_ctx {
     int device = 0;
+    bool force_f32 = false;        // JQ_FORCE_F32_PATH=1: always take the exact-decode float kernels
+    int* status_host = nullptr;    // pinned, device-visible: set to 1 by a kernel whose bounded wait gave up
+    int* status_dev = nullptr;
     std::mutex mu;
     std::vector<Workspace*> idle;
+    std::map<cudaStream_t, StreamScratch> scratch;
+
+    // Scratch for `stream`, at least `bytes` large.  Growing it frees the old buffer (cudaFree
+    // waits for the device), so warm a stream up at its largest shape before capturing it.
+    cudaError_t scratch_for(cudaStream_t stream, size_t bytes, void** out) {
+        std::lock_guard<std::mutex> g(mu);
+        StreamScratch& sc = scratch[stream];
+        if (bytes > sc.cap) {
+            if (sc.dev) cudaFree(sc.dev);
+            sc.dev = nullptr;
+            sc.cap = 0;
+            size_t want = (bytes + (1u << 20) - 1) & ~((size_t)(1u << 20) - 1);
+            cudaError_t e = cudaMalloc(&sc.dev, want);
+            if (e != cudaSuccess) return e;
+            sc.cap = want;
+        }
+        *out = sc.dev;
+        return cudaSuccess;
+    }
 
     Workspace* acquire() {
         {
@@ -133,7 +163,20 @@ int32_t validate_matmul(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, 
 // Picks the kernel for a device-resident product.
 int32_t matmul_device(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const float* lhs, float* dst,
                       cudaStream_t s) {
+    jq_ctx* ctx = w->ctx;
+    if (!ctx->force_f32 && jq::gemv_mma_supports(w->type, w->dev, n, k, m)) {
+        void* scratch = nullptr;
+        JQ_CUDA(ctx->scratch_for(s, jq::gemv_mma_scratch_bytes(m, k), &scratch));
+        JQ_CUDA(jq::launch_gemv_mma(w->type, w->dev, n, k, lhs, m, dst, scratch, ctx->status_dev, s));
+        return jq::OK;
+    }
     JQ_CUDA(jq::launch_matmul_f32(w->type, w->dev, n, k, lhs, m, dst, s));
+    return jq::OK;
+}
+
+int32_t check_device_status(const jq_ctx* ctx) {
+    if (ctx->status_host && *static_cast<volatile int*>(ctx->status_host) != 0)
+        return fail(jq::E_TIMEOUT, "a bounded wait inside a kernel gave up (device status flag is set)");
     return jq::OK;
 }
 
@@ -181,9 +224,19 @@ int32_t jq_init(int32_t device, jq_ctx** out) {
                                     std::to_string(prop.major) + std::to_string(prop.minor));
     JQ_CUDA(jq::tables_dequant());
     JQ_CUDA(jq::tables_gemv_f32());
+    JQ_CUDA(jq::tables_gemv_mma());
     jq_ctx* c = new (std::nothrow) jq_ctx();
     if (!c) return fail(jq::E_NOMEM, "jq_init: out of host memory");
     c->device = device;
+    const char* f = std::getenv("JQ_FORCE_F32_PATH");
+    c->force_f32 = f && f[0] == '1';
+    cudaError_t he = cudaHostAlloc(&c->status_host, sizeof(int), cudaHostAllocMapped);
+    if (he == cudaSuccess) he = cudaHostGetDevicePointer(&c->status_dev, c->status_host, 0);
+    if (he != cudaSuccess) {
+        delete c;
+        return fail_cuda(he, "jq_init: status flag");
+    }
+    *c->status_host = 0;
     *out = c;
     return jq::OK;
 }
@@ -191,6 +244,9 @@ int32_t jq_init(int32_t device, jq_ctx** out) {
 void jq_free(jq_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
+    cudaDeviceSynchronize();
+    for (auto& kv : ctx->scratch) cudaFree(kv.second.dev);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
     for (Workspace* w : ctx->idle) {
         cudaStreamSynchronize(w->stream);
         cudaFree(w->dev);
@@ -308,7 +364,7 @@ int32_t jq_matmul_t(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, cons
     if (int32_t rc = matmul_device(w, m, k, n, d_lhs, d_dst, s)) return rc;
     JQ_CUDA(cudaMemcpyAsync(dst, d_dst, dst_bytes, cudaMemcpyDeviceToHost, s));
     JQ_CUDA(cudaStreamSynchronize(s));
-    return jq::OK;
+    return check_device_status(w->ctx);
 }
 
 int32_t jq_matmul_t_f16(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const uint16_t* lhs,
@@ -333,7 +389,7 @@ int32_t jq_matmul_t_f16(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, 
     JQ_CUDA(cudaGetLastError());
     JQ_CUDA(cudaMemcpyAsync(dst, h_dst, d, cudaMemcpyDeviceToHost, s));
     JQ_CUDA(cudaStreamSynchronize(s));
-    return jq::OK;
+    return check_device_status(w->ctx);
 }
 
 int32_t jq_dequantize_dev(const jq_weight* w, float* out_dev, uint64_t elem_count, int32_t two_step, void* stream) {
@@ -392,6 +448,11 @@ int32_t jq_embedding(const jq_weight* w, const uint32_t* ids, uint64_t n_ids, ui
     JQ_CUDA(cudaMemcpyAsync(out, d_out, n_ids * hidden * 4, cudaMemcpyDeviceToHost, s));
     JQ_CUDA(cudaStreamSynchronize(s));
     return jq::OK;
+}
+
+int32_t jq_device_status(const jq_ctx* ctx) {
+    if (!ctx) return fail(jq::E_INVALID, "jq_device_status: NULL context");
+    return check_device_status(ctx);
 }
 
 int32_t jq_weight_from_float(jq_weight*, const float*, uint64_t) {

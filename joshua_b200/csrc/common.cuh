@@ -19,6 +19,7 @@ enum : int32_t {
     E_NOMEM = -4,        // device or pinned host allocation failed
     E_EXPERT_RANGE = -5, // router produced an expert id >= n_expert
     E_TOO_LARGE = -6,    // request exceeds a fixed capacity
+    E_TIMEOUT = -7,      // a bounded wait inside a kernel gave up
 };
 
 // dequant.cu
@@ -33,5 +34,15 @@ cudaError_t launch_embedding(uint32_t type, const uint8_t* w, uint64_t rows, uin
 cudaError_t tables_gemv_f32();
 cudaError_t launch_matmul_f32(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
                               float* dst, cudaStream_t s);
+
+// gemv_mma.cu: integer-code tensor-core path for batches 1..GEMV_MMA_MAX_M
+constexpr uint64_t GEMV_MMA_MAX_M = 16;
+cudaError_t tables_gemv_mma();
+// bytes of scratch (activation planes) a launch with these sizes needs
+size_t gemv_mma_scratch_bytes(uint64_t m, uint64_t k);
+bool gemv_mma_supports(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, uint64_t m);
+// error_flag: device int set to 1 if a bounded wait inside the kernel gave up
+cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
+                            float* dst, void* scratch, int* error_flag, cudaStream_t s);
 
 }  // namespace jq
