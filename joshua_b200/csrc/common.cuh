@@ -36,7 +36,7 @@ cudaError_t launch_matmul_f32(uint32_t type, const uint8_t* w, uint64_t n, uint6
                               float* dst, cudaStream_t s);
 
 // gemv_mma.cu: integer-code tensor-core path for batches 1..GEMV_MMA_MAX_M
-constexpr uint64_t GEMV_MMA_MAX_M = 16;
+constexpr uint64_t GEMV_MMA_MAX_M = 8;
 cudaError_t tables_gemv_mma();
 // bytes of scratch (activation planes) a launch with these sizes needs
 size_t gemv_mma_scratch_bytes(uint64_t m, uint64_t k);

@@ -13,8 +13,8 @@
 //   * q_c are the exact small integers of the format (Q8_0: int8; Q4_K: 0..15;
 //     Q2_K: 0..3; IQ2_XXS: +-8/25/43; MXFP4: twice the E2M1 value, 0..+-12).
 //   * each activation row is split, per 32-value group, into three int8 planes
-//     x ~= (s/254^2) * (254^2*hi + 254*mid + lo), |error| <= max|x| * 6.1e-8, i.e.
-//     to f32 precision (quantize_acts), so sum_c x_c q_c is three exact int32 dot
+//     x ~= (s/254^2) * (254^2*hi + 254*mid + lo) with one scale s per 256 values,
+//     |error| <= max|x| * 6.1e-8, i.e. f32 precision (quantize_acts), so sum_c x_c q_c is three exact int32 dot
 //     products computed by mma.sync.m16n8k32.s8 (m16n8k16 for the 16-value
 //     groups of Q2_K);
 //   * the f32 group scales s_g = d*sc, o_g = dmin*m and the f32 group sums of x
@@ -26,14 +26,13 @@
 // stages deep; warps split the chunk's blocks, and partial sums meet in shared
 // memory in a fixed order, so results do not depend on timing.
 //
-// MMA tile use: A = 16 weight rows x 32 codes.  B = 32 codes x 8 columns.  Two
-// MMAs share each A fragment: the first takes the (hi, mid) planes of a batch
-// row in a column pair, the second its lo plane in the even column of the same
-// pair.  With MB batch rows per MMA (1, 2 or 4) only MB column pairs are live,
-// so 4/MB consecutive groups are chained into one accumulator by giving each
-// its own pair: after the chain, thread t of a quad holds the three dots of
-// group (t / MB) and batch row (t % MB), and scales exactly that one.  Batches
-// above 4 run NH passes over the same A fragments.
+// MMA tile use: A = 16 weight rows x 32 codes, B = 32 codes x 8 columns.  The legacy integer MMA pipe is
+// the scarce unit on this part (one m16n8k32 per 8 cycles per SM), so one MMA per group must do: the
+// three planes of a batch row take three columns (a slot), an MMA carries two slots, and with one batch
+// row 2 consecutive groups are chained into one accumulator by giving each its own slot.  Group scales
+// that are small integers (Q4_K, Q2_K, IQ2_XXS) are multiplied in as integers and summed over the
+// 256-value unit before one float conversion; f16 / power-of-two scales (Q8_0, MXFP4) are applied in
+// float per group.  Batches above 2 run NH passes over the same A fragments.
 //
 // Algorithmic bytes per launch: n*k/B*S (weights) + 4*m*(k + n).
 #include <algorithm>
@@ -90,6 +89,13 @@ __device__ __forceinline__ void mma_k32(int c[4], const uint32_t a[4], uint32_t 
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// Same with an unsigned A operand (bytes 0..255).
+__device__ __forceinline__ void mma_k32_u8(int c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
 __device__ __forceinline__ void mma_k16(int c[4], uint32_t a0, uint32_t a1, uint32_t b0) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
@@ -123,7 +129,7 @@ __device__ __forceinline__ uint2 lds64_mis(const uint8_t* p) {
 //   planes[(i*NG + G)*96 + 0..31]   hi plane, int8, in the format's lane order
 //   planes[(i*NG + G)*96 + 32..63]  mid plane
 //   planes[(i*NG + G)*96 + 64..95]  lo plane
-//   meta[i*NG + G]                  float2 {s/254^2, sum of x over the group}
+//   meta[i*NG + G]                  float2 {s/254^2 of the group's 256-value unit, sum of x over the group}
 //   sum16[(i*NG + G)*2 + h]         sum of x over each 16-value half (Q2_K minima)
 // Lane order: position 8t+j holds the element that lane t of a quad feeds to
 // the MMA at byte j.  Identity for every format except MXFP4, whose packed
@@ -142,43 +148,59 @@ __device__ __forceinline__ uint32_t act_position(uint32_t type, uint32_t e) {
     return 8 * (r >> 2) + 2 * (r & 3) + half;
 }
 
+// Programmatic dependent launch: `pdl_wait` blocks until the preceding kernel in the stream has completed
+// and its writes are visible; `pdl_trigger` lets the next kernel (if it was launched with the programmatic
+// attribute) start its own prologue.  Both are no-ops for ordinary launches.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __global__ void __launch_bounds__(256) quantize_acts_kernel(const float* __restrict__ x, uint64_t m, uint64_t k,
                                                             uint32_t type, int8_t* __restrict__ planes,
                                                             float2* __restrict__ meta, float* __restrict__ sum16) {
-    const uint32_t lane = threadIdx.x & 31;
-    const uint64_t n_groups = k / 32;
-    const uint64_t total = m * n_groups;
-    for (uint64_t w = blockIdx.x * 8ull + (threadIdx.x >> 5); w < total; w += gridDim.x * 8ull) {
-        float v = x[w * 32 + lane];
-        float amax = fabsf(v);
-        float sum = v;
+    // one block per 256-value unit, one thread per value; warp = 32-value group
+    __shared__ float s_max[8];
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+    const uint64_t total = m * (k / 256);
+    for (uint64_t w = blockIdx.x; w < total; w += gridDim.x) {
+        float v = x[w * 256 + threadIdx.x];
+        float amax = fabsf(v), sum = v;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
             if (o < 16) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
         }
-        // `sum` now holds the sum of this lane's 16-value half
+        // `sum` holds the sum of the lane's 16-value half
         float other = __shfl_xor_sync(0xFFFFFFFFu, sum, 16);
-        float s = amax * (1.0f / 127.0f);
-        int hi = 0, mid = 0, lo = 0;
+        if (lane == 0) s_max[grp] = amax;
+        __syncthreads();
+        float umax = s_max[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) umax = fmaxf(umax, s_max[i]);
+        __syncthreads();
+        const float s = umax * (1.0f / 127.0f);
         const bool live = s > 0.0f && isfinite(s);
+        const float s1 = s * (1.0f / 254.0f), s2 = s1 * (1.0f / 254.0f);
+        int q0 = 0, q1 = 0, q2 = 0;
         if (live) {
-            hi = max(-127, min(127, __float2int_rn(v / s)));
-            float r1 = fmaf(-(float)hi, s, v);  // exact: |r1| <= s/2
-            float s1 = s * (1.0f / 254.0f);
-            mid = max(-127, min(127, __float2int_rn(r1 / s1)));
-            float r2 = fmaf(-(float)mid, s1, r1);
-            float s2 = s1 * (1.0f / 254.0f);
-            lo = max(-127, min(127, __float2int_rn(r2 / s2)));
+            // the rounded quotients need not be exact: each residual is formed exactly and handed down
+            const float inv = 1.0f / s;
+            q0 = max(-127, min(127, __float2int_rn(v * inv)));
+            float r1 = fmaf(-(float)q0, s, v);
+            q1 = max(-127, min(127, __float2int_rn(r1 * (inv * 254.0f))));
+            float r2 = fmaf(-(float)q1, s1, r1);
+            q2 = max(-127, min(127, __float2int_rn(r2 * (inv * 64516.0f))));
         }
-        uint32_t pos = act_position(type, lane);
-        planes[w * 96 + pos] = (int8_t)hi;
-        planes[w * 96 + 32 + pos] = (int8_t)mid;
-        planes[w * 96 + 64 + pos] = (int8_t)lo;
+        const uint64_t gbase = (w * 8 + grp) * 96;
+        const uint32_t pos = act_position(type, lane);
+        planes[gbase + pos] = (int8_t)q0;
+        planes[gbase + 32 + pos] = (int8_t)q1;
+        planes[gbase + 64 + pos] = (int8_t)q2;
         if (lane == 0) {
-            meta[w] = make_float2(live ? s * (1.0f / 254.0f) * (1.0f / 254.0f) : 0.0f, sum + other);
-            sum16[w * 2] = sum;
-            sum16[w * 2 + 1] = other;
+            meta[w * 8 + grp] = make_float2(live ? s2 : 0.0f, sum + other);
+            sum16[(w * 8 + grp) * 2] = sum;
+            sum16[(w * 8 + grp) * 2 + 1] = other;
         }
     }
 }
@@ -194,139 +216,228 @@ template <uint32_t TYPE>
 struct Traits;
 template <>
 struct Traits<T_Q4_K> {
-    static constexpr uint32_t UNIT_BYTES = 144, CHUNK_UNITS = 16, ALIGN = 16;
+    static constexpr uint32_t UNIT_BYTES = 144, CHUNK_UNITS = 16;
 };
 template <>
 struct Traits<T_Q8_0> {
-    static constexpr uint32_t UNIT_BYTES = 272, CHUNK_UNITS = 8, ALIGN = 16;
+    static constexpr uint32_t UNIT_BYTES = 272, CHUNK_UNITS = 8;
 };
 template <>
 struct Traits<T_Q2_K> {
-    static constexpr uint32_t UNIT_BYTES = 84, CHUNK_UNITS = 24, ALIGN = 4;
+    static constexpr uint32_t UNIT_BYTES = 84, CHUNK_UNITS = 24;
 };
 template <>
 struct Traits<T_IQ2_XXS> {
-    static constexpr uint32_t UNIT_BYTES = 66, CHUNK_UNITS = 32, ALIGN = 2;
+    static constexpr uint32_t UNIT_BYTES = 66, CHUNK_UNITS = 32;
 };
 template <>
 struct Traits<T_MXFP4> {
-    static constexpr uint32_t UNIT_BYTES = 136, CHUNK_UNITS = 16, ALIGN = 8;
+    static constexpr uint32_t UNIT_BYTES = 136, CHUNK_UNITS = 16;
 };
 
+// Activation data is read from shared memory when the kernel staged it there (ACT == 1) and from global
+// memory through the read-only path otherwise.
+template <int ACT, class T>
+__device__ __forceinline__ T ld_act(const T* p) {
+    if (ACT) return *p;
+    return __ldg(p);
+}
+
 // Per-lane roles, fixed for the kernel's lifetime.
+//
+// One MMA has 8 activation columns.  A slot is three columns (hi, mid, lo planes of one batch row for one
+// group); columns 0..2 are slot 0, 3..5 slot 1, 6..7 are fed zeros.  With MB batch rows per MMA (1 or 2),
+// 2/MB consecutive groups are chained into one accumulator, slot = position * MB + batch row.
+//   * supplier role: lane (g, t) feeds column g.
+//   * holder role: lane t of a quad receives columns 2t and 2t+1 of rows g and g+8.  Scaling is linear in
+//     every column, so each lane scales and accumulates its own two columns and the quad is summed once
+//     per tile.
 template <int MB, int NH>
 struct Roles {
-    static constexpr int CH = 4 / MB;  // groups chained into one accumulator
-    int g, t;                          // MMA row group and quad lane
-    int sup_p, sup_odd;                // as B supplier: chain position of column g, and whether g is odd
-    int fin_p;                         // as finaliser: chain position of columns 2t, 2t+1
-    uint32_t sup_row[NH], fin_row[NH]; // batch rows served in pass h, clamped to m-1 (clamped results are dropped)
+    static constexpr int CH = 2 / MB;  // groups chained into one accumulator
+    int g, t;
+    bool sup_live;                // column g carries data
+    int sup_p, sup_plane;         // chain position and plane of column g
+    uint32_t sup_row[NH];         // batch row fed in pass h (clamped to m-1; clamped results are dropped)
+    int col_p[2], col_i[2];       // chain position and batch row (within a pass) of held columns 2t, 2t+1
+    float col_w[2];               // plane weight of the held columns: 254^2, 254, 1, or 0 for a dead column
+    uint32_t sup_off[NH];         // byte offset of this lane's B bytes inside the planes, group 0 (dead lanes: 0)
+    uint32_t min_row[MB * NH];    // batch rows, clamped, for the minima terms
     __device__ __forceinline__ Roles(int lane, uint64_t m) {
         g = lane >> 2;
         t = lane & 3;
-        int pair = g >> 1;
-        sup_odd = g & 1;
-        sup_p = pair / MB;
-        fin_p = t / MB;
+        sup_live = g < 6;
+        int slot = g / 3;
+        sup_plane = g % 3;
+        sup_p = slot / MB;
 #pragma unroll
-        for (int h = 0; h < NH; ++h) {
-            sup_row[h] = (uint32_t)min((uint64_t)(pair % MB + 4 * h), m - 1);
-            fin_row[h] = (uint32_t)min((uint64_t)(t % MB + 4 * h), m - 1);
+        for (int h = 0; h < NH; ++h) sup_row[h] = (uint32_t)min((uint64_t)(h * MB + slot % MB), m - 1);
+#pragma unroll
+        for (int h = 0; h < NH; ++h) sup_off[h] = 0;  // filled by the kernel once n_groups is known
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            int col = 2 * t + j;
+            int s = col / 3, pl = col % 3;
+            col_p[j] = col < 6 ? s / MB : 0;
+            col_i[j] = col < 6 ? s % MB : 0;
+            col_w[j] = col >= 6 ? 0.0f : (pl == 0 ? 64516.0f : (pl == 1 ? 254.0f : 1.0f));
         }
+#pragma unroll
+        for (int b = 0; b < MB * NH; ++b) min_row[b] = (uint32_t)min((uint64_t)b, m - 1);
     }
 };
 
-// Scale and offset of Q4_K pair j taken from the 16 header bytes
-// (src/kquant_dot.rs:106-118); `hi_half` (j >= 4) is known at compile time.
-__device__ __forceinline__ void q4k_pair(const uint4& h, bool hi_half, uint32_t jj, float* d1, float* m1) {
-    float d = f16_bits_to_f32(h.x & 0xFFFF), dmin = f16_bits_to_f32(h.x >> 16);
-    uint32_t sh = 8 * jj;  // jj = j & 3
-    uint32_t sc, mn;
-    if (!hi_half) {
-        sc = (h.y >> sh) & 63;
-        mn = (h.z >> sh) & 63;
-    } else {
-        uint32_t a = (h.w >> sh) & 0xFF;
-        sc = (a & 0xF) | ((((h.y >> sh) & 0xFF) >> 6) << 4);
-        mn = (a >> 4) | ((((h.z >> sh) & 0xFF) >> 6) << 4);
-    }
-    *d1 = __fmul_rn(d, (float)sc);
-    *m1 = __fmul_rn(dmin, (float)mn);
-}
-
-// One unit (256 columns x 16 rows) of the warp's work.  u0 / u1 point at the
-// unit's bytes for rows g and g+8 in shared memory; G0 is the unit's first
-// 32-group index along k.  acc[h][0/1] accumulate rows g / g+8 for the lane's
-// finaliser batch row fin_i + 4h.
-template <uint32_t TYPE, int MB, int NH>
-__device__ __forceinline__ void process_unit(const uint8_t* u0, const uint8_t* u1, uint32_t G0, const ActPlanes& act,
+// One unit (256 columns x 16 rows) of a warp's work.  u0 / u1 point at the unit's bytes for rows g and
+// g+8 in shared memory; U is the unit's index along k (its first 32-group is 8U).
+//   colacc[h][j][r]  running sum of held column j, row r (0: g, 1: g+8), pass h
+//   minacc[b][r]     running sum of the minima terms of batch row b
+template <uint32_t TYPE, int MB, int NH, int ACT>
+__device__ __forceinline__ void process_unit(const uint8_t* u0, const uint8_t* u1, uint32_t U, const ActPlanes& act,
                                              const Roles<MB, NH>& ro, const uint2* s_grid, const uint2* s_mask,
-                                             float acc[NH][2]) {
+                                             float colacc[NH][2][2], float minacc[MB * NH][2]) {
     constexpr int CH = Roles<MB, NH>::CH;
-    int c[NH][4];   // (hi, mid) dots: c[0], c[1] row g; c[2], c[3] row g+8
-    int cl[NH][4];  // lo dots: cl[0] row g, cl[2] row g+8 (odd columns are fed zeros)
-    uint2 bsup[NH], bsupl[NH];
+    constexpr bool INT_SCALE = TYPE == T_Q4_K || TYPE == T_Q2_K || TYPE == T_IQ2_XXS;
+    const uint32_t G0 = 8 * U;
+    int c[NH][4];           // MMA accumulators: c[0], c[1] = columns 2t, 2t+1 of row g; c[2], c[3] of row g+8
+    int isum[NH][2][2];     // integer-scaled column sums over the unit (INT_SCALE formats)
+    float fsum[NH][2][2];   // float-scaled column sums over the unit (other formats)
+    uint2 bsup[NH];
+#pragma unroll
+    for (int h = 0; h < NH; ++h)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) isum[h][j][0] = isum[h][j][1] = 0, fsum[h][j][0] = fsum[h][j][1] = 0.0f;
 
-    // B fragment of the chain that starts at group Gc: the lane supplies column g for chain position sup_p.
-    auto load_b = [&](uint32_t Gc) {
+    // B fragment for the chain starting at group Gc (index inside the unit): this lane's column, 8 bytes
+    // of its plane (4 bytes at byte offset `off16` for the 16-value groups of Q2_K).
+    auto load_b = [&](uint32_t Gc, uint32_t off16, bool k16) {
 #pragma unroll
         for (int h = 0; h < NH; ++h) {
-            uint64_t idx = ((uint64_t)ro.sup_row[h] * act.n_groups + (G0 + Gc + ro.sup_p)) * 96 + 8 * ro.t;
-            bsup[h] = __ldg(reinterpret_cast<const uint2*>(act.planes + idx + 32 * ro.sup_odd));
-            bsupl[h] = ro.sup_odd ? make_uint2(0u, 0u) : __ldg(reinterpret_cast<const uint2*>(act.planes + idx + 64));
+            const int8_t* src = act.planes + ro.sup_off[h] + (uint64_t)(G0 + Gc) * 96;
+            if (!ro.sup_live) {
+                bsup[h] = make_uint2(0u, 0u);
+            } else if (k16) {
+                bsup[h].x = ld_act<ACT>(reinterpret_cast<const uint32_t*>(src + off16 - 4 * ro.t));
+                bsup[h].y = 0u;
+            } else {
+                bsup[h] = ld_act<ACT>(reinterpret_cast<const uint2*>(src));
+            }
         }
     };
-    // Scale the finished chain that started at group Gc: s0 / s1 multiply the integer dots of rows g / g+8,
-    // o0 / o1 multiply the group's sum of x.
-    auto finish = [&](uint32_t Gc, float s0, float s1, float o0, float o1) {
+    auto zero_c = [&]() {
 #pragma unroll
-        for (int h = 0; h < NH; ++h) {
-            float2 mt = __ldg(act.meta + (uint64_t)ro.fin_row[h] * act.n_groups + (G0 + Gc + ro.fin_p));
-            float i0 = fmaf((float)c[h][0], 64516.0f, (float)(c[h][1] * 254 + cl[h][0])) * mt.x;
-            float i1 = fmaf((float)c[h][2], 64516.0f, (float)(c[h][3] * 254 + cl[h][2])) * mt.x;
-            acc[h][0] = fmaf(s0, i0, fmaf(-o0, mt.y, acc[h][0]));
-            acc[h][1] = fmaf(s1, i1, fmaf(-o1, mt.y, acc[h][1]));
-        }
+        for (int h = 0; h < NH; ++h) c[h][0] = c[h][1] = c[h][2] = c[h][3] = 0;
     };
-    auto step = [&](int G, const uint32_t a[4]) {
-        const int p = G % CH;
-        if (p == 0) {
-            load_b(G);
-#pragma unroll
-            for (int h = 0; h < NH; ++h)
-                c[h][0] = c[h][1] = c[h][2] = c[h][3] = cl[h][0] = cl[h][1] = cl[h][2] = cl[h][3] = 0;
-        }
+    auto mma_step = [&](int p, const uint32_t a[4], bool a_unsigned) {
 #pragma unroll
         for (int h = 0; h < NH; ++h) {
             bool mine = ro.sup_p == p;
-            mma_k32(c[h], a, mine ? bsup[h].x : 0u, mine ? bsup[h].y : 0u);
-            mma_k32(cl[h], a, mine ? bsupl[h].x : 0u, mine ? bsupl[h].y : 0u);
+            if (a_unsigned)
+                mma_k32_u8(c[h], a, mine ? bsup[h].x : 0u, mine ? bsup[h].y : 0u);
+            else
+                mma_k32(c[h], a, mine ? bsup[h].x : 0u, mine ? bsup[h].y : 0u);
         }
+    };
+    // After a chain: fold the accumulators into the unit sums.  sc[j][r] is the scale of the group that held
+    // column j belongs to, for row r.
+    auto fold_int = [&](const uint32_t sc[2][2]) {
+#pragma unroll
+        for (int h = 0; h < NH; ++h)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                isum[h][j][0] += c[h][j] * (int)sc[j][0];
+                isum[h][j][1] += c[h][2 + j] * (int)sc[j][1];
+            }
+    };
+    auto fold_float = [&](const float sc[2][2]) {
+#pragma unroll
+        for (int h = 0; h < NH; ++h)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                fsum[h][j][0] = fmaf((float)c[h][j], sc[j][0], fsum[h][j][0]);
+                fsum[h][j][1] = fmaf((float)c[h][2 + j], sc[j][1], fsum[h][j][1]);
+            }
+    };
+    // Unit end: unit sums -> running column sums.  f0 / f1: the unit's float factor for rows g / g+8.
+    auto close_unit = [&](float f0, float f1) {
+#pragma unroll
+        for (int h = 0; h < NH; ++h)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                // activation scale of the batch row this column belongs to (one per 256-value unit)
+                uint32_t row = (uint32_t)min((uint64_t)(h * MB + ro.col_i[j]), (uint64_t)ro.min_row[MB * NH - 1]);
+                float sa = ld_act<ACT>(&act.meta[(uint64_t)row * act.n_groups + G0].x) * ro.col_w[j];
+                float v0 = INT_SCALE ? (float)isum[h][j][0] : fsum[h][j][0];
+                float v1 = INT_SCALE ? (float)isum[h][j][1] : fsum[h][j][1];
+                colacc[h][j][0] = fmaf(f0 * sa, v0, colacc[h][j][0]);
+                colacc[h][j][1] = fmaf(f1 * sa, v1, colacc[h][j][1]);
+            }
     };
 
     if constexpr (TYPE == T_Q4_K) {
         const uint4 h0 = lds128(u0), h1 = lds128(u1);
+        // The 8 six-bit scales and 8 minima of a row as two words of 4 bytes each (src/kquant_dot.rs:106-118):
+        // pairs 0..3 are the low 6 bits of bytes 0..3 / 4..7; pairs 4..7 take their low nibble from bytes
+        // 8..11 (scale: low nibble, minimum: high nibble) and bits 4..5 from the top of bytes 0..3 / 4..7.
+        const uint32_t sc0[2] = {h0.y & 0x3F3F3F3Fu, (h0.w & 0x0F0F0F0Fu) | ((h0.y >> 2) & 0x30303030u)};
+        const uint32_t sc1[2] = {h1.y & 0x3F3F3F3Fu, (h1.w & 0x0F0F0F0Fu) | ((h1.y >> 2) & 0x30303030u)};
+        const uint32_t mn0[2] = {h0.z & 0x3F3F3F3Fu, ((h0.w >> 4) & 0x0F0F0F0Fu) | ((h0.z >> 2) & 0x30303030u)};
+        const uint32_t mn1[2] = {h1.z & 0x3F3F3F3Fu, ((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u)};
+        // chunk cc = 64 values: low nibbles are group 2cc, high nibbles group 2cc+1.  High nibbles stay in
+        // place (16*q as an unsigned byte).  With two groups per chain a held column always sees groups of
+        // one parity, so the factor 16 sits in its column weight; otherwise even groups take 16*sc and the
+        // unit factor carries 1/16.
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
             uint2 q0 = lds64(u0 + 16 + 32 * cc + 8 * ro.t), q1 = lds64(u1 + 16 + 32 * cc + 8 * ro.t);
 #pragma unroll
             for (int nib = 0; nib < 2; ++nib) {
-                const int G = 2 * cc + nib;
-                uint32_t a[4] = {(q0.x >> (4 * nib)) & 0x0F0F0F0Fu, (q1.x >> (4 * nib)) & 0x0F0F0F0Fu,
-                                 (q0.y >> (4 * nib)) & 0x0F0F0F0Fu, (q1.y >> (4 * nib)) & 0x0F0F0F0Fu};
-                step(G, a);
-                if (G % CH == CH - 1) {
-                    const int Gc = G - (CH - 1);
-                    float d0, m0, d1, m1;
-                    q4k_pair(h0, Gc >= 4, (Gc & 3) + ro.fin_p, &d0, &m0);
-                    q4k_pair(h1, Gc >= 4, (Gc & 3) + ro.fin_p, &d1, &m1);
-                    finish(Gc, d0, d1, m0, m1);
+                const int G = 2 * cc + nib, p = G % CH;
+                if (p == 0) {
+                    load_b(G, 0, false);
+                    zero_c();
+                }
+                const uint32_t mask = nib ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
+                uint32_t a[4] = {q0.x & mask, q1.x & mask, q0.y & mask, q1.y & mask};
+                mma_step(p, a, true);
+                if (p == CH - 1) {
+                    uint32_t sc[2][2];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        // group of held column j: G - (CH-1) + col_p[j]; its byte inside the half-word
+                        const int Gc = G - (CH - 1);
+                        const uint32_t sh = 8 * ((Gc & 3) + ro.col_p[j]);
+                        sc[j][0] = (sc0[Gc >> 2] >> sh) & 0xFF;
+                        sc[j][1] = (sc1[Gc >> 2] >> sh) & 0xFF;
+                        if (CH == 1 && (G & 1) == 0) sc[j][0] <<= 4, sc[j][1] <<= 4;
+                    }
+                    fold_int(sc);
                 }
             }
         }
+        // minima: lane t takes pairs 2t and 2t+1 of both rows
+        const float dm0 = f16_bits_to_f32(h0.x >> 16), dm1 = f16_bits_to_f32(h1.x >> 16);
+        const uint32_t mw0 = ro.t < 2 ? mn0[0] : mn0[1], mw1 = ro.t < 2 ? mn1[0] : mn1[1];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const uint32_t sh = 8 * (2 * (ro.t & 1) + e);
+            float m0 = (float)((mw0 >> sh) & 0xFF) * dm0, m1 = (float)((mw1 >> sh) & 0xFF) * dm1;
+#pragma unroll
+            for (int b = 0; b < MB * NH; ++b) {
+                float sx = ld_act<ACT>(&act.meta[(uint64_t)ro.min_row[b] * act.n_groups + G0 + 2 * ro.t + e].y);
+                minacc[b][0] = fmaf(m0, sx, minacc[b][0]);
+                minacc[b][1] = fmaf(m1, sx, minacc[b][1]);
+            }
+        }
+        const float fu = CH == 1 ? 0.0625f : 1.0f;
+        close_unit(f16_bits_to_f32(h0.x & 0xFFFF) * fu, f16_bits_to_f32(h1.x & 0xFFFF) * fu);
     } else if constexpr (TYPE == T_Q8_0) {
 #pragma unroll
         for (int G = 0; G < 8; ++G) {
+            const int p = G % CH;
+            if (p == 0) {
+                load_b(G, 0, false);
+                zero_c();
+            }
             uint2 q0, q1;
             if (G % 2 == 0) {  // 34*G + 2 is 2 mod 4
                 q0 = lds64_mis<2>(u0 + 34 * G + 2 + 8 * ro.t);
@@ -336,24 +447,33 @@ __device__ __forceinline__ void process_unit(const uint8_t* u0, const uint8_t* u
                 q1 = lds64_mis<0>(u1 + 34 * G + 2 + 8 * ro.t);
             }
             uint32_t a[4] = {q0.x, q1.x, q0.y, q1.y};
-            step(G, a);
-            if (G % CH == CH - 1) {
-                const int Gc = G - (CH - 1);
-                float d0 = f16_bits_to_f32(lds16(u0 + 34 * (Gc + ro.fin_p)));
-                float d1 = f16_bits_to_f32(lds16(u1 + 34 * (Gc + ro.fin_p)));
-                finish(Gc, d0, d1, 0.0f, 0.0f);
+            mma_step(p, a, false);
+            if (p == CH - 1) {
+                float sc[2][2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    uint32_t Gj = G - (CH - 1) + ro.col_p[j];
+                    sc[j][0] = f16_bits_to_f32(lds16(u0 + 34 * Gj));
+                    sc[j][1] = f16_bits_to_f32(lds16(u1 + 34 * Gj));
+                }
+                fold_float(sc);
             }
         }
+        close_unit(1.0f, 1.0f);
     } else if constexpr (TYPE == T_IQ2_XXS) {
         // The block is 2-byte aligned; its 8-byte groups start at +2, so whether they are word aligned depends
         // on the block's position.  Read three aligned words and shift.
-        const float d0 = f16_bits_to_f32(lds16(u0)), d1 = f16_bits_to_f32(lds16(u1));
         const uint32_t s0 = 8 * (uint32_t)(reinterpret_cast<uintptr_t>(u0 + 2) & 3);
         const uint32_t s1 = 8 * (uint32_t)(reinterpret_cast<uintptr_t>(u1 + 2) & 3);
         const uint8_t* a0 = u0 + 2 - (s0 >> 3);
         const uint8_t* a1 = u1 + 2 - (s1 >> 3);
 #pragma unroll
         for (int G = 0; G < 8; ++G) {
+            const int p = G % CH;
+            if (p == 0) {
+                load_b(G, 0, false);
+                zero_c();
+            }
             // group bytes: 4 grid codes, then a word of 4 x 7 sign bits + 4-bit scale
             uint32_t x0 = lds32(a0 + 8 * G), x1 = lds32(a0 + 8 * G + 4), x2 = lds32(a0 + 8 * G + 8);
             uint32_t y0 = lds32(a1 + 8 * G), y1 = lds32(a1 + 8 * G + 4), y2 = lds32(a1 + 8 * G + 8);
@@ -364,16 +484,20 @@ __device__ __forceinline__ void process_unit(const uint8_t* u0, const uint8_t* u
             // negate the bytes under the mask: (v ^ 0xFF) + 1; grid bytes are never 0, so no carry leaves a byte
             uint32_t a[4] = {(g0.x ^ k0.x) + (k0.x & 0x01010101u), (g1.x ^ k1.x) + (k1.x & 0x01010101u),
                              (g0.y ^ k0.y) + (k0.y & 0x01010101u), (g1.y ^ k1.y) + (k1.y & 0x01010101u)};
-            step(G, a);
-            if (G % CH == CH - 1) {
-                const int Gc = G - (CH - 1);
-                // 4-bit scale of the finaliser's own group: top nibble of that group's last byte
-                uint32_t b0 = u0[2 + 8 * (Gc + ro.fin_p) + 7] >> 4, b1 = u1[2 + 8 * (Gc + ro.fin_p) + 7] >> 4;
-                float db0 = __fmul_rn(__fmul_rn(d0, __fadd_rn(0.5f, (float)b0)), 0.25f);
-                float db1 = __fmul_rn(__fmul_rn(d1, __fadd_rn(0.5f, (float)b1)), 0.25f);
-                finish(Gc, db0, db1, 0.0f, 0.0f);
+            mma_step(p, a, false);
+            if (p == CH - 1) {
+                // group scale (0.5 + s4) * 0.25 = (2*s4 + 1) / 8: the integer part here, 1/8 in the unit factor
+                uint32_t sc[2][2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    uint32_t Gj = G - (CH - 1) + ro.col_p[j];
+                    sc[j][0] = 2 * (u0[2 + 8 * Gj + 7] >> 4) + 1;
+                    sc[j][1] = 2 * (u1[2 + 8 * Gj + 7] >> 4) + 1;
+                }
+                fold_int(sc);
             }
         }
+        close_unit(f16_bits_to_f32(lds16(u0)) * 0.125f, f16_bits_to_f32(lds16(u1)) * 0.125f);
     } else if constexpr (TYPE == T_MXFP4) {
         // codes -> twice the E2M1 value by byte-permute lookups; sign picks between a positive and a negated table
         const uint32_t P0 = 0x03020100u, P1 = 0x0C080604u, N0 = 0xFDFEFF00u, N1 = 0xF4F8FAFCu;
@@ -382,8 +506,18 @@ __device__ __forceinline__ void process_unit(const uint8_t* u0, const uint8_t* u
             uint32_t sm = prmt(w, w4, sign_sel);  // 0xFF where the nibble's sign bit is set
             return (pos & ~sm) | (neg & sm);
         };
+        // codes are doubled, so a block's scale is 2^(e-128); e = 255 zeroes the block, e <= 1 is subnormal
+        auto block_scale = [&](uint32_t e) {
+            return e == 255 ? 0.0f
+                            : __uint_as_float(e > 1 ? (e - 1) << 23 : (e == 1 ? 0x00400000u : 0x00200000u));
+        };
 #pragma unroll
         for (int G = 0; G < 8; ++G) {
+            const int p = G % CH;
+            if (p == 0) {
+                load_b(G, 0, false);
+                zero_c();
+            }
             const int mis = (17 * G + 1) & 3;  // the unit is 4-byte aligned
             const uint8_t* p0 = u0 + 17 * G + 1 + 4 * ro.t - mis;
             const uint8_t* p1 = u1 + 17 * G + 1 + 4 * ro.t - mis;
@@ -395,22 +529,23 @@ __device__ __forceinline__ void process_unit(const uint8_t* u0, const uint8_t* u
             uint32_t m0 = w0 & 0x77777777u, m1 = w1 & 0x77777777u;
             uint32_t a[4] = {decode4(w0, w0 << 4, m0, 0x9D8Cu), decode4(w1, w1 << 4, m1, 0x9D8Cu),
                              decode4(w0, w0 << 4, m0 >> 16, 0xBFAEu), decode4(w1, w1 << 4, m1 >> 16, 0xBFAEu)};
-            step(G, a);
-            if (G % CH == CH - 1) {
-                const int Gc = G - (CH - 1);
-                uint32_t e0 = u0[17 * (Gc + ro.fin_p)], e1 = u1[17 * (Gc + ro.fin_p)];
-                // codes are doubled, so the scale is 2^(e-128); e = 255 zeroes the block, e <= 1 is subnormal
-                float sc0 = e0 == 255 ? 0.0f : __uint_as_float(e0 > 1 ? (e0 - 1) << 23 : (e0 == 1 ? 0x00400000u : 0x00200000u));
-                float sc1 = e1 == 255 ? 0.0f : __uint_as_float(e1 > 1 ? (e1 - 1) << 23 : (e1 == 1 ? 0x00400000u : 0x00200000u));
-                finish(Gc, sc0, sc1, 0.0f, 0.0f);
+            mma_step(p, a, false);
+            if (p == CH - 1) {
+                float sc[2][2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    uint32_t Gj = G - (CH - 1) + ro.col_p[j];
+                    sc[j][0] = block_scale(u0[17 * Gj]);
+                    sc[j][1] = block_scale(u1[17 * Gj]);
+                }
+                fold_float(sc);
             }
         }
+        close_unit(1.0f, 1.0f);
     } else if constexpr (TYPE == T_Q2_K) {
         // 16 groups of 16 values; word (sg, hf) of the 2-bit fields holds groups j = 2i + hf (shift 2i) of
         // super-group sg, which chain naturally.  m16n8k16: one A register per row, one B register.
         const uint32_t dd0 = lds32(u0 + 80), dd1 = lds32(u1 + 80);
-        const float d0 = f16_bits_to_f32(dd0 & 0xFFFF), dm0 = f16_bits_to_f32(dd0 >> 16);
-        const float d1 = f16_bits_to_f32(dd1 & 0xFFFF), dm1 = f16_bits_to_f32(dd1 >> 16);
 #pragma unroll
         for (int sg = 0; sg < 2; ++sg) {
 #pragma unroll
@@ -420,168 +555,268 @@ __device__ __forceinline__ void process_unit(const uint8_t* u0, const uint8_t* u
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int p = i % CH;
-                    const int j = 2 * i + hf;                  // 16-group inside the super-group
-                    const uint32_t G32 = 4 * sg + (j >> 1);    // its 32-group inside the unit (half = hf)
+                    // 16-group j = 2i + hf of the super-group lives in 32-group 4sg + i (half hf) of the unit
                     if (p == 0) {
-#pragma unroll
-                        for (int h = 0; h < NH; ++h) {
-                            // chain positions are groups j = 2(i + sup_p) + hf -> 32-group 4sg + i + sup_p
-                            uint64_t idx = ((uint64_t)ro.sup_row[h] * act.n_groups + (G0 + G32 + ro.sup_p)) * 96 +
-                                           16 * hf + 4 * ro.t;
-                            bsup[h].x = __ldg(reinterpret_cast<const uint32_t*>(act.planes + idx + 32 * ro.sup_odd));
-                            bsupl[h].x = ro.sup_odd ? 0u : __ldg(reinterpret_cast<const uint32_t*>(act.planes + idx + 64));
-                            c[h][0] = c[h][1] = c[h][2] = c[h][3] = cl[h][0] = cl[h][1] = cl[h][2] = cl[h][3] = 0;
-                        }
+                        load_b(4 * sg + i, 16 * hf, true);
+                        zero_c();
                     }
                     uint32_t a0 = (q0 >> (2 * i)) & 0x03030303u, a1 = (q1 >> (2 * i)) & 0x03030303u;
 #pragma unroll
-                    for (int h = 0; h < NH; ++h) {
-                        mma_k16(c[h], a0, a1, ro.sup_p == p ? bsup[h].x : 0u);
-                        mma_k16(cl[h], a0, a1, ro.sup_p == p ? bsupl[h].x : 0u);
-                    }
+                    for (int h = 0; h < NH; ++h) mma_k16(c[h], a0, a1, ro.sup_p == p ? bsup[h].x : 0u);
                     if (p == CH - 1) {
-                        const int ic = i - (CH - 1);  // first group of the chain
-                        const uint32_t jm = 2 * (ic + ro.fin_p) + hf;
-                        uint32_t sc0 = u0[8 * sg + jm], sc1 = u1[8 * sg + jm];
-                        float s0 = __fmul_rn(d0, (float)(sc0 & 15)), o0 = __fmul_rn(dm0, (float)(sc0 >> 4));
-                        float s1 = __fmul_rn(d1, (float)(sc1 & 15)), o1 = __fmul_rn(dm1, (float)(sc1 >> 4));
-                        const uint32_t Gm = G0 + 4 * sg + ic + ro.fin_p;
+                        uint32_t sc[2][2];
 #pragma unroll
-                        for (int h = 0; h < NH; ++h) {
-                            uint64_t mi = (uint64_t)ro.fin_row[h] * act.n_groups + Gm;
-                            float sa = __ldg(&act.meta[mi].x);
-                            float sx = __ldg(act.sum16 + mi * 2 + hf);
-                            float i0 = fmaf((float)c[h][0], 64516.0f, (float)(c[h][1] * 254 + cl[h][0])) * sa;
-                            float i1 = fmaf((float)c[h][2], 64516.0f, (float)(c[h][3] * 254 + cl[h][2])) * sa;
-                            acc[h][0] = fmaf(s0, i0, fmaf(-o0, sx, acc[h][0]));
-                            acc[h][1] = fmaf(s1, i1, fmaf(-o1, sx, acc[h][1]));
+                        for (int j = 0; j < 2; ++j) {
+                            uint32_t ij = i - (CH - 1) + ro.col_p[j];
+                            sc[j][0] = u0[8 * sg + 2 * ij + hf] & 15;
+                            sc[j][1] = u1[8 * sg + 2 * ij + hf] & 15;
                         }
+                        fold_int(sc);
                     }
                 }
             }
         }
+        // minima: lane t takes 16-groups 4t .. 4t+3 of both rows
+        const float dm0 = f16_bits_to_f32(dd0 >> 16), dm1 = f16_bits_to_f32(dd1 >> 16);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            uint32_t j16 = 4 * ro.t + e;  // 16-group of the unit; its 32-group is j16 / 2, half j16 & 1
+            // scale byte of 16-group j16: super-group j16 / 8, group (j16 % 8) -> scales[j16]
+            // value order inside a super-group is group-major, so 16-group j16 of the unit is scales[j16]
+            float m0 = (float)(u0[j16] >> 4) * dm0, m1 = (float)(u1[j16] >> 4) * dm1;
+#pragma unroll
+            for (int b = 0; b < MB * NH; ++b) {
+                float sx = ld_act<ACT>(act.sum16 + ((uint64_t)ro.min_row[b] * act.n_groups + G0) * 2 + j16);
+                minacc[b][0] = fmaf(m0, sx, minacc[b][0]);
+                minacc[b][1] = fmaf(m1, sx, minacc[b][1]);
+            }
+        }
+        close_unit(f16_bits_to_f32(dd0 & 0xFFFF), f16_bits_to_f32(dd1 & 0xFFFF));
     }
 }
 
 // ────────────────────────────── the kernel ────────────────────────────────
+//
+// Persistent: one CTA per SM walks row tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Warp 0 produces
+// (bulk copies into a ring of NS stages, each 16 rows x one K-chunk), warps 1..NCW consume (each takes
+// every NCW-th unit of the chunk and keeps its partial sums in registers across the tile's chunks),
+// warp NCW+1 reduces (adds the consumers' partial sums of a finished tile in a fixed order and stores
+// dst) so that consumers move on to the next tile without waiting.  The activation planes of the whole
+// product are copied to shared memory once per CTA when they fit.
 
-template <uint32_t TYPE, int MB, int NH, int NWARP>
-__global__ void __launch_bounds__(NWARP * 32)
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+struct SmemPlan {
+    uint32_t row_stride;   // bytes between rows of a stage
+    uint32_t n_stages;     // ring depth
+    uint32_t act_bytes;    // activation region (0 = read activations from global memory)
+    uint32_t total;        // dynamic shared memory of the launch
+};
+
+template <uint32_t TYPE, int MB, int NH, int NCW, int ACT>
+__global__ void __launch_bounds__((NCW + 2) * 32, 1)
     gemv_mma_kernel(const uint8_t* __restrict__ w, uint64_t n, uint64_t k, ActPlanes act, uint64_t m,
-                    float* __restrict__ dst, uint32_t row_stride, int* __restrict__ error_flag) {
+                    float* __restrict__ dst, SmemPlan plan, int* __restrict__ error_flag) {
     using Tr = Traits<TYPE>;
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: [2 stages][ROWS][row_stride] | grid table (IQ2_XXS) | reduction buffer | mbarriers
-    const uint32_t stage_bytes = ROWS * row_stride;
-    uint8_t* stages = smem;
-    uint2* s_grid = reinterpret_cast<uint2*>(smem + 2 * stage_bytes);
+    constexpr int NB = MB * NH;                       // batch rows covered
+    constexpr uint32_t RED_FLOATS = NCW * NB * ROWS;  // one reduction buffer
+    const uint32_t stage_bytes = ROWS * plan.row_stride;
+    // layout: activation region | ring | tables (IQ2_XXS) | 2 reduction buffers | mbarriers
+    uint8_t* s_act = smem;
+    uint8_t* ring = smem + plan.act_bytes;
+    uint2* s_grid = reinterpret_cast<uint2*>(ring + plan.n_stages * stage_bytes);
     uint2* s_mask = s_grid + (TYPE == T_IQ2_XXS ? 256 : 0);
     float* s_red = reinterpret_cast<float*>(s_mask + (TYPE == T_IQ2_XXS ? 128 : 0));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_red + NWARP * ROWS * 4 * NH);
+    uint64_t* full = reinterpret_cast<uint64_t*>(s_red + 2 * RED_FLOATS);
+    uint64_t* empty = full + plan.n_stages;
+    uint64_t* red_full = empty + plan.n_stages;
+    uint64_t* red_empty = red_full + 2;
+    uint64_t* act_bar = red_empty + 2;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const Roles<MB, NH> ro(lane, m);
-    const uint64_t row0 = (uint64_t)blockIdx.x * ROWS;
+    const uint32_t NS = plan.n_stages;
+    const uint64_t n_tiles = (n + ROWS - 1) / ROWS;
     const uint32_t units_per_row = (uint32_t)(k / 256);
     const uint64_t row_bytes = (uint64_t)units_per_row * Tr::UNIT_BYTES;
     const uint32_t n_chunks = (units_per_row + Tr::CHUNK_UNITS - 1) / Tr::CHUNK_UNITS;
 
     if (tid == 0) {
-        mbar_init(&bars[0], ROWS);
-        mbar_init(&bars[1], ROWS);
+        for (uint32_t s = 0; s < NS; ++s) {
+            mbar_init(&full[s], ROWS);
+            mbar_init(&empty[s], NCW);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&red_full[b], NCW);
+            mbar_init(&red_empty[b], 1);
+        }
+        mbar_init(act_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (TYPE == T_IQ2_XXS) {
-        for (int i = tid; i < 256; i += NWARP * 32) s_grid[i] = g_iq2xxs_grid[i];
-        for (int i = tid; i < 128; i += NWARP * 32) {
+        for (int i = tid; i < 256; i += (NCW + 2) * 32) s_grid[i] = g_iq2xxs_grid[i];
+        for (int i = tid; i < 128; i += (NCW + 2) * 32) {
             uint32_t sg = iq2_signs(i);
             uint32_t lo = ((sg & 0xF) * 0x00204081u) & 0x01010101u, hi = ((sg >> 4) * 0x00204081u) & 0x01010101u;
             s_mask[i] = make_uint2(lo * 0xFFu, hi * 0xFFu);
         }
     }
     __syncthreads();
+    // From here on the three roles only meet through mbarriers.  Every wait is bounded; a role whose wait
+    // runs out raises the error flag and leaves, and the roles that depend on it run out in turn.
 
-    // Row r of the tile, chunk c: copy the 16-byte aligned span that covers its bytes.
-    auto issue = [&](uint32_t chunk) {
-        if (warp == 0 && lane < ROWS) {
-            uint64_t row = row0 + lane < n ? row0 + lane : n - 1;
-            uint32_t u_lo = chunk * Tr::CHUNK_UNITS;
-            uint32_t u_hi = min(units_per_row, u_lo + Tr::CHUNK_UNITS);
-            uintptr_t beg = reinterpret_cast<uintptr_t>(w) + row * row_bytes + (uint64_t)u_lo * Tr::UNIT_BYTES;
-            uintptr_t end = beg + (uint64_t)(u_hi - u_lo) * Tr::UNIT_BYTES;
-            uintptr_t abeg = beg & ~(uintptr_t)15, aend = (end + 15) & ~(uintptr_t)15;
-            uint32_t bytes = (uint32_t)(aend - abeg);
-            uint64_t* bar = &bars[chunk & 1];
-            mbar_arrive_expect_tx(bar, bytes);
-            bulk_g2s(stages + (chunk & 1) * stage_bytes + lane * row_stride, reinterpret_cast<const void*>(abeg),
-                     bytes, bar);
+    pdl_trigger();
+    if (warp == 0) {
+        // ── producer ──  The weights never change, so their copies start at once; only the activation
+        // copy has to wait for the kernel that produced the planes.
+        if (ACT && lane == ROWS) {
+            pdl_wait();
+            // planes, meta and 16-value sums are one contiguous region of the scratch buffer
+            mbar_arrive_expect_tx(act_bar, plan.act_bytes);
+            for (uint32_t off = 0; off < plan.act_bytes; off += 32768) {
+                uint32_t bytes = min(32768u, plan.act_bytes - off);
+                bulk_g2s(s_act + off, reinterpret_cast<const uint8_t*>(act.planes) + off, bytes, act_bar);
+            }
         }
-    };
-
-    float acc[NH][2];
-#pragma unroll
-    for (int h = 0; h < NH; ++h) acc[h][0] = acc[h][1] = 0.0f;
-
-    issue(0);
-    if (n_chunks > 1) issue(1);
-
-    // byte offset of the row's first unit inside its aligned span
-    auto row_shift = [&](int r) -> uint32_t {
-        uint64_t row = row0 + r < n ? row0 + r : n - 1;
-        return (uint32_t)((reinterpret_cast<uintptr_t>(w) + row * row_bytes) & 15);
-    };
-    // chunk starts are multiples of CHUNK_UNITS * UNIT_BYTES, a multiple of 16 for every format,
-    // so the shift is the same for every chunk of a row
-    const uint32_t sh0 = row_shift(ro.g), sh1 = row_shift(ro.g + 8);
-
-    for (uint32_t chunk = 0; chunk < n_chunks; ++chunk) {
-        bool ok = mbar_wait(&bars[chunk & 1], (chunk >> 1) & 1);
-        if (!__syncthreads_and(ok)) {
-            if (tid == 0) *reinterpret_cast<volatile int*>(error_flag) = 1;
-            return;
+        if (lane < ROWS) {
+            uint32_t job = 0;
+            for (uint64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                uint64_t row = tile * ROWS + lane < n ? tile * ROWS + lane : n - 1;
+                for (uint32_t chunk = 0; chunk < n_chunks; ++chunk, ++job) {
+                    uint32_t s = job % NS, round = job / NS;
+                    if (!mbar_wait(&empty[s], (round & 1) ^ 1)) {
+                        *reinterpret_cast<volatile int*>(error_flag) = 1;
+                        return;
+                    }
+                    uint32_t u_lo = chunk * Tr::CHUNK_UNITS;
+                    uint32_t u_hi = min(units_per_row, u_lo + Tr::CHUNK_UNITS);
+                    uintptr_t beg = reinterpret_cast<uintptr_t>(w) + row * row_bytes + (uint64_t)u_lo * Tr::UNIT_BYTES;
+                    uintptr_t end = beg + (uint64_t)(u_hi - u_lo) * Tr::UNIT_BYTES;
+                    uintptr_t abeg = beg & ~(uintptr_t)15, aend = (end + 15) & ~(uintptr_t)15;
+                    uint32_t bytes = (uint32_t)(aend - abeg);
+                    mbar_arrive_expect_tx(&full[s], bytes);
+                    bulk_g2s(ring + s * stage_bytes + lane * plan.row_stride, reinterpret_cast<const void*>(abeg),
+                             bytes, &full[s]);
+                }
+            }
         }
-        const uint8_t* st = stages + (chunk & 1) * stage_bytes;
-        const uint32_t u_lo = chunk * Tr::CHUNK_UNITS;
-        const uint32_t cnt = min(units_per_row - u_lo, Tr::CHUNK_UNITS);
-        for (uint32_t u = warp; u < cnt; u += NWARP) {
-            const uint8_t* u0 = st + ro.g * row_stride + sh0 + u * Tr::UNIT_BYTES;
-            const uint8_t* u1 = st + (ro.g + 8) * row_stride + sh1 + u * Tr::UNIT_BYTES;
-            process_unit<TYPE, MB, NH>(u0, u1, (u_lo + u) * 8, act, ro, s_grid, s_mask, acc);
+    } else if (warp <= NCW) {
+        // ── consumers ──
+        const int cw = warp - 1;
+        Roles<MB, NH> ro(lane, m);
+#pragma unroll
+        for (int h = 0; h < NH; ++h)
+            ro.sup_off[h] = ro.sup_live ? (uint32_t)(((uint64_t)ro.sup_row[h] * act.n_groups + ro.sup_p) * 96 +
+                                                     32 * ro.sup_plane + 8 * ro.t)
+                                        : 0u;
+        if (TYPE == T_Q4_K && MB == 1) {
+            // two groups per chain: held column j only ever sees odd (high-nibble, 16x) or even groups
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+                if (ro.col_p[j] & 1) ro.col_w[j] *= 0.0625f;
         }
-        __syncthreads();  // every warp is done with this stage
-        if (chunk + 2 < n_chunks) issue(chunk + 2);
-    }
-
-    // Sum the chain positions that share a batch row, then the warps, in a fixed order.
-#pragma unroll
-    for (int h = 0; h < NH; ++h)
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            float v = acc[h][r];
-            if (MB == 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
-            if (MB <= 2) v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
-            acc[h][r] = v;
+        ActPlanes a = act;
+        if (!ACT) pdl_wait();
+        if (ACT) {
+            uint64_t groups = m * (uint64_t)act.n_groups;
+            a.planes = reinterpret_cast<const int8_t*>(s_act);
+            a.meta = reinterpret_cast<const float2*>(s_act + groups * 96);
+            a.sum16 = reinterpret_cast<const float*>(s_act + groups * 104);
+            if (!mbar_wait(act_bar, 0)) {
+                if (lane == 0) *reinterpret_cast<volatile int*>(error_flag) = 1;
+                return;
+            }
         }
-    if (ro.t < MB) {
+        float colacc[NH][2][2], minacc[NB][2];
+        uint32_t job = 0, tile_it = 0;
+        for (uint64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_it) {
 #pragma unroll
-        for (int h = 0; h < NH; ++h) {
-            s_red[((warp * NH + h) * 4 + ro.t) * ROWS + ro.g] = acc[h][0];
-            s_red[((warp * NH + h) * 4 + ro.t) * ROWS + ro.g + 8] = acc[h][1];
+            for (int h = 0; h < NH; ++h)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) colacc[h][j][0] = colacc[h][j][1] = 0.0f;
+#pragma unroll
+            for (int b = 0; b < NB; ++b) minacc[b][0] = minacc[b][1] = 0.0f;
+            const uint64_t row0 = tile * ROWS;
+            // byte offset of a row's first unit inside its 16-byte aligned span (the same for every chunk:
+            // chunk starts are multiples of 16 bytes for every format)
+            auto row_shift = [&](int r) -> uint32_t {
+                uint64_t row = row0 + r < n ? row0 + r : n - 1;
+                return (uint32_t)((reinterpret_cast<uintptr_t>(w) + row * row_bytes) & 15);
+            };
+            const uint32_t sh0 = row_shift(ro.g), sh1 = row_shift(ro.g + 8);
+            for (uint32_t chunk = 0; chunk < n_chunks; ++chunk, ++job) {
+                uint32_t s = job % NS, round = job / NS;
+                if (!mbar_wait(&full[s], round & 1)) {
+                    if (lane == 0) *reinterpret_cast<volatile int*>(error_flag) = 1;
+                    return;
+                }
+                const uint8_t* st = ring + s * stage_bytes;
+                const uint32_t u_lo = chunk * Tr::CHUNK_UNITS;
+                const uint32_t cnt = min(units_per_row - u_lo, Tr::CHUNK_UNITS);
+                for (uint32_t u = cw; u < cnt; u += NCW) {
+                    const uint8_t* u0 = st + ro.g * plan.row_stride + sh0 + u * Tr::UNIT_BYTES;
+                    const uint8_t* u1 = st + (ro.g + 8) * plan.row_stride + sh1 + u * Tr::UNIT_BYTES;
+                    process_unit<TYPE, MB, NH, ACT>(u0, u1, u_lo + u, a, ro, s_grid, s_mask, colacc, minacc);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+            }
+            // hand the tile's partial sums to the reducer: per batch row, the held columns that belong to
+            // it minus its minima terms, summed over the quad
+            const uint32_t rb = tile_it & 1;
+            if (!mbar_wait(&red_empty[rb], ((tile_it >> 1) & 1) ^ 1)) {
+                if (lane == 0) *reinterpret_cast<volatile int*>(error_flag) = 1;
+                return;
+            }
+            float* red = s_red + rb * RED_FLOATS;
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                const int h = b / MB, i = b % MB;
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    float v = -minacc[b][r];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) v += ro.col_i[j] == i ? colacc[h][j][r] : 0.0f;
+                    v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+                    v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
+                    if (ro.t == 0) red[(cw * NB + b) * ROWS + ro.g + 8 * r] = v;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&red_full[rb]);
         }
-    }
-    __syncthreads();
-    for (int o = tid; o < NH * MB * ROWS; o += NWARP * 32) {
-        int r = o % ROWS, bi = o / ROWS;  // bi = h * MB + i
-        int h = bi / MB, i = bi % MB;
-        uint64_t batch = (uint64_t)i + 4 * h;
-        if (batch < m && row0 + r < n) {
-            float v = 0.0f;
+    } else {
+        // ── reducer ──
+        pdl_wait();  // dst may still be read by the preceding kernel
+        uint32_t tile_it = 0;
+        for (uint64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_it) {
+            const uint32_t rb = tile_it & 1;
+            if (!mbar_wait(&red_full[rb], (tile_it >> 1) & 1)) {
+                if (lane == 0) *reinterpret_cast<volatile int*>(error_flag) = 1;
+                return;
+            }
+            const float* red = s_red + rb * RED_FLOATS;
+            const uint64_t row0 = tile * ROWS;
+            for (int o = lane; o < NB * ROWS; o += 32) {
+                int r = o % ROWS;
+                uint64_t batch = o / ROWS;
+                if (batch < m && row0 + r < n) {
+                    float v = 0.0f;
 #pragma unroll
-            for (int wv = 0; wv < NWARP; ++wv) v += s_red[((wv * NH + h) * 4 + i) * ROWS + r];
-            dst[batch * n + row0 + r] = v;
+                    for (int cwv = 0; cwv < NCW; ++cwv) v += red[(cwv * NB + (int)batch) * ROWS + r];
+                    dst[batch * n + row0 + r] = v;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&red_empty[rb]);
         }
     }
 }
+
+constexpr uint32_t SMEM_BUDGET = 220 * 1024;  // of the 227 KB a CTA may use
+constexpr uint32_t ACT_SMEM_MAX = 96 * 1024;
 
 template <uint32_t TYPE>
 uint32_t row_stride_for(uint64_t k) {
@@ -595,18 +830,77 @@ uint32_t row_stride_for(uint64_t k) {
     return (words + pad) * 4;
 }
 
+template <uint32_t TYPE, int NCW, int NB>
+SmemPlan plan_smem(uint64_t n, uint64_t k, uint64_t m, unsigned grid) {
+    using Tr = Traits<TYPE>;
+    SmemPlan p;
+    p.row_stride = row_stride_for<TYPE>(k);
+    uint32_t fixed = (TYPE == T_IQ2_XXS ? (256 + 128) * 8 : 0) + 2 * NCW * NB * ROWS * 4 + 8 * (2 * 8 + 5) + 128;
+    uint64_t act = m * (k / 32) * 112;
+    p.act_bytes = act <= ACT_SMEM_MAX ? (uint32_t)act : 0;
+    uint32_t stage = ROWS * p.row_stride;
+    uint32_t room = SMEM_BUDGET - fixed - p.act_bytes;
+    uint32_t n_chunks = (uint32_t)((k / 256 + Tr::CHUNK_UNITS - 1) / Tr::CHUNK_UNITS);
+    uint64_t jobs = ((n + ROWS - 1) / ROWS + grid - 1) / grid * n_chunks;  // per CTA
+    p.n_stages = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>({8, room / stage, jobs}));
+    p.total = p.act_bytes + p.n_stages * stage + fixed;
+    return p;
+}
+
+int g_num_sms = 0;
+
+// Launch with programmatic stream serialization: the kernel may start while its predecessor in the stream
+// is still draining; every access that depends on the predecessor sits behind pdl_wait().
+template <class... KArgs, class... Args>
+cudaError_t launch_pdl(void (*kern)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t s,
+                       Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 template <uint32_t TYPE, int MB, int NH>
 cudaError_t launch_one(const uint8_t* w, uint64_t n, uint64_t k, const ActPlanes& act, uint64_t m, float* dst,
                        int* error_flag, cudaStream_t s) {
-    constexpr int NWARP = 8;
-    uint32_t stride = row_stride_for<TYPE>(k);
-    size_t smem = 2 * (size_t)ROWS * stride + (TYPE == T_IQ2_XXS ? (256 + 128) * 8 : 0) +
-                  (size_t)NWARP * ROWS * 4 * NH * 4 + 16;
-    auto kern = gemv_mma_kernel<TYPE, MB, NH, NWARP>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    unsigned grid = (unsigned)((n + ROWS - 1) / ROWS);
-    kern<<<grid, NWARP * 32, smem, s>>>(w, n, k, act, m, dst, stride, error_flag);
+    constexpr int NCW = 16;
+    if (g_num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    uint64_t n_tiles = (n + ROWS - 1) / ROWS;
+    unsigned grid = (unsigned)std::min<uint64_t>(n_tiles, (uint64_t)g_num_sms);
+    SmemPlan plan = plan_smem<TYPE, NCW, MB * NH>(n, k, m, grid);
+    cudaError_t e;
+    if (plan.act_bytes) {
+        auto kern = gemv_mma_kernel<TYPE, MB, NH, NCW, 1>;
+        static bool configured = false;  // per instantiation; one device per process
+        if (!configured) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET);
+            if (e != cudaSuccess) return e;
+            configured = true;
+        }
+        e = launch_pdl(kern, grid, (NCW + 2) * 32, plan.total, s, w, n, k, act, m, dst, plan, error_flag);
+        if (e != cudaSuccess) return e;
+    } else {
+        auto kern = gemv_mma_kernel<TYPE, MB, NH, NCW, 0>;
+        static bool configured = false;
+        if (!configured) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET);
+            if (e != cudaSuccess) return e;
+            configured = true;
+        }
+        e = launch_pdl(kern, grid, (NCW + 2) * 32, plan.total, s, w, n, k, act, m, dst, plan, error_flag);
+        if (e != cudaSuccess) return e;
+    }
     return cudaGetLastError();
 }
 
@@ -615,9 +909,8 @@ cudaError_t launch_type(const uint8_t* w, uint64_t n, uint64_t k, const ActPlane
                         int* error_flag, cudaStream_t s) {
     if (m == 1) return launch_one<TYPE, 1, 1>(w, n, k, act, m, dst, error_flag, s);
     if (m == 2) return launch_one<TYPE, 2, 1>(w, n, k, act, m, dst, error_flag, s);
-    if (m <= 4) return launch_one<TYPE, 4, 1>(w, n, k, act, m, dst, error_flag, s);
-    if (m <= 8) return launch_one<TYPE, 4, 2>(w, n, k, act, m, dst, error_flag, s);
-    if (m <= 16) return launch_one<TYPE, 4, 4>(w, n, k, act, m, dst, error_flag, s);
+    if (m <= 4) return launch_one<TYPE, 2, 2>(w, n, k, act, m, dst, error_flag, s);
+    if (m <= 8) return launch_one<TYPE, 2, 4>(w, n, k, act, m, dst, error_flag, s);
     return cudaErrorInvalidValue;
 }
 
@@ -652,9 +945,8 @@ cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_
     act.meta = meta;
     act.sum16 = sum16;
     act.n_groups = (uint32_t)(k / 32);
-    unsigned qgrid = (unsigned)std::min<uint64_t>((groups + 7) / 8, 148 * 8);
-    quantize_acts_kernel<<<qgrid, 256, 0, s>>>(lhs, m, k, type, planes, meta, sum16);
-    cudaError_t e = cudaGetLastError();
+    unsigned qgrid = (unsigned)std::min<uint64_t>(m * (k / 256), 148 * 8);
+    cudaError_t e = launch_pdl(quantize_acts_kernel, qgrid, 256, 0, s, lhs, m, k, type, planes, meta, sum16);
     if (e != cudaSuccess) return e;
     switch (type) {
         case T_Q4_K: return launch_type<T_Q4_K>(w, n, k, act, m, dst, error_flag, s);
