@@ -154,6 +154,59 @@ __device__ __forceinline__ uint32_t act_position(uint32_t type, uint32_t e) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Warp-wide variant for use inside the matmul kernel: lane l holds values 8l .. 8l+7 of the unit (group
+// l / 4).  `planes` points at the unit's first group (8 x 96 bytes), `meta` / `sum16` at its first entries.
+__device__ __forceinline__ void quantize_unit_warp(const float* __restrict__ xu, uint32_t lane, uint32_t type,
+                                                   int8_t* planes, float2* meta, float* sum16) {
+    const float4* src = reinterpret_cast<const float4*>(xu + lane * 8);
+    float4 lo4 = __ldg(src), hi4 = __ldg(src + 1);
+    float v[8] = {lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
+    float amax = 0.0f, sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        amax = fmaxf(amax, fabsf(v[j]));
+        sum += v[j];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    float s16 = sum + __shfl_xor_sync(0xFFFFFFFFu, sum, 1);  // 16-value half: lanes 2h, 2h+1
+    float s32 = s16 + __shfl_xor_sync(0xFFFFFFFFu, s16, 2);  // 32-value group: lanes 4G .. 4G+3
+    const float s = amax * (1.0f / 127.0f);
+    const bool live = s > 0.0f && isfinite(s);
+    const float s1 = s * (1.0f / 254.0f), s2 = s1 * (1.0f / 254.0f);
+    const float inv = live ? 1.0f / s : 0.0f;
+    uint32_t pk[3][2] = {{0, 0}, {0, 0}, {0, 0}};
+    int8_t* gp = planes + (lane >> 2) * 96;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        int q0 = 0, q1 = 0, q2 = 0;
+        if (live) {
+            q0 = max(-127, min(127, __float2int_rn(v[j] * inv)));
+            float r1 = fmaf(-(float)q0, s, v[j]);
+            q1 = max(-127, min(127, __float2int_rn(r1 * (inv * 254.0f))));
+            float r2 = fmaf(-(float)q1, s1, r1);
+            q2 = max(-127, min(127, __float2int_rn(r2 * (inv * 64516.0f))));
+        }
+        if (type == T_MXFP4) {
+            uint32_t pos = act_position(type, 8 * (lane & 3) + j);
+            gp[pos] = (int8_t)q0;
+            gp[32 + pos] = (int8_t)q1;
+            gp[64 + pos] = (int8_t)q2;
+        } else {
+            pk[0][j >> 2] |= (uint32_t)(q0 & 0xFF) << (8 * (j & 3));
+            pk[1][j >> 2] |= (uint32_t)(q1 & 0xFF) << (8 * (j & 3));
+            pk[2][j >> 2] |= (uint32_t)(q2 & 0xFF) << (8 * (j & 3));
+        }
+    }
+    if (type != T_MXFP4) {
+#pragma unroll
+        for (int pl = 0; pl < 3; ++pl)
+            *reinterpret_cast<uint2*>(gp + 32 * pl + 8 * (lane & 3)) = make_uint2(pk[pl][0], pk[pl][1]);
+    }
+    if ((lane & 3) == 0) meta[lane >> 2] = make_float2(live ? s2 : 0.0f, s32);
+    if ((lane & 1) == 0) sum16[lane >> 1] = s16;
+}
+
 __global__ void __launch_bounds__(256) quantize_acts_kernel(const float* __restrict__ x, uint64_t m, uint64_t k,
                                                             uint32_t type, int8_t* __restrict__ planes,
                                                             float2* __restrict__ meta, float* __restrict__ sum16) {
@@ -617,8 +670,8 @@ struct SmemPlan {
 
 template <uint32_t TYPE, int MB, int NH, int NCW, int ACT>
 __global__ void __launch_bounds__((NCW + 2) * 32, 1)
-    gemv_mma_kernel(const uint8_t* __restrict__ w, uint64_t n, uint64_t k, ActPlanes act, uint64_t m,
-                    float* __restrict__ dst, SmemPlan plan, int* __restrict__ error_flag) {
+    gemv_mma_kernel(const uint8_t* __restrict__ w, uint64_t n, uint64_t k, ActPlanes act, const float* __restrict__ x,
+                    uint64_t m, float* __restrict__ dst, SmemPlan plan, int* __restrict__ error_flag) {
     using Tr = Traits<TYPE>;
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NB = MB * NH;                       // batch rows covered
@@ -668,18 +721,20 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
     // runs out raises the error flag and leaves, and the roles that depend on it run out in turn.
 
     pdl_trigger();
+    if (ACT && warp != 0) {
+        // Consumers and the reducer split the activations into planes in shared memory (ACT == 1); the
+        // producer meanwhile fills the ring.  x is the first thing that depends on the preceding kernel.
+        pdl_wait();
+        const uint64_t groups = m * (uint64_t)act.n_groups;
+        int8_t* planes = reinterpret_cast<int8_t*>(s_act);
+        float2* meta = reinterpret_cast<float2*>(s_act + groups * 96);
+        float* sum16 = reinterpret_cast<float*>(s_act + groups * 104);
+        for (uint64_t u = warp - 1; u < groups / 8; u += NCW + 1)
+            quantize_unit_warp(x + u * 256, lane, TYPE, planes + u * 768, meta + u * 8, sum16 + u * 16);
+        asm volatile("bar.sync 1, %0;" ::"r"((NCW + 1) * 32) : "memory");
+    }
     if (warp == 0) {
-        // ── producer ──  The weights never change, so their copies start at once; only the activation
-        // copy has to wait for the kernel that produced the planes.
-        if (ACT && lane == ROWS) {
-            pdl_wait();
-            // planes, meta and 16-value sums are one contiguous region of the scratch buffer
-            mbar_arrive_expect_tx(act_bar, plan.act_bytes);
-            for (uint32_t off = 0; off < plan.act_bytes; off += 32768) {
-                uint32_t bytes = min(32768u, plan.act_bytes - off);
-                bulk_g2s(s_act + off, reinterpret_cast<const uint8_t*>(act.planes) + off, bytes, act_bar);
-            }
-        }
+        // ── producer ──  The weights never change, so their copies start at once.
         if (lane < ROWS) {
             uint32_t job = 0;
             for (uint64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
@@ -724,10 +779,6 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
             a.planes = reinterpret_cast<const int8_t*>(s_act);
             a.meta = reinterpret_cast<const float2*>(s_act + groups * 96);
             a.sum16 = reinterpret_cast<const float*>(s_act + groups * 104);
-            if (!mbar_wait(act_bar, 0)) {
-                if (lane == 0) *reinterpret_cast<volatile int*>(error_flag) = 1;
-                return;
-            }
         }
         float colacc[NH][2][2], minacc[NB][2];
         uint32_t job = 0, tile_it = 0;
@@ -789,7 +840,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
         }
     } else {
         // ── reducer ──
-        pdl_wait();  // dst may still be read by the preceding kernel
+        if (!ACT) pdl_wait();  // dst may still be read by the preceding kernel
         uint32_t tile_it = 0;
         for (uint64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_it) {
             const uint32_t rb = tile_it & 1;
@@ -868,8 +919,8 @@ cudaError_t launch_pdl(void (*kern)(KArgs...), unsigned grid, unsigned block, si
 }
 
 template <uint32_t TYPE, int MB, int NH>
-cudaError_t launch_one(const uint8_t* w, uint64_t n, uint64_t k, const ActPlanes& act, uint64_t m, float* dst,
-                       int* error_flag, cudaStream_t s) {
+cudaError_t launch_one(const uint8_t* w, uint64_t n, uint64_t k, const ActPlanes& act, const float* x, uint64_t m,
+                       float* dst, int* error_flag, cudaStream_t s) {
     constexpr int NCW = 16;
     if (g_num_sms == 0) {
         int dev = 0;
@@ -888,7 +939,7 @@ cudaError_t launch_one(const uint8_t* w, uint64_t n, uint64_t k, const ActPlanes
             if (e != cudaSuccess) return e;
             configured = true;
         }
-        e = launch_pdl(kern, grid, (NCW + 2) * 32, plan.total, s, w, n, k, act, m, dst, plan, error_flag);
+        e = launch_pdl(kern, grid, (NCW + 2) * 32, plan.total, s, w, n, k, act, x, m, dst, plan, error_flag);
         if (e != cudaSuccess) return e;
     } else {
         auto kern = gemv_mma_kernel<TYPE, MB, NH, NCW, 0>;
@@ -898,25 +949,29 @@ cudaError_t launch_one(const uint8_t* w, uint64_t n, uint64_t k, const ActPlanes
             if (e != cudaSuccess) return e;
             configured = true;
         }
-        e = launch_pdl(kern, grid, (NCW + 2) * 32, plan.total, s, w, n, k, act, m, dst, plan, error_flag);
+        e = launch_pdl(kern, grid, (NCW + 2) * 32, plan.total, s, w, n, k, act, x, m, dst, plan, error_flag);
         if (e != cudaSuccess) return e;
     }
     return cudaGetLastError();
 }
 
 template <uint32_t TYPE>
-cudaError_t launch_type(const uint8_t* w, uint64_t n, uint64_t k, const ActPlanes& act, uint64_t m, float* dst,
-                        int* error_flag, cudaStream_t s) {
-    if (m == 1) return launch_one<TYPE, 1, 1>(w, n, k, act, m, dst, error_flag, s);
-    if (m == 2) return launch_one<TYPE, 2, 1>(w, n, k, act, m, dst, error_flag, s);
-    if (m <= 4) return launch_one<TYPE, 2, 2>(w, n, k, act, m, dst, error_flag, s);
-    if (m <= 8) return launch_one<TYPE, 2, 4>(w, n, k, act, m, dst, error_flag, s);
+cudaError_t launch_type(const uint8_t* w, uint64_t n, uint64_t k, const ActPlanes& act, const float* x, uint64_t m,
+                        float* dst, int* error_flag, cudaStream_t s) {
+    if (m == 1) return launch_one<TYPE, 1, 1>(w, n, k, act, x, m, dst, error_flag, s);
+    if (m == 2) return launch_one<TYPE, 2, 1>(w, n, k, act, x, m, dst, error_flag, s);
+    if (m <= 4) return launch_one<TYPE, 2, 2>(w, n, k, act, x, m, dst, error_flag, s);
+    if (m <= 8) return launch_one<TYPE, 2, 4>(w, n, k, act, x, m, dst, error_flag, s);
     return cudaErrorInvalidValue;
 }
 
 }  // namespace
 
+// Activation planes live in the kernel's shared memory when they fit; only larger products need scratch.
+static bool acts_fit_in_smem(uint64_t m, uint64_t k) { return m * (k / 32) * 112 <= ACT_SMEM_MAX; }
+
 size_t gemv_mma_scratch_bytes(uint64_t m, uint64_t k) {
+    if (acts_fit_in_smem(m, k)) return 0;
     uint64_t groups = m * (k / 32);
     return (size_t)(groups * 96 + groups * 8 + groups * 8 + 256);
 }
@@ -945,15 +1000,17 @@ cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_
     act.meta = meta;
     act.sum16 = sum16;
     act.n_groups = (uint32_t)(k / 32);
-    unsigned qgrid = (unsigned)std::min<uint64_t>(m * (k / 256), 148 * 8);
-    cudaError_t e = launch_pdl(quantize_acts_kernel, qgrid, 256, 0, s, lhs, m, k, type, planes, meta, sum16);
-    if (e != cudaSuccess) return e;
+    if (!acts_fit_in_smem(m, k)) {
+        unsigned qgrid = (unsigned)std::min<uint64_t>(m * (k / 256), 148 * 8);
+        cudaError_t e = launch_pdl(quantize_acts_kernel, qgrid, 256, 0, s, lhs, m, k, type, planes, meta, sum16);
+        if (e != cudaSuccess) return e;
+    }
     switch (type) {
-        case T_Q4_K: return launch_type<T_Q4_K>(w, n, k, act, m, dst, error_flag, s);
-        case T_Q8_0: return launch_type<T_Q8_0>(w, n, k, act, m, dst, error_flag, s);
-        case T_Q2_K: return launch_type<T_Q2_K>(w, n, k, act, m, dst, error_flag, s);
-        case T_IQ2_XXS: return launch_type<T_IQ2_XXS>(w, n, k, act, m, dst, error_flag, s);
-        case T_MXFP4: return launch_type<T_MXFP4>(w, n, k, act, m, dst, error_flag, s);
+        case T_Q4_K: return launch_type<T_Q4_K>(w, n, k, act, lhs, m, dst, error_flag, s);
+        case T_Q8_0: return launch_type<T_Q8_0>(w, n, k, act, lhs, m, dst, error_flag, s);
+        case T_Q2_K: return launch_type<T_Q2_K>(w, n, k, act, lhs, m, dst, error_flag, s);
+        case T_IQ2_XXS: return launch_type<T_IQ2_XXS>(w, n, k, act, lhs, m, dst, error_flag, s);
+        case T_MXFP4: return launch_type<T_MXFP4>(w, n, k, act, lhs, m, dst, error_flag, s);
         default: return cudaErrorInvalidValue;
     }
 }
