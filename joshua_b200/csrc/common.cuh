@@ -35,6 +35,14 @@ cudaError_t tables_gemv_f32();
 cudaError_t launch_matmul_f32(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
                               float* dst, cudaStream_t s);
 
+// One unit of grouped (MoE) work: up to 8 consecutive positions of the expert-sorted activation list,
+// all routed to `expert`.
+struct MoeJob {
+    uint32_t expert;
+    uint32_t row0;  // first position in the list
+    uint32_t cnt;   // positions (1..8)
+};
+
 // gemv_mma.cu: integer-code tensor-core path for batches 1..GEMV_MMA_MAX_M
 constexpr uint64_t GEMV_MMA_MAX_M = 8;
 cudaError_t tables_gemv_mma();
@@ -44,5 +52,29 @@ bool gemv_mma_supports(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, 
 // error_flag: device int set to 1 if a bounded wait inside the kernel gave up
 cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
                             float* dst, void* scratch, int* error_flag, cudaStream_t s);
+// f32 rows -> activation planes in `scratch` (gemv_mma_scratch_bytes(rows, k) bytes, for rows that do not fit
+// the kernel's shared memory)
+cudaError_t launch_quantize_acts(uint32_t type, const float* x, uint64_t rows, uint64_t k, void* scratch,
+                                 cudaStream_t s);
+// Grouped form: every job multiplies its list positions' activation rows by its expert's [n, k] matrix and
+// writes dst[position, n].  With a second bank the two results are combined as silu(clamp(g)) * clamp(u).
+struct GroupedLaunch {
+    uint32_t type;
+    const uint8_t* w0;        // bank of [n_expert][n][k] blocks
+    const uint8_t* w1;        // second bank (SwiGLU pair) or NULL
+    uint64_t n, k, expert_bytes;
+    const float* x;           // activation rows [x_rows, k]
+    uint32_t x_rows;
+    void* planes;             // pre-split planes of those rows (launch_quantize_acts), or NULL to split in-kernel
+    const uint32_t* act_rows; // activation row of each list position, NULL = identity
+    const MoeJob* jobs;       // device
+    const uint32_t* n_jobs;   // device
+    uint32_t max_jobs;        // host bound on *n_jobs (sizes the grid)
+    uint32_t rows_per_job;    // host bound on MoeJob::cnt (1, 2, 4 or 8)
+    float* dst;
+    float clamp;
+    int* error_flag;
+};
+cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s);
 
 }  // namespace jq

@@ -308,25 +308,23 @@ __device__ __forceinline__ T ld_act(const T* p) {
 template <int MB, int NH>
 struct Roles {
     static constexpr int CH = 2 / MB;  // groups chained into one accumulator
+    static constexpr int NB = MB * NH; // batch slots of a tile
     int g, t;
     bool sup_live;                // column g carries data
-    int sup_p, sup_plane;         // chain position and plane of column g
-    uint32_t sup_row[NH];         // batch row fed in pass h (clamped to m-1; clamped results are dropped)
-    int col_p[2], col_i[2];       // chain position and batch row (within a pass) of held columns 2t, 2t+1
+    int sup_p, sup_plane, sup_i;  // chain position, plane and batch slot (within a pass) of column g
+    int col_p[2], col_i[2];       // chain position and batch slot (within a pass) of held columns 2t, 2t+1
     float col_w[2];               // plane weight of the held columns: 254^2, 254, 1, or 0 for a dead column
-    uint32_t sup_off[NH];         // byte offset of this lane's B bytes inside the planes, group 0 (dead lanes: 0)
-    uint32_t min_row[MB * NH];    // batch rows, clamped, for the minima terms
-    __device__ __forceinline__ Roles(int lane, uint64_t m) {
+    uint32_t brow[NB];            // activation row of batch slot b for the current tile (unused slots repeat the last)
+    uint32_t col_row[NH][2];      // activation row behind held column j in pass h
+    uint32_t sup_off[NH];         // byte offset of this lane's B bytes inside the planes for group 0 of pass h
+    __device__ __forceinline__ explicit Roles(int lane) {
         g = lane >> 2;
         t = lane & 3;
         sup_live = g < 6;
         int slot = g / 3;
         sup_plane = g % 3;
         sup_p = slot / MB;
-#pragma unroll
-        for (int h = 0; h < NH; ++h) sup_row[h] = (uint32_t)min((uint64_t)(h * MB + slot % MB), m - 1);
-#pragma unroll
-        for (int h = 0; h < NH; ++h) sup_off[h] = 0;  // filled by the kernel once n_groups is known
+        sup_i = slot % MB;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             int col = 2 * t + j;
@@ -335,8 +333,30 @@ struct Roles {
             col_i[j] = col < 6 ? s % MB : 0;
             col_w[j] = col >= 6 ? 0.0f : (pl == 0 ? 64516.0f : (pl == 1 ? 254.0f : 1.0f));
         }
+    }
+    // Point the roles at a tile's activation rows: slot b reads row `row0 + min(b, cnt-1)` of the
+    // activation list (through `act_rows` when the rows are gathered).
+    __device__ __forceinline__ void set_rows(uint32_t row0, uint32_t cnt, const uint32_t* act_rows, uint32_t n_groups) {
 #pragma unroll
-        for (int b = 0; b < MB * NH; ++b) min_row[b] = (uint32_t)min((uint64_t)b, m - 1);
+        for (int b = 0; b < NB; ++b) {
+            uint32_t pos = row0 + min((uint32_t)b, cnt - 1);
+            brow[b] = act_rows ? __ldg(act_rows + pos) : pos;
+        }
+        // register arrays must only be indexed by compile-time constants: pick with selects
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+            uint32_t srow = brow[h * MB];
+#pragma unroll
+            for (int i = 1; i < MB; ++i) srow = sup_i == i ? brow[h * MB + i] : srow;
+            sup_off[h] = sup_live ? (uint32_t)(((uint64_t)srow * n_groups + sup_p) * 96 + 32 * sup_plane + 8 * t) : 0u;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                uint32_t r = brow[h * MB];
+#pragma unroll
+                for (int i = 1; i < MB; ++i) r = col_i[j] == i ? brow[h * MB + i] : r;
+                col_row[h][j] = r;
+            }
+        }
     }
 };
 
@@ -417,7 +437,7 @@ __device__ __forceinline__ void process_unit(const uint8_t* u0, const uint8_t* u
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 // activation scale of the batch row this column belongs to (one per 256-value unit)
-                uint32_t row = (uint32_t)min((uint64_t)(h * MB + ro.col_i[j]), (uint64_t)ro.min_row[MB * NH - 1]);
+                uint32_t row = ro.col_row[h][j];
                 float sa = ld_act<ACT>(&act.meta[(uint64_t)row * act.n_groups + G0].x) * ro.col_w[j];
                 float v0 = INT_SCALE ? (float)isum[h][j][0] : fsum[h][j][0];
                 float v1 = INT_SCALE ? (float)isum[h][j][1] : fsum[h][j][1];
@@ -476,7 +496,7 @@ __device__ __forceinline__ void process_unit(const uint8_t* u0, const uint8_t* u
             float m0 = (float)((mw0 >> sh) & 0xFF) * dm0, m1 = (float)((mw1 >> sh) & 0xFF) * dm1;
 #pragma unroll
             for (int b = 0; b < MB * NH; ++b) {
-                float sx = ld_act<ACT>(&act.meta[(uint64_t)ro.min_row[b] * act.n_groups + G0 + 2 * ro.t + e].y);
+                float sx = ld_act<ACT>(&act.meta[(uint64_t)ro.brow[b] * act.n_groups + G0 + 2 * ro.t + e].y);
                 minacc[b][0] = fmaf(m0, sx, minacc[b][0]);
                 minacc[b][1] = fmaf(m1, sx, minacc[b][1]);
             }
@@ -639,7 +659,7 @@ __device__ __forceinline__ void process_unit(const uint8_t* u0, const uint8_t* u
             float m0 = (float)(u0[j16] >> 4) * dm0, m1 = (float)(u1[j16] >> 4) * dm1;
 #pragma unroll
             for (int b = 0; b < MB * NH; ++b) {
-                float sx = ld_act<ACT>(act.sum16 + ((uint64_t)ro.min_row[b] * act.n_groups + G0) * 2 + j16);
+                float sx = ld_act<ACT>(act.sum16 + ((uint64_t)ro.brow[b] * act.n_groups + G0) * 2 + j16);
                 minacc[b][0] = fmaf(m0, sx, minacc[b][0]);
                 minacc[b][1] = fmaf(m1, sx, minacc[b][1]);
             }
@@ -664,18 +684,41 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 struct SmemPlan {
     uint32_t row_stride;   // bytes between rows of a stage
     uint32_t n_stages;     // ring depth
-    uint32_t act_bytes;    // activation region (0 = read activations from global memory)
+    uint32_t act_bytes;    // activation region (0 = read activation planes from global memory)
     uint32_t total;        // dynamic shared memory of the launch
 };
 
-template <uint32_t TYPE, int MB, int NH, int NCW, int ACT>
-__global__ void __launch_bounds__((NCW + 2) * 32, 1)
-    gemv_mma_kernel(const uint8_t* __restrict__ w, uint64_t n, uint64_t k, ActPlanes act, const float* __restrict__ x,
-                    uint64_t m, float* __restrict__ dst, SmemPlan plan, int* __restrict__ error_flag) {
+// Everything a launch needs.  A dense product is the single implicit job {expert 0, rows 0..m}.
+struct GemvArgs {
+    const uint8_t* w[2];        // weight bank; w[1] is the second bank of a SwiGLU pair (gate, up)
+    uint64_t n;                 // rows of one expert's matrix (dense: all rows)
+    uint64_t k;
+    uint64_t expert_bytes;      // bytes between experts in a bank
+    ActPlanes act;              // activation planes in global memory (ACT == 0)
+    const float* x;             // f32 activation rows, split into planes inside the kernel (ACT == 1)
+    uint32_t x_rows;            // rows of x to split (ACT == 1)
+    uint32_t m;                 // dense: batch rows
+    float* dst;                 // [activation list position, n]
+    const MoeJob* jobs;         // grouped: device job list, else NULL
+    const uint32_t* n_jobs;     // grouped: device count of jobs
+    const uint32_t* act_rows;   // grouped: activation row of each list position (NULL = the position itself)
+    float clamp;                // SwiGLU clamp (0 = off)
+    int swiglu;                 // 1: tiles come in (gate, up) pairs and dst = silu(g) * u
+    SmemPlan plan;
+    int* error_flag;
+};
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+
+// GROUPED == 0 is the dense product (one implicit job, one bank, plain store); the job list and the SwiGLU
+// pair are compiled in only for GROUPED == 1.
+template <uint32_t TYPE, int MB, int NH, int NCW, int ACT, int GROUPED>
+__global__ void __launch_bounds__((NCW + 2) * 32, 1) gemv_mma_kernel(const __grid_constant__ GemvArgs ga) {
     using Tr = Traits<TYPE>;
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int NB = MB * NH;                       // batch rows covered
+    constexpr int NB = MB * NH;                       // batch slots of a tile
     constexpr uint32_t RED_FLOATS = NCW * NB * ROWS;  // one reduction buffer
+    const SmemPlan& plan = ga.plan;
     const uint32_t stage_bytes = ROWS * plan.row_stride;
     // layout: activation region | ring | tables (IQ2_XXS) | 2 reduction buffers | mbarriers
     uint8_t* s_act = smem;
@@ -687,14 +730,18 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
     uint64_t* empty = full + plan.n_stages;
     uint64_t* red_full = empty + plan.n_stages;
     uint64_t* red_empty = red_full + 2;
-    uint64_t* act_bar = red_empty + 2;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t NS = plan.n_stages;
-    const uint64_t n_tiles = (n + ROWS - 1) / ROWS;
+    const uint64_t n = ga.n, k = ga.k;
+    const uint32_t tiles_per_expert = (uint32_t)((n + ROWS - 1) / ROWS);
     const uint32_t units_per_row = (uint32_t)(k / 256);
     const uint64_t row_bytes = (uint64_t)units_per_row * Tr::UNIT_BYTES;
     const uint32_t n_chunks = (units_per_row + Tr::CHUNK_UNITS - 1) / Tr::CHUNK_UNITS;
+    const uint32_t n_sub = GROUPED && ga.swiglu ? 2 : 1;  // weight banks visited per tile
+    constexpr bool grouped = GROUPED != 0;
+    const bool swiglu = GROUPED && ga.swiglu;
+    const uint32_t n_groups = (uint32_t)(k / 32);
 
     if (tid == 0) {
         for (uint32_t s = 0; s < NS; ++s) {
@@ -705,7 +752,6 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
             mbar_init(&red_full[b], NCW);
             mbar_init(&red_empty[b], 1);
         }
-        mbar_init(act_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (TYPE == T_IQ2_XXS) {
@@ -719,149 +765,190 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1)
     __syncthreads();
     // From here on the three roles only meet through mbarriers.  Every wait is bounded; a role whose wait
     // runs out raises the error flag and leaves, and the roles that depend on it run out in turn.
-
     pdl_trigger();
+    // A grouped launch learns its work from the kernel before it; a dense launch knows it already and may
+    // prefetch weights at once.
+    if (grouped || warp != 0) pdl_wait();
     if (ACT && warp != 0) {
-        // Consumers and the reducer split the activations into planes in shared memory (ACT == 1); the
-        // producer meanwhile fills the ring.  x is the first thing that depends on the preceding kernel.
-        pdl_wait();
-        const uint64_t groups = m * (uint64_t)act.n_groups;
+        // Consumers and the reducer split the activations into planes in shared memory while the producer
+        // fills the ring.
+        const uint64_t groups = (uint64_t)ga.x_rows * n_groups;
         int8_t* planes = reinterpret_cast<int8_t*>(s_act);
         float2* meta = reinterpret_cast<float2*>(s_act + groups * 96);
         float* sum16 = reinterpret_cast<float*>(s_act + groups * 104);
         for (uint64_t u = warp - 1; u < groups / 8; u += NCW + 1)
-            quantize_unit_warp(x + u * 256, lane, TYPE, planes + u * 768, meta + u * 8, sum16 + u * 16);
+            quantize_unit_warp(ga.x + u * 256, lane, TYPE, planes + u * 768, meta + u * 8, sum16 + u * 16);
         asm volatile("bar.sync 1, %0;" ::"r"((NCW + 1) * 32) : "memory");
     }
+    const uint32_t n_jobs = grouped ? __ldg(ga.n_jobs) : 1u;
+    const uint32_t n_tiles = n_jobs * tiles_per_expert;
+    // tile -> (job, row tile); the job gives the expert (weight offset) and the activation rows
+    auto job_of = [&](uint32_t tile, uint32_t* rt) -> MoeJob {
+        if (!grouped) {
+            *rt = tile;
+            return MoeJob{0u, 0u, ga.m};
+        }
+        uint32_t j = tile / tiles_per_expert;
+        *rt = tile - j * tiles_per_expert;
+        return ga.jobs[j];
+    };
+    // low four address bits of row `row` of expert `e` in bank `sub` (the offset of its bytes inside the
+    // 16-byte aligned span that is copied)
+    const uint32_t rb16 = (uint32_t)(row_bytes & 15), eb16 = (uint32_t)(ga.expert_bytes & 15);
+    auto shift_of = [&](uint32_t sub, uint32_t e, uint32_t row) -> uint32_t {
+        return ((uint32_t)(reinterpret_cast<uintptr_t>(ga.w[sub]) & 15) + e * eb16 + row * rb16) & 15;
+    };
+
     if (warp == 0) {
-        // ── producer ──  The weights never change, so their copies start at once.
+        // ── producer ──
         if (lane < ROWS) {
             uint32_t job = 0;
-            for (uint64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-                uint64_t row = tile * ROWS + lane < n ? tile * ROWS + lane : n - 1;
-                for (uint32_t chunk = 0; chunk < n_chunks; ++chunk, ++job) {
-                    uint32_t s = job % NS, round = job / NS;
-                    if (!mbar_wait(&empty[s], (round & 1) ^ 1)) {
-                        *reinterpret_cast<volatile int*>(error_flag) = 1;
-                        return;
+            for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                uint32_t rt;
+                const MoeJob jd = job_of(tile, &rt);
+                uint64_t row = (uint64_t)rt * ROWS + lane < n ? (uint64_t)rt * ROWS + lane : n - 1;
+                for (uint32_t sub = 0; sub < n_sub; ++sub) {
+                    const uint8_t* wrow = ga.w[sub] + (uint64_t)jd.expert * ga.expert_bytes + row * row_bytes;
+                    for (uint32_t chunk = 0; chunk < n_chunks; ++chunk, ++job) {
+                        uint32_t s = job % NS, round = job / NS;
+                        if (!mbar_wait(&empty[s], (round & 1) ^ 1)) {
+                            *reinterpret_cast<volatile int*>(ga.error_flag) = 1;
+                            return;
+                        }
+                        uint32_t u_lo = chunk * Tr::CHUNK_UNITS;
+                        uint32_t u_hi = min(units_per_row, u_lo + Tr::CHUNK_UNITS);
+                        uintptr_t beg = reinterpret_cast<uintptr_t>(wrow) + (uint64_t)u_lo * Tr::UNIT_BYTES;
+                        uintptr_t end = beg + (uint64_t)(u_hi - u_lo) * Tr::UNIT_BYTES;
+                        uintptr_t abeg = beg & ~(uintptr_t)15, aend = (end + 15) & ~(uintptr_t)15;
+                        uint32_t bytes = (uint32_t)(aend - abeg);
+                        mbar_arrive_expect_tx(&full[s], bytes);
+                        bulk_g2s(ring + s * stage_bytes + lane * plan.row_stride,
+                                 reinterpret_cast<const void*>(abeg), bytes, &full[s]);
                     }
-                    uint32_t u_lo = chunk * Tr::CHUNK_UNITS;
-                    uint32_t u_hi = min(units_per_row, u_lo + Tr::CHUNK_UNITS);
-                    uintptr_t beg = reinterpret_cast<uintptr_t>(w) + row * row_bytes + (uint64_t)u_lo * Tr::UNIT_BYTES;
-                    uintptr_t end = beg + (uint64_t)(u_hi - u_lo) * Tr::UNIT_BYTES;
-                    uintptr_t abeg = beg & ~(uintptr_t)15, aend = (end + 15) & ~(uintptr_t)15;
-                    uint32_t bytes = (uint32_t)(aend - abeg);
-                    mbar_arrive_expect_tx(&full[s], bytes);
-                    bulk_g2s(ring + s * stage_bytes + lane * plan.row_stride, reinterpret_cast<const void*>(abeg),
-                             bytes, &full[s]);
                 }
             }
         }
     } else if (warp <= NCW) {
         // ── consumers ──
         const int cw = warp - 1;
-        Roles<MB, NH> ro(lane, m);
-#pragma unroll
-        for (int h = 0; h < NH; ++h)
-            ro.sup_off[h] = ro.sup_live ? (uint32_t)(((uint64_t)ro.sup_row[h] * act.n_groups + ro.sup_p) * 96 +
-                                                     32 * ro.sup_plane + 8 * ro.t)
-                                        : 0u;
+        Roles<MB, NH> ro(lane);
         if (TYPE == T_Q4_K && MB == 1) {
             // two groups per chain: held column j only ever sees odd (high-nibble, 16x) or even groups
 #pragma unroll
             for (int j = 0; j < 2; ++j)
                 if (ro.col_p[j] & 1) ro.col_w[j] *= 0.0625f;
         }
-        ActPlanes a = act;
-        if (!ACT) pdl_wait();
+        ActPlanes a = ga.act;
         if (ACT) {
-            uint64_t groups = m * (uint64_t)act.n_groups;
+            const uint64_t groups = (uint64_t)ga.x_rows * n_groups;
             a.planes = reinterpret_cast<const int8_t*>(s_act);
             a.meta = reinterpret_cast<const float2*>(s_act + groups * 96);
             a.sum16 = reinterpret_cast<const float*>(s_act + groups * 104);
         }
+        a.n_groups = n_groups;
         float colacc[NH][2][2], minacc[NB][2];
-        uint32_t job = 0, tile_it = 0;
-        for (uint64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_it) {
+        uint32_t job = 0, red_it = 0;
+        for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            uint32_t rt;
+            const MoeJob jd = job_of(tile, &rt);
+            if (grouped || tile == blockIdx.x) ro.set_rows(jd.row0, jd.cnt, ga.act_rows, n_groups);
+            const uint64_t row0 = (uint64_t)rt * ROWS;
+            for (uint32_t sub = 0; sub < n_sub; ++sub, ++red_it) {
 #pragma unroll
-            for (int h = 0; h < NH; ++h)
+                for (int h = 0; h < NH; ++h)
 #pragma unroll
-                for (int j = 0; j < 2; ++j) colacc[h][j][0] = colacc[h][j][1] = 0.0f;
+                    for (int j = 0; j < 2; ++j) colacc[h][j][0] = colacc[h][j][1] = 0.0f;
 #pragma unroll
-            for (int b = 0; b < NB; ++b) minacc[b][0] = minacc[b][1] = 0.0f;
-            const uint64_t row0 = tile * ROWS;
-            // byte offset of a row's first unit inside its 16-byte aligned span (the same for every chunk:
-            // chunk starts are multiples of 16 bytes for every format)
-            auto row_shift = [&](int r) -> uint32_t {
-                uint64_t row = row0 + r < n ? row0 + r : n - 1;
-                return (uint32_t)((reinterpret_cast<uintptr_t>(w) + row * row_bytes) & 15);
-            };
-            const uint32_t sh0 = row_shift(ro.g), sh1 = row_shift(ro.g + 8);
-            for (uint32_t chunk = 0; chunk < n_chunks; ++chunk, ++job) {
-                uint32_t s = job % NS, round = job / NS;
-                if (!mbar_wait(&full[s], round & 1)) {
-                    if (lane == 0) *reinterpret_cast<volatile int*>(error_flag) = 1;
+                for (int b = 0; b < NB; ++b) minacc[b][0] = minacc[b][1] = 0.0f;
+                // byte offset of a row's first unit inside its 16-byte aligned span (the same for every
+                // chunk: chunk starts are multiples of 16 bytes for every format)
+                const uint32_t r0c = (uint32_t)min(row0 + ro.g, n - 1), r1c = (uint32_t)min(row0 + ro.g + 8, n - 1);
+                const uint32_t sh0 = shift_of(sub, jd.expert, r0c), sh1 = shift_of(sub, jd.expert, r1c);
+                for (uint32_t chunk = 0; chunk < n_chunks; ++chunk, ++job) {
+                    uint32_t s = job % NS, round = job / NS;
+                    if (!mbar_wait(&full[s], round & 1)) {
+                        if (lane == 0) *reinterpret_cast<volatile int*>(ga.error_flag) = 1;
+                        return;
+                    }
+                    const uint8_t* st = ring + s * stage_bytes;
+                    const uint32_t u_lo = chunk * Tr::CHUNK_UNITS;
+                    const uint32_t cnt = min(units_per_row - u_lo, Tr::CHUNK_UNITS);
+                    for (uint32_t u = cw; u < cnt; u += NCW) {
+                        const uint8_t* u0 = st + ro.g * plan.row_stride + sh0 + u * Tr::UNIT_BYTES;
+                        const uint8_t* u1 = st + (ro.g + 8) * plan.row_stride + sh1 + u * Tr::UNIT_BYTES;
+                        process_unit<TYPE, MB, NH, ACT>(u0, u1, u_lo + u, a, ro, s_grid, s_mask, colacc, minacc);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[s]);
+                }
+                // hand the partial sums to the reducer: per batch slot, the held columns that belong to it
+                // minus its minima terms, summed over the quad
+                const uint32_t rb = red_it & 1;
+                if (!mbar_wait(&red_empty[rb], ((red_it >> 1) & 1) ^ 1)) {
+                    if (lane == 0) *reinterpret_cast<volatile int*>(ga.error_flag) = 1;
                     return;
                 }
-                const uint8_t* st = ring + s * stage_bytes;
-                const uint32_t u_lo = chunk * Tr::CHUNK_UNITS;
-                const uint32_t cnt = min(units_per_row - u_lo, Tr::CHUNK_UNITS);
-                for (uint32_t u = cw; u < cnt; u += NCW) {
-                    const uint8_t* u0 = st + ro.g * plan.row_stride + sh0 + u * Tr::UNIT_BYTES;
-                    const uint8_t* u1 = st + (ro.g + 8) * plan.row_stride + sh1 + u * Tr::UNIT_BYTES;
-                    process_unit<TYPE, MB, NH, ACT>(u0, u1, u_lo + u, a, ro, s_grid, s_mask, colacc, minacc);
+                float* red = s_red + rb * RED_FLOATS;
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    const int h = b / MB, i = b % MB;
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        float v = -minacc[b][r];
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) v += ro.col_i[j] == i ? colacc[h][j][r] : 0.0f;
+                        v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+                        v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
+                        if (ro.t == 0) red[(cw * NB + b) * ROWS + ro.g + 8 * r] = v;
+                    }
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[s]);
+                if (lane == 0) mbar_arrive(&red_full[rb]);
             }
-            // hand the tile's partial sums to the reducer: per batch row, the held columns that belong to
-            // it minus its minima terms, summed over the quad
-            const uint32_t rb = tile_it & 1;
-            if (!mbar_wait(&red_empty[rb], ((tile_it >> 1) & 1) ^ 1)) {
-                if (lane == 0) *reinterpret_cast<volatile int*>(error_flag) = 1;
-                return;
-            }
-            float* red = s_red + rb * RED_FLOATS;
-#pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                const int h = b / MB, i = b % MB;
-#pragma unroll
-                for (int r = 0; r < 2; ++r) {
-                    float v = -minacc[b][r];
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) v += ro.col_i[j] == i ? colacc[h][j][r] : 0.0f;
-                    v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
-                    v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
-                    if (ro.t == 0) red[(cw * NB + b) * ROWS + ro.g + 8 * r] = v;
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&red_full[rb]);
         }
     } else {
         // ── reducer ──
-        if (!ACT) pdl_wait();  // dst may still be read by the preceding kernel
-        uint32_t tile_it = 0;
-        for (uint64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_it) {
-            const uint32_t rb = tile_it & 1;
-            if (!mbar_wait(&red_full[rb], (tile_it >> 1) & 1)) {
-                if (lane == 0) *reinterpret_cast<volatile int*>(error_flag) = 1;
-                return;
-            }
-            const float* red = s_red + rb * RED_FLOATS;
-            const uint64_t row0 = tile * ROWS;
-            for (int o = lane; o < NB * ROWS; o += 32) {
-                int r = o % ROWS;
-                uint64_t batch = o / ROWS;
-                if (batch < m && row0 + r < n) {
-                    float v = 0.0f;
-#pragma unroll
-                    for (int cwv = 0; cwv < NCW; ++cwv) v += red[(cwv * NB + (int)batch) * ROWS + r];
-                    dst[batch * n + row0 + r] = v;
+        constexpr int PER_LANE = (NB * ROWS + 31) / 32;
+        float gate[PER_LANE];
+        uint32_t red_it = 0;
+        for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            uint32_t rt;
+            const MoeJob jd = job_of(tile, &rt);
+            const uint64_t row0 = (uint64_t)rt * ROWS;
+            for (uint32_t sub = 0; sub < n_sub; ++sub, ++red_it) {
+                const uint32_t rb = red_it & 1;
+                if (!mbar_wait(&red_full[rb], (red_it >> 1) & 1)) {
+                    if (lane == 0) *reinterpret_cast<volatile int*>(ga.error_flag) = 1;
+                    return;
                 }
+                const float* red = s_red + rb * RED_FLOATS;
+#pragma unroll
+                for (int q = 0; q < PER_LANE; ++q) {
+                    const int o = lane + 32 * q;
+                    if (o < NB * ROWS) {
+                        const int r = o % ROWS;
+                        const uint32_t b = o / ROWS;
+                        float v = 0.0f;
+#pragma unroll
+                        for (int cwv = 0; cwv < NCW; ++cwv) v += red[(cwv * NB + (int)b) * ROWS + r];
+                        if (swiglu && sub == 0) {
+                            gate[q] = v;
+                        } else if (b < jd.cnt && row0 + r < n) {
+                            if (swiglu) {
+                                float gv = gate[q], uv = v;
+                                if (ga.clamp > 0.0f) {
+                                    gv = fminf(gv, ga.clamp);
+                                    uv = fmaxf(-ga.clamp, fminf(uv, ga.clamp));
+                                }
+                                v = silu_f(gv) * uv;
+                            }
+                            ga.dst[(uint64_t)(jd.row0 + b) * n + row0 + r] = v;
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&red_empty[rb]);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&red_empty[rb]);
         }
     }
 }
@@ -882,18 +969,17 @@ uint32_t row_stride_for(uint64_t k) {
 }
 
 template <uint32_t TYPE, int NCW, int NB>
-SmemPlan plan_smem(uint64_t n, uint64_t k, uint64_t m, unsigned grid) {
+SmemPlan plan_smem(uint64_t k, uint64_t act_rows_in_smem, uint64_t jobs_per_cta) {
     using Tr = Traits<TYPE>;
     SmemPlan p;
     p.row_stride = row_stride_for<TYPE>(k);
-    uint32_t fixed = (TYPE == T_IQ2_XXS ? (256 + 128) * 8 : 0) + 2 * NCW * NB * ROWS * 4 + 8 * (2 * 8 + 5) + 128;
-    uint64_t act = m * (k / 32) * 112;
-    p.act_bytes = act <= ACT_SMEM_MAX ? (uint32_t)act : 0;
+    uint32_t fixed = (TYPE == T_IQ2_XXS ? (256 + 128) * 8 : 0) + 2 * NCW * NB * ROWS * 4 + 8 * (2 * 8 + 4) + 128;
+    p.act_bytes = (uint32_t)(act_rows_in_smem * (k / 32) * 112);
     uint32_t stage = ROWS * p.row_stride;
     uint32_t room = SMEM_BUDGET - fixed - p.act_bytes;
     uint32_t n_chunks = (uint32_t)((k / 256 + Tr::CHUNK_UNITS - 1) / Tr::CHUNK_UNITS);
-    uint64_t jobs = ((n + ROWS - 1) / ROWS + grid - 1) / grid * n_chunks;  // per CTA
-    p.n_stages = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>({8, room / stage, jobs}));
+    uint64_t jobs = std::max<uint64_t>(1, jobs_per_cta) * n_chunks;
+    p.n_stages = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>({(uint64_t)8, (uint64_t)(room / stage), jobs}));
     p.total = p.act_bytes + p.n_stages * stage + fixed;
     return p;
 }
@@ -918,61 +1004,58 @@ cudaError_t launch_pdl(void (*kern)(KArgs...), unsigned grid, unsigned block, si
     return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
-template <uint32_t TYPE, int MB, int NH>
-cudaError_t launch_one(const uint8_t* w, uint64_t n, uint64_t k, const ActPlanes& act, const float* x, uint64_t m,
-                       float* dst, int* error_flag, cudaStream_t s) {
+template <uint32_t TYPE, int MB, int NH, int ACT, int GROUPED>
+cudaError_t launch_variant(GemvArgs& ga, uint64_t max_tiles, cudaStream_t s) {
     constexpr int NCW = 16;
     if (g_num_sms == 0) {
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
     }
-    uint64_t n_tiles = (n + ROWS - 1) / ROWS;
-    unsigned grid = (unsigned)std::min<uint64_t>(n_tiles, (uint64_t)g_num_sms);
-    SmemPlan plan = plan_smem<TYPE, NCW, MB * NH>(n, k, m, grid);
-    cudaError_t e;
-    if (plan.act_bytes) {
-        auto kern = gemv_mma_kernel<TYPE, MB, NH, NCW, 1>;
-        static bool configured = false;  // per instantiation; one device per process
-        if (!configured) {
-            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET);
-            if (e != cudaSuccess) return e;
-            configured = true;
-        }
-        e = launch_pdl(kern, grid, (NCW + 2) * 32, plan.total, s, w, n, k, act, x, m, dst, plan, error_flag);
+    unsigned grid = (unsigned)std::max<uint64_t>(1, std::min<uint64_t>(max_tiles, (uint64_t)g_num_sms));
+    uint64_t per_cta = (max_tiles + grid - 1) / grid * (ga.swiglu ? 2 : 1);
+    ga.plan = plan_smem<TYPE, NCW, MB * NH>(ga.k, ACT ? ga.x_rows : 0, per_cta);
+    auto kern = gemv_mma_kernel<TYPE, MB, NH, NCW, ACT, GROUPED>;
+    static bool configured = false;  // per instantiation; one device per process
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET);
         if (e != cudaSuccess) return e;
-    } else {
-        auto kern = gemv_mma_kernel<TYPE, MB, NH, NCW, 0>;
-        static bool configured = false;
-        if (!configured) {
-            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET);
-            if (e != cudaSuccess) return e;
-            configured = true;
-        }
-        e = launch_pdl(kern, grid, (NCW + 2) * 32, plan.total, s, w, n, k, act, x, m, dst, plan, error_flag);
-        if (e != cudaSuccess) return e;
+        configured = true;
     }
-    return cudaGetLastError();
+    cudaError_t e = launch_pdl(kern, grid, (NCW + 2) * 32, ga.plan.total, s, ga);
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
-template <uint32_t TYPE>
-cudaError_t launch_type(const uint8_t* w, uint64_t n, uint64_t k, const ActPlanes& act, const float* x, uint64_t m,
-                        float* dst, int* error_flag, cudaStream_t s) {
-    if (m == 1) return launch_one<TYPE, 1, 1>(w, n, k, act, x, m, dst, error_flag, s);
-    if (m == 2) return launch_one<TYPE, 2, 1>(w, n, k, act, x, m, dst, error_flag, s);
-    if (m <= 4) return launch_one<TYPE, 2, 2>(w, n, k, act, x, m, dst, error_flag, s);
-    if (m <= 8) return launch_one<TYPE, 2, 4>(w, n, k, act, x, m, dst, error_flag, s);
+// rows_per_job: the largest number of batch rows one tile carries (dense: m)
+template <uint32_t TYPE, int ACT, int GROUPED>
+cudaError_t launch_rows(GemvArgs& ga, uint32_t rows_per_job, uint64_t max_tiles, cudaStream_t s) {
+    if (rows_per_job == 1) return launch_variant<TYPE, 1, 1, ACT, GROUPED>(ga, max_tiles, s);
+    if (rows_per_job == 2) return launch_variant<TYPE, 2, 1, ACT, GROUPED>(ga, max_tiles, s);
+    if (rows_per_job <= 4) return launch_variant<TYPE, 2, 2, ACT, GROUPED>(ga, max_tiles, s);
+    if (rows_per_job <= 8) return launch_variant<TYPE, 2, 4, ACT, GROUPED>(ga, max_tiles, s);
     return cudaErrorInvalidValue;
+}
+
+template <int ACT, int GROUPED>
+cudaError_t launch_typed(uint32_t type, GemvArgs& ga, uint32_t rows_per_job, uint64_t max_tiles, cudaStream_t s) {
+    switch (type) {
+        case T_Q4_K: return launch_rows<T_Q4_K, ACT, GROUPED>(ga, rows_per_job, max_tiles, s);
+        case T_Q8_0: return launch_rows<T_Q8_0, ACT, GROUPED>(ga, rows_per_job, max_tiles, s);
+        case T_Q2_K: return launch_rows<T_Q2_K, ACT, GROUPED>(ga, rows_per_job, max_tiles, s);
+        case T_IQ2_XXS: return launch_rows<T_IQ2_XXS, ACT, GROUPED>(ga, rows_per_job, max_tiles, s);
+        case T_MXFP4: return launch_rows<T_MXFP4, ACT, GROUPED>(ga, rows_per_job, max_tiles, s);
+        default: return cudaErrorInvalidValue;
+    }
 }
 
 }  // namespace
 
 // Activation planes live in the kernel's shared memory when they fit; only larger products need scratch.
-static bool acts_fit_in_smem(uint64_t m, uint64_t k) { return m * (k / 32) * 112 <= ACT_SMEM_MAX; }
+static bool acts_fit_in_smem(uint64_t rows, uint64_t k) { return rows * (k / 32) * 112 <= ACT_SMEM_MAX; }
 
-size_t gemv_mma_scratch_bytes(uint64_t m, uint64_t k) {
-    if (acts_fit_in_smem(m, k)) return 0;
-    uint64_t groups = m * (k / 32);
+size_t gemv_mma_scratch_bytes(uint64_t rows, uint64_t k) {
+    if (acts_fit_in_smem(rows, k)) return 0;
+    uint64_t groups = rows * (k / 32);
     return (size_t)(groups * 96 + groups * 8 + groups * 8 + 256);
 }
 
@@ -989,30 +1072,64 @@ bool gemv_mma_supports(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, 
     }
 }
 
-cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
-                            float* dst, void* scratch, int* error_flag, cudaStream_t s) {
-    uint64_t groups = m * (k / 32);
+static ActPlanes planes_in(void* scratch, uint64_t rows, uint64_t k) {
+    uint64_t groups = rows * (k / 32);
     ActPlanes act;
     int8_t* planes = static_cast<int8_t*>(scratch);
-    float2* meta = reinterpret_cast<float2*>(planes + groups * 96);
-    float* sum16 = reinterpret_cast<float*>(meta + groups);
     act.planes = planes;
-    act.meta = meta;
-    act.sum16 = sum16;
+    act.meta = reinterpret_cast<float2*>(planes + groups * 96);
+    act.sum16 = reinterpret_cast<float*>(planes + groups * 104);
     act.n_groups = (uint32_t)(k / 32);
-    if (!acts_fit_in_smem(m, k)) {
-        unsigned qgrid = (unsigned)std::min<uint64_t>(m * (k / 256), 148 * 8);
-        cudaError_t e = launch_pdl(quantize_acts_kernel, qgrid, 256, 0, s, lhs, m, k, type, planes, meta, sum16);
-        if (e != cudaSuccess) return e;
-    }
-    switch (type) {
-        case T_Q4_K: return launch_type<T_Q4_K>(w, n, k, act, lhs, m, dst, error_flag, s);
-        case T_Q8_0: return launch_type<T_Q8_0>(w, n, k, act, lhs, m, dst, error_flag, s);
-        case T_Q2_K: return launch_type<T_Q2_K>(w, n, k, act, lhs, m, dst, error_flag, s);
-        case T_IQ2_XXS: return launch_type<T_IQ2_XXS>(w, n, k, act, lhs, m, dst, error_flag, s);
-        case T_MXFP4: return launch_type<T_MXFP4>(w, n, k, act, lhs, m, dst, error_flag, s);
-        default: return cudaErrorInvalidValue;
-    }
+    return act;
+}
+
+cudaError_t launch_quantize_acts(uint32_t type, const float* x, uint64_t rows, uint64_t k, void* scratch,
+                                 cudaStream_t s) {
+    ActPlanes act = planes_in(scratch, rows, k);
+    unsigned qgrid = (unsigned)std::max<uint64_t>(1, std::min<uint64_t>(rows * (k / 256), 148 * 8));
+    return launch_pdl(quantize_acts_kernel, qgrid, 256, 0, s, x, rows, k, type, const_cast<int8_t*>(act.planes),
+                      const_cast<float2*>(act.meta), const_cast<float*>(act.sum16));
+}
+
+cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
+                            float* dst, void* scratch, int* error_flag, cudaStream_t s) {
+    GemvArgs ga = {};
+    ga.w[0] = ga.w[1] = w;
+    ga.n = n;
+    ga.k = k;
+    ga.x = lhs;
+    ga.x_rows = (uint32_t)m;
+    ga.m = (uint32_t)m;
+    ga.dst = dst;
+    ga.error_flag = error_flag;
+    uint64_t tiles = (n + ROWS - 1) / ROWS;
+    if (acts_fit_in_smem(m, k)) return launch_typed<1, 0>(type, ga, (uint32_t)m, tiles, s);
+    cudaError_t e = launch_quantize_acts(type, lhs, m, k, scratch, s);
+    if (e != cudaSuccess) return e;
+    ga.act = planes_in(scratch, m, k);
+    return launch_typed<0, 0>(type, ga, (uint32_t)m, tiles, s);
+}
+
+cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s) {
+    GemvArgs ga = {};
+    ga.w[0] = g.w0;
+    ga.w[1] = g.w1 ? g.w1 : g.w0;
+    ga.n = g.n;
+    ga.k = g.k;
+    ga.expert_bytes = g.expert_bytes;
+    ga.x = g.x;
+    ga.x_rows = g.x_rows;
+    ga.dst = g.dst;
+    ga.jobs = g.jobs;
+    ga.n_jobs = g.n_jobs;
+    ga.act_rows = g.act_rows;
+    ga.clamp = g.clamp;
+    ga.swiglu = g.w1 != nullptr;
+    ga.error_flag = g.error_flag;
+    uint64_t tiles = (uint64_t)g.max_jobs * ((g.n + ROWS - 1) / ROWS);
+    if (g.planes == nullptr) return launch_typed<1, 1>(g.type, ga, g.rows_per_job, tiles, s);
+    ga.act = planes_in(g.planes, g.x_rows, g.k);
+    return launch_typed<0, 1>(g.type, ga, g.rows_per_job, tiles, s);
 }
 
 }  // namespace jq
