@@ -144,6 +144,74 @@ int32_t jq_embedding(const jq_weight* w, const uint32_t* ids, uint64_t n_ids, ui
  * borrowed tensors are read-only; always fails with JQ_E_INVALID. */
 int32_t jq_weight_from_float(jq_weight* w, const float* xs, uint64_t len);
 
+/* ── MoE layer ───────────────────────────────────────────────────────────
+ * Replaces `Moe::forward` of the three loaders: routing, per-expert gather,
+ * SwiGLU MLP over quantized expert banks, weighted scatter-add, optional
+ * shared expert (src/quantized_qwen3_moe.rs:412-520,
+ * src/quantized_deepseek2.rs:522-671, src/quantized_deepseek4.rs:1354-1492;
+ * Kimi routing rule src/kimi_k3.rs:256-282).  Routing, bucketing and the
+ * expert matmuls all run on the device; nothing is read back per layer. */
+#define JQ_GATE_SOFTMAX 0       /* qwen3moe, deepseek2 gating_func 1 */
+#define JQ_GATE_SIGMOID 1       /* deepseek2 gating_func 2 (V3, Kimi) */
+#define JQ_GATE_SQRT_SOFTPLUS 2 /* deepseek4 */
+
+typedef struct {
+    int32_t gating;          /* JQ_GATE_* */
+    uint32_t n_expert;       /* experts in the banks */
+    uint32_t n_used;         /* experts per token (top-k) */
+    uint32_t hidden;         /* model width (multiple of 256) */
+    uint32_t inter;          /* expert feed-forward width (multiple of 256) */
+    uint32_t n_group;        /* expert groups for group-limited selection (0 or 1 = off) */
+    uint32_t topk_group;     /* groups kept */
+    int32_t norm;            /* renormalise the selected weights (norm_topk_prob / expert_weights_norm) */
+    int32_t renorm_plus_eps; /* 0: divide by max(sum, 6.1035156e-5); 1: by sum + 1e-20 (Kimi) */
+    int32_t oob_policy;      /* expert id >= n_expert: 0 = fail with JQ_E_EXPERT_RANGE
+                                (src/quantized_qwen3_moe.rs:464-477), 1 = skip (src/quantized_deepseek4.rs:1439) */
+    float scale;             /* expert_weights_scale, applied when != 0 and != 1 */
+    float clamp;             /* SwiGLU clamp (src/quantized_deepseek4.rs:445-462), 0 = off */
+} jq_moe_config;
+
+/* `router`: host f32 [n_expert, hidden] (`ffn_gate_inp`); `bias`: host f32
+ * [n_expert] selection bias (`exp_probs_b`) or NULL.  gate / up / down: banks
+ * of n_expert contiguous experts, [n_expert*inter, hidden] twice and
+ * [n_expert*hidden, inter] (the layout `split_experts` slices).  sh_*: one
+ * shared expert or all NULL.  The weights must outlive the layer. */
+int32_t jq_moe_create(jq_ctx* ctx, const jq_moe_config* cfg, const float* router, const float* bias,
+                      const jq_weight* gate, const jq_weight* up, const jq_weight* down, const jq_weight* sh_gate,
+                      const jq_weight* sh_up, const jq_weight* sh_down, jq_moe** out);
+void jq_moe_free(jq_moe* m);
+
+/* Moe::forward with HOST buffers: x f32 [n_tokens, hidden] -> y f32
+ * [n_tokens, hidden].  `forced_ids` ([n_tokens, n_used], or NULL) replaces the
+ * top-k selection on hash-routed layers (`tid2eid[token_id]`,
+ * src/quantized_deepseek4.rs:1375-1398); weights still come from the gate. */
+int32_t jq_moe_forward(jq_moe* m, const float* x, uint64_t n_tokens, const uint32_t* forced_ids, float* y);
+
+/* Sizes the layer's device workspace for up to n_tokens tokens (and n_rows rows
+ * for jq_moe_experts_dev).  The *_dev entries never allocate: call this first
+ * (and before capturing a stream). */
+int32_t jq_moe_reserve(jq_moe* m, uint64_t n_tokens, uint64_t n_rows);
+
+/* The same with DEVICE buffers on a caller stream, no synchronisation. */
+int32_t jq_moe_forward_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, const uint32_t* forced_ids_dev,
+                           float* y_dev, void* stream);
+
+/* The two halves, for expert-parallel callers that exchange rows between
+ * devices in between: routing alone (ids, weights: [n_tokens, n_used]), and the
+ * expert MLPs alone over arbitrary rows, out[r] = MLP_{expert_ids[r]}(x[r])
+ * (unweighted; rows whose id is out of range come back as zeros). */
+int32_t jq_moe_route_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, const uint32_t* forced_ids_dev,
+                         uint32_t* ids_dev, float* wts_dev, void* stream);
+int32_t jq_moe_experts_dev(jq_moe* m, const float* x_dev, uint64_t n_rows, const uint32_t* expert_ids_dev,
+                           float* out_dev, void* stream);
+
+/* After synchronising: JQ_E_EXPERT_RANGE if an id was out of range under
+ * oob_policy 0, JQ_E_TIMEOUT as jq_device_status, else JQ_OK. */
+int32_t jq_moe_status(jq_moe* m);
+
+/* ids and weights chosen by the last forward (host copies), for inspection. */
+int32_t jq_moe_last_routing(jq_moe* m, uint64_t n_tokens, uint32_t* ids, float* wts);
+
 #ifdef __cplusplus
 }
 #endif

@@ -48,6 +48,15 @@ _SIGNATURES = {
     "jq_dequantize_dev": (i32, [vp, vp, u64, i32, vp]),
     "jq_embedding": (i32, [vp, vp, u64, u64, u64, vp]),
     "jq_weight_from_float": (i32, [vp, vp, u64]),
+    "jq_moe_create": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, pp]),
+    "jq_moe_free": (None, [vp]),
+    "jq_moe_forward": (i32, [vp, vp, u64, vp, vp]),
+    "jq_moe_reserve": (i32, [vp, u64, u64]),
+    "jq_moe_forward_dev": (i32, [vp, vp, u64, vp, vp, vp]),
+    "jq_moe_route_dev": (i32, [vp, vp, u64, vp, vp, vp, vp]),
+    "jq_moe_experts_dev": (i32, [vp, vp, u64, vp, vp, vp]),
+    "jq_moe_status": (i32, [vp]),
+    "jq_moe_last_routing": (i32, [vp, u64, vp, vp]),
 }
 
 

@@ -3,35 +3,21 @@
 // they replace are in include/joshua_b200.h.
 #include <cuda_fp16.h>
 
-#include <cstdlib>
-#include <map>
-#include <mutex>
-#include <new>
-#include <string>
-#include <vector>
-
-#include "../../include/joshua_b200.h"
-#include "common.cuh"
+#include "handles.cuh"
 
 namespace {
-
 thread_local std::string g_err;
+}
 
-int32_t fail(int32_t code, const std::string& msg) {
+int32_t jq_fail(int32_t code, const std::string& msg) {
     g_err = msg;
     return code;
 }
-int32_t fail_cuda(cudaError_t e, const char* what) {
-    return fail(e == cudaErrorMemoryAllocation ? jq::E_NOMEM : jq::E_CUDA,
-                std::string(what) + ": " + cudaGetErrorString(e));
+int32_t jq_fail_cuda(cudaError_t e, const char* what) {
+    return jq_fail(e == cudaErrorMemoryAllocation ? jq::E_NOMEM : jq::E_CUDA,
+                   std::string(what) + ": " + cudaGetErrorString(e));
 }
-#define JQ_CUDA(call)                                      \
-    do {                                                   \
-        cudaError_t e__ = (call);                          \
-        if (e__ != cudaSuccess) return fail_cuda(e__, #call); \
-    } while (0)
-
-const char* type_name(uint32_t t) {
+const char* jq_type_name(uint32_t t) {
     switch (t) {
         case jq::T_Q8_0: return "q8_0";
         case jq::T_Q2_K: return "q2_k";
@@ -41,95 +27,6 @@ const char* type_name(uint32_t t) {
         default: return "?";
     }
 }
-
-// A stream plus a grow-only device buffer, handed to one host-buffer call at a time.
-struct Workspace {
-    cudaStream_t stream = nullptr;
-    uint8_t* dev = nullptr;
-    size_t cap = 0;
-    int* flag = nullptr;  // device error flag (embedding id range)
-
-    cudaError_t reserve(size_t bytes) {
-        if (bytes <= cap) return cudaSuccess;
-        if (dev) cudaFree(dev);
-        dev = nullptr;
-        cap = 0;
-        size_t want = (bytes + (1u << 20) - 1) & ~((size_t)(1u << 20) - 1);
-        cudaError_t e = cudaMalloc(&dev, want);
-        if (e == cudaSuccess) cap = want;
-        return e;
-    }
-};
-
-}  // namespace
-
-// Scratch of the decode kernels (activation planes), one per caller stream.
-struct StreamScratch {
-    void* dev = nullptr;
-    size_t cap = 0;
-};
-
-struct jq_ctx {
-    int device = 0;
-    bool force_f32 = false;        // JQ_FORCE_F32_PATH=1: always take the exact-decode float kernels
-    int* status_host = nullptr;    // pinned, device-visible: set to 1 by a kernel whose bounded wait gave up
-    int* status_dev = nullptr;
-    std::mutex mu;
-    std::vector<Workspace*> idle;
-    std::map<cudaStream_t, StreamScratch> scratch;
-
-    // Scratch for `stream`, at least `bytes` large.  Growing it frees the old buffer (cudaFree
-    // waits for the device), so warm a stream up at its largest shape before capturing it.
-    cudaError_t scratch_for(cudaStream_t stream, size_t bytes, void** out) {
-        std::lock_guard<std::mutex> g(mu);
-        StreamScratch& sc = scratch[stream];
-        if (bytes > sc.cap) {
-            if (sc.dev) cudaFree(sc.dev);
-            sc.dev = nullptr;
-            sc.cap = 0;
-            size_t want = (bytes + (1u << 20) - 1) & ~((size_t)(1u << 20) - 1);
-            cudaError_t e = cudaMalloc(&sc.dev, want);
-            if (e != cudaSuccess) return e;
-            sc.cap = want;
-        }
-        *out = sc.dev;
-        return cudaSuccess;
-    }
-
-    Workspace* acquire() {
-        {
-            std::lock_guard<std::mutex> g(mu);
-            if (!idle.empty()) {
-                Workspace* w = idle.back();
-                idle.pop_back();
-                return w;
-            }
-        }
-        Workspace* w = new (std::nothrow) Workspace();
-        if (!w) return nullptr;
-        if (cudaStreamCreateWithFlags(&w->stream, cudaStreamNonBlocking) != cudaSuccess ||
-            cudaMalloc(&w->flag, sizeof(int)) != cudaSuccess) {
-            if (w->stream) cudaStreamDestroy(w->stream);
-            delete w;
-            return nullptr;
-        }
-        cudaMemsetAsync(w->flag, 0, sizeof(int), w->stream);
-        return w;
-    }
-    void release(Workspace* w) {
-        std::lock_guard<std::mutex> g(mu);
-        idle.push_back(w);
-    }
-};
-
-struct jq_weight {
-    jq_ctx* ctx;
-    uint32_t type;
-    jq::Format fmt;
-    const uint8_t* dev;
-    uint64_t n_blocks;
-    bool owns;
-};
 
 namespace {
 
@@ -144,25 +41,27 @@ struct WsGuard {
 // Shape rules of src/quant_matmul.rs:133-165 / src/iq2xxs.rs:126-153 / src/mxfp4.rs:142-172.
 int32_t validate_matmul(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, uint64_t lhs_len, uint64_t dst_len,
                         bool check_lens) {
-    if (!w) return fail(jq::E_INVALID, "matmul: NULL weight handle");
-    const char* name = type_name(w->type);
+    if (!w) return jq_fail(jq::E_INVALID, "matmul: NULL weight handle");
+    const char* name = jq_type_name(w->type);
     if (k % w->fmt.elems != 0)
-        return fail(jq::E_INVALID, std::string(name) + " matmul: k=" + std::to_string(k) +
+        return jq_fail(jq::E_INVALID, std::string(name) + " matmul: k=" + std::to_string(k) +
                                        " is not a multiple of the block size " + std::to_string(w->fmt.elems));
     uint64_t bpr = k / w->fmt.elems;
     if (w->n_blocks != n * bpr)
-        return fail(jq::E_INVALID, std::string(name) + " matmul: rhs holds " + std::to_string(w->n_blocks) +
+        return jq_fail(jq::E_INVALID, std::string(name) + " matmul: rhs holds " + std::to_string(w->n_blocks) +
                                        " blocks, expected " + std::to_string(n * bpr));
     if (check_lens && (lhs_len != m * k || dst_len != m * n))
-        return fail(jq::E_INVALID, std::string(name) + " matmul: lhs/dst sized " + std::to_string(lhs_len) + "/" +
+        return jq_fail(jq::E_INVALID, std::string(name) + " matmul: lhs/dst sized " + std::to_string(lhs_len) + "/" +
                                        std::to_string(dst_len) + " expected " + std::to_string(m * k) + "/" +
                                        std::to_string(m * n));
     return jq::OK;
 }
 
 // Picks the kernel for a device-resident product.
-int32_t matmul_device(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const float* lhs, float* dst,
-                      cudaStream_t s) {
+}  // namespace
+
+int32_t jq_matmul_device(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const float* lhs, float* dst,
+                         cudaStream_t s) {
     jq_ctx* ctx = w->ctx;
     if (!ctx->force_f32 && jq::gemv_mma_supports(w->type, w->dev, n, k, m)) {
         void* scratch = nullptr;
@@ -174,9 +73,11 @@ int32_t matmul_device(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, co
     return jq::OK;
 }
 
+namespace {
+
 int32_t check_device_status(const jq_ctx* ctx) {
     if (ctx->status_host && *static_cast<volatile int*>(ctx->status_host) != 0)
-        return fail(jq::E_TIMEOUT, "a bounded wait inside a kernel gave up (device status flag is set)");
+        return jq_fail(jq::E_TIMEOUT, "a bounded wait inside a kernel gave up (device status flag is set)");
     return jq::OK;
 }
 
@@ -199,34 +100,34 @@ const char* jq_last_error(void) { return g_err.c_str(); }
 
 int32_t jq_block_size(uint32_t type, uint64_t* elems, uint64_t* bytes) {
     jq::Format f;
-    if (!jq::format_of(type, &f)) return fail(jq::E_TYPE, "unsupported GGUF type id " + std::to_string(type));
+    if (!jq::format_of(type, &f)) return jq_fail(jq::E_TYPE, "unsupported GGUF type id " + std::to_string(type));
     if (elems) *elems = f.elems;
     if (bytes) *bytes = f.bytes;
     return jq::OK;
 }
 
 int32_t jq_init(int32_t device, jq_ctx** out) {
-    if (!out) return fail(jq::E_INVALID, "jq_init: NULL out");
+    if (!out) return jq_fail(jq::E_INVALID, "jq_init: NULL out");
     *out = nullptr;
     int count = 0;
     cudaError_t e = cudaGetDeviceCount(&count);
     if (e != cudaSuccess || count == 0)
-        return fail(jq::E_CUDA, std::string("jq_init: no CUDA device (") +
+        return jq_fail(jq::E_CUDA, std::string("jq_init: no CUDA device (") +
                                     (e != cudaSuccess ? cudaGetErrorString(e) : "device count 0") +
                                     "); this library has no CPU path");
     if (device < 0 || device >= count)
-        return fail(jq::E_INVALID, "jq_init: device " + std::to_string(device) + " out of " + std::to_string(count));
+        return jq_fail(jq::E_INVALID, "jq_init: device " + std::to_string(device) + " out of " + std::to_string(count));
     JQ_CUDA(cudaSetDevice(device));
     cudaDeviceProp prop;
     JQ_CUDA(cudaGetDeviceProperties(&prop, device));
     if (prop.major != 10)
-        return fail(jq::E_CUDA, "jq_init: kernels are built for sm_100a only, device is sm_" +
+        return jq_fail(jq::E_CUDA, "jq_init: kernels are built for sm_100a only, device is sm_" +
                                     std::to_string(prop.major) + std::to_string(prop.minor));
     JQ_CUDA(jq::tables_dequant());
     JQ_CUDA(jq::tables_gemv_f32());
     JQ_CUDA(jq::tables_gemv_mma());
     jq_ctx* c = new (std::nothrow) jq_ctx();
-    if (!c) return fail(jq::E_NOMEM, "jq_init: out of host memory");
+    if (!c) return jq_fail(jq::E_NOMEM, "jq_init: out of host memory");
     c->device = device;
     const char* f = std::getenv("JQ_FORCE_F32_PATH");
     c->force_f32 = f && f[0] == '1';
@@ -234,7 +135,7 @@ int32_t jq_init(int32_t device, jq_ctx** out) {
     if (he == cudaSuccess) he = cudaHostGetDevicePointer(&c->status_dev, c->status_host, 0);
     if (he != cudaSuccess) {
         delete c;
-        return fail_cuda(he, "jq_init: status flag");
+        return jq_fail_cuda(he, "jq_init: status flag");
     }
     *c->status_host = 0;
     *out = c;
@@ -260,7 +161,7 @@ void jq_free(jq_ctx* ctx) {
 static int32_t make_weight(jq_ctx* ctx, uint32_t type, const uint8_t* dev, uint64_t nbytes, bool owns,
                            jq_weight** out) {
     jq_weight* w = new (std::nothrow) jq_weight();
-    if (!w) return fail(jq::E_NOMEM, "out of host memory");
+    if (!w) return jq_fail(jq::E_NOMEM, "out of host memory");
     w->ctx = ctx;
     w->type = type;
     jq::format_of(type, &w->fmt);
@@ -273,16 +174,16 @@ static int32_t make_weight(jq_ctx* ctx, uint32_t type, const uint8_t* dev, uint6
 
 static int32_t check_blocks(const char* who, uint32_t type, uint64_t nbytes, jq::Format* f) {
     if (!jq::format_of(type, f))
-        return fail(jq::E_TYPE, std::string(who) + ": unsupported GGUF type id " + std::to_string(type));
+        return jq_fail(jq::E_TYPE, std::string(who) + ": unsupported GGUF type id " + std::to_string(type));
     if (nbytes % f->bytes != 0)
-        return fail(jq::E_INVALID, std::string(type_name(type)) + ": " + std::to_string(nbytes) +
+        return jq_fail(jq::E_INVALID, std::string(jq_type_name(type)) + ": " + std::to_string(nbytes) +
                                        " bytes is not a whole number of " + std::to_string(f->bytes) +
                                        " byte blocks");
     return jq::OK;
 }
 
 int32_t jq_weight_upload(jq_ctx* ctx, uint32_t type, const void* bytes, uint64_t nbytes, jq_weight** out) {
-    if (!ctx || !out || (!bytes && nbytes)) return fail(jq::E_INVALID, "jq_weight_upload: NULL argument");
+    if (!ctx || !out || (!bytes && nbytes)) return jq_fail(jq::E_INVALID, "jq_weight_upload: NULL argument");
     *out = nullptr;
     jq::Format f;
     if (int32_t rc = check_blocks("jq_weight_upload", type, nbytes, &f)) return rc;
@@ -294,7 +195,7 @@ int32_t jq_weight_upload(jq_ctx* ctx, uint32_t type, const void* bytes, uint64_t
     if (e == cudaSuccess) e = cudaMemset(dev + nbytes, 0, 16);
     if (e != cudaSuccess) {
         cudaFree(dev);
-        return fail_cuda(e, "jq_weight_upload copy");
+        return jq_fail_cuda(e, "jq_weight_upload copy");
     }
     int32_t rc = make_weight(ctx, type, dev, nbytes, true, out);
     if (rc) cudaFree(dev);
@@ -303,20 +204,20 @@ int32_t jq_weight_upload(jq_ctx* ctx, uint32_t type, const void* bytes, uint64_t
 
 int32_t jq_weight_from_device(jq_ctx* ctx, uint32_t type, const void* device_bytes, uint64_t nbytes,
                               jq_weight** out) {
-    if (!ctx || !out || (!device_bytes && nbytes)) return fail(jq::E_INVALID, "jq_weight_from_device: NULL argument");
+    if (!ctx || !out || (!device_bytes && nbytes)) return jq_fail(jq::E_INVALID, "jq_weight_from_device: NULL argument");
     *out = nullptr;
     jq::Format f;
     if (int32_t rc = check_blocks("jq_weight_from_device", type, nbytes, &f)) return rc;
     if (reinterpret_cast<uintptr_t>(device_bytes) % 16 != 0)
-        return fail(jq::E_INVALID, "jq_weight_from_device: device pointer must be 16-byte aligned");
+        return jq_fail(jq::E_INVALID, "jq_weight_from_device: device pointer must be 16-byte aligned");
     return make_weight(ctx, type, static_cast<const uint8_t*>(device_bytes), nbytes, false, out);
 }
 
 int32_t jq_weight_slice(const jq_weight* parent, uint64_t block0, uint64_t n_blocks, jq_weight** out) {
-    if (!parent || !out) return fail(jq::E_INVALID, "jq_weight_slice: NULL argument");
+    if (!parent || !out) return jq_fail(jq::E_INVALID, "jq_weight_slice: NULL argument");
     *out = nullptr;
     if (block0 > parent->n_blocks || n_blocks > parent->n_blocks - block0)
-        return fail(jq::E_INVALID, "jq_weight_slice: blocks [" + std::to_string(block0) + ", +" +
+        return jq_fail(jq::E_INVALID, "jq_weight_slice: blocks [" + std::to_string(block0) + ", +" +
                                        std::to_string(n_blocks) + ") outside the tensor's " +
                                        std::to_string(parent->n_blocks));
     return make_weight(parent->ctx, parent->type, parent->dev + block0 * parent->fmt.bytes,
@@ -341,27 +242,27 @@ int32_t jq_matmul_t_dev(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, 
                         float* dst_dev, void* stream) {
     if (int32_t rc = validate_matmul(w, m, k, n, 0, 0, false)) return rc;
     if (m == 0 || n == 0) return jq::OK;
-    if (!lhs_dev || !dst_dev) return fail(jq::E_INVALID, "jq_matmul_t_dev: NULL buffer");
+    if (!lhs_dev || !dst_dev) return jq_fail(jq::E_INVALID, "jq_matmul_t_dev: NULL buffer");
     if (reinterpret_cast<uintptr_t>(lhs_dev) % 16 != 0)
-        return fail(jq::E_INVALID, "jq_matmul_t_dev: lhs must be 16-byte aligned");
-    return matmul_device(w, m, k, n, lhs_dev, dst_dev, static_cast<cudaStream_t>(stream));
+        return jq_fail(jq::E_INVALID, "jq_matmul_t_dev: lhs must be 16-byte aligned");
+    return jq_matmul_device(w, m, k, n, lhs_dev, dst_dev, static_cast<cudaStream_t>(stream));
 }
 
 int32_t jq_matmul_t(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const float* lhs, uint64_t lhs_len,
                     float* dst, uint64_t dst_len) {
     if (int32_t rc = validate_matmul(w, m, k, n, lhs_len, dst_len, true)) return rc;
     if (m == 0 || n == 0) return jq::OK;
-    if (!lhs || !dst) return fail(jq::E_INVALID, "jq_matmul_t: NULL buffer");
+    if (!lhs || !dst) return jq_fail(jq::E_INVALID, "jq_matmul_t: NULL buffer");
     JQ_CUDA(cudaSetDevice(w->ctx->device));
     WsGuard g{w->ctx, w->ctx->acquire()};
-    if (!g.ws) return fail(jq::E_NOMEM, "jq_matmul_t: no workspace");
+    if (!g.ws) return jq_fail(jq::E_NOMEM, "jq_matmul_t: no workspace");
     size_t lhs_bytes = align_up(m * k * 4, 256), dst_bytes = m * n * 4;
     JQ_CUDA(g.ws->reserve(lhs_bytes + dst_bytes));
     float* d_lhs = reinterpret_cast<float*>(g.ws->dev);
     float* d_dst = reinterpret_cast<float*>(g.ws->dev + lhs_bytes);
     cudaStream_t s = g.ws->stream;
     JQ_CUDA(cudaMemcpyAsync(d_lhs, lhs, m * k * 4, cudaMemcpyHostToDevice, s));
-    if (int32_t rc = matmul_device(w, m, k, n, d_lhs, d_dst, s)) return rc;
+    if (int32_t rc = jq_matmul_device(w, m, k, n, d_lhs, d_dst, s)) return rc;
     JQ_CUDA(cudaMemcpyAsync(dst, d_dst, dst_bytes, cudaMemcpyDeviceToHost, s));
     JQ_CUDA(cudaStreamSynchronize(s));
     return check_device_status(w->ctx);
@@ -371,10 +272,10 @@ int32_t jq_matmul_t_f16(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, 
                         uint64_t lhs_len, uint16_t* dst, uint64_t dst_len) {
     if (int32_t rc = validate_matmul(w, m, k, n, lhs_len, dst_len, true)) return rc;
     if (m == 0 || n == 0) return jq::OK;
-    if (!lhs || !dst) return fail(jq::E_INVALID, "jq_matmul_t_f16: NULL buffer");
+    if (!lhs || !dst) return jq_fail(jq::E_INVALID, "jq_matmul_t_f16: NULL buffer");
     JQ_CUDA(cudaSetDevice(w->ctx->device));
     WsGuard g{w->ctx, w->ctx->acquire()};
-    if (!g.ws) return fail(jq::E_NOMEM, "jq_matmul_t_f16: no workspace");
+    if (!g.ws) return jq_fail(jq::E_NOMEM, "jq_matmul_t_f16: no workspace");
     size_t a = align_up(m * k * 4, 256), b = align_up(m * n * 4, 256), c = align_up(m * k * 2, 256), d = m * n * 2;
     JQ_CUDA(g.ws->reserve(a + b + c + d));
     float* d_lhs = reinterpret_cast<float*>(g.ws->dev);
@@ -384,7 +285,7 @@ int32_t jq_matmul_t_f16(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, 
     cudaStream_t s = g.ws->stream;
     JQ_CUDA(cudaMemcpyAsync(h_lhs, lhs, m * k * 2, cudaMemcpyHostToDevice, s));
     f16_to_f32_kernel<<<(unsigned)((m * k + 255) / 256), 256, 0, s>>>(h_lhs, d_lhs, m * k);
-    if (int32_t rc = matmul_device(w, m, k, n, d_lhs, d_dst, s)) return rc;
+    if (int32_t rc = jq_matmul_device(w, m, k, n, d_lhs, d_dst, s)) return rc;
     f32_to_f16_kernel<<<(unsigned)((m * n + 255) / 256), 256, 0, s>>>(d_dst, h_dst, m * n);
     JQ_CUDA(cudaGetLastError());
     JQ_CUDA(cudaMemcpyAsync(dst, h_dst, d, cudaMemcpyDeviceToHost, s));
@@ -393,24 +294,24 @@ int32_t jq_matmul_t_f16(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, 
 }
 
 int32_t jq_dequantize_dev(const jq_weight* w, float* out_dev, uint64_t elem_count, int32_t two_step, void* stream) {
-    if (!w) return fail(jq::E_INVALID, "jq_dequantize: NULL weight handle");
+    if (!w) return jq_fail(jq::E_INVALID, "jq_dequantize: NULL weight handle");
     if (elem_count != w->n_blocks * w->fmt.elems)
-        return fail(jq::E_INVALID, std::string(type_name(w->type)) + ": output holds " + std::to_string(elem_count) +
+        return jq_fail(jq::E_INVALID, std::string(jq_type_name(w->type)) + ": output holds " + std::to_string(elem_count) +
                                        " values, expected " + std::to_string(w->n_blocks * w->fmt.elems));
     if (elem_count == 0) return jq::OK;
     if (!out_dev || reinterpret_cast<uintptr_t>(out_dev) % 16 != 0)
-        return fail(jq::E_INVALID, "jq_dequantize_dev: output must be a 16-byte aligned device buffer");
+        return jq_fail(jq::E_INVALID, "jq_dequantize_dev: output must be a 16-byte aligned device buffer");
     JQ_CUDA(jq::launch_dequant(w->type, w->dev, w->n_blocks, out_dev, two_step != 0,
                                static_cast<cudaStream_t>(stream)));
     return jq::OK;
 }
 
 int32_t jq_dequantize(const jq_weight* w, float* out, uint64_t elem_count, int32_t two_step) {
-    if (!w) return fail(jq::E_INVALID, "jq_dequantize: NULL weight handle");
-    if (elem_count && !out) return fail(jq::E_INVALID, "jq_dequantize: NULL output");
+    if (!w) return jq_fail(jq::E_INVALID, "jq_dequantize: NULL weight handle");
+    if (elem_count && !out) return jq_fail(jq::E_INVALID, "jq_dequantize: NULL output");
     JQ_CUDA(cudaSetDevice(w->ctx->device));
     WsGuard g{w->ctx, w->ctx->acquire()};
-    if (!g.ws) return fail(jq::E_NOMEM, "jq_dequantize: no workspace");
+    if (!g.ws) return jq_fail(jq::E_NOMEM, "jq_dequantize: no workspace");
     JQ_CUDA(g.ws->reserve(elem_count * 4 + 16));
     if (int32_t rc = jq_dequantize_dev(w, reinterpret_cast<float*>(g.ws->dev), elem_count, two_step, g.ws->stream))
         return rc;
@@ -422,22 +323,22 @@ int32_t jq_dequantize(const jq_weight* w, float* out, uint64_t elem_count, int32
 
 int32_t jq_embedding(const jq_weight* w, const uint32_t* ids, uint64_t n_ids, uint64_t rows, uint64_t hidden,
                      float* out) {
-    if (!w) return fail(jq::E_INVALID, "jq_embedding: NULL weight handle");
+    if (!w) return jq_fail(jq::E_INVALID, "jq_embedding: NULL weight handle");
     if (hidden % w->fmt.elems != 0)
-        return fail(jq::E_INVALID, "quantized embedding hidden size " + std::to_string(hidden) +
+        return jq_fail(jq::E_INVALID, "quantized embedding hidden size " + std::to_string(hidden) +
                                        " is not divisible by block size " + std::to_string(w->fmt.elems));
     if (w->n_blocks != rows * (hidden / w->fmt.elems))
-        return fail(jq::E_INVALID, "quantized tensor has " + std::to_string(w->n_blocks) + " blocks, expected " +
+        return jq_fail(jq::E_INVALID, "quantized tensor has " + std::to_string(w->n_blocks) + " blocks, expected " +
                                        std::to_string(rows * (hidden / w->fmt.elems)));
     if (n_ids == 0) return jq::OK;
-    if (!ids || !out) return fail(jq::E_INVALID, "jq_embedding: NULL buffer");
+    if (!ids || !out) return jq_fail(jq::E_INVALID, "jq_embedding: NULL buffer");
     for (uint64_t i = 0; i < n_ids; ++i)
         if (ids[i] >= rows)
-            return fail(jq::E_INVALID, "embedding id " + std::to_string(ids[i]) + " is out of range for " +
+            return jq_fail(jq::E_INVALID, "embedding id " + std::to_string(ids[i]) + " is out of range for " +
                                            std::to_string(rows) + " rows");
     JQ_CUDA(cudaSetDevice(w->ctx->device));
     WsGuard g{w->ctx, w->ctx->acquire()};
-    if (!g.ws) return fail(jq::E_NOMEM, "jq_embedding: no workspace");
+    if (!g.ws) return jq_fail(jq::E_NOMEM, "jq_embedding: no workspace");
     size_t out_bytes = align_up(n_ids * hidden * 4, 256);
     JQ_CUDA(g.ws->reserve(out_bytes + n_ids * 4));
     float* d_out = reinterpret_cast<float*>(g.ws->dev);
@@ -451,12 +352,12 @@ int32_t jq_embedding(const jq_weight* w, const uint32_t* ids, uint64_t n_ids, ui
 }
 
 int32_t jq_device_status(const jq_ctx* ctx) {
-    if (!ctx) return fail(jq::E_INVALID, "jq_device_status: NULL context");
+    if (!ctx) return jq_fail(jq::E_INVALID, "jq_device_status: NULL context");
     return check_device_status(ctx);
 }
 
 int32_t jq_weight_from_float(jq_weight*, const float*, uint64_t) {
-    return fail(jq::E_INVALID, "cannot quantize into a read-only device-resident tensor");
+    return jq_fail(jq::E_INVALID, "cannot quantize into a read-only device-resident tensor");
 }
 
 }  // extern "C"

@@ -77,4 +77,25 @@ struct GroupedLaunch {
 };
 cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s);
 
+// moe.cu: routing on the device
+enum : int32_t { MOE_GATE_SOFTMAX = 0, MOE_GATE_SIGMOID = 1, MOE_GATE_SQRT_SOFTPLUS = 2 };
+struct MoeRouteParams {
+    int32_t gating;           // MOE_GATE_*
+    uint32_t n_expert, n_used;
+    uint32_t n_group, topk_group;
+    int32_t norm;             // renormalise the selected weights
+    int32_t renorm_plus_eps;  // 0: / max(sum, 6.1035156e-5); 1: / (sum + 1e-20)
+    float scale;              // applied when != 0 and != 1
+};
+cudaError_t launch_moe_logits(const float* x, const float* router, uint32_t T, uint32_t E, uint32_t h, float* logits,
+                              cudaStream_t s);
+cudaError_t launch_moe_route(const float* logits, const MoeRouteParams& rp, uint32_t T, const float* bias,
+                             const uint32_t* forced_ids, uint32_t* ids, float* wts, cudaStream_t s);
+cudaError_t launch_moe_jobs(const uint32_t* ids, uint32_t T, uint32_t K, uint32_t E, uint32_t rows_per_job,
+                            uint32_t* list_token, uint32_t* inv, MoeJob* jobs, uint32_t* n_jobs, uint32_t* n_list,
+                            int* bad_id, cudaStream_t s);
+cudaError_t launch_moe_combine(const float* out, const uint32_t* inv, const float* wts, const float* shared, uint32_t T,
+                               uint32_t K, uint32_t h, float* y, cudaStream_t s);
+cudaError_t launch_swiglu(const float* g, const float* u, uint64_t n, float clamp, float* out, cudaStream_t s);
+
 }  // namespace jq

@@ -1,0 +1,114 @@
+// Internal definitions shared by the translation units that implement the C ABI.
+#pragma once
+
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/joshua_b200.h"
+#include "common.cuh"
+
+// error reporting (thread-local message behind jq_last_error)
+int32_t jq_fail(int32_t code, const std::string& msg);
+int32_t jq_fail_cuda(cudaError_t e, const char* what);
+#define JQ_CUDA(call)                                         \
+    do {                                                      \
+        cudaError_t e__ = (call);                             \
+        if (e__ != cudaSuccess) return jq_fail_cuda(e__, #call); \
+    } while (0)
+
+const char* jq_type_name(uint32_t t);
+
+// A stream plus a grow-only device buffer, handed to one host-buffer call at a time.
+struct Workspace {
+    cudaStream_t stream = nullptr;
+    uint8_t* dev = nullptr;
+    size_t cap = 0;
+    int* flag = nullptr;  // device error flag (embedding id range)
+
+    cudaError_t reserve(size_t bytes) {
+        if (bytes <= cap) return cudaSuccess;
+        if (dev) cudaFree(dev);
+        dev = nullptr;
+        cap = 0;
+        size_t want = (bytes + (1u << 20) - 1) & ~((size_t)(1u << 20) - 1);
+        cudaError_t e = cudaMalloc(&dev, want);
+        if (e == cudaSuccess) cap = want;
+        return e;
+    }
+};
+
+// Scratch of the decode kernels (activation planes), one per caller stream.
+struct StreamScratch {
+    void* dev = nullptr;
+    size_t cap = 0;
+};
+
+struct jq_ctx {
+    int device = 0;
+    bool force_f32 = false;        // JQ_FORCE_F32_PATH=1: always take the exact-decode float kernels
+    int* status_host = nullptr;    // pinned, device-visible: set to 1 by a kernel whose bounded wait gave up
+    int* status_dev = nullptr;
+    std::mutex mu;
+    std::vector<Workspace*> idle;
+    std::map<cudaStream_t, StreamScratch> scratch;
+
+    // Scratch for `stream`, at least `bytes` large.  Growing it frees the old buffer (cudaFree
+    // waits for the device), so warm a stream up at its largest shape before capturing it.
+    cudaError_t scratch_for(cudaStream_t stream, size_t bytes, void** out) {
+        std::lock_guard<std::mutex> g(mu);
+        StreamScratch& sc = scratch[stream];
+        if (bytes > sc.cap) {
+            if (sc.dev) cudaFree(sc.dev);
+            sc.dev = nullptr;
+            sc.cap = 0;
+            size_t want = (bytes + (1u << 20) - 1) & ~((size_t)(1u << 20) - 1);
+            cudaError_t e = cudaMalloc(&sc.dev, want);
+            if (e != cudaSuccess) return e;
+            sc.cap = want;
+        }
+        *out = sc.dev;
+        return cudaSuccess;
+    }
+
+    Workspace* acquire() {
+        {
+            std::lock_guard<std::mutex> g(mu);
+            if (!idle.empty()) {
+                Workspace* w = idle.back();
+                idle.pop_back();
+                return w;
+            }
+        }
+        Workspace* w = new (std::nothrow) Workspace();
+        if (!w) return nullptr;
+        if (cudaStreamCreateWithFlags(&w->stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaMalloc(&w->flag, sizeof(int)) != cudaSuccess) {
+            if (w->stream) cudaStreamDestroy(w->stream);
+            delete w;
+            return nullptr;
+        }
+        cudaMemsetAsync(w->flag, 0, sizeof(int), w->stream);
+        return w;
+    }
+    void release(Workspace* w) {
+        std::lock_guard<std::mutex> g(mu);
+        idle.push_back(w);
+    }
+};
+
+struct jq_weight {
+    jq_ctx* ctx;
+    uint32_t type;
+    jq::Format fmt;
+    const uint8_t* dev;
+    uint64_t n_blocks;
+    bool owns;
+};
+
+// Picks the kernel for a device-resident product (abi.cu).
+int32_t jq_matmul_device(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const float* lhs, float* dst,
+                         cudaStream_t s);

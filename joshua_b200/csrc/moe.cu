@@ -1,0 +1,330 @@
+// Device-side MoE routing: router logits, gating + top-k, and the expert-sorted job list that feeds the
+// grouped matmul, plus the weighted combine.  Replaces the host-side routing and bucketing of the
+// reference's loaders, which read the ids and weights back to the host on every layer
+// (src/quantized_qwen3_moe.rs:424-520, src/quantized_deepseek2.rs:522-671,
+// src/quantized_deepseek4.rs:1354-1492, src/kimi_k3.rs:256-282).  Nothing here synchronises with the host.
+#include "common.cuh"
+
+namespace jq {
+
+namespace {
+
+// logits[t, e] = sum_j x[t, j] * router[e, j]: one warp per (token, expert) pair, f32.
+__global__ void __launch_bounds__(256) moe_logits_kernel(const float* __restrict__ x, const float* __restrict__ router,
+                                                         uint32_t T, uint32_t E, uint32_t h,
+                                                         float* __restrict__ logits) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t lane = threadIdx.x & 31;
+    const uint64_t total = (uint64_t)T * E;
+    for (uint64_t p = blockIdx.x * 8ull + (threadIdx.x >> 5); p < total; p += gridDim.x * 8ull) {
+        const uint32_t t = (uint32_t)(p / E), e = (uint32_t)(p % E);
+        const float4* a = reinterpret_cast<const float4*>(x + (uint64_t)t * h);
+        const float4* b = reinterpret_cast<const float4*>(router + (uint64_t)e * h);
+        float acc = 0.0f;
+        for (uint32_t j = lane; j < h / 4; j += 32) {
+            float4 u = __ldg(a + j), v = __ldg(b + j);
+            acc = fmaf(u.x, v.x, acc);
+            acc = fmaf(u.y, v.y, acc);
+            acc = fmaf(u.z, v.z, acc);
+            acc = fmaf(u.w, v.w, acc);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+        if (lane == 0) logits[p] = acc;
+    }
+}
+
+// Warp-wide arg-max over values held one-per-slot in shared memory, ties to the lower index (the order a
+// stable descending sort gives).  `taken` marks slots already chosen.
+__device__ __forceinline__ uint32_t warp_argmax(const float* v, const uint8_t* taken, uint32_t n, uint32_t lane) {
+    float best = -INFINITY;
+    uint32_t idx = 0xFFFFFFFFu;
+    for (uint32_t i = lane; i < n; i += 32) {
+        float f = v[i];
+        if (!taken[i] && (idx == 0xFFFFFFFFu || f > best)) {  // strictly greater keeps the lower index
+            best = f;
+            idx = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ob = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+        uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, idx, o);
+        bool take = oi != 0xFFFFFFFFu && (idx == 0xFFFFFFFFu || ob > best || (ob == best && oi < idx));
+        if (take) {
+            best = ob;
+            idx = oi;
+        }
+    }
+    return idx;
+}
+
+constexpr uint32_t MAX_EXPERTS = 512;
+
+// One warp per token: scores, selection (bias, group limit), top-k, weights.
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, MoeRouteParams rp, uint32_t T,
+                                                        const float* __restrict__ bias,
+                                                        const uint32_t* __restrict__ forced_ids,
+                                                        uint32_t* __restrict__ ids, float* __restrict__ wts) {
+    __shared__ float s_prob[4][MAX_EXPERTS];
+    __shared__ float s_sel[4][MAX_EXPERTS];
+    __shared__ uint8_t s_taken[4][MAX_EXPERTS];
+    __shared__ float s_group[4][64];
+    __shared__ uint8_t s_gtaken[4][64];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t lane = threadIdx.x & 31, wq = threadIdx.x >> 5;
+    const uint32_t E = rp.n_expert, K = rp.n_used;
+    float* prob = s_prob[wq];
+    float* sel = s_sel[wq];
+    uint8_t* taken = s_taken[wq];
+    for (uint32_t t = blockIdx.x * 4 + wq; t < T; t += gridDim.x * 4) {
+        const float* lg = logits + (uint64_t)t * E;
+        // scores
+        if (rp.gating == MOE_GATE_SOFTMAX) {
+            float mx = -INFINITY;
+            for (uint32_t e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+            float sum = 0.0f;
+            for (uint32_t e = lane; e < E; e += 32) {
+                float p = expf(lg[e] - mx);
+                prob[e] = p;
+                sum += p;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+            for (uint32_t e = lane; e < E; e += 32) prob[e] = prob[e] / sum;
+        } else if (rp.gating == MOE_GATE_SIGMOID) {
+            for (uint32_t e = lane; e < E; e += 32) prob[e] = 1.0f / (1.0f + expf(-lg[e]));
+        } else {  // sqrt(softplus), softplus(x) = max(x, 0) + log(1 + exp(-|x|))
+            for (uint32_t e = lane; e < E; e += 32) {
+                float v = lg[e];
+                prob[e] = sqrtf(fmaxf(v, 0.0f) + logf(expf(-fabsf(v)) + 1.0f));
+            }
+        }
+        for (uint32_t e = lane; e < E; e += 32) {
+            sel[e] = bias ? prob[e] + bias[e] : prob[e];
+            taken[e] = 0;
+        }
+        __syncwarp();
+        uint32_t* id = ids + (uint64_t)t * K;
+        float* w = wts + (uint64_t)t * K;
+        if (forced_ids) {
+            // hash-routed layers: ids come from a token-id table, weights from the gate scores
+            for (uint32_t s = lane; s < K; s += 32) id[s] = forced_ids[(uint64_t)t * K + s];
+        } else {
+            if (rp.n_group > 1) {
+                // group-limited selection: score groups by their two best members (sigmoid) or their best
+                // member (softmax), keep the top `topk_group`, push everything else down by 1e30
+                const uint32_t per = E / rp.n_group;
+                for (uint32_t g = lane; g < rp.n_group; g += 32) {
+                    const float* p = sel + g * per;
+                    float b1 = -INFINITY, b2 = -INFINITY;
+                    for (uint32_t i = 0; i < per; ++i) {
+                        float f = p[i];
+                        if (f > b1) {
+                            b2 = b1;
+                            b1 = f;
+                        } else if (f > b2) {
+                            b2 = f;
+                        }
+                    }
+                    s_group[wq][g] = rp.gating == MOE_GATE_SIGMOID ? b1 + b2 : b1;
+                    s_gtaken[wq][g] = 0;
+                }
+                __syncwarp();
+                for (uint32_t r = 0; r < rp.topk_group; ++r) {
+                    uint32_t g = warp_argmax(s_group[wq], s_gtaken[wq], rp.n_group, lane);
+                    __syncwarp();
+                    if (lane == 0) s_gtaken[wq][g] = 1;
+                    __syncwarp();
+                }
+                for (uint32_t e = lane; e < E; e += 32) {
+                    float mask = s_gtaken[wq][e / per] ? 1.0f : 0.0f;
+                    sel[e] = sel[e] + (mask * 1e30f + -1e30f);
+                }
+                __syncwarp();
+            }
+            for (uint32_t s = 0; s < K; ++s) {
+                uint32_t e = warp_argmax(sel, taken, E, lane);
+                __syncwarp();
+                if (lane == 0) {
+                    taken[e] = 1;
+                    id[s] = e;
+                }
+                __syncwarp();
+            }
+        }
+        __syncwarp();
+        // weights from the unbiased scores of the chosen experts
+        if (lane == 0) {
+            float sum = 0.0f;
+            for (uint32_t s = 0; s < K; ++s) {
+                uint32_t e = id[s];
+                float p = e < E ? prob[e] : 0.0f;
+                w[s] = p;
+                sum += p;
+            }
+            if (rp.norm) {
+                float denom = rp.renorm_plus_eps ? sum + 1e-20f : fmaxf(sum, 6.1035156e-5f);
+                for (uint32_t s = 0; s < K; ++s) w[s] = w[s] / denom;
+            }
+            if (rp.scale != 0.0f && rp.scale != 1.0f)
+                for (uint32_t s = 0; s < K; ++s) w[s] = w[s] * rp.scale;
+        }
+        __syncwarp();
+    }
+}
+
+// One CTA: expert histogram, offsets, the expert-sorted list of (token, slot) pairs (token-major inside an
+// expert, like the reference's buckets), and the job list in chunks of `rows_per_job` positions.
+//   list_token[pos]  token of list position pos (the activation row of the gate/up products)
+//   inv[pair]        list position of pair = token * K + slot, or 0xFFFFFFFF if the id was out of range
+// Out-of-range ids raise *bad_id (the caller turns it into an error or ignores it, per loader).
+__global__ void __launch_bounds__(1024) moe_jobs_kernel(const uint32_t* __restrict__ ids, uint32_t T, uint32_t K,
+                                                        uint32_t E, uint32_t rows_per_job,
+                                                        uint32_t* __restrict__ list_token, uint32_t* __restrict__ inv,
+                                                        MoeJob* __restrict__ jobs, uint32_t* __restrict__ n_jobs,
+                                                        uint32_t* __restrict__ n_list, int* __restrict__ bad_id) {
+    __shared__ uint32_t s_cnt[MAX_EXPERTS];
+    __shared__ uint32_t s_off[MAX_EXPERTS];
+    __shared__ uint32_t s_job[MAX_EXPERTS];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+    const uint32_t P = T * K;
+    for (uint32_t e = tid; e < E; e += blockDim.x) s_cnt[e] = 0;
+    __syncthreads();
+    for (uint32_t p = tid; p < P; p += blockDim.x) {
+        uint32_t e = ids[p];
+        if (e < E)
+            atomicAdd(&s_cnt[e], 1u);
+        else {
+            inv[p] = 0xFFFFFFFFu;
+            *bad_id = 1;
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t off = 0, job = 0;
+        for (uint32_t e = 0; e < E; ++e) {
+            s_off[e] = off;
+            s_job[e] = job;
+            off += s_cnt[e];
+            job += (s_cnt[e] + rows_per_job - 1) / rows_per_job;
+        }
+        *n_jobs = job;
+        *n_list = off;
+    }
+    __syncthreads();
+    // stable fill: a warp owns an expert and walks the pairs in order
+    for (uint32_t e = warp; e < E; e += nwarp) {
+        const uint32_t cnt = s_cnt[e];
+        if (cnt == 0) continue;
+        uint32_t base = s_off[e];
+        for (uint32_t p0 = 0; p0 < P; p0 += 32) {
+            uint32_t p = p0 + lane;
+            bool hit = p < P && ids[p] == e;
+            uint32_t ballot = __ballot_sync(0xFFFFFFFFu, hit);
+            if (hit) {
+                uint32_t pos = base + __popc(ballot & ((1u << lane) - 1));
+                list_token[pos] = p / K;
+                inv[p] = pos;
+            }
+            base += __popc(ballot);
+        }
+        for (uint32_t j = lane; j * rows_per_job < cnt; j += 32) {
+            MoeJob jd;
+            jd.expert = e;
+            jd.row0 = s_off[e] + j * rows_per_job;
+            jd.cnt = min(rows_per_job, cnt - j * rows_per_job);
+            jobs[s_job[e] + j] = jd;
+        }
+    }
+}
+
+// y[t, :] = sum over slots (in slot order) of w[t, s] * out[inv[t*K + s], :]  (+ shared[t, :])
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ out, const uint32_t* __restrict__ inv,
+                                                          const float* __restrict__ wts, const float* __restrict__ shared,
+                                                          uint32_t T, uint32_t K, uint32_t h, float* __restrict__ y) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint64_t total = (uint64_t)T * (h / 4);
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total;
+         i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t t = (uint32_t)(i / (h / 4)), c = (uint32_t)(i % (h / 4));
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t s = 0; s < K; ++s) {
+            uint32_t pos = inv[(uint64_t)t * K + s];
+            if (pos == 0xFFFFFFFFu) continue;
+            float w = wts[(uint64_t)t * K + s];
+            float4 v = *reinterpret_cast<const float4*>(out + (uint64_t)pos * h + 4 * c);
+            acc.x += v.x * w;
+            acc.y += v.y * w;
+            acc.z += v.z * w;
+            acc.w += v.w * w;
+        }
+        if (shared) {
+            float4 v = *reinterpret_cast<const float4*>(shared + (uint64_t)t * h + 4 * c);
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+        }
+        *reinterpret_cast<float4*>(y + (uint64_t)t * h + 4 * c) = acc;
+    }
+}
+
+// out = silu(clamp(g)) * clamp(u), element-wise (the dense shared-expert path at batches the grouped kernel
+// does not take)
+__global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ g, const float* __restrict__ u,
+                                                     uint64_t n, float clamp, float* __restrict__ out) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        float gv = g[i], uv = u[i];
+        if (clamp > 0.0f) {
+            gv = fminf(gv, clamp);
+            uv = fmaxf(-clamp, fminf(uv, clamp));
+        }
+        out[i] = gv / (1.0f + expf(-gv)) * uv;
+    }
+}
+
+unsigned blocks_for(uint64_t work, unsigned per_block) {
+    uint64_t b = (work + per_block - 1) / per_block;
+    return (unsigned)(b < 1 ? 1 : (b > 148ull * 16 ? 148ull * 16 : b));
+}
+
+}  // namespace
+
+cudaError_t launch_moe_logits(const float* x, const float* router, uint32_t T, uint32_t E, uint32_t h, float* logits,
+                              cudaStream_t s) {
+    moe_logits_kernel<<<blocks_for((uint64_t)T * E, 8), 256, 0, s>>>(x, router, T, E, h, logits);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_route(const float* logits, const MoeRouteParams& rp, uint32_t T, const float* bias,
+                             const uint32_t* forced_ids, uint32_t* ids, float* wts, cudaStream_t s) {
+    if (rp.n_expert > MAX_EXPERTS || rp.n_group > 64) return cudaErrorInvalidValue;
+    moe_route_kernel<<<blocks_for(T, 4), 128, 0, s>>>(logits, rp, T, bias, forced_ids, ids, wts);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_jobs(const uint32_t* ids, uint32_t T, uint32_t K, uint32_t E, uint32_t rows_per_job,
+                            uint32_t* list_token, uint32_t* inv, MoeJob* jobs, uint32_t* n_jobs, uint32_t* n_list,
+                            int* bad_id, cudaStream_t s) {
+    if (E > MAX_EXPERTS) return cudaErrorInvalidValue;
+    moe_jobs_kernel<<<1, 1024, 0, s>>>(ids, T, K, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_combine(const float* out, const uint32_t* inv, const float* wts, const float* shared, uint32_t T,
+                               uint32_t K, uint32_t h, float* y, cudaStream_t s) {
+    moe_combine_kernel<<<blocks_for((uint64_t)T * (h / 4), 256), 256, 0, s>>>(out, inv, wts, shared, T, K, h, y);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu(const float* g, const float* u, uint64_t n, float clamp, float* out, cudaStream_t s) {
+    swiglu_kernel<<<blocks_for(n, 256), 256, 0, s>>>(g, u, n, clamp, out);
+    return cudaGetLastError();
+}
+
+}  // namespace jq

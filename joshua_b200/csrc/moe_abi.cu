@@ -1,0 +1,385 @@
+// C ABI of the MoE layer: routing on the device, grouped expert matmuls, weighted combine.
+// Declarations and the reference interfaces they replace are in include/joshua_b200.h.
+#include "handles.cuh"
+
+struct jq_moe {
+    jq_ctx* ctx;
+    jq_moe_config cfg;
+    jq::MoeRouteParams rp;
+    float* router = nullptr;  // [E, h] f32, device
+    float* bias = nullptr;    // [E] or NULL
+    const jq_weight *gate, *up, *down, *sh_gate, *sh_up, *sh_down;
+    uint64_t gate_expert_bytes, down_expert_bytes;
+    // workspace, grown to the largest (tokens, pairs) seen
+    uint64_t cap_tokens = 0, cap_pairs = 0;
+    uint8_t* ws = nullptr;
+    float *logits, *wts, *hidden, *out, *sh_hidden, *sh_out, *ones;
+    uint32_t *ids, *list_token, *inv, *n_jobs, *n_list;
+    jq::MoeJob* jobs;
+    void *planes_x, *planes_h;
+    // constants on the device: jobs {0, 0, c} for c = 1..8 (a dense product as a single job) and the count 1
+    jq::MoeJob* dense_jobs = nullptr;
+    uint32_t* one = nullptr;
+    int* bad_host = nullptr;  // pinned, device-visible: an expert id was out of range
+    int* bad_dev = nullptr;
+    std::mutex mu;
+};
+
+namespace {
+
+size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+uint32_t rows_per_job_for(uint64_t pairs, uint64_t tokens, uint32_t n_expert) {
+    if (tokens == 1) return 1;
+    if (pairs <= n_expert) return 2;
+    if (pairs <= 4ull * n_expert) return 4;
+    return 8;
+}
+
+int32_t reserve(jq_moe* m, uint64_t T, uint64_t P) {
+    if (T <= m->cap_tokens && P <= m->cap_pairs) return jq::OK;
+    T = std::max(T, m->cap_tokens);
+    P = std::max(P, m->cap_pairs);
+    const jq_moe_config& c = m->cfg;
+    if (m->ws) cudaFree(m->ws);
+    m->ws = nullptr;
+    m->cap_tokens = m->cap_pairs = 0;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        size_t o = off;
+        off += up256(bytes);
+        return o;
+    };
+    size_t o_logits = take(T * c.n_expert * 4), o_ids = take(P * 4), o_wts = take(P * 4), o_list = take(P * 4),
+           o_inv = take(P * 4), o_jobs = take((P + c.n_expert) * sizeof(jq::MoeJob)), o_nj = take(8),
+           o_hidden = take(P * c.inter * 4), o_out = take(P * c.hidden * 4), o_shh = take(T * c.inter * 4 * 3),
+           o_sho = take(T * c.hidden * 4), o_ones = take(P * 4),
+           o_px = take(jq::gemv_mma_scratch_bytes(T, c.hidden) + (T * (c.hidden / 32) * 112) + 256),
+           o_ph = take(jq::gemv_mma_scratch_bytes(P, c.inter) + (P * (c.inter / 32) * 112) + 256);
+    JQ_CUDA(cudaMalloc(&m->ws, off));
+    uint8_t* b = m->ws;
+    m->logits = (float*)(b + o_logits);
+    m->ids = (uint32_t*)(b + o_ids);
+    m->wts = (float*)(b + o_wts);
+    m->list_token = (uint32_t*)(b + o_list);
+    m->inv = (uint32_t*)(b + o_inv);
+    m->jobs = (jq::MoeJob*)(b + o_jobs);
+    m->n_jobs = (uint32_t*)(b + o_nj);
+    m->n_list = m->n_jobs + 1;
+    m->hidden = (float*)(b + o_hidden);
+    m->out = (float*)(b + o_out);
+    m->sh_hidden = (float*)(b + o_shh);
+    m->sh_out = (float*)(b + o_sho);
+    m->ones = (float*)(b + o_ones);
+    m->planes_x = b + o_px;
+    m->planes_h = b + o_ph;
+    std::vector<float> ones(P, 1.0f);
+    JQ_CUDA(cudaMemcpy(m->ones, ones.data(), P * 4, cudaMemcpyHostToDevice));
+    m->cap_tokens = T;
+    m->cap_pairs = P;
+    return jq::OK;
+}
+
+bool fits_smem(uint64_t rows, uint64_t k) { return jq::gemv_mma_scratch_bytes(rows, k) == 0; }
+
+// out_list[pos, :] = MLP_expert(pos)(x[list_token[pos], :]) for the list built by the jobs kernel.
+// R activation rows, P list positions at most.
+int32_t run_experts(jq_moe* m, const float* x, uint64_t R, uint64_t P, uint32_t rows_per_job, cudaStream_t s) {
+    const jq_moe_config& c = m->cfg;
+    jq::GroupedLaunch g = {};
+    g.jobs = m->jobs;
+    g.n_jobs = m->n_jobs;
+    // a job holds at most rows_per_job positions of one expert
+    g.max_jobs = (uint32_t)std::min<uint64_t>(P, P / rows_per_job + c.n_expert);
+    g.rows_per_job = rows_per_job;
+    g.clamp = c.clamp;
+    g.error_flag = m->ctx->status_dev;
+    // gate and up with the SwiGLU epilogue: hidden[pos, inter]
+    g.type = m->gate->type;
+    g.w0 = m->gate->dev;
+    g.w1 = m->up->dev;
+    g.n = c.inter;
+    g.k = c.hidden;
+    g.expert_bytes = m->gate_expert_bytes;
+    g.x = x;
+    g.x_rows = (uint32_t)R;
+    g.act_rows = m->list_token;
+    g.dst = m->hidden;
+    if (fits_smem(R, c.hidden)) {
+        g.planes = nullptr;
+    } else {
+        JQ_CUDA(jq::launch_quantize_acts(g.type, x, R, c.hidden, m->planes_x, s));
+        g.planes = m->planes_x;
+    }
+    JQ_CUDA(jq::launch_gemv_grouped(g, s));
+    // down: out[pos, hidden]; activation row = list position
+    g.type = m->down->type;
+    g.w0 = m->down->dev;
+    g.w1 = nullptr;
+    g.n = c.hidden;
+    g.k = c.inter;
+    g.expert_bytes = m->down_expert_bytes;
+    g.x = m->hidden;
+    g.x_rows = (uint32_t)P;
+    g.act_rows = nullptr;
+    g.dst = m->out;
+    g.clamp = 0.0f;
+    if (fits_smem(P, c.inter)) {
+        g.planes = nullptr;
+    } else {
+        JQ_CUDA(jq::launch_quantize_acts(g.type, m->hidden, P, c.inter, m->planes_h, s));
+        g.planes = m->planes_h;
+    }
+    JQ_CUDA(jq::launch_gemv_grouped(g, s));
+    return jq::OK;
+}
+
+// sh_out[T, hidden] = shared expert MLP over all tokens
+int32_t run_shared(jq_moe* m, const float* x, uint64_t T, cudaStream_t s) {
+    const jq_moe_config& c = m->cfg;
+    const bool mma_ok = T <= 8 && !m->ctx->force_f32 &&
+                        jq::gemv_mma_supports(m->sh_gate->type, m->sh_gate->dev, c.inter, c.hidden, T) &&
+                        jq::gemv_mma_supports(m->sh_down->type, m->sh_down->dev, c.hidden, c.inter, T) &&
+                        fits_smem(T, c.hidden) && fits_smem(T, c.inter) && m->sh_gate->type == m->sh_up->type;
+    if (mma_ok) {
+        jq::GroupedLaunch g = {};
+        g.jobs = m->dense_jobs + (T - 1);
+        g.n_jobs = m->one;
+        g.max_jobs = 1;
+        g.rows_per_job = (uint32_t)T;
+        g.clamp = c.clamp;
+        g.error_flag = m->ctx->status_dev;
+        g.type = m->sh_gate->type;
+        g.w0 = m->sh_gate->dev;
+        g.w1 = m->sh_up->dev;
+        g.n = c.inter;
+        g.k = c.hidden;
+        g.x = x;
+        g.x_rows = (uint32_t)T;
+        g.dst = m->sh_hidden;
+        JQ_CUDA(jq::launch_gemv_grouped(g, s));
+        g.type = m->sh_down->type;
+        g.w0 = m->sh_down->dev;
+        g.w1 = nullptr;
+        g.n = c.hidden;
+        g.k = c.inter;
+        g.x = m->sh_hidden;
+        g.dst = m->sh_out;
+        g.clamp = 0.0f;
+        JQ_CUDA(jq::launch_gemv_grouped(g, s));
+        return jq::OK;
+    }
+    float* gbuf = m->sh_hidden + T * c.inter;
+    float* ubuf = gbuf + T * c.inter;
+    if (int32_t rc = jq_matmul_device(m->sh_gate, T, c.hidden, c.inter, x, gbuf, s)) return rc;
+    if (int32_t rc = jq_matmul_device(m->sh_up, T, c.hidden, c.inter, x, ubuf, s)) return rc;
+    JQ_CUDA(jq::launch_swiglu(gbuf, ubuf, T * c.inter, c.clamp, m->sh_hidden, s));
+    return jq_matmul_device(m->sh_down, T, c.inter, c.hidden, m->sh_hidden, m->sh_out, s);
+}
+
+int32_t check_bank(const char* name, const jq_weight* w, uint64_t experts, uint64_t rows, uint64_t cols,
+                   uint64_t* expert_bytes) {
+    if (!w) return jq_fail(jq::E_INVALID, std::string("jq_moe_create: NULL ") + name + " bank");
+    if (cols % w->fmt.elems != 0)
+        return jq_fail(jq::E_INVALID, std::string("jq_moe_create: ") + name + " width " + std::to_string(cols) +
+                                          " is not a multiple of the block size " + std::to_string(w->fmt.elems));
+    uint64_t per = rows * (cols / w->fmt.elems);
+    if (w->n_blocks != experts * per)
+        return jq_fail(jq::E_INVALID, std::string("jq_moe_create: ") + name + " bank holds " +
+                                          std::to_string(w->n_blocks) + " blocks, expected " +
+                                          std::to_string(experts * per));
+    if (expert_bytes) *expert_bytes = per * w->fmt.bytes;
+    return jq::OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t jq_moe_create(jq_ctx* ctx, const jq_moe_config* cfg, const float* router, const float* bias,
+                      const jq_weight* gate, const jq_weight* up, const jq_weight* down, const jq_weight* sh_gate,
+                      const jq_weight* sh_up, const jq_weight* sh_down, jq_moe** out) {
+    if (!ctx || !cfg || !router || !out) return jq_fail(jq::E_INVALID, "jq_moe_create: NULL argument");
+    *out = nullptr;
+    const jq_moe_config& c = *cfg;
+    if (c.n_expert == 0 || c.n_used == 0 || c.n_used > c.n_expert || c.n_expert > 512)
+        return jq_fail(jq::E_INVALID, "jq_moe_create: need 0 < n_used <= n_expert <= 512");
+    if (c.gating < 0 || c.gating > 2) return jq_fail(jq::E_INVALID, "jq_moe_create: unknown gating function");
+    if (c.hidden % 256 || c.inter % 256)
+        return jq_fail(jq::E_INVALID, "jq_moe_create: hidden and inter must be multiples of 256");
+    if (c.n_group > 1 && (c.n_expert % c.n_group || c.topk_group == 0 || c.topk_group > c.n_group || c.n_group > 64))
+        return jq_fail(jq::E_INVALID, "jq_moe_create: bad expert group settings");
+    uint64_t geb = 0, ueb = 0, deb = 0;
+    if (int32_t rc = check_bank("gate", gate, c.n_expert, c.inter, c.hidden, &geb)) return rc;
+    if (int32_t rc = check_bank("up", up, c.n_expert, c.inter, c.hidden, &ueb)) return rc;
+    if (int32_t rc = check_bank("down", down, c.n_expert, c.hidden, c.inter, &deb)) return rc;
+    if (gate->type != up->type) return jq_fail(jq::E_INVALID, "jq_moe_create: gate and up banks differ in type");
+    if (!jq::gemv_mma_supports(gate->type, gate->dev, c.inter, c.hidden, 1) ||
+        !jq::gemv_mma_supports(up->type, up->dev, c.inter, c.hidden, 1) ||
+        !jq::gemv_mma_supports(down->type, down->dev, c.hidden, c.inter, 1))
+        return jq_fail(jq::E_INVALID, "jq_moe_create: expert banks are not aligned for the grouped kernel");
+    if (sh_gate || sh_up || sh_down) {
+        if (int32_t rc = check_bank("shared gate", sh_gate, 1, c.inter, c.hidden, nullptr)) return rc;
+        if (int32_t rc = check_bank("shared up", sh_up, 1, c.inter, c.hidden, nullptr)) return rc;
+        if (int32_t rc = check_bank("shared down", sh_down, 1, c.hidden, c.inter, nullptr)) return rc;
+    }
+    JQ_CUDA(cudaSetDevice(ctx->device));
+    jq_moe* m = new (std::nothrow) jq_moe();
+    if (!m) return jq_fail(jq::E_NOMEM, "jq_moe_create: out of host memory");
+    m->ctx = ctx;
+    m->cfg = c;
+    m->rp = {c.gating, c.n_expert, c.n_used, c.n_group ? c.n_group : 1, c.topk_group ? c.topk_group : 1,
+             c.norm, c.renorm_plus_eps, c.scale};
+    m->gate = gate, m->up = up, m->down = down, m->sh_gate = sh_gate, m->sh_up = sh_up, m->sh_down = sh_down;
+    m->gate_expert_bytes = geb;
+    m->down_expert_bytes = deb;
+    cudaError_t e = cudaMalloc(&m->router, (size_t)c.n_expert * c.hidden * 4);
+    if (e == cudaSuccess) e = cudaMemcpy(m->router, router, (size_t)c.n_expert * c.hidden * 4, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess && bias) {
+        e = cudaMalloc(&m->bias, c.n_expert * 4);
+        if (e == cudaSuccess) e = cudaMemcpy(m->bias, bias, c.n_expert * 4, cudaMemcpyHostToDevice);
+    }
+    jq::MoeJob dj[8];
+    for (uint32_t i = 0; i < 8; ++i) dj[i] = {0u, 0u, i + 1};
+    uint32_t one = 1;
+    if (e == cudaSuccess) e = cudaMalloc(&m->dense_jobs, sizeof(dj));
+    if (e == cudaSuccess) e = cudaMemcpy(m->dense_jobs, dj, sizeof(dj), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMalloc(&m->one, 4);
+    if (e == cudaSuccess) e = cudaMemcpy(m->one, &one, 4, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaHostAlloc(&m->bad_host, sizeof(int), cudaHostAllocMapped);
+    if (e == cudaSuccess) e = cudaHostGetDevicePointer(&m->bad_dev, m->bad_host, 0);
+    if (e != cudaSuccess) {
+        jq_moe_free(m);
+        return jq_fail_cuda(e, "jq_moe_create");
+    }
+    *m->bad_host = 0;
+    *out = m;
+    return jq::OK;
+}
+
+void jq_moe_free(jq_moe* m) {
+    if (!m) return;
+    cudaSetDevice(m->ctx->device);
+    cudaDeviceSynchronize();
+    cudaFree(m->router);
+    cudaFree(m->bias);
+    cudaFree(m->ws);
+    cudaFree(m->dense_jobs);
+    cudaFree(m->one);
+    if (m->bad_host) cudaFreeHost(m->bad_host);
+    delete m;
+}
+
+int32_t jq_moe_reserve(jq_moe* m, uint64_t n_tokens, uint64_t n_rows) {
+    if (!m) return jq_fail(jq::E_INVALID, "jq_moe_reserve: NULL handle");
+    std::lock_guard<std::mutex> g(m->mu);
+    JQ_CUDA(cudaSetDevice(m->ctx->device));
+    return reserve(m, std::max<uint64_t>(n_tokens, n_rows), std::max<uint64_t>(n_tokens * m->cfg.n_used, n_rows));
+}
+
+int32_t jq_moe_route_dev(jq_moe* m, const float* x_dev, uint64_t T, const uint32_t* forced_ids_dev,
+                         uint32_t* ids_dev, float* wts_dev, void* stream) {
+    if (!m) return jq_fail(jq::E_INVALID, "jq_moe_route_dev: NULL handle");
+    if (T == 0) return jq::OK;
+    if (!x_dev || !ids_dev || !wts_dev) return jq_fail(jq::E_INVALID, "jq_moe_route_dev: NULL buffer");
+    if (T > m->cap_tokens) return jq_fail(jq::E_TOO_LARGE, "jq_moe_route_dev: call jq_moe_reserve for this many tokens first");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const jq_moe_config& c = m->cfg;
+    JQ_CUDA(jq::launch_moe_logits(x_dev, m->router, (uint32_t)T, c.n_expert, c.hidden, m->logits, s));
+    JQ_CUDA(jq::launch_moe_route(m->logits, m->rp, (uint32_t)T, m->bias, forced_ids_dev, ids_dev, wts_dev, s));
+    return jq::OK;
+}
+
+int32_t jq_moe_experts_dev(jq_moe* m, const float* x_dev, uint64_t n_rows, const uint32_t* expert_ids_dev,
+                           float* out_dev, void* stream) {
+    if (!m) return jq_fail(jq::E_INVALID, "jq_moe_experts_dev: NULL handle");
+    if (n_rows == 0) return jq::OK;
+    if (!x_dev || !expert_ids_dev || !out_dev) return jq_fail(jq::E_INVALID, "jq_moe_experts_dev: NULL buffer");
+    if (n_rows > m->cap_tokens || n_rows > m->cap_pairs)
+        return jq_fail(jq::E_TOO_LARGE, "jq_moe_experts_dev: call jq_moe_reserve for this many rows first");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const jq_moe_config& c = m->cfg;
+    uint32_t rpj = rows_per_job_for(n_rows, n_rows == 1 ? 1 : 2, c.n_expert);
+    JQ_CUDA(jq::launch_moe_jobs(expert_ids_dev, (uint32_t)n_rows, 1, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
+                                m->n_jobs, m->n_list, m->bad_dev, s));
+    if (int32_t rc = run_experts(m, x_dev, n_rows, n_rows, rpj, s)) return rc;
+    // back to row order: out[r] = out_list[inv[r]] (rows with an id out of range come back as zeros)
+    JQ_CUDA(jq::launch_moe_combine(m->out, m->inv, m->ones, nullptr, (uint32_t)n_rows, 1, c.hidden, out_dev, s));
+    return jq::OK;
+}
+
+int32_t jq_moe_forward_dev(jq_moe* m, const float* x_dev, uint64_t T, const uint32_t* forced_ids_dev, float* y_dev,
+                           void* stream) {
+    if (!m) return jq_fail(jq::E_INVALID, "jq_moe_forward_dev: NULL handle");
+    if (T == 0) return jq::OK;
+    if (!x_dev || !y_dev) return jq_fail(jq::E_INVALID, "jq_moe_forward_dev: NULL buffer");
+    const jq_moe_config& c = m->cfg;
+    const uint64_t P = T * c.n_used;
+    if (T > m->cap_tokens || P > m->cap_pairs)
+        return jq_fail(jq::E_TOO_LARGE, "jq_moe_forward_dev: call jq_moe_reserve for this many tokens first");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (int32_t rc = jq_moe_route_dev(m, x_dev, T, forced_ids_dev, m->ids, m->wts, stream)) return rc;
+    uint32_t rpj = rows_per_job_for(P, T, c.n_expert);
+    JQ_CUDA(jq::launch_moe_jobs(m->ids, (uint32_t)T, c.n_used, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
+                                m->n_jobs, m->n_list, m->bad_dev, s));
+    if (int32_t rc = run_experts(m, x_dev, T, P, rpj, s)) return rc;
+    const float* shared = nullptr;
+    if (m->sh_gate) {
+        if (int32_t rc = run_shared(m, x_dev, T, s)) return rc;
+        shared = m->sh_out;
+    }
+    JQ_CUDA(jq::launch_moe_combine(m->out, m->inv, m->wts, shared, (uint32_t)T, c.n_used, c.hidden, y_dev, s));
+    return jq::OK;
+}
+
+int32_t jq_moe_status(jq_moe* m) {
+    if (!m) return jq_fail(jq::E_INVALID, "jq_moe_status: NULL handle");
+    if (*static_cast<volatile int*>(m->bad_host) != 0) {
+        *m->bad_host = 0;
+        if (m->cfg.oob_policy == 0)
+            return jq_fail(jq::E_EXPERT_RANGE, "moe: router selected an expert id out of " +
+                                                   std::to_string(m->cfg.n_expert));
+    }
+    return jq_device_status(m->ctx);
+}
+
+int32_t jq_moe_forward(jq_moe* m, const float* x, uint64_t T, const uint32_t* forced_ids, float* y) {
+    if (!m) return jq_fail(jq::E_INVALID, "jq_moe_forward: NULL handle");
+    if (T == 0) return jq::OK;
+    if (!x || !y) return jq_fail(jq::E_INVALID, "jq_moe_forward: NULL buffer");
+    std::lock_guard<std::mutex> g(m->mu);
+    JQ_CUDA(cudaSetDevice(m->ctx->device));
+    const jq_moe_config& c = m->cfg;
+    if (int32_t rc = reserve(m, T, T * c.n_used)) return rc;
+    Workspace* ws = m->ctx->acquire();
+    if (!ws) return jq_fail(jq::E_NOMEM, "jq_moe_forward: no workspace");
+    struct Rel {
+        jq_ctx* c;
+        Workspace* w;
+        ~Rel() { c->release(w); }
+    } rel{m->ctx, ws};
+    size_t xb = up256(T * c.hidden * 4), fb = up256(T * c.n_used * 4);
+    JQ_CUDA(ws->reserve(2 * xb + fb));
+    float* d_x = reinterpret_cast<float*>(ws->dev);
+    float* d_y = reinterpret_cast<float*>(ws->dev + xb);
+    uint32_t* d_f = reinterpret_cast<uint32_t*>(ws->dev + 2 * xb);
+    cudaStream_t s = ws->stream;
+    JQ_CUDA(cudaMemcpyAsync(d_x, x, T * c.hidden * 4, cudaMemcpyHostToDevice, s));
+    if (forced_ids) JQ_CUDA(cudaMemcpyAsync(d_f, forced_ids, T * c.n_used * 4, cudaMemcpyHostToDevice, s));
+    if (int32_t rc = jq_moe_forward_dev(m, d_x, T, forced_ids ? d_f : nullptr, d_y, s)) return rc;
+    JQ_CUDA(cudaMemcpyAsync(y, d_y, T * c.hidden * 4, cudaMemcpyDeviceToHost, s));
+    JQ_CUDA(cudaStreamSynchronize(s));
+    return jq_moe_status(m);
+}
+
+int32_t jq_moe_last_routing(jq_moe* m, uint64_t T, uint32_t* ids, float* wts) {
+    if (!m || !ids || !wts) return jq_fail(jq::E_INVALID, "jq_moe_last_routing: NULL argument");
+    if (T * m->cfg.n_used > m->cap_pairs) return jq_fail(jq::E_INVALID, "jq_moe_last_routing: no such forward");
+    JQ_CUDA(cudaSetDevice(m->ctx->device));
+    JQ_CUDA(cudaDeviceSynchronize());
+    JQ_CUDA(cudaMemcpy(ids, m->ids, T * m->cfg.n_used * 4, cudaMemcpyDeviceToHost));
+    JQ_CUDA(cudaMemcpy(wts, m->wts, T * m->cfg.n_used * 4, cudaMemcpyDeviceToHost));
+    return jq::OK;
+}
+
+}  // extern "C"
