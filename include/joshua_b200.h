@@ -175,7 +175,9 @@ typedef struct {
  * [n_expert] selection bias (`exp_probs_b`) or NULL.  gate / up / down: banks
  * of n_expert contiguous experts, [n_expert*inter, hidden] twice and
  * [n_expert*hidden, inter] (the layout `split_experts` slices).  sh_*: one
- * shared expert or all NULL.  The weights must outlive the layer. */
+ * shared expert or all NULL.  The weights must outlive the layer.  gate, up
+ * and down may all be NULL: the layer then only routes (jq_moe_route_dev), for
+ * expert-parallel callers whose banks live in a second, per-device layer. */
 int32_t jq_moe_create(jq_ctx* ctx, const jq_moe_config* cfg, const float* router, const float* bias,
                       const jq_weight* gate, const jq_weight* up, const jq_weight* down, const jq_weight* sh_gate,
                       const jq_weight* sh_up, const jq_weight* sh_down, jq_moe** out);

@@ -210,6 +210,11 @@ int32_t jq_moe_create(jq_ctx* ctx, const jq_moe_config* cfg, const float* router
     if (c.n_group > 1 && (c.n_expert % c.n_group || c.topk_group == 0 || c.topk_group > c.n_group || c.n_group > 64))
         return jq_fail(jq::E_INVALID, "jq_moe_create: bad expert group settings");
     uint64_t geb = 0, ueb = 0, deb = 0;
+    const bool router_only = !gate && !up && !down;  // expert-parallel callers route here and compute elsewhere
+    if (router_only) {
+        if (sh_gate || sh_up || sh_down)
+            return jq_fail(jq::E_INVALID, "jq_moe_create: a router-only layer takes no shared expert");
+    } else {
     if (int32_t rc = check_bank("gate", gate, c.n_expert, c.inter, c.hidden, &geb)) return rc;
     if (int32_t rc = check_bank("up", up, c.n_expert, c.inter, c.hidden, &ueb)) return rc;
     if (int32_t rc = check_bank("down", down, c.n_expert, c.hidden, c.inter, &deb)) return rc;
@@ -218,6 +223,7 @@ int32_t jq_moe_create(jq_ctx* ctx, const jq_moe_config* cfg, const float* router
         !jq::gemv_mma_supports(up->type, up->dev, c.inter, c.hidden, 1) ||
         !jq::gemv_mma_supports(down->type, down->dev, c.hidden, c.inter, 1))
         return jq_fail(jq::E_INVALID, "jq_moe_create: expert banks are not aligned for the grouped kernel");
+    }
     if (sh_gate || sh_up || sh_down) {
         if (int32_t rc = check_bank("shared gate", sh_gate, 1, c.inter, c.hidden, nullptr)) return rc;
         if (int32_t rc = check_bank("shared up", sh_up, 1, c.inter, c.hidden, nullptr)) return rc;
@@ -295,6 +301,7 @@ int32_t jq_moe_experts_dev(jq_moe* m, const float* x_dev, uint64_t n_rows, const
     if (!m) return jq_fail(jq::E_INVALID, "jq_moe_experts_dev: NULL handle");
     if (n_rows == 0) return jq::OK;
     if (!x_dev || !expert_ids_dev || !out_dev) return jq_fail(jq::E_INVALID, "jq_moe_experts_dev: NULL buffer");
+    if (!m->gate) return jq_fail(jq::E_INVALID, "jq_moe_experts_dev: this layer was created without expert banks");
     if (n_rows > m->cap_tokens || n_rows > m->cap_pairs)
         return jq_fail(jq::E_TOO_LARGE, "jq_moe_experts_dev: call jq_moe_reserve for this many rows first");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -315,6 +322,7 @@ int32_t jq_moe_forward_dev(jq_moe* m, const float* x_dev, uint64_t T, const uint
     if (!x_dev || !y_dev) return jq_fail(jq::E_INVALID, "jq_moe_forward_dev: NULL buffer");
     const jq_moe_config& c = m->cfg;
     const uint64_t P = T * c.n_used;
+    if (!m->gate) return jq_fail(jq::E_INVALID, "jq_moe_forward_dev: this layer was created without expert banks");
     if (T > m->cap_tokens || P > m->cap_pairs)
         return jq_fail(jq::E_TOO_LARGE, "jq_moe_forward_dev: call jq_moe_reserve for this many tokens first");
     cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -56,17 +56,19 @@ def _ptr(a):
 
 
 class Moe:
-    def __init__(self, cfg: MoeConfig, router, gate: QTensor, up: QTensor, down: QTensor, bias=None, shared=None,
+    def __init__(self, cfg: MoeConfig, router, gate: QTensor | None, up: QTensor | None, down: QTensor | None,
+                 bias=None, shared=None,
                  ctx: Context | None = None):
         self.cfg, self.ctx = cfg, ctx or default_context()
         router = np.ascontiguousarray(router, dtype=np.float32)
         bias = np.ascontiguousarray(bias, dtype=np.float32) if bias is not None else None
         self._keep = (gate, up, down, shared)
         sh = [w._h for w in shared] if shared else [None, None, None]
+        gh, uh, dh = (gate._h, up._h, down._h) if gate is not None else (None, None, None)
         self._h = ctypes.c_void_p()
         c = cfg.to_c()
-        check(_lib.lib().jq_moe_create(self.ctx._h, ctypes.byref(c), _ptr(router), _ptr(bias), gate._h, up._h,
-                                       down._h, sh[0], sh[1], sh[2], ctypes.byref(self._h)))
+        check(_lib.lib().jq_moe_create(self.ctx._h, ctypes.byref(c), _ptr(router), _ptr(bias), gh, uh, dh, sh[0],
+                                       sh[1], sh[2], ctypes.byref(self._h)))
 
     def __del__(self):
         try:
