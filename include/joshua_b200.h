@@ -124,6 +124,28 @@ int32_t jq_matmul_t_f16(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, 
 int32_t jq_matmul_t_dev(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const float* lhs_dev,
                         float* dst_dev, void* stream);
 
+/* The same product for callers that must not allocate.  It has no counterpart
+ * in the reference.  Some hosts hand this library a GPU whose memory is
+ * already fully carved up (weights, KV cache, their own pools), or call it from
+ * a latency-critical loop where a cudaMalloc - which takes the driver lock and
+ * may synchronise the device - is not acceptable.  jq_matmul_t_dev may
+ * allocate scratch the first time a stream needs it; this entry never does: it
+ * calls no cudaMalloc, cudaFree or other allocating routine.  The activation
+ * planes it needs between its two kernels live in a 4 MiB array that is part of
+ * the library image (every GPU that loads the library holds those 4 MiB until
+ * the process exits).
+ *   Limits: 1 <= m <= 8, k a multiple of 256, and m * (k/32) * 112 + 256 bytes
+ *   must fit the 4 MiB array (about m*k <= 1.19 million activations); beyond
+ *   that it fails with JQ_E_TOO_LARGE and touches nothing.
+ *   The first call on a device looks up the array's device address and sets
+ *   kernel attributes; make that call before capturing a stream.
+ *   All calls on a device share the array and it is not cleared between
+ *   calls (each call rewrites what it reads).  Calls whose kernels overlap on
+ *   the GPU - different streams, or two host threads - race on it: keep them on
+ *   one stream or serialise them.  Inputs and outputs are the caller's. */
+int32_t jq_matmul_t_dev_noalloc(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const float* lhs_dev,
+                                float* dst_dev, void* stream);
+
 /* QuantizedType::dequantize (src/mmap_tensor.rs:169-174) and
  * decode_raw_to_f32 (src/quant_matmul.rs:36-103): all blocks to f32.
  * `two_step` != 0 gives the separately rounded k-quant form fl(fl(d*sc*)q)-m

@@ -44,6 +44,7 @@ _SIGNATURES = {
     "jq_matmul_t": (i32, [vp, u64, u64, u64, vp, u64, vp, u64]),
     "jq_matmul_t_f16": (i32, [vp, u64, u64, u64, vp, u64, vp, u64]),
     "jq_matmul_t_dev": (i32, [vp, u64, u64, u64, vp, vp, vp]),
+    "jq_matmul_t_dev_noalloc": (i32, [vp, u64, u64, u64, vp, vp, vp]),
     "jq_dequantize": (i32, [vp, vp, u64, i32]),
     "jq_dequantize_dev": (i32, [vp, vp, u64, i32, vp]),
     "jq_embedding": (i32, [vp, vp, u64, u64, u64, vp]),

@@ -248,6 +248,28 @@ int32_t jq_matmul_t_dev(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, 
     return jq_matmul_device(w, m, k, n, lhs_dev, dst_dev, static_cast<cudaStream_t>(stream));
 }
 
+int32_t jq_matmul_t_dev_noalloc(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const float* lhs_dev,
+                                float* dst_dev, void* stream) {
+    if (int32_t rc = validate_matmul(w, m, k, n, 0, 0, false)) return rc;
+    if (m == 0 || n == 0) return jq::OK;
+    if (!lhs_dev || !dst_dev) return jq_fail(jq::E_INVALID, "jq_matmul_t_dev_noalloc: NULL buffer");
+    if (reinterpret_cast<uintptr_t>(lhs_dev) % 16 != 0)
+        return jq_fail(jq::E_INVALID, "jq_matmul_t_dev_noalloc: lhs must be 16-byte aligned");
+    if (!jq::gemv_mma_supports(w->type, w->dev, n, k, m))
+        return jq_fail(jq::E_TOO_LARGE, "jq_matmul_t_dev_noalloc: only batches of 1..8 rows with k a multiple of 256 "
+                                        "are served without allocating");
+    if (jq::gemv_mma_static_bytes_needed(m, k) > jq::GEMV_STATIC_SCRATCH_BYTES)
+        return jq_fail(jq::E_TOO_LARGE, "jq_matmul_t_dev_noalloc: m*k = " + std::to_string(m * k) +
+                                            " activations need " +
+                                            std::to_string(jq::gemv_mma_static_bytes_needed(m, k)) +
+                                            " bytes of scratch, the built-in array holds " +
+                                            std::to_string(jq::GEMV_STATIC_SCRATCH_BYTES));
+    JQ_CUDA(cudaSetDevice(w->ctx->device));
+    JQ_CUDA(jq::launch_gemv_mma_static(w->type, w->dev, n, k, lhs_dev, m, dst_dev, w->ctx->status_dev,
+                                       static_cast<cudaStream_t>(stream)));
+    return jq::OK;
+}
+
 int32_t jq_matmul_t(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const float* lhs, uint64_t lhs_len,
                     float* dst, uint64_t dst_len) {
     if (int32_t rc = validate_matmul(w, m, k, n, lhs_len, dst_len, true)) return rc;

@@ -52,6 +52,11 @@ bool gemv_mma_supports(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, 
 // error_flag: device int set to 1 if a bounded wait inside the kernel gave up
 cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
                             float* dst, void* scratch, int* error_flag, cudaStream_t s);
+// Allocation-free variant: planes in a fixed array inside the library image (see gemv_mma.cu).
+constexpr size_t GEMV_STATIC_SCRATCH_BYTES = 4u << 20;
+size_t gemv_mma_static_bytes_needed(uint64_t m, uint64_t k);
+cudaError_t launch_gemv_mma_static(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs,
+                                   uint64_t m, float* dst, int* error_flag, cudaStream_t s);
 // f32 rows -> activation planes in `scratch` (gemv_mma_scratch_bytes(rows, k) bytes, for rows that do not fit
 // the kernel's shared memory)
 cudaError_t launch_quantize_acts(uint32_t type, const float* x, uint64_t rows, uint64_t k, void* scratch,

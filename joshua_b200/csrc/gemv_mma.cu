@@ -1110,6 +1110,59 @@ cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_
     return launch_typed<0, 0>(type, ga, (uint32_t)m, tiles, s);
 }
 
+// ── the allocation-free variant ──────────────────────────────────────────────────────────────────────
+//
+// Same product as launch_gemv_mma on its scratch path (activation planes written to global memory by
+// quantize_acts_kernel, then read by the matmul kernel), but the planes live in a fixed array that is part
+// of the library image instead of a buffer from cudaMalloc.  Every GPU that loads the library carries these
+// 4 MiB until the process exits.  All calls on a device share the array, and it keeps whatever the last
+// call left there; nothing in it has to start at zero, because the first kernel of a call rewrites every
+// byte the second one reads.  Two calls whose kernels overlap on the GPU (different streams, or the same
+// call issued from two threads) would overwrite each other's planes.
+static __device__ __align__(256) unsigned char g_static_planes[GEMV_STATIC_SCRATCH_BYTES];
+
+// The array's name is only a handle on the host side; the device address has to be asked for, once per
+// device and with that device current.
+static void* g_static_planes_addr[64];
+
+cudaError_t gemv_mma_static_setup(void** addr) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (g_static_planes_addr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_planes);
+        if (e != cudaSuccess) return e;
+        if (p == nullptr) return cudaErrorInvalidSymbol;
+        g_static_planes_addr[dev] = p;
+    }
+    *addr = g_static_planes_addr[dev];
+    return cudaSuccess;
+}
+
+size_t gemv_mma_static_bytes_needed(uint64_t m, uint64_t k) { return (size_t)(m * (k / 32) * 112 + 256); }
+
+cudaError_t launch_gemv_mma_static(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs,
+                                   uint64_t m, float* dst, int* error_flag, cudaStream_t s) {
+    void* planes = nullptr;
+    cudaError_t e = gemv_mma_static_setup(&planes);
+    if (e != cudaSuccess) return e;
+    e = launch_quantize_acts(type, lhs, m, k, planes, s);
+    if (e != cudaSuccess) return e;
+    GemvArgs ga = {};
+    ga.w[0] = ga.w[1] = w;
+    ga.n = n;
+    ga.k = k;
+    ga.x = lhs;
+    ga.x_rows = (uint32_t)m;
+    ga.m = (uint32_t)m;
+    ga.dst = dst;
+    ga.error_flag = error_flag;
+    ga.act = planes_in(planes, m, k);
+    return launch_typed<0, 0>(type, ga, (uint32_t)m, (n + ROWS - 1) / ROWS, s);
+}
+
 cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s) {
     GemvArgs ga = {};
     ga.w[0] = g.w0;
