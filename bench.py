@@ -3,9 +3,10 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 Workloads
-  llama8b  (default) decode of a Llama-8B-shaped model, every linear Q4_K, batch 1:
-           one step = one token through all 32 layers' quantized linears and the
-           output head (4.22 GB of raw Q4_K blocks read once per token).
+  llama8b  (default) decode of a Llama-8B-shaped model, every linear Q4_K, batch 1
+           (--batch up to 8): the KV cache is filled with --prefill positions, then one
+           step = one greedily decoded token, the whole step on the device
+           (4.22 GB of raw Q4_K blocks read once per token).
   gemv     one quantized matmul shape, rotated over a working set larger than L2
            (--type, --n, --k, --m, --rotate-gb): the kernel-level roofline probe
            and the command used for ncu captures.
@@ -240,6 +241,8 @@ def main():
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--rotate-gb", type=float, default=1.0)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--prefill", type=int, default=512)
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -166,6 +166,55 @@ int32_t jq_embedding(const jq_weight* w, const uint32_t* ids, uint64_t n_ids, ui
  * borrowed tensors are read-only; always fails with JQ_E_INVALID. */
 int32_t jq_weight_from_float(jq_weight* w, const float* xs, uint64_t len);
 
+/* ── around the matmuls: the rest of a decode step, on the device ───────
+ * The callers on either side of the matmul path.  In the reference they are
+ * candle tensor ops inside the loaders; here they are kernels so that a token
+ * does not leave the device between two quantized matmuls.  All f32, all on a
+ * caller stream without synchronisation. */
+
+/* `Mlp::forward` up to the down projection: dst = silu(gate x) * up x, with the
+ * optional clamp of src/quantized_deepseek4.rs:445-462 (clamp <= 0: none)
+ * (src/quantized_qwen3_moe.rs:396-402).  One launch for batches of 1..8. */
+int32_t jq_matmul_swiglu_dev(const jq_weight* gate, const jq_weight* up, uint64_t m, uint64_t k, uint64_t n,
+                             const float* lhs_dev, float* dst_dev, float clamp, void* stream);
+
+/* QuantizedType::embedding with device ids (src/mmap_tensor.rs:140-167); an id
+ * >= rows sets *bad_id_dev to 1 and leaves that row untouched. */
+int32_t jq_embedding_dev(const jq_weight* w, const uint32_t* ids_dev, uint64_t n_ids, uint64_t rows, uint64_t hidden,
+                         float* out_dev, int32_t* bad_id_dev, void* stream);
+
+/* RmsNorm (src/quantized_qwen3_moe.rs:532-553): out = (x [+ residual]) /
+ * sqrt(mean(.^2) + eps) * weight.  With `residual`, the sum is also written to
+ * sum_out (the new residual stream).  weight may be NULL (ones). */
+int32_t jq_rmsnorm_dev(const float* x, const float* residual, const float* weight, float eps, uint64_t rows,
+                       uint64_t hidden, float* sum_out, float* out, void* stream);
+
+/* Rotary embedding of q and k (pairing element i with i + head_dim/2) at
+ * position pos[b], then k and v appended to the cache: the rope + `Tensor::cat`
+ * of src/quantized_qwen3_moe.rs:330-364.  qkv: [batch, (n_q + 2 n_kv) *
+ * head_dim]; cache_k, cache_v: [batch, n_kv, max_ctx, head_dim]. */
+int32_t jq_rope_append_dev(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t n_q, uint32_t n_kv,
+                           uint32_t head_dim, uint32_t max_ctx, float theta, float* q_out, float* cache_k,
+                           float* cache_v, void* stream);
+
+/* Grouped-query attention of one new token per sequence over positions
+ * 0..pos[b] of the cache (src/quantized_qwen3_moe.rs:366-386).  `scratch`:
+ * jq_attention_scratch_bytes(...) bytes of caller device memory (per-chunk
+ * partial results, merged in position order). */
+uint64_t jq_attention_scratch_bytes(uint32_t batch, uint32_t n_q, uint32_t head_dim, uint32_t max_ctx);
+int32_t jq_attention_decode_dev(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,
+                                uint32_t batch, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t max_ctx,
+                                float* out, float* scratch, void* stream);
+
+int32_t jq_add_dev(const float* a, const float* b, uint64_t n, float* y, void* stream);
+
+/* Greedy sampling (src/engine.rs:2371-2378): arg-max of each row, the LAST
+ * maximal index winning ties; pos (may be NULL) is advanced by one per row.
+ * `scratch`: jq_argmax_scratch_bytes(rows) bytes of caller device memory. */
+uint64_t jq_argmax_scratch_bytes(uint64_t rows);
+int32_t jq_argmax_dev(const float* logits, uint64_t rows, uint64_t vocab, int32_t* token, int32_t* pos, void* scratch,
+                      void* stream);
+
 /* ── MoE layer ───────────────────────────────────────────────────────────
  * Replaces `Moe::forward` of the three loaders: routing, per-expert gather,
  * SwiGLU MLP over quantized expert banks, weighted scatter-add, optional

@@ -49,6 +49,15 @@ _SIGNATURES = {
     "jq_dequantize_dev": (i32, [vp, vp, u64, i32, vp]),
     "jq_embedding": (i32, [vp, vp, u64, u64, u64, vp]),
     "jq_weight_from_float": (i32, [vp, vp, u64]),
+    "jq_matmul_swiglu_dev": (i32, [vp, vp, u64, u64, u64, vp, vp, ctypes.c_float, vp]),
+    "jq_embedding_dev": (i32, [vp, vp, u64, u64, u64, vp, vp, vp]),
+    "jq_rmsnorm_dev": (i32, [vp, vp, vp, ctypes.c_float, u64, u64, vp, vp, vp]),
+    "jq_rope_append_dev": (i32, [vp, vp, u32, u32, u32, u32, u32, ctypes.c_float, vp, vp, vp, vp]),
+    "jq_attention_scratch_bytes": (u64, [u32, u32, u32, u32]),
+    "jq_attention_decode_dev": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp, vp, vp]),
+    "jq_add_dev": (i32, [vp, vp, u64, vp, vp]),
+    "jq_argmax_scratch_bytes": (u64, [u64]),
+    "jq_argmax_dev": (i32, [vp, u64, u64, vp, vp, vp, vp]),
     "jq_moe_create": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, pp]),
     "jq_moe_free": (None, [vp]),
     "jq_moe_forward": (i32, [vp, vp, u64, vp, vp]),

@@ -1,17 +1,16 @@
 """The `llama8b` benchmark workload: batch-1 decode of a Llama-8B-shaped model with every linear in Q4_K.
 
-One step = one token through the 32 layers' quantized linears and the output
-head, with the element-wise glue between them (residual adds, RMS
-normalisation, SwiGLU) as plain torch ops on the same stream; the whole step is
-captured in one CUDA graph.  Attention over the KV cache is not part of this
-workload yet (the attention output is stood in for by the query projection), so
-the figure measures the quantized-matmul path of a decode step, which is where
-a batch-1 step spends its memory traffic: 4.22 GB of weights per token against
-~40 MB of KV cache at 640 positions.
+The model is `joshua_b200.llama.LlamaDecoder`: random-init, 32 layers, hidden 4096, 32 query / 8 KV heads of
+128, SwiGLU FFN 14336, vocabulary 128256, all linears and the embedding as raw Q4_K blocks.  The KV cache is
+first filled by feeding token id 42 for `--prefill` positions (the reference's own benchmark feeds a repeated
+token, examples/bench_qwen3moe.rs:148-162), one position per step; then one timed step = one greedily decoded
+token: embedding row, 32 x {RMS norm, fused QKV matmul, RoPE + cache append, attention over the cache, output
+projection, residual + RMS norm, gate/up matmul with SwiGLU, down matmul}, final norm, output head, arg-max.
+Everything runs on the device; the step is one CUDA graph.  4.22 GB of weights are read per token.
 
-With --gpus N > 1 every rank holds a full replica (dense weights are replicated
-by design; only MoE expert banks shard) and decodes its own sequence: weak
-scaling with no data-path collective, whole-job tokens/s = N x per-rank.
+With --gpus N > 1 every rank holds a full replica (dense weights are replicated by design; only MoE expert
+banks shard) and decodes its own sequence: weak scaling with no data-path collective, whole-job tokens/s =
+N x per-rank.
 """
 from __future__ import annotations
 
@@ -22,112 +21,7 @@ import time
 import numpy as np
 
 from . import synth
-from .qtensor import QTensor
-
-LLAMA = dict(layers=32, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=14336, vocab=128256)
-
-
-class LlamaLinears:
-    """Device-resident Q4_K linears of the model, random-init, plus the decode step over them."""
-
-    def __init__(self, device, seed=0, cfg=LLAMA):
-        import torch
-
-        self.torch, self.dev, self.cfg = torch, device, cfg
-        h, kv, ffn = cfg["hidden"], cfg["kv_heads"] * cfg["head_dim"], cfg["ffn"]
-        self.shapes = {"wqkv": (h + 2 * kv, h), "wo": (h, h), "w_gate": (ffn, h), "w_up": (ffn, h), "w_down": (h, ffn)}
-        self.layers = []
-        self.weight_bytes = 0
-        for layer in range(cfg["layers"]):
-            ws = {}
-            for i, (name, (n, k)) in enumerate(self.shapes.items()):
-                ws[name] = self._weight(n, k, seed * 100003 + layer * 16 + i)
-            self.layers.append(ws)
-        self.head = self._weight(cfg["vocab"], h, seed * 100003 + 999983)
-        self.n_matmuls = cfg["layers"] * len(self.shapes) + 1
-        # fixed activation buffers (the graph replays over them)
-        f32 = dict(dtype=torch.float32, device=device)
-        self.x = torch.randn(1, h, **f32)
-        self.qkv = torch.empty(1, h + 2 * kv, **f32)
-        self.attn = torch.empty(1, h, **f32)
-        self.o = torch.empty(1, h, **f32)
-        self.xn = torch.empty(1, h, **f32)
-        self.g = torch.empty(1, ffn, **f32)
-        self.u = torch.empty(1, ffn, **f32)
-        self.act = torch.empty(1, ffn, **f32)
-        self.d = torch.empty(1, h, **f32)
-        self.logits = torch.empty(1, cfg["vocab"], **f32)
-        self.token = torch.zeros(1, dtype=torch.int64, device=device)
-
-    def _weight(self, n, k, seed):
-        raw = synth.random_weight_torch(synth.Q4_K, n, k, seed, self.dev)
-        raw = self.torch.cat([raw, self.torch.zeros(16, dtype=self.torch.uint8, device=self.dev)])
-        nbytes = synth.tensor_bytes(synth.Q4_K, n, k)
-        self.weight_bytes += nbytes
-        return QTensor.from_device(synth.Q4_K, raw[:nbytes]), n, k
-
-    @staticmethod
-    def _mm(w, x, y):
-        q, n, k = w
-        q.matmul_t_dev((x.shape[0], k, n), x, y)
-
-    def _rms(self, x, out):
-        t = self.torch
-        t.mul(x, t.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + 1e-5), out=out)
-
-    def step(self):
-        """One decoded token (launches only; no synchronisation)."""
-        t, h = self.torch, self.cfg["hidden"]
-        x = self.x
-        for ws in self.layers:
-            self._rms(x, self.xn)
-            self._mm(ws["wqkv"], self.xn, self.qkv)
-            self._rms(self.qkv[:, :h], self.attn)  # stand-in for attention over the KV cache
-            self._mm(ws["wo"], self.attn, self.o)
-            x = x + self.o * 0.1
-            self._rms(x, self.xn)
-            self._mm(ws["w_gate"], self.xn, self.g)
-            self._mm(ws["w_up"], self.xn, self.u)
-            self._rms(self.g, self.g)
-            self._rms(self.u, self.u)
-            t.mul(t.nn.functional.silu(self.g), self.u, out=self.act)
-            self._mm(ws["w_down"], self.act, self.d)
-            self._rms(self.d, self.d)
-            x = x + self.d * 0.1
-        self._rms(x, self.xn)
-        self._mm(self.head, self.xn, self.logits)
-        t.argmax(self.logits, dim=-1, out=self.token)
-        # next token's embedding: a deterministic function of the sampled id keeps the chain data-dependent
-        self.x.copy_(t.sin(self.xn * (1.0 + (self.token % 7).to(t.float32))))
-
-    def matmuls_only(self):
-        """The quantized matmuls of one token back to back (the roofline probe)."""
-        for ws in self.layers:
-            self._mm(ws["wqkv"], self.xn, self.qkv)
-            self._mm(ws["wo"], self.attn, self.o)
-            self._mm(ws["w_gate"], self.xn, self.g)
-            self._mm(ws["w_up"], self.xn, self.u)
-            self._mm(ws["w_down"], self.act, self.d)
-        self._mm(self.head, self.xn, self.logits)
-
-    def algorithmic_bytes(self):
-        """Weight bytes + f32 activations in and out, summed over the token's matmuls."""
-        c = self.cfg
-        io = 0
-        for n, k in self.shapes.values():
-            io += 4 * (n + k)
-        io = io * c["layers"] + 4 * (c["vocab"] + c["hidden"])
-        return self.weight_bytes + io
-
-
-def host_api_step(model_host, x_host):
-    """The same token through the host-buffer C ABI (jq_matmul_t): every matmul copies in and out."""
-    h2d = d2h = 0
-    for q, n, k, inp in model_host:
-        y = q.matmul_t((1, k, n), x_host[inp])
-        h2d += 4 * k
-        d2h += 4 * n
-    return h2d, d2h, y
+from .llama import LlamaConfig, LlamaDecoder
 
 
 def run(args):
@@ -148,7 +42,11 @@ def run(args):
         if world > 1:
             dist.barrier()
 
-    model = LlamaLinears(dev, seed=rank)
+    warmup = max(3, args.warmup)
+    cfg = LlamaConfig()
+    batch = args.batch
+    max_ctx = args.prefill + warmup + args.steps + 8
+    model = LlamaDecoder(cfg, dev, batch=batch, max_ctx=max_ctx, seed=rank)
     stream = torch.cuda.Stream()
 
     def capture(fn):
@@ -163,10 +61,16 @@ def run(args):
 
     step_graph = capture(model.step)
     mm_graph = capture(model.matmuls_only)
+    with torch.cuda.stream(stream):
+        model.reset(42)
+        for _ in range(args.prefill):  # fill the cache: the same token at every position
+            step_graph.replay()
+            model.force_token(42)
+        stream.synchronize()
 
-    def timed(graph, steps, warmup):
+    def timed(graph, steps, warm):
         with torch.cuda.stream(stream):
-            for _ in range(warmup):
+            for _ in range(warm):
                 graph.replay()
             stream.synchronize()
             barrier()
@@ -180,56 +84,69 @@ def run(args):
         return s.elapsed_time(e) * 1e-3 / steps
 
     with ClockSampler(local) as clocks:
-        dt = timed(step_graph, args.steps, max(3, args.warmup))
-    dt_mm = timed(mm_graph, args.steps, max(3, args.warmup))
+        dt = timed(step_graph, args.steps, warmup)
+    assert int(model.bad.item()) == 0 and int(model.pos.max().item()) < max_ctx
+    dt_mm = timed(mm_graph, args.steps, warmup)
     if world > 1:
         tmax = torch.tensor([dt], device=dev, dtype=torch.float64)
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         dt = float(tmax.item())
 
     if rank == 0:
-        # end to end through the host-buffer ABI: layer 0's linears + head measured, scaled to the token by calls
-        qs = []
-        for name in ("wqkv", "wo", "w_gate", "w_up", "w_down"):
-            q, n, k = model.layers[0][name]
-            qs.append((q, n, k, k))
-        x_host = {k: np.random.default_rng(0).standard_normal(k).astype(np.float32) for k in {q[2] for q in qs}}
+        # end to end through the host-buffer ABI: layer 0's matmuls + head measured, scaled to the token
+        ly = model.layers[0]
+        c = cfg
+        qs = [(ly["wqkv"], c.qkv_rows, c.hidden, c.hidden), (ly["wo"], c.hidden, c.q_heads * c.head_dim, c.hidden),
+              (ly["w_gate"], c.ffn, c.hidden, c.hidden), (ly["w_up"], c.ffn, c.hidden, c.hidden),
+              (ly["w_down"], c.hidden, c.ffn, c.ffn)]
+        x_host = {k: np.random.default_rng(0).standard_normal((batch, k)).astype(np.float32) for k in (c.hidden, c.ffn)}
+
+        def host_layer():
+            h2d = d2h = 0
+            for q, n, k, inp in qs:
+                q.matmul_t((batch, k, n), x_host[inp])
+                h2d += 4 * k * batch
+                d2h += 4 * n * batch
+            return h2d, d2h
+
         for _ in range(3):
-            host_api_step(qs, x_host)
+            host_layer()
         reps = 10
         t0 = time.perf_counter()
         for _ in range(reps):
-            h2d_l, d2h_l, _ = host_api_step(qs, x_host)
+            h2d_l, d2h_l = host_layer()
         per_layer = (time.perf_counter() - t0) / reps
-        q, n, k = model.head
-        model.head[0].matmul_t((1, k, n), x_host[k])
+        model.output.matmul_t((batch, c.hidden, c.vocab), x_host[c.hidden])
         t0 = time.perf_counter()
         for _ in range(reps):
-            model.head[0].matmul_t((1, k, n), x_host[k])
+            model.output.matmul_t((batch, c.hidden, c.vocab), x_host[c.hidden])
         per_head = (time.perf_counter() - t0) / reps
-        L = model.cfg["layers"]
-        e2e_dt = per_layer * L + per_head
-        h2d, d2h = h2d_l * L + 4 * k, d2h_l * L + 4 * n
+        e2e_dt = per_layer * c.layers + per_head
+        h2d, d2h = h2d_l * c.layers + 4 * c.hidden * batch, d2h_l * c.layers + 4 * c.vocab * batch
 
         peak, which = measured_peaks()
         alg = model.algorithmic_bytes()
-        launches = model.n_matmuls
+        launches = model.matmuls_per_step
         ach = alg / dt_mm / 1e9
         line = {
-            "metric": "decode_tok_s", "value": world / dt, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "int8 codes x int8 activation planes -> int32, f32 scales",
-            "data": "synthetic",
-            "config": {"workload": "llama8b_q4k_decode_b1", **model.cfg, "batch": 1,
-                       "step": "32 layers x (qkv, o, gate, up, down) + head, Q4_K; torch glue; attention stand-in",
+            "metric": "decode_tok_s", "value": world * batch / dt, "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 codes x int8 activation planes -> int32, f32 scales and glue", "data": "synthetic",
+            "config": {"workload": f"llama8b_q4k_decode_b{batch}", "layers": c.layers, "hidden": c.hidden,
+                       "q_heads": c.q_heads, "kv_heads": c.kv_heads, "head_dim": c.head_dim, "ffn": c.ffn,
+                       "vocab": c.vocab, "batch": batch, "prefill": args.prefill,
+                       "step": "full decode step on the device (embedding, norms, RoPE, attention over the KV cache, "
+                               "quantized matmuls, greedy arg-max), one CUDA graph",
                        "l2": "4.22 GB of weights per step, far larger than L2", "parallelism": f"replicas x{world}"},
-            "e2e": {"value": 1.0 / e2e_dt, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "how": "every matmul through jq_matmul_t with host buffers; layer 0 + head timed, x32 layers"},
+            "e2e": {"value": batch / e2e_dt, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "how": "every matmul of the token through jq_matmul_t with host buffers; layer 0 + head timed, "
+                           "x32 layers"},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                         "traffic": None, "peak_source": which, "kernel": "gemv_mma_kernel<Q4_K, m=1>",
+                         "traffic": None, "peak_source": which, "kernel": "gemv_mma_kernel<Q4_K>",
                          "launches_per_step": launches, "avg_launch_us": dt_mm / launches * 1e6,
                          "bytes_per_step": alg},
-            "gpu_launches": launches * args.steps, "clocks": clocks.summary(),
+            "gpu_launches": model.launches_per_step * args.steps, "clocks": clocks.summary(),
         }
         try:
             base = cpu_llama_sample(seconds_budget=12.0)

@@ -8,6 +8,24 @@
 
 namespace jq {
 
+// Launch with programmatic stream serialization: the kernel may start while its predecessor in the stream
+// is still draining; every access that depends on the predecessor sits behind pdl_wait().
+template <class... KArgs, class... Args>
+cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, unsigned block, size_t smem, cudaStream_t s,
+                       Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 // Status codes of the C ABI (0 = success, negative = failure), following the
 // int32 status / opaque handle convention of the reference's only C ABI
 // (src/npu/mod.rs:32-50).
@@ -52,6 +70,10 @@ bool gemv_mma_supports(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, 
 // error_flag: device int set to 1 if a bounded wait inside the kernel gave up
 cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
                             float* dst, void* scratch, int* error_flag, cudaStream_t s);
+// Fused gate / up pair with the SwiGLU epilogue; valid when gemv_mma_scratch_bytes(m, k) == 0.
+cudaError_t launch_gemv_mma_swiglu(uint32_t type, const uint8_t* w_gate, const uint8_t* w_up, uint64_t n, uint64_t k,
+                                   const float* lhs, uint64_t m, float* dst, float clamp, int* error_flag,
+                                   cudaStream_t s);
 // Allocation-free variant: planes in a fixed array inside the library image (see gemv_mma.cu).
 constexpr size_t GEMV_STATIC_SCRATCH_BYTES = 4u << 20;
 size_t gemv_mma_static_bytes_needed(uint64_t m, uint64_t k);
@@ -102,5 +124,21 @@ cudaError_t launch_moe_jobs(const uint32_t* ids, uint32_t T, uint32_t K, uint32_
 cudaError_t launch_moe_combine(const float* out, const uint32_t* inv, const float* wts, const float* shared, uint32_t T,
                                uint32_t K, uint32_t h, float* y, cudaStream_t s);
 cudaError_t launch_swiglu(const float* g, const float* u, uint64_t n, float clamp, float* out, cudaStream_t s);
+
+// decoder.cu: the element-wise and attention steps around the matmuls of a decode step
+cudaError_t launch_rmsnorm(const float* x, const float* res, const float* w, float eps, uint64_t rows, uint32_t h,
+                           float* sum_out, float* out, cudaStream_t s);
+cudaError_t launch_rope_append(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
+                               uint32_t hd, uint32_t max_ctx, float theta, float* q_out, float* cache_k, float* cache_v,
+                               cudaStream_t s);
+// scratch: attention_scratch_bytes(...) bytes of per-chunk partial results
+size_t attention_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t hd, uint32_t max_ctx);
+cudaError_t launch_attention_decode(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,
+                                    uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx, float* out,
+                                    float* scratch, cudaStream_t s);
+cudaError_t launch_add(const float* a, const float* b, uint64_t n, float* y, cudaStream_t s);
+size_t argmax_scratch_bytes(uint32_t rows);
+cudaError_t launch_argmax(const float* logits, uint32_t rows, uint32_t vocab, int32_t* token, int32_t* pos,
+                          void* scratch, cudaStream_t s);
 
 }  // namespace jq

@@ -1,0 +1,357 @@
+// Element-wise and attention kernels of a decode step, so that a token never leaves the device between the
+// quantized matmuls: RMS norm (optionally fused with the residual add), rotary embedding + KV-cache append,
+// attention over the cache for one new token per sequence, SwiGLU, arg-max sampling.
+//
+// These are the callers on either side of the matmul path: the reference runs them as candle tensor ops
+// in its loaders (RmsNorm / rope / softmax / cat of the KV cache, src/quantized_qwen3_moe.rs:297-386;
+// greedy arg-max with the last maximal index winning ties, src/engine.rs:2371-2378).  All f32.
+#include "common.cuh"
+
+namespace jq {
+
+namespace {
+
+__device__ __forceinline__ void pdl_wait_() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = 0.0f;
+    for (int i = 0; i < nw; ++i) t += red[i];  // fixed order
+    __syncthreads();
+    return t;
+}
+
+// out[r, :] = rmsnorm(x[r, :] (+ res[r, :])) * w;  when res != NULL the sum is also written to sum_out
+// (the new residual stream).  One CTA of 1024 threads per row; each thread keeps its float4 pieces in
+// registers between the two passes (rows up to 16384 wide; wider rows re-read).
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ res,
+                                                       const float* __restrict__ w, float eps, uint32_t h,
+                                                       float* __restrict__ sum_out, float* __restrict__ out) {
+    __shared__ float red[32];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    pdl_wait_();
+    const uint64_t row = blockIdx.x;
+    const uint32_t n4 = h / 4;
+    const float4* x4 = reinterpret_cast<const float4*>(x + row * h);
+    const float4* r4 = res ? reinterpret_cast<const float4*>(res + row * h) : nullptr;
+    float4* s4 = sum_out ? reinterpret_cast<float4*>(sum_out + row * h) : nullptr;
+    float4 keep[4];
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t i = threadIdx.x + c * 1024;
+        if (i < n4) {
+            float4 v = x4[i];
+            if (r4) {
+                float4 r = r4[i];
+                v.x += r.x, v.y += r.y, v.z += r.z, v.w += r.w;
+            }
+            if (s4) s4[i] = v;
+            keep[c] = v;
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+    }
+    for (uint32_t i = threadIdx.x + 4096; i < n4; i += 1024) {  // rows wider than 16384
+        float4 v = x4[i];
+        if (r4) {
+            float4 r = r4[i];
+            v.x += r.x, v.y += r.y, v.z += r.z, v.w += r.w;
+        }
+        if (s4) s4[i] = v;
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+    }
+    const float tot = block_sum(ss, red);
+    const float scale = rsqrtf(tot / (float)h + eps);
+    const float4* w4 = w ? reinterpret_cast<const float4*>(w) : nullptr;
+    float4* o4 = reinterpret_cast<float4*>(out + row * h);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t i = threadIdx.x + c * 1024;
+        if (i < n4) {
+            float4 v = keep[c], g = w4 ? w4[i] : make_float4(1.f, 1.f, 1.f, 1.f);
+            o4[i] = make_float4(v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
+        }
+    }
+    for (uint32_t i = threadIdx.x + 4096; i < n4; i += 1024) {
+        float4 v = x4[i];
+        if (r4) {
+            float4 r = r4[i];
+            v.x += r.x, v.y += r.y, v.z += r.z, v.w += r.w;
+        }
+        float4 g = w4 ? w4[i] : make_float4(1.f, 1.f, 1.f, 1.f);
+        o4[i] = make_float4(v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
+    }
+}
+
+// Rotary embedding (rotate-half pairing: element i pairs with i + hd/2) of the q and k parts of a fused
+// qkv row, then k and v are appended to the cache at position pos[b].
+//   qkv [B, (nq + 2*nkv) * hd];  q_out [B, nq*hd];  cache_k / cache_v [B, nkv, max_ctx, hd]
+__global__ void __launch_bounds__(128) rope_append_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ pos,
+                                                          uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx,
+                                                          float theta, float* __restrict__ q_out,
+                                                          float* __restrict__ cache_k, float* __restrict__ cache_v) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    pdl_wait_();
+    const uint32_t b = blockIdx.y, head = blockIdx.x;  // heads 0..nq-1: q; nq..nq+nkv-1: k; then v
+    const uint32_t p = (uint32_t)pos[b];
+    const float* src = qkv + ((uint64_t)b * (nq + 2 * nkv) + head) * hd;
+    const uint32_t half = hd / 2;
+    if (head < nq + nkv) {
+        float* dst = head < nq ? q_out + ((uint64_t)b * nq + head) * hd
+                               : cache_k + (((uint64_t)b * nkv + (head - nq)) * max_ctx + p) * hd;
+        for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
+            float freq = powf(theta, -2.0f * (float)i / (float)hd);
+            float s, c;
+            sincosf((float)p * freq, &s, &c);
+            float a = src[i], bb = src[i + half];
+            dst[i] = a * c - bb * s;
+            dst[i + half] = a * s + bb * c;
+        }
+    } else {
+        float* dst = cache_v + (((uint64_t)b * nkv + (head - nq - nkv)) * max_ctx + p) * hd;
+        for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+// One new token per sequence: out[b, head, :] = softmax(q . K^T / sqrt(hd)) V over positions 0..pos[b].
+// The positions are cut into chunks of ATT_CHUNK; one CTA per (q head, chunk, sequence) produces the
+// chunk's un-normalised result with its own maximum and sum, and a second kernel merges the chunks in
+// order.  Grouped-query: q head -> kv head = head / (nq / nkv).
+constexpr uint32_t ATT_CHUNK = 64;
+
+// part[b, head, chunk, 0..hd-1] = sum_t exp(s_t - m) V[t, :];  part[.., hd] = m;  part[.., hd+1] = sum_t exp(s_t - m)
+__global__ void __launch_bounds__(128) attention_partial_kernel(const float* __restrict__ q, const float* __restrict__ cache_k,
+                                                                const float* __restrict__ cache_v,
+                                                                const int32_t* __restrict__ pos, uint32_t nq, uint32_t nkv,
+                                                                uint32_t hd, uint32_t max_ctx, uint32_t n_chunks,
+                                                                float* __restrict__ part) {
+    extern __shared__ float s_att[];  // hd (q) + ATT_CHUNK (scores)
+    __shared__ float red[4];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    pdl_wait_();
+    const uint32_t head = blockIdx.x, chunk = blockIdx.y, b = blockIdx.z, kvh = head / (nq / nkv);
+    const uint32_t n_ctx = (uint32_t)pos[b] + 1;
+    const uint32_t t0 = chunk * ATT_CHUNK;
+    float* dst = part + (((uint64_t)b * nq + head) * n_chunks + chunk) * (hd + 2);
+    if (t0 >= n_ctx) {
+        if (threadIdx.x == 0) {
+            dst[hd] = -INFINITY;
+            dst[hd + 1] = 0.0f;
+        }
+        return;
+    }
+    const uint32_t cnt = min(ATT_CHUNK, n_ctx - t0);
+    float* sq = s_att;
+    float* sc = s_att + hd;
+    const float* qr = q + ((uint64_t)b * nq + head) * hd;
+    for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) sq[i] = qr[i];
+    __syncthreads();
+    const float* K = cache_k + (((uint64_t)b * nkv + kvh) * max_ctx + t0) * hd;
+    const float* V = cache_v + (((uint64_t)b * nkv + kvh) * max_ctx + t0) * hd;
+    const float scale = rsqrtf((float)hd);
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float mx = -INFINITY;
+    for (uint32_t t = warp; t < cnt; t += nw) {
+        const float* kr = K + (uint64_t)t * hd;
+        float acc = 0.0f;
+        for (uint32_t i = lane; i < hd; i += 32) acc = fmaf(sq[i], kr[i], acc);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+        acc *= scale;
+        if (lane == 0) sc[t] = acc;
+        mx = fmaxf(mx, acc);
+    }
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (uint32_t i = 1; i < nw; ++i) mx = fmaxf(mx, red[i]);
+    __syncthreads();
+    float sum = 0.0f;
+    for (uint32_t t = threadIdx.x; t < cnt; t += blockDim.x) {
+        float e = expf(sc[t] - mx);
+        sc[t] = e;
+        sum += e;
+    }
+    sum = block_sum(sum, red);
+    for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) {
+        float acc = 0.0f;
+        for (uint32_t t = 0; t < cnt; ++t) acc = fmaf(sc[t], V[(uint64_t)t * hd + i], acc);
+        dst[i] = acc;
+    }
+    if (threadIdx.x == 0) {
+        dst[hd] = mx;
+        dst[hd + 1] = sum;
+    }
+}
+
+__global__ void __launch_bounds__(128) attention_merge_kernel(const float* __restrict__ part, uint32_t hd, uint32_t n_chunks,
+                                                              float* __restrict__ out) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    pdl_wait_();
+    const uint64_t bh = blockIdx.x;  // (sequence, head)
+    const float* src = part + bh * n_chunks * (hd + 2);
+    float mx = -INFINITY;
+    for (uint32_t c = 0; c < n_chunks; ++c) mx = fmaxf(mx, src[(uint64_t)c * (hd + 2) + hd]);
+    float den = 0.0f;
+    for (uint32_t c = 0; c < n_chunks; ++c) {
+        float m = src[(uint64_t)c * (hd + 2) + hd];
+        if (m != -INFINITY) den += expf(m - mx) * src[(uint64_t)c * (hd + 2) + hd + 1];
+    }
+    for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) {
+        float acc = 0.0f;
+        for (uint32_t c = 0; c < n_chunks; ++c) {
+            float m = src[(uint64_t)c * (hd + 2) + hd];
+            if (m != -INFINITY) acc = fmaf(expf(m - mx), src[(uint64_t)c * (hd + 2) + i], acc);
+        }
+        out[bh * hd + i] = acc / den;
+    }
+}
+
+// y = a + b
+__global__ void __launch_bounds__(256) add_kernel(const float* __restrict__ a, const float* __restrict__ b, uint64_t n,
+                                                  float* __restrict__ y) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    pdl_wait_();
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        y[i] = a[i] + b[i];
+}
+
+// Greedy sampling: index of the maximum of each row; among equal maxima the LAST index wins, as
+// `iter().enumerate().max_by(partial_cmp)` does (src/engine.rs:2371-2378).  Two stages: ARGMAX_SLICES CTAs
+// per row reduce a slice each, then one CTA per row merges them and advances pos[b].
+constexpr uint32_t ARGMAX_SLICES = 64;
+
+__device__ __forceinline__ void argmax_merge(float& best, uint32_t& idx, float ob, uint32_t oi) {
+    if (ob > best || (ob == best && oi > idx)) {
+        best = ob;
+        idx = oi;
+    }
+}
+
+__device__ __forceinline__ void argmax_block(float& best, uint32_t& idx, float* sv, uint32_t* si) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ob = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+        uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, idx, o);
+        argmax_merge(best, idx, ob, oi);
+    }
+    if (lane == 0) {
+        sv[warp] = best;
+        si[warp] = idx;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0)
+        for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) argmax_merge(best, idx, sv[w], si[w]);
+}
+
+__global__ void __launch_bounds__(256) argmax_slices_kernel(const float* __restrict__ logits, uint32_t vocab,
+                                                            float* __restrict__ part_v, uint32_t* __restrict__ part_i) {
+    __shared__ float sv[8];
+    __shared__ uint32_t si[8];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    pdl_wait_();
+    const float* row = logits + (uint64_t)blockIdx.y * vocab;
+    const uint32_t per = (vocab + ARGMAX_SLICES - 1) / ARGMAX_SLICES;
+    const uint32_t lo = blockIdx.x * per, hi = min(vocab, lo + per);
+    float best = -INFINITY;
+    uint32_t idx = 0;
+    for (uint32_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        float v = row[i];
+        if (v >= best) {
+            best = v;
+            idx = i;
+        }
+    }
+    argmax_block(best, idx, sv, si);
+    if (threadIdx.x == 0) {
+        part_v[blockIdx.y * ARGMAX_SLICES + blockIdx.x] = best;
+        part_i[blockIdx.y * ARGMAX_SLICES + blockIdx.x] = idx;
+    }
+}
+
+__global__ void __launch_bounds__(64) argmax_final_kernel(const float* __restrict__ part_v, const uint32_t* __restrict__ part_i,
+                                                          int32_t* __restrict__ token, int32_t* __restrict__ pos) {
+    __shared__ float sv[2];
+    __shared__ uint32_t si[2];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    pdl_wait_();
+    float best = part_v[blockIdx.x * ARGMAX_SLICES + threadIdx.x];
+    uint32_t idx = part_i[blockIdx.x * ARGMAX_SLICES + threadIdx.x];
+    argmax_block(best, idx, sv, si);
+    if (threadIdx.x == 0) {
+        token[blockIdx.x] = (int32_t)idx;
+        if (pos) pos[blockIdx.x] += 1;
+    }
+}
+
+unsigned blocks_for(uint64_t work, unsigned per_block) {
+    uint64_t b = (work + per_block - 1) / per_block;
+    return (unsigned)(b < 1 ? 1 : (b > 148ull * 16 ? 148ull * 16 : b));
+}
+
+}  // namespace
+
+cudaError_t launch_rmsnorm(const float* x, const float* res, const float* w, float eps, uint64_t rows, uint32_t h,
+                           float* sum_out, float* out, cudaStream_t s) {
+    if (h % 4) return cudaErrorInvalidValue;
+    cudaError_t le1__ = launch_pdl(rmsnorm_kernel, (unsigned)rows, 1024, 0, s, x, res, w, eps, h, sum_out, out);
+    if (le1__ != cudaSuccess) return le1__;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rope_append(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
+                               uint32_t hd, uint32_t max_ctx, float theta, float* q_out, float* cache_k, float* cache_v,
+                               cudaStream_t s) {
+    cudaError_t le2__ = launch_pdl(rope_append_kernel, dim3(nq + 2 * nkv, batch), 128, 0, s, qkv, pos, nq, nkv, hd, max_ctx, theta, q_out, cache_k,
+                                                                 cache_v);
+    if (le2__ != cudaSuccess) return le2__;
+    return cudaGetLastError();
+}
+
+size_t attention_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t hd, uint32_t max_ctx) {
+    uint32_t n_chunks = (max_ctx + ATT_CHUNK - 1) / ATT_CHUNK;
+    return (size_t)batch * nq * n_chunks * (hd + 2) * 4;
+}
+
+cudaError_t launch_attention_decode(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,
+                                    uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx, float* out,
+                                    float* scratch, cudaStream_t s) {
+    uint32_t n_chunks = (max_ctx + ATT_CHUNK - 1) / ATT_CHUNK;
+    size_t smem = (size_t)(hd + ATT_CHUNK) * 4;
+    cudaError_t le3__ = launch_pdl(attention_partial_kernel, dim3(nq, n_chunks, batch), 128, smem, s, q, cache_k, cache_v, pos, nq, nkv, hd, max_ctx,
+                                                                          n_chunks, scratch);
+    if (le3__ != cudaSuccess) return le3__;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    cudaError_t le4__ = launch_pdl(attention_merge_kernel, batch * nq, 128, 0, s, scratch, hd, n_chunks, out);
+    if (le4__ != cudaSuccess) return le4__;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_add(const float* a, const float* b, uint64_t n, float* y, cudaStream_t s) {
+    cudaError_t le5__ = launch_pdl(add_kernel, blocks_for(n, 256), 256, 0, s, a, b, n, y);
+    if (le5__ != cudaSuccess) return le5__;
+    return cudaGetLastError();
+}
+
+size_t argmax_scratch_bytes(uint32_t rows) { return (size_t)rows * ARGMAX_SLICES * 8; }
+
+cudaError_t launch_argmax(const float* logits, uint32_t rows, uint32_t vocab, int32_t* token, int32_t* pos,
+                          void* scratch, cudaStream_t s) {
+    float* pv = static_cast<float*>(scratch);
+    uint32_t* pi = reinterpret_cast<uint32_t*>(pv + (size_t)rows * ARGMAX_SLICES);
+    cudaError_t le6__ = launch_pdl(argmax_slices_kernel, dim3(ARGMAX_SLICES, rows), 256, 0, s, logits, vocab, pv, pi);
+    if (le6__ != cudaSuccess) return le6__;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    cudaError_t le7__ = launch_pdl(argmax_final_kernel, rows, 64, 0, s, pv, pi, token, pos);
+    if (le7__ != cudaSuccess) return le7__;
+    return cudaGetLastError();
+}
+
+}  // namespace jq

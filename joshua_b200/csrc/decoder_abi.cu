@@ -1,0 +1,107 @@
+// C ABI of the decode-step kernels around the matmuls.  Declarations are in include/joshua_b200.h.
+#include "handles.cuh"
+
+extern "C" {
+
+int32_t jq_matmul_swiglu_dev(const jq_weight* gate, const jq_weight* up, uint64_t m, uint64_t k, uint64_t n,
+                             const float* lhs_dev, float* dst_dev, float clamp, void* stream) {
+    if (!gate || !up) return jq_fail(jq::E_INVALID, "jq_matmul_swiglu_dev: NULL weight handle");
+    if (gate->type != up->type || gate->n_blocks != up->n_blocks)
+        return jq_fail(jq::E_INVALID, "jq_matmul_swiglu_dev: gate and up differ in type or size");
+    if (k % gate->fmt.elems != 0 || gate->n_blocks != n * (k / gate->fmt.elems))
+        return jq_fail(jq::E_INVALID, std::string(jq_type_name(gate->type)) + " matmul: rhs holds " +
+                                          std::to_string(gate->n_blocks) + " blocks, expected " +
+                                          std::to_string(k % gate->fmt.elems ? 0 : n * (k / gate->fmt.elems)));
+    if (m == 0 || n == 0) return jq::OK;
+    if (!lhs_dev || !dst_dev) return jq_fail(jq::E_INVALID, "jq_matmul_swiglu_dev: NULL buffer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    jq_ctx* ctx = gate->ctx;
+    if (!ctx->force_f32 && jq::gemv_mma_supports(gate->type, gate->dev, n, k, m) &&
+        jq::gemv_mma_supports(up->type, up->dev, n, k, m) && jq::gemv_mma_scratch_bytes(m, k) == 0) {
+        JQ_CUDA(jq::launch_gemv_mma_swiglu(gate->type, gate->dev, up->dev, n, k, lhs_dev, m, dst_dev, clamp,
+                                           ctx->status_dev, s));
+        return jq::OK;
+    }
+    // two products into scratch, then the element-wise combine
+    void* scratch = nullptr;
+    size_t need = 2 * m * n * 4 + 512;
+    JQ_CUDA(ctx->scratch_for(reinterpret_cast<cudaStream_t>(reinterpret_cast<uintptr_t>(s) ^ 1), need, &scratch));
+    float* g = static_cast<float*>(scratch);
+    float* u = g + ((m * n + 63) & ~(uint64_t)63);
+    if (int32_t rc = jq_matmul_device(gate, m, k, n, lhs_dev, g, s)) return rc;
+    if (int32_t rc = jq_matmul_device(up, m, k, n, lhs_dev, u, s)) return rc;
+    JQ_CUDA(jq::launch_swiglu(g, u, m * n, clamp, dst_dev, s));
+    return jq::OK;
+}
+
+int32_t jq_embedding_dev(const jq_weight* w, const uint32_t* ids_dev, uint64_t n_ids, uint64_t rows, uint64_t hidden,
+                         float* out_dev, int32_t* bad_id_dev, void* stream) {
+    if (!w) return jq_fail(jq::E_INVALID, "jq_embedding_dev: NULL weight handle");
+    if (hidden % w->fmt.elems != 0)
+        return jq_fail(jq::E_INVALID, "quantized embedding hidden size " + std::to_string(hidden) +
+                                          " is not divisible by block size " + std::to_string(w->fmt.elems));
+    if (w->n_blocks != rows * (hidden / w->fmt.elems))
+        return jq_fail(jq::E_INVALID, "quantized tensor has " + std::to_string(w->n_blocks) + " blocks, expected " +
+                                          std::to_string(rows * (hidden / w->fmt.elems)));
+    if (n_ids == 0) return jq::OK;
+    if (!ids_dev || !out_dev || !bad_id_dev) return jq_fail(jq::E_INVALID, "jq_embedding_dev: NULL buffer");
+    JQ_CUDA(jq::launch_embedding(w->type, w->dev, rows, hidden, ids_dev, n_ids, out_dev, bad_id_dev,
+                                 static_cast<cudaStream_t>(stream)));
+    return jq::OK;
+}
+
+int32_t jq_rmsnorm_dev(const float* x, const float* residual, const float* weight, float eps, uint64_t rows,
+                       uint64_t hidden, float* sum_out, float* out, void* stream) {
+    if (rows == 0) return jq::OK;
+    if (!x || !out || hidden == 0) return jq_fail(jq::E_INVALID, "jq_rmsnorm_dev: NULL buffer");
+    if (residual && !sum_out) return jq_fail(jq::E_INVALID, "jq_rmsnorm_dev: a residual needs sum_out");
+    JQ_CUDA(jq::launch_rmsnorm(x, residual, weight, eps, rows, (uint32_t)hidden, sum_out, out,
+                               static_cast<cudaStream_t>(stream)));
+    return jq::OK;
+}
+
+int32_t jq_rope_append_dev(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t n_q, uint32_t n_kv,
+                           uint32_t head_dim, uint32_t max_ctx, float theta, float* q_out, float* cache_k,
+                           float* cache_v, void* stream) {
+    if (batch == 0) return jq::OK;
+    if (!qkv || !pos || !q_out || !cache_k || !cache_v || head_dim % 2 || n_kv == 0 || n_q % n_kv)
+        return jq_fail(jq::E_INVALID, "jq_rope_append_dev: bad argument");
+    JQ_CUDA(jq::launch_rope_append(qkv, pos, batch, n_q, n_kv, head_dim, max_ctx, theta, q_out, cache_k, cache_v,
+                                   static_cast<cudaStream_t>(stream)));
+    return jq::OK;
+}
+
+uint64_t jq_attention_scratch_bytes(uint32_t batch, uint32_t n_q, uint32_t head_dim, uint32_t max_ctx) {
+    return jq::attention_scratch_bytes(batch, n_q, head_dim, max_ctx);
+}
+
+int32_t jq_attention_decode_dev(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,
+                                uint32_t batch, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t max_ctx,
+                                float* out, float* scratch, void* stream) {
+    if (batch == 0) return jq::OK;
+    if (!q || !cache_k || !cache_v || !pos || !out || !scratch || n_kv == 0 || n_q % n_kv)
+        return jq_fail(jq::E_INVALID, "jq_attention_decode_dev: bad argument");
+    JQ_CUDA(jq::launch_attention_decode(q, cache_k, cache_v, pos, batch, n_q, n_kv, head_dim, max_ctx, out, scratch,
+                                        static_cast<cudaStream_t>(stream)));
+    return jq::OK;
+}
+
+int32_t jq_add_dev(const float* a, const float* b, uint64_t n, float* y, void* stream) {
+    if (n == 0) return jq::OK;
+    if (!a || !b || !y) return jq_fail(jq::E_INVALID, "jq_add_dev: NULL buffer");
+    JQ_CUDA(jq::launch_add(a, b, n, y, static_cast<cudaStream_t>(stream)));
+    return jq::OK;
+}
+
+uint64_t jq_argmax_scratch_bytes(uint64_t rows) { return jq::argmax_scratch_bytes((uint32_t)rows); }
+
+int32_t jq_argmax_dev(const float* logits, uint64_t rows, uint64_t vocab, int32_t* token, int32_t* pos, void* scratch,
+                      void* stream) {
+    if (rows == 0) return jq::OK;
+    if (!logits || !token || !scratch || vocab == 0) return jq_fail(jq::E_INVALID, "jq_argmax_dev: bad argument");
+    JQ_CUDA(jq::launch_argmax(logits, (uint32_t)rows, (uint32_t)vocab, token, pos, scratch,
+                              static_cast<cudaStream_t>(stream)));
+    return jq::OK;
+}
+
+}  // extern "C"

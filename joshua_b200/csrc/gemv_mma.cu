@@ -710,8 +710,8 @@ struct GemvArgs {
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 
-// GROUPED == 0 is the dense product (one implicit job, one bank, plain store); the job list and the SwiGLU
-// pair are compiled in only for GROUPED == 1.
+// GROUPED == 0 is the dense product (one implicit job, one bank, plain store), 1 the dense SwiGLU pair
+// (two banks, dst = silu(g) * u); the job list is compiled in only for GROUPED == 2.
 template <uint32_t TYPE, int MB, int NH, int NCW, int ACT, int GROUPED>
 __global__ void __launch_bounds__((NCW + 2) * 32, 1) gemv_mma_kernel(const __grid_constant__ GemvArgs ga) {
     using Tr = Traits<TYPE>;
@@ -738,9 +738,9 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1) gemv_mma_kernel(const __gri
     const uint32_t units_per_row = (uint32_t)(k / 256);
     const uint64_t row_bytes = (uint64_t)units_per_row * Tr::UNIT_BYTES;
     const uint32_t n_chunks = (units_per_row + Tr::CHUNK_UNITS - 1) / Tr::CHUNK_UNITS;
-    const uint32_t n_sub = GROUPED && ga.swiglu ? 2 : 1;  // weight banks visited per tile
-    constexpr bool grouped = GROUPED != 0;
-    const bool swiglu = GROUPED && ga.swiglu;
+    constexpr bool grouped = GROUPED == 2;
+    const bool swiglu = GROUPED == 1 || (GROUPED == 2 && ga.swiglu);
+    const uint32_t n_sub = swiglu ? 2 : 1;  // weight banks visited per tile
     const uint32_t n_groups = (uint32_t)(k / 32);
 
     if (tid == 0) {
@@ -986,24 +986,6 @@ SmemPlan plan_smem(uint64_t k, uint64_t act_rows_in_smem, uint64_t jobs_per_cta)
 
 int g_num_sms = 0;
 
-// Launch with programmatic stream serialization: the kernel may start while its predecessor in the stream
-// is still draining; every access that depends on the predecessor sits behind pdl_wait().
-template <class... KArgs, class... Args>
-cudaError_t launch_pdl(void (*kern)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t s,
-                       Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(block);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
-}
-
 template <uint32_t TYPE, int MB, int NH, int ACT, int GROUPED>
 cudaError_t launch_variant(GemvArgs& ga, uint64_t max_tiles, cudaStream_t s) {
     constexpr int NCW = 16;
@@ -1110,6 +1092,26 @@ cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_
     return launch_typed<0, 0>(type, ga, (uint32_t)m, tiles, s);
 }
 
+// silu(clamp(gate x)) * clamp(up x) in one launch (activation planes in shared memory only)
+cudaError_t launch_gemv_mma_swiglu(uint32_t type, const uint8_t* w_gate, const uint8_t* w_up, uint64_t n, uint64_t k,
+                                   const float* lhs, uint64_t m, float* dst, float clamp, int* error_flag,
+                                   cudaStream_t s) {
+    if (!acts_fit_in_smem(m, k)) return cudaErrorInvalidValue;
+    GemvArgs ga = {};
+    ga.w[0] = w_gate;
+    ga.w[1] = w_up;
+    ga.n = n;
+    ga.k = k;
+    ga.x = lhs;
+    ga.x_rows = (uint32_t)m;
+    ga.m = (uint32_t)m;
+    ga.dst = dst;
+    ga.clamp = clamp;
+    ga.swiglu = 1;
+    ga.error_flag = error_flag;
+    return launch_typed<1, 1>(type, ga, (uint32_t)m, (n + ROWS - 1) / ROWS, s);
+}
+
 // ── the allocation-free variant ──────────────────────────────────────────────────────────────────────
 //
 // Same product as launch_gemv_mma on its scratch path (activation planes written to global memory by
@@ -1180,9 +1182,9 @@ cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s) {
     ga.swiglu = g.w1 != nullptr;
     ga.error_flag = g.error_flag;
     uint64_t tiles = (uint64_t)g.max_jobs * ((g.n + ROWS - 1) / ROWS);
-    if (g.planes == nullptr) return launch_typed<1, 1>(g.type, ga, g.rows_per_job, tiles, s);
+    if (g.planes == nullptr) return launch_typed<1, 2>(g.type, ga, g.rows_per_job, tiles, s);
     ga.act = planes_in(g.planes, g.x_rows, g.k);
-    return launch_typed<0, 1>(g.type, ga, g.rows_per_job, tiles, s);
+    return launch_typed<0, 2>(g.type, ga, g.rows_per_job, tiles, s);
 }
 
 }  // namespace jq

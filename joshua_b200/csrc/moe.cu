@@ -13,6 +13,7 @@ namespace {
 __global__ void __launch_bounds__(256) moe_logits_kernel(const float* __restrict__ x, const float* __restrict__ router,
                                                          uint32_t T, uint32_t E, uint32_t h,
                                                          float* __restrict__ logits) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t lane = threadIdx.x & 31;
     const uint64_t total = (uint64_t)T * E;
@@ -71,6 +72,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     __shared__ uint8_t s_taken[4][MAX_EXPERTS];
     __shared__ float s_group[4][64];
     __shared__ uint8_t s_gtaken[4][64];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t lane = threadIdx.x & 31, wq = threadIdx.x >> 5;
     const uint32_t E = rp.n_expert, K = rp.n_used;
@@ -189,6 +191,7 @@ __global__ void __launch_bounds__(1024) moe_jobs_kernel(const uint32_t* __restri
     __shared__ uint32_t s_cnt[MAX_EXPERTS];
     __shared__ uint32_t s_off[MAX_EXPERTS];
     __shared__ uint32_t s_job[MAX_EXPERTS];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
     const uint32_t P = T * K;
@@ -246,6 +249,7 @@ __global__ void __launch_bounds__(1024) moe_jobs_kernel(const uint32_t* __restri
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ out, const uint32_t* __restrict__ inv,
                                                           const float* __restrict__ wts, const float* __restrict__ shared,
                                                           uint32_t T, uint32_t K, uint32_t h, float* __restrict__ y) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint64_t total = (uint64_t)T * (h / 4);
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total;
@@ -277,6 +281,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
 // does not take)
 __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ g, const float* __restrict__ u,
                                                      uint64_t n, float clamp, float* __restrict__ out) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
         float gv = g[i], uv = u[i];
@@ -297,14 +302,16 @@ unsigned blocks_for(uint64_t work, unsigned per_block) {
 
 cudaError_t launch_moe_logits(const float* x, const float* router, uint32_t T, uint32_t E, uint32_t h, float* logits,
                               cudaStream_t s) {
-    moe_logits_kernel<<<blocks_for((uint64_t)T * E, 8), 256, 0, s>>>(x, router, T, E, h, logits);
+    cudaError_t le1__ = launch_pdl(moe_logits_kernel, blocks_for((uint64_t)T * E, 8), 256, 0, s, x, router, T, E, h, logits);
+    if (le1__ != cudaSuccess) return le1__;
     return cudaGetLastError();
 }
 
 cudaError_t launch_moe_route(const float* logits, const MoeRouteParams& rp, uint32_t T, const float* bias,
                              const uint32_t* forced_ids, uint32_t* ids, float* wts, cudaStream_t s) {
     if (rp.n_expert > MAX_EXPERTS || rp.n_group > 64) return cudaErrorInvalidValue;
-    moe_route_kernel<<<blocks_for(T, 4), 128, 0, s>>>(logits, rp, T, bias, forced_ids, ids, wts);
+    cudaError_t le2__ = launch_pdl(moe_route_kernel, blocks_for(T, 4), 128, 0, s, logits, rp, T, bias, forced_ids, ids, wts);
+    if (le2__ != cudaSuccess) return le2__;
     return cudaGetLastError();
 }
 
@@ -312,18 +319,21 @@ cudaError_t launch_moe_jobs(const uint32_t* ids, uint32_t T, uint32_t K, uint32_
                             uint32_t* list_token, uint32_t* inv, MoeJob* jobs, uint32_t* n_jobs, uint32_t* n_list,
                             int* bad_id, cudaStream_t s) {
     if (E > MAX_EXPERTS) return cudaErrorInvalidValue;
-    moe_jobs_kernel<<<1, 1024, 0, s>>>(ids, T, K, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id);
+    cudaError_t le3__ = launch_pdl(moe_jobs_kernel, 1, 1024, 0, s, ids, T, K, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id);
+    if (le3__ != cudaSuccess) return le3__;
     return cudaGetLastError();
 }
 
 cudaError_t launch_moe_combine(const float* out, const uint32_t* inv, const float* wts, const float* shared, uint32_t T,
                                uint32_t K, uint32_t h, float* y, cudaStream_t s) {
-    moe_combine_kernel<<<blocks_for((uint64_t)T * (h / 4), 256), 256, 0, s>>>(out, inv, wts, shared, T, K, h, y);
+    cudaError_t le4__ = launch_pdl(moe_combine_kernel, blocks_for((uint64_t)T * (h / 4), 256), 256, 0, s, out, inv, wts, shared, T, K, h, y);
+    if (le4__ != cudaSuccess) return le4__;
     return cudaGetLastError();
 }
 
 cudaError_t launch_swiglu(const float* g, const float* u, uint64_t n, float clamp, float* out, cudaStream_t s) {
-    swiglu_kernel<<<blocks_for(n, 256), 256, 0, s>>>(g, u, n, clamp, out);
+    cudaError_t le5__ = launch_pdl(swiglu_kernel, blocks_for(n, 256), 256, 0, s, g, u, n, clamp, out);
+    if (le5__ != cudaSuccess) return le5__;
     return cudaGetLastError();
 }
 

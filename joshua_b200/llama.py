@@ -1,0 +1,146 @@
+"""A Llama-style decoder whose every step runs on the device through the C ABI.
+
+Host-side model code in the manner of the reference's loaders (embedding ->
+per layer {RMS norm -> attention -> residual -> RMS norm -> SwiGLU MLP ->
+residual} -> norm -> output head -> greedy token; the shape of
+`GGUFQWenMoE::forward`, src/quantized_qwen3_moe.rs:793-819, with a dense MLP).
+Weights are quantized tensors (`QTensor`); the step is a fixed sequence of
+launches on one stream with no host round trip, so it can be captured in a CUDA
+graph.  The KV cache is f32 [batch, n_kv, max_ctx, head_dim] per layer.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+from . import _lib, synth
+from ._lib import check
+from .qtensor import QTensor
+
+
+@dataclass
+class LlamaConfig:
+    layers: int = 32
+    hidden: int = 4096
+    q_heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 14336
+    vocab: int = 128256
+    rope_theta: float = 500000.0
+    eps: float = 1e-5
+
+    @property
+    def qkv_rows(self) -> int:
+        return (self.q_heads + 2 * self.kv_heads) * self.head_dim
+
+
+class LlamaDecoder:
+    """Random-init model of `cfg` with every linear (and the embedding) stored as `wtype` blocks."""
+
+    def __init__(self, cfg: LlamaConfig, device, batch: int = 1, max_ctx: int = 640, wtype: int = synth.Q4_K,
+                 seed: int = 0, weights=None):
+        import torch
+
+        self.torch, self.cfg, self.dev, self.batch, self.max_ctx, self.wtype = torch, cfg, device, batch, max_ctx, wtype
+        self.weight_bytes = 0
+        h, f32 = cfg.hidden, dict(dtype=torch.float32, device=device)
+        gen = torch.Generator(device=device)
+        gen.manual_seed(seed)
+        mk = weights or (lambda name, n, k, s: synth.random_weight_torch(wtype, n, k, s, device))
+        self._raw = {}
+
+        def q(name, n, k, s):
+            raw = mk(name, n, k, s)
+            raw = torch.cat([raw.to(device), torch.zeros(16, dtype=torch.uint8, device=device)])
+            nbytes = synth.tensor_bytes(wtype, n, k)
+            self.weight_bytes += nbytes
+            self._raw[name] = raw
+            return QTensor.from_device(wtype, raw[:nbytes])
+
+        self.embed = q("token_embd", cfg.vocab, h, seed * 7919 + 1)
+        self.weight_bytes -= synth.tensor_bytes(wtype, cfg.vocab, h)  # one row is read per token, not the table
+        self.layers = []
+        for l in range(cfg.layers):
+            s0 = seed * 7919 + 100 + l * 10
+            self.layers.append(dict(
+                attn_norm=1.0 + 0.1 * torch.randn(h, generator=gen, **f32),
+                ffn_norm=1.0 + 0.1 * torch.randn(h, generator=gen, **f32),
+                wqkv=q(f"l{l}.wqkv", cfg.qkv_rows, h, s0), wo=q(f"l{l}.wo", h, cfg.q_heads * cfg.head_dim, s0 + 1),
+                w_gate=q(f"l{l}.w_gate", cfg.ffn, h, s0 + 2), w_up=q(f"l{l}.w_up", cfg.ffn, h, s0 + 3),
+                w_down=q(f"l{l}.w_down", h, cfg.ffn, s0 + 4),
+                k=torch.zeros(batch, cfg.kv_heads, max_ctx, cfg.head_dim, **f32),
+                v=torch.zeros(batch, cfg.kv_heads, max_ctx, cfg.head_dim, **f32)))
+        self.out_norm = 1.0 + 0.1 * torch.randn(h, generator=gen, **f32)
+        self.output = q("output", cfg.vocab, h, seed * 7919 + 2)
+        B = batch
+        self.token = torch.full((B,), 42, dtype=torch.int32, device=device)
+        self.pos = torch.zeros(B, dtype=torch.int32, device=device)
+        self.bad = torch.zeros(1, dtype=torch.int32, device=device)
+        self.x = torch.empty(B, h, **f32)
+        self.x1 = torch.empty(B, h, **f32)
+        self.xn = torch.empty(B, h, **f32)
+        self.qkv = torch.empty(B, cfg.qkv_rows, **f32)
+        self.q = torch.empty(B, cfg.q_heads * cfg.head_dim, **f32)
+        self.attn = torch.empty(B, cfg.q_heads * cfg.head_dim, **f32)
+        self.o = torch.empty(B, h, **f32)
+        self.act = torch.empty(B, cfg.ffn, **f32)
+        self.d = torch.empty(B, h, **f32)
+        self.logits = torch.empty(B, cfg.vocab, **f32)
+        att_bytes = _lib.lib().jq_attention_scratch_bytes(B, cfg.q_heads, cfg.head_dim, max_ctx)
+        self.att_scratch = torch.empty(att_bytes // 4 + 1, **f32)
+        self.argmax_scratch = torch.empty(_lib.lib().jq_argmax_scratch_bytes(B) // 4 + 1, **f32)
+        self.launches_per_step = 9 * cfg.layers + 5
+        self.matmuls_per_step = 4 * cfg.layers + 1
+
+    # ── one token ───────────────────────────────────────────────────────
+    def step(self, stream=None) -> None:
+        """Decode one token per sequence: reads self.token / self.pos, writes self.logits, the next
+        self.token and advances self.pos.  Launches only."""
+        L, c, B = _lib.lib(), self.cfg, self.batch
+        s = self.torch.cuda.current_stream(self.dev).cuda_stream if stream is None else stream
+        h, P = c.hidden, lambda t: t.data_ptr()
+        check(L.jq_embedding_dev(self.embed._h, P(self.token), B, c.vocab, h, P(self.x), P(self.bad), s))
+        for i, ly in enumerate(self.layers):
+            if i == 0:
+                check(L.jq_rmsnorm_dev(P(self.x), None, P(ly["attn_norm"]), c.eps, B, h, None, P(self.xn), s))
+            else:  # x = x1 + d of the previous layer, fused with this layer's norm
+                check(L.jq_rmsnorm_dev(P(self.d), P(self.x1), P(ly["attn_norm"]), c.eps, B, h, P(self.x), P(self.xn), s))
+            check(L.jq_matmul_t_dev(ly["wqkv"]._h, B, h, c.qkv_rows, P(self.xn), P(self.qkv), s))
+            check(L.jq_rope_append_dev(P(self.qkv), P(self.pos), B, c.q_heads, c.kv_heads, c.head_dim, self.max_ctx,
+                                       c.rope_theta, P(self.q), P(ly["k"]), P(ly["v"]), s))
+            check(L.jq_attention_decode_dev(P(self.q), P(ly["k"]), P(ly["v"]), P(self.pos), B, c.q_heads, c.kv_heads,
+                                            c.head_dim, self.max_ctx, P(self.attn), P(self.att_scratch), s))
+            check(L.jq_matmul_t_dev(ly["wo"]._h, B, c.q_heads * c.head_dim, h, P(self.attn), P(self.o), s))
+            check(L.jq_rmsnorm_dev(P(self.o), P(self.x), P(ly["ffn_norm"]), c.eps, B, h, P(self.x1), P(self.xn), s))
+            check(L.jq_matmul_swiglu_dev(ly["w_gate"]._h, ly["w_up"]._h, B, h, c.ffn, P(self.xn), P(self.act), 0.0, s))
+            check(L.jq_matmul_t_dev(ly["w_down"]._h, B, c.ffn, h, P(self.act), P(self.d), s))
+        check(L.jq_rmsnorm_dev(P(self.d), P(self.x1), P(self.out_norm), c.eps, B, h, P(self.x), P(self.xn), s))
+        check(L.jq_matmul_t_dev(self.output._h, B, h, c.vocab, P(self.xn), P(self.logits), s))
+        check(L.jq_argmax_dev(P(self.logits), B, c.vocab, P(self.token), P(self.pos), P(self.argmax_scratch), s))
+
+    def matmuls_only(self, stream=None) -> None:
+        """The quantized matmuls of one token back to back (the kernel-level roofline probe)."""
+        L, c, B = _lib.lib(), self.cfg, self.batch
+        s = self.torch.cuda.current_stream(self.dev).cuda_stream if stream is None else stream
+        h, P = c.hidden, lambda t: t.data_ptr()
+        for ly in self.layers:
+            check(L.jq_matmul_t_dev(ly["wqkv"]._h, B, h, c.qkv_rows, P(self.xn), P(self.qkv), s))
+            check(L.jq_matmul_t_dev(ly["wo"]._h, B, c.q_heads * c.head_dim, h, P(self.attn), P(self.o), s))
+            check(L.jq_matmul_swiglu_dev(ly["w_gate"]._h, ly["w_up"]._h, B, h, c.ffn, P(self.xn), P(self.act), 0.0, s))
+            check(L.jq_matmul_t_dev(ly["w_down"]._h, B, c.ffn, h, P(self.act), P(self.d), s))
+        check(L.jq_matmul_t_dev(self.output._h, B, h, c.vocab, P(self.xn), P(self.logits), s))
+
+    def algorithmic_bytes(self) -> int:
+        """Weight bytes of the matmuls + their f32 inputs and outputs, per token step."""
+        c, B = self.cfg, self.batch
+        io = c.layers * 4 * B * ((c.hidden + c.qkv_rows) + (c.q_heads * c.head_dim + c.hidden) +
+                                 (c.hidden + c.ffn) + (c.ffn + c.hidden)) + 4 * B * (c.hidden + c.vocab)
+        return self.weight_bytes + io
+
+    def reset(self, token: int = 42) -> None:
+        self.token.fill_(token)
+        self.pos.zero_()
+
+    def force_token(self, token: int) -> None:
+        self.token.fill_(token)
