@@ -69,6 +69,10 @@ int32_t jq_matmul_device(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n,
         JQ_CUDA(jq::launch_gemv_mma(w->type, w->dev, n, k, lhs, m, dst, scratch, ctx->status_dev, s));
         return jq::OK;
     }
+    if (!ctx->force_f32 && m > jq::GEMV_MMA_MAX_M && jq::gemm_tc_supports(w->type, w->dev, n, k, m)) {
+        JQ_CUDA(jq::launch_gemm_tc(w->type, w->dev, n, k, lhs, m, dst, ctx->status_dev, s));
+        return jq::OK;
+    }
     JQ_CUDA(jq::launch_matmul_f32(w->type, w->dev, n, k, lhs, m, dst, s));
     return jq::OK;
 }
@@ -126,6 +130,7 @@ int32_t jq_init(int32_t device, jq_ctx** out) {
     JQ_CUDA(jq::tables_dequant());
     JQ_CUDA(jq::tables_gemv_f32());
     JQ_CUDA(jq::tables_gemv_mma());
+    JQ_CUDA(jq::tables_gemm_tc());
     jq_ctx* c = new (std::nothrow) jq_ctx();
     if (!c) return jq_fail(jq::E_NOMEM, "jq_init: out of host memory");
     c->device = device;

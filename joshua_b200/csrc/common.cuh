@@ -53,6 +53,12 @@ cudaError_t tables_gemv_f32();
 cudaError_t launch_matmul_f32(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
                               float* dst, cudaStream_t s);
 
+// gemm_tc.cu: tcgen05 tile GEMM for m > 8 (prefill, batched decode)
+cudaError_t tables_gemm_tc();
+bool gemm_tc_supports(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, uint64_t m);
+cudaError_t launch_gemm_tc(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
+                           float* dst, int* error_flag, cudaStream_t s);
+
 // One unit of grouped (MoE) work: up to 8 consecutive positions of the expert-sorted activation list,
 // all routed to `expert`.
 struct MoeJob {
