@@ -7,6 +7,9 @@ Workloads
            (--batch up to 8): the KV cache is filled with --prefill positions, then one
            step = one greedily decoded token, the whole step on the device
            (4.22 GB of raw Q4_K blocks read once per token).
+  qwen3moe decode of a Qwen3-MoE-shaped model (128 experts top-8, Q4_K experts, Q8_0 attention);
+           with --gpus N > 1 (under torchrun) the experts are split over the ranks and rows
+           are exchanged by NCCL all-to-all.
   gemv     one quantized matmul shape, rotated over a working set larger than L2
            (--type, --n, --k, --m, --rotate-gb): the kernel-level roofline probe
            and the command used for ncu captures.
@@ -235,7 +238,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama8b", choices=["llama8b", "gemv"])
+    ap.add_argument("--workload", default="llama8b", choices=["llama8b", "gemv", "qwen3moe"])
     ap.add_argument("--type", default="q4_k", choices=sorted(TYPE_BY_NAME))
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -248,6 +251,10 @@ def main():
         return run_reference(args)
     if args.workload == "gemv":
         return run_gemv(args)
+    if args.workload == "qwen3moe":
+        from joshua_b200 import bench_moe
+
+        return bench_moe.run(args)
     from joshua_b200 import bench_llama
 
     return bench_llama.run(args)

@@ -117,6 +117,58 @@ class ExpertParallelMoe:
         return y
 
 
+def _all_to_all_equal(out: torch.Tensor, inp: torch.Tensor, group) -> None:
+    """Equal-split all-to-all: block p of `inp` goes to rank p."""
+    if dist.get_backend(group) == "nccl":
+        dist.all_to_all_single(out, inp, group=group)
+        return
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    gathered = [torch.empty_like(inp) for _ in range(world)]
+    dist.all_gather(gathered, inp, group=group)
+    n = inp.shape[0] // world
+    for src in range(world):
+        out[src * n:(src + 1) * n] = gathered[src][rank * n:(rank + 1) * n]
+
+
+def _forward_fixed(self, x: torch.Tensor) -> torch.Tensor:
+    """The same layer without any host read: every rank sends every peer a block of fixed capacity
+    T * k rows (unused rows carry an out-of-range expert id and come back as zeros), so all sizes are known
+    up front and the layer can be captured in a CUDA graph.  Meant for decode-sized batches."""
+    T, h = x.shape
+    K, W = self.n_used, self.world
+    cap = T * K
+    ids, wts = self.compute.route(x)
+    flat = ids.reshape(-1).to(torch.int64)
+    owner = torch.div(flat, self.per_rank, rounding_mode="floor")
+    order = torch.argsort(owner, stable=True)
+    counts = torch.bincount(owner, minlength=W)[:W]
+    starts = torch.cumsum(counts, 0) - counts
+    owner_sorted = owner.index_select(0, order)
+    slot_sorted = owner_sorted * cap + (torch.arange(cap, device=x.device) - starts.index_select(0, owner_sorted))
+    slot = torch.empty_like(slot_sorted)
+    slot.index_copy_(0, order, slot_sorted)                      # slot of pair p in the send buffer
+    send_rows = x.new_zeros((W * cap, h))
+    send_ids = torch.full((W * cap,), self.per_rank, dtype=torch.int32, device=x.device)  # out of range = unused
+    token_of = torch.div(torch.arange(cap, device=x.device), K, rounding_mode="floor")
+    send_rows.index_copy_(0, slot, x.index_select(0, token_of))
+    send_ids.index_copy_(0, slot, (flat - owner * self.per_rank).to(torch.int32))
+    recv_rows = torch.empty_like(send_rows)
+    recv_ids = torch.empty_like(send_ids)
+    _all_to_all_equal(recv_rows, send_rows, self.group)
+    _all_to_all_equal(recv_ids, send_ids, self.group)
+    out_rows = self.compute.experts(recv_rows, recv_ids)
+    back = torch.empty_like(out_rows)
+    _all_to_all_equal(back, out_rows, self.group)
+    per_pair = back.index_select(0, slot).reshape(T, K, h)
+    y = torch.zeros_like(x)
+    for s in range(K):
+        y.addcmul_(per_pair[:, s, :], wts[:, s:s + 1])
+    return y
+
+
+ExpertParallelMoe.forward_fixed = _forward_fixed
+
+
 def cuda_compute(router_layer, expert_layer) -> EpCompute:
     """EpCompute over two `joshua_b200.moe.Moe` layers: a router-only layer with the global expert count and
     a layer holding this rank's expert banks."""

@@ -113,11 +113,16 @@ class LlamaDecoder:
                                             c.head_dim, self.max_ctx, P(self.attn), P(self.att_scratch), s))
             check(L.jq_matmul_t_dev(ly["wo"]._h, B, c.q_heads * c.head_dim, h, P(self.attn), P(self.o), s))
             check(L.jq_rmsnorm_dev(P(self.o), P(self.x), P(ly["ffn_norm"]), c.eps, B, h, P(self.x1), P(self.xn), s))
-            check(L.jq_matmul_swiglu_dev(ly["w_gate"]._h, ly["w_up"]._h, B, h, c.ffn, P(self.xn), P(self.act), 0.0, s))
-            check(L.jq_matmul_t_dev(ly["w_down"]._h, B, c.ffn, h, P(self.act), P(self.d), s))
+            self._ffn(ly, s)
         check(L.jq_rmsnorm_dev(P(self.d), P(self.x1), P(self.out_norm), c.eps, B, h, P(self.x), P(self.xn), s))
         check(L.jq_matmul_t_dev(self.output._h, B, h, c.vocab, P(self.xn), P(self.logits), s))
         check(L.jq_argmax_dev(P(self.logits), B, c.vocab, P(self.token), P(self.pos), P(self.argmax_scratch), s))
+
+    def _ffn(self, ly, s) -> None:
+        """self.d = FFN(self.xn): the dense SwiGLU MLP."""
+        L, c, B, P = _lib.lib(), self.cfg, self.batch, lambda t: t.data_ptr()
+        check(L.jq_matmul_swiglu_dev(ly["w_gate"]._h, ly["w_up"]._h, B, c.hidden, c.ffn, P(self.xn), P(self.act), 0.0, s))
+        check(L.jq_matmul_t_dev(ly["w_down"]._h, B, c.ffn, c.hidden, P(self.act), P(self.d), s))
 
     def matmuls_only(self, stream=None) -> None:
         """The quantized matmuls of one token back to back (the kernel-level roofline probe)."""

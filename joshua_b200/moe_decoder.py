@@ -1,0 +1,104 @@
+"""A Qwen3-MoE-shaped decoder: the Llama-style step of `llama.py` with a routed-expert FFN in every layer.
+
+Attention projections are `attn_type` blocks (Q8_0 in the benchmark configuration), expert banks `expert_type`
+blocks (Q4_K).  On one GPU a layer's FFN is `Moe.forward_dev`.  With an expert-parallel group the banks are
+split over the ranks and the FFN is `ep.ExpertParallelMoe`: every rank decodes its own sequences, routes
+locally, and exchanges activation rows with the owners of the chosen experts.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib, synth
+from .llama import LlamaConfig, LlamaDecoder
+from .moe import GATE_SOFTMAX, OOB_SKIP, Moe, MoeConfig
+from .qtensor import QTensor, default_context
+
+
+@dataclass
+class MoeDecoderConfig(LlamaConfig):
+    layers: int = 48
+    hidden: int = 2048
+    q_heads: int = 32
+    kv_heads: int = 4
+    head_dim: int = 128
+    ffn: int = 256          # unused dense width (kept small: no dense FFN weights are built)
+    vocab: int = 151936
+    rope_theta: float = 1000000.0
+    n_expert: int = 128
+    n_used: int = 8
+    moe_inter: int = 768
+
+
+class MoeDecoder(LlamaDecoder):
+    def __init__(self, cfg: MoeDecoderConfig, device, batch: int = 1, max_ctx: int = 640, attn_type: int = synth.Q8_0,
+                 expert_type: int = synth.Q4_K, seed: int = 0, group=None):
+        import torch
+        import torch.distributed as dist
+
+        self.group = group
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self._expert_type = expert_type
+        self._dense_ffn = False
+        super().__init__(cfg, device, batch=batch, max_ctx=max_ctx, wtype=attn_type, seed=seed)
+        ctx = default_context(device.index or 0)
+        E, K, h, I = cfg.n_expert, cfg.n_used, cfg.hidden, cfg.moe_inter
+        per = E // self.world
+        self.ffn_layers = []
+        self.expert_bytes = 0
+        gen = torch.Generator(device=device)
+        for l in range(cfg.layers):
+            # router and banks are the same on every rank for the same layer (seeded by layer, not by rank)
+            gen.manual_seed(1000 + l)
+            router = (torch.randn(E, h, generator=gen, device=device, dtype=torch.float32) * 0.5).cpu().numpy()
+            banks = []
+            for i, (rows, cols) in enumerate([(I, h), (I, h), (h, I)]):
+                full_seed = 5000 + l * 8 + i
+                # each rank draws only its own experts' blocks; the seed folds in the first local expert
+                raw = synth.random_weight_torch(expert_type, per * rows, cols, full_seed * 1000 + self.rank * per, device)
+                raw = torch.cat([raw, torch.zeros(16, dtype=torch.uint8, device=device)])
+                nbytes = synth.tensor_bytes(expert_type, per * rows, cols)
+                self.expert_bytes += nbytes
+                banks.append((QTensor.from_device(expert_type, raw[:nbytes], ctx), raw))
+            if self.world == 1:
+                layer = Moe(MoeConfig(gating=GATE_SOFTMAX, n_expert=E, n_used=K, hidden=h, inter=I, norm=True),
+                            router, banks[0][0], banks[1][0], banks[2][0], ctx=ctx)
+                layer.reserve(batch, batch * K)
+                self.ffn_layers.append(dict(moe=layer, keep=banks))
+            else:
+                from .ep import ExpertParallelMoe, cuda_compute
+
+                rl = Moe(MoeConfig(gating=GATE_SOFTMAX, n_expert=E, n_used=K, hidden=h, inter=I, norm=True), router,
+                         None, None, None, ctx=ctx)
+                el = Moe(MoeConfig(gating=GATE_SOFTMAX, n_expert=per, n_used=1, hidden=h, inter=I, oob_policy=OOB_SKIP),
+                         np.zeros((per, h), np.float32), banks[0][0], banks[1][0], banks[2][0], ctx=ctx)
+                cap = batch * K * self.world
+                rl.reserve(batch, 0)
+                el.reserve(cap, cap)
+                ep = ExpertParallelMoe(E, K, cuda_compute(rl, el), group=group)
+                self.ffn_layers.append(dict(ep=ep, keep=(banks, rl, el)))
+        self.launches_per_step = (7 + 6) * cfg.layers + 5
+
+    # the dense FFN weights of the parent are never used: build tiny ones
+    def _ffn(self, ly, s) -> None:
+        i = self._layer_index[id(ly)]
+        f = self.ffn_layers[i]
+        if "moe" in f:
+            f["moe"].forward_dev(self.xn, self.d, stream=s)
+        else:
+            self.d.copy_(f["ep"].forward_fixed(self.xn))
+
+    def step(self, stream=None) -> None:
+        if not hasattr(self, "_layer_index"):
+            self._layer_index = {id(ly): i for i, ly in enumerate(self.layers)}
+        super().step(stream)
+
+    def expert_bytes_per_token(self) -> int:
+        """Expert-bank bytes one token touches: n_used experts x 3 matrices per layer."""
+        c = self.cfg
+        per_expert = 2 * synth.tensor_bytes(self._expert_type, c.moe_inter, c.hidden) + \
+            synth.tensor_bytes(self._expert_type, c.hidden, c.moe_inter)
+        return c.layers * c.n_used * per_expert

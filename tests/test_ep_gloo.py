@@ -49,7 +49,7 @@ def _worker(rank, world, port, out_dir):
              banks[2][rank * elem_d:(rank + 1) * elem_d]]
     gcfg = oracle.moe_cfg(gating=oracle.GATE_SOFTMAX, n_expert=E, n_used=K, hidden=H, inter=INTER)
     lcfg = oracle.moe_cfg(gating=oracle.GATE_SOFTMAX, n_expert=per, n_used=1, hidden=H, inter=INTER,
-                          decode_path=False)
+                          decode_path=False, oob_policy=oracle.OOB_SKIP)
 
     def route(x):
         ids, w = oracle.moe_route(gcfg, oracle.moe_logits(x.numpy(), router))
@@ -57,6 +57,7 @@ def _worker(rank, world, port, out_dir):
 
     def experts(rows, local_ids):
         ones = np.ones((rows.shape[0], 1), np.float32)
+        # unused rows of the fixed-capacity exchange carry an out-of-range id and must come back as zeros
         y = oracle.moe_dispatch(lcfg, rows.numpy(), local_ids.numpy().astype(np.uint32).reshape(-1, 1), ones,
                                 [TYPE] * 3, local)
         return torch.from_numpy(y)
@@ -64,6 +65,9 @@ def _worker(rank, world, port, out_dir):
     layer = ExpertParallelMoe(E, K, EpCompute(route, experts))
     y = layer.forward(torch.from_numpy(xs[rank]))
     np.save(os.path.join(out_dir, f"y{rank}.npy"), y.numpy())
+    # the fixed-capacity variant needs the same number of tokens on every rank
+    yf = layer.forward_fixed(torch.from_numpy(xs[rank][:T]))
+    np.save(os.path.join(out_dir, f"yf{rank}.npy"), yf.numpy())
     np.save(os.path.join(out_dir, f"load{rank}.npy"), np.array([layer.last_load]))
     dist.destroy_process_group()
 
@@ -83,4 +87,6 @@ def test_two_rank_expert_parallel_matches_single_process(tmp_path):
         got = np.load(tmp_path / f"y{r}.npy")
         assert np.all(np.abs(got - want) <= 1e-4 * np.maximum(np.abs(want), 1.0))
         loads += int(np.load(tmp_path / f"load{r}.npy")[0])
+        got_fixed = np.load(tmp_path / f"yf{r}.npy")
+        assert np.all(np.abs(got_fixed - want[:T]) <= 1e-4 * np.maximum(np.abs(want[:T]), 1.0))
     assert loads == sum(x.shape[0] for x in xs) * K  # every pair was computed exactly once
