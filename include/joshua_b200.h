@@ -285,6 +285,41 @@ int32_t jq_moe_status(jq_moe* m);
 /* ids and weights chosen by the last forward (host copies), for inspection. */
 int32_t jq_moe_last_routing(jq_moe* m, uint64_t n_tokens, uint32_t* ids, float* wts);
 
+/* ── Expert-parallel exchange: one process per GPU, experts split contiguously over the ranks ──
+ * No counterpart in the reference, which runs every expert of a layer in one
+ * process (src/quantized_qwen3_moe.rs:385-542, expert tensors laid out
+ * [n_expert, out, in], :572-613); this is the one place the path shards.
+ * Activation rows travel to the rank that owns the chosen expert and the
+ * outputs travel back by direct stores into peer memory over NVLink (CUDA IPC
+ * mappings); every rank passes its own tokens and gets its own outputs,
+ * y[t] = sum over slots in slot order of w[t,s] * MLP_{id[t,s]}(x[t]), the
+ * same values for any number of ranks.
+ *
+ *   jq_ep_create   on every rank (rank < world <= 8, n_expert % world == 0,
+ *                  max_tokens * n_used <= 4096): allocates this rank's window
+ *   jq_ep_export   writes the JQ_EP_HANDLE_BYTES-byte handle of the window;
+ *                  the host gathers the handles of all ranks, in rank order,
+ *                  by whatever means it has (MPI, a store, torch.distributed)
+ *   jq_ep_connect  maps the peers' windows (handles: world x 64 bytes); every
+ *                  rank must have connected before any rank's first forward
+ *   jq_ep_forward_dev  one layer.  `router` is a layer with the global expert
+ *                  count (it may be router-only), `experts` a layer whose
+ *                  banks hold this rank's n_expert / world experts (oob_policy
+ *                  1; reserved for world * max_tokens * n_used rows).  Every
+ *                  rank must call it the same number of times in the same
+ *                  order, one exchange per call.  Waits on peers are bounded
+ *                  (about a second): a rank that never arrives is reported by
+ *                  jq_device_status as JQ_E_TIMEOUT instead of a hang. */
+#define JQ_EP_HANDLE_BYTES 64
+typedef struct jq_ep jq_ep;
+int32_t jq_ep_create(jq_ctx* ctx, uint32_t rank, uint32_t world, uint32_t n_expert, uint32_t n_used, uint32_t hidden,
+                     uint32_t max_tokens, jq_ep** out);
+void jq_ep_free(jq_ep* e);
+int32_t jq_ep_export(jq_ep* e, uint8_t* handle);
+int32_t jq_ep_connect(jq_ep* e, const uint8_t* handles);
+int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float* x_dev, uint64_t n_tokens,
+                          float* y_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

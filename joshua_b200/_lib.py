@@ -67,6 +67,11 @@ _SIGNATURES = {
     "jq_moe_experts_dev": (i32, [vp, vp, u64, vp, vp, vp]),
     "jq_moe_status": (i32, [vp]),
     "jq_moe_last_routing": (i32, [vp, u64, vp, vp]),
+    "jq_ep_create": (i32, [vp, u32, u32, u32, u32, u32, u32, ctypes.POINTER(vp)]),
+    "jq_ep_free": (None, [vp]),
+    "jq_ep_export": (i32, [vp, vp]),
+    "jq_ep_connect": (i32, [vp, vp]),
+    "jq_ep_forward_dev": (i32, [vp, vp, vp, vp, u64, vp, vp]),
 }
 
 

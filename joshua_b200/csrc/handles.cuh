@@ -112,3 +112,30 @@ struct jq_weight {
 // Picks the kernel for a device-resident product (abi.cu).
 int32_t jq_matmul_device(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const float* lhs, float* dst,
                          cudaStream_t s);
+
+// One MoE layer (moe_abi.cu); shared with the expert-parallel exchange (ep.cu).
+struct jq_moe {
+    jq_ctx* ctx;
+    jq_moe_config cfg;
+    jq::MoeRouteParams rp;
+    float* router = nullptr;  // [E, h] f32, device
+    float* bias = nullptr;    // [E] or NULL
+    const jq_weight *gate, *up, *down, *sh_gate, *sh_up, *sh_down;
+    uint64_t gate_expert_bytes, down_expert_bytes;
+    // workspace, grown to the largest (tokens, pairs) seen
+    uint64_t cap_tokens = 0, cap_pairs = 0;
+    uint8_t* ws = nullptr;
+    float *logits, *wts, *hidden, *out, *sh_hidden, *sh_out, *ones;
+    uint32_t *ids, *list_token, *inv, *n_jobs, *n_list;
+    jq::MoeJob* jobs;
+    void *planes_x, *planes_h;
+    // constants on the device: jobs {0, 0, c} for c = 1..8 (a dense product as a single job) and the count 1
+    jq::MoeJob* dense_jobs = nullptr;
+    uint32_t* one = nullptr;
+    int* bad_host = nullptr;  // pinned, device-visible: an expert id was out of range
+    int* bad_dev = nullptr;
+    std::mutex mu;
+};
+
+int32_t jq_moe_experts_list(jq_moe* m, const float* x_dev, uint64_t n_rows, const uint32_t* expert_ids_dev,
+                            cudaStream_t s);

@@ -2,28 +2,6 @@
 // Declarations and the reference interfaces they replace are in include/joshua_b200.h.
 #include "handles.cuh"
 
-struct jq_moe {
-    jq_ctx* ctx;
-    jq_moe_config cfg;
-    jq::MoeRouteParams rp;
-    float* router = nullptr;  // [E, h] f32, device
-    float* bias = nullptr;    // [E] or NULL
-    const jq_weight *gate, *up, *down, *sh_gate, *sh_up, *sh_down;
-    uint64_t gate_expert_bytes, down_expert_bytes;
-    // workspace, grown to the largest (tokens, pairs) seen
-    uint64_t cap_tokens = 0, cap_pairs = 0;
-    uint8_t* ws = nullptr;
-    float *logits, *wts, *hidden, *out, *sh_hidden, *sh_out, *ones;
-    uint32_t *ids, *list_token, *inv, *n_jobs, *n_list;
-    jq::MoeJob* jobs;
-    void *planes_x, *planes_h;
-    // constants on the device: jobs {0, 0, c} for c = 1..8 (a dense product as a single job) and the count 1
-    jq::MoeJob* dense_jobs = nullptr;
-    uint32_t* one = nullptr;
-    int* bad_host = nullptr;  // pinned, device-visible: an expert id was out of range
-    int* bad_dev = nullptr;
-    std::mutex mu;
-};
 
 namespace {
 
@@ -194,6 +172,17 @@ int32_t check_bank(const char* name, const jq_weight* w, uint64_t experts, uint6
 
 }  // namespace
 
+// Expert MLPs over rows with one expert id each, left in expert-sorted list order: row r's output is
+// m->out[m->inv[r], :] (inv = 0xFFFFFFFF for an id out of range).  Arguments are checked by the callers.
+int32_t jq_moe_experts_list(jq_moe* m, const float* x_dev, uint64_t n_rows, const uint32_t* expert_ids_dev,
+                            cudaStream_t s) {
+    const jq_moe_config& c = m->cfg;
+    uint32_t rpj = rows_per_job_for(n_rows, n_rows == 1 ? 1 : 2, c.n_expert);
+    JQ_CUDA(jq::launch_moe_jobs(expert_ids_dev, (uint32_t)n_rows, 1, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
+                                m->n_jobs, m->n_list, m->bad_dev, s));
+    return run_experts(m, x_dev, n_rows, n_rows, rpj, s);
+}
+
 extern "C" {
 
 int32_t jq_moe_create(jq_ctx* ctx, const jq_moe_config* cfg, const float* router, const float* bias,
@@ -305,13 +294,9 @@ int32_t jq_moe_experts_dev(jq_moe* m, const float* x_dev, uint64_t n_rows, const
     if (n_rows > m->cap_tokens || n_rows > m->cap_pairs)
         return jq_fail(jq::E_TOO_LARGE, "jq_moe_experts_dev: call jq_moe_reserve for this many rows first");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const jq_moe_config& c = m->cfg;
-    uint32_t rpj = rows_per_job_for(n_rows, n_rows == 1 ? 1 : 2, c.n_expert);
-    JQ_CUDA(jq::launch_moe_jobs(expert_ids_dev, (uint32_t)n_rows, 1, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
-                                m->n_jobs, m->n_list, m->bad_dev, s));
-    if (int32_t rc = run_experts(m, x_dev, n_rows, n_rows, rpj, s)) return rc;
+    if (int32_t rc = jq_moe_experts_list(m, x_dev, n_rows, expert_ids_dev, s)) return rc;
     // back to row order: out[r] = out_list[inv[r]] (rows with an id out of range come back as zeros)
-    JQ_CUDA(jq::launch_moe_combine(m->out, m->inv, m->ones, nullptr, (uint32_t)n_rows, 1, c.hidden, out_dev, s));
+    JQ_CUDA(jq::launch_moe_combine(m->out, m->inv, m->ones, nullptr, (uint32_t)n_rows, 1, m->cfg.hidden, out_dev, s));
     return jq::OK;
 }
 

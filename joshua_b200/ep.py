@@ -187,3 +187,54 @@ def cuda_compute(router_layer, expert_layer) -> EpCompute:
         return out
 
     return EpCompute(route, experts)
+
+
+class PeerExchange:
+    """The exchange of `ExpertParallelMoe` done by the library's own kernels: rows are stored straight into
+    the owning rank's memory over NVLink (CUDA IPC mappings) and polled for with bounded waits, with no
+    collective call and no host read, so a whole decode step can be one CUDA graph.  One object serves every
+    layer of a model.  `torch.distributed` is used once, to hand the window handles round."""
+
+    def __init__(self, ctx, n_expert: int, n_used: int, hidden: int, max_tokens: int, group=None):
+        import ctypes
+
+        from . import _lib
+
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.ctx = ctx
+        self.hidden, self.max_tokens = hidden, max_tokens
+        self.rows = self.world * max_tokens * n_used      # rows the local expert layer must be reserved for
+        self._h = ctypes.c_void_p()
+        _lib.check(_lib.lib().jq_ep_create(ctx._h, self.rank, self.world, n_expert, n_used, hidden, max_tokens,
+                                           ctypes.byref(self._h)))
+        if self.world > 1:
+            mine = (ctypes.c_uint8 * 64)()
+            _lib.check(_lib.lib().jq_ep_export(self._h, mine))
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(mine), group=group)
+            blob = (ctypes.c_uint8 * (64 * self.world)).from_buffer_copy(b"".join(handles))
+            _lib.check(_lib.lib().jq_ep_connect(self._h, blob))
+            dist.barrier(group=group)                      # nobody stores into a window that is not mapped yet
+
+    def forward_dev(self, router_layer, expert_layer, x, y, stream=None) -> None:
+        from . import _lib
+
+        T = x.numel() // self.hidden
+        s = torch.cuda.current_stream(x.device).cuda_stream if stream is None else stream
+        _lib.check(_lib.lib().jq_ep_forward_dev(self._h, router_layer._h, expert_layer._h, x.data_ptr(), T,
+                                                y.data_ptr(), s))
+
+    def close(self) -> None:
+        from . import _lib
+
+        if self._h:
+            _lib.lib().jq_ep_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -69,8 +69,10 @@ class MoeDecoder(LlamaDecoder):
                 layer.reserve(batch, batch * K)
                 self.ffn_layers.append(dict(moe=layer, keep=banks))
             else:
-                from .ep import ExpertParallelMoe, cuda_compute
+                from .ep import PeerExchange
 
+                if l == 0:
+                    self.exchange = PeerExchange(ctx, E, K, h, batch, group=group)
                 rl = Moe(MoeConfig(gating=GATE_SOFTMAX, n_expert=E, n_used=K, hidden=h, inter=I, norm=True), router,
                          None, None, None, ctx=ctx)
                 el = Moe(MoeConfig(gating=GATE_SOFTMAX, n_expert=per, n_used=1, hidden=h, inter=I, oob_policy=OOB_SKIP),
@@ -78,9 +80,8 @@ class MoeDecoder(LlamaDecoder):
                 cap = batch * K * self.world
                 rl.reserve(batch, 0)
                 el.reserve(cap, cap)
-                ep = ExpertParallelMoe(E, K, cuda_compute(rl, el), group=group)
-                self.ffn_layers.append(dict(ep=ep, keep=(banks, rl, el)))
-        self.launches_per_step = (7 + 6) * cfg.layers + 5
+                self.ffn_layers.append(dict(router=rl, experts=el, keep=banks))
+        self.launches_per_step = (7 + (6 if self.world == 1 else 9)) * cfg.layers + 5
 
     # the dense FFN weights of the parent are never used: build tiny ones
     def _ffn(self, ly, s) -> None:
@@ -89,7 +90,7 @@ class MoeDecoder(LlamaDecoder):
         if "moe" in f:
             f["moe"].forward_dev(self.xn, self.d, stream=s)
         else:
-            self.d.copy_(f["ep"].forward_fixed(self.xn))
+            self.exchange.forward_dev(f["router"], f["experts"], self.xn, self.d, stream=s)
 
     def step(self, stream=None) -> None:
         if not hasattr(self, "_layer_index"):

@@ -1,4 +1,5 @@
-"""Expert-parallel MoE over NCCL on two GPUs against the single-GPU layer (skipped with fewer than two GPUs)."""
+"""Expert-parallel MoE on two GPUs against the single-GPU layer (skipped with fewer than two GPUs): the
+torch.distributed orchestration over NCCL all-to-all, and the library's own exchange over peer memory."""
 import os
 import socket
 import sys
@@ -26,8 +27,8 @@ def _worker(rank, world, port, out_dir):
     import torch.distributed as dist
 
     from joshua_b200 import synth
-    from joshua_b200.ep import ExpertParallelMoe, cuda_compute
-    from joshua_b200.moe import GATE_SOFTMAX, Moe, MoeConfig
+    from joshua_b200.ep import ExpertParallelMoe, PeerExchange, cuda_compute
+    from joshua_b200.moe import GATE_SOFTMAX, OOB_SKIP, Moe, MoeConfig
     from joshua_b200.qtensor import Context, QTensor
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -59,9 +60,24 @@ def _worker(rank, world, port, out_dir):
     torch.cuda.synchronize()
     expert_layer.status()
     want = single.forward(x)
+    # the same layer through the peer-memory exchange: three exchanges in a row over one window
+    exchange = PeerExchange(ctx, E, K, H, max_tokens=8)
+    skip_cfg = MoeConfig(gating=GATE_SOFTMAX, n_expert=per, n_used=1, hidden=H, inter=INTER, oob_policy=OOB_SKIP)
+    peer_experts = Moe(skip_cfg, np.zeros((per, H), np.float32), *local, ctx=ctx)
+    peer_experts.reserve(0, exchange.rows)
+    xd = torch.from_numpy(x).cuda()
+    outs = [torch.empty_like(xd) for _ in range(3)]
+    for o in outs:
+        exchange.forward_dev(router_layer, peer_experts, xd, o)
+    torch.cuda.synchronize()
+    peer_experts.status()
+    dist.barrier()
+    peer_err = float(np.abs(outs[0].cpu().numpy() - want).max() / max(1.0, np.abs(want).max()))
+    peer_diff = float(sum((o != outs[0]).sum().item() for o in outs))
     np.save(os.path.join(out_dir, f"ok{rank}.npy"),
             np.array([float(np.abs(y.cpu().numpy() - want).max() / max(1.0, np.abs(want).max())),
-                      float((y != y2).sum().item())]))
+                      float((y != y2).sum().item()), peer_err, peer_diff]))
+    exchange.close()
     dist.destroy_process_group()
 
 
@@ -73,5 +89,6 @@ def test_two_gpu_expert_parallel(tmp_path):
         pytest.skip("needs two GPUs")
     mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     for r in range(2):
-        err, diff = np.load(tmp_path / f"ok{r}.npy")
+        err, diff, peer_err, peer_diff = np.load(tmp_path / f"ok{r}.npy")
         assert err <= 1e-5 and diff == 0
+        assert peer_err <= 1e-5 and peer_diff == 0   # and the same bits on every exchange
