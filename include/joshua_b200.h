@@ -189,6 +189,22 @@ int32_t jq_embedding_dev(const jq_weight* w, const uint32_t* ids_dev, uint64_t n
 int32_t jq_rmsnorm_dev(const float* x, const float* residual, const float* weight, float eps, uint64_t rows,
                        uint64_t hidden, float* sum_out, float* out, void* stream);
 
+/* The same with the RMS norm of the block folded in: dst = silu(gate xn) * up xn
+ * with xn = rmsnorm(lhs; norm_w, eps) computed inside the matmul kernel. */
+int32_t jq_matmul_swiglu_norm_dev(const jq_weight* gate, const jq_weight* up, uint64_t m, uint64_t k, uint64_t n,
+                                  const float* lhs_dev, const float* norm_w_dev, float eps, float* dst_dev,
+                                  float clamp, void* stream);
+
+/* dst = residual + rmsnorm(lhs; norm_w, eps) . W^T: a quantized linear with the
+ * RMS norm in front of it and the residual add behind it in the same launch
+ * (the `RmsNorm` -> `QMatMul::forward` -> `xs + residual` pattern of
+ * src/quantized_qwen3_moe.rs:793-819).  norm_w_dev and residual_dev are each
+ * optional; residual_dev may be dst_dev.  One launch when m <= 8 and the
+ * activation planes fit shared memory, otherwise the separate kernels. */
+int32_t jq_matmul_norm_dev(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const float* lhs_dev,
+                           const float* norm_w_dev, float eps, const float* residual_dev, float* dst_dev,
+                           void* stream);
+
 /* Rotary embedding of q and k (pairing element i with i + head_dim/2) at
  * position pos[b], then k and v appended to the cache: the rope + `Tensor::cat`
  * of src/quantized_qwen3_moe.rs:330-364.  qkv: [batch, (n_q + 2 n_kv) *
@@ -196,6 +212,17 @@ int32_t jq_rmsnorm_dev(const float* x, const float* residual, const float* weigh
 int32_t jq_rope_append_dev(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t n_q, uint32_t n_kv,
                            uint32_t head_dim, uint32_t max_ctx, float theta, float* q_out, float* cache_k,
                            float* cache_v, void* stream);
+
+/* Rope, cache append and attention in ONE launch, straight from the fused qkv
+ * row: out[b, head, :] as jq_rope_append_dev + jq_attention_decode_dev give it.
+ * `scratch`: jq_attention_fused_scratch_bytes(...) bytes of caller device
+ * memory, ZEROED once before the first call (it holds arrival counters that
+ * the kernel leaves at zero).  n_q / n_kv <= 8, head_dim <= 256. */
+uint64_t jq_attention_fused_scratch_bytes(uint32_t batch, uint32_t n_q, uint32_t n_kv, uint32_t head_dim,
+                                          uint32_t max_ctx);
+int32_t jq_attention_fused_dev(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t n_q, uint32_t n_kv,
+                               uint32_t head_dim, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,
+                               float* out, void* scratch, void* stream);
 
 /* Grouped-query attention of one new token per sequence over positions
  * 0..pos[b] of the cache (src/quantized_qwen3_moe.rs:366-386).  `scratch`:
@@ -269,6 +296,11 @@ int32_t jq_moe_reserve(jq_moe* m, uint64_t n_tokens, uint64_t n_rows);
 int32_t jq_moe_forward_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, const uint32_t* forced_ids_dev,
                            float* y_dev, void* stream);
 
+/* y = residual + layer(x): the residual add of the surrounding block folded into
+ * the combine (residual_dev may be y_dev, or NULL for jq_moe_forward_dev). */
+int32_t jq_moe_forward_add_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, const uint32_t* forced_ids_dev,
+                               const float* residual_dev, float* y_dev, void* stream);
+
 /* The two halves, for expert-parallel callers that exchange rows between
  * devices in between: routing alone (ids, weights: [n_tokens, n_used]), and the
  * expert MLPs alone over arbitrary rows, out[r] = MLP_{expert_ids[r]}(x[r])
@@ -307,7 +339,8 @@ int32_t jq_moe_last_routing(jq_moe* m, uint64_t n_tokens, uint32_t* ids, float* 
  *                  banks hold this rank's n_expert / world experts (oob_policy
  *                  1; reserved for world * max_tokens * n_used rows).  Every
  *                  rank must call it the same number of times in the same
- *                  order, one exchange per call.  Waits on peers are bounded
+ *                  order, one exchange per call.  residual_dev (optional, may be
+ *                  y_dev) is added to the result.  Waits on peers are bounded
  *                  (about a second): a rank that never arrives is reported by
  *                  jq_device_status as JQ_E_TIMEOUT instead of a hang. */
 #define JQ_EP_HANDLE_BYTES 64
@@ -318,7 +351,7 @@ void jq_ep_free(jq_ep* e);
 int32_t jq_ep_export(jq_ep* e, uint8_t* handle);
 int32_t jq_ep_connect(jq_ep* e, const uint8_t* handles);
 int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float* x_dev, uint64_t n_tokens,
-                          float* y_dev, void* stream);
+                          const float* residual_dev, float* y_dev, void* stream);
 
 #ifdef __cplusplus
 }

@@ -24,7 +24,7 @@ class JoshuaB200Error(RuntimeError):
 
 _lib = None
 
-u64, i32, u32, vp = ctypes.c_uint64, ctypes.c_int32, ctypes.c_uint32, ctypes.c_void_p
+u64, i32, u32, vp, f32 = ctypes.c_uint64, ctypes.c_int32, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_float
 pp = ctypes.POINTER(ctypes.c_void_p)
 
 _SIGNATURES = {
@@ -71,7 +71,12 @@ _SIGNATURES = {
     "jq_ep_free": (None, [vp]),
     "jq_ep_export": (i32, [vp, vp]),
     "jq_ep_connect": (i32, [vp, vp]),
-    "jq_ep_forward_dev": (i32, [vp, vp, vp, vp, u64, vp, vp]),
+    "jq_ep_forward_dev": (i32, [vp, vp, vp, vp, u64, vp, vp, vp]),
+    "jq_moe_forward_add_dev": (i32, [vp, vp, u64, vp, vp, vp, vp]),
+    "jq_matmul_swiglu_norm_dev": (i32, [vp, vp, u64, u64, u64, vp, vp, f32, vp, f32, vp]),
+    "jq_matmul_norm_dev": (i32, [vp, u64, u64, u64, vp, vp, f32, vp, vp, vp]),
+    "jq_attention_fused_scratch_bytes": (u64, [u32, u32, u32, u32, u32]),
+    "jq_attention_fused_dev": (i32, [vp, vp, u32, u32, u32, u32, u32, f32, vp, vp, vp, vp, vp]),
 }
 
 

@@ -76,10 +76,17 @@ bool gemv_mma_supports(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, 
 // error_flag: device int set to 1 if a bounded wait inside the kernel gave up
 cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
                             float* dst, void* scratch, int* error_flag, cudaStream_t s);
-// Fused gate / up pair with the SwiGLU epilogue; valid when gemv_mma_scratch_bytes(m, k) == 0.
+// Fused gate / up pair with the SwiGLU epilogue; valid when gemv_mma_scratch_bytes(m, k) == 0.  With norm_w
+// the rows of lhs are RMS-normalised (weights norm_w, epsilon eps) inside the kernel first.
 cudaError_t launch_gemv_mma_swiglu(uint32_t type, const uint8_t* w_gate, const uint8_t* w_up, uint64_t n, uint64_t k,
                                    const float* lhs, uint64_t m, float* dst, float clamp, int* error_flag,
-                                   cudaStream_t s);
+                                   cudaStream_t s, const float* norm_w = nullptr, float eps = 0.0f);
+// dst = residual + rmsnorm(lhs; norm_w, eps) . W^T in one launch (norm_w, residual optional; residual may be
+// dst).  Valid when gemv_mma_fusable(m, k).
+bool gemv_mma_fusable(uint64_t m, uint64_t k);
+cudaError_t launch_gemv_mma_fused(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs,
+                                  uint64_t m, float* dst, const float* norm_w, float eps, const float* residual,
+                                  int* error_flag, cudaStream_t s);
 // Allocation-free variant: planes in a fixed array inside the library image (see gemv_mma.cu).
 constexpr size_t GEMV_STATIC_SCRATCH_BYTES = 4u << 20;
 size_t gemv_mma_static_bytes_needed(uint64_t m, uint64_t k);
@@ -128,7 +135,7 @@ cudaError_t launch_moe_jobs(const uint32_t* ids, uint32_t T, uint32_t K, uint32_
                             uint32_t* list_token, uint32_t* inv, MoeJob* jobs, uint32_t* n_jobs, uint32_t* n_list,
                             int* bad_id, cudaStream_t s);
 cudaError_t launch_moe_combine(const float* out, const uint32_t* inv, const float* wts, const float* shared, uint32_t T,
-                               uint32_t K, uint32_t h, float* y, cudaStream_t s);
+                               uint32_t K, uint32_t h, float* y, cudaStream_t s, const float* residual = nullptr);
 cudaError_t launch_swiglu(const float* g, const float* u, uint64_t n, float clamp, float* out, cudaStream_t s);
 
 // decoder.cu: the element-wise and attention steps around the matmuls of a decode step
@@ -137,6 +144,11 @@ cudaError_t launch_rmsnorm(const float* x, const float* res, const float* w, flo
 cudaError_t launch_rope_append(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
                                uint32_t hd, uint32_t max_ctx, float theta, float* q_out, float* cache_k, float* cache_v,
                                cudaStream_t s);
+// rope + cache append + attention + merge in one launch, from the fused qkv row (decoder.cu)
+size_t attention_fused_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx);
+cudaError_t launch_attention_fused(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
+                                   uint32_t hd, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,
+                                   float* out, void* scratch, cudaStream_t s);
 // scratch: attention_scratch_bytes(...) bytes of per-chunk partial results
 size_t attention_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t hd, uint32_t max_ctx);
 cudaError_t launch_attention_decode(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,

@@ -34,6 +34,79 @@ int32_t jq_matmul_swiglu_dev(const jq_weight* gate, const jq_weight* up, uint64_
     return jq::OK;
 }
 
+int32_t jq_matmul_swiglu_norm_dev(const jq_weight* gate, const jq_weight* up, uint64_t m, uint64_t k, uint64_t n,
+                                  const float* lhs_dev, const float* norm_w_dev, float eps, float* dst_dev,
+                                  float clamp, void* stream) {
+    if (!norm_w_dev) return jq_matmul_swiglu_dev(gate, up, m, k, n, lhs_dev, dst_dev, clamp, stream);
+    if (!gate || !up) return jq_fail(jq::E_INVALID, "jq_matmul_swiglu_norm_dev: NULL weight handle");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    jq_ctx* ctx = gate->ctx;
+    const bool shapes_ok = gate->type == up->type && gate->n_blocks == up->n_blocks && k % gate->fmt.elems == 0 &&
+                           gate->n_blocks == n * (k / gate->fmt.elems) && m > 0 && n > 0 && lhs_dev && dst_dev;
+    if (shapes_ok && !ctx->force_f32 && jq::gemv_mma_supports(gate->type, gate->dev, n, k, m) &&
+        jq::gemv_mma_supports(up->type, up->dev, n, k, m) && jq::gemv_mma_fusable(m, k)) {
+        JQ_CUDA(jq::launch_gemv_mma_swiglu(gate->type, gate->dev, up->dev, n, k, lhs_dev, m, dst_dev, clamp,
+                                           ctx->status_dev, s, norm_w_dev, eps));
+        return jq::OK;
+    }
+    // separate kernels: normalise into scratch, then the plain entry (which validates)
+    void* scratch = nullptr;
+    JQ_CUDA(ctx->scratch_for(reinterpret_cast<cudaStream_t>(reinterpret_cast<uintptr_t>(s) ^ 2), m * k * 4 + 256, &scratch));
+    JQ_CUDA(jq::launch_rmsnorm(lhs_dev, nullptr, norm_w_dev, eps, m, (uint32_t)k, nullptr, static_cast<float*>(scratch), s));
+    return jq_matmul_swiglu_dev(gate, up, m, k, n, static_cast<const float*>(scratch), dst_dev, clamp, stream);
+}
+
+int32_t jq_matmul_norm_dev(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n, const float* lhs_dev,
+                           const float* norm_w_dev, float eps, const float* residual_dev, float* dst_dev,
+                           void* stream) {
+    if (!w) return jq_fail(jq::E_INVALID, "jq_matmul_norm_dev: NULL weight handle");
+    if (!norm_w_dev && !residual_dev) return jq_matmul_t_dev(w, m, k, n, lhs_dev, dst_dev, stream);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    jq_ctx* ctx = w->ctx;
+    const bool shapes_ok = k % w->fmt.elems == 0 && w->n_blocks == n * (k / w->fmt.elems) && m > 0 && n > 0 &&
+                           lhs_dev && dst_dev;
+    if (shapes_ok && !ctx->force_f32 && jq::gemv_mma_supports(w->type, w->dev, n, k, m) && jq::gemv_mma_fusable(m, k)) {
+        JQ_CUDA(jq::launch_gemv_mma_fused(w->type, w->dev, n, k, lhs_dev, m, dst_dev, norm_w_dev, eps, residual_dev,
+                                          ctx->status_dev, s));
+        return jq::OK;
+    }
+    // separate kernels: norm into scratch, product into scratch, then the add
+    if (m == 0 || n == 0) return jq_matmul_t_dev(w, m, k, n, lhs_dev, dst_dev, stream);
+    void* scratch = nullptr;
+    const uint64_t xk = (m * k + 63) & ~(uint64_t)63;
+    JQ_CUDA(ctx->scratch_for(reinterpret_cast<cudaStream_t>(reinterpret_cast<uintptr_t>(s) ^ 2), (xk + m * n) * 4 + 256, &scratch));
+    float* xn = static_cast<float*>(scratch);
+    float* prod = xn + xk;
+    const float* in = lhs_dev;
+    if (norm_w_dev) {
+        if (!lhs_dev) return jq_fail(jq::E_INVALID, "jq_matmul_norm_dev: NULL buffer");
+        JQ_CUDA(jq::launch_rmsnorm(lhs_dev, nullptr, norm_w_dev, eps, m, (uint32_t)k, nullptr, xn, s));
+        in = xn;
+    }
+    if (!residual_dev) return jq_matmul_t_dev(w, m, k, n, in, dst_dev, stream);
+    if (int32_t rc = jq_matmul_t_dev(w, m, k, n, in, prod, stream)) return rc;
+    JQ_CUDA(jq::launch_add(residual_dev, prod, m * n, dst_dev, s));
+    return jq::OK;
+}
+
+uint64_t jq_attention_fused_scratch_bytes(uint32_t batch, uint32_t n_q, uint32_t n_kv, uint32_t head_dim,
+                                          uint32_t max_ctx) {
+    return jq::attention_fused_scratch_bytes(batch, n_q, n_kv, head_dim, max_ctx);
+}
+
+int32_t jq_attention_fused_dev(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t n_q, uint32_t n_kv,
+                               uint32_t head_dim, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,
+                               float* out, void* scratch, void* stream) {
+    if (batch == 0) return jq::OK;
+    if (!qkv || !pos || !cache_k || !cache_v || !out || !scratch)
+        return jq_fail(jq::E_INVALID, "jq_attention_fused_dev: NULL buffer");
+    if (n_kv == 0 || n_q % n_kv || n_q / n_kv > 8 || head_dim == 0 || head_dim > 256 || head_dim % 2)
+        return jq_fail(jq::E_INVALID, "jq_attention_fused_dev: need n_q a multiple of n_kv (at most 8 per kv head) and an even head_dim <= 256");
+    JQ_CUDA(jq::launch_attention_fused(qkv, pos, batch, n_q, n_kv, head_dim, max_ctx, theta, cache_k, cache_v, out,
+                                       scratch, static_cast<cudaStream_t>(stream)));
+    return jq::OK;
+}
+
 int32_t jq_embedding_dev(const jq_weight* w, const uint32_t* ids_dev, uint64_t n_ids, uint64_t rows, uint64_t hidden,
                          float* out_dev, int32_t* bad_id_dev, void* stream) {
     if (!w) return jq_fail(jq::E_INVALID, "jq_embedding_dev: NULL weight handle");

@@ -173,8 +173,8 @@ __global__ void __launch_bounds__(256) ep_return_kernel(Window win, Layout l, ui
 __global__ void __launch_bounds__(256) ep_combine_kernel(const uint8_t* __restrict__ my_window, Layout l,
                                                          const uint32_t* __restrict__ pair_slot,
                                                          const float* __restrict__ wts, uint32_t T, uint32_t K,
-                                                         const uint32_t* __restrict__ epoch, float* __restrict__ y,
-                                                         int* status) {
+                                                         const uint32_t* __restrict__ epoch, const float* residual,
+                                                         float* y, int* status) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x < l.world)
@@ -197,6 +197,10 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const uint8_t* __restri
             acc.y += v.y * w;
             acc.z += v.z * w;
             acc.w += v.w * w;
+        }
+        if (residual) {
+            const float4 v = *reinterpret_cast<const float4*>(residual + (uint64_t)t * l.hidden + 4 * c);
+            acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
         }
         *reinterpret_cast<float4*>(y + (uint64_t)t * l.hidden + 4 * c) = acc;
     }
@@ -298,8 +302,8 @@ int32_t jq_ep_connect(jq_ep* e, const uint8_t* handles) {
     return jq::OK;
 }
 
-int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float* x_dev, uint64_t T, float* y_dev,
-                          void* stream) {
+int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float* x_dev, uint64_t T,
+                          const float* residual_dev, float* y_dev, void* stream) {
     if (!e || !router || !experts) return jq_fail(jq::E_INVALID, "jq_ep_forward_dev: NULL handle");
     if (!e->connected) return jq_fail(jq::E_INVALID, "jq_ep_forward_dev: call jq_ep_connect first");
     if (!x_dev || !y_dev) return jq_fail(jq::E_INVALID, "jq_ep_forward_dev: NULL buffer");
@@ -330,7 +334,7 @@ int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float
     const unsigned cblocks = (unsigned)std::min<uint64_t>(((uint64_t)T * (e->hidden / 4) + 255) / 256, 148 * 4);
     JQ_CUDA(jq::launch_pdl(ep_combine_kernel, dim3(cblocks), 256, 0, s, (const uint8_t*)mine, e->lay,
                            (const uint32_t*)e->pair_slot, (const float*)e->wts, (uint32_t)T, e->n_used,
-                           (const uint32_t*)e->epoch, y_dev, e->ctx->status_dev));
+                           (const uint32_t*)e->epoch, residual_dev, y_dev, e->ctx->status_dev));
     return jq::OK;
 }
 

@@ -156,11 +156,19 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 
 // Warp-wide variant for use inside the matmul kernel: lane l holds values 8l .. 8l+7 of the unit (group
 // l / 4).  `planes` points at the unit's first group (8 x 96 bytes), `meta` / `sum16` at its first entries.
+// With `nw` (the unit's 256 RMS-norm weights) the values split are x * rs * nw, i.e. the normalised row.
 __device__ __forceinline__ void quantize_unit_warp(const float* __restrict__ xu, uint32_t lane, uint32_t type,
-                                                   int8_t* planes, float2* meta, float* sum16) {
+                                                   int8_t* planes, float2* meta, float* sum16,
+                                                   const float* __restrict__ nw = nullptr, float rs = 1.0f) {
     const float4* src = reinterpret_cast<const float4*>(xu + lane * 8);
     float4 lo4 = __ldg(src), hi4 = __ldg(src + 1);
     float v[8] = {lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
+    if (nw) {
+        const float4* wsrc = reinterpret_cast<const float4*>(nw + lane * 8);
+        float4 w0 = __ldg(wsrc), w1 = __ldg(wsrc + 1);
+        v[0] = v[0] * rs * w0.x, v[1] = v[1] * rs * w0.y, v[2] = v[2] * rs * w0.z, v[3] = v[3] * rs * w0.w;
+        v[4] = v[4] * rs * w1.x, v[5] = v[5] * rs * w1.y, v[6] = v[6] * rs * w1.z, v[7] = v[7] * rs * w1.w;
+    }
     float amax = 0.0f, sum = 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -704,6 +712,9 @@ struct GemvArgs {
     const uint32_t* act_rows;   // grouped: activation row of each list position (NULL = the position itself)
     float clamp;                // SwiGLU clamp (0 = off)
     int swiglu;                 // 1: tiles come in (gate, up) pairs and dst = silu(g) * u
+    const float* norm_w;        // ACT == 1, dense: RMS-normalise every row of x with these k weights first
+    float norm_eps;
+    const float* residual;      // dense: dst = residual + product (may alias dst)
     SmemPlan plan;
     int* error_flag;
 };
@@ -776,8 +787,38 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1) gemv_mma_kernel(const __gri
         int8_t* planes = reinterpret_cast<int8_t*>(s_act);
         float2* meta = reinterpret_cast<float2*>(s_act + groups * 96);
         float* sum16 = reinterpret_cast<float*>(s_act + groups * 104);
-        for (uint64_t u = warp - 1; u < groups / 8; u += NCW + 1)
-            quantize_unit_warp(ga.x + u * 256, lane, TYPE, planes + u * 768, meta + u * 8, sum16 + u * 16);
+        if (ga.norm_w != nullptr) {
+            // RMS norm fused in: 1 / rms of every row first (fixed summation order: lane-strided, warp
+            // shuffle tree, then the warps' partial sums in warp order), then the split sees x * rs * w
+            __shared__ float s_part[NCW + 1][GEMV_MMA_MAX_M];
+            __shared__ float s_rs[GEMV_MMA_MAX_M];
+            for (uint32_t r = 0; r < ga.x_rows; ++r) {
+                const float4* xr = reinterpret_cast<const float4*>(ga.x + (uint64_t)r * k);
+                float ss = 0.0f;
+                for (uint32_t i = (warp - 1) * 32 + lane; i < k / 4; i += (NCW + 1) * 32) {
+                    float4 v = __ldg(xr + i);
+                    ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+                if (lane == 0) s_part[warp - 1][r] = ss;
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"((NCW + 1) * 32) : "memory");
+            if (warp == 1 && lane < ga.x_rows) {
+                float tot = 0.0f;
+                for (int w = 0; w < NCW + 1; ++w) tot += s_part[w][lane];
+                s_rs[lane] = rsqrtf(tot / (float)k + ga.norm_eps);
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"((NCW + 1) * 32) : "memory");
+            for (uint64_t u = warp - 1; u < groups / 8; u += NCW + 1) {
+                const uint32_t r = (uint32_t)(u / units_per_row), uc = (uint32_t)(u % units_per_row);
+                quantize_unit_warp(ga.x + u * 256, lane, TYPE, planes + u * 768, meta + u * 8, sum16 + u * 16,
+                                   ga.norm_w + uc * 256, s_rs[r]);
+            }
+        } else {
+            for (uint64_t u = warp - 1; u < groups / 8; u += NCW + 1)
+                quantize_unit_warp(ga.x + u * 256, lane, TYPE, planes + u * 768, meta + u * 8, sum16 + u * 16);
+        }
         asm volatile("bar.sync 1, %0;" ::"r"((NCW + 1) * 32) : "memory");
     }
     const uint32_t n_jobs = grouped ? __ldg(ga.n_jobs) : 1u;
@@ -942,7 +983,9 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1) gemv_mma_kernel(const __gri
                                 }
                                 v = silu_f(gv) * uv;
                             }
-                            ga.dst[(uint64_t)(jd.row0 + b) * n + row0 + r] = v;
+                            const uint64_t o_idx = (uint64_t)(jd.row0 + b) * n + row0 + r;
+                            if (GROUPED != 2 && ga.residual != nullptr) v += ga.residual[o_idx];
+                            ga.dst[o_idx] = v;
                         }
                     }
                 }
@@ -1073,6 +1116,28 @@ cudaError_t launch_quantize_acts(uint32_t type, const float* x, uint64_t rows, u
                       const_cast<float2*>(act.meta), const_cast<float*>(act.sum16));
 }
 
+bool gemv_mma_fusable(uint64_t m, uint64_t k) { return m <= GEMV_MMA_MAX_M && acts_fit_in_smem(m, k); }
+
+// dst = residual + rmsnorm(lhs; norm_w, eps) . W^T in one launch; norm_w and residual are optional.
+cudaError_t launch_gemv_mma_fused(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs,
+                                  uint64_t m, float* dst, const float* norm_w, float eps, const float* residual,
+                                  int* error_flag, cudaStream_t s) {
+    if (!gemv_mma_fusable(m, k)) return cudaErrorInvalidValue;
+    GemvArgs ga = {};
+    ga.w[0] = ga.w[1] = w;
+    ga.n = n;
+    ga.k = k;
+    ga.x = lhs;
+    ga.x_rows = (uint32_t)m;
+    ga.m = (uint32_t)m;
+    ga.dst = dst;
+    ga.norm_w = norm_w;
+    ga.norm_eps = eps;
+    ga.residual = residual;
+    ga.error_flag = error_flag;
+    return launch_typed<1, 0>(type, ga, (uint32_t)m, (n + ROWS - 1) / ROWS, s);
+}
+
 cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
                             float* dst, void* scratch, int* error_flag, cudaStream_t s) {
     GemvArgs ga = {};
@@ -1095,7 +1160,7 @@ cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_
 // silu(clamp(gate x)) * clamp(up x) in one launch (activation planes in shared memory only)
 cudaError_t launch_gemv_mma_swiglu(uint32_t type, const uint8_t* w_gate, const uint8_t* w_up, uint64_t n, uint64_t k,
                                    const float* lhs, uint64_t m, float* dst, float clamp, int* error_flag,
-                                   cudaStream_t s) {
+                                   cudaStream_t s, const float* norm_w, float eps) {
     if (!acts_fit_in_smem(m, k)) return cudaErrorInvalidValue;
     GemvArgs ga = {};
     ga.w[0] = w_gate;
@@ -1108,6 +1173,8 @@ cudaError_t launch_gemv_mma_swiglu(uint32_t type, const uint8_t* w_gate, const u
     ga.dst = dst;
     ga.clamp = clamp;
     ga.swiglu = 1;
+    ga.norm_w = norm_w;
+    ga.norm_eps = eps;
     ga.error_flag = error_flag;
     return launch_typed<1, 1>(type, ga, (uint32_t)m, (n + ROWS - 1) / ROWS, s);
 }

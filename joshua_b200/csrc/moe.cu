@@ -245,10 +245,12 @@ __global__ void __launch_bounds__(1024) moe_jobs_kernel(const uint32_t* __restri
     }
 }
 
-// y[t, :] = sum over slots (in slot order) of w[t, s] * out[inv[t*K + s], :]  (+ shared[t, :])
+// y[t, :] = sum over slots (in slot order) of w[t, s] * out[inv[t*K + s], :]  (+ shared[t, :]) (+ residual[t, :],
+// which may be y itself)
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ out, const uint32_t* __restrict__ inv,
                                                           const float* __restrict__ wts, const float* __restrict__ shared,
-                                                          uint32_t T, uint32_t K, uint32_t h, float* __restrict__ y) {
+                                                          const float* residual, uint32_t T, uint32_t K, uint32_t h,
+                                                          float* y) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint64_t total = (uint64_t)T * (h / 4);
@@ -268,6 +270,13 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
         }
         if (shared) {
             float4 v = *reinterpret_cast<const float4*>(shared + (uint64_t)t * h + 4 * c);
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+        }
+        if (residual) {
+            float4 v = *reinterpret_cast<const float4*>(residual + (uint64_t)t * h + 4 * c);
             acc.x += v.x;
             acc.y += v.y;
             acc.z += v.z;
@@ -325,8 +334,8 @@ cudaError_t launch_moe_jobs(const uint32_t* ids, uint32_t T, uint32_t K, uint32_
 }
 
 cudaError_t launch_moe_combine(const float* out, const uint32_t* inv, const float* wts, const float* shared, uint32_t T,
-                               uint32_t K, uint32_t h, float* y, cudaStream_t s) {
-    cudaError_t le4__ = launch_pdl(moe_combine_kernel, blocks_for((uint64_t)T * (h / 4), 256), 256, 0, s, out, inv, wts, shared, T, K, h, y);
+                               uint32_t K, uint32_t h, float* y, cudaStream_t s, const float* residual) {
+    cudaError_t le4__ = launch_pdl(moe_combine_kernel, blocks_for((uint64_t)T * (h / 4), 256), 256, 0, s, out, inv, wts, shared, residual, T, K, h, y);
     if (le4__ != cudaSuccess) return le4__;
     return cudaGetLastError();
 }

@@ -302,6 +302,11 @@ int32_t jq_moe_experts_dev(jq_moe* m, const float* x_dev, uint64_t n_rows, const
 
 int32_t jq_moe_forward_dev(jq_moe* m, const float* x_dev, uint64_t T, const uint32_t* forced_ids_dev, float* y_dev,
                            void* stream) {
+    return jq_moe_forward_add_dev(m, x_dev, T, forced_ids_dev, nullptr, y_dev, stream);
+}
+
+int32_t jq_moe_forward_add_dev(jq_moe* m, const float* x_dev, uint64_t T, const uint32_t* forced_ids_dev,
+                               const float* residual_dev, float* y_dev, void* stream) {
     if (!m) return jq_fail(jq::E_INVALID, "jq_moe_forward_dev: NULL handle");
     if (T == 0) return jq::OK;
     if (!x_dev || !y_dev) return jq_fail(jq::E_INVALID, "jq_moe_forward_dev: NULL buffer");
@@ -321,7 +326,7 @@ int32_t jq_moe_forward_dev(jq_moe* m, const float* x_dev, uint64_t T, const uint
         if (int32_t rc = run_shared(m, x_dev, T, s)) return rc;
         shared = m->sh_out;
     }
-    JQ_CUDA(jq::launch_moe_combine(m->out, m->inv, m->wts, shared, (uint32_t)T, c.n_used, c.hidden, y_dev, s));
+    JQ_CUDA(jq::launch_moe_combine(m->out, m->inv, m->wts, shared, (uint32_t)T, c.n_used, c.hidden, y_dev, s, residual_dev));
     return jq::OK;
 }
 

@@ -218,12 +218,14 @@ class PeerExchange:
             _lib.check(_lib.lib().jq_ep_connect(self._h, blob))
             dist.barrier(group=group)                      # nobody stores into a window that is not mapped yet
 
-    def forward_dev(self, router_layer, expert_layer, x, y, stream=None) -> None:
+    def forward_dev(self, router_layer, expert_layer, x, y, residual=None, stream=None) -> None:
+        """y = (residual +) layer(x); `residual` may be `y`."""
         from . import _lib
 
         T = x.numel() // self.hidden
         s = torch.cuda.current_stream(x.device).cuda_stream if stream is None else stream
         _lib.check(_lib.lib().jq_ep_forward_dev(self._h, router_layer._h, expert_layer._h, x.data_ptr(), T,
+                                                residual.data_ptr() if residual is not None else None,
                                                 y.data_ptr(), s))
 
     def close(self) -> None:

@@ -89,40 +89,63 @@ class LlamaDecoder:
         self.logits = torch.empty(B, cfg.vocab, **f32)
         att_bytes = _lib.lib().jq_attention_scratch_bytes(B, cfg.q_heads, cfg.head_dim, max_ctx)
         self.att_scratch = torch.empty(att_bytes // 4 + 1, **f32)
+        fused_bytes = _lib.lib().jq_attention_fused_scratch_bytes(B, cfg.q_heads, cfg.kv_heads, cfg.head_dim, max_ctx)
+        self.att_fused_scratch = torch.zeros(fused_bytes // 4 + 1, **f32)   # holds arrival counters: starts at zero
         self.argmax_scratch = torch.empty(_lib.lib().jq_argmax_scratch_bytes(B) // 4 + 1, **f32)
-        self.launches_per_step = 9 * cfg.layers + 5
+        self.launches_per_step = 5 * cfg.layers + 4
         self.matmuls_per_step = 4 * cfg.layers + 1
 
     # ── one token ───────────────────────────────────────────────────────
     def step(self, stream=None) -> None:
         """Decode one token per sequence: reads self.token / self.pos, writes self.logits, the next
-        self.token and advances self.pos.  Launches only."""
+        self.token and advances self.pos.  Launches only.  Five launches per layer: the RMS norms ride in the
+        prologue of the matmul that consumes them, the residual adds in the epilogue of the matmul that
+        produces the branch, and rope + cache append + attention + merge are one kernel.  self.x is the
+        residual stream, updated in place."""
         L, c, B = _lib.lib(), self.cfg, self.batch
         s = self.torch.cuda.current_stream(self.dev).cuda_stream if stream is None else stream
         h, P = c.hidden, lambda t: t.data_ptr()
         check(L.jq_embedding_dev(self.embed._h, P(self.token), B, c.vocab, h, P(self.x), P(self.bad), s))
-        for i, ly in enumerate(self.layers):
-            if i == 0:
-                check(L.jq_rmsnorm_dev(P(self.x), None, P(ly["attn_norm"]), c.eps, B, h, None, P(self.xn), s))
-            else:  # x = x1 + d of the previous layer, fused with this layer's norm
-                check(L.jq_rmsnorm_dev(P(self.d), P(self.x1), P(ly["attn_norm"]), c.eps, B, h, P(self.x), P(self.xn), s))
+        for ly in self.layers:
+            check(L.jq_matmul_norm_dev(ly["wqkv"]._h, B, h, c.qkv_rows, P(self.x), P(ly["attn_norm"]), c.eps, None,
+                                       P(self.qkv), s))
+            check(L.jq_attention_fused_dev(P(self.qkv), P(self.pos), B, c.q_heads, c.kv_heads, c.head_dim,
+                                           self.max_ctx, c.rope_theta, P(ly["k"]), P(ly["v"]), P(self.attn),
+                                           P(self.att_fused_scratch), s))
+            check(L.jq_matmul_norm_dev(ly["wo"]._h, B, c.q_heads * c.head_dim, h, P(self.attn), None, 0.0, P(self.x),
+                                       P(self.x), s))
+            self._ffn(ly, s)
+        check(L.jq_matmul_norm_dev(self.output._h, B, h, c.vocab, P(self.x), P(self.out_norm), c.eps, None,
+                                   P(self.logits), s))
+        check(L.jq_argmax_dev(P(self.logits), B, c.vocab, P(self.token), P(self.pos), P(self.argmax_scratch), s))
+
+    def step_unfused(self, stream=None) -> None:
+        """The same step from the separate kernels (norm, rope, attention partial + merge as their own
+        launches); kept as the cross-check of the fused step."""
+        L, c, B = _lib.lib(), self.cfg, self.batch
+        s = self.torch.cuda.current_stream(self.dev).cuda_stream if stream is None else stream
+        h, P = c.hidden, lambda t: t.data_ptr()
+        check(L.jq_embedding_dev(self.embed._h, P(self.token), B, c.vocab, h, P(self.x), P(self.bad), s))
+        for ly in self.layers:
+            check(L.jq_rmsnorm_dev(P(self.x), None, P(ly["attn_norm"]), c.eps, B, h, None, P(self.xn), s))
             check(L.jq_matmul_t_dev(ly["wqkv"]._h, B, h, c.qkv_rows, P(self.xn), P(self.qkv), s))
             check(L.jq_rope_append_dev(P(self.qkv), P(self.pos), B, c.q_heads, c.kv_heads, c.head_dim, self.max_ctx,
                                        c.rope_theta, P(self.q), P(ly["k"]), P(ly["v"]), s))
             check(L.jq_attention_decode_dev(P(self.q), P(ly["k"]), P(ly["v"]), P(self.pos), B, c.q_heads, c.kv_heads,
                                             c.head_dim, self.max_ctx, P(self.attn), P(self.att_scratch), s))
             check(L.jq_matmul_t_dev(ly["wo"]._h, B, c.q_heads * c.head_dim, h, P(self.attn), P(self.o), s))
-            check(L.jq_rmsnorm_dev(P(self.o), P(self.x), P(ly["ffn_norm"]), c.eps, B, h, P(self.x1), P(self.xn), s))
+            check(L.jq_add_dev(P(self.x), P(self.o), B * h, P(self.x), s))
             self._ffn(ly, s)
-        check(L.jq_rmsnorm_dev(P(self.d), P(self.x1), P(self.out_norm), c.eps, B, h, P(self.x), P(self.xn), s))
+        check(L.jq_rmsnorm_dev(P(self.x), None, P(self.out_norm), c.eps, B, h, None, P(self.xn), s))
         check(L.jq_matmul_t_dev(self.output._h, B, h, c.vocab, P(self.xn), P(self.logits), s))
         check(L.jq_argmax_dev(P(self.logits), B, c.vocab, P(self.token), P(self.pos), P(self.argmax_scratch), s))
 
     def _ffn(self, ly, s) -> None:
-        """self.d = FFN(self.xn): the dense SwiGLU MLP."""
+        """self.x += FFN(rmsnorm(self.x; ffn_norm)): the dense SwiGLU MLP in two launches."""
         L, c, B, P = _lib.lib(), self.cfg, self.batch, lambda t: t.data_ptr()
-        check(L.jq_matmul_swiglu_dev(ly["w_gate"]._h, ly["w_up"]._h, B, c.hidden, c.ffn, P(self.xn), P(self.act), 0.0, s))
-        check(L.jq_matmul_t_dev(ly["w_down"]._h, B, c.ffn, c.hidden, P(self.act), P(self.d), s))
+        check(L.jq_matmul_swiglu_norm_dev(ly["w_gate"]._h, ly["w_up"]._h, B, c.hidden, c.ffn, P(self.x),
+                                          P(ly["ffn_norm"]), c.eps, P(self.act), 0.0, s))
+        check(L.jq_matmul_norm_dev(ly["w_down"]._h, B, c.ffn, c.hidden, P(self.act), None, 0.0, P(self.x), P(self.x), s))
 
     def matmuls_only(self, stream=None) -> None:
         """The quantized matmuls of one token back to back (the kernel-level roofline probe)."""

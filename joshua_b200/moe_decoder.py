@@ -81,16 +81,17 @@ class MoeDecoder(LlamaDecoder):
                 rl.reserve(batch, 0)
                 el.reserve(cap, cap)
                 self.ffn_layers.append(dict(router=rl, experts=el, keep=banks))
-        self.launches_per_step = (7 + (6 if self.world == 1 else 9)) * cfg.layers + 5
+        self.launches_per_step = (4 + (6 if self.world == 1 else 9)) * cfg.layers + 4
 
-    # the dense FFN weights of the parent are never used: build tiny ones
     def _ffn(self, ly, s) -> None:
-        i = self._layer_index[id(ly)]
-        f = self.ffn_layers[i]
+        """self.x += MoE(rmsnorm(self.x; ffn_norm)); the residual add rides in the combine kernel."""
+        L, c, B, P = _lib.lib(), self.cfg, self.batch, lambda t: t.data_ptr()
+        f = self.ffn_layers[self._layer_index[id(ly)]]
+        _lib.check(L.jq_rmsnorm_dev(P(self.x), None, P(ly["ffn_norm"]), c.eps, B, c.hidden, None, P(self.xn), s))
         if "moe" in f:
-            f["moe"].forward_dev(self.xn, self.d, stream=s)
+            _lib.check(L.jq_moe_forward_add_dev(f["moe"]._h, P(self.xn), B, None, P(self.x), P(self.x), s))
         else:
-            self.exchange.forward_dev(f["router"], f["experts"], self.xn, self.d, stream=s)
+            self.exchange.forward_dev(f["router"], f["experts"], self.xn, self.x, residual=self.x, stream=s)
 
     def step(self, stream=None) -> None:
         if not hasattr(self, "_layer_index"):

@@ -110,3 +110,71 @@ def test_argmax_last_index_wins_ties():
                                         scratch.data_ptr(), torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     assert tok.tolist() == [903, 999] and pos.tolist() == [4, 10]
+
+
+def _small_weights(wtype):
+    import torch
+
+    def small(name, n, k, s):
+        raw = synth.random_weight(wtype, n, k, s).reshape(-1, synth.BLOCK[wtype][1]).copy()
+        for off in synth._F16_FIELDS[wtype]:
+            sc = raw[:, off:off + 2].copy().view(np.float16).astype(np.float32) * 0.02
+            raw[:, off:off + 2] = sc.astype(np.float16).view(np.uint8).reshape(-1, 2)
+        return torch.from_numpy(raw.reshape(-1))
+
+    return small
+
+
+@pytest.mark.parametrize("batch", [1, 3])
+def test_fused_step_matches_separate_kernels(batch):
+    """The five-launch layer (norms and residuals inside the matmuls, one attention kernel) against the same
+    step from the separate kernels, over enough positions to span several attention chunks."""
+    import torch
+
+    cfg = LlamaConfig(layers=2, hidden=512, q_heads=8, kv_heads=2, head_dim=64, ffn=768, vocab=512)
+    mk = _small_weights(synth.Q4_K)
+    a = LlamaDecoder(cfg, torch.device("cuda", 0), batch=batch, max_ctx=80, seed=5, weights=mk)
+    b = LlamaDecoder(cfg, torch.device("cuda", 0), batch=batch, max_ctx=80, seed=5, weights=mk)
+    a.reset(7)
+    b.reset(7)
+    for step in range(70):
+        a.step()
+        b.step_unfused()
+        torch.cuda.synchronize()
+        la, lb = a.logits.cpu().numpy(), b.logits.cpu().numpy()
+        scale = max(1.0, float(np.abs(lb).max()))
+        assert float(np.abs(la - lb).max()) <= 2e-4 * scale, step
+        b.token.copy_(a.token)   # keep both on the same token stream whatever near-ties do
+    assert a.pos.tolist() == [70] * batch
+
+
+@pytest.mark.parametrize("nq,nkv,hd,ctx", [(8, 2, 64, 1), (8, 8, 128, 33), (32, 4, 128, 100), (16, 2, 256, 64)])
+def test_fused_attention_matches_rope_append_attention(nq, nkv, hd, ctx):
+    import torch
+
+    from joshua_b200 import _lib
+
+    L = _lib.lib()
+    B, max_ctx, theta = 2, 128, 10000.0
+    g = torch.Generator(device="cuda").manual_seed(ctx)
+    qkv = torch.randn(B, (nq + 2 * nkv) * hd, device="cuda", generator=g)
+    ck = torch.randn(B, nkv, max_ctx, hd, device="cuda", generator=g)
+    cv = torch.randn(B, nkv, max_ctx, hd, device="cuda", generator=g)
+    ck2, cv2 = ck.clone(), cv.clone()
+    pos = torch.tensor([ctx - 1, max(0, ctx - 2)], dtype=torch.int32, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    q = torch.empty(B, nq * hd, device="cuda")
+    want = torch.empty(B, nq * hd, device="cuda")
+    scratch = torch.empty(L.jq_attention_scratch_bytes(B, nq, hd, max_ctx) // 4 + 1, device="cuda")
+    _lib.check(L.jq_rope_append_dev(qkv.data_ptr(), pos.data_ptr(), B, nq, nkv, hd, max_ctx, theta, q.data_ptr(),
+                                    ck.data_ptr(), cv.data_ptr(), s))
+    _lib.check(L.jq_attention_decode_dev(q.data_ptr(), ck.data_ptr(), cv.data_ptr(), pos.data_ptr(), B, nq, nkv, hd,
+                                         max_ctx, want.data_ptr(), scratch.data_ptr(), s))
+    got = torch.empty(B, nq * hd, device="cuda")
+    fscratch = torch.zeros(L.jq_attention_fused_scratch_bytes(B, nq, nkv, hd, max_ctx) // 4 + 1, device="cuda")
+    for _ in range(2):   # twice: the arrival counters must come back to zero
+        _lib.check(L.jq_attention_fused_dev(qkv.data_ptr(), pos.data_ptr(), B, nq, nkv, hd, max_ctx, theta,
+                                            ck2.data_ptr(), cv2.data_ptr(), got.data_ptr(), fscratch.data_ptr(), s))
+    torch.cuda.synchronize()
+    assert torch.equal(ck, ck2) and torch.equal(cv, cv2)          # same appended rows, bit for bit
+    assert float((got - want).abs().max()) <= 2e-5 * max(1.0, float(want.abs().max()))
