@@ -217,7 +217,7 @@ int32_t jq_rope_append_dev(const float* qkv, const int32_t* pos, uint32_t batch,
  * row: out[b, head, :] as jq_rope_append_dev + jq_attention_decode_dev give it.
  * `scratch`: jq_attention_fused_scratch_bytes(...) bytes of caller device
  * memory, ZEROED once before the first call (it holds arrival counters that
- * the kernel leaves at zero).  n_q / n_kv <= 8, head_dim <= 256. */
+ * the kernel leaves at zero).  head_dim 64, 128 or 256; n_q / n_kv 1, 2, 4 or 8. */
 uint64_t jq_attention_fused_scratch_bytes(uint32_t batch, uint32_t n_q, uint32_t n_kv, uint32_t head_dim,
                                           uint32_t max_ctx);
 int32_t jq_attention_fused_dev(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t n_q, uint32_t n_kv,
@@ -316,6 +316,34 @@ int32_t jq_moe_status(jq_moe* m);
 
 /* ids and weights chosen by the last forward (host copies), for inspection. */
 int32_t jq_moe_last_routing(jq_moe* m, uint64_t n_tokens, uint32_t* ids, float* wts);
+
+/* ── A decode chain: many dependent steps in one launch ────────────────
+ * No counterpart in the reference (its steps are separate candle ops).  A
+ * chain is a fixed list of operations over fixed device buffers: quantized
+ * linears in the forms of jq_matmul_norm_dev / jq_matmul_swiglu_norm_dev (w_up
+ * non-NULL = the gate / up SwiGLU pair) and attention steps as
+ * jq_attention_fused_dev, run in order by one persistent kernel whose CTAs
+ * synchronise on a device counter between operations while the next
+ * operation's weights are already streaming in.  All linears share the block
+ * type given at creation (Q4_K or Q8_0) and the batch m (1..8).  The first
+ * jq_chain_run uploads the list (it allocates: run once before capturing a
+ * stream); after it the chain cannot grow.  The kernel needs every SM of the
+ * device for itself (cooperative launch).  Results are those of the separate
+ * entries, operation by operation. */
+typedef struct jq_chain jq_chain;
+int32_t jq_chain_create(jq_ctx* ctx, uint32_t type, uint32_t m, jq_chain** out);
+void jq_chain_free(jq_chain* c);
+int32_t jq_chain_add_linear(jq_chain* c, const jq_weight* w, const jq_weight* w_up, uint64_t k, uint64_t n,
+                            const float* x_dev, const float* norm_w_dev, float eps, const float* residual_dev,
+                            float clamp, float* dst_dev);
+int32_t jq_chain_add_attention(jq_chain* c, const float* qkv, const int32_t* pos, uint32_t n_q, uint32_t n_kv,
+                               uint32_t head_dim, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,
+                               float* out, void* scratch);
+int32_t jq_chain_run(jq_chain* c, void* stream);
+/* Profiling aid: with a device buffer of 3 * (number of operations) uint64, CTA 0 of later runs stores the
+ * GPU nanosecond timer when it enters each operation, when its activations are split, and after its last
+ * store.  NULL switches it off. */
+int32_t jq_chain_set_trace(jq_chain* c, uint64_t* trace_dev);
 
 /* ── Expert-parallel exchange: one process per GPU, experts split contiguously over the ranks ──
  * No counterpart in the reference, which runs every expert of a layer in one

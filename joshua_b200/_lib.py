@@ -67,6 +67,12 @@ _SIGNATURES = {
     "jq_moe_experts_dev": (i32, [vp, vp, u64, vp, vp, vp]),
     "jq_moe_status": (i32, [vp]),
     "jq_moe_last_routing": (i32, [vp, u64, vp, vp]),
+    "jq_chain_create": (i32, [vp, u32, u32, ctypes.POINTER(vp)]),
+    "jq_chain_free": (None, [vp]),
+    "jq_chain_add_linear": (i32, [vp, vp, vp, u64, u64, vp, vp, f32, vp, f32, vp]),
+    "jq_chain_add_attention": (i32, [vp, vp, vp, u32, u32, u32, u32, f32, vp, vp, vp, vp]),
+    "jq_chain_run": (i32, [vp, vp]),
+    "jq_chain_set_trace": (i32, [vp, vp]),
     "jq_ep_create": (i32, [vp, u32, u32, u32, u32, u32, u32, ctypes.POINTER(vp)]),
     "jq_ep_free": (None, [vp]),
     "jq_ep_export": (i32, [vp, vp]),

@@ -59,7 +59,8 @@ def run(args):
                 fn()
         return g
 
-    step_graph = capture(model.step)
+    use_chain = bool(getattr(args, 'chain', False))
+    step_graph = capture(model.step_chain if use_chain else model.step)
     mm_graph = capture(model.matmuls_only)
     with torch.cuda.stream(stream):
         model.reset(42)
@@ -137,7 +138,8 @@ def run(args):
                        "q_heads": c.q_heads, "kv_heads": c.kv_heads, "head_dim": c.head_dim, "ffn": c.ffn,
                        "vocab": c.vocab, "batch": batch, "prefill": args.prefill,
                        "step": "full decode step on the device (embedding, norms, RoPE, attention over the KV cache, "
-                               "quantized matmuls, greedy arg-max), one CUDA graph",
+                               "quantized matmuls, greedy arg-max), one CUDA graph; "
+                               + ("layers + head in one persistent chain launch" if use_chain else "five launches per layer"),
                        "l2": "4.22 GB of weights per step, far larger than L2", "parallelism": f"replicas x{world}"},
             "e2e": {"value": batch / e2e_dt, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "how": "every matmul of the token through jq_matmul_t with host buffers; layer 0 + head timed, "
@@ -146,7 +148,7 @@ def run(args):
                          "traffic": None, "peak_source": which, "kernel": "gemv_mma_kernel<Q4_K>",
                          "launches_per_step": launches, "avg_launch_us": dt_mm / launches * 1e6,
                          "bytes_per_step": alg},
-            "gpu_launches": model.launches_per_step * args.steps, "clocks": clocks.summary(),
+            "gpu_launches": (4 if use_chain else model.launches_per_step) * args.steps, "clocks": clocks.summary(),
         }
         try:
             base = cpu_llama_sample(seconds_budget=12.0)

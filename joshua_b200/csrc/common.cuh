@@ -145,6 +145,10 @@ cudaError_t launch_rope_append(const float* qkv, const int32_t* pos, uint32_t ba
                                uint32_t hd, uint32_t max_ctx, float theta, float* q_out, float* cache_k, float* cache_v,
                                cudaStream_t s);
 // rope + cache append + attention + merge in one launch, from the fused qkv row (decoder.cu)
+struct AttnArgs;
+bool attention_fused_args(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd,
+                          uint32_t max_ctx, float theta, float* cache_k, float* cache_v, float* out, void* scratch,
+                          AttnArgs* a);
 size_t attention_fused_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx);
 cudaError_t launch_attention_fused(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
                                    uint32_t hd, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,

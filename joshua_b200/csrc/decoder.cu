@@ -7,6 +7,7 @@
 // greedy arg-max with the last maximal index winning ties, src/engine.rs:2371-2378).  All f32.
 #include <algorithm>
 
+#include "attention_fused.cuh"
 #include "common.cuh"
 
 namespace jq {
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const float* __restric
         float* dst = head < nq ? q_out + ((uint64_t)b * nq + head) * hd
                                : cache_k + (((uint64_t)b * nkv + (head - nq)) * max_ctx + p) * hd;
         for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
-            float freq = powf(theta, -2.0f * (float)i / (float)hd);
+            float freq = rope_freq(theta, i, hd);
             float s, c;
             sincosf((float)p * freq, &s, &c);
             float a = src[i], bb = src[i + half];
@@ -213,194 +214,14 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const float* __res
     }
 }
 
-// The same attention in ONE launch, straight from the fused qkv row: rotary embedding of q and of the new k,
-// append of k / v to the cache, the chunk partials and their merge.  One CTA per (chunk of ATT_FUSED_CHUNK
-// positions, kv head, sequence) serves all nq / nkv query heads of its kv head, so a K or V row is read once
-// per group.  The CTA that holds the newest position ropes k, stores k and v into the cache and uses them
-// from shared memory.  Each CTA writes its partials, then counts itself in; the last one of a (sequence, kv
-// head) merges the chunks in chunk order and resets the counter.
-constexpr uint32_t ATT_FUSED_CHUNK = 32;
-constexpr uint32_t ATT_FUSED_THREADS = 256;
-constexpr uint32_t ATT_MAX_GROUP = 8;   // query heads per kv head
-constexpr uint32_t ATT_MAX_HD = 256;
-
-__global__ void __launch_bounds__(ATT_FUSED_THREADS) attention_fused_kernel(
-    const float* __restrict__ qkv, const int32_t* __restrict__ pos, uint32_t nq, uint32_t nkv, uint32_t hd,
-    uint32_t max_ctx, float theta, uint32_t n_chunks, float* __restrict__ cache_k, float* __restrict__ cache_v,
-    float* __restrict__ part, uint32_t* __restrict__ counters, float* __restrict__ out) {
-    // q [G][hd] | new k [hd] | new v [hd] | scores [G][CHUNK] | max [G] | sum [G] | V partial sums [PG][G][hd]
+// The same attention in ONE launch, straight from the fused qkv row (attention_fused.cuh): one CTA per
+// (chunk, kv head, sequence).
+__global__ void __launch_bounds__(ATT_FUSED_THREADS) attention_fused_kernel(AttnArgs a) {
     extern __shared__ float s_f[];
     __shared__ uint32_t s_last;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     pdl_wait_();
-    const uint32_t chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, G = nq / nkv;
-    const uint32_t p = (uint32_t)pos[b], n_ctx = p + 1;
-    const uint32_t active = (n_ctx + ATT_FUSED_CHUNK - 1) / ATT_FUSED_CHUNK;
-    if (chunk >= active) return;
-    const uint32_t t0 = chunk * ATT_FUSED_CHUNK, cnt = min(ATT_FUSED_CHUNK, n_ctx - t0);
-    const bool newest = chunk == active - 1;  // this chunk holds position p
-    const uint32_t PG = max(1u, ATT_FUSED_THREADS / hd);  // position groups of the V pass
-    float* sq = s_f;
-    float* sk = sq + G * hd;
-    float* sv = sk + hd;
-    float* sc = sv + hd;
-    float* smx = sc + G * ATT_FUSED_CHUNK;
-    float* ssum = smx + G;
-    float* spv = ssum + G;
-    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, half = hd / 2;
-    constexpr uint32_t NW = ATT_FUSED_THREADS / 32;
-    const float* row = qkv + (uint64_t)b * (nq + 2 * nkv) * hd;
-    // rotate-half rotary embedding at position p of the group's q heads (and of the new k)
-    const uint32_t n_rot = (G + (newest ? 1u : 0u)) * half;
-    for (uint32_t idx = tid; idx < n_rot; idx += ATT_FUSED_THREADS) {
-        const uint32_t g = idx / half, i = idx - g * half;
-        const float* src = g < G ? row + (uint64_t)(kvh * G + g) * hd : row + (uint64_t)(nq + kvh) * hd;
-        float* dst = g < G ? sq + g * hd : sk;
-        float freq = powf(theta, -2.0f * (float)i / (float)hd);
-        float sn, cs;
-        sincosf((float)p * freq, &sn, &cs);
-        float a = src[i], bb = src[i + half];
-        dst[i] = a * cs - bb * sn;
-        dst[i + half] = a * sn + bb * cs;
-    }
-    if (newest)
-        for (uint32_t i = tid; i < hd; i += ATT_FUSED_THREADS) sv[i] = row[(uint64_t)(nq + nkv + kvh) * hd + i];
-    __syncthreads();
-    float* Kc = cache_k + (((uint64_t)b * nkv + kvh) * max_ctx) * hd;
-    float* Vc = cache_v + (((uint64_t)b * nkv + kvh) * max_ctx) * hd;
-    if (newest)
-        for (uint32_t i = tid; i < hd; i += ATT_FUSED_THREADS) {
-            Kc[(uint64_t)p * hd + i] = sk[i];
-            Vc[(uint64_t)p * hd + i] = sv[i];
-        }
-    // scores: a warp takes positions warp, warp + 8, ...; all its K rows are requested before any is used
-    const float scale = rsqrtf((float)hd);
-    {
-        constexpr uint32_t PER_WARP = ATT_FUSED_CHUNK / NW;  // 4
-        float kreg[PER_WARP][ATT_MAX_HD / 32];
-#pragma unroll
-        for (uint32_t u = 0; u < PER_WARP; ++u) {
-            const uint32_t t = warp + u * NW;
-            const float* kr = (t0 + t == p) ? sk : Kc + (uint64_t)(t0 + t) * hd;
-#pragma unroll
-            for (uint32_t j = 0; j < ATT_MAX_HD / 32; ++j)
-                kreg[u][j] = (t < cnt && lane + 32 * j < hd) ? kr[lane + 32 * j] : 0.0f;
-        }
-#pragma unroll
-        for (uint32_t u = 0; u < PER_WARP; ++u) {
-            const uint32_t t = warp + u * NW;
-            if (t < cnt) {
-                for (uint32_t g = 0; g < G; ++g) {
-                    float acc = 0.0f;
-#pragma unroll
-                    for (uint32_t j = 0; j < ATT_MAX_HD / 32; ++j)
-                        if (lane + 32 * j < hd) acc = fmaf(sq[g * hd + lane + 32 * j], kreg[u][j], acc);
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-                    if (lane == 0) sc[g * ATT_FUSED_CHUNK + t] = acc * scale;
-                }
-            }
-        }
-    }
-    __syncthreads();
-    // per head: maximum, exponentials, their sum (one warp per head, lane = position)
-    for (uint32_t g = warp; g < G; g += NW) {
-        float v = lane < cnt ? sc[g * ATT_FUSED_CHUNK + lane] : -INFINITY;
-        float mx = v;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-        float e = lane < cnt ? expf(v - mx) : 0.0f;
-        sc[g * ATT_FUSED_CHUNK + lane] = e;
-        float sum = e;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
-        if (lane == 0) {
-            smx[g] = mx;
-            ssum[g] = sum;
-        }
-    }
-    __syncthreads();
-    // weighted V sum: thread = (position group, output dimension); a V element is read once for the group
-    if (tid < PG * hd) {
-        const uint32_t pg = tid / hd, i = tid - pg * hd;
-        float acc[ATT_MAX_GROUP];
-#pragma unroll
-        for (uint32_t g = 0; g < ATT_MAX_GROUP; ++g) acc[g] = 0.0f;
-        constexpr uint32_t UN = 8;
-        for (uint32_t tb = pg; tb < cnt; tb += PG * UN) {
-            float vreg[UN];
-#pragma unroll
-            for (uint32_t u = 0; u < UN; ++u) {
-                const uint32_t t = tb + u * PG;
-                vreg[u] = t < cnt ? ((t0 + t == p) ? sv[i] : Vc[(uint64_t)(t0 + t) * hd + i]) : 0.0f;
-            }
-#pragma unroll
-            for (uint32_t u = 0; u < UN; ++u) {
-                const uint32_t t = min(tb + u * PG, ATT_FUSED_CHUNK - 1);  // padding rows carry v = 0
-#pragma unroll
-                for (uint32_t g = 0; g < ATT_MAX_GROUP; ++g)
-                    if (g < G) acc[g] = fmaf(sc[g * ATT_FUSED_CHUNK + t], vreg[u], acc[g]);
-            }
-        }
-#pragma unroll
-        for (uint32_t g = 0; g < ATT_MAX_GROUP; ++g)
-            if (g < G) spv[(pg * G + g) * hd + i] = acc[g];
-    }
-    __syncthreads();
-    for (uint32_t idx = tid; idx < G * hd; idx += ATT_FUSED_THREADS) {
-        const uint32_t g = idx / hd, i = idx - g * hd;
-        float v = 0.0f;
-        for (uint32_t pg = 0; pg < PG; ++pg) v += spv[(pg * G + g) * hd + i];  // fixed order
-        part[(((uint64_t)b * nq + kvh * G + g) * n_chunks + chunk) * (hd + 2) + i] = v;
-    }
-    if (tid < G) {
-        float* dst = part + (((uint64_t)b * nq + kvh * G + tid) * n_chunks + chunk) * (hd + 2);
-        dst[hd] = smx[tid];
-        dst[hd + 1] = ssum[tid];
-    }
-    // count in; the last CTA of this (sequence, kv head) merges
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const uint32_t old = atomicAdd(&counters[b * nkv + kvh], 1u);
-        s_last = old == active - 1 ? 1u : 0u;
-        if (s_last) counters[b * nkv + kvh] = 0;
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    // merge: a warp per query head; chunk c's statistics sit in lane c % 32 (round c / 32)
-    for (uint32_t g = warp; g < G; g += NW) {
-        const float* src = part + (((uint64_t)b * nq + kvh * G + g) * n_chunks) * (hd + 2);
-        float mx = -INFINITY;
-        for (uint32_t c = lane; c < active; c += 32) mx = fmaxf(mx, __ldcg(src + (uint64_t)c * (hd + 2) + hd));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-        float acc[ATT_MAX_HD / 32];
-#pragma unroll
-        for (uint32_t j = 0; j < ATT_MAX_HD / 32; ++j) acc[j] = 0.0f;
-        float den = 0.0f;
-        for (uint32_t c0 = 0; c0 < active; c0 += 32) {
-            const uint32_t c = c0 + lane;
-            float e = 0.0f, sm = 0.0f;
-            if (c < active) {
-                e = expf(__ldcg(src + (uint64_t)c * (hd + 2) + hd) - mx);
-                sm = __ldcg(src + (uint64_t)c * (hd + 2) + hd + 1);
-            }
-            const uint32_t lim = min(32u, active - c0);
-            for (uint32_t cc = 0; cc < lim; ++cc) {   // chunk order: fixed summation order
-                const float ec = __shfl_sync(0xFFFFFFFFu, e, cc), sc_ = __shfl_sync(0xFFFFFFFFu, sm, cc);
-                den = fmaf(ec, sc_, den);
-                const float* pr = src + (uint64_t)(c0 + cc) * (hd + 2);
-#pragma unroll
-                for (uint32_t j = 0; j < ATT_MAX_HD / 32; ++j)
-                    if (lane + 32 * j < hd) acc[j] = fmaf(ec, __ldcg(pr + lane + 32 * j), acc[j]);
-            }
-        }
-#pragma unroll
-        for (uint32_t j = 0; j < ATT_MAX_HD / 32; ++j)
-            if (lane + 32 * j < hd) out[((uint64_t)b * nq + kvh * G + g) * hd + lane + 32 * j] = acc[j] / den;
-    }
+    attention_fused_item<0>(a, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x, s_f, &s_last);
 }
 
 // y = a + b
@@ -535,17 +356,25 @@ size_t attention_fused_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t nkv, 
 cudaError_t launch_attention_fused(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
                                    uint32_t hd, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,
                                    float* out, void* scratch, cudaStream_t s) {
-    if (nkv == 0 || nq % nkv || nq / nkv > ATT_MAX_GROUP || hd > ATT_MAX_HD || hd % 2) return cudaErrorInvalidValue;
-    uint32_t n_chunks = (max_ctx + ATT_FUSED_CHUNK - 1) / ATT_FUSED_CHUNK;
-    uint32_t G = nq / nkv;
-    float* part = static_cast<float*>(scratch);
-    uint32_t* counters = reinterpret_cast<uint32_t*>(part + (size_t)batch * nq * n_chunks * (hd + 2));
-    uint32_t PG = std::max(1u, ATT_FUSED_THREADS / hd);
-    size_t smem = (size_t)(G * hd + 2 * hd + G * ATT_FUSED_CHUNK + 2 * G + PG * G * hd) * 4;
-    cudaError_t e = launch_pdl(attention_fused_kernel, dim3(n_chunks, nkv, batch), ATT_FUSED_THREADS, smem, s, qkv, pos, nq, nkv, hd,
-                               max_ctx, theta, n_chunks, cache_k, cache_v, part, counters, out);
+    AttnArgs a;
+    if (!attention_fused_args(qkv, pos, batch, nq, nkv, hd, max_ctx, theta, cache_k, cache_v, out, scratch, &a))
+        return cudaErrorInvalidValue;
+    size_t smem = (size_t)attention_fused_smem_floats(nq, nkv, hd, a.n_chunks) * 4;
+    cudaError_t e = launch_pdl(attention_fused_kernel, dim3(a.n_chunks, nkv, batch), ATT_FUSED_THREADS, smem, s, a);
     if (e != cudaSuccess) return e;
     return cudaGetLastError();
+}
+
+bool attention_fused_args(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd,
+                          uint32_t max_ctx, float theta, float* cache_k, float* cache_v, float* out, void* scratch,
+                          AttnArgs* a) {
+    if (!attention_fused_shape_ok(nq, nkv, hd)) return false;
+    uint32_t n_chunks = (max_ctx + ATT_FUSED_CHUNK - 1) / ATT_FUSED_CHUNK;
+    if ((size_t)attention_fused_smem_floats(nq, nkv, hd, n_chunks) * 4 > 48 * 1024) return false;
+    float* part = static_cast<float*>(scratch);
+    *a = AttnArgs{qkv, pos, batch, nq, nkv, hd, max_ctx, n_chunks, theta, cache_k, cache_v, part,
+                  reinterpret_cast<uint32_t*>(part + (size_t)batch * nq * n_chunks * (hd + 2)), out};
+    return true;
 }
 
 cudaError_t launch_add(const float* a, const float* b, uint64_t n, float* y, cudaStream_t s) {

@@ -100,8 +100,9 @@ int32_t jq_attention_fused_dev(const float* qkv, const int32_t* pos, uint32_t ba
     if (batch == 0) return jq::OK;
     if (!qkv || !pos || !cache_k || !cache_v || !out || !scratch)
         return jq_fail(jq::E_INVALID, "jq_attention_fused_dev: NULL buffer");
-    if (n_kv == 0 || n_q % n_kv || n_q / n_kv > 8 || head_dim == 0 || head_dim > 256 || head_dim % 2)
-        return jq_fail(jq::E_INVALID, "jq_attention_fused_dev: need n_q a multiple of n_kv (at most 8 per kv head) and an even head_dim <= 256");
+    if (n_kv == 0 || n_q % n_kv || !(head_dim == 64 || head_dim == 128 || head_dim == 256) ||
+        !(n_q / n_kv == 1 || n_q / n_kv == 2 || n_q / n_kv == 4 || n_q / n_kv == 8))
+        return jq_fail(jq::E_INVALID, "jq_attention_fused_dev: need head_dim 64, 128 or 256 and 1, 2, 4 or 8 query heads per kv head");
     JQ_CUDA(jq::launch_attention_fused(qkv, pos, batch, n_q, n_kv, head_dim, max_ctx, theta, cache_k, cache_v, out,
                                        scratch, static_cast<cudaStream_t>(stream)));
     return jq::OK;

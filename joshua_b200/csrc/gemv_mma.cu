@@ -37,6 +37,7 @@
 // Algorithmic bytes per launch: n*k/B*S (weights) + 4*m*(k + n).
 #include <algorithm>
 
+#include "chain.cuh"
 #include "common.cuh"
 
 namespace jq {
@@ -154,21 +155,10 @@ __device__ __forceinline__ uint32_t act_position(uint32_t type, uint32_t e) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// Warp-wide variant for use inside the matmul kernel: lane l holds values 8l .. 8l+7 of the unit (group
-// l / 4).  `planes` points at the unit's first group (8 x 96 bytes), `meta` / `sum16` at its first entries.
-// With `nw` (the unit's 256 RMS-norm weights) the values split are x * rs * nw, i.e. the normalised row.
-__device__ __forceinline__ void quantize_unit_warp(const float* __restrict__ xu, uint32_t lane, uint32_t type,
-                                                   int8_t* planes, float2* meta, float* sum16,
-                                                   const float* __restrict__ nw = nullptr, float rs = 1.0f) {
-    const float4* src = reinterpret_cast<const float4*>(xu + lane * 8);
-    float4 lo4 = __ldg(src), hi4 = __ldg(src + 1);
-    float v[8] = {lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
-    if (nw) {
-        const float4* wsrc = reinterpret_cast<const float4*>(nw + lane * 8);
-        float4 w0 = __ldg(wsrc), w1 = __ldg(wsrc + 1);
-        v[0] = v[0] * rs * w0.x, v[1] = v[1] * rs * w0.y, v[2] = v[2] * rs * w0.z, v[3] = v[3] * rs * w0.w;
-        v[4] = v[4] * rs * w1.x, v[5] = v[5] * rs * w1.y, v[6] = v[6] * rs * w1.z, v[7] = v[7] * rs * w1.w;
-    }
+// Splits the 256 values of one unit, 8 per lane (lane l holds values 8l .. 8l+7, group l / 4), into the three
+// planes.  `planes` points at the unit's first group (8 x 96 bytes), `meta` / `sum16` at its first entries.
+__device__ __forceinline__ void quantize_unit_values(const float (&v)[8], uint32_t lane, uint32_t type, int8_t* planes,
+                                                     float2* meta, float* sum16) {
     float amax = 0.0f, sum = 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -213,6 +203,124 @@ __device__ __forceinline__ void quantize_unit_warp(const float* __restrict__ xu,
     }
     if ((lane & 3) == 0) meta[lane >> 2] = make_float2(live ? s2 : 0.0f, s32);
     if ((lane & 1) == 0) sum16[lane >> 1] = s16;
+}
+
+
+// The unit's values come from memory.  COHERENT: x may have been written by another CTA of this same launch
+// (the persistent chain): read it from L2.  With `nw` (the unit's 256 RMS-norm weights) the values split are
+// x * rs * nw, i.e. the normalised row.
+template <bool COHERENT = false>
+__device__ __forceinline__ void load_unit_values(const float* __restrict__ xu, uint32_t lane, float (&v)[8]) {
+    const float4* src = reinterpret_cast<const float4*>(xu + lane * 8);
+    float4 lo4 = COHERENT ? __ldcg(src) : __ldg(src), hi4 = COHERENT ? __ldcg(src + 1) : __ldg(src + 1);
+    v[0] = lo4.x, v[1] = lo4.y, v[2] = lo4.z, v[3] = lo4.w, v[4] = hi4.x, v[5] = hi4.y, v[6] = hi4.z, v[7] = hi4.w;
+}
+
+template <bool COHERENT = false>
+__device__ __forceinline__ void quantize_unit_warp(const float* __restrict__ xu, uint32_t lane, uint32_t type,
+                                                   int8_t* planes, float2* meta, float* sum16,
+                                                   const float* __restrict__ nw = nullptr, float rs = 1.0f) {
+    float v[8];
+    load_unit_values<COHERENT>(xu, lane, v);
+    if (nw) {
+        float g[8];
+        load_unit_values<false>(nw, lane, g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = v[j] * rs * g[j];
+    }
+    quantize_unit_values(v, lane, type, planes, meta, sum16);
+}
+
+// The activation prologue of the matmul kernels: `rows` x k f32 values -> planes in shared memory, by NW warps
+// (w = 0 .. NW-1) that meet on named barrier 1.  Loads are requested in batches before any is used, so the
+// prologue costs about one trip to L2 instead of one per unit.  With `norm_w` every row is RMS-normalised
+// first (1 / rms from the units' sums of squares, added in unit order).  s_tmp: NW * GEMV_MMA_MAX_M floats.
+template <bool COHERENT, int NW>
+__device__ __forceinline__ void split_activations(const float* __restrict__ x, uint32_t rows, uint32_t k,
+                                                  const float* __restrict__ norm_w, float eps, uint32_t type,
+                                                  uint8_t* s_act, int w, uint32_t lane, float* s_tmp) {
+    const uint32_t units_per_row = k / 256, total = rows * units_per_row;
+    const uint64_t groups = (uint64_t)rows * (k / 32);
+    int8_t* planes = reinterpret_cast<int8_t*>(s_act);
+    float2* meta = reinterpret_cast<float2*>(s_act + groups * 96);
+    float* sum16 = reinterpret_cast<float*>(s_act + groups * 104);
+    if (norm_w == nullptr) {
+        for (uint32_t u0 = w; u0 < total; u0 += 4 * NW) {
+            float v[4][8];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                if (u0 + r * NW < total) load_unit_values<COHERENT>(x + (uint64_t)(u0 + r * NW) * 256, lane, v[r]);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const uint32_t u = u0 + r * NW;
+                if (u < total) quantize_unit_values(v[r], lane, type, planes + (uint64_t)u * 768, meta + u * 8, sum16 + u * 16);
+            }
+        }
+    } else if (total <= 2 * NW && total <= (uint32_t)NW * GEMV_MMA_MAX_M) {
+        // at most two units per warp: values stay in registers between the sum of squares and the split
+        float v[2][8], g[2][8];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t u = w + r * NW;
+            if (u < total) {
+                load_unit_values<COHERENT>(x + (uint64_t)u * 256, lane, v[r]);
+                load_unit_values<false>(norm_w + (u % units_per_row) * 256, lane, g[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t u = w + r * NW;
+            if (u < total) {
+                float ss = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss = fmaf(v[r][j], v[r][j], ss);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+                if (lane == 0) s_tmp[u] = ss;
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(NW * 32) : "memory");
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t u = w + r * NW;
+            if (u < total) {
+                const uint32_t row = u / units_per_row;
+                float tot = 0.0f;
+                for (uint32_t q = 0; q < units_per_row; ++q) tot += s_tmp[row * units_per_row + q];
+                const float rs = rsqrtf(tot / (float)k + eps);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[r][j] = v[r][j] * rs * g[r][j];
+                quantize_unit_values(v[r], lane, type, planes + (uint64_t)u * 768, meta + u * 8, sum16 + u * 16);
+            }
+        }
+    } else {
+        // wider inputs: two passes over x
+        float* s_rs = s_tmp + (NW - 1) * GEMV_MMA_MAX_M;  // the last warp's slots double as the row scales
+        for (uint32_t r = 0; r < rows; ++r) {
+            const float4* xr = reinterpret_cast<const float4*>(x + (uint64_t)r * k);
+            float ss = 0.0f;
+            for (uint32_t i = w * 32 + lane; i < k / 4; i += NW * 32) {
+                float4 q = COHERENT ? __ldcg(xr + i) : __ldg(xr + i);
+                ss = fmaf(q.x, q.x, fmaf(q.y, q.y, fmaf(q.z, q.z, fmaf(q.w, q.w, ss))));
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+            float tot = 0.0f;
+            // every warp's partial sum, in warp order, through shared memory (one row at a time)
+            asm volatile("bar.sync 1, %0;" ::"r"(NW * 32) : "memory");
+            if (lane == 0) s_tmp[w * GEMV_MMA_MAX_M] = ss;
+            asm volatile("bar.sync 1, %0;" ::"r"(NW * 32) : "memory");
+            for (int q = 0; q < NW; ++q) tot += s_tmp[q * GEMV_MMA_MAX_M];
+            const float rs = rsqrtf(tot / (float)k + eps);
+            for (uint32_t uc = w; uc < units_per_row; uc += NW) {
+                const uint32_t u = r * units_per_row + uc;
+                quantize_unit_warp<COHERENT>(x + (uint64_t)u * 256, lane, type, planes + (uint64_t)u * 768, meta + u * 8,
+                                             sum16 + u * 16, norm_w + uc * 256, rs);
+            }
+        }
+        (void)s_rs;
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(NW * 32) : "memory");
 }
 
 __global__ void __launch_bounds__(256) quantize_acts_kernel(const float* __restrict__ x, uint64_t m, uint64_t k,
@@ -783,43 +891,9 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1) gemv_mma_kernel(const __gri
     if (ACT && warp != 0) {
         // Consumers and the reducer split the activations into planes in shared memory while the producer
         // fills the ring.
-        const uint64_t groups = (uint64_t)ga.x_rows * n_groups;
-        int8_t* planes = reinterpret_cast<int8_t*>(s_act);
-        float2* meta = reinterpret_cast<float2*>(s_act + groups * 96);
-        float* sum16 = reinterpret_cast<float*>(s_act + groups * 104);
-        if (ga.norm_w != nullptr) {
-            // RMS norm fused in: 1 / rms of every row first (fixed summation order: lane-strided, warp
-            // shuffle tree, then the warps' partial sums in warp order), then the split sees x * rs * w
-            __shared__ float s_part[NCW + 1][GEMV_MMA_MAX_M];
-            __shared__ float s_rs[GEMV_MMA_MAX_M];
-            for (uint32_t r = 0; r < ga.x_rows; ++r) {
-                const float4* xr = reinterpret_cast<const float4*>(ga.x + (uint64_t)r * k);
-                float ss = 0.0f;
-                for (uint32_t i = (warp - 1) * 32 + lane; i < k / 4; i += (NCW + 1) * 32) {
-                    float4 v = __ldg(xr + i);
-                    ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
-                if (lane == 0) s_part[warp - 1][r] = ss;
-            }
-            asm volatile("bar.sync 1, %0;" ::"r"((NCW + 1) * 32) : "memory");
-            if (warp == 1 && lane < ga.x_rows) {
-                float tot = 0.0f;
-                for (int w = 0; w < NCW + 1; ++w) tot += s_part[w][lane];
-                s_rs[lane] = rsqrtf(tot / (float)k + ga.norm_eps);
-            }
-            asm volatile("bar.sync 1, %0;" ::"r"((NCW + 1) * 32) : "memory");
-            for (uint64_t u = warp - 1; u < groups / 8; u += NCW + 1) {
-                const uint32_t r = (uint32_t)(u / units_per_row), uc = (uint32_t)(u % units_per_row);
-                quantize_unit_warp(ga.x + u * 256, lane, TYPE, planes + u * 768, meta + u * 8, sum16 + u * 16,
-                                   ga.norm_w + uc * 256, s_rs[r]);
-            }
-        } else {
-            for (uint64_t u = warp - 1; u < groups / 8; u += NCW + 1)
-                quantize_unit_warp(ga.x + u * 256, lane, TYPE, planes + u * 768, meta + u * 8, sum16 + u * 16);
-        }
-        asm volatile("bar.sync 1, %0;" ::"r"((NCW + 1) * 32) : "memory");
+        __shared__ float s_tmp[(NCW + 1) * GEMV_MMA_MAX_M];
+        split_activations<false, NCW + 1>(ga.x, ga.x_rows, (uint32_t)k, GROUPED == 2 ? nullptr : ga.norm_w, ga.norm_eps,
+                                          TYPE, s_act, warp - 1, lane, s_tmp);
     }
     const uint32_t n_jobs = grouped ? __ldg(ga.n_jobs) : 1u;
     const uint32_t n_tiles = n_jobs * tiles_per_expert;
@@ -992,6 +1066,330 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1) gemv_mma_kernel(const __gri
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&red_empty[rb]);
             }
+        }
+    }
+}
+
+// ───────────────────────────── persistent chain ───────────────────────────
+//
+// A whole sequence of dependent decode operations in ONE launch: quantized linears (with the RMS-norm
+// prologue / residual epilogue / SwiGLU pair forms of the kernel above) and fused attention steps, executed in
+// order by the same 148 persistent CTAs.  Between two operations every CTA must have finished the first: the
+// reducer warp of each CTA counts itself in on a global arrival counter after its last store of an operation
+// and the consumer + reducer warps wait for `gridDim.x` arrivals before they read the next operation's input.
+// The producer warp never waits for that: weights do not depend on activations, so it streams the NEXT
+// operation's tiles into the ring while the consumers are still at the barrier or splitting activations,
+// and the ring is full when they get there.  What a kernel boundary costs (drain, launch, first-load
+// latency) shrinks to one counter round trip.
+//
+// All CTAs must be resident at once (cooperative launch, grid <= SM count, one CTA per SM).  The arrival
+// counter only grows: launch L starts at L * gridDim.x * n_ops, which every CTA recovers by rounding the
+// value it reads on entry down to a multiple of that.  Every poll is bounded; a wait that gives up raises the
+// error flag and the CTA's warps leave (the roles that depend on them run out of their own bounded waits).
+struct ChainArgs {
+    const ChainOp* ops;
+    uint32_t n_ops, m;
+    unsigned long long* arrivals;
+    SmemPlan plan;  // row_stride / act_bytes: the largest any operation needs
+    int* error_flag;
+    unsigned long long* trace;  // optional: CTA 0 stores %globaltimer at three points of every operation
+};
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+constexpr uint32_t CHAIN_POLLS = 1u << 22;
+
+template <uint32_t TYPE, int MB, int NH>
+__global__ void __launch_bounds__((16 + 2) * 32, 1) gemv_chain_kernel(const __grid_constant__ ChainArgs ca) {
+    using Tr = Traits<TYPE>;
+    constexpr int NCW = 16;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint32_t s_abort, s_att_last;
+    __shared__ float s_part[NCW + 1][GEMV_MMA_MAX_M];
+    constexpr int NB = MB * NH;
+    constexpr uint32_t RED_FLOATS = NCW * NB * ROWS;
+    const SmemPlan& plan = ca.plan;
+    const uint32_t stage_bytes = ROWS * plan.row_stride;
+    uint8_t* s_act = smem;
+    uint8_t* ring = smem + plan.act_bytes;
+    uint2* s_grid = reinterpret_cast<uint2*>(ring + plan.n_stages * stage_bytes);
+    uint2* s_mask = s_grid + (TYPE == T_IQ2_XXS ? 256 : 0);
+    float* s_red = reinterpret_cast<float*>(s_mask + (TYPE == T_IQ2_XXS ? 128 : 0));
+    uint64_t* full = reinterpret_cast<uint64_t*>(s_red + 2 * RED_FLOATS);
+    uint64_t* empty = full + plan.n_stages;
+    uint64_t* red_full = empty + plan.n_stages;
+    uint64_t* red_empty = red_full + 2;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t NS = plan.n_stages;
+    if (tid == 0) {
+        for (uint32_t st = 0; st < NS; ++st) {
+            mbar_init(&full[st], ROWS);
+            mbar_init(&empty[st], NCW);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&red_full[b], NCW);
+            mbar_init(&red_empty[b], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_abort = 0;
+    }
+    if (TYPE == T_IQ2_XXS) {
+        for (int i = tid; i < 256; i += (NCW + 2) * 32) s_grid[i] = g_iq2xxs_grid[i];
+        for (int i = tid; i < 128; i += (NCW + 2) * 32) {
+            uint32_t sg = iq2_signs(i);
+            uint32_t lo = ((sg & 0xF) * 0x00204081u) & 0x01010101u, hi = ((sg >> 4) * 0x00204081u) & 0x01010101u;
+            s_mask[i] = make_uint2(lo * 0xFFu, hi * 0xFFu);
+        }
+    }
+    __syncthreads();
+    pdl_wait();
+
+    if (warp == 0) {
+        // ── producer: every linear's tiles, one after the other, never waiting for activations ──
+        if (lane < ROWS) {
+            uint32_t job = 0;
+            for (uint32_t oi = 0; oi < ca.n_ops; ++oi) {
+                const ChainOp* op = ca.ops + oi;
+                if (op->kind != 0) continue;
+                const uint64_t n = op->n, k = op->k;
+                const uint32_t n_tiles = (uint32_t)((n + ROWS - 1) / ROWS);
+                const uint32_t units_per_row = (uint32_t)(k / 256);
+                const uint64_t row_bytes = (uint64_t)units_per_row * Tr::UNIT_BYTES;
+                const uint32_t n_chunks = (units_per_row + Tr::CHUNK_UNITS - 1) / Tr::CHUNK_UNITS;
+                const uint32_t n_sub = op->swiglu ? 2 : 1;
+                for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                    uint64_t row = (uint64_t)tile * ROWS + lane < n ? (uint64_t)tile * ROWS + lane : n - 1;
+                    for (uint32_t sub = 0; sub < n_sub; ++sub) {
+                        const uint8_t* wrow = op->w[sub] + row * row_bytes;
+                        for (uint32_t chunk = 0; chunk < n_chunks; ++chunk, ++job) {
+                            uint32_t st = job % NS, round = job / NS;
+                            if (!mbar_wait(&empty[st], (round & 1) ^ 1)) {
+                                *reinterpret_cast<volatile int*>(ca.error_flag) = 1;
+                                return;
+                            }
+                            uint32_t u_lo = chunk * Tr::CHUNK_UNITS;
+                            uint32_t u_hi = min(units_per_row, u_lo + Tr::CHUNK_UNITS);
+                            uintptr_t beg = reinterpret_cast<uintptr_t>(wrow) + (uint64_t)u_lo * Tr::UNIT_BYTES;
+                            uintptr_t end = beg + (uint64_t)(u_hi - u_lo) * Tr::UNIT_BYTES;
+                            uintptr_t abeg = beg & ~(uintptr_t)15, aend = (end + 15) & ~(uintptr_t)15;
+                            uint32_t bytes = (uint32_t)(aend - abeg);
+                            mbar_arrive_expect_tx(&full[st], bytes);
+                            bulk_g2s(ring + st * stage_bytes + lane * plan.row_stride,
+                                     reinterpret_cast<const void*>(abeg), bytes, &full[st]);
+                        }
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // ── consumers (warps 1..NCW) and the reducer (warp NCW + 1) walk the operations together ──
+    const bool is_reducer = warp == NCW + 1;
+    const int cw = warp - 1;
+    Roles<MB, NH> ro(lane);
+    if (TYPE == T_Q4_K && MB == 1) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+            if (ro.col_p[j] & 1) ro.col_w[j] *= 0.0625f;
+    }
+    const unsigned long long per_launch = (unsigned long long)gridDim.x * ca.n_ops;
+    unsigned long long base = 0;
+    if (is_reducer && lane == 0) {
+        unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(ca.arrivals);
+        base = seen / per_launch * per_launch;
+    }
+    uint32_t job = 0, red_it = 0;
+    // A warp whose bounded wait ran out must not leave on its own: the others would wait for it at the next
+    // named barrier for ever.  It marks the CTA as aborting, stops working, and leaves with everybody else
+    // after that barrier.
+    bool dead = false;
+    float colacc[NH][2][2], minacc[NB][2];
+    constexpr int PER_LANE = (NB * ROWS + 31) / 32;
+    float gate[PER_LANE];
+    const uint32_t group_threads = (NCW + 1) * 32;
+
+    for (uint32_t oi = 0; oi < ca.n_ops; ++oi) {
+        const ChainOp* op = ca.ops + oi;
+        if (oi > 0) {
+            // every CTA has finished operation oi - 1?
+            if (is_reducer && lane == 0) {
+                const unsigned long long want = base + (unsigned long long)oi * gridDim.x;
+                bool ok = false;
+                for (uint32_t it = 0; it < CHAIN_POLLS; ++it) {
+                    unsigned long long v;
+                    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ca.arrivals) : "memory");
+                    if (v >= want) {
+                        ok = true;
+                        break;
+                    }
+                    __nanosleep(40);
+                }
+                if (!ok) {
+                    *reinterpret_cast<volatile int*>(ca.error_flag) = 1;
+                    s_abort = 1;
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(group_threads) : "memory");
+            if (s_abort) return;
+        }
+        const bool tracer = ca.trace != nullptr && blockIdx.x == 0 && is_reducer && lane == 0;
+        if (tracer) ca.trace[3 * oi] = global_ns();
+        if (op->kind == 1) {
+            // ── attention: items (chunk, kv head, sequence) dealt round-robin to the CTAs; warps 1..8 work ──
+            AttnArgs at = op->att;
+            if (ca.trace != nullptr) at.trace = ca.trace + 3 * ca.n_ops + 8 * oi;
+            const uint32_t items = at.n_chunks * at.nkv * at.batch;
+            if (warp >= 1 && warp <= 8) {
+                for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+                    const uint32_t chunk = item % at.n_chunks, rest = item / at.n_chunks;
+                    attention_fused_item_chain<2>(at, chunk, rest % at.nkv, rest / at.nkv, (uint32_t)(tid - 32),
+                                            reinterpret_cast<float*>(s_act), &s_att_last);
+                    att_sync<2>();
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(group_threads) : "memory");
+            if (is_reducer && lane == 0) {
+                __threadfence();
+                atomicAdd(ca.arrivals, 1ull);
+            }
+            if (tracer) ca.trace[3 * oi + 1] = ca.trace[3 * oi + 2] = global_ns();
+            continue;
+        }
+        // ── quantized linear ──
+        const uint64_t n = op->n, k = op->k;
+        const uint32_t n_tiles = (uint32_t)((n + ROWS - 1) / ROWS);
+        const uint32_t units_per_row = (uint32_t)(k / 256);
+        const uint32_t n_chunks = (units_per_row + Tr::CHUNK_UNITS - 1) / Tr::CHUNK_UNITS;
+        const uint64_t row_bytes = (uint64_t)units_per_row * Tr::UNIT_BYTES;
+        const bool swiglu = op->swiglu != 0;
+        const uint32_t n_sub = swiglu ? 2 : 1;
+        const uint32_t n_groups = (uint32_t)(k / 32);
+        const uint64_t groups = (uint64_t)ca.m * n_groups;
+        int8_t* planes = reinterpret_cast<int8_t*>(s_act);
+        float2* meta = reinterpret_cast<float2*>(s_act + groups * 96);
+        float* sum16 = reinterpret_cast<float*>(s_act + groups * 104);
+        split_activations<true, NCW + 1>(op->x, ca.m, (uint32_t)k, op->norm_w, op->norm_eps, TYPE, s_act, warp - 1, lane,
+                                         &s_part[0][0]);
+        if (tracer) ca.trace[3 * oi + 1] = global_ns();
+        const uint32_t rb16 = (uint32_t)(row_bytes & 15);
+        if (!is_reducer) {
+            ActPlanes a;
+            a.planes = planes;
+            a.meta = meta;
+            a.sum16 = sum16;
+            a.n_groups = n_groups;
+            ro.set_rows(0u, ca.m, nullptr, n_groups);
+            for (uint32_t tile = blockIdx.x; !dead && tile < n_tiles; tile += gridDim.x) {
+                const uint64_t row0 = (uint64_t)tile * ROWS;
+                for (uint32_t sub = 0; !dead && sub < n_sub; ++sub, ++red_it) {
+#pragma unroll
+                    for (int h = 0; h < NH; ++h)
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) colacc[h][j][0] = colacc[h][j][1] = 0.0f;
+#pragma unroll
+                    for (int b = 0; b < NB; ++b) minacc[b][0] = minacc[b][1] = 0.0f;
+                    const uint32_t r0c = (uint32_t)min(row0 + ro.g, n - 1), r1c = (uint32_t)min(row0 + ro.g + 8, n - 1);
+                    const uint32_t wlow = (uint32_t)(reinterpret_cast<uintptr_t>(op->w[sub]) & 15);
+                    const uint32_t sh0 = (wlow + r0c * rb16) & 15, sh1 = (wlow + r1c * rb16) & 15;
+                    for (uint32_t chunk = 0; !dead && chunk < n_chunks; ++chunk, ++job) {
+                        uint32_t st = job % NS, round = job / NS;
+                        if (!mbar_wait(&full[st], round & 1)) {
+                            if (lane == 0) *reinterpret_cast<volatile int*>(ca.error_flag) = 1;
+                            s_abort = 1;
+                            dead = true;
+                            break;
+                        }
+                        const uint8_t* sp = ring + st * stage_bytes;
+                        const uint32_t u_lo = chunk * Tr::CHUNK_UNITS;
+                        const uint32_t cnt = min(units_per_row - u_lo, Tr::CHUNK_UNITS);
+                        for (uint32_t u = cw; u < cnt; u += NCW) {
+                            const uint8_t* u0 = sp + ro.g * plan.row_stride + sh0 + u * Tr::UNIT_BYTES;
+                            const uint8_t* u1 = sp + (ro.g + 8) * plan.row_stride + sh1 + u * Tr::UNIT_BYTES;
+                            process_unit<TYPE, MB, NH, 1>(u0, u1, u_lo + u, a, ro, s_grid, s_mask, colacc, minacc);
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&empty[st]);
+                    }
+                    const uint32_t rb = red_it & 1;
+                    if (dead || !mbar_wait(&red_empty[rb], ((red_it >> 1) & 1) ^ 1)) {
+                        if (lane == 0) *reinterpret_cast<volatile int*>(ca.error_flag) = 1;
+                        s_abort = 1;
+                        dead = true;
+                        break;
+                    }
+                    float* red = s_red + rb * RED_FLOATS;
+#pragma unroll
+                    for (int b = 0; b < NB; ++b) {
+                        const int h = b / MB, i = b % MB;
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            float v = -minacc[b][r];
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) v += ro.col_i[j] == i ? colacc[h][j][r] : 0.0f;
+                            v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+                            v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
+                            if (ro.t == 0) red[(cw * NB + b) * ROWS + ro.g + 8 * r] = v;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&red_full[rb]);
+                }
+            }
+        } else {
+            for (uint32_t tile = blockIdx.x; !dead && tile < n_tiles; tile += gridDim.x) {
+                const uint64_t row0 = (uint64_t)tile * ROWS;
+                for (uint32_t sub = 0; sub < n_sub; ++sub, ++red_it) {
+                    const uint32_t rb = red_it & 1;
+                    if (!mbar_wait(&red_full[rb], (red_it >> 1) & 1)) {
+                        if (lane == 0) *reinterpret_cast<volatile int*>(ca.error_flag) = 1;
+                        s_abort = 1;
+                        dead = true;
+                        break;
+                    }
+                    const float* red = s_red + rb * RED_FLOATS;
+#pragma unroll
+                    for (int q = 0; q < PER_LANE; ++q) {
+                        const int o = lane + 32 * q;
+                        if (o < NB * ROWS) {
+                            const int r = o % ROWS;
+                            const uint32_t b = o / ROWS;
+                            float v = 0.0f;
+#pragma unroll
+                            for (int cwv = 0; cwv < NCW; ++cwv) v += red[(cwv * NB + (int)b) * ROWS + r];
+                            if (swiglu && sub == 0) {
+                                gate[q] = v;
+                            } else if (b < ca.m && row0 + r < n) {
+                                if (swiglu) {
+                                    float gv = gate[q], uv = v;
+                                    if (op->clamp > 0.0f) {
+                                        gv = fminf(gv, op->clamp);
+                                        uv = fmaxf(-op->clamp, fminf(uv, op->clamp));
+                                    }
+                                    v = silu_f(gv) * uv;
+                                }
+                                const uint64_t o_idx = (uint64_t)b * n + row0 + r;
+                                if (op->residual != nullptr) v += __ldcg(op->residual + o_idx);
+                                op->dst[o_idx] = v;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&red_empty[rb]);
+                }
+            }
+            // this CTA's part of the operation is stored: count in
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence();
+                atomicAdd(ca.arrivals, 1ull);
+            }
+            if (tracer) ca.trace[3 * oi + 2] = global_ns();
         }
     }
 }
@@ -1252,6 +1650,83 @@ cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s) {
     if (g.planes == nullptr) return launch_typed<1, 2>(g.type, ga, g.rows_per_job, tiles, s);
     ga.act = planes_in(g.planes, g.x_rows, g.k);
     return launch_typed<0, 2>(g.type, ga, g.rows_per_job, tiles, s);
+}
+
+// ── launching a chain ───────────────────────────────────────────────────────────────────────────────
+namespace {
+
+template <uint32_t TYPE, int MB, int NH>
+cudaError_t launch_chain_variant(ChainArgs& ca, uint64_t max_k, uint32_t att_floats, cudaStream_t s) {
+    constexpr int NCW = 16;
+    if (g_num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    SmemPlan p = plan_smem<TYPE, NCW, MB * NH>(max_k, ca.m, 8);
+    uint32_t act = std::max<uint32_t>(p.act_bytes, att_floats * 4);
+    act = (act + 127) & ~127u;
+    uint32_t fixed = p.total - p.act_bytes - p.n_stages * ROWS * p.row_stride;
+    uint32_t stage = ROWS * p.row_stride;
+    if (act + fixed + stage > SMEM_BUDGET) return cudaErrorInvalidValue;
+    p.act_bytes = act;
+    p.n_stages = std::min<uint32_t>(8, (SMEM_BUDGET - fixed - act) / stage);
+    p.total = act + p.n_stages * stage + fixed;
+    ca.plan = p;
+    auto kern = gemv_chain_kernel<TYPE, MB, NH>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)g_num_sms);
+    cfg.blockDim = dim3((NCW + 2) * 32);
+    cfg.dynamicSmemBytes = p.total;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident at once: they wait on one another
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ca);
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+template <uint32_t TYPE>
+cudaError_t launch_chain_rows(ChainArgs& ca, uint64_t max_k, uint32_t att_floats, cudaStream_t s) {
+    if (ca.m == 1) return launch_chain_variant<TYPE, 1, 1>(ca, max_k, att_floats, s);
+    if (ca.m == 2) return launch_chain_variant<TYPE, 2, 1>(ca, max_k, att_floats, s);
+    if (ca.m <= 4) return launch_chain_variant<TYPE, 2, 2>(ca, max_k, att_floats, s);
+    if (ca.m <= 8) return launch_chain_variant<TYPE, 2, 4>(ca, max_k, att_floats, s);
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+bool gemv_chain_supports(uint32_t type, uint64_t m, uint64_t max_k, uint32_t att_floats) {
+    if (type != T_Q4_K && type != T_Q8_0) return false;  // the chain is instantiated for the decode formats
+    return m >= 1 && m <= GEMV_MMA_MAX_M && max_k % 256 == 0 && acts_fit_in_smem(m, max_k) &&
+           att_floats * 4 <= ACT_SMEM_MAX;
+}
+
+cudaError_t launch_gemv_chain(uint32_t type, uint32_t m, const ChainOp* ops_dev, uint32_t n_ops, uint64_t max_k,
+                              uint32_t att_floats, unsigned long long* arrivals, int* error_flag, cudaStream_t s,
+                              unsigned long long* trace) {
+    if (!gemv_chain_supports(type, m, max_k, att_floats) || n_ops == 0) return cudaErrorInvalidValue;
+    ChainArgs ca = {};
+    ca.trace = trace;
+    ca.ops = ops_dev;
+    ca.n_ops = n_ops;
+    ca.m = m;
+    ca.arrivals = arrivals;
+    ca.error_flag = error_flag;
+    switch (type) {
+        case T_Q4_K: return launch_chain_rows<T_Q4_K>(ca, max_k, att_floats, s);
+        case T_Q8_0: return launch_chain_rows<T_Q8_0>(ca, max_k, att_floats, s);
+        default: return cudaErrorInvalidValue;
+    }
 }
 
 }  // namespace jq

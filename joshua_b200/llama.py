@@ -119,6 +119,48 @@ class LlamaDecoder:
                                    P(self.logits), s))
         check(L.jq_argmax_dev(P(self.logits), B, c.vocab, P(self.token), P(self.pos), P(self.argmax_scratch), s))
 
+    def build_chain(self) -> None:
+        """The layers and the output head as ONE persistent launch (`jq_chain_*`): per layer the QKV linear
+        (norm prologue), attention, the output projection (residual epilogue), the gate / up SwiGLU pair (norm
+        prologue) and the down projection (residual epilogue), then the head (norm prologue)."""
+        L, c, B, P = _lib.lib(), self.cfg, self.batch, lambda t: t.data_ptr()
+        h = c.hidden
+        ch = ctypes.c_void_p()
+        check(L.jq_chain_create(self.embed.ctx._h, self.wtype, B, ctypes.byref(ch)))
+        self._chain = ch
+        for ly in self.layers:
+            check(L.jq_chain_add_linear(ch, ly["wqkv"]._h, None, h, c.qkv_rows, P(self.x), P(ly["attn_norm"]), c.eps,
+                                        None, 0.0, P(self.qkv)))
+            check(L.jq_chain_add_attention(ch, P(self.qkv), P(self.pos), c.q_heads, c.kv_heads, c.head_dim,
+                                           self.max_ctx, c.rope_theta, P(ly["k"]), P(ly["v"]), P(self.attn),
+                                           P(self.att_fused_scratch)))
+            check(L.jq_chain_add_linear(ch, ly["wo"]._h, None, c.q_heads * c.head_dim, h, P(self.attn), None, 0.0,
+                                        P(self.x), 0.0, P(self.x)))
+            check(L.jq_chain_add_linear(ch, ly["w_gate"]._h, ly["w_up"]._h, h, c.ffn, P(self.x), P(ly["ffn_norm"]),
+                                        c.eps, None, 0.0, P(self.act)))
+            check(L.jq_chain_add_linear(ch, ly["w_down"]._h, None, c.ffn, h, P(self.act), None, 0.0, P(self.x), 0.0,
+                                        P(self.x)))
+        check(L.jq_chain_add_linear(ch, self.output._h, None, h, c.vocab, P(self.x), P(self.out_norm), c.eps, None, 0.0,
+                                    P(self.logits)))
+
+    def step_chain(self, stream=None) -> None:
+        """The same step in four launches: embedding, the chain, the two arg-max stages."""
+        L, c, B, P = _lib.lib(), self.cfg, self.batch, lambda t: t.data_ptr()
+        s = self.torch.cuda.current_stream(self.dev).cuda_stream if stream is None else stream
+        if getattr(self, "_chain", None) is None:
+            self.build_chain()
+        check(L.jq_embedding_dev(self.embed._h, P(self.token), B, c.vocab, c.hidden, P(self.x), P(self.bad), s))
+        check(L.jq_chain_run(self._chain, s))
+        check(L.jq_argmax_dev(P(self.logits), B, c.vocab, P(self.token), P(self.pos), P(self.argmax_scratch), s))
+
+    def __del__(self):
+        try:
+            if getattr(self, "_chain", None) is not None:
+                _lib.lib().jq_chain_free(self._chain)
+                self._chain = None
+        except Exception:
+            pass
+
     def step_unfused(self, stream=None) -> None:
         """The same step from the separate kernels (norm, rope, attention partial + merge as their own
         launches); kept as the cross-check of the fused step."""

@@ -148,7 +148,8 @@ def test_fused_step_matches_separate_kernels(batch):
     assert a.pos.tolist() == [70] * batch
 
 
-@pytest.mark.parametrize("nq,nkv,hd,ctx", [(8, 2, 64, 1), (8, 8, 128, 33), (32, 4, 128, 100), (16, 2, 256, 64)])
+@pytest.mark.parametrize("nq,nkv,hd,ctx", [(8, 2, 64, 1), (8, 8, 128, 33), (32, 4, 128, 100), (16, 2, 256, 64),
+                                            (32, 8, 128, 128), (4, 2, 64, 65), (16, 2, 128, 127)])
 def test_fused_attention_matches_rope_append_attention(nq, nkv, hd, ctx):
     import torch
 
@@ -178,3 +179,29 @@ def test_fused_attention_matches_rope_append_attention(nq, nkv, hd, ctx):
     torch.cuda.synchronize()
     assert torch.equal(ck, ck2) and torch.equal(cv, cv2)          # same appended rows, bit for bit
     assert float((got - want).abs().max()) <= 2e-5 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("batch,wtype", [(1, synth.Q4_K), (3, synth.Q4_K), (1, synth.Q8_0)])
+def test_chain_step_matches_separate_launches(batch, wtype):
+    """The persistent chain (one launch for all layers and the head) against the five-launch-per-layer step:
+    same kernels' arithmetic operation by operation, so the logits agree to rounding of the norm sums."""
+    import torch
+
+    cfg = LlamaConfig(layers=3, hidden=512, q_heads=8, kv_heads=2, head_dim=128, ffn=768, vocab=1000)
+    mk = _small_weights(wtype)
+    a = LlamaDecoder(cfg, torch.device("cuda", 0), batch=batch, max_ctx=150, wtype=wtype, seed=5, weights=mk)
+    b = LlamaDecoder(cfg, torch.device("cuda", 0), batch=batch, max_ctx=150, wtype=wtype, seed=5, weights=mk)
+    a.reset(7)
+    b.reset(7)
+    for step in range(140):
+        a.step_chain()
+        b.step()
+        torch.cuda.synchronize()
+        la, lb = a.logits.cpu().numpy(), b.logits.cpu().numpy()
+        scale = max(1.0, float(np.abs(lb).max()))
+        assert float(np.abs(la - lb).max()) <= 1e-5 * scale, step
+        b.token.copy_(a.token)
+    assert a.pos.tolist() == [140] * batch
+    from joshua_b200.qtensor import default_context
+    from joshua_b200 import _lib
+    _lib.check(_lib.lib().jq_device_status(default_context(0)._h))
