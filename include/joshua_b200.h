@@ -301,6 +301,13 @@ int32_t jq_moe_forward_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, con
 int32_t jq_moe_forward_add_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, const uint32_t* forced_ids_dev,
                                const float* residual_dev, float* y_dev, void* stream);
 
+/* The same with the RMS norm of the block folded in: y = residual +
+ * layer(rmsnorm(x; norm_w, eps)).  For batches of up to 8 tokens the layer is
+ * four launches: router + routing + job list, gate/up, down, combine. */
+int32_t jq_moe_forward_norm_add_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, const uint32_t* forced_ids_dev,
+                                    const float* norm_w_dev, float eps, const float* residual_dev, float* y_dev,
+                                    void* stream);
+
 /* The two halves, for expert-parallel callers that exchange rows between
  * devices in between: routing alone (ids, weights: [n_tokens, n_used]), and the
  * expert MLPs alone over arbitrary rows, out[r] = MLP_{expert_ids[r]}(x[r])
@@ -309,6 +316,10 @@ int32_t jq_moe_route_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, const
                          uint32_t* ids_dev, float* wts_dev, void* stream);
 int32_t jq_moe_experts_dev(jq_moe* m, const float* x_dev, uint64_t n_rows, const uint32_t* expert_ids_dev,
                            float* out_dev, void* stream);
+
+/* Profiling aid: with a device buffer of 8 uint64 the last CTA of the decode router kernel stores the GPU
+ * nanosecond timer at its phases (entered, logits stored, counted in, routed, jobs built); NULL = off. */
+int32_t jq_debug_moe_trace(uint64_t* trace_dev);
 
 /* After synchronising: JQ_E_EXPERT_RANGE if an id was out of range under
  * oob_policy 0, JQ_E_TIMEOUT as jq_device_status, else JQ_OK. */

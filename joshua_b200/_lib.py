@@ -66,6 +66,7 @@ _SIGNATURES = {
     "jq_moe_route_dev": (i32, [vp, vp, u64, vp, vp, vp, vp]),
     "jq_moe_experts_dev": (i32, [vp, vp, u64, vp, vp, vp]),
     "jq_moe_status": (i32, [vp]),
+    "jq_debug_moe_trace": (i32, [vp]),
     "jq_moe_last_routing": (i32, [vp, u64, vp, vp]),
     "jq_chain_create": (i32, [vp, u32, u32, ctypes.POINTER(vp)]),
     "jq_chain_free": (None, [vp]),
@@ -79,6 +80,7 @@ _SIGNATURES = {
     "jq_ep_connect": (i32, [vp, vp]),
     "jq_ep_forward_dev": (i32, [vp, vp, vp, vp, u64, vp, vp, vp]),
     "jq_moe_forward_add_dev": (i32, [vp, vp, u64, vp, vp, vp, vp]),
+    "jq_moe_forward_norm_add_dev": (i32, [vp, vp, u64, vp, vp, f32, vp, vp, vp]),
     "jq_matmul_swiglu_norm_dev": (i32, [vp, vp, u64, u64, u64, vp, vp, f32, vp, f32, vp]),
     "jq_matmul_norm_dev": (i32, [vp, u64, u64, u64, vp, vp, f32, vp, vp, vp]),
     "jq_attention_fused_scratch_bytes": (u64, [u32, u32, u32, u32, u32]),

@@ -114,6 +114,8 @@ struct GroupedLaunch {
     float* dst;
     float clamp;
     int* error_flag;
+    const float* norm_w;      // planes == NULL only: RMS-normalise the activation rows with these weights first
+    float norm_eps;
 };
 cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s);
 
@@ -134,6 +136,14 @@ cudaError_t launch_moe_route(const float* logits, const MoeRouteParams& rp, uint
 cudaError_t launch_moe_jobs(const uint32_t* ids, uint32_t T, uint32_t K, uint32_t E, uint32_t rows_per_job,
                             uint32_t* list_token, uint32_t* inv, MoeJob* jobs, uint32_t* n_jobs, uint32_t* n_list,
                             int* bad_id, cudaStream_t s);
+cudaError_t moe_set_trace(unsigned long long* dev_buf);
+// logits + routing (+ job list) in one launch for decode-sized batches; `counter`: a device word that is zero
+// between calls.  With norm_w the tokens are RMS-normalised inside the kernel.
+cudaError_t launch_moe_route_fused(const float* x, const float* norm_w, float eps, const float* router, uint32_t T,
+                                   uint32_t h, float* logits, const MoeRouteParams& rp, const float* bias,
+                                   const uint32_t* forced_ids, uint32_t* ids, float* wts, bool do_jobs,
+                                   uint32_t rows_per_job, uint32_t* list_token, uint32_t* inv, MoeJob* jobs,
+                                   uint32_t* n_jobs, uint32_t* n_list, int* bad_id, uint32_t* counter, cudaStream_t s);
 cudaError_t launch_moe_combine(const float* out, const uint32_t* inv, const float* wts, const float* shared, uint32_t T,
                                uint32_t K, uint32_t h, float* y, cudaStream_t s, const float* residual = nullptr);
 cudaError_t launch_swiglu(const float* g, const float* u, uint64_t n, float clamp, float* out, cudaStream_t s);

@@ -892,7 +892,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1) gemv_mma_kernel(const __gri
         // Consumers and the reducer split the activations into planes in shared memory while the producer
         // fills the ring.
         __shared__ float s_tmp[(NCW + 1) * GEMV_MMA_MAX_M];
-        split_activations<false, NCW + 1>(ga.x, ga.x_rows, (uint32_t)k, GROUPED == 2 ? nullptr : ga.norm_w, ga.norm_eps,
+        split_activations<false, NCW + 1>(ga.x, ga.x_rows, (uint32_t)k, ga.norm_w, ga.norm_eps,
                                           TYPE, s_act, warp - 1, lane, s_tmp);
     }
     const uint32_t n_jobs = grouped ? __ldg(ga.n_jobs) : 1u;
@@ -1646,6 +1646,8 @@ cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s) {
     ga.clamp = g.clamp;
     ga.swiglu = g.w1 != nullptr;
     ga.error_flag = g.error_flag;
+    ga.norm_w = g.planes == nullptr ? g.norm_w : nullptr;
+    ga.norm_eps = g.norm_eps;
     uint64_t tiles = (uint64_t)g.max_jobs * ((g.n + ROWS - 1) / ROWS);
     if (g.planes == nullptr) return launch_typed<1, 2>(g.type, ga, g.rows_per_job, tiles, s);
     ga.act = planes_in(g.planes, g.x_rows, g.k);

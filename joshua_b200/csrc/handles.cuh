@@ -132,6 +132,8 @@ struct jq_moe {
     // constants on the device: jobs {0, 0, c} for c = 1..8 (a dense product as a single job) and the count 1
     jq::MoeJob* dense_jobs = nullptr;
     uint32_t* one = nullptr;
+    uint32_t* counter = nullptr;  // arrival counter of the fused router kernel (zero between calls)
+    float* xn = nullptr;          // normalised tokens, for the paths that cannot fold the norm in
     int* bad_host = nullptr;  // pinned, device-visible: an expert id was out of range
     int* bad_dev = nullptr;
     std::mutex mu;

@@ -62,25 +62,43 @@ __device__ __forceinline__ uint32_t warp_argmax(const float* v, const uint8_t* t
 
 constexpr uint32_t MAX_EXPERTS = 512;
 
-// One warp per token: scores, selection (bias, group limit), top-k, weights.
-__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, MoeRouteParams rp, uint32_t T,
-                                                        const float* __restrict__ bias,
-                                                        const uint32_t* __restrict__ forced_ids,
-                                                        uint32_t* __restrict__ ids, float* __restrict__ wts) {
-    __shared__ float s_prob[4][MAX_EXPERTS];
-    __shared__ float s_sel[4][MAX_EXPERTS];
-    __shared__ uint8_t s_taken[4][MAX_EXPERTS];
-    __shared__ float s_group[4][64];
-    __shared__ uint8_t s_gtaken[4][64];
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t lane = threadIdx.x & 31, wq = threadIdx.x >> 5;
+// Profiling aid (jq_debug_moe_trace): when set, the last CTA of the fused router kernel stores the GPU
+// nanosecond timer at its phases.
+__device__ unsigned long long* g_moe_trace = nullptr;
+__device__ __forceinline__ unsigned long long moe_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Shared memory of the routing code for up to four warps (one token per warp at a time).
+struct RouteSmem {
+    float prob[4][MAX_EXPERTS];
+    float sel[4][MAX_EXPERTS];
+    uint8_t taken[4][MAX_EXPERTS];
+    float group[4][64];
+    uint8_t gtaken[4][64];
+    uint32_t chosen[4][MAX_EXPERTS];  // the ids picked for the current token, in slot order
+};
+
+// One warp per token: scores, selection (bias, group limit), top-k, weights.  Warp `wq` of `nwq` (at most 4)
+// takes tokens first + wq, first + wq + stride, ...
+__device__ __forceinline__ void route_tokens(const float* __restrict__ logits, const MoeRouteParams& rp, uint32_t T,
+                                             const float* __restrict__ bias, const uint32_t* __restrict__ forced_ids,
+                                             uint32_t* __restrict__ ids, float* __restrict__ wts, RouteSmem& sm,
+                                             uint32_t first, uint32_t stride, uint32_t wq, uint32_t lane) {
     const uint32_t E = rp.n_expert, K = rp.n_used;
-    float* prob = s_prob[wq];
-    float* sel = s_sel[wq];
-    uint8_t* taken = s_taken[wq];
-    for (uint32_t t = blockIdx.x * 4 + wq; t < T; t += gridDim.x * 4) {
-        const float* lg = logits + (uint64_t)t * E;
+    float* prob = sm.prob[wq];
+    float* sel = sm.sel[wq];
+    uint8_t* taken = sm.taken[wq];
+    float (*s_group)[64] = sm.group;
+    uint8_t (*s_gtaken)[64] = sm.gtaken;
+    uint32_t* chosen = sm.chosen[wq];
+    for (uint32_t t = first + wq; t < T; t += stride) {
+        // one trip to memory for the token's logits (they were written by other CTAs: read through L2)
+        for (uint32_t e = lane; e < E; e += 32) sel[e] = __ldcg(logits + (uint64_t)t * E + e);
+        __syncwarp();
+        const float* lg = sel;
         // scores
         if (rp.gating == MOE_GATE_SOFTMAX) {
             float mx = -INFINITY;
@@ -113,7 +131,10 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
         float* w = wts + (uint64_t)t * K;
         if (forced_ids) {
             // hash-routed layers: ids come from a token-id table, weights from the gate scores
-            for (uint32_t s = lane; s < K; s += 32) id[s] = forced_ids[(uint64_t)t * K + s];
+            for (uint32_t s = lane; s < K; s += 32) {
+                chosen[s] = forced_ids[(uint64_t)t * K + s];
+                id[s] = chosen[s];
+            }
         } else {
             if (rp.n_group > 1) {
                 // group-limited selection: score groups by their two best members (sigmoid) or their best
@@ -147,35 +168,71 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
                 }
                 __syncwarp();
             }
+            // top-k in registers: lane l holds sel[l + 32 i]; every round is a local scan, one warp-wide
+            // maximum of the order-preserving integer image of the value, and one warp-wide minimum of the
+            // candidates' indices (ties go to the lower index, the order a stable descending sort gives)
+            constexpr int EPL = MAX_EXPERTS / 32;
+            const int epl = (int)((E + 31) / 32);
+            float val[EPL];
+            uint32_t live = 0;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                const uint32_t e = lane + 32 * i;
+                val[i] = (i < epl && e < E) ? sel[e] : -INFINITY;
+                if (i < epl && e < E) live |= 1u << i;
+            }
             for (uint32_t s = 0; s < K; ++s) {
-                uint32_t e = warp_argmax(sel, taken, E, lane);
-                __syncwarp();
+                float best = -INFINITY;
+                int bi = -1;
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) {
+                    if (i >= epl) break;
+                    if (((live >> i) & 1u) && (bi < 0 || val[i] > best)) {
+                        best = val[i];
+                        bi = i;
+                    }
+                }
+                const uint32_t bits = __float_as_uint(best);
+                const uint32_t key = bi < 0 ? 0u : (bits ^ ((bits >> 31) ? 0xFFFFFFFFu : 0x80000000u));
+                const uint32_t mx = __reduce_max_sync(0xFFFFFFFFu, key);
+                const uint32_t cand = (bi >= 0 && key == mx) ? lane + 32u * (uint32_t)bi : 0xFFFFFFFFu;
+                const uint32_t e = __reduce_min_sync(0xFFFFFFFFu, cand);
+                if (e != 0xFFFFFFFFu && (e & 31u) == lane) live &= ~(1u << (e >> 5));
                 if (lane == 0) {
-                    taken[e] = 1;
+                    chosen[s] = e;
                     id[s] = e;
                 }
-                __syncwarp();
             }
         }
         __syncwarp();
-        // weights from the unbiased scores of the chosen experts
-        if (lane == 0) {
-            float sum = 0.0f;
-            for (uint32_t s = 0; s < K; ++s) {
-                uint32_t e = id[s];
-                float p = e < E ? prob[e] : 0.0f;
-                w[s] = p;
-                sum += p;
-            }
-            if (rp.norm) {
-                float denom = rp.renorm_plus_eps ? sum + 1e-20f : fmaxf(sum, 6.1035156e-5f);
-                for (uint32_t s = 0; s < K; ++s) w[s] = w[s] / denom;
-            }
-            if (rp.scale != 0.0f && rp.scale != 1.0f)
-                for (uint32_t s = 0; s < K; ++s) w[s] = w[s] * rp.scale;
+        // weights from the unbiased scores of the chosen experts: the sum runs in slot order, then every
+        // weight is written once
+        float sum = 0.0f;
+        for (uint32_t s = 0; s < K; ++s) {
+            const uint32_t e = chosen[s];
+            sum += e < E ? prob[e] : 0.0f;
+        }
+        const float denom = rp.renorm_plus_eps ? sum + 1e-20f : fmaxf(sum, 6.1035156e-5f);
+        for (uint32_t s = lane; s < K; s += 32) {
+            const uint32_t e = chosen[s];
+            float p = e < E ? prob[e] : 0.0f;
+            if (rp.norm) p = p / denom;
+            if (rp.scale != 0.0f && rp.scale != 1.0f) p = p * rp.scale;
+            w[s] = p;
         }
         __syncwarp();
     }
+}
+
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, MoeRouteParams rp, uint32_t T,
+                                                        const float* __restrict__ bias,
+                                                        const uint32_t* __restrict__ forced_ids,
+                                                        uint32_t* __restrict__ ids, float* __restrict__ wts) {
+    __shared__ RouteSmem sm;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    route_tokens(logits, rp, T, bias, forced_ids, ids, wts, sm, blockIdx.x * 4, gridDim.x * 4, threadIdx.x >> 5,
+                 threadIdx.x & 31);
 }
 
 // One CTA: expert histogram, offsets, the expert-sorted list of (token, slot) pairs (token-major inside an
@@ -183,21 +240,26 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 //   list_token[pos]  token of list position pos (the activation row of the gate/up products)
 //   inv[pair]        list position of pair = token * K + slot, or 0xFFFFFFFF if the id was out of range
 // Out-of-range ids raise *bad_id (the caller turns it into an error or ignores it, per loader).
-__global__ void __launch_bounds__(1024) moe_jobs_kernel(const uint32_t* __restrict__ ids, uint32_t T, uint32_t K,
-                                                        uint32_t E, uint32_t rows_per_job,
-                                                        uint32_t* __restrict__ list_token, uint32_t* __restrict__ inv,
-                                                        MoeJob* __restrict__ jobs, uint32_t* __restrict__ n_jobs,
-                                                        uint32_t* __restrict__ n_list, int* __restrict__ bad_id) {
-    __shared__ uint32_t s_cnt[MAX_EXPERTS];
-    __shared__ uint32_t s_off[MAX_EXPERTS];
-    __shared__ uint32_t s_job[MAX_EXPERTS];
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+struct JobsSmem {
+    uint32_t cnt[MAX_EXPERTS], off[MAX_EXPERTS], job[MAX_EXPERTS];
+};
+
+// Body of the job builder for the `nthreads` threads of one CTA (tid = 0 .. nthreads - 1, whole warps).
+template <class Sync>
+__device__ __forceinline__ void build_jobs(const uint32_t* __restrict__ ids, uint32_t T, uint32_t K, uint32_t E,
+                                           uint32_t rows_per_job, uint32_t* __restrict__ list_token,
+                                           uint32_t* __restrict__ inv, MoeJob* __restrict__ jobs,
+                                           uint32_t* __restrict__ n_jobs, uint32_t* __restrict__ n_list,
+                                           int* __restrict__ bad_id, JobsSmem& js, uint32_t tid, uint32_t nthreads,
+                                           Sync cta_sync) {
+    uint32_t* s_cnt = js.cnt;
+    uint32_t* s_off = js.off;
+    uint32_t* s_job = js.job;
+    const uint32_t lane = tid & 31, warp = tid >> 5, nwarp = nthreads >> 5;
     const uint32_t P = T * K;
-    for (uint32_t e = tid; e < E; e += blockDim.x) s_cnt[e] = 0;
-    __syncthreads();
-    for (uint32_t p = tid; p < P; p += blockDim.x) {
+    for (uint32_t e = tid; e < E; e += nthreads) s_cnt[e] = 0;
+    cta_sync();
+    for (uint32_t p = tid; p < P; p += nthreads) {
         uint32_t e = ids[p];
         if (e < E)
             atomicAdd(&s_cnt[e], 1u);
@@ -206,7 +268,7 @@ __global__ void __launch_bounds__(1024) moe_jobs_kernel(const uint32_t* __restri
             *bad_id = 1;
         }
     }
-    __syncthreads();
+    cta_sync();
     if (tid == 0) {
         uint32_t off = 0, job = 0;
         for (uint32_t e = 0; e < E; ++e) {
@@ -218,7 +280,7 @@ __global__ void __launch_bounds__(1024) moe_jobs_kernel(const uint32_t* __restri
         *n_jobs = job;
         *n_list = off;
     }
-    __syncthreads();
+    cta_sync();
     // stable fill: a warp owns an expert and walks the pairs in order
     for (uint32_t e = warp; e < E; e += nwarp) {
         const uint32_t cnt = s_cnt[e];
@@ -242,6 +304,111 @@ __global__ void __launch_bounds__(1024) moe_jobs_kernel(const uint32_t* __restri
             jd.cnt = min(rows_per_job, cnt - j * rows_per_job);
             jobs[s_job[e] + j] = jd;
         }
+    }
+}
+
+
+__global__ void __launch_bounds__(1024) moe_jobs_kernel(const uint32_t* __restrict__ ids, uint32_t T, uint32_t K,
+                                                        uint32_t E, uint32_t rows_per_job,
+                                                        uint32_t* __restrict__ list_token, uint32_t* __restrict__ inv,
+                                                        MoeJob* __restrict__ jobs, uint32_t* __restrict__ n_jobs,
+                                                        uint32_t* __restrict__ n_list, int* __restrict__ bad_id) {
+    __shared__ JobsSmem js;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    build_jobs(ids, T, K, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id, js, threadIdx.x, blockDim.x,
+               [] { __syncthreads(); });
+}
+
+// Decode-sized batches (T <= 8): router logits, routing and the job list in ONE launch.  A CTA per (token,
+// expert) dot product, spread over many CTAs so that the [E, h] router matrix streams at full speed; each CTA
+// counts itself in when its logits are stored and the last one routes the tokens and builds the jobs.  With
+// `norm_w` the tokens are RMS-normalised first (every CTA derives 1 / rms of its tokens itself), so the norm
+// kernel in front of the layer disappears.
+__global__ void __launch_bounds__(128) moe_route_fused_kernel(
+    const float* __restrict__ x, const float* __restrict__ norm_w, float eps, const float* __restrict__ router,
+    uint32_t T, uint32_t h, float* __restrict__ logits, MoeRouteParams rp, const float* __restrict__ bias,
+    const uint32_t* __restrict__ forced_ids, uint32_t* __restrict__ ids, float* __restrict__ wts, int do_jobs,
+    uint32_t rows_per_job, uint32_t* __restrict__ list_token, uint32_t* __restrict__ inv, MoeJob* __restrict__ jobs,
+    uint32_t* __restrict__ n_jobs, uint32_t* __restrict__ n_list, int* __restrict__ bad_id,
+    uint32_t* __restrict__ counter) {
+    __shared__ RouteSmem sm;
+    __shared__ JobsSmem js;
+    __shared__ uint32_t s_last;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t lane = threadIdx.x & 31, wq = threadIdx.x >> 5, E = rp.n_expert;
+    __shared__ float s_acc[4], s_ss[4];
+    unsigned long long* trace = g_moe_trace;
+    unsigned long long t_start = 0, t_logits = 0, t_counted = 0;
+    if (trace && threadIdx.x == 0) t_start = moe_now();
+    {
+        // one CTA per (token, expert) dot product; every thread requests all its pieces before using any
+        const uint32_t pair = blockIdx.x, t = pair / E, e = pair - t * E;
+        const float4* a = reinterpret_cast<const float4*>(x + (uint64_t)t * h);
+        const float4* b = reinterpret_cast<const float4*>(router + (uint64_t)e * h);
+        const float4* g = reinterpret_cast<const float4*>(norm_w);
+        float acc = 0.0f, ss = 0.0f;
+        for (uint32_t j0 = threadIdx.x; j0 < h / 4; j0 += 128 * 4) {
+            float4 u[4], v[4], w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t j = j0 + q * 128;
+                const bool in = j < h / 4;
+                u[q] = in ? __ldg(a + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[q] = in ? __ldg(b + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                w[q] = (in && norm_w) ? __ldg(g + j) : make_float4(1.f, 1.f, 1.f, 1.f);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                ss = fmaf(u[q].x, u[q].x, fmaf(u[q].y, u[q].y, fmaf(u[q].z, u[q].z, fmaf(u[q].w, u[q].w, ss))));
+                acc = fmaf(u[q].x * w[q].x, v[q].x, acc);
+                acc = fmaf(u[q].y * w[q].y, v[q].y, acc);
+                acc = fmaf(u[q].z * w[q].z, v[q].z, acc);
+                acc = fmaf(u[q].w * w[q].w, v[q].w, acc);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+            ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+        }
+        if (lane == 0) {
+            s_acc[wq] = acc;
+            s_ss[wq] = ss;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const float tot = (s_acc[0] + s_acc[1]) + (s_acc[2] + s_acc[3]);
+            const float sq = (s_ss[0] + s_ss[1]) + (s_ss[2] + s_ss[3]);
+            logits[pair] = norm_w ? tot * rsqrtf(sq / (float)h + eps) : tot;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (trace) t_logits = moe_now();
+        __threadfence();
+        const uint32_t old = atomicAdd(counter, 1u);
+        s_last = old == gridDim.x - 1 ? 1u : 0u;
+        if (s_last) {
+            *counter = 0;
+            __threadfence();
+        }
+        if (trace) t_counted = moe_now();
+    }
+    __syncthreads();
+    if (!s_last) return;
+    route_tokens(logits, rp, T, bias, forced_ids, ids, wts, sm, 0, 4, wq, lane);
+    unsigned long long t_routed = 0;
+    if (trace && threadIdx.x == 0) t_routed = moe_now();
+    if (do_jobs) {
+        __threadfence_block();
+        __syncthreads();
+        build_jobs(ids, T, rp.n_used, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id, js, threadIdx.x,
+                   128u, [] { __syncthreads(); });
+    }
+    if (trace && threadIdx.x == 0) {
+        trace[0] = t_start, trace[1] = t_logits, trace[2] = t_counted, trace[3] = t_routed, trace[4] = moe_now();
     }
 }
 
@@ -330,6 +497,24 @@ cudaError_t launch_moe_jobs(const uint32_t* ids, uint32_t T, uint32_t K, uint32_
     if (E > MAX_EXPERTS) return cudaErrorInvalidValue;
     cudaError_t le3__ = launch_pdl(moe_jobs_kernel, 1, 1024, 0, s, ids, T, K, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id);
     if (le3__ != cudaSuccess) return le3__;
+    return cudaGetLastError();
+}
+
+cudaError_t moe_set_trace(unsigned long long* dev_buf) {
+    return cudaMemcpyToSymbol(g_moe_trace, &dev_buf, sizeof(dev_buf));
+}
+
+cudaError_t launch_moe_route_fused(const float* x, const float* norm_w, float eps, const float* router, uint32_t T,
+                                   uint32_t h, float* logits, const MoeRouteParams& rp, const float* bias,
+                                   const uint32_t* forced_ids, uint32_t* ids, float* wts, bool do_jobs,
+                                   uint32_t rows_per_job, uint32_t* list_token, uint32_t* inv, MoeJob* jobs,
+                                   uint32_t* n_jobs, uint32_t* n_list, int* bad_id, uint32_t* counter, cudaStream_t s) {
+    if (rp.n_expert > MAX_EXPERTS || rp.n_group > 64 || h % 4) return cudaErrorInvalidValue;
+    unsigned grid = T * rp.n_expert;
+    cudaError_t e = launch_pdl(moe_route_fused_kernel, grid, 128, 0, s, x, norm_w, eps, router, T, h, logits, rp, bias,
+                               forced_ids, ids, wts, do_jobs ? 1 : 0, rows_per_job, list_token, inv, jobs, n_jobs,
+                               n_list, bad_id, counter);
+    if (e != cudaSuccess) return e;
     return cudaGetLastError();
 }
 

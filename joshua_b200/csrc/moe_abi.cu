@@ -31,7 +31,7 @@ int32_t reserve(jq_moe* m, uint64_t T, uint64_t P) {
     size_t o_logits = take(T * c.n_expert * 4), o_ids = take(P * 4), o_wts = take(P * 4), o_list = take(P * 4),
            o_inv = take(P * 4), o_jobs = take((P + c.n_expert) * sizeof(jq::MoeJob)), o_nj = take(8),
            o_hidden = take(P * c.inter * 4), o_out = take(P * c.hidden * 4), o_shh = take(T * c.inter * 4 * 3),
-           o_sho = take(T * c.hidden * 4), o_ones = take(P * 4),
+           o_sho = take(T * c.hidden * 4), o_ones = take(P * 4), o_xn = take(T * c.hidden * 4),
            o_px = take(jq::gemv_mma_scratch_bytes(T, c.hidden) + (T * (c.hidden / 32) * 112) + 256),
            o_ph = take(jq::gemv_mma_scratch_bytes(P, c.inter) + (P * (c.inter / 32) * 112) + 256);
     JQ_CUDA(cudaMalloc(&m->ws, off));
@@ -49,6 +49,7 @@ int32_t reserve(jq_moe* m, uint64_t T, uint64_t P) {
     m->sh_hidden = (float*)(b + o_shh);
     m->sh_out = (float*)(b + o_sho);
     m->ones = (float*)(b + o_ones);
+    m->xn = (float*)(b + o_xn);
     m->planes_x = b + o_px;
     m->planes_h = b + o_ph;
     std::vector<float> ones(P, 1.0f);
@@ -62,7 +63,8 @@ bool fits_smem(uint64_t rows, uint64_t k) { return jq::gemv_mma_scratch_bytes(ro
 
 // out_list[pos, :] = MLP_expert(pos)(x[list_token[pos], :]) for the list built by the jobs kernel.
 // R activation rows, P list positions at most.
-int32_t run_experts(jq_moe* m, const float* x, uint64_t R, uint64_t P, uint32_t rows_per_job, cudaStream_t s) {
+int32_t run_experts(jq_moe* m, const float* x, uint64_t R, uint64_t P, uint32_t rows_per_job, cudaStream_t s,
+                    const float* norm_w = nullptr, float eps = 0.0f) {
     const jq_moe_config& c = m->cfg;
     jq::GroupedLaunch g = {};
     g.jobs = m->jobs;
@@ -85,7 +87,10 @@ int32_t run_experts(jq_moe* m, const float* x, uint64_t R, uint64_t P, uint32_t 
     g.dst = m->hidden;
     if (fits_smem(R, c.hidden)) {
         g.planes = nullptr;
+        g.norm_w = norm_w;
+        g.norm_eps = eps;
     } else {
+        if (norm_w) return jq_fail(jq::E_INVALID, "moe: internal: norm requested for rows that do not fit shared memory");
         JQ_CUDA(jq::launch_quantize_acts(g.type, x, R, c.hidden, m->planes_x, s));
         g.planes = m->planes_x;
     }
@@ -102,6 +107,7 @@ int32_t run_experts(jq_moe* m, const float* x, uint64_t R, uint64_t P, uint32_t 
     g.act_rows = nullptr;
     g.dst = m->out;
     g.clamp = 0.0f;
+    g.norm_w = nullptr;
     if (fits_smem(P, c.inter)) {
         g.planes = nullptr;
     } else {
@@ -113,7 +119,15 @@ int32_t run_experts(jq_moe* m, const float* x, uint64_t R, uint64_t P, uint32_t 
 }
 
 // sh_out[T, hidden] = shared expert MLP over all tokens
-int32_t run_shared(jq_moe* m, const float* x, uint64_t T, cudaStream_t s) {
+bool shared_mma_ok(jq_moe* m, uint64_t T) {
+    const jq_moe_config& c = m->cfg;
+    return T <= 8 && !m->ctx->force_f32 &&
+           jq::gemv_mma_supports(m->sh_gate->type, m->sh_gate->dev, c.inter, c.hidden, T) &&
+           jq::gemv_mma_supports(m->sh_down->type, m->sh_down->dev, c.hidden, c.inter, T) &&
+           fits_smem(T, c.hidden) && fits_smem(T, c.inter) && m->sh_gate->type == m->sh_up->type;
+}
+
+int32_t run_shared(jq_moe* m, const float* x, uint64_t T, cudaStream_t s, const float* norm_w = nullptr, float eps = 0.0f) {
     const jq_moe_config& c = m->cfg;
     const bool mma_ok = T <= 8 && !m->ctx->force_f32 &&
                         jq::gemv_mma_supports(m->sh_gate->type, m->sh_gate->dev, c.inter, c.hidden, T) &&
@@ -135,7 +149,10 @@ int32_t run_shared(jq_moe* m, const float* x, uint64_t T, cudaStream_t s) {
         g.x = x;
         g.x_rows = (uint32_t)T;
         g.dst = m->sh_hidden;
+        g.norm_w = norm_w;
+        g.norm_eps = eps;
         JQ_CUDA(jq::launch_gemv_grouped(g, s));
+        g.norm_w = nullptr;
         g.type = m->sh_down->type;
         g.w0 = m->sh_down->dev;
         g.w1 = nullptr;
@@ -239,8 +256,10 @@ int32_t jq_moe_create(jq_ctx* ctx, const jq_moe_config* cfg, const float* router
     uint32_t one = 1;
     if (e == cudaSuccess) e = cudaMalloc(&m->dense_jobs, sizeof(dj));
     if (e == cudaSuccess) e = cudaMemcpy(m->dense_jobs, dj, sizeof(dj), cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = cudaMalloc(&m->one, 4);
+    if (e == cudaSuccess) e = cudaMalloc(&m->one, 256);
+    if (e == cudaSuccess) e = cudaMemset(m->one, 0, 256);
     if (e == cudaSuccess) e = cudaMemcpy(m->one, &one, 4, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) m->counter = m->one + 16;
     if (e == cudaSuccess) e = cudaHostAlloc(&m->bad_host, sizeof(int), cudaHostAllocMapped);
     if (e == cudaSuccess) e = cudaHostGetDevicePointer(&m->bad_dev, m->bad_host, 0);
     if (e != cudaSuccess) {
@@ -280,6 +299,12 @@ int32_t jq_moe_route_dev(jq_moe* m, const float* x_dev, uint64_t T, const uint32
     if (T > m->cap_tokens) return jq_fail(jq::E_TOO_LARGE, "jq_moe_route_dev: call jq_moe_reserve for this many tokens first");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const jq_moe_config& c = m->cfg;
+    if (T <= 8 && c.hidden % 4 == 0) {
+        JQ_CUDA(jq::launch_moe_route_fused(x_dev, nullptr, 0.0f, m->router, (uint32_t)T, c.hidden, m->logits, m->rp,
+                                           m->bias, forced_ids_dev, ids_dev, wts_dev, false, 1, nullptr, nullptr, nullptr,
+                                           nullptr, nullptr, nullptr, m->counter, s));
+        return jq::OK;
+    }
     JQ_CUDA(jq::launch_moe_logits(x_dev, m->router, (uint32_t)T, c.n_expert, c.hidden, m->logits, s));
     JQ_CUDA(jq::launch_moe_route(m->logits, m->rp, (uint32_t)T, m->bias, forced_ids_dev, ids_dev, wts_dev, s));
     return jq::OK;
@@ -307,6 +332,12 @@ int32_t jq_moe_forward_dev(jq_moe* m, const float* x_dev, uint64_t T, const uint
 
 int32_t jq_moe_forward_add_dev(jq_moe* m, const float* x_dev, uint64_t T, const uint32_t* forced_ids_dev,
                                const float* residual_dev, float* y_dev, void* stream) {
+    return jq_moe_forward_norm_add_dev(m, x_dev, T, forced_ids_dev, nullptr, 0.0f, residual_dev, y_dev, stream);
+}
+
+int32_t jq_moe_forward_norm_add_dev(jq_moe* m, const float* x_dev, uint64_t T, const uint32_t* forced_ids_dev,
+                                    const float* norm_w_dev, float eps, const float* residual_dev, float* y_dev,
+                                    void* stream) {
     if (!m) return jq_fail(jq::E_INVALID, "jq_moe_forward_dev: NULL handle");
     if (T == 0) return jq::OK;
     if (!x_dev || !y_dev) return jq_fail(jq::E_INVALID, "jq_moe_forward_dev: NULL buffer");
@@ -316,17 +347,38 @@ int32_t jq_moe_forward_add_dev(jq_moe* m, const float* x_dev, uint64_t T, const 
     if (T > m->cap_tokens || P > m->cap_pairs)
         return jq_fail(jq::E_TOO_LARGE, "jq_moe_forward_dev: call jq_moe_reserve for this many tokens first");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (int32_t rc = jq_moe_route_dev(m, x_dev, T, forced_ids_dev, m->ids, m->wts, stream)) return rc;
-    uint32_t rpj = rows_per_job_for(P, T, c.n_expert);
-    JQ_CUDA(jq::launch_moe_jobs(m->ids, (uint32_t)T, c.n_used, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
-                                m->n_jobs, m->n_list, m->bad_dev, s));
-    if (int32_t rc = run_experts(m, x_dev, T, P, rpj, s)) return rc;
+    const uint32_t rpj = rows_per_job_for(P, T, c.n_expert);
+    // Decode-sized batches: router, routing and job list in one launch, the RMS norm folded into it and into
+    // the expert (and shared-expert) matmuls' activation split.
+    const bool fused = T <= 8 && fits_smem(T, c.hidden) && (!m->sh_gate || shared_mma_ok(m, T));
+    const float* x_in = x_dev;
+    const float* nw = norm_w_dev;
+    if (!fused && norm_w_dev) {
+        JQ_CUDA(jq::launch_rmsnorm(x_dev, nullptr, norm_w_dev, eps, T, c.hidden, nullptr, m->xn, s));
+        x_in = m->xn;
+        nw = nullptr;
+    }
+    if (fused) {
+        JQ_CUDA(jq::launch_moe_route_fused(x_in, nw, eps, m->router, (uint32_t)T, c.hidden, m->logits, m->rp, m->bias,
+                                           forced_ids_dev, m->ids, m->wts, true, rpj, m->list_token, m->inv, m->jobs,
+                                           m->n_jobs, m->n_list, m->bad_dev, m->counter, s));
+    } else {
+        if (int32_t rc = jq_moe_route_dev(m, x_in, T, forced_ids_dev, m->ids, m->wts, stream)) return rc;
+        JQ_CUDA(jq::launch_moe_jobs(m->ids, (uint32_t)T, c.n_used, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
+                                    m->n_jobs, m->n_list, m->bad_dev, s));
+    }
+    if (int32_t rc = run_experts(m, x_in, T, P, rpj, s, nw, eps)) return rc;
     const float* shared = nullptr;
     if (m->sh_gate) {
-        if (int32_t rc = run_shared(m, x_dev, T, s)) return rc;
+        if (int32_t rc = run_shared(m, x_in, T, s, nw, eps)) return rc;
         shared = m->sh_out;
     }
     JQ_CUDA(jq::launch_moe_combine(m->out, m->inv, m->wts, shared, (uint32_t)T, c.n_used, c.hidden, y_dev, s, residual_dev));
+    return jq::OK;
+}
+
+int32_t jq_debug_moe_trace(uint64_t* trace_dev) {
+    JQ_CUDA(jq::moe_set_trace(reinterpret_cast<unsigned long long*>(trace_dev)));
     return jq::OK;
 }
 

@@ -81,16 +81,17 @@ class MoeDecoder(LlamaDecoder):
                 rl.reserve(batch, 0)
                 el.reserve(cap, cap)
                 self.ffn_layers.append(dict(router=rl, experts=el, keep=banks))
-        self.launches_per_step = (4 + (6 if self.world == 1 else 9)) * cfg.layers + 4
+        self.launches_per_step = (3 + (4 if self.world == 1 else 9)) * cfg.layers + 4
 
     def _ffn(self, ly, s) -> None:
         """self.x += MoE(rmsnorm(self.x; ffn_norm)); the residual add rides in the combine kernel."""
         L, c, B, P = _lib.lib(), self.cfg, self.batch, lambda t: t.data_ptr()
         f = self.ffn_layers[self._layer_index[id(ly)]]
-        _lib.check(L.jq_rmsnorm_dev(P(self.x), None, P(ly["ffn_norm"]), c.eps, B, c.hidden, None, P(self.xn), s))
         if "moe" in f:
-            _lib.check(L.jq_moe_forward_add_dev(f["moe"]._h, P(self.xn), B, None, P(self.x), P(self.x), s))
+            _lib.check(L.jq_moe_forward_norm_add_dev(f["moe"]._h, P(self.x), B, None, P(ly["ffn_norm"]), c.eps,
+                                                     P(self.x), P(self.x), s))
         else:
+            _lib.check(L.jq_rmsnorm_dev(P(self.x), None, P(ly["ffn_norm"]), c.eps, B, c.hidden, None, P(self.xn), s))
             self.exchange.forward_dev(f["router"], f["experts"], self.xn, self.x, residual=self.x, stream=s)
 
     def step(self, stream=None) -> None:

@@ -183,3 +183,34 @@ def test_create_rejects_bad_banks():
         Moe(cfg, router, g, g, short)
     with pytest.raises(JoshuaB200Error, match="n_used"):
         Moe(MoeConfig(gating=GATE_SOFTMAX, n_expert=4, n_used=5, hidden=256, inter=256), router, g, g, g)
+
+
+@pytest.mark.parametrize("T", [1, 4, 8, 12])
+@pytest.mark.parametrize("shared", [False, True])
+def test_forward_with_norm_and_residual_folded_in(T, shared):
+    """y = residual + layer(rmsnorm(x)) in place, against the separate norm kernel + plain layer + add; T <= 8
+    takes the four-launch decode path (router, routing and jobs in one kernel), T = 12 the general one."""
+    import torch
+
+    from joshua_b200 import _lib
+
+    cfg = MoeConfig(gating=GATE_SOFTMAX, n_expert=16, n_used=4, hidden=512, inter=256, norm=True)
+    moe, router, banks, types, _ = build(cfg, synth.Q4_K, seed=51, shared_type=synth.Q8_0 if shared else None)
+    moe.reserve(T, T * cfg.n_used)
+    g = torch.Generator(device="cuda").manual_seed(T)
+    x = torch.randn(T, cfg.hidden, device="cuda", generator=g)
+    nw = 0.02 * (1.0 + 0.1 * torch.randn(cfg.hidden, device="cuda", generator=g))   # keeps expert outputs O(1)
+    L, s = _lib.lib(), torch.cuda.current_stream().cuda_stream
+    xn = torch.empty_like(x)
+    _lib.check(L.jq_rmsnorm_dev(x.data_ptr(), None, nw.data_ptr(), 1e-6, T, cfg.hidden, None, xn.data_ptr(), s))
+    want = torch.empty_like(x)
+    moe.forward_dev(xn, want)
+    want += x
+    got = x.clone()
+    for _ in range(2):   # twice: the router kernel's arrival counter must come back to zero
+        got.copy_(x)
+        _lib.check(L.jq_moe_forward_norm_add_dev(moe._h, got.data_ptr(), T, None, nw.data_ptr(), 1e-6, got.data_ptr(),
+                                                 got.data_ptr(), s))
+    torch.cuda.synchronize()
+    moe.status()
+    assert float((got - want).abs().max()) <= 1e-4 * max(1.0, float(want.abs().max()))
