@@ -1,7 +1,7 @@
 // Prefill / batched matmul (m > 8) over raw GGUF blocks on the 5th-generation tensor cores.
 //
 // dst[m, n] = lhs[m, k] . W[n, k]^T with W left in its GGUF bytes.  A CTA owns a 128-row tile of W and a tile
-// of up to 128 activation rows.  Per 32-column K step its converter warps decode the 128 x 32 weight block to
+// of up to 256 activation rows (the wider the tile, the fewer times a weight is decoded).  Per 32-column K step its converter warps decode the 128 x 32 weight block to
 // the exact f32 weights the reference forms (formats.cuh), split weights and activations into two TF32 terms
 // (hi = top 11 significant bits, lo = the exact remainder), and store both terms K-major in the 128-byte
 // swizzled layout the tensor core reads.  One thread issues tcgen05.mma (kind::tf32) for the three
@@ -32,7 +32,7 @@ namespace {
 constexpr int TC_M = 128;          // weight rows per CTA = MMA M = TMEM lanes
 constexpr int TC_K = 32;           // K per stage: 32 tf32 = one 128-byte swizzled row
 constexpr int TC_CHUNK = 4;        // K steps accumulated in tensor memory before a read-back
-constexpr int TC_CONV_WARPS = 8;   // converter / epilogue warps
+constexpr int TC_CONV_WARPS = 16;  // converter / epilogue warps: 4 per quarter of the accumulator's lanes
 constexpr int TC_THREADS = (TC_CONV_WARPS + 1) * 32;
 constexpr uint32_t PLANE_A = TC_M * 128;  // bytes of one term of the weight tile
 
@@ -105,6 +105,24 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t r[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t r[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32"
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t r[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32"
+        "{%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 // Split 4 floats into their TF32 hi parts and exact remainders and store both 16-byte chunks.  `row_base`
 // is the byte offset of the row inside a term's tile; `chunk` the 16-byte chunk inside the 128-byte row.
 __device__ __forceinline__ void store_split(uint8_t* hi_tile, uint8_t* lo_tile, uint32_t row, uint32_t chunk,
@@ -167,17 +185,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     const uint32_t tmem_d = tmem_base_slot;
 
     if (warp < TC_CONV_WARPS) {
-        // ── converters: weight rows and activation rows -> two TF32 terms each; between chunks they read the
-        // finished accumulator back.  Warp q of each group of four reads TMEM lanes 32q .. 32q+31 (its weight
-        // rows); the two groups split the columns (tokens). ──
-        const uint32_t r = tid & 127, half = tid >> 7;  // row of the tile, half of the K step
+        // ── converters: per K step thread (r, unit) decodes 8 weights of row r, and the 512 threads split the
+        // N_TILE x 32 activation block between them (16-byte pieces, 8 consecutive threads per 128-byte row).
+        // Between chunks they read the finished accumulator back: warp w reads TMEM lanes 32 (w % 4) .. + 31
+        // (its weight rows) and the quarter w / 4 of the columns (tokens). ──
+        const uint32_t r = tid & 127, unit = tid >> 7;  // weight row of the tile, 8-value unit of the K step
         const uint64_t wrow = row0 + r < n ? row0 + r : n - 1;
         const uint8_t* wr = w + wrow * row_bytes;
-        const bool tok_live = r < N_TILE;
-        const bool tok_real = tok_live && tok0 + r < m;
-        const float* xr = lhs + (tok0 + (tok_real ? r : 0)) * k;
+        constexpr int B_PER = (N_TILE * 8 + TC_CONV_WARPS * 32 - 1) / (TC_CONV_WARPS * 32);  // 16-byte pieces per thread
+        const uint32_t brow0 = tid >> 3, bchunk = tid & 7;
         const uint32_t q = warp & 3, grp = warp >> 2;
-        constexpr int MY_COLS = N_TILE >= 64 ? N_TILE / 2 : 32;  // columns this thread accumulates
+        constexpr int MY_COLS = N_TILE / 4;  // columns this thread accumulates
         float sums[MY_COLS];
 #pragma unroll
         for (int c = 0; c < MY_COLS; ++c) sums[c] = 0.0f;
@@ -186,12 +204,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             const uint32_t buf = c & 1;
             if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[buf], (c >> 1) & 1))) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (N_TILE >= 64 || grp == 0) {
+            const uint32_t taddr = tmem_d + ((q * 32) << 16) + buf * N_TILE + grp * MY_COLS;
+            if constexpr (MY_COLS == 8) {
+                uint32_t rr[8];
+                tmem_ld8(taddr, rr);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sums[i] += __uint_as_float(rr[i]);
+            } else if constexpr (MY_COLS == 16) {
+                uint32_t rr[16];
+                tmem_ld16(taddr, rr);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) sums[i] += __uint_as_float(rr[i]);
+            } else {
 #pragma unroll
                 for (int part = 0; part < MY_COLS / 32; ++part) {
                     uint32_t rr[32];
-                    const uint32_t col = (N_TILE >= 64 ? grp * MY_COLS : 0) + part * 32;
-                    tmem_ld32(tmem_d + ((q * 32) << 16) + buf * N_TILE + col, rr);
+                    tmem_ld32(taddr + part * 32, rr);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) sums[part * 32 + i] += __uint_as_float(rr[i]);
                 }
@@ -201,30 +229,42 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
             return true;
         };
+        // this thread's activation pieces of K step ks (requested one step ahead of their use)
+        float4 xb[B_PER];
+        auto load_b = [&](uint32_t ks) {
+#pragma unroll
+            for (int j = 0; j < B_PER; ++j) {
+                const uint32_t br = brow0 + j * (TC_CONV_WARPS * 4);
+                const bool real = br < N_TILE && tok0 + br < m;
+                xb[j] = real ? __ldg(reinterpret_cast<const float4*>(lhs + (tok0 + br) * k + (uint64_t)ks * TC_K + bchunk * 4))
+                             : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        };
         bool ok = true;
         uint32_t drained = 0;
+        load_b(0);
         for (uint32_t ks = 0; ks < k_steps && ok; ++ks) {
             const uint32_t s = ks % n_stages, round = ks / n_stages;
+            // decode before waiting for the stage: the global loads overlap the wait
+            float v[8];
+            {
+                const uint32_t u = ks * 4 + unit;  // 8-value unit of the row
+                decode_unit<TYPE>(wr + (uint64_t)(u / UPB) * BYTES, u % UPB, v, false);
+            }
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(&empty[s], (round & 1) ^ 1));  // warp-uniform
             if (!ok) break;
             uint8_t* st = smem + (size_t)s * STAGE;
+            store_split(st, st + PLANE_A, r, unit * 2, v);
+            store_split(st, st + PLANE_A, r, unit * 2 + 1, v + 4);
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const uint32_t u = ks * 4 + half * 2 + j;  // 8-value unit of the row
-                float v[8];
-                decode_unit<TYPE>(wr + (uint64_t)(u / UPB) * BYTES, u % UPB, v, false);
-                store_split(st, st + PLANE_A, r, (half * 2 + j) * 2, v);
-                store_split(st, st + PLANE_A, r, (half * 2 + j) * 2 + 1, v + 4);
-            }
-            if (tok_live) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float4 x4 = tok_real ? __ldg(reinterpret_cast<const float4*>(xr + ks * TC_K + half * 16 + j * 4))
-                                         : make_float4(0.f, 0.f, 0.f, 0.f);
-                    float v[4] = {x4.x, x4.y, x4.z, x4.w};
-                    store_split(st + 2 * PLANE_A, st + 2 * PLANE_A + PLANE_B, r, half * 4 + j, v);
+            for (int j = 0; j < B_PER; ++j) {
+                const uint32_t br = brow0 + j * (TC_CONV_WARPS * 4);
+                if (br < N_TILE) {
+                    float bv[4] = {xb[j].x, xb[j].y, xb[j].z, xb[j].w};
+                    store_split(st + 2 * PLANE_A, st + 2 * PLANE_A + PLANE_B, br, bchunk, bv);
                 }
             }
+            if (ks + 1 < k_steps) load_b(ks + 1);
             // make the generic-proxy stores visible to the tensor core's async proxy, then hand over
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
@@ -237,13 +277,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         if (!ok) abort_flag = 1;
         if (ok) {
             const uint64_t out_row = row0 + q * 32 + lane;
-            if (N_TILE >= 64 || grp == 0) {
 #pragma unroll
-                for (int c = 0; c < MY_COLS; ++c) {
-                    const uint32_t col = (N_TILE >= 64 ? grp * MY_COLS : 0) + c;
-                    const uint64_t tok = tok0 + col;
-                    if (tok < m && out_row < n) dst[tok * n + out_row] = sums[c];
-                }
+            for (int c = 0; c < MY_COLS; ++c) {
+                const uint64_t tok = tok0 + grp * MY_COLS + c;
+                if (tok < m && out_row < n) dst[tok * n + out_row] = sums[c];
             }
         }
     } else {
@@ -292,12 +329,12 @@ template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE>
 cudaError_t launch_tile(const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m, float* dst,
                         int* error_flag, cudaStream_t s) {
     constexpr uint32_t STAGE = 2 * PLANE_A + 2 * N_TILE * 128;
-    uint32_t n_stages = std::min<uint32_t>(8, std::min<uint32_t>((uint32_t)(k / TC_K), (200 * 1024) / STAGE));
+    uint32_t n_stages = std::min<uint32_t>(8, std::min<uint32_t>((uint32_t)(k / TC_K), (216 * 1024) / STAGE));
     size_t smem = (size_t)n_stages * STAGE + 1024;
     auto kern = gemm_tc_kernel<TYPE, ELEMS, BYTES, N_TILE>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
         if (e != cudaSuccess) return e;
         configured = true;
     }
@@ -311,7 +348,11 @@ cudaError_t launch_type(const uint8_t* w, uint64_t n, uint64_t k, const float* l
                         int* error_flag, cudaStream_t s) {
     if (m <= 32) return launch_tile<TYPE, ELEMS, BYTES, 32>(w, n, k, lhs, m, dst, error_flag, s);
     if (m <= 64) return launch_tile<TYPE, ELEMS, BYTES, 64>(w, n, k, lhs, m, dst, error_flag, s);
-    return launch_tile<TYPE, ELEMS, BYTES, 128>(w, n, k, lhs, m, dst, error_flag, s);
+    if (m <= 128) return launch_tile<TYPE, ELEMS, BYTES, 128>(w, n, k, lhs, m, dst, error_flag, s);
+    // 256-token tiles decode every weight half as often, but only pay off once they still fill the SMs
+    const uint64_t ctas256 = ((n + TC_M - 1) / TC_M) * ((m + 255) / 256);
+    if (ctas256 < 148) return launch_tile<TYPE, ELEMS, BYTES, 128>(w, n, k, lhs, m, dst, error_flag, s);
+    return launch_tile<TYPE, ELEMS, BYTES, 256>(w, n, k, lhs, m, dst, error_flag, s);
 }
 
 }  // namespace

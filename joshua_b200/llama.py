@@ -208,6 +208,40 @@ class LlamaDecoder:
                                  (c.hidden + c.ffn) + (c.ffn + c.hidden)) + 4 * B * (c.hidden + c.vocab)
         return self.weight_bytes + io
 
+    # ── the model-level call with host buffers ──────────────────────────
+    def forward_host(self, token_ids, out_logits=None):
+        """`ModelWeights::forward(input_ids, index_pos) -> logits` for one new token per sequence with HOST
+        buffers on both sides (the shape of the reference's model call, src/model.rs:362-364): the token ids
+        are copied to the device from pinned memory, the step runs (a CUDA graph captured on first use), the
+        logits are copied back to pinned memory and the call returns when they have arrived.  Positions
+        advance by one per call; `reset` starts a new sequence."""
+        torch = self.torch
+        if getattr(self, "_host", None) is None:
+            stream = torch.cuda.Stream(self.dev)
+            tok_pin = torch.empty(self.batch, dtype=torch.int32).pin_memory()
+            log_pin = torch.empty(self.batch, self.cfg.vocab, dtype=torch.float32).pin_memory()
+            with torch.cuda.stream(stream):
+                pos0 = self.pos.clone()
+                self.step(stream.cuda_stream)      # warm-up outside the capture (scratch allocation)
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    self.step(stream.cuda_stream)
+                self.pos.copy_(pos0)
+                stream.synchronize()
+            self._host = (stream, tok_pin, log_pin, graph)
+        stream, tok_pin, log_pin, graph = self._host
+        tok_pin.copy_(torch.as_tensor(token_ids, dtype=torch.int32).reshape(self.batch))
+        with torch.cuda.stream(stream):
+            self.token.copy_(tok_pin, non_blocking=True)
+            graph.replay()
+            log_pin.copy_(self.logits, non_blocking=True)
+            stream.synchronize()
+        if out_logits is not None:
+            out_logits[...] = log_pin.numpy()
+            return out_logits
+        return log_pin.numpy()
+
     def reset(self, token: int = 42) -> None:
         self.token.fill_(token)
         self.pos.zero_()

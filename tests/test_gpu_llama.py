@@ -205,3 +205,24 @@ def test_chain_step_matches_separate_launches(batch, wtype):
     from joshua_b200.qtensor import default_context
     from joshua_b200 import _lib
     _lib.check(_lib.lib().jq_device_status(default_context(0)._h))
+
+
+def test_forward_host_matches_device_steps():
+    """The model-level call with host buffers (token ids in, logits out) against the device-resident step."""
+    import torch
+
+    cfg = LlamaConfig(layers=2, hidden=512, q_heads=8, kv_heads=2, head_dim=64, ffn=768, vocab=700)
+    mk = _small_weights(synth.Q4_K)
+    a = LlamaDecoder(cfg, torch.device("cuda", 0), batch=2, max_ctx=32, seed=9, weights=mk)
+    b = LlamaDecoder(cfg, torch.device("cuda", 0), batch=2, max_ctx=32, seed=9, weights=mk)
+    a.reset(3)
+    b.reset(3)
+    tok = np.array([3, 3], np.int32)
+    for step in range(10):
+        logits = a.forward_host(tok).copy()
+        b.token.copy_(torch.from_numpy(tok).cuda())
+        b.step()
+        torch.cuda.synchronize()
+        assert np.array_equal(logits, b.logits.cpu().numpy()), step
+        tok = logits.argmax(axis=1).astype(np.int32)
+    assert a.pos.tolist() == [10, 10]
