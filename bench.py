@@ -150,12 +150,66 @@ def cpu_llama_sample(seconds_budget: float = 15.0):
             "gbs": sample_bytes / dt / 1e9}
 
 
+def cpu_moe_sample(cfg, seconds_budget: float = 12.0):
+    """Times the oracle on one Qwen3-MoE-shaped layer at batch 1: the Q8_0 attention projections, the f32
+    router product and the eight routed experts' Q4_K matmuls, scaled to a token by the layer count plus the
+    output head (same kernels, scaled by bytes)."""
+    import oracle
+
+    h, inter = cfg.hidden, cfg.moe_inter
+    shapes = [(synth.Q8_0, cfg.qkv_rows, h), (synth.Q8_0, h, cfg.q_heads * cfg.head_dim)]
+    for _ in range(cfg.n_used):
+        shapes += [(synth.Q4_K, inter, h), (synth.Q4_K, inter, h), (synth.Q4_K, h, inter)]
+    weights = [synth.random_weight(t, n, k, seed=i) for i, (t, n, k) in enumerate(shapes)]
+    acts = {k: synth.random_activations(1, k, seed=k) for k in {s[2] for s in shapes}}
+    router = np.random.default_rng(0).standard_normal((cfg.n_expert, h)).astype(np.float32)
+    layer_bytes = sum(w.size for w in weights)
+    head_bytes = synth.tensor_bytes(synth.Q8_0, cfg.vocab, h)
+
+    def one_layer():
+        for w, (t, n, k) in zip(weights, shapes):
+            oracle.matmul_t(t, (1, k, n), acts[k], w)
+        router @ acts[h][0]
+
+    one_layer()
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        one_layer()
+        reps += 1
+        if time.perf_counter() - t0 > seconds_budget or reps >= 400:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    tok_s = 1.0 / (dt * (cfg.layers + head_bytes / layer_bytes))
+    return {"value": tok_s, "unit": "tok/s", "cores": oracle.threads(), "kind": "port",
+            "sample": f"one layer at batch 1 (2 Q8_0 attention linears, router, {cfg.n_used} experts x 3 Q4_K matmuls, "
+                      f"{layer_bytes / 1e6:.0f} MB), {reps} passes, scaled by layers + head bytes"}
+
+
 def run_reference(args):
     """`--impl reference`: the reference's CPU kernels (C++ oracle port) on this host, all cores."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     t0 = time.perf_counter()
+    if args.workload == "qwen3moe":
+        from joshua_b200.moe_decoder import MoeDecoderConfig
+
+        cfg = MoeDecoderConfig()
+        base = cpu_moe_sample(cfg, seconds_budget=max(5.0, min(60.0, 2.0 * (args.steps + args.warmup))))
+        line = {
+            "impl": "reference", "metric": "decode_tok_s", "value": base["value"], "unit": "tok/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 / base["value"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"qwen3moe_decode_b{args.batch}", "layers": cfg.layers, "hidden": cfg.hidden,
+                       "n_expert": cfg.n_expert, "n_used": cfg.n_used, "moe_inter": cfg.moe_inter},
+            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
+        }
+        print(json.dumps(line))
+        return
     base = cpu_llama_sample(seconds_budget=max(5.0, min(60.0, 2.0 * (args.steps + args.warmup))))
     line = {
         "impl": "reference", "metric": "decode_tok_s", "value": base["value"], "unit": "tok/s",

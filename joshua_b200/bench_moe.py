@@ -20,7 +20,11 @@ def run(args):
     import torch
     import torch.distributed as dist
 
-    from bench import ClockSampler, measured_peaks
+    import time
+
+    import numpy as np
+
+    from bench import ClockSampler, cpu_moe_sample, measured_peaks
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -41,7 +45,7 @@ def run(args):
     cfg = MoeDecoderConfig()
     batch = args.batch
     prefill = min(args.prefill, 128)
-    max_ctx = prefill + 2 * (warmup + args.steps) + 16
+    max_ctx = prefill + 3 * (warmup + args.steps) + 24
     model = MoeDecoder(cfg, dev, batch=batch, max_ctx=max_ctx, seed=rank, group=group)
     stream = torch.cuda.Stream()
     graph = None
@@ -91,6 +95,22 @@ def run(args):
         tmax = torch.tensor([dt], device=dev, dtype=torch.float64)
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         dt = float(tmax.item())
+    # end to end, model level: host token ids in, host logits out, every step (every rank does its own copies)
+    tok = np.full(batch, 42, np.int32)
+    for _ in range(3):
+        model.forward_host(tok)
+    torch.cuda.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        logits_host = model.forward_host(tok)
+        tok = logits_host.argmax(axis=1).astype(np.int32)
+    e2e_dt = (time.perf_counter() - t0) / args.steps
+    if world > 1:
+        tmax = torch.tensor([e2e_dt], device=dev, dtype=torch.float64)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        e2e_dt = float(tmax.item())
+    assert int(model.pos.max().item()) < max_ctx
     if rank == 0:
         peak, which = measured_peaks()
         # bytes one rank's step must read: attention weights + head once, expert banks once per distinct expert
@@ -113,8 +133,19 @@ def run(args):
                          "frac": alg / dt / 1e9 / peak, "traffic": None, "peak_source": which,
                          "note": "whole step (all kernels) over the weight bytes one rank must read, upper bound "
                                  "on distinct experts"},
+            "e2e": {"value": world * batch / e2e_dt, "unit": "tok/s", "h2d_bytes_per_step": 4 * batch * world,
+                    "d2h_bytes_per_step": 4 * batch * cfg.vocab * world,
+                    "how": "model-level call with host buffers on every rank (forward_host): token ids host->device, "
+                           "one decode step, logits device->host, the host picks the next token; wall clock, max "
+                           "over ranks"},
             "gpu_launches": model.launches_per_step * args.steps, "clocks": clocks.summary(),
         }
+        if world == 1:
+            try:
+                base = cpu_moe_sample(cfg, seconds_budget=10.0)
+                line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            except Exception as exc:  # the oracle is test infrastructure; the line stands without it
+                line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": 0, "kind": "port", "sample": repr(exc)}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -36,6 +36,7 @@
 //
 // Algorithmic bytes per launch: n*k/B*S (weights) + 4*m*(k + n).
 #include <algorithm>
+#include <cstdlib>
 
 #include "chain.cuh"
 #include "common.cuh"
@@ -1070,6 +1071,230 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1) gemv_mma_kernel(const __gri
     }
 }
 
+// ───────────────────────── narrow-K grouped variant ───────────────────────
+//
+// Expert matrices are small: with k = 768 a row is three units, so in the kernel above three consumer warps
+// would work and thirteen would wait.  Here a ring stage holds T = NCW / units_per_row consecutive 16-row
+// tiles of one job, whole rows at a time, and consumer warp c takes unit c % units_per_row of tile
+// c / units_per_row, so (almost) every warp has a unit.  A stage is a complete product for its T tiles: the
+// partial sums go to the reducer after every stage, which adds each tile's units_per_row partials in unit
+// order.  Grouped (job list) launches only, 2 <= units_per_row <= 8.
+template <uint32_t TYPE, int MB, int NH, int ACT>
+__global__ void __launch_bounds__((16 + 2) * 32, 1) gemv_narrow_kernel(const __grid_constant__ GemvArgs ga) {
+    using Tr = Traits<TYPE>;
+    constexpr int NCW = 16;
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int NB = MB * NH;
+    constexpr uint32_t RED_FLOATS = NCW * NB * ROWS;
+    const SmemPlan& plan = ga.plan;
+    const uint64_t n = ga.n, k = ga.k;
+    const uint32_t upr = (uint32_t)(k / 256);        // units per row = consumer warps per tile
+    const uint32_t T = NCW / upr;                    // tiles per stage
+    const uint32_t stage_bytes = T * ROWS * plan.row_stride;
+    uint8_t* s_act = smem;
+    uint8_t* ring = smem + plan.act_bytes;
+    uint2* s_grid = reinterpret_cast<uint2*>(ring + plan.n_stages * stage_bytes);
+    uint2* s_mask = s_grid + (TYPE == T_IQ2_XXS ? 256 : 0);
+    float* s_red = reinterpret_cast<float*>(s_mask + (TYPE == T_IQ2_XXS ? 128 : 0));
+    uint64_t* full = reinterpret_cast<uint64_t*>(s_red + 2 * RED_FLOATS);
+    uint64_t* empty = full + plan.n_stages;
+    uint64_t* red_full = empty + plan.n_stages;
+    uint64_t* red_empty = red_full + 2;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t NS = plan.n_stages;
+    const uint32_t tiles_per_expert = (uint32_t)((n + ROWS - 1) / ROWS);
+    const uint32_t st_per_expert = (tiles_per_expert + T - 1) / T;
+    const uint64_t row_bytes = (uint64_t)upr * Tr::UNIT_BYTES;
+    const bool swiglu = ga.swiglu != 0;
+    const uint32_t n_sub = swiglu ? 2 : 1;
+    const uint32_t n_groups = (uint32_t)(k / 32);
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < NS; ++s) {
+            mbar_init(&full[s], ROWS);
+            mbar_init(&empty[s], NCW);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&red_full[b], NCW);
+            mbar_init(&red_empty[b], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (TYPE == T_IQ2_XXS) {
+        for (int i = tid; i < 256; i += (NCW + 2) * 32) s_grid[i] = g_iq2xxs_grid[i];
+        for (int i = tid; i < 128; i += (NCW + 2) * 32) {
+            uint32_t sg = iq2_signs(i);
+            uint32_t lo = ((sg & 0xF) * 0x00204081u) & 0x01010101u, hi = ((sg >> 4) * 0x00204081u) & 0x01010101u;
+            s_mask[i] = make_uint2(lo * 0xFFu, hi * 0xFFu);
+        }
+    }
+    __syncthreads();
+    pdl_trigger();
+    pdl_wait();  // the job list comes from the kernel before this one
+    if (ACT && warp != 0) {
+        __shared__ float s_tmp[(NCW + 1) * GEMV_MMA_MAX_M];
+        split_activations<false, NCW + 1>(ga.x, ga.x_rows, (uint32_t)k, ga.norm_w, ga.norm_eps, TYPE, s_act, warp - 1,
+                                          lane, s_tmp);
+    }
+    const uint32_t n_st = __ldg(ga.n_jobs) * st_per_expert;
+    const uint32_t rb16 = (uint32_t)(row_bytes & 15), eb16 = (uint32_t)(ga.expert_bytes & 15);
+    auto shift_of = [&](uint32_t sub, uint32_t e, uint32_t row) -> uint32_t {
+        return ((uint32_t)(reinterpret_cast<uintptr_t>(ga.w[sub]) & 15) + e * eb16 + row * rb16) & 15;
+    };
+
+    if (warp == 0) {
+        // ── producer: lane l copies row l of each of the stage's tiles ──
+        if (lane < ROWS) {
+            uint32_t job = 0;
+            for (uint32_t st = blockIdx.x; st < n_st; st += gridDim.x) {
+                const uint32_t j = st / st_per_expert, rt0 = (st - j * st_per_expert) * T;
+                const MoeJob jd = ga.jobs[j];
+                const uint32_t nt = min(T, tiles_per_expert - rt0);
+                for (uint32_t sub = 0; sub < n_sub; ++sub, ++job) {
+                    const uint32_t s = job % NS, round = job / NS;
+                    if (!mbar_wait(&empty[s], (round & 1) ^ 1)) {
+                        *reinterpret_cast<volatile int*>(ga.error_flag) = 1;
+                        return;
+                    }
+                    const uint8_t* wbase = ga.w[sub] + (uint64_t)jd.expert * ga.expert_bytes;
+                    uint32_t total = 0;
+                    for (uint32_t ti = 0; ti < nt; ++ti) {
+                        uint64_t row = (uint64_t)(rt0 + ti) * ROWS + lane;
+                        row = row < n ? row : n - 1;
+                        uintptr_t beg = reinterpret_cast<uintptr_t>(wbase + row * row_bytes), end = beg + row_bytes;
+                        total += (uint32_t)(((end + 15) & ~(uintptr_t)15) - (beg & ~(uintptr_t)15));
+                    }
+                    mbar_arrive_expect_tx(&full[s], total);
+                    for (uint32_t ti = 0; ti < nt; ++ti) {
+                        uint64_t row = (uint64_t)(rt0 + ti) * ROWS + lane;
+                        row = row < n ? row : n - 1;
+                        uintptr_t beg = reinterpret_cast<uintptr_t>(wbase + row * row_bytes), end = beg + row_bytes;
+                        uintptr_t abeg = beg & ~(uintptr_t)15, aend = (end + 15) & ~(uintptr_t)15;
+                        bulk_g2s(ring + s * stage_bytes + (ti * ROWS + lane) * plan.row_stride,
+                                 reinterpret_cast<const void*>(abeg), (uint32_t)(aend - abeg), &full[s]);
+                    }
+                }
+            }
+        }
+    } else if (warp <= NCW) {
+        // ── consumers: warp c -> (tile c / upr of the stage, unit c % upr) ──
+        const uint32_t cw = warp - 1, ti = cw / upr, u = cw - ti * upr;
+        Roles<MB, NH> ro(lane);
+        if (TYPE == T_Q4_K && MB == 1) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+                if (ro.col_p[j] & 1) ro.col_w[j] *= 0.0625f;
+        }
+        ActPlanes a = ga.act;
+        if (ACT) {
+            const uint64_t groups = (uint64_t)ga.x_rows * n_groups;
+            a.planes = reinterpret_cast<const int8_t*>(s_act);
+            a.meta = reinterpret_cast<const float2*>(s_act + groups * 96);
+            a.sum16 = reinterpret_cast<const float*>(s_act + groups * 104);
+        }
+        a.n_groups = n_groups;
+        float colacc[NH][2][2], minacc[NB][2];
+        uint32_t job = 0;
+        for (uint32_t st = blockIdx.x; st < n_st; st += gridDim.x) {
+            const uint32_t j = st / st_per_expert, rt0 = (st - j * st_per_expert) * T;
+            const MoeJob jd = ga.jobs[j];
+            const uint32_t nt = min(T, tiles_per_expert - rt0);
+            const bool active = ti < nt;
+            ro.set_rows(jd.row0, jd.cnt, ga.act_rows, n_groups);
+            const uint64_t row0 = (uint64_t)(rt0 + ti) * ROWS;
+            for (uint32_t sub = 0; sub < n_sub; ++sub, ++job) {
+#pragma unroll
+                for (int h = 0; h < NH; ++h)
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj) colacc[h][jj][0] = colacc[h][jj][1] = 0.0f;
+#pragma unroll
+                for (int b = 0; b < NB; ++b) minacc[b][0] = minacc[b][1] = 0.0f;
+                const uint32_t s = job % NS, round = job / NS;
+                if (!mbar_wait(&full[s], round & 1)) {
+                    if (lane == 0) *reinterpret_cast<volatile int*>(ga.error_flag) = 1;
+                    return;
+                }
+                if (active) {
+                    const uint32_t r0c = (uint32_t)min(row0 + ro.g, n - 1), r1c = (uint32_t)min(row0 + ro.g + 8, n - 1);
+                    const uint32_t sh0 = shift_of(sub, jd.expert, r0c), sh1 = shift_of(sub, jd.expert, r1c);
+                    const uint8_t* sp = ring + s * stage_bytes + ti * ROWS * plan.row_stride;
+                    const uint8_t* u0 = sp + ro.g * plan.row_stride + sh0 + u * Tr::UNIT_BYTES;
+                    const uint8_t* u1 = sp + (ro.g + 8) * plan.row_stride + sh1 + u * Tr::UNIT_BYTES;
+                    process_unit<TYPE, MB, NH, ACT>(u0, u1, u, a, ro, s_grid, s_mask, colacc, minacc);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+                const uint32_t rb = job & 1;
+                if (!mbar_wait(&red_empty[rb], ((job >> 1) & 1) ^ 1)) {
+                    if (lane == 0) *reinterpret_cast<volatile int*>(ga.error_flag) = 1;
+                    return;
+                }
+                float* red = s_red + rb * RED_FLOATS;
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    const int h = b / MB, i = b % MB;
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        float v = -minacc[b][r];
+#pragma unroll
+                        for (int jj = 0; jj < 2; ++jj) v += ro.col_i[jj] == i ? colacc[h][jj][r] : 0.0f;
+                        v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+                        v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
+                        if (ro.t == 0) red[(cw * NB + b) * ROWS + ro.g + 8 * r] = active ? v : 0.0f;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&red_full[rb]);
+            }
+        }
+    } else {
+        // ── reducer: per stage, each tile's partials in unit order ──
+        constexpr int PER_LANE = (8 * NB * ROWS + 31) / 32;  // T <= 8
+        float gate[PER_LANE];
+        uint32_t job = 0;
+        for (uint32_t st = blockIdx.x; st < n_st; st += gridDim.x) {
+            const uint32_t j = st / st_per_expert, rt0 = (st - j * st_per_expert) * T;
+            const MoeJob jd = ga.jobs[j];
+            const uint32_t nt = min(T, tiles_per_expert - rt0);
+            for (uint32_t sub = 0; sub < n_sub; ++sub, ++job) {
+                const uint32_t rb = job & 1;
+                if (!mbar_wait(&red_full[rb], (job >> 1) & 1)) {
+                    if (lane == 0) *reinterpret_cast<volatile int*>(ga.error_flag) = 1;
+                    return;
+                }
+                const float* red = s_red + rb * RED_FLOATS;
+#pragma unroll
+                for (int q = 0; q < PER_LANE; ++q) {
+                    const uint32_t o = lane + 32 * q;
+                    if (o < T * NB * ROWS) {
+                        const uint32_t tt = o / (NB * ROWS), rem = o - tt * (NB * ROWS);
+                        const uint32_t b = rem / ROWS, r = rem - b * ROWS;
+                        float v = 0.0f;
+                        for (uint32_t uu = 0; uu < upr; ++uu) v += red[((tt * upr + uu) * NB + b) * ROWS + r];
+                        const uint64_t orow = (uint64_t)(rt0 + tt) * ROWS + r;
+                        if (swiglu && sub == 0) {
+                            gate[q] = v;
+                        } else if (tt < nt && b < jd.cnt && orow < n) {
+                            if (swiglu) {
+                                float gv = gate[q], uv = v;
+                                if (ga.clamp > 0.0f) {
+                                    gv = fminf(gv, ga.clamp);
+                                    uv = fmaxf(-ga.clamp, fminf(uv, ga.clamp));
+                                }
+                                v = silu_f(gv) * uv;
+                            }
+                            ga.dst[(uint64_t)(jd.row0 + b) * n + orow] = v;
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&red_empty[rb]);
+            }
+        }
+    }
+}
+
 // ───────────────────────────── persistent chain ───────────────────────────
 //
 // A whole sequence of dependent decode operations in ONE launch: quantized linears (with the RMS-norm
@@ -1630,6 +1855,81 @@ cudaError_t launch_gemv_mma_static(uint32_t type, const uint8_t* w, uint64_t n, 
     return launch_typed<0, 0>(type, ga, (uint32_t)m, (n + ROWS - 1) / ROWS, s);
 }
 
+// ── narrow-K grouped launch ─────────────────────────────────────────────────────────────────────────
+namespace {
+
+template <uint32_t TYPE, int MB, int NH, int ACT>
+cudaError_t launch_narrow_variant(GemvArgs& ga, uint32_t max_jobs, cudaStream_t s) {
+    using Tr = Traits<TYPE>;
+    constexpr int NCW = 16;
+    if (g_num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const uint32_t upr = (uint32_t)(ga.k / 256), T = NCW / upr;
+    const uint32_t tiles = (uint32_t)((ga.n + ROWS - 1) / ROWS), spe = (tiles + T - 1) / T;
+    const uint64_t n_st = (uint64_t)max_jobs * spe;
+    SmemPlan p;
+    p.row_stride = row_stride_for<TYPE>(ga.k);
+    const uint32_t fixed = (TYPE == T_IQ2_XXS ? (256 + 128) * 8 : 0) + 2 * NCW * MB * NH * ROWS * 4 + 8 * (2 * 8 + 4) + 128;
+    p.act_bytes = ACT ? (uint32_t)((uint64_t)ga.x_rows * (ga.k / 32) * 112) : 0;
+    const uint32_t stage = T * ROWS * p.row_stride;
+    if (fixed + p.act_bytes + stage > SMEM_BUDGET) return cudaErrorInvalidValue;
+    unsigned grid = (unsigned)std::max<uint64_t>(1, std::min<uint64_t>(n_st, (uint64_t)g_num_sms));
+    const uint64_t per_cta = (n_st + grid - 1) / grid * (ga.swiglu ? 2 : 1);
+    p.n_stages = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>({(uint64_t)8, (uint64_t)((SMEM_BUDGET - fixed - p.act_bytes) / stage), per_cta}));
+    p.total = p.act_bytes + p.n_stages * stage + fixed;
+    ga.plan = p;
+    (void)sizeof(Tr);
+    auto kern = gemv_narrow_kernel<TYPE, MB, NH, ACT>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    cudaError_t e = launch_pdl(kern, grid, (NCW + 2) * 32, p.total, s, ga);
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+template <uint32_t TYPE, int ACT>
+cudaError_t launch_narrow_rows(GemvArgs& ga, uint32_t rows_per_job, uint32_t max_jobs, cudaStream_t s) {
+    if (rows_per_job == 1) return launch_narrow_variant<TYPE, 1, 1, ACT>(ga, max_jobs, s);
+    if (rows_per_job == 2) return launch_narrow_variant<TYPE, 2, 1, ACT>(ga, max_jobs, s);
+    if (rows_per_job <= 4) return launch_narrow_variant<TYPE, 2, 2, ACT>(ga, max_jobs, s);
+    if (rows_per_job <= 8) return launch_narrow_variant<TYPE, 2, 4, ACT>(ga, max_jobs, s);
+    return cudaErrorInvalidValue;
+}
+
+template <int ACT>
+cudaError_t launch_narrow_typed(uint32_t type, GemvArgs& ga, uint32_t rows_per_job, uint32_t max_jobs, cudaStream_t s) {
+    switch (type) {
+        case T_Q4_K: return launch_narrow_rows<T_Q4_K, ACT>(ga, rows_per_job, max_jobs, s);
+        case T_Q8_0: return launch_narrow_rows<T_Q8_0, ACT>(ga, rows_per_job, max_jobs, s);
+        case T_Q2_K: return launch_narrow_rows<T_Q2_K, ACT>(ga, rows_per_job, max_jobs, s);
+        case T_IQ2_XXS: return launch_narrow_rows<T_IQ2_XXS, ACT>(ga, rows_per_job, max_jobs, s);
+        case T_MXFP4: return launch_narrow_rows<T_MXFP4, ACT>(ga, rows_per_job, max_jobs, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+// units per row the narrow kernel takes: at least two tiles per stage, and one chunk per row
+bool narrow_k(uint32_t type, uint64_t k) {
+    const uint64_t upr = k / 256;
+    uint32_t chunk = 8;
+    switch (type) {
+        case T_Q4_K: chunk = Traits<T_Q4_K>::CHUNK_UNITS; break;
+        case T_Q8_0: chunk = Traits<T_Q8_0>::CHUNK_UNITS; break;
+        case T_Q2_K: chunk = Traits<T_Q2_K>::CHUNK_UNITS; break;
+        case T_IQ2_XXS: chunk = Traits<T_IQ2_XXS>::CHUNK_UNITS; break;
+        case T_MXFP4: chunk = Traits<T_MXFP4>::CHUNK_UNITS; break;
+    }
+    return upr >= 2 && upr <= 8 && upr <= chunk;
+}
+
+}  // namespace
+
 cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s) {
     GemvArgs ga = {};
     ga.w[0] = g.w0;
@@ -1649,9 +1949,14 @@ cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s) {
     ga.norm_w = g.planes == nullptr ? g.norm_w : nullptr;
     ga.norm_eps = g.norm_eps;
     uint64_t tiles = (uint64_t)g.max_jobs * ((g.n + ROWS - 1) / ROWS);
-    if (g.planes == nullptr) return launch_typed<1, 2>(g.type, ga, g.rows_per_job, tiles, s);
+    static const bool narrow_off = std::getenv("JQ_NO_NARROW_K") != nullptr;  // A/B switch for measurements
+    const bool narrow = !narrow_off && narrow_k(g.type, g.k);
+    if (g.planes == nullptr)
+        return narrow ? launch_narrow_typed<1>(g.type, ga, g.rows_per_job, g.max_jobs, s)
+                      : launch_typed<1, 2>(g.type, ga, g.rows_per_job, tiles, s);
     ga.act = planes_in(g.planes, g.x_rows, g.k);
-    return launch_typed<0, 2>(g.type, ga, g.rows_per_job, tiles, s);
+    return narrow ? launch_narrow_typed<0>(g.type, ga, g.rows_per_job, g.max_jobs, s)
+                  : launch_typed<0, 2>(g.type, ga, g.rows_per_job, tiles, s);
 }
 
 // ── launching a chain ───────────────────────────────────────────────────────────────────────────────
