@@ -69,6 +69,20 @@ int32_t jq_matmul_device(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n,
         JQ_CUDA(jq::launch_gemv_mma(w->type, w->dev, n, k, lhs, m, dst, scratch, ctx->status_dev, s));
         return jq::OK;
     }
+    // Batches a little above the decode kernel's eight rows: eight rows at a time through the decode kernel
+    // (the weights are read once per slice, from L2 when they fit) still beats the tile GEMM, whose K loop
+    // costs the same at any batch.
+    if (!ctx->force_f32 && m > jq::GEMV_MMA_MAX_M && m <= ctx->sliced_max_m &&
+        jq::gemv_mma_supports(w->type, w->dev, n, k, jq::GEMV_MMA_MAX_M)) {
+        void* scratch = nullptr;
+        JQ_CUDA(ctx->scratch_for(s, jq::gemv_mma_scratch_bytes(jq::GEMV_MMA_MAX_M, k), &scratch));
+        for (uint64_t r0 = 0; r0 < m; r0 += jq::GEMV_MMA_MAX_M) {
+            const uint64_t rows = std::min<uint64_t>(jq::GEMV_MMA_MAX_M, m - r0);
+            JQ_CUDA(jq::launch_gemv_mma(w->type, w->dev, n, k, lhs + r0 * k, rows, dst + r0 * n, scratch,
+                                        ctx->status_dev, s));
+        }
+        return jq::OK;
+    }
     if (!ctx->force_f32 && m > jq::GEMV_MMA_MAX_M && jq::gemm_tc_supports(w->type, w->dev, n, k, m)) {
         JQ_CUDA(jq::launch_gemm_tc(w->type, w->dev, n, k, lhs, m, dst, ctx->status_dev, s));
         return jq::OK;
@@ -136,6 +150,7 @@ int32_t jq_init(int32_t device, jq_ctx** out) {
     c->device = device;
     const char* f = std::getenv("JQ_FORCE_F32_PATH");
     c->force_f32 = f && f[0] == '1';
+    if (const char* sm = std::getenv("JQ_SLICED_MAX_M")) c->sliced_max_m = std::strtoull(sm, nullptr, 10);
     cudaError_t he = cudaHostAlloc(&c->status_host, sizeof(int), cudaHostAllocMapped);
     if (he == cudaSuccess) he = cudaHostGetDevicePointer(&c->status_dev, c->status_host, 0);
     if (he != cudaSuccess) {

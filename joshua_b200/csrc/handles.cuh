@@ -50,6 +50,7 @@ struct StreamScratch {
 struct jq_ctx {
     int device = 0;
     bool force_f32 = false;        // JQ_FORCE_F32_PATH=1: always take the exact-decode float kernels
+    uint64_t sliced_max_m = 64;    // JQ_SLICED_MAX_M: largest batch run as 8-row slices of the decode kernel (0 = never)
     int* status_host = nullptr;    // pinned, device-visible: set to 1 by a kernel whose bounded wait gave up
     int* status_dev = nullptr;
     std::mutex mu;
