@@ -93,18 +93,24 @@ def run(args):
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         dt = float(tmax.item())
 
+    # end to end, model level: host token ids in, host logits out, every step (pinned buffers), on every rank
+    tok = np.full(batch, 42, np.int32)
+    for _ in range(3):
+        model.forward_host(tok)
+    torch.cuda.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        logits_host = model.forward_host(tok)
+        tok = logits_host.argmax(axis=1).astype(np.int32)   # the host picks the next token from the logits
+    e2e_dt = (time.perf_counter() - t0) / args.steps
+    h2d, d2h = 4 * batch * world, 4 * batch * cfg.vocab * world
+    if world > 1:
+        tmax = torch.tensor([e2e_dt], device=dev, dtype=torch.float64)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        e2e_dt = float(tmax.item())
+
     if rank == 0:
-        # end to end, model level: host token ids in, host logits out, every step (pinned buffers)
-        tok = np.full(batch, 42, np.int32)
-        for _ in range(3):
-            model.forward_host(tok)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            logits_host = model.forward_host(tok)
-            tok = logits_host.argmax(axis=1).astype(np.int32)   # the host picks the next token from the logits
-        e2e_dt = (time.perf_counter() - t0) / args.steps
-        h2d, d2h = 4 * batch, 4 * batch * cfg.vocab
         # end to end, operator level: every matmul of the token through jq_matmul_t with host buffers (layer 0 and
         # the head timed, x layers)
         ly = model.layers[0]
@@ -148,7 +154,7 @@ def run(args):
                                "quantized matmuls, greedy arg-max), one CUDA graph; "
                                + ("layers + head in one persistent chain launch" if use_chain else "five launches per layer"),
                        "l2": "4.22 GB of weights per step, far larger than L2", "parallelism": f"replicas x{world}"},
-            "e2e": {"value": batch / e2e_dt, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "e2e": {"value": world * batch / e2e_dt, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "how": "model-level call with host buffers (LlamaDecoder.forward_host, the shape of the "
                            "reference's ModelWeights::forward): token ids host->device, one decode step, logits "
                            "device->host, the host picks the next token; wall clock over the timed steps",
