@@ -29,11 +29,12 @@ struct AttnArgs {
     const float* qkv;      // [B, (nq + 2 nkv) * hd], before the rotary embedding
     const int32_t* pos;    // [B]
     uint32_t batch, nq, nkv, hd, max_ctx, n_chunks;
+    uint32_t gsplit;       // CTAs that share one kv head's query heads (1 or 2); an item serves nq / nkv / gsplit heads
     float theta;
     float* cache_k;        // [B, nkv, max_ctx, hd]
     float* cache_v;
     float* part;           // [B, nq, n_chunks, hd + 2]
-    uint32_t* counters;    // [B * nkv], zero between calls
+    uint32_t* counters;    // [B * nkv * gsplit], zero between calls
     float* out;            // [B, nq * hd]
     unsigned long long* trace = nullptr;  // profiling aid: item (0, 0, 0) stores the GPU timer at its phases
 };
@@ -76,8 +77,8 @@ __device__ __forceinline__ void att_sync() {
 // One (chunk, kv head, sequence) item.  tid = 0..255 inside the group of threads; s_f: the item's shared
 // memory (attention_fused_smem_floats floats); s_last: one shared word.
 template <int BAR, uint32_t HD, uint32_t G>
-__device__ __forceinline__ void attention_fused_item_t(const AttnArgs& a, uint32_t chunk, uint32_t kvh, uint32_t b,
-                                                       uint32_t tid, float* s_f, uint32_t* s_last) {
+__device__ __forceinline__ void attention_fused_item_t(const AttnArgs& a, uint32_t chunk, uint32_t kvh, uint32_t sg,
+                                                       uint32_t b, uint32_t tid, float* s_f, uint32_t* s_last) {
     constexpr uint32_t NW = ATT_FUSED_THREADS / 32;
     constexpr uint32_t PER_WARP = ATT_FUSED_CHUNK / NW;        // positions a warp scores: 8
     constexpr uint32_t PG = ATT_FUSED_THREADS / HD > 0 ? ATT_FUSED_THREADS / HD : 1;  // position groups of the V pass
@@ -89,7 +90,9 @@ __device__ __forceinline__ void attention_fused_item_t(const AttnArgs& a, uint32
     constexpr uint32_t OUT_PER = (G * HD + ATT_FUSED_THREADS - 1) / ATT_FUSED_THREADS;
     const uint32_t nq = a.nq, nkv = a.nkv, max_ctx = a.max_ctx, n_chunks = a.n_chunks;
     const uint32_t lane = tid & 31, warp = tid >> 5;
-    const bool tr = a.trace != nullptr && chunk == 0 && kvh == 0 && b == 0 && tid == 0;
+    const uint32_t hb = kvh * (nq / nkv) + sg * G;   // first query head of this item
+    const uint32_t cix = (b * nkv + kvh) * a.gsplit + sg;  // its arrival counter
+    const bool tr = a.trace != nullptr && chunk == 0 && kvh == 0 && sg == 0 && b == 0 && tid == 0;
     att_trace(a, tr, 0);
     float* sq = s_f;
     float* sk = sq + G * HD;
@@ -113,7 +116,7 @@ __device__ __forceinline__ void attention_fused_item_t(const AttnArgs& a, uint32
         const uint32_t idx = tid + r * ATT_FUSED_THREADS;
         if (idx < N_ROT) {
             const uint32_t g = idx / HALF, i = idx - g * HALF;
-            const float* src = g < G ? row + (uint64_t)(kvh * G + g) * HD : row + (uint64_t)(nq + kvh) * HD;
+            const float* src = g < G ? row + (uint64_t)(hb + g) * HD : row + (uint64_t)(nq + kvh) * HD;
             ra[r] = __ldcg(src + i);  // qkv may have been written earlier in this same launch: read through L2
             rb[r] = __ldcg(src + i + HALF);
         }
@@ -158,7 +161,7 @@ __device__ __forceinline__ void attention_fused_item_t(const AttnArgs& a, uint32
     }
     if (tid < HD) sv[tid] = vnew;
     att_sync<BAR>();
-    if (newest && tid < HD) {
+    if (newest && sg == 0 && tid < HD) {
         Kc[(uint64_t)p * HD + tid] = sk[tid];
         Vc[(uint64_t)p * HD + tid] = sv[tid];
     }
@@ -236,11 +239,11 @@ __device__ __forceinline__ void attention_fused_item_t(const AttnArgs& a, uint32
             float v = 0.0f;
 #pragma unroll
             for (uint32_t pg = 0; pg < PG; ++pg) v += spv[(pg * G + g) * HD + i];  // fixed order
-            a.part[(((uint64_t)b * nq + kvh * G + g) * n_chunks + chunk) * (HD + 2) + i] = v;
+            a.part[(((uint64_t)b * nq + hb + g) * n_chunks + chunk) * (HD + 2) + i] = v;
         }
     }
     if (tid < G) {
-        float* dst = a.part + (((uint64_t)b * nq + kvh * G + tid) * n_chunks + chunk) * (HD + 2);
+        float* dst = a.part + (((uint64_t)b * nq + hb + tid) * n_chunks + chunk) * (HD + 2);
         dst[HD] = smx[tid];
         dst[HD + 1] = ssum[tid];
     }
@@ -250,10 +253,10 @@ __device__ __forceinline__ void attention_fused_item_t(const AttnArgs& a, uint32
     att_sync<BAR>();
     if (tid == 0) {
         __threadfence();
-        const uint32_t old = atomicAdd(&a.counters[b * nkv + kvh], 1u);
+        const uint32_t old = atomicAdd(&a.counters[cix], 1u);
         *s_last = old == active - 1 ? 1u : 0u;
         if (*s_last) {
-            a.counters[b * nkv + kvh] = 0;
+            a.counters[cix] = 0;
             __threadfence();
         }
     }
@@ -266,14 +269,14 @@ __device__ __forceinline__ void attention_fused_item_t(const AttnArgs& a, uint32
     for (uint32_t r = 0; r < OUT_PER; ++r) {
         const uint32_t idx = tid + r * ATT_FUSED_THREADS;
         const uint32_t g = idx / HD, i = idx - g * HD;
-        const float* src = a.part + (((uint64_t)b * nq + kvh * G + g) * n_chunks) * (HD + 2) + i;
+        const float* src = a.part + (((uint64_t)b * nq + hb + g) * n_chunks) * (HD + 2) + i;
 #pragma unroll
         for (uint32_t u = 0; u < ATT_MERGE_BATCH; ++u)
             pv[r][u] = (idx < G * HD && u < active) ? __ldcg(src + (uint64_t)u * (HD + 2)) : 0.0f;
     }
     // a warp per query head turns the chunks' (max, sum) into weights exp(m_c - max) and the denominator
     for (uint32_t g = warp; g < G; g += NW) {
-        const float* src = a.part + (((uint64_t)b * nq + kvh * G + g) * n_chunks) * (HD + 2);
+        const float* src = a.part + (((uint64_t)b * nq + hb + g) * n_chunks) * (HD + 2);
         float mx = -INFINITY;
         for (uint32_t c = lane; c < active; c += 32) mx = fmaxf(mx, __ldcg(src + (uint64_t)c * (HD + 2) + HD));
 #pragma unroll
@@ -299,7 +302,7 @@ __device__ __forceinline__ void attention_fused_item_t(const AttnArgs& a, uint32
         const uint32_t idx = tid + r * ATT_FUSED_THREADS;
         if (idx < G * HD) {
             const uint32_t g = idx / HD, i = idx - g * HD;
-            const float* src = a.part + (((uint64_t)b * nq + kvh * G + g) * n_chunks) * (HD + 2) + i;
+            const float* src = a.part + (((uint64_t)b * nq + hb + g) * n_chunks) * (HD + 2) + i;
             const float* wg = se + g * n_chunks;
             float acc = 0.0f;
 #pragma unroll
@@ -314,18 +317,18 @@ __device__ __forceinline__ void attention_fused_item_t(const AttnArgs& a, uint32
                 for (uint32_t u = 0; u < ATT_MERGE_BATCH; ++u)
                     if (c0 + u < active) acc = fmaf(wg[c0 + u], more[u], acc);
             }
-            a.out[((uint64_t)b * nq + kvh * G + g) * HD + i] = acc / sden[g];
+            a.out[((uint64_t)b * nq + hb + g) * HD + i] = acc / sden[g];
         }
     }
 }
 
-// Dispatch on the head size and group size (attention_fused_shape_ok).
+// Dispatch on the head size and the heads per item (attention_fused_shape_ok).
 template <int BAR>
-__device__ __forceinline__ void attention_fused_item(const AttnArgs& a, uint32_t chunk, uint32_t kvh, uint32_t b,
-                                                     uint32_t tid, float* s_f, uint32_t* s_last) {
-    const uint32_t G = a.nq / a.nkv;
+__device__ __forceinline__ void attention_fused_item(const AttnArgs& a, uint32_t chunk, uint32_t kvh, uint32_t sg,
+                                                     uint32_t b, uint32_t tid, float* s_f, uint32_t* s_last) {
+    const uint32_t G = a.nq / a.nkv / a.gsplit;
 #define JQ_ATT_CASE(HDV, GV) \
-    if (a.hd == HDV && G == GV) return attention_fused_item_t<BAR, HDV, GV>(a, chunk, kvh, b, tid, s_f, s_last);
+    if (a.hd == HDV && G == GV) return attention_fused_item_t<BAR, HDV, GV>(a, chunk, kvh, sg, b, tid, s_f, s_last);
     JQ_ATT_CASE(128, 4)
     JQ_ATT_CASE(128, 8)
     JQ_ATT_CASE(128, 1)
@@ -342,14 +345,14 @@ __device__ __forceinline__ void attention_fused_item(const AttnArgs& a, uint32_t
 }
 
 // The persistent chain only carries the two shapes of the benchmark models (head size 128, 4 or 8 query heads
-// per kv head), to keep its code small.
+// per kv head, one item per kv head), to keep its code small.
 template <int BAR>
 __device__ __forceinline__ void attention_fused_item_chain(const AttnArgs& a, uint32_t chunk, uint32_t kvh, uint32_t b,
                                                            uint32_t tid, float* s_f, uint32_t* s_last) {
     if (a.nq / a.nkv == 4)
-        attention_fused_item_t<BAR, 128, 4>(a, chunk, kvh, b, tid, s_f, s_last);
+        attention_fused_item_t<BAR, 128, 4>(a, chunk, kvh, 0, b, tid, s_f, s_last);
     else
-        attention_fused_item_t<BAR, 128, 8>(a, chunk, kvh, b, tid, s_f, s_last);
+        attention_fused_item_t<BAR, 128, 8>(a, chunk, kvh, 0, b, tid, s_f, s_last);
 }
 
 }  // namespace jq

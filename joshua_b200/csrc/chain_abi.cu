@@ -100,6 +100,7 @@ int32_t jq_chain_add_attention(jq_chain* c, const float* qkv, const int32_t* pos
                                       "and a context that fits the kernel's shared memory");
     if (head_dim != 128 || (n_q / n_kv != 4 && n_q / n_kv != 8))
         return jq_fail(jq::E_INVALID, "jq_chain_add_attention: the chain carries head_dim 128 with 4 or 8 query heads per kv head");
+    op.att.gsplit = 1;  // the chain runs one item per kv head
     uint32_t fl = jq::attention_fused_smem_floats(n_q, n_kv, head_dim, op.att.n_chunks);
     if (!jq::gemv_chain_supports(c->type, c->m, std::max<uint64_t>(c->max_k, 256), std::max(c->att_floats, fl)))
         return jq_fail(jq::E_INVALID, "jq_chain_add_attention: the attention step does not fit the chain's shared memory");

@@ -221,7 +221,8 @@ __global__ void __launch_bounds__(ATT_FUSED_THREADS) attention_fused_kernel(Attn
     __shared__ uint32_t s_last;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     pdl_wait_();
-    attention_fused_item<0>(a, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x, s_f, &s_last);
+    attention_fused_item<0>(a, blockIdx.x, blockIdx.y / a.gsplit, blockIdx.y % a.gsplit, blockIdx.z, threadIdx.x, s_f,
+                            &s_last);
 }
 
 // y = a + b
@@ -348,7 +349,7 @@ cudaError_t launch_attention_decode(const float* q, const float* cache_k, const 
 
 size_t attention_fused_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx) {
     uint32_t n_chunks = (max_ctx + ATT_FUSED_CHUNK - 1) / ATT_FUSED_CHUNK;
-    return (size_t)batch * nq * n_chunks * (hd + 2) * 4 + (size_t)batch * nkv * 4;
+    return (size_t)batch * nq * n_chunks * (hd + 2) * 4 + (size_t)batch * nkv * 2 * 4;  // partials + counters
 }
 
 // scratch: attention_fused_scratch_bytes bytes whose last batch * nkv words (the counters) are zero before
@@ -359,8 +360,8 @@ cudaError_t launch_attention_fused(const float* qkv, const int32_t* pos, uint32_
     AttnArgs a;
     if (!attention_fused_args(qkv, pos, batch, nq, nkv, hd, max_ctx, theta, cache_k, cache_v, out, scratch, &a))
         return cudaErrorInvalidValue;
-    size_t smem = (size_t)attention_fused_smem_floats(nq, nkv, hd, a.n_chunks) * 4;
-    cudaError_t e = launch_pdl(attention_fused_kernel, dim3(a.n_chunks, nkv, batch), ATT_FUSED_THREADS, smem, s, a);
+    size_t smem = (size_t)attention_fused_smem_floats(nq / a.gsplit, nkv, hd, a.n_chunks) * 4;
+    cudaError_t e = launch_pdl(attention_fused_kernel, dim3(a.n_chunks, nkv * a.gsplit, batch), ATT_FUSED_THREADS, smem, s, a);
     if (e != cudaSuccess) return e;
     return cudaGetLastError();
 }
@@ -372,7 +373,10 @@ bool attention_fused_args(const float* qkv, const int32_t* pos, uint32_t batch, 
     uint32_t n_chunks = (max_ctx + ATT_FUSED_CHUNK - 1) / ATT_FUSED_CHUNK;
     if ((size_t)attention_fused_smem_floats(nq, nkv, hd, n_chunks) * 4 > 48 * 1024) return false;
     float* part = static_cast<float*>(scratch);
-    *a = AttnArgs{qkv, pos, batch, nq, nkv, hd, max_ctx, n_chunks, theta, cache_k, cache_v, part,
+    // eight query heads per kv head are shared by two CTAs: the K / V rows are read twice, the per-CTA chain
+    // of work halves
+    const uint32_t gsplit = nq / nkv == 8 ? 2u : 1u;
+    *a = AttnArgs{qkv, pos, batch, nq, nkv, hd, max_ctx, n_chunks, gsplit, theta, cache_k, cache_v, part,
                   reinterpret_cast<uint32_t*>(part + (size_t)batch * nq * n_chunks * (hd + 2)), out};
     return true;
 }

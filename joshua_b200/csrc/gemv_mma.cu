@@ -670,7 +670,16 @@ __device__ __forceinline__ void process_unit(const uint8_t* u0, const uint8_t* u
             uint32_t lo0 = __funnelshift_r(x0, x1, s0), hi0 = __funnelshift_r(x1, x2, s0);
             uint32_t lo1 = __funnelshift_r(y0, y1, s1), hi1 = __funnelshift_r(y1, y2, s1);
             uint2 g0 = s_grid[(lo0 >> (8 * ro.t)) & 0xFF], g1 = s_grid[(lo1 >> (8 * ro.t)) & 0xFF];
-            uint2 k0 = s_mask[(hi0 >> (7 * ro.t)) & 127], k1 = s_mask[(hi1 >> (7 * ro.t)) & 127];
+            // sign masks by arithmetic instead of a second table: the shared-memory pipe, not the ALU, is what
+            // this format saturates (random 8-byte lookups conflict).  Seven stored sign bits, the eighth is
+            // their parity; bit b of the byte -> 0xFF in byte b.
+            auto sign_mask = [](uint32_t idx) {
+                const uint32_t sg = idx | ((__popc(idx) & 1u) << 7);
+                const uint32_t lo = ((sg & 0xFu) * 0x00204081u) & 0x01010101u;
+                const uint32_t hi = ((sg >> 4) * 0x00204081u) & 0x01010101u;
+                return make_uint2(lo * 0xFFu, hi * 0xFFu);
+            };
+            const uint2 k0 = sign_mask((hi0 >> (7 * ro.t)) & 127), k1 = sign_mask((hi1 >> (7 * ro.t)) & 127);
             // negate the bytes under the mask: (v ^ 0xFF) + 1; grid bytes are never 0, so no carry leaves a byte
             uint32_t a[4] = {(g0.x ^ k0.x) + (k0.x & 0x01010101u), (g1.x ^ k1.x) + (k1.x & 0x01010101u),
                              (g0.y ^ k0.y) + (k0.y & 0x01010101u), (g1.y ^ k1.y) + (k1.y & 0x01010101u)};
