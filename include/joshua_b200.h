@@ -317,6 +317,11 @@ int32_t jq_moe_route_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, const
 int32_t jq_moe_experts_dev(jq_moe* m, const float* x_dev, uint64_t n_rows, const uint32_t* expert_ids_dev,
                            float* out_dev, void* stream);
 
+/* Profiling aid: with a device buffer of 256 uint64, CTA (0, 0) of the tile GEMM stores four GPU nanosecond
+ * timestamps per K step for its first 64 steps (stage free, stage handed over, operands complete, MMAs
+ * issued); NULL = off. */
+int32_t jq_debug_gemm_trace(uint64_t* trace_dev);
+
 /* Profiling aid: with a device buffer of 8 uint64 the last CTA of the decode router kernel stores the GPU
  * nanosecond timer at its phases (entered, logits stored, counted in, routed, jobs built); NULL = off. */
 int32_t jq_debug_moe_trace(uint64_t* trace_dev);

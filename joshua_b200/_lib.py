@@ -67,6 +67,7 @@ _SIGNATURES = {
     "jq_moe_experts_dev": (i32, [vp, vp, u64, vp, vp, vp]),
     "jq_moe_status": (i32, [vp]),
     "jq_debug_moe_trace": (i32, [vp]),
+    "jq_debug_gemm_trace": (i32, [vp]),
     "jq_moe_last_routing": (i32, [vp, u64, vp, vp]),
     "jq_chain_create": (i32, [vp, u32, u32, ctypes.POINTER(vp)]),
     "jq_chain_free": (None, [vp]),

@@ -84,10 +84,17 @@ int32_t jq_matmul_device(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n,
         return jq::OK;
     }
     if (!ctx->force_f32 && m > jq::GEMV_MMA_MAX_M && jq::gemm_tc_supports(w->type, w->dev, n, k, m)) {
-        JQ_CUDA(jq::launch_gemm_tc(w->type, w->dev, n, k, lhs, m, dst, ctx->status_dev, s));
+        void* scratch = nullptr;
+        JQ_CUDA(ctx->scratch_for(reinterpret_cast<cudaStream_t>(reinterpret_cast<uintptr_t>(s) ^ 3), jq::gemm_tc_scratch_bytes(m, k), &scratch));
+        JQ_CUDA(jq::launch_gemm_tc(w->type, w->dev, n, k, lhs, m, dst, scratch, ctx->status_dev, s));
         return jq::OK;
     }
     JQ_CUDA(jq::launch_matmul_f32(w->type, w->dev, n, k, lhs, m, dst, s));
+    return jq::OK;
+}
+
+extern "C" int32_t jq_debug_gemm_trace(uint64_t* trace_dev) {
+    jq::gemm_tc_set_trace(reinterpret_cast<unsigned long long*>(trace_dev));
     return jq::OK;
 }
 

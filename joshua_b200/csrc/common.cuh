@@ -56,8 +56,11 @@ cudaError_t launch_matmul_f32(uint32_t type, const uint8_t* w, uint64_t n, uint6
 // gemm_tc.cu: tcgen05 tile GEMM for m > 8 (prefill, batched decode)
 cudaError_t tables_gemm_tc();
 bool gemm_tc_supports(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, uint64_t m);
+// scratch: gemm_tc_scratch_bytes(m, k) bytes (the activations' two TF32 terms), 256-byte aligned
+size_t gemm_tc_scratch_bytes(uint64_t m, uint64_t k);
+void gemm_tc_set_trace(unsigned long long* dev_buf);  // profiling aid, see gemm_tc.cu
 cudaError_t launch_gemm_tc(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
-                           float* dst, int* error_flag, cudaStream_t s);
+                           float* dst, void* scratch, int* error_flag, cudaStream_t s);
 
 // One unit of grouped (MoE) work: up to 8 consecutive positions of the expert-sorted activation list,
 // all routed to `expert`.

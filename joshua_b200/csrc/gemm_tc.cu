@@ -13,6 +13,10 @@
 // accumulates in the other half of tensor memory.  The result then matches f32 accumulation
 // (src/kquant_dot.rs:268-483) to the tolerance the path is held to.
 //
+// The activations are split once per launch by a small kernel (two f32 arrays, hi and lo) and reach shared
+// memory by TMA (`cp.async.bulk.tensor.2d`, 128-byte swizzle) without passing through the converter warps or
+// the L1 cache, which the weight decode then has to itself.
+//
 // Pipeline: NS shared-memory stages, each guarded by a `full` mbarrier (converters -> issuer, after a
 // generic-to-async proxy fence) and an `empty` mbarrier (tcgen05.commit -> converters).  Every wait is
 // bounded; a wait that runs out raises the device status flag, and every thread still reaches the common
@@ -20,6 +24,10 @@
 //
 // Tensor-pipe bound for large m: 3 x 2*m*n*k TF32 flops per launch.  Algorithmic flops: 2*m*n*k.
 #include <algorithm>
+#include <cstdlib>
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
 
 #include "common.cuh"
 
@@ -58,6 +66,42 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         if (done) return true;
     }
     return false;
+}
+
+__device__ __forceinline__ unsigned long long tc_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Profiling aid (jq_debug_gemm_trace): CTA (0, 0) stores four timestamps per K step for its first 64 steps:
+// stage free (converter), stage handed over (converter), operands complete (issuer), MMAs issued (issuer).
+unsigned long long* g_gemm_trace = nullptr;
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// One box of a 2-D tensor map (x = element offset along k, a multiple of 4 floats; y = row) into shared memory.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint32_t x, uint32_t y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// x -> its TF32 part (top 11 significant bits) and the exact remainder, element-wise.
+__global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict__ x, uint64_t n4, float* __restrict__ hi,
+                                                         float* __restrict__ lo) {
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n4; i += (uint64_t)gridDim.x * blockDim.x) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(x) + i);
+        float4 h;
+        h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+        h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+        h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+        h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+        reinterpret_cast<float4*>(hi)[i] = h;
+        reinterpret_cast<float4*>(lo)[i] = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+    }
 }
 
 // Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
@@ -141,8 +185,9 @@ __device__ __forceinline__ void store_split(uint8_t* hi_tile, uint8_t* lo_tile, 
 
 template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-    gemm_tc_kernel(const uint8_t* __restrict__ w, uint64_t n, uint64_t k, const float* __restrict__ lhs, uint64_t m,
-                   float* __restrict__ dst, uint32_t n_stages, int* __restrict__ error_flag) {
+    gemm_tc_kernel(const uint8_t* __restrict__ w, uint64_t n, uint64_t k, const __grid_constant__ CUtensorMap map_hi,
+                   const __grid_constant__ CUtensorMap map_lo, uint64_t m, float* __restrict__ dst, uint32_t n_stages,
+                   int* __restrict__ error_flag, unsigned long long* __restrict__ trace, int dbg_skip) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // stage layout: A hi | A lo | B hi | B lo, every tile 1024-byte aligned
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -156,6 +201,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     const uint64_t row0 = (uint64_t)blockIdx.x * TC_M;
     const uint64_t tok0 = (uint64_t)blockIdx.y * N_TILE;
     const uint32_t k_steps = (uint32_t)(k / TC_K);
+    // The converter warps can work in 1, 2 or 4 groups that take alternate K steps (more steps in flight, more
+    // units per thread).  Measured: no gain at 2 groups and a loss at 4 (m = 512: 0.30 -> 0.35 ms at 4096 x 4096,
+    // MXFP4 m = 4096: 0.91 -> 1.06 ms), because a step is bound by the converters' instruction throughput, not by
+    // the latency of one step's chain; with the weight decode switched off (JQ_DEBUG_TC_SKIP=1) a step takes
+    // 1.0 us against 2.2 us with it.  One group it is.
+    constexpr uint32_t n_groups = 1u;
     const uint32_t n_chunks = (k_steps + TC_CHUNK - 1) / TC_CHUNK;
     const uint64_t row_bytes = k / ELEMS * BYTES;
     constexpr uint32_t UPB = ELEMS / 8;
@@ -163,7 +214,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 
     if (tid == 0) {
         for (uint32_t s = 0; s < n_stages; ++s) {
-            mbar_init(&full[s], TC_CONV_WARPS);
+            mbar_init(&full[s], TC_CONV_WARPS / n_groups + 1);  // a group's warps and the thread that starts the TMA copies
             mbar_init(&empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -185,15 +236,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     const uint32_t tmem_d = tmem_base_slot;
 
     if (warp < TC_CONV_WARPS) {
-        // ── converters: per K step thread (r, unit) decodes 8 weights of row r, and the 512 threads split the
-        // N_TILE x 32 activation block between them (16-byte pieces, 8 consecutive threads per 128-byte row).
+        // ── converters: per K step thread (r, unit) decodes 8 weights of row r and stores their two TF32 terms;
+        // thread 0 also starts the TMA copies of the step's activation tiles.
         // Between chunks they read the finished accumulator back: warp w reads TMEM lanes 32 (w % 4) .. + 31
         // (its weight rows) and the quarter w / 4 of the columns (tokens). ──
-        const uint32_t r = tid & 127, unit = tid >> 7;  // weight row of the tile, 8-value unit of the K step
-        const uint64_t wrow = row0 + r < n ? row0 + r : n - 1;
-        const uint8_t* wr = w + wrow * row_bytes;
-        constexpr int B_PER = (N_TILE * 8 + TC_CONV_WARPS * 32 - 1) / (TC_CONV_WARPS * 32);  // 16-byte pieces per thread
-        const uint32_t brow0 = tid >> 3, bchunk = tid & 7;
+        const uint32_t tg = (TC_CONV_WARPS * 32) / n_groups;   // threads per group
+        const uint32_t sg = tid / tg, gt = tid - sg * tg;      // step group, thread inside it
         const uint32_t q = warp & 3, grp = warp >> 2;
         constexpr int MY_COLS = N_TILE / 4;  // columns this thread accumulates
         float sums[MY_COLS];
@@ -229,49 +277,52 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
             return true;
         };
-        // this thread's activation pieces of K step ks (requested one step ahead of their use)
-        float4 xb[B_PER];
-        auto load_b = [&](uint32_t ks) {
-#pragma unroll
-            for (int j = 0; j < B_PER; ++j) {
-                const uint32_t br = brow0 + j * (TC_CONV_WARPS * 4);
-                const bool real = br < N_TILE && tok0 + br < m;
-                xb[j] = real ? __ldg(reinterpret_cast<const float4*>(lhs + (tok0 + br) * k + (uint64_t)ks * TC_K + bchunk * 4))
-                             : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        };
         bool ok = true;
         uint32_t drained = 0;
-        load_b(0);
-        for (uint32_t ks = 0; ks < k_steps && ok; ++ks) {
+        for (uint32_t ks = sg; ks < k_steps && ok; ks += n_groups) {
             const uint32_t s = ks % n_stages, round = ks / n_stages;
-            // decode before waiting for the stage: the global loads overlap the wait
-            float v[8];
-            {
-                const uint32_t u = ks * 4 + unit;  // 8-value unit of the row
-                decode_unit<TYPE>(wr + (uint64_t)(u / UPB) * BYTES, u % UPB, v, false);
+            // decode before waiting for the stage (the loads overlap the wait): the group's threads share the
+            // 128 rows x 4 units of the step, item = gt + i * tg -> (row item % 128, unit item / 128)
+            float v[4][8];
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) {
+                if (i < n_groups && !(dbg_skip & 1)) {
+                    const uint32_t item = gt + i * tg, r = item & 127, unit = item >> 7;
+                    const uint64_t wrow = row0 + r < n ? row0 + r : n - 1;
+                    const uint32_t u = ks * 4 + unit;  // 8-value unit of the row
+                    decode_unit<TYPE>(w + wrow * row_bytes + (uint64_t)(u / UPB) * BYTES, u % UPB, v[i], false);
+                }
             }
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(&empty[s], (round & 1) ^ 1));  // warp-uniform
             if (!ok) break;
+            const bool tr = trace != nullptr && gt == 0 && blockIdx.x == 0 && blockIdx.y == 0 && ks < 64;
+            if (tr) trace[4 * ks] = tc_now();
             uint8_t* st = smem + (size_t)s * STAGE;
-            store_split(st, st + PLANE_A, r, unit * 2, v);
-            store_split(st, st + PLANE_A, r, unit * 2 + 1, v + 4);
-#pragma unroll
-            for (int j = 0; j < B_PER; ++j) {
-                const uint32_t br = brow0 + j * (TC_CONV_WARPS * 4);
-                if (br < N_TILE) {
-                    float bv[4] = {xb[j].x, xb[j].y, xb[j].z, xb[j].w};
-                    store_split(st + 2 * PLANE_A, st + 2 * PLANE_A + PLANE_B, br, bchunk, bv);
+            if (gt == 0) {
+                // the stage is free: start the two activation tiles (hi, lo) of this K step on their way
+                if (dbg_skip & 2) {
+                    mbar_arrive(&full[s]);
+                } else {
+                    mbar_arrive_expect_tx(&full[s], 2 * PLANE_B);
+                    tma_load_2d(st + 2 * PLANE_A, &map_hi, ks * TC_K, (uint32_t)tok0, &full[s]);
+                    tma_load_2d(st + 2 * PLANE_A + PLANE_B, &map_lo, ks * TC_K, (uint32_t)tok0, &full[s]);
                 }
             }
-            if (ks + 1 < k_steps) load_b(ks + 1);
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) {
+                if (i < n_groups && !(dbg_skip & 1)) {
+                    const uint32_t item = gt + i * tg, r = item & 127, unit = item >> 7;
+                    store_split(st, st + PLANE_A, r, unit * 2, v[i]);
+                    store_split(st, st + PLANE_A, r, unit * 2 + 1, v[i] + 4);
+                }
+            }
             // make the generic-proxy stores visible to the tensor core's async proxy, then hand over
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&full[s]);
-            // at a chunk boundary drain every finished chunk but the newest (which is still accumulating)
-            if ((ks + 1) % TC_CHUNK == 0)
-                while (ok && drained + 1 < (ks + 1) / TC_CHUNK) ok = drain(drained++);
+            if (tr) trace[4 * ks + 1] = tc_now();
+            // drain every finished chunk but the newest (which is still accumulating)
+            while (ok && drained + 1 < (ks + 1) / TC_CHUNK) ok = drain(drained++);
         }
         while (ok && drained < n_chunks) ok = drain(drained++);
         if (!ok) abort_flag = 1;
@@ -287,6 +338,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         // ── issuer: one thread feeds the tensor core ──
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(N_TILE);
+            const uint32_t base0 = smem_u32(smem);
+            const uint64_t d0_a_hi = umma_desc(base0), d0_a_lo = umma_desc(base0 + PLANE_A);
+            const uint64_t d0_b_hi = umma_desc(base0 + 2 * PLANE_A), d0_b_lo = umma_desc(base0 + 2 * PLANE_A + PLANE_B);
             bool ok = true;
             for (uint32_t ks = 0; ks < k_steps && ok; ++ks) {
                 const uint32_t s = ks % n_stages, round = ks / n_stages;
@@ -298,19 +352,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 }
                 ok = mbar_wait(&full[s], round & 1);
                 if (!ok) break;
+                const bool tr = trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && ks < 64;
+                if (tr) trace[4 * ks + 2] = tc_now();
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_hi = smem_u32(smem + (size_t)s * STAGE), a_lo = a_hi + PLANE_A;
-                const uint32_t b_hi = a_hi + 2 * PLANE_A, b_lo = b_hi + PLANE_B;
+                // descriptors differ from the stage-0 ones only in the start-address field (bytes / 16, no carry
+                // out of its 14 bits below 256 KB): one add each instead of rebuilding them, the issuing thread's
+                // own instruction latency being what bounds a K step once the operands are there
+                const uint64_t so = (uint64_t)s * (STAGE >> 4);
+                const uint64_t da_hi = d0_a_hi + so, da_lo = d0_a_lo + so, db_hi = d0_b_hi + so, db_lo = d0_b_lo + so;
                 const uint32_t d = tmem_d + buf * N_TILE;
 #pragma unroll
                 for (uint32_t kk = 0; kk < TC_K / 8; ++kk) {
                     // one instruction covers K = 8 tf32 = 32 bytes of the swizzled row
-                    const uint32_t adv = kk * 32;
-                    umma_tf32(d, umma_desc(a_hi + adv), umma_desc(b_hi + adv), idesc, (ks % TC_CHUNK != 0) || kk != 0);
-                    umma_tf32(d, umma_desc(a_hi + adv), umma_desc(b_lo + adv), idesc, 1);
-                    umma_tf32(d, umma_desc(a_lo + adv), umma_desc(b_hi + adv), idesc, 1);
+                    const uint64_t adv = kk * 2;
+                    umma_tf32(d, da_hi + adv, db_hi + adv, idesc, (ks % TC_CHUNK != 0) || kk != 0);
+                    umma_tf32(d, da_hi + adv, db_lo + adv, idesc, 1);
+                    umma_tf32(d, da_lo + adv, db_hi + adv, idesc, 1);
                 }
                 umma_commit(&empty[s]);  // arrives when the instructions above have finished reading the stage
+                if (tr) trace[4 * ks + 3] = tc_now();
                 if ((ks + 1) % TC_CHUNK == 0 || ks + 1 == k_steps) umma_commit(&acc_full[buf]);
             }
             if (!ok) abort_flag = 1;
@@ -325,9 +385,30 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
 }
 
+PFN_cuTensorMapEncodeTiled g_encode_tiled = nullptr;
+
+cudaError_t tensor_map_for(const float* base, uint64_t m, uint64_t k, uint32_t n_tile, CUtensorMap* out) {
+    if (!g_encode_tiled) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess) return e;
+        if (qres != cudaDriverEntryPointSuccess || !fn) return cudaErrorNotSupported;
+        g_encode_tiled = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+    }
+    const cuuint64_t dims[2] = {k, m};
+    const cuuint64_t strides[1] = {k * 4};             // bytes between rows (a multiple of 16: k % 32 == 0)
+    const cuuint32_t box[2] = {(cuuint32_t)TC_K, n_tile};  // 32 floats = one 128-byte swizzled row, n_tile rows
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode_tiled(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);  // rows beyond m read as zeros
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE>
-cudaError_t launch_tile(const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m, float* dst,
-                        int* error_flag, cudaStream_t s) {
+cudaError_t launch_tile(const uint8_t* w, uint64_t n, uint64_t k, const float* x_hi, const float* x_lo, uint64_t m,
+                        float* dst, int* error_flag, cudaStream_t s) {
     constexpr uint32_t STAGE = 2 * PLANE_A + 2 * N_TILE * 128;
     uint32_t n_stages = std::min<uint32_t>(8, std::min<uint32_t>((uint32_t)(k / TC_K), (216 * 1024) / STAGE));
     size_t smem = (size_t)n_stages * STAGE + 1024;
@@ -338,21 +419,33 @@ cudaError_t launch_tile(const uint8_t* w, uint64_t n, uint64_t k, const float* l
         if (e != cudaSuccess) return e;
         configured = true;
     }
+    CUtensorMap map_hi, map_lo;
+    cudaError_t e = tensor_map_for(x_hi, m, k, N_TILE, &map_hi);
+    if (e == cudaSuccess) e = tensor_map_for(x_lo, m, k, N_TILE, &map_lo);
+    if (e != cudaSuccess) return e;
     dim3 grid((unsigned)((n + TC_M - 1) / TC_M), (unsigned)((m + N_TILE - 1) / N_TILE));
-    kern<<<grid, TC_THREADS, smem, s>>>(w, n, k, lhs, m, dst, n_stages, error_flag);
+    // JQ_DEBUG_TC_SKIP (measurement only, results are wrong): bit 0 = no weight decode / stores, bit 1 = no TMA
+    static const int dbg_skip = std::getenv("JQ_DEBUG_TC_SKIP") ? std::atoi(std::getenv("JQ_DEBUG_TC_SKIP")) : 0;
+    kern<<<grid, TC_THREADS, smem, s>>>(w, n, k, map_hi, map_lo, m, dst, n_stages, error_flag, g_gemm_trace, dbg_skip);
     return cudaGetLastError();
 }
 
 template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES>
 cudaError_t launch_type(const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m, float* dst,
-                        int* error_flag, cudaStream_t s) {
-    if (m <= 32) return launch_tile<TYPE, ELEMS, BYTES, 32>(w, n, k, lhs, m, dst, error_flag, s);
-    if (m <= 64) return launch_tile<TYPE, ELEMS, BYTES, 64>(w, n, k, lhs, m, dst, error_flag, s);
-    if (m <= 128) return launch_tile<TYPE, ELEMS, BYTES, 128>(w, n, k, lhs, m, dst, error_flag, s);
+                        float* scratch, int* error_flag, cudaStream_t s) {
+    // split the activations once: hi and lo arrays of m * k floats each
+    float* x_hi = scratch;
+    float* x_lo = scratch + ((m * k + 63) & ~(uint64_t)63);
+    const uint64_t n4 = m * k / 4;
+    split_tf32_kernel<<<(unsigned)std::min<uint64_t>((n4 + 255) / 256, 148 * 16), 256, 0, s>>>(lhs, n4, x_hi, x_lo);
+    if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
+    if (m <= 32) return launch_tile<TYPE, ELEMS, BYTES, 32>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+    if (m <= 64) return launch_tile<TYPE, ELEMS, BYTES, 64>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+    if (m <= 128) return launch_tile<TYPE, ELEMS, BYTES, 128>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
     // 256-token tiles decode every weight half as often, but only pay off once they still fill the SMs
     const uint64_t ctas256 = ((n + TC_M - 1) / TC_M) * ((m + 255) / 256);
-    if (ctas256 < 148) return launch_tile<TYPE, ELEMS, BYTES, 128>(w, n, k, lhs, m, dst, error_flag, s);
-    return launch_tile<TYPE, ELEMS, BYTES, 256>(w, n, k, lhs, m, dst, error_flag, s);
+    if (ctas256 < 148) return launch_tile<TYPE, ELEMS, BYTES, 128>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+    return launch_tile<TYPE, ELEMS, BYTES, 256>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
 }
 
 }  // namespace
@@ -374,14 +467,19 @@ bool gemm_tc_supports(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, u
     }
 }
 
+void gemm_tc_set_trace(unsigned long long* dev_buf) { g_gemm_trace = dev_buf; }
+
+size_t gemm_tc_scratch_bytes(uint64_t m, uint64_t k) { return (size_t)(2 * ((m * k + 63) & ~(uint64_t)63) * 4 + 256); }
+
 cudaError_t launch_gemm_tc(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
-                           float* dst, int* error_flag, cudaStream_t s) {
+                           float* dst, void* scratch_v, int* error_flag, cudaStream_t s) {
+    float* scratch = static_cast<float*>(scratch_v);
     switch (type) {
-        case T_Q8_0: return launch_type<T_Q8_0, 32, 34>(w, n, k, lhs, m, dst, error_flag, s);
-        case T_Q2_K: return launch_type<T_Q2_K, 256, 84>(w, n, k, lhs, m, dst, error_flag, s);
-        case T_Q4_K: return launch_type<T_Q4_K, 256, 144>(w, n, k, lhs, m, dst, error_flag, s);
-        case T_IQ2_XXS: return launch_type<T_IQ2_XXS, 256, 66>(w, n, k, lhs, m, dst, error_flag, s);
-        case T_MXFP4: return launch_type<T_MXFP4, 32, 17>(w, n, k, lhs, m, dst, error_flag, s);
+        case T_Q8_0: return launch_type<T_Q8_0, 32, 34>(w, n, k, lhs, m, dst, scratch, error_flag, s);
+        case T_Q2_K: return launch_type<T_Q2_K, 256, 84>(w, n, k, lhs, m, dst, scratch, error_flag, s);
+        case T_Q4_K: return launch_type<T_Q4_K, 256, 144>(w, n, k, lhs, m, dst, scratch, error_flag, s);
+        case T_IQ2_XXS: return launch_type<T_IQ2_XXS, 256, 66>(w, n, k, lhs, m, dst, scratch, error_flag, s);
+        case T_MXFP4: return launch_type<T_MXFP4, 32, 17>(w, n, k, lhs, m, dst, scratch, error_flag, s);
         default: return cudaErrorInvalidValue;
     }
 }
