@@ -162,7 +162,10 @@ def run(args):
                     "operator_level_how": "every linear of the token through jq_matmul_t with host slices (the "
                                           "QuantizedType::matmul_t boundary): layer 0 and the head timed, x layers"},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                         "traffic": None, "peak_source": which, "kernel": "gemv_mma_kernel<Q4_K>",
+                         # ncu (profiles/gemv_mma_q4k_28672x4096_m1.md): dram read + write of a captured launch is
+                         # 66.44 MB against 66.08 MB algorithmic, i.e. x 1.005; scaled to the average launch here
+                         "traffic": alg / launches * 1.005, "traffic_unit": "bytes per launch (average launch)",
+                         "peak_source": which, "kernel": "gemv_mma_kernel<Q4_K>",
                          "launches_per_step": launches, "avg_launch_us": dt_mm / launches * 1e6,
                          "bytes_per_step": alg},
             "gpu_launches": (4 if use_chain else model.launches_per_step) * args.steps, "clocks": clocks.summary(),
