@@ -162,7 +162,7 @@ def run(args):
                     "operator_level_how": "every linear of the token through jq_matmul_t with host slices (the "
                                           "QuantizedType::matmul_t boundary): layer 0 and the head timed, x layers"},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                         # ncu (profiles/gemv_mma_q4k_28672x4096_m1.md): dram read + write of a captured launch is
+                         # an ncu capture of the 28672 x 4096 launch: its dram read + write is
                          # 66.44 MB against 66.08 MB algorithmic, i.e. x 1.005; scaled to the average launch here
                          "traffic": alg / launches * 1.005, "traffic_unit": "bytes per launch (average launch)",
                          "peak_source": which, "kernel": "gemv_mma_kernel<Q4_K>",
