@@ -12,13 +12,13 @@
 // with cap = max_tokens * n_used (a rank can send at most that many rows to one peer).  One layer is
 //
 //   route                                   (replicated router, local)
-//   dispatch   every (token, slot) pair's row is stored into its owner's rows_in, then flag_in[me] = epoch
-//   wait_in    one CTA polls flag_in[*] (bounded)
+//   dispatch   every (token, slot) pair's row is stored into its owner's rows_in, then flag_in[me] = epoch;
+//              its last thread polls flag_in[*] (bounded) before the kernel ends
 //   experts    grouped gate/up + SwiGLU and down products over rows_in (the single-GPU kernels)
 //   return     valid rows' outputs are stored into their source's rows_back, then flag_back[me] = epoch
 //   combine    polls flag_back[*] (bounded), y[t] = sum over slots in slot order of w * rows_back[...]
 //
-// No collective library call and no host read: the layer is nine kernel launches in one stream and can be
+// No collective library call and no host read: the layer is eight kernel launches in one stream and can be
 // replayed from a CUDA graph.  One window serves every layer of a model: a rank can only run one exchange
 // ahead of a peer, and the flags order every reuse (a peer's next dispatch needs my return of this layer,
 // which follows my last read of rows_in; my next return needs the peer's next dispatch, which follows its
@@ -78,8 +78,8 @@ __device__ void wait_flag(const uint32_t* flag, uint32_t target, int* status) {
 }
 
 // The last CTA of the grid to arrive publishes `epoch` in slot `me` of the given flag array of every peer.
-// All data stores of the grid are ordered before the flag stores.
-__device__ void publish(uint32_t* done, const Window& win, uint64_t flag_off, uint32_t world, uint32_t me,
+// All data stores of the grid are ordered before the flag stores.  Returns true in thread 0 of that last CTA.
+__device__ bool publish(uint32_t* done, const Window& win, uint64_t flag_off, uint32_t world, uint32_t me,
                         uint32_t epoch) {
     __threadfence_system();
     __syncthreads();
@@ -90,8 +90,10 @@ __device__ void publish(uint32_t* done, const Window& win, uint64_t flag_off, ui
             __threadfence_system();
             for (uint32_t d = 0; d < world; ++d)
                 st_release_sys(reinterpret_cast<uint32_t*>(win.base[d] + flag_off) + me, epoch);
+            return true;
         }
     }
+    return false;
 }
 
 // grid = P + world CTAs.  CTA p < P stores pair p's activation row and local expert id into its owner's
@@ -99,7 +101,7 @@ __device__ void publish(uint32_t* done, const Window& win, uint64_t flag_off, ui
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(Window win, Layout l, uint32_t me, const float* __restrict__ x,
                                                           const uint32_t* __restrict__ ids, uint32_t T, uint32_t K,
                                                           uint32_t* __restrict__ pair_slot, uint32_t* __restrict__ epoch,
-                                                          uint32_t* __restrict__ done) {
+                                                          uint32_t* __restrict__ done, int* status) {
     __shared__ uint32_t s_red[8];
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t P = T * K, tid = threadIdx.x;
@@ -134,19 +136,15 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(Window win, Layout l, 
         uint32_t* idd = reinterpret_cast<uint32_t*>(win.base[d] + l.o_ids_in) + (uint64_t)me * l.cap;
         for (uint32_t sl = cnt + tid; sl < l.cap; sl += blockDim.x) idd[sl] = l.n_local;
     }
-    publish(done, win, l.o_flag_in, l.world, me, next_epoch);
-}
-
-// One warp: waits for every rank's dispatch of the next epoch, then advances the local epoch counter; the
-// kernels behind it in the stream read rows_in / ids_in and the new epoch.
-__global__ void __launch_bounds__(32) ep_wait_in_kernel(const uint32_t* __restrict__ flag_in, uint32_t world,
-                                                        uint32_t* __restrict__ epoch, int* status) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t target = *epoch + 1;
-    __syncwarp();
-    if (threadIdx.x < world) wait_flag(flag_in + threadIdx.x, target, status);
-    __syncwarp();
-    if (threadIdx.x == 0) *epoch = target;
+    if (publish(done, win, l.o_flag_in, l.world, me, next_epoch)) {
+        // The publishing thread also waits (bounded) for every rank's dispatch of this epoch and then advances
+        // the local epoch counter: the kernels behind this one in the stream read rows_in / ids_in and the new
+        // epoch, so the kernel must not end before the rows are there.  Every CTA of this grid read the old
+        // epoch before it counted itself in.
+        for (uint32_t r = 0; r < l.world; ++r)
+            wait_flag(reinterpret_cast<const uint32_t*>(win.base[me] + l.o_flag_in) + r, next_epoch, status);
+        *epoch = next_epoch;
+    }
 }
 
 // grid = world * cap CTAs: row r of my rows_in (source rank r / cap, its slot r % cap).  A valid row's output,
@@ -322,9 +320,8 @@ int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float
     const uint32_t P = (uint32_t)T * e->n_used;
     if (int32_t r = jq_moe_route_dev(router, x_dev, T, nullptr, e->ids, e->wts, stream)) return r;
     JQ_CUDA(jq::launch_pdl(ep_dispatch_kernel, dim3(P + e->world), 256, 0, s, e->win, e->lay, e->rank, x_dev,
-                           (const uint32_t*)e->ids, (uint32_t)T, e->n_used, e->pair_slot, e->epoch, e->done));
-    JQ_CUDA(jq::launch_pdl(ep_wait_in_kernel, dim3(1), 32, 0, s,
-                           (const uint32_t*)(mine + e->lay.o_flag_in), e->world, e->epoch, e->ctx->status_dev));
+                           (const uint32_t*)e->ids, (uint32_t)T, e->n_used, e->pair_slot, e->epoch, e->done,
+                           e->ctx->status_dev));
     if (int32_t r = jq_moe_experts_list(experts, reinterpret_cast<const float*>(mine + e->lay.o_rows_in), rows,
                                         reinterpret_cast<const uint32_t*>(mine + e->lay.o_ids_in), s))
         return r;
