@@ -10,6 +10,8 @@ Workloads
   qwen3moe decode of a Qwen3-MoE-shaped model (128 experts top-8, Q4_K experts, Q8_0 attention);
            with --gpus N > 1 (under torchrun) the experts are split over the ranks and rows
            are exchanged by NCCL all-to-all.
+  moe_layer one routed-expert layer (--type, --experts, --used, --k hidden, --n expert width, --m tokens):
+           the grouped expert matmuls at a given token count.
   gemv     one quantized matmul shape, rotated over a working set larger than L2
            (--type, --n, --k, --m, --rotate-gb): the kernel-level roofline probe
            and the command used for ncu captures.
@@ -286,18 +288,75 @@ def run_gemv(args):
     print(json.dumps(line))
 
 
+def run_moe_layer(args):
+    """One routed-expert layer at a given token count: the grouped expert matmuls of the MoE configurations
+    (MXFP4 384 experts / IQ2_XXS 256 experts / Q4_K 128 experts), device-resident, CUDA events."""
+    import torch
+
+    from joshua_b200.moe import GATE_SOFTMAX, Moe, MoeConfig
+    from joshua_b200.qtensor import QTensor, default_context
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    t = TYPE_BY_NAME[args.type]
+    E, K, h, inter, T = args.experts, args.used, args.k, args.n, args.m
+    ctx = default_context(dev.index or 0)
+    banks, keep = [], []
+    for i, (rows, cols) in enumerate([(inter, h), (inter, h), (h, inter)]):
+        nbytes = synth.tensor_bytes(t, E * rows, cols)
+        raw = torch.cat([synth.random_weight_torch(t, E * rows, cols, 31 + i, dev), torch.zeros(16, dtype=torch.uint8, device=dev)])
+        keep.append(raw)
+        banks.append(QTensor.from_device(t, raw[:nbytes], ctx))
+    router = (np.random.default_rng(0).standard_normal((E, h)) * 0.5).astype(np.float32)
+    layer = Moe(MoeConfig(gating=GATE_SOFTMAX, n_expert=E, n_used=K, hidden=h, inter=inter, norm=True), router, *banks, ctx=ctx)
+    layer.reserve(T, T * K)
+    # a different token set every call, so that the experts touched change from call to call
+    xs = [torch.randn(T, h, device=dev) * 0.02 for _ in range(8)]
+    y = torch.empty(T, h, device=dev)
+    it = [0]
+
+    def step():
+        layer.forward_dev(xs[it[0] % len(xs)], y)
+        it[0] += 1
+
+    with ClockSampler(dev.index or 0) as clocks:
+        dt = cuda_time(step, args.steps, max(3, args.warmup))
+    layer.status()
+    per_expert = 2 * synth.tensor_bytes(t, inter, h) + synth.tensor_bytes(t, h, inter)
+    # expected number of distinct experts hit by T*K uniform picks
+    distinct = E * (1.0 - (1.0 - 1.0 / E) ** (T * K)) if T * K < 50 * E else float(E)
+    alg = distinct * per_expert + 8.0 * T * h
+    flops = 2.0 * T * K * 3 * h * inter
+    peak, which = measured_peaks()
+    line = {
+        "metric": "moe_layer_tokens_s", "value": T / dt, "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "i8xi8->i32, f32 scales", "data": "synthetic",
+        "config": {"workload": f"moe_layer {args.type} E={E} k={K} h={h} inter={inter} tokens={T}",
+                   "l2": "expert banks far larger than L2; tokens change every call"},
+        "roofline": {"bound": "hbm", "achieved": alg / dt / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": alg / dt / 1e9 / peak, "traffic": None, "peak_source": which,
+                     "note": "bytes of the expected number of distinct experts hit, read once",
+                     "tflops_algorithmic": flops / dt / 1e12},
+        "gpu_launches": 4 * args.steps, "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama8b", choices=["llama8b", "gemv", "qwen3moe"])
+    ap.add_argument("--workload", default="llama8b", choices=["llama8b", "gemv", "qwen3moe", "moe_layer"])
     ap.add_argument("--type", default="q4_k", choices=sorted(TYPE_BY_NAME))
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--rotate-gb", type=float, default=1.0)
+    ap.add_argument("--experts", type=int, default=384)
+    ap.add_argument("--used", type=int, default=8)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prefill", type=int, default=512)
     ap.add_argument("--chain", action="store_true",
@@ -307,6 +366,8 @@ def main():
         return run_reference(args)
     if args.workload == "gemv":
         return run_gemv(args)
+    if args.workload == "moe_layer":
+        return run_moe_layer(args)
     if args.workload == "qwen3moe":
         from joshua_b200 import bench_moe
 

@@ -140,6 +140,9 @@ cudaError_t launch_moe_jobs(const uint32_t* ids, uint32_t T, uint32_t K, uint32_
                             uint32_t* list_token, uint32_t* inv, MoeJob* jobs, uint32_t* n_jobs, uint32_t* n_list,
                             int* bad_id, cudaStream_t s);
 cudaError_t moe_set_trace(unsigned long long* dev_buf);
+// xs[pos, :] = x[list_token[pos], :] for pos < min(P, *n_list)
+cudaError_t launch_moe_gather(const float* x, const uint32_t* list_token, const uint32_t* n_list, uint32_t P, uint32_t h,
+                              float* xs, cudaStream_t s);
 // logits + routing (+ job list) in one launch for decode-sized batches; `counter`: a device word that is zero
 // between calls.  With norm_w the tokens are RMS-normalised inside the kernel.
 cudaError_t launch_moe_route_fused(const float* x, const float* norm_w, float eps, const float* router, uint32_t T,

@@ -135,6 +135,8 @@ struct jq_moe {
     uint32_t* one = nullptr;
     uint32_t* counter = nullptr;  // arrival counter of the fused router kernel (zero between calls)
     float* xn = nullptr;          // normalised tokens, for the paths that cannot fold the norm in
+    float* bucket = nullptr;      // prefill path: gathered rows [P, hidden] + gate and up products [2][P, inter]
+    uint64_t bucket_pairs = 0;
     int* bad_host = nullptr;  // pinned, device-visible: an expert id was out of range
     int* bad_dev = nullptr;
     std::mutex mu;

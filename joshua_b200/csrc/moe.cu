@@ -469,6 +469,22 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ g
     }
 }
 
+// xs[pos, :] = x[list_token[pos], :] for the expert-sorted list (pos < *n_list): the activation rows in bucket
+// order, so that an expert's rows are contiguous for a tile GEMM.
+__global__ void __launch_bounds__(256) moe_gather_kernel(const float* __restrict__ x, const uint32_t* __restrict__ list_token,
+                                                         const uint32_t* __restrict__ n_list, uint32_t P, uint32_t h,
+                                                         float* __restrict__ xs) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t live = min(P, *n_list), h4 = h / 4;
+    const uint64_t total = (uint64_t)live * h4;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t pos = (uint32_t)(i / h4), c = (uint32_t)(i % h4);
+        reinterpret_cast<float4*>(xs)[(uint64_t)pos * h4 + c] =
+            __ldg(reinterpret_cast<const float4*>(x) + (uint64_t)list_token[pos] * h4 + c);
+    }
+}
+
 unsigned blocks_for(uint64_t work, unsigned per_block) {
     uint64_t b = (work + per_block - 1) / per_block;
     return (unsigned)(b < 1 ? 1 : (b > 148ull * 16 ? 148ull * 16 : b));
@@ -497,6 +513,14 @@ cudaError_t launch_moe_jobs(const uint32_t* ids, uint32_t T, uint32_t K, uint32_
     if (E > MAX_EXPERTS) return cudaErrorInvalidValue;
     cudaError_t le3__ = launch_pdl(moe_jobs_kernel, 1, 1024, 0, s, ids, T, K, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id);
     if (le3__ != cudaSuccess) return le3__;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_gather(const float* x, const uint32_t* list_token, const uint32_t* n_list, uint32_t P, uint32_t h,
+                              float* xs, cudaStream_t s) {
+    cudaError_t e = launch_pdl(moe_gather_kernel, blocks_for((uint64_t)P * (h / 4), 256), 256, 0, s, x, list_token, n_list,
+                               P, h, xs);
+    if (e != cudaSuccess) return e;
     return cudaGetLastError();
 }
 

@@ -119,6 +119,70 @@ int32_t run_experts(jq_moe* m, const float* x, uint64_t R, uint64_t P, uint32_t 
 }
 
 // sh_out[T, hidden] = shared expert MLP over all tokens
+// The prefill form of the expert MLPs, as the reference buckets tokens per expert and runs one matmul per
+// bucket (src/quantized_qwen3_moe.rs:455-520): when an expert sees dozens of rows, its rows are gathered into
+// bucket order and every expert's gate / up / down product is one call of the batched matmul (tile GEMM on the
+// tensor cores for more than 64 rows).  The expert histogram is read back to the host once, which synchronises
+// the stream.
+int32_t run_experts_bucketed(jq_moe* m, const float* x, uint64_t T, uint64_t P, cudaStream_t s) {
+    const jq_moe_config& c = m->cfg;
+    if (P > m->bucket_pairs) {
+        if (m->bucket) cudaFree(m->bucket);
+        m->bucket = nullptr;
+        m->bucket_pairs = 0;
+        JQ_CUDA(cudaMalloc(&m->bucket, (P * c.hidden + 2 * P * c.inter) * sizeof(float)));
+        m->bucket_pairs = P;
+    }
+    float* xs = m->bucket;
+    float* gbuf = xs + P * c.hidden;
+    float* ubuf = gbuf + P * c.inter;
+    uint32_t n_jobs = 0;
+    JQ_CUDA(cudaMemcpyAsync(&n_jobs, m->n_jobs, sizeof(n_jobs), cudaMemcpyDeviceToHost, s));
+    JQ_CUDA(cudaStreamSynchronize(s));
+    std::vector<jq::MoeJob> jobs(n_jobs);
+    if (n_jobs) JQ_CUDA(cudaMemcpyAsync(jobs.data(), m->jobs, n_jobs * sizeof(jq::MoeJob), cudaMemcpyDeviceToHost, s));
+    JQ_CUDA(jq::launch_moe_gather(x, m->list_token, m->n_list, (uint32_t)P, c.hidden, xs, s));
+    JQ_CUDA(cudaStreamSynchronize(s));
+    // consecutive jobs of one expert form its bucket
+    struct Bucket {
+        uint32_t expert, row0, cnt;
+    };
+    std::vector<Bucket> buckets;
+    for (const jq::MoeJob& j : jobs) {
+        if (!buckets.empty() && buckets.back().expert == j.expert && buckets.back().row0 + buckets.back().cnt == j.row0)
+            buckets.back().cnt += j.cnt;
+        else
+            buckets.push_back({j.expert, j.row0, j.cnt});
+    }
+    auto slice = [&](const jq_weight* bank, uint64_t expert_bytes, uint32_t e) {
+        jq_weight w = *bank;
+        w.dev = bank->dev + (uint64_t)e * expert_bytes;
+        w.n_blocks = expert_bytes / bank->fmt.bytes;
+        w.owns = false;
+        return w;
+    };
+    for (const Bucket& b : buckets) {
+        const jq_weight wg = slice(m->gate, m->gate_expert_bytes, b.expert), wu = slice(m->up, m->gate_expert_bytes, b.expert);
+        if (int32_t rc = jq_matmul_device(&wg, b.cnt, c.hidden, c.inter, xs + (uint64_t)b.row0 * c.hidden,
+                                          gbuf + (uint64_t)b.row0 * c.inter, s))
+            return rc;
+        if (int32_t rc = jq_matmul_device(&wu, b.cnt, c.hidden, c.inter, xs + (uint64_t)b.row0 * c.hidden,
+                                          ubuf + (uint64_t)b.row0 * c.inter, s))
+            return rc;
+    }
+    uint64_t live = 0;
+    for (const Bucket& b : buckets) live = std::max<uint64_t>(live, (uint64_t)b.row0 + b.cnt);
+    if (live) JQ_CUDA(jq::launch_swiglu(gbuf, ubuf, live * c.inter, c.clamp, m->hidden, s));
+    for (const Bucket& b : buckets) {
+        const jq_weight wd = slice(m->down, m->down_expert_bytes, b.expert);
+        if (int32_t rc = jq_matmul_device(&wd, b.cnt, c.inter, c.hidden, m->hidden + (uint64_t)b.row0 * c.inter,
+                                          m->out + (uint64_t)b.row0 * c.hidden, s))
+            return rc;
+    }
+    (void)T;
+    return jq::OK;
+}
+
 bool shared_mma_ok(jq_moe* m, uint64_t T) {
     const jq_moe_config& c = m->cfg;
     return T <= 8 && !m->ctx->force_f32 &&
@@ -278,6 +342,7 @@ void jq_moe_free(jq_moe* m) {
     cudaFree(m->router);
     cudaFree(m->bias);
     cudaFree(m->ws);
+    cudaFree(m->bucket);
     cudaFree(m->dense_jobs);
     cudaFree(m->one);
     if (m->bad_host) cudaFreeHost(m->bad_host);
@@ -367,7 +432,16 @@ int32_t jq_moe_forward_norm_add_dev(jq_moe* m, const float* x_dev, uint64_t T, c
         JQ_CUDA(jq::launch_moe_jobs(m->ids, (uint32_t)T, c.n_used, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
                                     m->n_jobs, m->n_list, m->bad_dev, s));
     }
-    if (int32_t rc = run_experts(m, x_in, T, P, rpj, s, nw, eps)) return rc;
+    // prefill-sized batches (hundreds of rows per expert on average): one batched matmul per expert bucket.
+    // Measured on 384 MXFP4 experts of 7168 x 2048 at 4096 tokens (85 rows per expert): 322 ms this way against
+    // 127 ms for the grouped decode kernel, because one expert's tile GEMM fills 16 of 148 SMs; the crossover
+    // needs buckets of several token tiles, hence the threshold.
+    const bool bucketed = !fused && !m->ctx->force_f32 && P >= 256ull * c.n_expert;
+    if (bucketed) {
+        if (int32_t rc = run_experts_bucketed(m, x_in, T, P, s)) return rc;
+    } else if (int32_t rc = run_experts(m, x_in, T, P, rpj, s, nw, eps)) {
+        return rc;
+    }
     const float* shared = nullptr;
     if (m->sh_gate) {
         if (int32_t rc = run_shared(m, x_in, T, s, nw, eps)) return rc;

@@ -52,7 +52,7 @@ def tokens(T, h, seed):
     return (np.random.default_rng(seed).standard_normal((T, h)) * 0.02).astype(np.float32)
 
 
-@pytest.mark.parametrize("T", [1, 2, 5, 16, 70])
+@pytest.mark.parametrize("T", [1, 2, 5, 16, 70, 1100])   # 1100 tokens: the bucketed (one matmul per expert) path
 def test_qwen3moe_style(T):
     cfg = MoeConfig(gating=GATE_SOFTMAX, n_expert=16, n_used=4, hidden=512, inter=256, norm=True)
     moe, router, banks, types, _ = build(cfg, synth.Q4_K, seed=7)
@@ -65,7 +65,7 @@ def test_qwen3moe_style(T):
     assert_close(got, want, what=f"qwen3moe T={T}")
 
 
-@pytest.mark.parametrize("T", [1, 3, 33])
+@pytest.mark.parametrize("T", [1, 3, 33, 2100])   # 2100 tokens: bucketed experts + batched shared expert
 def test_deepseek2_style_sigmoid_groups_bias_shared(T):
     cfg = MoeConfig(gating=GATE_SIGMOID, n_expert=32, n_used=4, hidden=512, inter=256, n_group=8, topk_group=4,
                     norm=True, scale=2.5)
