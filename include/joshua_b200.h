@@ -293,7 +293,7 @@ int32_t jq_moe_forward(jq_moe* m, const float* x, uint64_t n_tokens, const uint3
 int32_t jq_moe_reserve(jq_moe* m, uint64_t n_tokens, uint64_t n_rows);
 
 /* The same with DEVICE buffers on a caller stream.  No synchronisation for decode-sized and moderate batches;
- * when n_tokens * n_used >= 256 * n_expert (prefill) the call reads the expert histogram back once, which
+ * when n_tokens * n_used >= 64 * n_expert (192 * n_expert for experts under 8 M weights; prefill) the call reads the expert histogram back once, which
  * synchronises the stream, and may allocate: such batches cannot be captured in a CUDA graph. */
 int32_t jq_moe_forward_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, const uint32_t* forced_ids_dev,
                            float* y_dev, void* stream);

@@ -137,6 +137,8 @@ struct jq_moe {
     float* xn = nullptr;          // normalised tokens, for the paths that cannot fold the norm in
     float* bucket = nullptr;      // prefill path: gathered rows [P, hidden] + gate and up products [2][P, inter]
     uint64_t bucket_pairs = 0;
+    cudaStream_t aux[8] = {};     // prefill path: the experts' matmuls are spread over these streams
+    cudaEvent_t fork_ev = nullptr, join_ev[8] = {};
     int* bad_host = nullptr;  // pinned, device-visible: an expert id was out of range
     int* bad_dev = nullptr;
     std::mutex mu;
