@@ -174,6 +174,11 @@ void jq_free(jq_ctx* ctx) {
     cudaSetDevice(ctx->device);
     cudaDeviceSynchronize();
     for (auto& kv : ctx->scratch) cudaFree(kv.second.dev);
+    for (int i = 0; i < 8; ++i) {
+        if (ctx->aux[i]) cudaStreamDestroy(ctx->aux[i]);
+        if (ctx->join_ev[i]) cudaEventDestroy(ctx->join_ev[i]);
+    }
+    if (ctx->fork_ev) cudaEventDestroy(ctx->fork_ev);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     for (Workspace* w : ctx->idle) {
         cudaStreamSynchronize(w->stream);

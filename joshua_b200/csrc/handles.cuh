@@ -54,6 +54,11 @@ struct jq_ctx {
     int* status_host = nullptr;    // pinned, device-visible: set to 1 by a kernel whose bounded wait gave up
     int* status_dev = nullptr;
     std::mutex mu;
+    // MoE prefill path: the experts' matmuls are spread over these streams (created on first use, shared by all
+    // layers of the context; `aux_mu` serialises the host-side fork / launch / join sequences that use them)
+    std::mutex aux_mu;
+    cudaStream_t aux[8] = {};
+    cudaEvent_t fork_ev = nullptr, join_ev[8] = {};
     std::vector<Workspace*> idle;
     std::map<cudaStream_t, StreamScratch> scratch;
 
@@ -137,8 +142,6 @@ struct jq_moe {
     float* xn = nullptr;          // normalised tokens, for the paths that cannot fold the norm in
     float* bucket = nullptr;      // prefill path: gathered rows [P, hidden] + gate and up products [2][P, inter]
     uint64_t bucket_pairs = 0;
-    cudaStream_t aux[8] = {};     // prefill path: the experts' matmuls are spread over these streams
-    cudaEvent_t fork_ev = nullptr, join_ev[8] = {};
     int* bad_host = nullptr;  // pinned, device-visible: an expert id was out of range
     int* bad_dev = nullptr;
     std::mutex mu;

@@ -164,30 +164,32 @@ int32_t run_experts_bucketed(jq_moe* m, const float* x, uint64_t T, uint64_t P, 
     // One expert's product fills only a fraction of the GPU (n / 128 CTAs), so the buckets are dealt to eight
     // auxiliary streams that fork from and join the caller's stream around each phase.
     constexpr int NAUX = 8;
-    if (!m->fork_ev) {
-        JQ_CUDA(cudaEventCreateWithFlags(&m->fork_ev, cudaEventDisableTiming));
+    jq_ctx* cx = m->ctx;
+    std::lock_guard<std::mutex> aux_lock(cx->aux_mu);
+    if (!cx->fork_ev) {
+        JQ_CUDA(cudaEventCreateWithFlags(&cx->fork_ev, cudaEventDisableTiming));
         for (int i = 0; i < NAUX; ++i) {
-            JQ_CUDA(cudaStreamCreateWithFlags(&m->aux[i], cudaStreamNonBlocking));
-            JQ_CUDA(cudaEventCreateWithFlags(&m->join_ev[i], cudaEventDisableTiming));
+            JQ_CUDA(cudaStreamCreateWithFlags(&cx->aux[i], cudaStreamNonBlocking));
+            JQ_CUDA(cudaEventCreateWithFlags(&cx->join_ev[i], cudaEventDisableTiming));
         }
     }
     auto fork = [&]() -> cudaError_t {
-        cudaError_t e = cudaEventRecord(m->fork_ev, s);
-        for (int i = 0; i < NAUX && e == cudaSuccess; ++i) e = cudaStreamWaitEvent(m->aux[i], m->fork_ev, 0);
+        cudaError_t e = cudaEventRecord(cx->fork_ev, s);
+        for (int i = 0; i < NAUX && e == cudaSuccess; ++i) e = cudaStreamWaitEvent(cx->aux[i], cx->fork_ev, 0);
         return e;
     };
     auto join = [&]() -> cudaError_t {
         cudaError_t e = cudaSuccess;
         for (int i = 0; i < NAUX && e == cudaSuccess; ++i) {
-            e = cudaEventRecord(m->join_ev[i], m->aux[i]);
-            if (e == cudaSuccess) e = cudaStreamWaitEvent(s, m->join_ev[i], 0);
+            e = cudaEventRecord(cx->join_ev[i], cx->aux[i]);
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(s, cx->join_ev[i], 0);
         }
         return e;
     };
     JQ_CUDA(fork());
     for (size_t bi = 0; bi < buckets.size(); ++bi) {
         const Bucket& b = buckets[bi];
-        cudaStream_t as = m->aux[bi % NAUX];
+        cudaStream_t as = cx->aux[bi % NAUX];
         const jq_weight wg = slice(m->gate, m->gate_expert_bytes, b.expert), wu = slice(m->up, m->gate_expert_bytes, b.expert);
         if (int32_t rc = jq_matmul_device(&wg, b.cnt, c.hidden, c.inter, xs + (uint64_t)b.row0 * c.hidden,
                                           gbuf + (uint64_t)b.row0 * c.inter, as))
@@ -205,7 +207,7 @@ int32_t run_experts_bucketed(jq_moe* m, const float* x, uint64_t T, uint64_t P, 
         const Bucket& b = buckets[bi];
         const jq_weight wd = slice(m->down, m->down_expert_bytes, b.expert);
         if (int32_t rc = jq_matmul_device(&wd, b.cnt, c.inter, c.hidden, m->hidden + (uint64_t)b.row0 * c.inter,
-                                          m->out + (uint64_t)b.row0 * c.hidden, m->aux[bi % NAUX]))
+                                          m->out + (uint64_t)b.row0 * c.hidden, cx->aux[bi % NAUX]))
             return rc;
     }
     JQ_CUDA(join());
@@ -373,11 +375,6 @@ void jq_moe_free(jq_moe* m) {
     cudaFree(m->bias);
     cudaFree(m->ws);
     cudaFree(m->bucket);
-    for (int i = 0; i < 8; ++i) {
-        if (m->aux[i]) cudaStreamDestroy(m->aux[i]);
-        if (m->join_ev[i]) cudaEventDestroy(m->join_ev[i]);
-    }
-    if (m->fork_ev) cudaEventDestroy(m->fork_ev);
     cudaFree(m->dense_jobs);
     cudaFree(m->one);
     if (m->bad_host) cudaFreeHost(m->bad_host);
