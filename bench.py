@@ -359,8 +359,6 @@ def main():
     ap.add_argument("--used", type=int, default=8)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prefill", type=int, default=512)
-    ap.add_argument("--chain", action="store_true",
-                    help="llama8b: layers + head as one persistent chain launch instead of five launches per layer")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

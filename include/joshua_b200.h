@@ -67,7 +67,8 @@ void jq_free(jq_ctx* ctx);
 /* Every wait inside a kernel (on a copy in flight) is bounded; a kernel whose
  * wait runs out sets a device-visible flag and returns.  Host-buffer entries
  * check the flag themselves; callers of the *_dev entries poll it here after
- * synchronising their stream.  JQ_OK or JQ_E_TIMEOUT.  (The reference's
+ * synchronising their stream.  JQ_OK or JQ_E_TIMEOUT; a reported timeout is
+ * cleared, so the next call answers for the work after it.  (The reference's
  * counterpart is the deadline handling of its plugin shim, src/npu/shim.rs:1-8.) */
 int32_t jq_device_status(const jq_ctx* ctx);
 
@@ -208,30 +209,37 @@ int32_t jq_matmul_norm_dev(const jq_weight* w, uint64_t m, uint64_t k, uint64_t 
 /* Rotary embedding of q and k (pairing element i with i + head_dim/2) at
  * position pos[b], then k and v appended to the cache: the rope + `Tensor::cat`
  * of src/quantized_qwen3_moe.rs:330-364.  qkv: [batch, (n_q + 2 n_kv) *
- * head_dim]; cache_k, cache_v: [batch, n_kv, max_ctx, head_dim]. */
+ * head_dim]; cache_k, cache_v: [batch, n_kv, max_ctx, head_dim].  The cache
+ * holds max_ctx positions (the reference stops generating at n_ctx,
+ * src/engine.rs:1246-1249): a sequence whose pos[b] is negative or >= max_ctx
+ * stores nothing and sets *bad_pos_dev (device int32, may be NULL) to 1. */
 int32_t jq_rope_append_dev(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t n_q, uint32_t n_kv,
                            uint32_t head_dim, uint32_t max_ctx, float theta, float* q_out, float* cache_k,
-                           float* cache_v, void* stream);
+                           float* cache_v, int32_t* bad_pos_dev, void* stream);
 
 /* Rope, cache append and attention in ONE launch, straight from the fused qkv
  * row: out[b, head, :] as jq_rope_append_dev + jq_attention_decode_dev give it.
  * `scratch`: jq_attention_fused_scratch_bytes(...) bytes of caller device
  * memory, ZEROED once before the first call (it holds arrival counters that
- * the kernel leaves at zero).  head_dim 64, 128 or 256; n_q / n_kv 1, 2, 4 or 8. */
+ * the kernel leaves at zero).  head_dim 64, 128 or 256; n_q / n_kv 1, 2, 4 or 8.
+ * A sequence whose pos[b] lies outside [0, max_ctx) is skipped entirely - no
+ * cache store, its rows of `out` untouched - and *bad_pos_dev (may be NULL) is
+ * set to 1. */
 uint64_t jq_attention_fused_scratch_bytes(uint32_t batch, uint32_t n_q, uint32_t n_kv, uint32_t head_dim,
                                           uint32_t max_ctx);
 int32_t jq_attention_fused_dev(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t n_q, uint32_t n_kv,
                                uint32_t head_dim, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,
-                               float* out, void* scratch, void* stream);
+                               float* out, void* scratch, int32_t* bad_pos_dev, void* stream);
 
 /* Grouped-query attention of one new token per sequence over positions
  * 0..pos[b] of the cache (src/quantized_qwen3_moe.rs:366-386).  `scratch`:
  * jq_attention_scratch_bytes(...) bytes of caller device memory (per-chunk
- * partial results, merged in position order). */
+ * partial results, merged in position order).  pos[b] outside [0, max_ctx)
+ * reads nothing, gives NaN rows and sets *bad_pos_dev (may be NULL). */
 uint64_t jq_attention_scratch_bytes(uint32_t batch, uint32_t n_q, uint32_t head_dim, uint32_t max_ctx);
 int32_t jq_attention_decode_dev(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,
                                 uint32_t batch, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t max_ctx,
-                                float* out, float* scratch, void* stream);
+                                float* out, float* scratch, int32_t* bad_pos_dev, void* stream);
 
 int32_t jq_add_dev(const float* a, const float* b, uint64_t n, float* y, void* stream);
 
@@ -241,6 +249,21 @@ int32_t jq_add_dev(const float* a, const float* b, uint64_t n, float* y, void* s
 uint64_t jq_argmax_scratch_bytes(uint64_t rows);
 int32_t jq_argmax_dev(const float* logits, uint64_t rows, uint64_t vocab, int32_t* token, int32_t* pos, void* scratch,
                       void* stream);
+
+/* The reference's greedy sampler with its repetition penalty (sample_token,
+ * src/engine.rs:2339-2378; default penalty 1.1): for every occurrence of a
+ * token id in the recent window its logit is divided by the penalty when
+ * positive and multiplied by it otherwise, then the arg-max (last maximal index)
+ * is taken, and the sampled id is pushed into the window, which holds the last
+ * JQ_SAMPLE_WINDOW ids (src/engine.rs:1222-1232,1265-1269).  `logits` is left
+ * as it was.  window: device int32 [rows, JQ_SAMPLE_WINDOW]; window_state:
+ * device int32 [rows, 2] = {ids held, slot the next id goes to}; seed both
+ * with the tail of the prompt, or zero them.  window and window_state NULL =
+ * jq_argmax_dev.  `scratch` as for jq_argmax_dev. */
+#define JQ_SAMPLE_WINDOW 64
+int32_t jq_sample_greedy_dev(const float* logits, uint64_t rows, uint64_t vocab, float repetition_penalty,
+                             int32_t* window, int32_t* window_state, int32_t* token, int32_t* pos, void* scratch,
+                             void* stream);
 
 /* ── MoE layer ───────────────────────────────────────────────────────────
  * Replaces `Moe::forward` of the three loaders: routing, per-expert gather,
@@ -319,49 +342,12 @@ int32_t jq_moe_route_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, const
 int32_t jq_moe_experts_dev(jq_moe* m, const float* x_dev, uint64_t n_rows, const uint32_t* expert_ids_dev,
                            float* out_dev, void* stream);
 
-/* Profiling aid: with a device buffer of 256 uint64, CTA (0, 0) of the tile GEMM stores four GPU nanosecond
- * timestamps per K step for its first 64 steps (stage free, stage handed over, operands complete, MMAs
- * issued); NULL = off. */
-int32_t jq_debug_gemm_trace(uint64_t* trace_dev);
-
-/* Profiling aid: with a device buffer of 8 uint64 the last CTA of the decode router kernel stores the GPU
- * nanosecond timer at its phases (entered, logits stored, counted in, routed, jobs built); NULL = off. */
-int32_t jq_debug_moe_trace(uint64_t* trace_dev);
-
 /* After synchronising: JQ_E_EXPERT_RANGE if an id was out of range under
  * oob_policy 0, JQ_E_TIMEOUT as jq_device_status, else JQ_OK. */
 int32_t jq_moe_status(jq_moe* m);
 
 /* ids and weights chosen by the last forward (host copies), for inspection. */
 int32_t jq_moe_last_routing(jq_moe* m, uint64_t n_tokens, uint32_t* ids, float* wts);
-
-/* ── A decode chain: many dependent steps in one launch ────────────────
- * No counterpart in the reference (its steps are separate candle ops).  A
- * chain is a fixed list of operations over fixed device buffers: quantized
- * linears in the forms of jq_matmul_norm_dev / jq_matmul_swiglu_norm_dev (w_up
- * non-NULL = the gate / up SwiGLU pair) and attention steps as
- * jq_attention_fused_dev, run in order by one persistent kernel whose CTAs
- * synchronise on a device counter between operations while the next
- * operation's weights are already streaming in.  All linears share the block
- * type given at creation (Q4_K or Q8_0) and the batch m (1..8).  The first
- * jq_chain_run uploads the list (it allocates: run once before capturing a
- * stream); after it the chain cannot grow.  The kernel needs every SM of the
- * device for itself (cooperative launch).  Results are those of the separate
- * entries, operation by operation. */
-typedef struct jq_chain jq_chain;
-int32_t jq_chain_create(jq_ctx* ctx, uint32_t type, uint32_t m, jq_chain** out);
-void jq_chain_free(jq_chain* c);
-int32_t jq_chain_add_linear(jq_chain* c, const jq_weight* w, const jq_weight* w_up, uint64_t k, uint64_t n,
-                            const float* x_dev, const float* norm_w_dev, float eps, const float* residual_dev,
-                            float clamp, float* dst_dev);
-int32_t jq_chain_add_attention(jq_chain* c, const float* qkv, const int32_t* pos, uint32_t n_q, uint32_t n_kv,
-                               uint32_t head_dim, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,
-                               float* out, void* scratch);
-int32_t jq_chain_run(jq_chain* c, void* stream);
-/* Profiling aid: with a device buffer of 3 * (number of operations) uint64, CTA 0 of later runs stores the
- * GPU nanosecond timer when it enters each operation, when its activations are split, and after its last
- * store.  NULL switches it off. */
-int32_t jq_chain_set_trace(jq_chain* c, uint64_t* trace_dev);
 
 /* ── Expert-parallel exchange: one process per GPU, experts split contiguously over the ranks ──
  * No counterpart in the reference, which runs every expert of a layer in one
@@ -387,8 +373,14 @@ int32_t jq_chain_set_trace(jq_chain* c, uint64_t* trace_dev);
  *                  rank must call it the same number of times in the same
  *                  order, one exchange per call.  residual_dev (optional, may be
  *                  y_dev) is added to the result.  Waits on peers are bounded
- *                  (about a second): a rank that never arrives is reported by
- *                  jq_device_status as JQ_E_TIMEOUT instead of a hang. */
+ *                  (about a second by default): a rank that never arrives is
+ *                  reported by jq_device_status as JQ_E_TIMEOUT instead of a hang.
+ *   jq_ep_set_poll_limit  the bound of those waits, in polls of a peer flag
+ *                  (a poll costs 0.2 - 1 us; 0 restores the default of 2^22)
+ *   jq_ep_connect_loopback  instead of jq_ep_connect: every peer window becomes a
+ *                  private allocation on this device that nobody serves.  For
+ *                  single-GPU tests of the wait bound and of the addressing; the
+ *                  waits on the absent peers run out and are reported. */
 #define JQ_EP_HANDLE_BYTES 64
 typedef struct jq_ep jq_ep;
 int32_t jq_ep_create(jq_ctx* ctx, uint32_t rank, uint32_t world, uint32_t n_expert, uint32_t n_used, uint32_t hidden,
@@ -396,6 +388,8 @@ int32_t jq_ep_create(jq_ctx* ctx, uint32_t rank, uint32_t world, uint32_t n_expe
 void jq_ep_free(jq_ep* e);
 int32_t jq_ep_export(jq_ep* e, uint8_t* handle);
 int32_t jq_ep_connect(jq_ep* e, const uint8_t* handles);
+int32_t jq_ep_connect_loopback(jq_ep* e);
+int32_t jq_ep_set_poll_limit(jq_ep* e, uint32_t polls);
 int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float* x_dev, uint64_t n_tokens,
                           const float* residual_dev, float* y_dev, void* stream);
 

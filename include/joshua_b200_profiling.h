@@ -1,0 +1,26 @@
+/* joshua_b200 - profiling aids, exported only by builds made with -DJQ_PROFILING
+ * (python -m joshua_b200.build --profiling).  Release builds do not contain these entry
+ * points, nor the measurement switches read from the environment (JQ_DEBUG_TC_SKIP,
+ * JQ_NO_NARROW_K, JQ_MOE_BUCKET_ROWS).  No counterpart in the reference. */
+#ifndef JOSHUA_B200_PROFILING_H
+#define JOSHUA_B200_PROFILING_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Profiling aid: with a device buffer of 256 uint64, CTA (0, 0) of the tile GEMM stores four GPU nanosecond
+ * timestamps per K step for its first 64 steps (stage free, stage handed over, operands complete, MMAs
+ * issued); NULL = off. */
+int32_t jq_debug_gemm_trace(uint64_t* trace_dev);
+
+/* Profiling aid: with a device buffer of 8 uint64 the last CTA of the decode router kernel stores the GPU
+ * nanosecond timer at its phases (entered, logits stored, counted in, routed, jobs built); NULL = off. */
+int32_t jq_debug_moe_trace(uint64_t* trace_dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JOSHUA_B200_PROFILING_H */

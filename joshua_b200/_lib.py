@@ -52,12 +52,13 @@ _SIGNATURES = {
     "jq_matmul_swiglu_dev": (i32, [vp, vp, u64, u64, u64, vp, vp, ctypes.c_float, vp]),
     "jq_embedding_dev": (i32, [vp, vp, u64, u64, u64, vp, vp, vp]),
     "jq_rmsnorm_dev": (i32, [vp, vp, vp, ctypes.c_float, u64, u64, vp, vp, vp]),
-    "jq_rope_append_dev": (i32, [vp, vp, u32, u32, u32, u32, u32, ctypes.c_float, vp, vp, vp, vp]),
+    "jq_rope_append_dev": (i32, [vp, vp, u32, u32, u32, u32, u32, ctypes.c_float, vp, vp, vp, vp, vp]),
     "jq_attention_scratch_bytes": (u64, [u32, u32, u32, u32]),
-    "jq_attention_decode_dev": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp, vp, vp]),
+    "jq_attention_decode_dev": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp, vp, vp, vp]),
     "jq_add_dev": (i32, [vp, vp, u64, vp, vp]),
     "jq_argmax_scratch_bytes": (u64, [u64]),
     "jq_argmax_dev": (i32, [vp, u64, u64, vp, vp, vp, vp]),
+    "jq_sample_greedy_dev": (i32, [vp, u64, u64, f32, vp, vp, vp, vp, vp, vp]),
     "jq_moe_create": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, pp]),
     "jq_moe_free": (None, [vp]),
     "jq_moe_forward": (i32, [vp, vp, u64, vp, vp]),
@@ -66,26 +67,26 @@ _SIGNATURES = {
     "jq_moe_route_dev": (i32, [vp, vp, u64, vp, vp, vp, vp]),
     "jq_moe_experts_dev": (i32, [vp, vp, u64, vp, vp, vp]),
     "jq_moe_status": (i32, [vp]),
-    "jq_debug_moe_trace": (i32, [vp]),
-    "jq_debug_gemm_trace": (i32, [vp]),
     "jq_moe_last_routing": (i32, [vp, u64, vp, vp]),
-    "jq_chain_create": (i32, [vp, u32, u32, ctypes.POINTER(vp)]),
-    "jq_chain_free": (None, [vp]),
-    "jq_chain_add_linear": (i32, [vp, vp, vp, u64, u64, vp, vp, f32, vp, f32, vp]),
-    "jq_chain_add_attention": (i32, [vp, vp, vp, u32, u32, u32, u32, f32, vp, vp, vp, vp]),
-    "jq_chain_run": (i32, [vp, vp]),
-    "jq_chain_set_trace": (i32, [vp, vp]),
     "jq_ep_create": (i32, [vp, u32, u32, u32, u32, u32, u32, ctypes.POINTER(vp)]),
     "jq_ep_free": (None, [vp]),
     "jq_ep_export": (i32, [vp, vp]),
     "jq_ep_connect": (i32, [vp, vp]),
+    "jq_ep_connect_loopback": (i32, [vp]),
+    "jq_ep_set_poll_limit": (i32, [vp, u32]),
     "jq_ep_forward_dev": (i32, [vp, vp, vp, vp, u64, vp, vp, vp]),
     "jq_moe_forward_add_dev": (i32, [vp, vp, u64, vp, vp, vp, vp]),
     "jq_moe_forward_norm_add_dev": (i32, [vp, vp, u64, vp, vp, f32, vp, vp, vp]),
     "jq_matmul_swiglu_norm_dev": (i32, [vp, vp, u64, u64, u64, vp, vp, f32, vp, f32, vp]),
     "jq_matmul_norm_dev": (i32, [vp, u64, u64, u64, vp, vp, f32, vp, vp, vp]),
     "jq_attention_fused_scratch_bytes": (u64, [u32, u32, u32, u32, u32]),
-    "jq_attention_fused_dev": (i32, [vp, vp, u32, u32, u32, u32, u32, f32, vp, vp, vp, vp, vp]),
+    "jq_attention_fused_dev": (i32, [vp, vp, u32, u32, u32, u32, u32, f32, vp, vp, vp, vp, vp, vp]),
+}
+
+
+_PROFILING_SIGNATURES = {
+    "jq_debug_moe_trace": (i32, [vp]),
+    "jq_debug_gemm_trace": (i32, [vp]),
 }
 
 
@@ -102,6 +103,11 @@ def lib() -> ctypes.CDLL:
             fn = getattr(handle, name)
             fn.restype = res
             fn.argtypes = args
+        for name, (res, args) in _PROFILING_SIGNATURES.items():  # present in profiling builds only
+            fn = getattr(handle, name, None)
+            if fn is not None:
+                fn.restype = res
+                fn.argtypes = args
         _lib = handle
     return _lib
 

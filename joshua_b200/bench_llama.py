@@ -59,8 +59,7 @@ def run(args):
                 fn()
         return g
 
-    use_chain = bool(getattr(args, 'chain', False))
-    step_graph = capture(model.step_chain if use_chain else model.step)
+    step_graph = capture(model.step)
     mm_graph = capture(model.matmuls_only)
     with torch.cuda.stream(stream):
         model.reset(42)
@@ -152,7 +151,7 @@ def run(args):
                        "vocab": c.vocab, "batch": batch, "prefill": args.prefill,
                        "step": "full decode step on the device (embedding, norms, RoPE, attention over the KV cache, "
                                "quantized matmuls, greedy arg-max), one CUDA graph; "
-                               + ("layers + head in one persistent chain launch" if use_chain else "five launches per layer"),
+                               "five launches per layer",
                        "l2": "4.22 GB of weights per step, far larger than L2", "parallelism": f"replicas x{world}"},
             "e2e": {"value": world * batch / e2e_dt, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "how": "model-level call with host buffers (LlamaDecoder.forward_host, the shape of the "
@@ -168,7 +167,7 @@ def run(args):
                          "peak_source": which, "kernel": "gemv_mma_kernel<Q4_K>",
                          "launches_per_step": launches, "avg_launch_us": dt_mm / launches * 1e6,
                          "bytes_per_step": alg},
-            "gpu_launches": (4 if use_chain else model.launches_per_step) * args.steps, "clocks": clocks.summary(),
+            "gpu_launches": model.launches_per_step * args.steps, "clocks": clocks.summary(),
         }
         try:
             base = cpu_llama_sample(seconds_budget=12.0)

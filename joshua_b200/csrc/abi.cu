@@ -93,16 +93,23 @@ int32_t jq_matmul_device(const jq_weight* w, uint64_t m, uint64_t k, uint64_t n,
     return jq::OK;
 }
 
+#ifdef JQ_PROFILING
 extern "C" int32_t jq_debug_gemm_trace(uint64_t* trace_dev) {
     jq::gemm_tc_set_trace(reinterpret_cast<unsigned long long*>(trace_dev));
     return jq::OK;
 }
+#endif
 
 namespace {
 
+// Reports a kernel wait that gave up, once: the flag is cleared as it is reported, so that one late peer or one
+// lost copy does not fail every later call on the context.
 int32_t check_device_status(const jq_ctx* ctx) {
-    if (ctx->status_host && *static_cast<volatile int*>(ctx->status_host) != 0)
-        return jq_fail(jq::E_TIMEOUT, "a bounded wait inside a kernel gave up (device status flag is set)");
+    volatile int* flag = static_cast<volatile int*>(ctx->status_host);
+    if (flag && *flag != 0) {
+        *flag = 0;
+        return jq_fail(jq::E_TIMEOUT, "a bounded wait inside a kernel gave up (device status flag was set)");
+    }
     return jq::OK;
 }
 

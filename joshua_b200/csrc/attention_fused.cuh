@@ -1,6 +1,5 @@
 // Rope + KV-cache append + attention over the cache + merge for one new token per sequence, as a device
-// function over 256 threads, so that it can be a kernel of its own (decoder.cu) or one step of a persistent
-// chain (gemv_mma.cu).
+// function over 256 threads (the kernel that runs it is in decoder.cu).
 //
 // One item = (chunk of ATT_FUSED_CHUNK positions, kv head, sequence); it serves all G = nq / nkv query heads
 // of its kv head, so a K or V row is read once per group.  The item that holds the newest position ropes k,
@@ -37,6 +36,7 @@ struct AttnArgs {
     uint32_t* counters;    // [B * nkv * gsplit], zero between calls
     float* out;            // [B, nq * hd]
     unsigned long long* trace = nullptr;  // profiling aid: item (0, 0, 0) stores the GPU timer at its phases
+    int32_t* bad_pos = nullptr;  // set to 1 when a position lies outside the cache (the item then does nothing)
 };
 
 // dynamic shared memory the item needs, in floats
@@ -140,6 +140,12 @@ __device__ __forceinline__ void attention_fused_item_t(const AttnArgs& a, uint32
         vreg[u] = (v_thread && t < max_ctx) ? Vc[(uint64_t)t * HD + vi] : 0.0f;
     }
 
+    // A position outside [0, max_ctx) has no cache row: store nothing, attend to nothing, say so.  Every item of
+    // the sequence takes this exit, so the arrival counters stay at zero.
+    if (p_raw < 0 || (uint32_t)p_raw >= max_ctx) {
+        if (tid == 0 && a.bad_pos) atomicExch(a.bad_pos, 1);
+        return;
+    }
     const uint32_t p = (uint32_t)p_raw, n_ctx = p + 1;
     const uint32_t active = (n_ctx + ATT_FUSED_CHUNK - 1) / ATT_FUSED_CHUNK;
     if (chunk >= active) return;
@@ -342,17 +348,6 @@ __device__ __forceinline__ void attention_fused_item(const AttnArgs& a, uint32_t
     JQ_ATT_CASE(256, 4)
     JQ_ATT_CASE(256, 8)
 #undef JQ_ATT_CASE
-}
-
-// The persistent chain only carries the two shapes of the benchmark models (head size 128, 4 or 8 query heads
-// per kv head, one item per kv head), to keep its code small.
-template <int BAR>
-__device__ __forceinline__ void attention_fused_item_chain(const AttnArgs& a, uint32_t chunk, uint32_t kvh, uint32_t b,
-                                                           uint32_t tid, float* s_f, uint32_t* s_last) {
-    if (a.nq / a.nkv == 4)
-        attention_fused_item_t<BAR, 128, 4>(a, chunk, kvh, 0, b, tid, s_f, s_last);
-    else
-        attention_fused_item_t<BAR, 128, 8>(a, chunk, kvh, 0, b, tid, s_f, s_last);
 }
 
 }  // namespace jq

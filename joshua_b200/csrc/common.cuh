@@ -26,6 +26,30 @@ cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, unsigned block, size_t
     return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
+// Kernel attributes and device properties are per device: a process may hold contexts on several GPUs, so
+// every one-time setup is keyed by the device that is current when it runs.
+constexpr int MAX_DEVICES = 64;
+inline int current_device() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return dev >= 0 && dev < MAX_DEVICES ? dev : 0;
+}
+inline int num_sms() {
+    static int cached[MAX_DEVICES] = {};
+    const int dev = current_device();
+    if (cached[dev] == 0) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+    return cached[dev] > 0 ? cached[dev] : 148;
+}
+// Raises a kernel's dynamic shared-memory limit once per device; `done` is a per-kernel array of MAX_DEVICES flags.
+template <class K>
+cudaError_t set_max_smem_once(K kern, int bytes, bool* done) {
+    const int dev = current_device();
+    if (done[dev]) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) done[dev] = true;
+    return e;
+}
+
 // Status codes of the C ABI (0 = success, negative = failure), following the
 // int32 status / opaque handle convention of the reference's only C ABI
 // (src/npu/mod.rs:32-50).
@@ -159,7 +183,7 @@ cudaError_t launch_rmsnorm(const float* x, const float* res, const float* w, flo
                            float* sum_out, float* out, cudaStream_t s);
 cudaError_t launch_rope_append(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
                                uint32_t hd, uint32_t max_ctx, float theta, float* q_out, float* cache_k, float* cache_v,
-                               cudaStream_t s);
+                               int32_t* bad_pos, cudaStream_t s);
 // rope + cache append + attention + merge in one launch, from the fused qkv row (decoder.cu)
 struct AttnArgs;
 bool attention_fused_args(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd,
@@ -168,15 +192,18 @@ bool attention_fused_args(const float* qkv, const int32_t* pos, uint32_t batch, 
 size_t attention_fused_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx);
 cudaError_t launch_attention_fused(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
                                    uint32_t hd, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,
-                                   float* out, void* scratch, cudaStream_t s);
+                                   float* out, void* scratch, int32_t* bad_pos, cudaStream_t s);
 // scratch: attention_scratch_bytes(...) bytes of per-chunk partial results
 size_t attention_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t hd, uint32_t max_ctx);
 cudaError_t launch_attention_decode(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,
                                     uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx, float* out,
-                                    float* scratch, cudaStream_t s);
+                                    float* scratch, int32_t* bad_pos, cudaStream_t s);
 cudaError_t launch_add(const float* a, const float* b, uint64_t n, float* y, cudaStream_t s);
 size_t argmax_scratch_bytes(uint32_t rows);
+// greedy token per row; with a window (ids [rows, 64] + state [rows, 2]) and penalty != 1 the reference's
+// repetition penalty is applied first and the sampled id is pushed into the window
 cudaError_t launch_argmax(const float* logits, uint32_t rows, uint32_t vocab, int32_t* token, int32_t* pos,
-                          void* scratch, cudaStream_t s);
+                          void* scratch, cudaStream_t s, float penalty = 1.0f, int32_t* window = nullptr,
+                          int32_t* win_state = nullptr);
 
 }  // namespace jq

@@ -96,11 +96,18 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__
 __global__ void __launch_bounds__(128) rope_append_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ pos,
                                                           uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx,
                                                           float theta, float* __restrict__ q_out,
-                                                          float* __restrict__ cache_k, float* __restrict__ cache_v) {
+                                                          float* __restrict__ cache_k, float* __restrict__ cache_v,
+                                                          int32_t* __restrict__ bad_pos) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     pdl_wait_();
     const uint32_t b = blockIdx.y, head = blockIdx.x;  // heads 0..nq-1: q; nq..nq+nkv-1: k; then v
-    const uint32_t p = (uint32_t)pos[b];
+    const int32_t p_raw = pos[b];
+    if (p_raw < 0 || (uint32_t)p_raw >= max_ctx) {
+        // the cache has no row for this position: nothing is stored, the flag says why
+        if (threadIdx.x == 0 && bad_pos) atomicExch(bad_pos, 1);
+        return;
+    }
+    const uint32_t p = (uint32_t)p_raw;
     const float* src = qkv + ((uint64_t)b * (nq + 2 * nkv) + head) * hd;
     const uint32_t half = hd / 2;
     if (head < nq + nkv) {
@@ -131,13 +138,16 @@ __global__ void __launch_bounds__(128) attention_partial_kernel(const float* __r
                                                                 const float* __restrict__ cache_v,
                                                                 const int32_t* __restrict__ pos, uint32_t nq, uint32_t nkv,
                                                                 uint32_t hd, uint32_t max_ctx, uint32_t n_chunks,
-                                                                float* __restrict__ part) {
+                                                                float* __restrict__ part, int32_t* __restrict__ bad_pos) {
     extern __shared__ float s_att[];  // hd (q) + ATT_CHUNK (scores)
     __shared__ float red[4];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     pdl_wait_();
     const uint32_t head = blockIdx.x, chunk = blockIdx.y, b = blockIdx.z, kvh = head / (nq / nkv);
-    const uint32_t n_ctx = (uint32_t)pos[b] + 1;
+    const int32_t p_raw = pos[b];
+    const bool in_cache = p_raw >= 0 && (uint32_t)p_raw < max_ctx;
+    if (!in_cache && threadIdx.x == 0 && bad_pos) atomicExch(bad_pos, 1);
+    const uint32_t n_ctx = in_cache ? (uint32_t)p_raw + 1 : 0u;  // a position outside the cache attends to nothing
     const uint32_t t0 = chunk * ATT_CHUNK;
     float* dst = part + (((uint64_t)b * nq + head) * n_chunks + chunk) * (hd + 2);
     if (t0 >= n_ctx) {
@@ -263,15 +273,55 @@ __device__ __forceinline__ void argmax_block(float& best, uint32_t& idx, float* 
         for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) argmax_merge(best, idx, sv[w], si[w]);
 }
 
-__global__ void __launch_bounds__(256) argmax_slices_kernel(const float* __restrict__ logits, uint32_t vocab,
-                                                            float* __restrict__ part_v, uint32_t* __restrict__ part_i) {
+// Repetition penalty of the reference's sampler (src/engine.rs:2349-2365): every OCCURRENCE of a token in the
+// recent window divides its logit by `penalty` when positive and multiplies it otherwise, applied one
+// occurrence after another.  The window (SAMPLE_WINDOW ids per row, src/engine.rs:1222-1232,1265-1269) is a ring:
+// state[2b] = ids held, state[2b+1] = slot the next id goes to.  The slice's CTA writes the penalised values of
+// its own tokens into the row, scans, and puts the originals back, so the logits the caller sees are unchanged
+// as in the reference (which penalises a copy).
+constexpr uint32_t SAMPLE_WINDOW = 64;
+
+__global__ void __launch_bounds__(256) argmax_slices_kernel(float* __restrict__ logits, uint32_t vocab,
+                                                            float* __restrict__ part_v, uint32_t* __restrict__ part_i,
+                                                            float penalty, const int32_t* __restrict__ window,
+                                                            const int32_t* __restrict__ win_state) {
     __shared__ float sv[8];
     __shared__ uint32_t si[8];
+    __shared__ int32_t s_win[SAMPLE_WINDOW];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     pdl_wait_();
-    const float* row = logits + (uint64_t)blockIdx.y * vocab;
+    float* row = logits + (uint64_t)blockIdx.y * vocab;
     const uint32_t per = (vocab + ARGMAX_SLICES - 1) / ARGMAX_SLICES;
     const uint32_t lo = blockIdx.x * per, hi = min(vocab, lo + per);
+    // penalties of this slice's tokens: the thread of a token's first occurrence applies all of them
+    float original = 0.0f;
+    int32_t mine = -1;
+    const bool penalise = window != nullptr && penalty != 1.0f;
+    if (penalise) {
+        const uint32_t held = min((uint32_t)win_state[2 * blockIdx.y], SAMPLE_WINDOW);
+        if (threadIdx.x < SAMPLE_WINDOW)
+            s_win[threadIdx.x] = threadIdx.x < held ? window[(uint64_t)blockIdx.y * SAMPLE_WINDOW + threadIdx.x] : -1;
+        __syncthreads();
+        if (threadIdx.x < held) {
+            const int32_t tok = s_win[threadIdx.x];
+            bool first = tok >= (int32_t)lo && tok < (int32_t)hi;
+            uint32_t occ = 0;
+            for (uint32_t i = 0; i < held; ++i) {
+                if (s_win[i] == tok) {
+                    if (i < threadIdx.x) first = false;
+                    ++occ;
+                }
+            }
+            if (first) {
+                mine = tok;
+                original = row[tok];
+                float v = original;
+                for (uint32_t i = 0; i < occ; ++i) v = v > 0.0f ? v / penalty : v * penalty;
+                row[tok] = v;
+            }
+        }
+        __syncthreads();
+    }
     float best = -INFINITY;
     uint32_t idx = 0;
     for (uint32_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
@@ -281,7 +331,8 @@ __global__ void __launch_bounds__(256) argmax_slices_kernel(const float* __restr
             idx = i;
         }
     }
-    argmax_block(best, idx, sv, si);
+    argmax_block(best, idx, sv, si);  // contains a barrier: every thread's reads of the row are done after it
+    if (mine >= 0) row[mine] = original;
     if (threadIdx.x == 0) {
         part_v[blockIdx.y * ARGMAX_SLICES + blockIdx.x] = best;
         part_i[blockIdx.y * ARGMAX_SLICES + blockIdx.x] = idx;
@@ -289,7 +340,8 @@ __global__ void __launch_bounds__(256) argmax_slices_kernel(const float* __restr
 }
 
 __global__ void __launch_bounds__(64) argmax_final_kernel(const float* __restrict__ part_v, const uint32_t* __restrict__ part_i,
-                                                          int32_t* __restrict__ token, int32_t* __restrict__ pos) {
+                                                          int32_t* __restrict__ token, int32_t* __restrict__ pos,
+                                                          int32_t* __restrict__ window, int32_t* __restrict__ win_state) {
     __shared__ float sv[2];
     __shared__ uint32_t si[2];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -300,6 +352,14 @@ __global__ void __launch_bounds__(64) argmax_final_kernel(const float* __restric
     if (threadIdx.x == 0) {
         token[blockIdx.x] = (int32_t)idx;
         if (pos) pos[blockIdx.x] += 1;
+        if (window) {
+            // push the sampled id; once the window is full the oldest id is the one replaced
+            int32_t held = win_state[2 * blockIdx.x], next = win_state[2 * blockIdx.x + 1];
+            next = next < 0 || next >= (int32_t)SAMPLE_WINDOW ? 0 : next;
+            window[(uint64_t)blockIdx.x * SAMPLE_WINDOW + next] = (int32_t)idx;
+            win_state[2 * blockIdx.x] = min(held + 1, (int32_t)SAMPLE_WINDOW);
+            win_state[2 * blockIdx.x + 1] = (next + 1) % (int32_t)SAMPLE_WINDOW;
+        }
     }
 }
 
@@ -320,9 +380,9 @@ cudaError_t launch_rmsnorm(const float* x, const float* res, const float* w, flo
 
 cudaError_t launch_rope_append(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
                                uint32_t hd, uint32_t max_ctx, float theta, float* q_out, float* cache_k, float* cache_v,
-                               cudaStream_t s) {
+                               int32_t* bad_pos, cudaStream_t s) {
     cudaError_t le2__ = launch_pdl(rope_append_kernel, dim3(nq + 2 * nkv, batch), 128, 0, s, qkv, pos, nq, nkv, hd, max_ctx, theta, q_out, cache_k,
-                                                                 cache_v);
+                                                                 cache_v, bad_pos);
     if (le2__ != cudaSuccess) return le2__;
     return cudaGetLastError();
 }
@@ -334,11 +394,11 @@ size_t attention_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t hd, uint32_
 
 cudaError_t launch_attention_decode(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,
                                     uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx, float* out,
-                                    float* scratch, cudaStream_t s) {
+                                    float* scratch, int32_t* bad_pos, cudaStream_t s) {
     uint32_t n_chunks = (max_ctx + ATT_CHUNK - 1) / ATT_CHUNK;
     size_t smem = (size_t)(hd + ATT_CHUNK) * 4;
     cudaError_t le3__ = launch_pdl(attention_partial_kernel, dim3(nq, n_chunks, batch), 128, smem, s, q, cache_k, cache_v, pos, nq, nkv, hd, max_ctx,
-                                                                          n_chunks, scratch);
+                                                                          n_chunks, scratch, bad_pos);
     if (le3__ != cudaSuccess) return le3__;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
@@ -356,10 +416,11 @@ size_t attention_fused_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t nkv, 
 // the first call; the kernel leaves them zero.
 cudaError_t launch_attention_fused(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
                                    uint32_t hd, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,
-                                   float* out, void* scratch, cudaStream_t s) {
+                                   float* out, void* scratch, int32_t* bad_pos, cudaStream_t s) {
     AttnArgs a;
     if (!attention_fused_args(qkv, pos, batch, nq, nkv, hd, max_ctx, theta, cache_k, cache_v, out, scratch, &a))
         return cudaErrorInvalidValue;
+    a.bad_pos = bad_pos;
     size_t smem = (size_t)attention_fused_smem_floats(nq / a.gsplit, nkv, hd, a.n_chunks) * 4;
     cudaError_t e = launch_pdl(attention_fused_kernel, dim3(a.n_chunks, nkv * a.gsplit, batch), ATT_FUSED_THREADS, smem, s, a);
     if (e != cudaSuccess) return e;
@@ -392,14 +453,15 @@ cudaError_t launch_add(const float* a, const float* b, uint64_t n, float* y, cud
 size_t argmax_scratch_bytes(uint32_t rows) { return (size_t)rows * ARGMAX_SLICES * 8; }
 
 cudaError_t launch_argmax(const float* logits, uint32_t rows, uint32_t vocab, int32_t* token, int32_t* pos,
-                          void* scratch, cudaStream_t s) {
+                          void* scratch, cudaStream_t s, float penalty, int32_t* window, int32_t* win_state) {
     float* pv = static_cast<float*>(scratch);
     uint32_t* pi = reinterpret_cast<uint32_t*>(pv + (size_t)rows * ARGMAX_SLICES);
-    cudaError_t le6__ = launch_pdl(argmax_slices_kernel, dim3(ARGMAX_SLICES, rows), 256, 0, s, logits, vocab, pv, pi);
+    cudaError_t le6__ = launch_pdl(argmax_slices_kernel, dim3(ARGMAX_SLICES, rows), 256, 0, s, const_cast<float*>(logits), vocab, pv, pi,
+                                   penalty, (const int32_t*)window, (const int32_t*)win_state);
     if (le6__ != cudaSuccess) return le6__;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    cudaError_t le7__ = launch_pdl(argmax_final_kernel, rows, 64, 0, s, pv, pi, token, pos);
+    cudaError_t le7__ = launch_pdl(argmax_final_kernel, rows, 64, 0, s, pv, pi, token, pos, window, win_state);
     if (le7__ != cudaSuccess) return le7__;
     return cudaGetLastError();
 }

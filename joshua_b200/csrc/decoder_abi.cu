@@ -96,7 +96,7 @@ uint64_t jq_attention_fused_scratch_bytes(uint32_t batch, uint32_t n_q, uint32_t
 
 int32_t jq_attention_fused_dev(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t n_q, uint32_t n_kv,
                                uint32_t head_dim, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,
-                               float* out, void* scratch, void* stream) {
+                               float* out, void* scratch, int32_t* bad_pos_dev, void* stream) {
     if (batch == 0) return jq::OK;
     if (!qkv || !pos || !cache_k || !cache_v || !out || !scratch)
         return jq_fail(jq::E_INVALID, "jq_attention_fused_dev: NULL buffer");
@@ -104,7 +104,7 @@ int32_t jq_attention_fused_dev(const float* qkv, const int32_t* pos, uint32_t ba
         !(n_q / n_kv == 1 || n_q / n_kv == 2 || n_q / n_kv == 4 || n_q / n_kv == 8))
         return jq_fail(jq::E_INVALID, "jq_attention_fused_dev: need head_dim 64, 128 or 256 and 1, 2, 4 or 8 query heads per kv head");
     JQ_CUDA(jq::launch_attention_fused(qkv, pos, batch, n_q, n_kv, head_dim, max_ctx, theta, cache_k, cache_v, out,
-                                       scratch, static_cast<cudaStream_t>(stream)));
+                                       scratch, bad_pos_dev, static_cast<cudaStream_t>(stream)));
     return jq::OK;
 }
 
@@ -136,12 +136,12 @@ int32_t jq_rmsnorm_dev(const float* x, const float* residual, const float* weigh
 
 int32_t jq_rope_append_dev(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t n_q, uint32_t n_kv,
                            uint32_t head_dim, uint32_t max_ctx, float theta, float* q_out, float* cache_k,
-                           float* cache_v, void* stream) {
+                           float* cache_v, int32_t* bad_pos_dev, void* stream) {
     if (batch == 0) return jq::OK;
     if (!qkv || !pos || !q_out || !cache_k || !cache_v || head_dim % 2 || n_kv == 0 || n_q % n_kv)
         return jq_fail(jq::E_INVALID, "jq_rope_append_dev: bad argument");
     JQ_CUDA(jq::launch_rope_append(qkv, pos, batch, n_q, n_kv, head_dim, max_ctx, theta, q_out, cache_k, cache_v,
-                                   static_cast<cudaStream_t>(stream)));
+                                   bad_pos_dev, static_cast<cudaStream_t>(stream)));
     return jq::OK;
 }
 
@@ -151,12 +151,12 @@ uint64_t jq_attention_scratch_bytes(uint32_t batch, uint32_t n_q, uint32_t head_
 
 int32_t jq_attention_decode_dev(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,
                                 uint32_t batch, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t max_ctx,
-                                float* out, float* scratch, void* stream) {
+                                float* out, float* scratch, int32_t* bad_pos_dev, void* stream) {
     if (batch == 0) return jq::OK;
     if (!q || !cache_k || !cache_v || !pos || !out || !scratch || n_kv == 0 || n_q % n_kv)
         return jq_fail(jq::E_INVALID, "jq_attention_decode_dev: bad argument");
     JQ_CUDA(jq::launch_attention_decode(q, cache_k, cache_v, pos, batch, n_q, n_kv, head_dim, max_ctx, out, scratch,
-                                        static_cast<cudaStream_t>(stream)));
+                                        bad_pos_dev, static_cast<cudaStream_t>(stream)));
     return jq::OK;
 }
 
@@ -175,6 +175,19 @@ int32_t jq_argmax_dev(const float* logits, uint64_t rows, uint64_t vocab, int32_
     if (!logits || !token || !scratch || vocab == 0) return jq_fail(jq::E_INVALID, "jq_argmax_dev: bad argument");
     JQ_CUDA(jq::launch_argmax(logits, (uint32_t)rows, (uint32_t)vocab, token, pos, scratch,
                               static_cast<cudaStream_t>(stream)));
+    return jq::OK;
+}
+
+int32_t jq_sample_greedy_dev(const float* logits, uint64_t rows, uint64_t vocab, float repetition_penalty,
+                             int32_t* window, int32_t* window_state, int32_t* token, int32_t* pos, void* scratch,
+                             void* stream) {
+    if (rows == 0) return jq::OK;
+    if (!logits || !token || !scratch || vocab == 0) return jq_fail(jq::E_INVALID, "jq_sample_greedy_dev: bad argument");
+    if ((window == nullptr) != (window_state == nullptr))
+        return jq_fail(jq::E_INVALID, "jq_sample_greedy_dev: window and window_state go together");
+    if (!(repetition_penalty > 0.0f)) return jq_fail(jq::E_INVALID, "jq_sample_greedy_dev: the penalty must be positive");
+    JQ_CUDA(jq::launch_argmax(logits, (uint32_t)rows, (uint32_t)vocab, token, pos, scratch,
+                              static_cast<cudaStream_t>(stream), repetition_penalty, window, window_state));
     return jq::OK;
 }
 

@@ -34,7 +34,8 @@
 namespace {
 
 constexpr uint32_t EP_MAX_WORLD = 8;
-constexpr uint32_t EP_POLLS = 1u << 22;  // x ~0.25 us: about a second
+constexpr uint32_t EP_POLLS = 1u << 22;  // default bound of a wait: x ~0.25 us, about a second
+constexpr uint32_t EP_SPIN = 64;         // polls without a pause before the wait starts to sleep between polls
 
 struct Window {
     uint8_t* base[EP_MAX_WORLD];
@@ -68,11 +69,13 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Polls until *flag has reached `target` (wrap-safe).  Gives up after EP_POLLS polls and raises *status.
-__device__ void wait_flag(const uint32_t* flag, uint32_t target, int* status) {
-    for (uint32_t i = 0; i < EP_POLLS; ++i) {
+// Polls until *flag has reached `target` (wrap-safe).  Gives up after `polls` polls and raises *status.  The
+// first polls come back to back (a peer that is in step arrives within a few microseconds); after that the
+// thread sleeps between polls.
+__device__ void wait_flag(const uint32_t* flag, uint32_t target, uint32_t polls, int* status) {
+    for (uint32_t i = 0; i < polls; ++i) {
         if ((int32_t)(ld_acquire_sys(flag) - target) >= 0) return;
-        __nanosleep(200);
+        if (i >= EP_SPIN) __nanosleep(200);
     }
     *status = 1;
 }
@@ -101,7 +104,7 @@ __device__ bool publish(uint32_t* done, const Window& win, uint64_t flag_off, ui
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(Window win, Layout l, uint32_t me, const float* __restrict__ x,
                                                           const uint32_t* __restrict__ ids, uint32_t T, uint32_t K,
                                                           uint32_t* __restrict__ pair_slot, uint32_t* __restrict__ epoch,
-                                                          uint32_t* __restrict__ done, int* status) {
+                                                          uint32_t* __restrict__ done, uint32_t polls, int* status) {
     __shared__ uint32_t s_red[8];
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t P = T * K, tid = threadIdx.x;
@@ -142,7 +145,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(Window win, Layout l, 
         // epoch, so the kernel must not end before the rows are there.  Every CTA of this grid read the old
         // epoch before it counted itself in.
         for (uint32_t r = 0; r < l.world; ++r)
-            wait_flag(reinterpret_cast<const uint32_t*>(win.base[me] + l.o_flag_in) + r, next_epoch, status);
+            wait_flag(reinterpret_cast<const uint32_t*>(win.base[me] + l.o_flag_in) + r, next_epoch, polls, status);
         *epoch = next_epoch;
     }
 }
@@ -172,11 +175,11 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const uint8_t* __restri
                                                          const uint32_t* __restrict__ pair_slot,
                                                          const float* __restrict__ wts, uint32_t T, uint32_t K,
                                                          const uint32_t* __restrict__ epoch, const float* residual,
-                                                         float* y, int* status) {
+                                                         float* y, uint32_t polls, int* status) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x < l.world)
-        wait_flag(reinterpret_cast<const uint32_t*>(my_window + l.o_flag_back) + threadIdx.x, *epoch, status);
+        wait_flag(reinterpret_cast<const uint32_t*>(my_window + l.o_flag_back) + threadIdx.x, *epoch, polls, status);
     __syncthreads();
     const float* back = reinterpret_cast<const float*>(my_window + l.o_rows_back);
     const uint32_t h4 = l.hidden / 4;
@@ -212,6 +215,8 @@ struct jq_ep {
     Layout lay;
     Window win;            // win.base[rank] is my own allocation, the others are IPC mappings
     bool connected = false;
+    bool loopback = false;  // peer windows are private local allocations (single-GPU tests)
+    uint32_t polls = EP_POLLS;
     uint32_t *ids = nullptr, *pair_slot = nullptr, *epoch = nullptr, *done = nullptr;  // local device state
     float* wts = nullptr;
 };
@@ -262,7 +267,7 @@ void jq_ep_free(jq_ep* e) {
     cudaDeviceSynchronize();
     for (uint32_t i = 0; i < e->world; ++i) {
         if (!e->win.base[i]) continue;
-        if (i == e->rank)
+        if (i == e->rank || e->loopback)
             cudaFree(e->win.base[i]);
         else
             cudaIpcCloseMemHandle(e->win.base[i]);
@@ -300,6 +305,27 @@ int32_t jq_ep_connect(jq_ep* e, const uint8_t* handles) {
     return jq::OK;
 }
 
+int32_t jq_ep_connect_loopback(jq_ep* e) {
+    if (!e) return jq_fail(jq::E_INVALID, "jq_ep_connect_loopback: NULL handle");
+    if (e->connected) return jq_fail(jq::E_INVALID, "jq_ep_connect_loopback: already connected");
+    JQ_CUDA(cudaSetDevice(e->ctx->device));
+    e->loopback = true;
+    for (uint32_t i = 0; i < e->world; ++i) {
+        if (i == e->rank) continue;
+        JQ_CUDA(cudaMalloc(&e->win.base[i], e->lay.bytes));
+        JQ_CUDA(cudaMemset(e->win.base[i], 0, e->lay.bytes));
+    }
+    JQ_CUDA(cudaDeviceSynchronize());
+    e->connected = true;
+    return jq::OK;
+}
+
+int32_t jq_ep_set_poll_limit(jq_ep* e, uint32_t polls) {
+    if (!e) return jq_fail(jq::E_INVALID, "jq_ep_set_poll_limit: NULL handle");
+    e->polls = polls ? polls : EP_POLLS;
+    return jq::OK;
+}
+
 int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float* x_dev, uint64_t T,
                           const float* residual_dev, float* y_dev, void* stream) {
     if (!e || !router || !experts) return jq_fail(jq::E_INVALID, "jq_ep_forward_dev: NULL handle");
@@ -321,7 +347,7 @@ int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float
     if (int32_t r = jq_moe_route_dev(router, x_dev, T, nullptr, e->ids, e->wts, stream)) return r;
     JQ_CUDA(jq::launch_pdl(ep_dispatch_kernel, dim3(P + e->world), 256, 0, s, e->win, e->lay, e->rank, x_dev,
                            (const uint32_t*)e->ids, (uint32_t)T, e->n_used, e->pair_slot, e->epoch, e->done,
-                           e->ctx->status_dev));
+                           e->polls, e->ctx->status_dev));
     if (int32_t r = jq_moe_experts_list(experts, reinterpret_cast<const float*>(mine + e->lay.o_rows_in), rows,
                                         reinterpret_cast<const uint32_t*>(mine + e->lay.o_ids_in), s))
         return r;
@@ -331,7 +357,7 @@ int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float
     const unsigned cblocks = (unsigned)std::min<uint64_t>(((uint64_t)T * (e->hidden / 4) + 255) / 256, 148 * 4);
     JQ_CUDA(jq::launch_pdl(ep_combine_kernel, dim3(cblocks), 256, 0, s, (const uint8_t*)mine, e->lay,
                            (const uint32_t*)e->pair_slot, (const float*)e->wts, (uint32_t)T, e->n_used,
-                           (const uint32_t*)e->epoch, residual_dev, y_dev, e->ctx->status_dev));
+                           (const uint32_t*)e->epoch, residual_dev, y_dev, e->polls, e->ctx->status_dev));
     return jq::OK;
 }
 

@@ -413,19 +413,19 @@ cudaError_t launch_tile(const uint8_t* w, uint64_t n, uint64_t k, const float* x
     uint32_t n_stages = std::min<uint32_t>(8, std::min<uint32_t>((uint32_t)(k / TC_K), (216 * 1024) / STAGE));
     size_t smem = (size_t)n_stages * STAGE + 1024;
     auto kern = gemm_tc_kernel<TYPE, ELEMS, BYTES, N_TILE>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static bool configured[MAX_DEVICES] = {};
+    if (cudaError_t ce = set_max_smem_once(kern, 226 * 1024, configured); ce != cudaSuccess) return ce;
     CUtensorMap map_hi, map_lo;
     cudaError_t e = tensor_map_for(x_hi, m, k, N_TILE, &map_hi);
     if (e == cudaSuccess) e = tensor_map_for(x_lo, m, k, N_TILE, &map_lo);
     if (e != cudaSuccess) return e;
     dim3 grid((unsigned)((n + TC_M - 1) / TC_M), (unsigned)((m + N_TILE - 1) / N_TILE));
     // JQ_DEBUG_TC_SKIP (measurement only, results are wrong): bit 0 = no weight decode / stores, bit 1 = no TMA
+#ifdef JQ_PROFILING
     static const int dbg_skip = std::getenv("JQ_DEBUG_TC_SKIP") ? std::atoi(std::getenv("JQ_DEBUG_TC_SKIP")) : 0;
+#else
+    constexpr int dbg_skip = 0;  // the measurement switch exists in profiling builds only
+#endif
     kern<<<grid, TC_THREADS, smem, s>>>(w, n, k, map_hi, map_lo, m, dst, n_stages, error_flag, g_gemm_trace, dbg_skip);
     return cudaGetLastError();
 }

@@ -38,7 +38,6 @@
 #include <algorithm>
 #include <cstdlib>
 
-#include "chain.cuh"
 #include "common.cuh"
 
 namespace jq {
@@ -1304,330 +1303,6 @@ __global__ void __launch_bounds__((16 + 2) * 32, 1) gemv_narrow_kernel(const __g
     }
 }
 
-// ───────────────────────────── persistent chain ───────────────────────────
-//
-// A whole sequence of dependent decode operations in ONE launch: quantized linears (with the RMS-norm
-// prologue / residual epilogue / SwiGLU pair forms of the kernel above) and fused attention steps, executed in
-// order by the same 148 persistent CTAs.  Between two operations every CTA must have finished the first: the
-// reducer warp of each CTA counts itself in on a global arrival counter after its last store of an operation
-// and the consumer + reducer warps wait for `gridDim.x` arrivals before they read the next operation's input.
-// The producer warp never waits for that: weights do not depend on activations, so it streams the NEXT
-// operation's tiles into the ring while the consumers are still at the barrier or splitting activations,
-// and the ring is full when they get there.  What a kernel boundary costs (drain, launch, first-load
-// latency) shrinks to one counter round trip.
-//
-// All CTAs must be resident at once (cooperative launch, grid <= SM count, one CTA per SM).  The arrival
-// counter only grows: launch L starts at L * gridDim.x * n_ops, which every CTA recovers by rounding the
-// value it reads on entry down to a multiple of that.  Every poll is bounded; a wait that gives up raises the
-// error flag and the CTA's warps leave (the roles that depend on them run out of their own bounded waits).
-struct ChainArgs {
-    const ChainOp* ops;
-    uint32_t n_ops, m;
-    unsigned long long* arrivals;
-    SmemPlan plan;  // row_stride / act_bytes: the largest any operation needs
-    int* error_flag;
-    unsigned long long* trace;  // optional: CTA 0 stores %globaltimer at three points of every operation
-};
-
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
-constexpr uint32_t CHAIN_POLLS = 1u << 22;
-
-template <uint32_t TYPE, int MB, int NH>
-__global__ void __launch_bounds__((16 + 2) * 32, 1) gemv_chain_kernel(const __grid_constant__ ChainArgs ca) {
-    using Tr = Traits<TYPE>;
-    constexpr int NCW = 16;
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ uint32_t s_abort, s_att_last;
-    __shared__ float s_part[NCW + 1][GEMV_MMA_MAX_M];
-    constexpr int NB = MB * NH;
-    constexpr uint32_t RED_FLOATS = NCW * NB * ROWS;
-    const SmemPlan& plan = ca.plan;
-    const uint32_t stage_bytes = ROWS * plan.row_stride;
-    uint8_t* s_act = smem;
-    uint8_t* ring = smem + plan.act_bytes;
-    uint2* s_grid = reinterpret_cast<uint2*>(ring + plan.n_stages * stage_bytes);
-    uint2* s_mask = s_grid + (TYPE == T_IQ2_XXS ? 256 : 0);
-    float* s_red = reinterpret_cast<float*>(s_mask + (TYPE == T_IQ2_XXS ? 128 : 0));
-    uint64_t* full = reinterpret_cast<uint64_t*>(s_red + 2 * RED_FLOATS);
-    uint64_t* empty = full + plan.n_stages;
-    uint64_t* red_full = empty + plan.n_stages;
-    uint64_t* red_empty = red_full + 2;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t NS = plan.n_stages;
-    if (tid == 0) {
-        for (uint32_t st = 0; st < NS; ++st) {
-            mbar_init(&full[st], ROWS);
-            mbar_init(&empty[st], NCW);
-        }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&red_full[b], NCW);
-            mbar_init(&red_empty[b], 1);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        s_abort = 0;
-    }
-    if (TYPE == T_IQ2_XXS) {
-        for (int i = tid; i < 256; i += (NCW + 2) * 32) s_grid[i] = g_iq2xxs_grid[i];
-        for (int i = tid; i < 128; i += (NCW + 2) * 32) {
-            uint32_t sg = iq2_signs(i);
-            uint32_t lo = ((sg & 0xF) * 0x00204081u) & 0x01010101u, hi = ((sg >> 4) * 0x00204081u) & 0x01010101u;
-            s_mask[i] = make_uint2(lo * 0xFFu, hi * 0xFFu);
-        }
-    }
-    __syncthreads();
-    pdl_wait();
-
-    if (warp == 0) {
-        // ── producer: every linear's tiles, one after the other, never waiting for activations ──
-        if (lane < ROWS) {
-            uint32_t job = 0;
-            for (uint32_t oi = 0; oi < ca.n_ops; ++oi) {
-                const ChainOp* op = ca.ops + oi;
-                if (op->kind != 0) continue;
-                const uint64_t n = op->n, k = op->k;
-                const uint32_t n_tiles = (uint32_t)((n + ROWS - 1) / ROWS);
-                const uint32_t units_per_row = (uint32_t)(k / 256);
-                const uint64_t row_bytes = (uint64_t)units_per_row * Tr::UNIT_BYTES;
-                const uint32_t n_chunks = (units_per_row + Tr::CHUNK_UNITS - 1) / Tr::CHUNK_UNITS;
-                const uint32_t n_sub = op->swiglu ? 2 : 1;
-                for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-                    uint64_t row = (uint64_t)tile * ROWS + lane < n ? (uint64_t)tile * ROWS + lane : n - 1;
-                    for (uint32_t sub = 0; sub < n_sub; ++sub) {
-                        const uint8_t* wrow = op->w[sub] + row * row_bytes;
-                        for (uint32_t chunk = 0; chunk < n_chunks; ++chunk, ++job) {
-                            uint32_t st = job % NS, round = job / NS;
-                            if (!mbar_wait(&empty[st], (round & 1) ^ 1)) {
-                                *reinterpret_cast<volatile int*>(ca.error_flag) = 1;
-                                return;
-                            }
-                            uint32_t u_lo = chunk * Tr::CHUNK_UNITS;
-                            uint32_t u_hi = min(units_per_row, u_lo + Tr::CHUNK_UNITS);
-                            uintptr_t beg = reinterpret_cast<uintptr_t>(wrow) + (uint64_t)u_lo * Tr::UNIT_BYTES;
-                            uintptr_t end = beg + (uint64_t)(u_hi - u_lo) * Tr::UNIT_BYTES;
-                            uintptr_t abeg = beg & ~(uintptr_t)15, aend = (end + 15) & ~(uintptr_t)15;
-                            uint32_t bytes = (uint32_t)(aend - abeg);
-                            mbar_arrive_expect_tx(&full[st], bytes);
-                            bulk_g2s(ring + st * stage_bytes + lane * plan.row_stride,
-                                     reinterpret_cast<const void*>(abeg), bytes, &full[st]);
-                        }
-                    }
-                }
-            }
-        }
-        return;
-    }
-
-    // ── consumers (warps 1..NCW) and the reducer (warp NCW + 1) walk the operations together ──
-    const bool is_reducer = warp == NCW + 1;
-    const int cw = warp - 1;
-    Roles<MB, NH> ro(lane);
-    if (TYPE == T_Q4_K && MB == 1) {
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-            if (ro.col_p[j] & 1) ro.col_w[j] *= 0.0625f;
-    }
-    const unsigned long long per_launch = (unsigned long long)gridDim.x * ca.n_ops;
-    unsigned long long base = 0;
-    if (is_reducer && lane == 0) {
-        unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(ca.arrivals);
-        base = seen / per_launch * per_launch;
-    }
-    uint32_t job = 0, red_it = 0;
-    // A warp whose bounded wait ran out must not leave on its own: the others would wait for it at the next
-    // named barrier for ever.  It marks the CTA as aborting, stops working, and leaves with everybody else
-    // after that barrier.
-    bool dead = false;
-    float colacc[NH][2][2], minacc[NB][2];
-    constexpr int PER_LANE = (NB * ROWS + 31) / 32;
-    float gate[PER_LANE];
-    const uint32_t group_threads = (NCW + 1) * 32;
-
-    for (uint32_t oi = 0; oi < ca.n_ops; ++oi) {
-        const ChainOp* op = ca.ops + oi;
-        if (oi > 0) {
-            // every CTA has finished operation oi - 1?
-            if (is_reducer && lane == 0) {
-                const unsigned long long want = base + (unsigned long long)oi * gridDim.x;
-                bool ok = false;
-                for (uint32_t it = 0; it < CHAIN_POLLS; ++it) {
-                    unsigned long long v;
-                    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ca.arrivals) : "memory");
-                    if (v >= want) {
-                        ok = true;
-                        break;
-                    }
-                    __nanosleep(40);
-                }
-                if (!ok) {
-                    *reinterpret_cast<volatile int*>(ca.error_flag) = 1;
-                    s_abort = 1;
-                }
-            }
-            asm volatile("bar.sync 1, %0;" ::"r"(group_threads) : "memory");
-            if (s_abort) return;
-        }
-        const bool tracer = ca.trace != nullptr && blockIdx.x == 0 && is_reducer && lane == 0;
-        if (tracer) ca.trace[3 * oi] = global_ns();
-        if (op->kind == 1) {
-            // ── attention: items (chunk, kv head, sequence) dealt round-robin to the CTAs; warps 1..8 work ──
-            AttnArgs at = op->att;
-            if (ca.trace != nullptr) at.trace = ca.trace + 3 * ca.n_ops + 8 * oi;
-            const uint32_t items = at.n_chunks * at.nkv * at.batch;
-            if (warp >= 1 && warp <= 8) {
-                for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
-                    const uint32_t chunk = item % at.n_chunks, rest = item / at.n_chunks;
-                    attention_fused_item_chain<2>(at, chunk, rest % at.nkv, rest / at.nkv, (uint32_t)(tid - 32),
-                                            reinterpret_cast<float*>(s_act), &s_att_last);
-                    att_sync<2>();
-                }
-            }
-            asm volatile("bar.sync 1, %0;" ::"r"(group_threads) : "memory");
-            if (is_reducer && lane == 0) {
-                __threadfence();
-                atomicAdd(ca.arrivals, 1ull);
-            }
-            if (tracer) ca.trace[3 * oi + 1] = ca.trace[3 * oi + 2] = global_ns();
-            continue;
-        }
-        // ── quantized linear ──
-        const uint64_t n = op->n, k = op->k;
-        const uint32_t n_tiles = (uint32_t)((n + ROWS - 1) / ROWS);
-        const uint32_t units_per_row = (uint32_t)(k / 256);
-        const uint32_t n_chunks = (units_per_row + Tr::CHUNK_UNITS - 1) / Tr::CHUNK_UNITS;
-        const uint64_t row_bytes = (uint64_t)units_per_row * Tr::UNIT_BYTES;
-        const bool swiglu = op->swiglu != 0;
-        const uint32_t n_sub = swiglu ? 2 : 1;
-        const uint32_t n_groups = (uint32_t)(k / 32);
-        const uint64_t groups = (uint64_t)ca.m * n_groups;
-        int8_t* planes = reinterpret_cast<int8_t*>(s_act);
-        float2* meta = reinterpret_cast<float2*>(s_act + groups * 96);
-        float* sum16 = reinterpret_cast<float*>(s_act + groups * 104);
-        split_activations<true, NCW + 1>(op->x, ca.m, (uint32_t)k, op->norm_w, op->norm_eps, TYPE, s_act, warp - 1, lane,
-                                         &s_part[0][0]);
-        if (tracer) ca.trace[3 * oi + 1] = global_ns();
-        const uint32_t rb16 = (uint32_t)(row_bytes & 15);
-        if (!is_reducer) {
-            ActPlanes a;
-            a.planes = planes;
-            a.meta = meta;
-            a.sum16 = sum16;
-            a.n_groups = n_groups;
-            ro.set_rows(0u, ca.m, nullptr, n_groups);
-            for (uint32_t tile = blockIdx.x; !dead && tile < n_tiles; tile += gridDim.x) {
-                const uint64_t row0 = (uint64_t)tile * ROWS;
-                for (uint32_t sub = 0; !dead && sub < n_sub; ++sub, ++red_it) {
-#pragma unroll
-                    for (int h = 0; h < NH; ++h)
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) colacc[h][j][0] = colacc[h][j][1] = 0.0f;
-#pragma unroll
-                    for (int b = 0; b < NB; ++b) minacc[b][0] = minacc[b][1] = 0.0f;
-                    const uint32_t r0c = (uint32_t)min(row0 + ro.g, n - 1), r1c = (uint32_t)min(row0 + ro.g + 8, n - 1);
-                    const uint32_t wlow = (uint32_t)(reinterpret_cast<uintptr_t>(op->w[sub]) & 15);
-                    const uint32_t sh0 = (wlow + r0c * rb16) & 15, sh1 = (wlow + r1c * rb16) & 15;
-                    for (uint32_t chunk = 0; !dead && chunk < n_chunks; ++chunk, ++job) {
-                        uint32_t st = job % NS, round = job / NS;
-                        if (!mbar_wait(&full[st], round & 1)) {
-                            if (lane == 0) *reinterpret_cast<volatile int*>(ca.error_flag) = 1;
-                            s_abort = 1;
-                            dead = true;
-                            break;
-                        }
-                        const uint8_t* sp = ring + st * stage_bytes;
-                        const uint32_t u_lo = chunk * Tr::CHUNK_UNITS;
-                        const uint32_t cnt = min(units_per_row - u_lo, Tr::CHUNK_UNITS);
-                        for (uint32_t u = cw; u < cnt; u += NCW) {
-                            const uint8_t* u0 = sp + ro.g * plan.row_stride + sh0 + u * Tr::UNIT_BYTES;
-                            const uint8_t* u1 = sp + (ro.g + 8) * plan.row_stride + sh1 + u * Tr::UNIT_BYTES;
-                            process_unit<TYPE, MB, NH, 1>(u0, u1, u_lo + u, a, ro, s_grid, s_mask, colacc, minacc);
-                        }
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&empty[st]);
-                    }
-                    const uint32_t rb = red_it & 1;
-                    if (dead || !mbar_wait(&red_empty[rb], ((red_it >> 1) & 1) ^ 1)) {
-                        if (lane == 0) *reinterpret_cast<volatile int*>(ca.error_flag) = 1;
-                        s_abort = 1;
-                        dead = true;
-                        break;
-                    }
-                    float* red = s_red + rb * RED_FLOATS;
-#pragma unroll
-                    for (int b = 0; b < NB; ++b) {
-                        const int h = b / MB, i = b % MB;
-#pragma unroll
-                        for (int r = 0; r < 2; ++r) {
-                            float v = -minacc[b][r];
-#pragma unroll
-                            for (int j = 0; j < 2; ++j) v += ro.col_i[j] == i ? colacc[h][j][r] : 0.0f;
-                            v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
-                            v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
-                            if (ro.t == 0) red[(cw * NB + b) * ROWS + ro.g + 8 * r] = v;
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&red_full[rb]);
-                }
-            }
-        } else {
-            for (uint32_t tile = blockIdx.x; !dead && tile < n_tiles; tile += gridDim.x) {
-                const uint64_t row0 = (uint64_t)tile * ROWS;
-                for (uint32_t sub = 0; sub < n_sub; ++sub, ++red_it) {
-                    const uint32_t rb = red_it & 1;
-                    if (!mbar_wait(&red_full[rb], (red_it >> 1) & 1)) {
-                        if (lane == 0) *reinterpret_cast<volatile int*>(ca.error_flag) = 1;
-                        s_abort = 1;
-                        dead = true;
-                        break;
-                    }
-                    const float* red = s_red + rb * RED_FLOATS;
-#pragma unroll
-                    for (int q = 0; q < PER_LANE; ++q) {
-                        const int o = lane + 32 * q;
-                        if (o < NB * ROWS) {
-                            const int r = o % ROWS;
-                            const uint32_t b = o / ROWS;
-                            float v = 0.0f;
-#pragma unroll
-                            for (int cwv = 0; cwv < NCW; ++cwv) v += red[(cwv * NB + (int)b) * ROWS + r];
-                            if (swiglu && sub == 0) {
-                                gate[q] = v;
-                            } else if (b < ca.m && row0 + r < n) {
-                                if (swiglu) {
-                                    float gv = gate[q], uv = v;
-                                    if (op->clamp > 0.0f) {
-                                        gv = fminf(gv, op->clamp);
-                                        uv = fmaxf(-op->clamp, fminf(uv, op->clamp));
-                                    }
-                                    v = silu_f(gv) * uv;
-                                }
-                                const uint64_t o_idx = (uint64_t)b * n + row0 + r;
-                                if (op->residual != nullptr) v += __ldcg(op->residual + o_idx);
-                                op->dst[o_idx] = v;
-                            }
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&red_empty[rb]);
-                }
-            }
-            // this CTA's part of the operation is stored: count in
-            __syncwarp();
-            if (lane == 0) {
-                __threadfence();
-                atomicAdd(ca.arrivals, 1ull);
-            }
-            if (tracer) ca.trace[3 * oi + 2] = global_ns();
-        }
-    }
-}
-
 constexpr uint32_t SMEM_BUDGET = 220 * 1024;  // of the 227 KB a CTA may use
 constexpr uint32_t ACT_SMEM_MAX = 96 * 1024;  // measured: 116 KB (8 rows of k = 4096 in shared memory, two ring stages left) is slower than planes in global memory with a deeper ring
 
@@ -1659,26 +1334,16 @@ SmemPlan plan_smem(uint64_t k, uint64_t act_rows_in_smem, uint64_t jobs_per_cta)
     return p;
 }
 
-int g_num_sms = 0;
-
 template <uint32_t TYPE, int MB, int NH, int ACT, int GROUPED>
 cudaError_t launch_variant(GemvArgs& ga, uint64_t max_tiles, cudaStream_t s) {
     constexpr int NCW = 16;
-    if (g_num_sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-    }
+    const int g_num_sms = num_sms();
     unsigned grid = (unsigned)std::max<uint64_t>(1, std::min<uint64_t>(max_tiles, (uint64_t)g_num_sms));
     uint64_t per_cta = (max_tiles + grid - 1) / grid * (ga.swiglu ? 2 : 1);
     ga.plan = plan_smem<TYPE, NCW, MB * NH>(ga.k, ACT ? ga.x_rows : 0, per_cta);
     auto kern = gemv_mma_kernel<TYPE, MB, NH, NCW, ACT, GROUPED>;
-    static bool configured = false;  // per instantiation; one device per process
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static bool configured[MAX_DEVICES] = {};  // per instantiation and device
+    if (cudaError_t ce = set_max_smem_once(kern, (int)SMEM_BUDGET, configured); ce != cudaSuccess) return ce;
     cudaError_t e = launch_pdl(kern, grid, (NCW + 2) * 32, ga.plan.total, s, ga);
     return e != cudaSuccess ? e : cudaGetLastError();
 }
@@ -1846,6 +1511,8 @@ size_t gemv_mma_static_bytes_needed(uint64_t m, uint64_t k) { return (size_t)(m 
 
 cudaError_t launch_gemv_mma_static(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs,
                                    uint64_t m, float* dst, int* error_flag, cudaStream_t s) {
+    if (m == 0 || m > GEMV_MMA_MAX_M || k % 256 != 0 || gemv_mma_static_bytes_needed(m, k) > GEMV_STATIC_SCRATCH_BYTES)
+        return cudaErrorInvalidValue;  // the planes would not fit the fixed array
     void* planes = nullptr;
     cudaError_t e = gemv_mma_static_setup(&planes);
     if (e != cudaSuccess) return e;
@@ -1871,11 +1538,7 @@ template <uint32_t TYPE, int MB, int NH, int ACT>
 cudaError_t launch_narrow_variant(GemvArgs& ga, uint32_t max_jobs, cudaStream_t s) {
     using Tr = Traits<TYPE>;
     constexpr int NCW = 16;
-    if (g_num_sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-    }
+    const int g_num_sms = num_sms();
     const uint32_t upr = (uint32_t)(ga.k / 256), T = NCW / upr;
     const uint32_t tiles = (uint32_t)((ga.n + ROWS - 1) / ROWS), spe = (tiles + T - 1) / T;
     const uint64_t n_st = (uint64_t)max_jobs * spe;
@@ -1892,12 +1555,8 @@ cudaError_t launch_narrow_variant(GemvArgs& ga, uint32_t max_jobs, cudaStream_t 
     ga.plan = p;
     (void)sizeof(Tr);
     auto kern = gemv_narrow_kernel<TYPE, MB, NH, ACT>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static bool configured[MAX_DEVICES] = {};
+    if (cudaError_t ce = set_max_smem_once(kern, (int)SMEM_BUDGET, configured); ce != cudaSuccess) return ce;
     cudaError_t e = launch_pdl(kern, grid, (NCW + 2) * 32, p.total, s, ga);
     return e != cudaSuccess ? e : cudaGetLastError();
 }
@@ -1958,7 +1617,11 @@ cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s) {
     ga.norm_w = g.planes == nullptr ? g.norm_w : nullptr;
     ga.norm_eps = g.norm_eps;
     uint64_t tiles = (uint64_t)g.max_jobs * ((g.n + ROWS - 1) / ROWS);
+#ifdef JQ_PROFILING
     static const bool narrow_off = std::getenv("JQ_NO_NARROW_K") != nullptr;  // A/B switch for measurements
+#else
+    constexpr bool narrow_off = false;
+#endif
     // measured on the Qwen3-MoE shape: +5..8 % at 8 and 16 tokens per step, -2 % at one (where a job is one row)
     const bool narrow = !narrow_off && g.rows_per_job > 1 && narrow_k(g.type, g.k);
     if (g.planes == nullptr)
@@ -1967,83 +1630,6 @@ cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s) {
     ga.act = planes_in(g.planes, g.x_rows, g.k);
     return narrow ? launch_narrow_typed<0>(g.type, ga, g.rows_per_job, g.max_jobs, s)
                   : launch_typed<0, 2>(g.type, ga, g.rows_per_job, tiles, s);
-}
-
-// ── launching a chain ───────────────────────────────────────────────────────────────────────────────
-namespace {
-
-template <uint32_t TYPE, int MB, int NH>
-cudaError_t launch_chain_variant(ChainArgs& ca, uint64_t max_k, uint32_t att_floats, cudaStream_t s) {
-    constexpr int NCW = 16;
-    if (g_num_sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-    }
-    SmemPlan p = plan_smem<TYPE, NCW, MB * NH>(max_k, ca.m, 8);
-    uint32_t act = std::max<uint32_t>(p.act_bytes, att_floats * 4);
-    act = (act + 127) & ~127u;
-    uint32_t fixed = p.total - p.act_bytes - p.n_stages * ROWS * p.row_stride;
-    uint32_t stage = ROWS * p.row_stride;
-    if (act + fixed + stage > SMEM_BUDGET) return cudaErrorInvalidValue;
-    p.act_bytes = act;
-    p.n_stages = std::min<uint32_t>(8, (SMEM_BUDGET - fixed - act) / stage);
-    p.total = act + p.n_stages * stage + fixed;
-    ca.plan = p;
-    auto kern = gemv_chain_kernel<TYPE, MB, NH>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)g_num_sms);
-    cfg.blockDim = dim3((NCW + 2) * 32);
-    cfg.dynamicSmemBytes = p.total;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident at once: they wait on one another
-    attr[0].val.cooperative = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ca);
-    return e != cudaSuccess ? e : cudaGetLastError();
-}
-
-template <uint32_t TYPE>
-cudaError_t launch_chain_rows(ChainArgs& ca, uint64_t max_k, uint32_t att_floats, cudaStream_t s) {
-    if (ca.m == 1) return launch_chain_variant<TYPE, 1, 1>(ca, max_k, att_floats, s);
-    if (ca.m == 2) return launch_chain_variant<TYPE, 2, 1>(ca, max_k, att_floats, s);
-    if (ca.m <= 4) return launch_chain_variant<TYPE, 2, 2>(ca, max_k, att_floats, s);
-    if (ca.m <= 8) return launch_chain_variant<TYPE, 2, 4>(ca, max_k, att_floats, s);
-    return cudaErrorInvalidValue;
-}
-
-}  // namespace
-
-bool gemv_chain_supports(uint32_t type, uint64_t m, uint64_t max_k, uint32_t att_floats) {
-    if (type != T_Q4_K && type != T_Q8_0) return false;  // the chain is instantiated for the decode formats
-    return m >= 1 && m <= GEMV_MMA_MAX_M && max_k % 256 == 0 && acts_fit_in_smem(m, max_k) &&
-           att_floats * 4 <= ACT_SMEM_MAX;
-}
-
-cudaError_t launch_gemv_chain(uint32_t type, uint32_t m, const ChainOp* ops_dev, uint32_t n_ops, uint64_t max_k,
-                              uint32_t att_floats, unsigned long long* arrivals, int* error_flag, cudaStream_t s,
-                              unsigned long long* trace) {
-    if (!gemv_chain_supports(type, m, max_k, att_floats) || n_ops == 0) return cudaErrorInvalidValue;
-    ChainArgs ca = {};
-    ca.trace = trace;
-    ca.ops = ops_dev;
-    ca.n_ops = n_ops;
-    ca.m = m;
-    ca.arrivals = arrivals;
-    ca.error_flag = error_flag;
-    switch (type) {
-        case T_Q4_K: return launch_chain_rows<T_Q4_K>(ca, max_k, att_floats, s);
-        case T_Q8_0: return launch_chain_rows<T_Q8_0>(ca, max_k, att_floats, s);
-        default: return cudaErrorInvalidValue;
-    }
 }
 
 }  // namespace jq

@@ -186,31 +186,34 @@ int32_t run_experts_bucketed(jq_moe* m, const float* x, uint64_t T, uint64_t P, 
         }
         return e;
     };
+    // A failure between fork and join must still join: the caller's stream has to wait for whatever the
+    // auxiliary streams were already given before it (or the next layer) reuses the buffers.
+    int32_t first_rc = jq::OK;
     JQ_CUDA(fork());
-    for (size_t bi = 0; bi < buckets.size(); ++bi) {
+    for (size_t bi = 0; bi < buckets.size() && first_rc == jq::OK; ++bi) {
         const Bucket& b = buckets[bi];
         cudaStream_t as = cx->aux[bi % NAUX];
         const jq_weight wg = slice(m->gate, m->gate_expert_bytes, b.expert), wu = slice(m->up, m->gate_expert_bytes, b.expert);
-        if (int32_t rc = jq_matmul_device(&wg, b.cnt, c.hidden, c.inter, xs + (uint64_t)b.row0 * c.hidden,
-                                          gbuf + (uint64_t)b.row0 * c.inter, as))
-            return rc;
-        if (int32_t rc = jq_matmul_device(&wu, b.cnt, c.hidden, c.inter, xs + (uint64_t)b.row0 * c.hidden,
-                                          ubuf + (uint64_t)b.row0 * c.inter, as))
-            return rc;
+        first_rc = jq_matmul_device(&wg, b.cnt, c.hidden, c.inter, xs + (uint64_t)b.row0 * c.hidden,
+                                    gbuf + (uint64_t)b.row0 * c.inter, as);
+        if (first_rc == jq::OK)
+            first_rc = jq_matmul_device(&wu, b.cnt, c.hidden, c.inter, xs + (uint64_t)b.row0 * c.hidden,
+                                        ubuf + (uint64_t)b.row0 * c.inter, as);
     }
     JQ_CUDA(join());
+    if (first_rc != jq::OK) return first_rc;
     uint64_t live = 0;
     for (const Bucket& b : buckets) live = std::max<uint64_t>(live, (uint64_t)b.row0 + b.cnt);
     if (live) JQ_CUDA(jq::launch_swiglu(gbuf, ubuf, live * c.inter, c.clamp, m->hidden, s));
     JQ_CUDA(fork());
-    for (size_t bi = 0; bi < buckets.size(); ++bi) {
+    for (size_t bi = 0; bi < buckets.size() && first_rc == jq::OK; ++bi) {
         const Bucket& b = buckets[bi];
         const jq_weight wd = slice(m->down, m->down_expert_bytes, b.expert);
-        if (int32_t rc = jq_matmul_device(&wd, b.cnt, c.inter, c.hidden, m->hidden + (uint64_t)b.row0 * c.inter,
-                                          m->out + (uint64_t)b.row0 * c.hidden, cx->aux[bi % NAUX]))
-            return rc;
+        first_rc = jq_matmul_device(&wd, b.cnt, c.inter, c.hidden, m->hidden + (uint64_t)b.row0 * c.inter,
+                                    m->out + (uint64_t)b.row0 * c.hidden, cx->aux[bi % NAUX]);
     }
     JQ_CUDA(join());
+    if (first_rc != jq::OK) return first_rc;
     (void)T;
     return jq::OK;
 }
@@ -468,7 +471,11 @@ int32_t jq_moe_forward_norm_add_dev(jq_moe* m, const float* x_dev, uint64_t T, c
     // buckets spread over eight streams.  Measured on 384 MXFP4 experts of 7168 x 2048 at 4096 tokens (85 rows per
     // expert): 61 ms this way against 126 ms for the grouped decode kernel (322 ms on a single stream, where one
     // expert's tile GEMM fills 16 of 148 SMs).
+#ifdef JQ_PROFILING
     static const char* thr_env = std::getenv("JQ_MOE_BUCKET_ROWS");  // average rows per expert from which to bucket
+#else
+    constexpr const char* thr_env = nullptr;
+#endif
     // small experts (Qwen3-MoE: 2048 x 768) need more rows before a bucket beats the grouped kernel: measured
     // 9.0 against 3.9 ms at 64 rows per expert, 11.5 against 14.9 ms at 256
     const uint64_t thr = thr_env ? std::strtoull(thr_env, nullptr, 10)
@@ -488,10 +495,12 @@ int32_t jq_moe_forward_norm_add_dev(jq_moe* m, const float* x_dev, uint64_t T, c
     return jq::OK;
 }
 
+#ifdef JQ_PROFILING
 int32_t jq_debug_moe_trace(uint64_t* trace_dev) {
     JQ_CUDA(jq::moe_set_trace(reinterpret_cast<unsigned long long*>(trace_dev)));
     return jq::OK;
 }
+#endif
 
 int32_t jq_moe_status(jq_moe* m) {
     if (!m) return jq_fail(jq::E_INVALID, "jq_moe_status: NULL handle");

@@ -77,6 +77,11 @@ class LlamaDecoder:
         self.token = torch.full((B,), 42, dtype=torch.int32, device=device)
         self.pos = torch.zeros(B, dtype=torch.int32, device=device)
         self.bad = torch.zeros(1, dtype=torch.int32, device=device)
+        self.bad_pos = torch.zeros(1, dtype=torch.int32, device=device)   # a position ran past the KV cache
+        # greedy sampling with the reference's repetition penalty (1.0 = plain arg-max) over the last 64 ids
+        self.repetition_penalty = 1.0
+        self.window = torch.zeros(B, 64, dtype=torch.int32, device=device)
+        self.window_state = torch.zeros(B, 2, dtype=torch.int32, device=device)
         self.x = torch.empty(B, h, **f32)
         self.x1 = torch.empty(B, h, **f32)
         self.xn = torch.empty(B, h, **f32)
@@ -111,55 +116,41 @@ class LlamaDecoder:
                                        P(self.qkv), s))
             check(L.jq_attention_fused_dev(P(self.qkv), P(self.pos), B, c.q_heads, c.kv_heads, c.head_dim,
                                            self.max_ctx, c.rope_theta, P(ly["k"]), P(ly["v"]), P(self.attn),
-                                           P(self.att_fused_scratch), s))
+                                           P(self.att_fused_scratch), P(self.bad_pos), s))
             check(L.jq_matmul_norm_dev(ly["wo"]._h, B, c.q_heads * c.head_dim, h, P(self.attn), None, 0.0, P(self.x),
                                        P(self.x), s))
             self._ffn(ly, s)
         check(L.jq_matmul_norm_dev(self.output._h, B, h, c.vocab, P(self.x), P(self.out_norm), c.eps, None,
                                    P(self.logits), s))
-        check(L.jq_argmax_dev(P(self.logits), B, c.vocab, P(self.token), P(self.pos), P(self.argmax_scratch), s))
+        self._sample(s)
 
-    def build_chain(self) -> None:
-        """The layers and the output head as ONE persistent launch (`jq_chain_*`): per layer the QKV linear
-        (norm prologue), attention, the output projection (residual epilogue), the gate / up SwiGLU pair (norm
-        prologue) and the down projection (residual epilogue), then the head (norm prologue)."""
+    def _sample(self, s) -> None:
+        """Next token of every sequence from self.logits (`sample_token` of src/engine.rs:2339-2378 at
+        temperature 0): repetition penalty over the recent-id window, arg-max with the last maximal index
+        winning ties, the id pushed into the window, the position advanced."""
         L, c, B, P = _lib.lib(), self.cfg, self.batch, lambda t: t.data_ptr()
-        h = c.hidden
-        ch = ctypes.c_void_p()
-        check(L.jq_chain_create(self.embed.ctx._h, self.wtype, B, ctypes.byref(ch)))
-        self._chain = ch
-        for ly in self.layers:
-            check(L.jq_chain_add_linear(ch, ly["wqkv"]._h, None, h, c.qkv_rows, P(self.x), P(ly["attn_norm"]), c.eps,
-                                        None, 0.0, P(self.qkv)))
-            check(L.jq_chain_add_attention(ch, P(self.qkv), P(self.pos), c.q_heads, c.kv_heads, c.head_dim,
-                                           self.max_ctx, c.rope_theta, P(ly["k"]), P(ly["v"]), P(self.attn),
-                                           P(self.att_fused_scratch)))
-            check(L.jq_chain_add_linear(ch, ly["wo"]._h, None, c.q_heads * c.head_dim, h, P(self.attn), None, 0.0,
-                                        P(self.x), 0.0, P(self.x)))
-            check(L.jq_chain_add_linear(ch, ly["w_gate"]._h, ly["w_up"]._h, h, c.ffn, P(self.x), P(ly["ffn_norm"]),
-                                        c.eps, None, 0.0, P(self.act)))
-            check(L.jq_chain_add_linear(ch, ly["w_down"]._h, None, c.ffn, h, P(self.act), None, 0.0, P(self.x), 0.0,
-                                        P(self.x)))
-        check(L.jq_chain_add_linear(ch, self.output._h, None, h, c.vocab, P(self.x), P(self.out_norm), c.eps, None, 0.0,
-                                    P(self.logits)))
+        if self.repetition_penalty == 1.0:
+            self._sample(s)
+        else:
+            check(L.jq_sample_greedy_dev(P(self.logits), B, c.vocab, self.repetition_penalty, P(self.window),
+                                         P(self.window_state), P(self.token), P(self.pos), P(self.argmax_scratch), s))
 
-    def step_chain(self, stream=None) -> None:
-        """The same step in four launches: embedding, the chain, the two arg-max stages."""
-        L, c, B, P = _lib.lib(), self.cfg, self.batch, lambda t: t.data_ptr()
-        s = self.torch.cuda.current_stream(self.dev).cuda_stream if stream is None else stream
-        if getattr(self, "_chain", None) is None:
-            self.build_chain()
-        check(L.jq_embedding_dev(self.embed._h, P(self.token), B, c.vocab, c.hidden, P(self.x), P(self.bad), s))
-        check(L.jq_chain_run(self._chain, s))
-        check(L.jq_argmax_dev(P(self.logits), B, c.vocab, P(self.token), P(self.pos), P(self.argmax_scratch), s))
+    def seed_window(self, prompt_ids) -> None:
+        """Fills the recent-id window with the tail of the prompt, as the reference's decode loop does
+        (src/engine.rs:1222-1232)."""
+        torch = self.torch
+        tail = [int(t) for t in prompt_ids][-64:]
+        w = torch.zeros(self.batch, 64, dtype=torch.int32)
+        w[:, :len(tail)] = torch.tensor(tail, dtype=torch.int32)
+        self.window.copy_(w)
+        self.window_state.copy_(torch.tensor([[len(tail), len(tail) % 64]] * self.batch, dtype=torch.int32))
 
-    def __del__(self):
-        try:
-            if getattr(self, "_chain", None) is not None:
-                _lib.lib().jq_chain_free(self._chain)
-                self._chain = None
-        except Exception:
-            pass
+    def check_flags(self) -> None:
+        """Raises if a token id was out of range or a position ran past the KV cache (synchronises)."""
+        if int(self.bad.item()) != 0:
+            raise _lib.JoshuaB200Error(_lib.E_INVALID, "embedding id out of range")
+        if int(self.bad_pos.item()) != 0:
+            raise _lib.JoshuaB200Error(_lib.E_TOO_LARGE, f"a position ran past the KV cache of {self.max_ctx} positions")
 
     def step_unfused(self, stream=None) -> None:
         """The same step from the separate kernels (norm, rope, attention partial + merge as their own
@@ -172,15 +163,15 @@ class LlamaDecoder:
             check(L.jq_rmsnorm_dev(P(self.x), None, P(ly["attn_norm"]), c.eps, B, h, None, P(self.xn), s))
             check(L.jq_matmul_t_dev(ly["wqkv"]._h, B, h, c.qkv_rows, P(self.xn), P(self.qkv), s))
             check(L.jq_rope_append_dev(P(self.qkv), P(self.pos), B, c.q_heads, c.kv_heads, c.head_dim, self.max_ctx,
-                                       c.rope_theta, P(self.q), P(ly["k"]), P(ly["v"]), s))
+                                       c.rope_theta, P(self.q), P(ly["k"]), P(ly["v"]), P(self.bad_pos), s))
             check(L.jq_attention_decode_dev(P(self.q), P(ly["k"]), P(ly["v"]), P(self.pos), B, c.q_heads, c.kv_heads,
-                                            c.head_dim, self.max_ctx, P(self.attn), P(self.att_scratch), s))
+                                            c.head_dim, self.max_ctx, P(self.attn), P(self.att_scratch), P(self.bad_pos), s))
             check(L.jq_matmul_t_dev(ly["wo"]._h, B, c.q_heads * c.head_dim, h, P(self.attn), P(self.o), s))
             check(L.jq_add_dev(P(self.x), P(self.o), B * h, P(self.x), s))
             self._ffn(ly, s)
         check(L.jq_rmsnorm_dev(P(self.x), None, P(self.out_norm), c.eps, B, h, None, P(self.xn), s))
         check(L.jq_matmul_t_dev(self.output._h, B, h, c.vocab, P(self.xn), P(self.logits), s))
-        check(L.jq_argmax_dev(P(self.logits), B, c.vocab, P(self.token), P(self.pos), P(self.argmax_scratch), s))
+        self._sample(s)
 
     def _ffn(self, ly, s) -> None:
         """self.x += FFN(rmsnorm(self.x; ffn_norm)): the dense SwiGLU MLP in two launches."""
@@ -230,7 +221,11 @@ class LlamaDecoder:
                 self.pos.copy_(pos0)
                 stream.synchronize()
             self._host = (stream, tok_pin, log_pin, graph)
+            self._host_calls = int(self.pos.max().item())
         stream, tok_pin, log_pin, graph = self._host
+        if self._host_calls >= self.max_ctx:
+            raise _lib.JoshuaB200Error(_lib.E_TOO_LARGE, f"the KV cache holds {self.max_ctx} positions; reset() starts a new sequence")
+        self._host_calls += 1
         tok_pin.copy_(torch.as_tensor(token_ids, dtype=torch.int32).reshape(self.batch))
         with torch.cuda.stream(stream):
             self.token.copy_(tok_pin, non_blocking=True)
@@ -245,6 +240,9 @@ class LlamaDecoder:
     def reset(self, token: int = 42) -> None:
         self.token.fill_(token)
         self.pos.zero_()
+        self.window.zero_()
+        self.window_state.zero_()
+        self._host_calls = 0
 
     def force_token(self, token: int) -> None:
         self.token.fill_(token)

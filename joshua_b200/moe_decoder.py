@@ -34,7 +34,10 @@ class MoeDecoderConfig(LlamaConfig):
 
 class MoeDecoder(LlamaDecoder):
     def __init__(self, cfg: MoeDecoderConfig, device, batch: int = 1, max_ctx: int = 640, attn_type: int = synth.Q8_0,
-                 expert_type: int = synth.Q4_K, seed: int = 0, group=None):
+                 expert_type: int = synth.Q4_K, seed: int = 0, group=None, weights=None, expert_weights=None):
+        """`weights(name, rows, cols, seed)` / `expert_weights(name, rows, cols, seed)` may supply the raw blocks
+        of the dense linears / of this rank's slice of an expert bank (flat uint8 tensors); the defaults draw
+        them on the device.  `seed` must be the same on every rank: dense weights are replicated."""
         import torch
         import torch.distributed as dist
 
@@ -43,7 +46,9 @@ class MoeDecoder(LlamaDecoder):
         self.rank = dist.get_rank(group) if group is not None else 0
         self._expert_type = expert_type
         self._dense_ffn = False
-        super().__init__(cfg, device, batch=batch, max_ctx=max_ctx, wtype=attn_type, seed=seed)
+        super().__init__(cfg, device, batch=batch, max_ctx=max_ctx, wtype=attn_type, seed=seed, weights=weights)
+        mk_expert = expert_weights or (lambda name, rows, cols, s: synth.random_weight_torch(expert_type, rows, cols, s, device))
+        self.routers, self._expert_raw = [], []
         ctx = default_context(device.index or 0)
         E, K, h, I = cfg.n_expert, cfg.n_used, cfg.hidden, cfg.moe_inter
         per = E // self.world
@@ -58,11 +63,13 @@ class MoeDecoder(LlamaDecoder):
             for i, (rows, cols) in enumerate([(I, h), (I, h), (h, I)]):
                 full_seed = 5000 + l * 8 + i
                 # each rank draws only its own experts' blocks; the seed folds in the first local expert
-                raw = synth.random_weight_torch(expert_type, per * rows, cols, full_seed * 1000 + self.rank * per, device)
+                raw = mk_expert(f"l{l}.experts{i}", per * rows, cols, full_seed * 1000 + self.rank * per).to(device)
                 raw = torch.cat([raw, torch.zeros(16, dtype=torch.uint8, device=device)])
                 nbytes = synth.tensor_bytes(expert_type, per * rows, cols)
                 self.expert_bytes += nbytes
                 banks.append((QTensor.from_device(expert_type, raw[:nbytes], ctx), raw))
+            self.routers.append(router)
+            self._expert_raw.append([b[1] for b in banks])
             if self.world == 1:
                 layer = Moe(MoeConfig(gating=GATE_SOFTMAX, n_expert=E, n_used=K, hidden=h, inter=I, norm=True),
                             router, banks[0][0], banks[1][0], banks[2][0], ctx=ctx)

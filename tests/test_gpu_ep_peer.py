@@ -69,3 +69,56 @@ def test_exchange_rejects_bad_arguments():
     assert b"evenly" in _lib.lib().jq_last_error()
     assert _lib.lib().jq_ep_create(ctx._h, 2, 2, 16, 4, 512, 8, ctypes.byref(h)) != 0   # rank out of range
     assert _lib.lib().jq_ep_create(ctx._h, 0, 1, 16, 4, 512, 4096, ctypes.byref(h)) != 0  # window too large
+
+
+def test_absent_peer_times_out_and_the_context_stays_usable():
+    """Rank 0 of a two-rank layout whose peer never serves its window (loopback: the peer's window is a private
+    local allocation, nothing publishes its flags).  With the wait bound cut to a few thousand polls both waits of
+    the layer run out, the kernels return, the status is JQ_E_TIMEOUT exactly once, and ordinary work on the
+    same context still passes.  No rank dies and nothing waits without a bound."""
+    import ctypes
+
+    import torch
+
+    import oracle
+    from joshua_b200 import _lib
+    from joshua_b200.moe import GATE_SOFTMAX, OOB_SKIP, Moe, MoeConfig
+    from joshua_b200.qtensor import QTensor, default_context
+
+    L, ctx = _lib.lib(), default_context(0)
+    world, per = 2, E // 2
+    rng = np.random.default_rng(11)
+    router = rng.standard_normal((E, H)).astype(np.float32) * 0.5
+    banks = [QTensor.from_bytes(synth.Q4_K, synth.random_weight(synth.Q4_K, per * INTER, H, 1), ctx),
+             QTensor.from_bytes(synth.Q4_K, synth.random_weight(synth.Q4_K, per * INTER, H, 2), ctx),
+             QTensor.from_bytes(synth.Q4_K, synth.random_weight(synth.Q4_K, per * H, INTER, 3), ctx)]
+    router_layer = Moe(MoeConfig(gating=GATE_SOFTMAX, n_expert=E, n_used=K, hidden=H, inter=INTER), router,
+                       None, None, None, ctx=ctx)
+    experts = Moe(MoeConfig(gating=GATE_SOFTMAX, n_expert=per, n_used=1, hidden=H, inter=INTER, oob_policy=OOB_SKIP),
+                  np.zeros((per, H), np.float32), *banks, ctx=ctx)
+    T = 2
+    ep = ctypes.c_void_p()
+    _lib.check(L.jq_ep_create(ctx._h, 0, world, E, K, H, T, ctypes.byref(ep)))
+    try:
+        _lib.check(L.jq_ep_connect_loopback(ep))
+        _lib.check(L.jq_ep_set_poll_limit(ep, 4000))
+        router_layer.reserve(T, 0)
+        experts.reserve(world * T * K, world * T * K)
+        _lib.check(L.jq_device_status(ctx._h))            # clean before
+        x = torch.from_numpy((rng.standard_normal((T, H)) * 0.02).astype(np.float32)).cuda()
+        y = torch.zeros_like(x)
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(L.jq_ep_forward_dev(ep, router_layer._h, experts._h, x.data_ptr(), T, None, y.data_ptr(), s))
+        torch.cuda.synchronize()                          # returns: the waits were bounded
+        assert L.jq_device_status(ctx._h) == _lib.E_TIMEOUT
+        assert L.jq_device_status(ctx._h) == _lib.OK      # reported once, then cleared
+        assert bool(torch.isfinite(y).all())
+    finally:
+        L.jq_ep_free(ep)
+    # the context still serves ordinary products
+    m, k, n = 1, 1024, 256
+    raw = synth.random_weight(synth.Q4_K, n, k, seed=5)
+    lhs = synth.random_activations(m, k, seed=6)
+    got = QTensor.from_bytes(synth.Q4_K, raw, ctx).matmul_t((m, k, n), lhs)
+    want = oracle.matmul_t(synth.Q4_K, (m, k, n), lhs, raw)
+    assert float((np.abs(got - want) / np.maximum(np.abs(want), 1.0)).max()) <= 1e-3

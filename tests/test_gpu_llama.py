@@ -87,7 +87,7 @@ def test_decode_steps_match_torch_reference(wtype):
         scale = max(1.0, float(np.abs(want[step]).max()))
         assert float(np.abs(got[step] - want[step]).max()) <= 2e-3 * scale, step
         # greedy token: last maximal index wins ties (src/engine.rs:2371-2378)
-        ref_tok = len(want[step]) - 1 - int(np.argmax(got[step][::-1]))
+        ref_tok = len(want[step]) - 1 - int(np.argmax(want[step][::-1]))
         nxt = fed[step + 1] if step + 1 < len(fed) else int(dec.token.item())
         assert nxt == ref_tok
 
@@ -168,43 +168,141 @@ def test_fused_attention_matches_rope_append_attention(nq, nkv, hd, ctx):
     want = torch.empty(B, nq * hd, device="cuda")
     scratch = torch.empty(L.jq_attention_scratch_bytes(B, nq, hd, max_ctx) // 4 + 1, device="cuda")
     _lib.check(L.jq_rope_append_dev(qkv.data_ptr(), pos.data_ptr(), B, nq, nkv, hd, max_ctx, theta, q.data_ptr(),
-                                    ck.data_ptr(), cv.data_ptr(), s))
+                                    ck.data_ptr(), cv.data_ptr(), None, s))
     _lib.check(L.jq_attention_decode_dev(q.data_ptr(), ck.data_ptr(), cv.data_ptr(), pos.data_ptr(), B, nq, nkv, hd,
-                                         max_ctx, want.data_ptr(), scratch.data_ptr(), s))
+                                         max_ctx, want.data_ptr(), scratch.data_ptr(), None, s))
     got = torch.empty(B, nq * hd, device="cuda")
     fscratch = torch.zeros(L.jq_attention_fused_scratch_bytes(B, nq, nkv, hd, max_ctx) // 4 + 1, device="cuda")
     for _ in range(2):   # twice: the arrival counters must come back to zero
         _lib.check(L.jq_attention_fused_dev(qkv.data_ptr(), pos.data_ptr(), B, nq, nkv, hd, max_ctx, theta,
-                                            ck2.data_ptr(), cv2.data_ptr(), got.data_ptr(), fscratch.data_ptr(), s))
+                                            ck2.data_ptr(), cv2.data_ptr(), got.data_ptr(), fscratch.data_ptr(),
+                                            None, s))
     torch.cuda.synchronize()
     assert torch.equal(ck, ck2) and torch.equal(cv, cv2)          # same appended rows, bit for bit
     assert float((got - want).abs().max()) <= 2e-5 * max(1.0, float(want.abs().max()))
 
 
-@pytest.mark.parametrize("batch,wtype", [(1, synth.Q4_K), (3, synth.Q4_K), (1, synth.Q8_0)])
-def test_chain_step_matches_separate_launches(batch, wtype):
-    """The persistent chain (one launch for all layers and the head) against the five-launch-per-layer step:
-    same kernels' arithmetic operation by operation, so the logits agree to rounding of the norm sums."""
+def test_positions_beyond_the_cache_store_nothing_and_raise_the_flag():
+    """Stepping past max_ctx: the kernels skip the append and the attention for that sequence, the flag is set,
+    the memory behind the cache is untouched (the cache is the front part of a larger canary-filled buffer),
+    and a negative position is treated the same way.  Nothing faults: the checks skip the access."""
     import torch
 
-    cfg = LlamaConfig(layers=3, hidden=512, q_heads=8, kv_heads=2, head_dim=128, ffn=768, vocab=1000)
-    mk = _small_weights(wtype)
-    a = LlamaDecoder(cfg, torch.device("cuda", 0), batch=batch, max_ctx=150, wtype=wtype, seed=5, weights=mk)
-    b = LlamaDecoder(cfg, torch.device("cuda", 0), batch=batch, max_ctx=150, wtype=wtype, seed=5, weights=mk)
-    a.reset(7)
-    b.reset(7)
-    for step in range(140):
-        a.step_chain()
-        b.step()
-        torch.cuda.synchronize()
-        la, lb = a.logits.cpu().numpy(), b.logits.cpu().numpy()
-        scale = max(1.0, float(np.abs(lb).max()))
-        assert float(np.abs(la - lb).max()) <= 1e-5 * scale, step
-        b.token.copy_(a.token)
-    assert a.pos.tolist() == [140] * batch
-    from joshua_b200.qtensor import default_context
     from joshua_b200 import _lib
-    _lib.check(_lib.lib().jq_device_status(default_context(0)._h))
+
+    L = _lib.lib()
+    B, nq, nkv, hd, max_ctx, theta = 2, 8, 2, 64, 8, 10000.0
+    cache_elems = B * nkv * max_ctx * hd
+    s = torch.cuda.current_stream().cuda_stream
+    for bad_value in (max_ctx, max_ctx + 5, -1):
+        big_k = torch.full((cache_elems + 4096,), 7.5, device="cuda")
+        big_v = torch.full((cache_elems + 4096,), -7.5, device="cuda")
+        qkv = torch.randn(B, (nq + 2 * nkv) * hd, device="cuda")
+        pos = torch.tensor([3, bad_value], dtype=torch.int32, device="cuda")
+        out = torch.full((B, nq * hd), 123.0, device="cuda")
+        q = torch.empty(B, nq * hd, device="cuda")
+        flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+        fscratch = torch.zeros(L.jq_attention_fused_scratch_bytes(B, nq, nkv, hd, max_ctx) // 4 + 1, device="cuda")
+        _lib.check(L.jq_attention_fused_dev(qkv.data_ptr(), pos.data_ptr(), B, nq, nkv, hd, max_ctx, theta,
+                                            big_k.data_ptr(), big_v.data_ptr(), out.data_ptr(), fscratch.data_ptr(),
+                                            flag.data_ptr(), s))
+        torch.cuda.synchronize()
+        assert int(flag.item()) == 1
+        assert bool((big_k[cache_elems:] == 7.5).all()) and bool((big_v[cache_elems:] == -7.5).all())
+        # sequence 1 stored nothing anywhere in its own cache block either; sequence 0 appended at position 3
+        k4 = big_k[:cache_elems].view(B, nkv, max_ctx, hd)
+        assert bool((k4[1] == 7.5).all()) and not bool((k4[0, :, 3] == 7.5).all())
+        assert bool((out[1] == 123.0).all()) and bool(torch.isfinite(out[0]).all()) and not bool((out[0] == 123.0).any())
+        assert bool((fscratch[-B * nkv * 2 - 1:] == 0).all())         # arrival counters back at zero
+        flag.zero_()
+        _lib.check(L.jq_rope_append_dev(qkv.data_ptr(), pos.data_ptr(), B, nq, nkv, hd, max_ctx, theta, q.data_ptr(),
+                                        big_k.data_ptr(), big_v.data_ptr(), flag.data_ptr(), s))
+        scratch = torch.empty(L.jq_attention_scratch_bytes(B, nq, hd, max_ctx) // 4 + 1, device="cuda")
+        _lib.check(L.jq_attention_decode_dev(q.data_ptr(), big_k.data_ptr(), big_v.data_ptr(), pos.data_ptr(), B, nq,
+                                             nkv, hd, max_ctx, out.data_ptr(), scratch.data_ptr(), flag.data_ptr(), s))
+        torch.cuda.synchronize()
+        assert int(flag.item()) == 1
+        assert bool((big_k[cache_elems:] == 7.5).all()) and bool((big_v[cache_elems:] == -7.5).all())
+        assert bool(torch.isnan(out[1]).all()) and bool(torch.isfinite(out[0]).all())
+
+
+def test_decoder_reports_a_full_cache():
+    import torch
+
+    cfg = LlamaConfig(layers=1, hidden=256, q_heads=4, kv_heads=2, head_dim=64, ffn=256, vocab=256)
+    dec = LlamaDecoder(cfg, torch.device("cuda", 0), batch=1, max_ctx=4, seed=1, weights=_small_weights(synth.Q4_K))
+    dec.reset(5)
+    for _ in range(4):
+        dec.step()
+    dec.check_flags()
+    dec.step()                      # position 4 of a 4-position cache
+    with pytest.raises(Exception, match="KV cache"):
+        dec.check_flags()
+    dec2 = LlamaDecoder(cfg, torch.device("cuda", 0), batch=1, max_ctx=4, seed=1, weights=_small_weights(synth.Q4_K))
+    tok = np.array([5], np.int32)
+    for _ in range(4):
+        dec2.forward_host(tok)
+    with pytest.raises(Exception, match="KV cache"):
+        dec2.forward_host(tok)
+
+
+def reference_sample(logits, penalty, recent):
+    """sample_token at temperature 0 (src/engine.rs:2339-2378), in float32 like the reference."""
+    v = logits.astype(np.float32).copy()
+    p = np.float32(penalty)
+    if penalty != 1.0:
+        for t in recent:
+            if 0 <= t < len(v):
+                v[t] = v[t] / p if v[t] > 0 else v[t] * p
+    return len(v) - 1 - int(np.argmax(v[::-1]))      # the last maximal index
+
+
+def test_greedy_sampler_with_repetition_penalty_matches_the_reference_rule():
+    import torch
+
+    from joshua_b200 import _lib
+
+    L = _lib.lib()
+    rng = np.random.default_rng(0)
+    rows, vocab, penalty = 3, 5000, 1.1
+    s = torch.cuda.current_stream().cuda_stream
+    scratch = torch.empty(L.jq_argmax_scratch_bytes(rows) // 4 + 1, device="cuda")
+    window = torch.zeros(rows, 64, dtype=torch.int32, device="cuda")
+    state = torch.zeros(rows, 2, dtype=torch.int32, device="cuda")
+    token = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    pos = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    recent = [[] for _ in range(rows)]
+    for step in range(150):         # runs well past 64 ids: the ring wraps
+        base = rng.standard_normal((rows, vocab)).astype(np.float32)
+        # a few near-tied leaders per row, several of them recently sampled, so that the penalty decides
+        for r in range(rows):
+            lead = list(rng.integers(0, vocab, 3)) + recent[r][-3:]
+            base[r, lead] = 4.0 + 0.05 * rng.standard_normal(len(lead)).astype(np.float32)
+            if step % 7 == 0 and recent[r]:
+                base[r, :] = -np.abs(base[r, :])            # all negative: the penalty multiplies
+                base[r, recent[r][-1]] = -1e-3
+                base[r, (recent[r][-1] + 1) % vocab] = np.float32(-1.05e-3)
+        logits = torch.from_numpy(base).cuda()
+        _lib.check(L.jq_sample_greedy_dev(logits.data_ptr(), rows, vocab, penalty, window.data_ptr(), state.data_ptr(),
+                                          token.data_ptr(), pos.data_ptr(), scratch.data_ptr(), s))
+        torch.cuda.synchronize()
+        assert torch.equal(logits.cpu(), torch.from_numpy(base))       # the caller's logits are unchanged
+        got = token.tolist()
+        for r in range(rows):
+            want = reference_sample(base[r], penalty, recent[r])
+            assert got[r] == want, (step, r, got[r], want)
+            recent[r] = (recent[r] + [want])[-64:]
+    assert pos.tolist() == [150] * rows
+    # duplicates count once per occurrence: an id held three times is divided three times
+    base = np.zeros((1, vocab), np.float32)
+    base[0, 10], base[0, 20] = 1.30, 1.0
+    window[0, :3] = 10
+    state[0] = torch.tensor([3, 3], dtype=torch.int32)
+    logits = torch.from_numpy(base).cuda()
+    _lib.check(L.jq_sample_greedy_dev(logits.data_ptr(), 1, vocab, penalty, window.data_ptr(), state.data_ptr(),
+                                      token.data_ptr(), pos.data_ptr(), scratch.data_ptr(), s))
+    torch.cuda.synchronize()
+    assert int(token[0]) == 20 == reference_sample(base[0], penalty, [10, 10, 10])   # 1.3 / 1.1^3 < 1.0
 
 
 def test_forward_host_matches_device_steps():

@@ -6,13 +6,16 @@ not tolerable.  For them the library carries its scratch - the int8 activation p
 two kernels of a decode product - in a fixed 4 MiB device array.  The test calls the entry through the C ABI
 twice in a row with different inputs (the array keeps the first call's contents, so the second call shows
 that stale data is not read) and compares with `jq_matmul_t_dev`, which takes its planes in shared memory or
-in allocated scratch.  This file is collected last, so a failure here cannot hide another test's result.
+in allocated scratch, and with the CPU oracle.  It also checks the property the entry exists for: once the
+first call on the device has done its set-up, a call leaves the amount of free device memory unchanged.
+This file is collected last, so a failure here cannot hide another test's result.
 """
 import ctypes
 
 import numpy as np
 import pytest
 
+import oracle
 from joshua_b200 import _lib, synth
 from joshua_b200._lib import JoshuaB200Error, check
 from joshua_b200.qtensor import QTensor
@@ -36,15 +39,37 @@ def test_two_calls_in_a_row_match_the_allocating_entry(type_id, mkn):
     import torch
 
     m, k, n = mkn
-    q = QTensor.from_bytes(type_id, synth.random_weight(type_id, n, k, seed=n))
+    raw = synth.random_weight(type_id, n, k, seed=n)
+    q = QTensor.from_bytes(type_id, raw)
     for call in range(2):
-        x = torch.from_numpy(synth.random_activations(m, k, seed=100 * call + m)).cuda() * (1.0 + 3.0 * call)
+        lhs = synth.random_activations(m, k, seed=100 * call + m) * np.float32(1.0 + 3.0 * call)
+        x = torch.from_numpy(lhs).cuda()
         want = torch.empty(m, n, device="cuda")
         got = torch.full((m, n), 7.25, device="cuda")
         q.matmul_t_dev(mkn, x, want)
         noalloc(q, mkn, x, got)
         torch.cuda.synchronize()
-        assert_close(got.cpu().numpy(), want.cpu().numpy(), tol=TOL, what=f"{synth.NAMES[type_id]} {mkn} call {call}")
+        what = f"{synth.NAMES[type_id]} {mkn} call {call}"
+        assert_close(got.cpu().numpy(), want.cpu().numpy(), tol=TOL, what=what + " vs jq_matmul_t_dev")
+        assert_close(got.cpu().numpy(), oracle.matmul_t(type_id, mkn, lhs, raw), tol=TOL, what=what + " vs oracle")
+
+
+def test_a_call_leaves_free_device_memory_unchanged():
+    """After the set-up call, further calls - also with a shape that was never seen before, and one whose planes
+    would fit shared memory - neither take nor return device memory."""
+    import torch
+
+    shapes = [(synth.Q4_K, (8, 14336, 256)), (synth.Q4_K, (1, 1024, 512)), (synth.Q8_0, (4, 8192, 128))]
+    qs = [(QTensor.from_bytes(t, synth.random_weight(t, mkn[2], mkn[1], seed=3)), mkn) for t, mkn in shapes]
+    bufs = [(torch.randn(m, k, device="cuda"), torch.empty(m, n, device="cuda")) for _, (m, k, n) in qs]
+    noalloc(qs[0][0], qs[0][1], *bufs[0])     # the first call on the device: symbol address, kernel attributes
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for (q, mkn), (x, y) in zip(qs, bufs):
+        noalloc(q, mkn, x, y)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
 
 
 def test_sizes_beyond_the_built_in_array_are_refused():
