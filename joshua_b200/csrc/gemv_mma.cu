@@ -39,6 +39,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "pipe.cuh"
 
 namespace jq {
 
@@ -49,40 +50,6 @@ namespace {
 constexpr int ROWS = 16;  // weight rows per CTA (one MMA M tile)
 
 // ───────────────────────────── PTX helpers ────────────────────────────────
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
-// Bounded wait: returns false when the phase has not completed after ~2^26 polls.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t addr = smem_u32(bar);
-    for (uint32_t it = 0; it < (1u << 26); ++it) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-// 1-D bulk copy global -> shared, completion counted on an mbarrier.  All of
-// dst, src and bytes are multiples of 16.
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
 
 __device__ __forceinline__ void mma_k32(int c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -111,10 +78,6 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     return r;
 }
 
-__device__ __forceinline__ uint32_t lds32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
-__device__ __forceinline__ uint2 lds64(const uint8_t* p) { return *reinterpret_cast<const uint2*>(p); }
-__device__ __forceinline__ uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
-__device__ __forceinline__ uint32_t lds16(const uint8_t* p) { return *reinterpret_cast<const unsigned short*>(p); }
 // 8 bytes starting at p (p 2-byte aligned with the given word misalignment in bytes: 0 or 2).
 template <int MIS>
 __device__ __forceinline__ uint2 lds64_mis(const uint8_t* p) {
@@ -148,12 +111,6 @@ __device__ __forceinline__ uint32_t act_position(uint32_t type, uint32_t e) {
     uint32_t half = e >> 4, r = e & 15;
     return 8 * (r >> 2) + 2 * (r & 3) + half;
 }
-
-// Programmatic dependent launch: `pdl_wait` blocks until the preceding kernel in the stream has completed
-// and its writes are visible; `pdl_trigger` lets the next kernel (if it was launched with the programmatic
-// attribute) start its own prologue.  Both are no-ops for ordinary launches.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Splits the 256 values of one unit, 8 per lane (lane l holds values 8l .. 8l+7, group l / 4), into the three
 // planes.  `planes` points at the unit's first group (8 x 96 bytes), `meta` / `sum16` at its first entries.
@@ -802,10 +759,6 @@ __device__ __forceinline__ void process_unit(const uint8_t* u0, const uint8_t* u
 // dst) so that consumers move on to the next tile without waiting.  The activation planes of the whole
 // product are copied to shared memory once per CTA when they fit.
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
 struct SmemPlan {
     uint32_t row_stride;   // bytes between rows of a stage
     uint32_t n_stages;     // ring depth
@@ -880,7 +833,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 1) gemv_mma_kernel(const __gri
             mbar_init(&red_full[b], NCW);
             mbar_init(&red_empty[b], 1);
         }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_fence_init();
     }
     if (TYPE == T_IQ2_XXS) {
         for (int i = tid; i < 256; i += (NCW + 2) * 32) s_grid[i] = g_iq2xxs_grid[i];
@@ -1127,7 +1080,7 @@ __global__ void __launch_bounds__((16 + 2) * 32, 1) gemv_narrow_kernel(const __g
             mbar_init(&red_full[b], NCW);
             mbar_init(&red_empty[b], 1);
         }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_fence_init();
     }
     if (TYPE == T_IQ2_XXS) {
         for (int i = tid; i < 256; i += (NCW + 2) * 32) s_grid[i] = g_iq2xxs_grid[i];
@@ -1420,6 +1373,8 @@ cudaError_t launch_gemv_mma_fused(uint32_t type, const uint8_t* w, uint64_t n, u
                                   uint64_t m, float* dst, const float* norm_w, float eps, const float* residual,
                                   int* error_flag, cudaStream_t s) {
     if (!gemv_mma_fusable(m, k)) return cudaErrorInvalidValue;
+    if (m == 1 && gemv_dp4a_supports(type, w, n, k, 1))
+        return launch_gemv_dp4a(type, w, nullptr, n, k, lhs, dst, norm_w, eps, residual, 0.0f, error_flag, s);
     GemvArgs ga = {};
     ga.w[0] = ga.w[1] = w;
     ga.n = n;
@@ -1437,6 +1392,8 @@ cudaError_t launch_gemv_mma_fused(uint32_t type, const uint8_t* w, uint64_t n, u
 
 cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
                             float* dst, void* scratch, int* error_flag, cudaStream_t s) {
+    if (m == 1 && gemv_dp4a_supports(type, w, n, k, 1))
+        return launch_gemv_dp4a(type, w, nullptr, n, k, lhs, dst, nullptr, 0.0f, nullptr, 0.0f, error_flag, s);
     GemvArgs ga = {};
     ga.w[0] = ga.w[1] = w;
     ga.n = n;
@@ -1459,6 +1416,8 @@ cudaError_t launch_gemv_mma_swiglu(uint32_t type, const uint8_t* w_gate, const u
                                    const float* lhs, uint64_t m, float* dst, float clamp, int* error_flag,
                                    cudaStream_t s, const float* norm_w, float eps) {
     if (!acts_fit_in_smem(m, k)) return cudaErrorInvalidValue;
+    if (m == 1 && gemv_dp4a_supports(type, w_gate, n, k, 1) && gemv_dp4a_supports(type, w_up, n, k, 1))
+        return launch_gemv_dp4a(type, w_gate, w_up, n, k, lhs, dst, norm_w, eps, nullptr, clamp, error_flag, s);
     GemvArgs ga = {};
     ga.w[0] = w_gate;
     ga.w[1] = w_up;
@@ -1599,6 +1558,10 @@ bool narrow_k(uint32_t type, uint64_t k) {
 }  // namespace
 
 cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s) {
+    // one-row jobs whose activation rows fit shared memory: the single-row kernel
+    if (g.rows_per_job == 1 && g.planes == nullptr && gemv_dp4a_supports(g.type, g.w0, g.n, g.k, g.x_rows) &&
+        (g.w1 == nullptr || gemv_dp4a_supports(g.type, g.w1, g.n, g.k, g.x_rows)))
+        return launch_gemv_dp4a_grouped(g, s);
     GemvArgs ga = {};
     ga.w[0] = g.w0;
     ga.w[1] = g.w1 ? g.w1 : g.w0;

@@ -130,7 +130,7 @@ class LlamaDecoder:
         winning ties, the id pushed into the window, the position advanced."""
         L, c, B, P = _lib.lib(), self.cfg, self.batch, lambda t: t.data_ptr()
         if self.repetition_penalty == 1.0:
-            self._sample(s)
+            check(L.jq_argmax_dev(P(self.logits), B, c.vocab, P(self.token), P(self.pos), P(self.argmax_scratch), s))
         else:
             check(L.jq_sample_greedy_dev(P(self.logits), B, c.vocab, self.repetition_penalty, P(self.window),
                                          P(self.window_state), P(self.token), P(self.pos), P(self.argmax_scratch), s))

@@ -55,14 +55,15 @@ def test_two_calls_in_a_row_match_the_allocating_entry(type_id, mkn):
 
 
 def test_a_call_leaves_free_device_memory_unchanged():
-    """After the set-up call, further calls - also with a shape that was never seen before, and one whose planes
-    would fit shared memory - neither take nor return device memory."""
+    """Once every kernel variant involved has run once (the first launch of a kernel may make the driver load its
+    code), calls - including one whose planes would fit shared memory - neither take nor return device memory."""
     import torch
 
     shapes = [(synth.Q4_K, (8, 14336, 256)), (synth.Q4_K, (1, 1024, 512)), (synth.Q8_0, (4, 8192, 128))]
     qs = [(QTensor.from_bytes(t, synth.random_weight(t, mkn[2], mkn[1], seed=3)), mkn) for t, mkn in shapes]
     bufs = [(torch.randn(m, k, device="cuda"), torch.empty(m, n, device="cuda")) for _, (m, k, n) in qs]
-    noalloc(qs[0][0], qs[0][1], *bufs[0])     # the first call on the device: symbol address, kernel attributes
+    for (q, mkn), (x, y) in zip(qs, bufs):    # first calls: symbol address, kernel attributes, code loading
+        noalloc(q, mkn, x, y)
     torch.cuda.synchronize()
     free_before, _ = torch.cuda.mem_get_info()
     for (q, mkn), (x, y) in zip(qs, bufs):
