@@ -24,6 +24,15 @@ const char* jq_type_name(uint32_t t) {
         case jq::T_Q4_K: return "q4_k";
         case jq::T_IQ2_XXS: return "iq2_xxs";
         case jq::T_MXFP4: return "mxfp4";
+        case jq::T_Q4_0: return "q4_0";
+        case jq::T_Q4_1: return "q4_1";
+        case jq::T_Q5_0: return "q5_0";
+        case jq::T_Q5_1: return "q5_1";
+        case jq::T_Q8_1: return "q8_1";
+        case jq::T_Q3_K: return "q3_k";
+        case jq::T_Q5_K: return "q5_k";
+        case jq::T_Q6_K: return "q6_k";
+        case jq::T_Q8_K: return "q8_k";
         default: return "?";
     }
 }

@@ -146,14 +146,6 @@ struct GroupedLaunch {
 };
 cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s);
 
-// gemv_dp4a.cu: the single-row decode path (batch 1 and one-row expert jobs) for Q4_K and Q8_0.  `w_up` makes the
-// launch a SwiGLU pair; norm_w / residual as in launch_gemv_mma_fused.
-bool gemv_dp4a_supports(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, uint32_t x_rows);
-cudaError_t launch_gemv_dp4a(uint32_t type, const uint8_t* w, const uint8_t* w_up, uint64_t n, uint64_t k,
-                             const float* x, float* dst, const float* norm_w, float eps, const float* residual,
-                             float clamp, int* error_flag, cudaStream_t s);
-cudaError_t launch_gemv_dp4a_grouped(const GroupedLaunch& g, cudaStream_t s);
-
 // moe.cu: routing on the device
 enum : int32_t { MOE_GATE_SOFTMAX = 0, MOE_GATE_SIGMOID = 1, MOE_GATE_SQRT_SOFTPLUS = 2 };
 struct MoeRouteParams {

@@ -68,11 +68,10 @@ cudaError_t launch_dequant(uint32_t type, const uint8_t* w, uint64_t n_blocks, f
     uint64_t n_units = n_blocks * (f.elems / 8);
     unsigned g = grid_for(n_units);
     switch (type) {
-        case T_Q8_0: dequant_kernel<T_Q8_0, 32, 34><<<g, 256, 0, s>>>(w, n_units, out, two_step); break;
-        case T_Q2_K: dequant_kernel<T_Q2_K, 256, 84><<<g, 256, 0, s>>>(w, n_units, out, two_step); break;
-        case T_Q4_K: dequant_kernel<T_Q4_K, 256, 144><<<g, 256, 0, s>>>(w, n_units, out, two_step); break;
-        case T_IQ2_XXS: dequant_kernel<T_IQ2_XXS, 256, 66><<<g, 256, 0, s>>>(w, n_units, out, two_step); break;
-        case T_MXFP4: dequant_kernel<T_MXFP4, 32, 17><<<g, 256, 0, s>>>(w, n_units, out, two_step); break;
+#define JQ_DEQ(T, E, B) \
+    case T: dequant_kernel<T, E, B><<<g, 256, 0, s>>>(w, n_units, out, two_step); break;
+        JQ_FOR_EACH_TYPE(JQ_DEQ)
+#undef JQ_DEQ
     }
     return cudaGetLastError();
 }
@@ -83,14 +82,9 @@ cudaError_t launch_embedding(uint32_t type, const uint8_t* w, uint64_t rows, uin
     if (!format_of(type, &f)) return cudaErrorInvalidValue;
     if (n_ids == 0) return cudaSuccess;
     unsigned g = grid_for(n_ids * (hidden / 8));
-#define JQ_EMB(T, E, B) embedding_kernel<T, E, B><<<g, 256, 0, s>>>(w, rows, hidden, ids, n_ids, out, bad_id)
-    switch (type) {
-        case T_Q8_0: JQ_EMB(T_Q8_0, 32, 34); break;
-        case T_Q2_K: JQ_EMB(T_Q2_K, 256, 84); break;
-        case T_Q4_K: JQ_EMB(T_Q4_K, 256, 144); break;
-        case T_IQ2_XXS: JQ_EMB(T_IQ2_XXS, 256, 66); break;
-        case T_MXFP4: JQ_EMB(T_MXFP4, 32, 17); break;
-    }
+#define JQ_EMB(T, E, B) \
+    case T: embedding_kernel<T, E, B><<<g, 256, 0, s>>>(w, rows, hidden, ids, n_ids, out, bad_id); break;
+    switch (type) { JQ_FOR_EACH_TYPE(JQ_EMB) }
 #undef JQ_EMB
     return cudaGetLastError();
 }

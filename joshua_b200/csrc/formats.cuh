@@ -20,7 +20,18 @@
 
 namespace jq {
 
-enum : uint32_t { T_Q8_0 = 8, T_Q2_K = 10, T_Q4_K = 12, T_IQ2_XXS = 16, T_MXFP4 = 39 };
+enum : uint32_t {
+    T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q8_1 = 9, T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12,
+    T_Q5_K = 13, T_Q6_K = 14, T_Q8_K = 15, T_IQ2_XXS = 16, T_MXFP4 = 39
+};
+
+// Every block type with a decoder here: X(type id, elements per block, bytes per block).  The first five are
+// the types of the fused decode kernels; the rest take the exact-decode float path only, as in the reference
+// (its generic path dequantises a row and dots it, src/quant_matmul.rs:228-249; block sizes src/gguf_ext.rs:483-512).
+#define JQ_FOR_EACH_TYPE(X)                                                                                      \
+    X(T_Q8_0, 32, 34) X(T_Q2_K, 256, 84) X(T_Q4_K, 256, 144) X(T_IQ2_XXS, 256, 66) X(T_MXFP4, 32, 17)            \
+    X(T_Q4_0, 32, 18) X(T_Q4_1, 32, 20) X(T_Q5_0, 32, 22) X(T_Q5_1, 32, 24) X(T_Q8_1, 32, 36) X(T_Q3_K, 256, 110) \
+    X(T_Q5_K, 256, 176) X(T_Q6_K, 256, 210) X(T_Q8_K, 256, 292)
 
 struct Format {
     uint32_t elems;  // weights per block
@@ -34,6 +45,15 @@ __host__ __device__ inline bool format_of(uint32_t type, Format* f) {
         case T_Q4_K: *f = {256, 144}; return true;
         case T_IQ2_XXS: *f = {256, 66}; return true;
         case T_MXFP4: *f = {32, 17}; return true;
+        case T_Q4_0: *f = {32, 18}; return true;
+        case T_Q4_1: *f = {32, 20}; return true;
+        case T_Q5_0: *f = {32, 22}; return true;
+        case T_Q5_1: *f = {32, 24}; return true;
+        case T_Q8_1: *f = {32, 36}; return true;
+        case T_Q3_K: *f = {256, 110}; return true;
+        case T_Q5_K: *f = {256, 176}; return true;
+        case T_Q6_K: *f = {256, 210}; return true;
+        case T_Q8_K: *f = {256, 292}; return true;
         default: return false;
     }
 }
@@ -185,6 +205,131 @@ __device__ __forceinline__ void decode_unit<T_MXFP4>(const uint8_t* row, uint32_
     for (int i = 0; i < 8; ++i) {
         uint32_t code = (ld_u8(q + i) >> shift) & 15u;
         w[i] = e == 0xFFu ? 0.0f : __fmul_rn(scale, e2m1_value(code));
+    }
+}
+
+// ── the other GGUF block types (exact path only) ──
+// The reference decodes these with candle's `k_quants::*::to_float`, a port of ggml's `dequantize_row_*`; the
+// layouts and the order of the float operations below are the published ggml ones.  All loads are single bytes:
+// these blocks have no alignment beyond two.  `two_step` does not apply (one form each).
+__device__ __forceinline__ float ld_f16(const uint8_t* p) { return f16_bits_to_f32(ld_u8(p) | (ld_u8(p + 1) << 8)); }
+
+// 32-value blocks with split halves: value j < 16 is the low nibble of byte j, value j + 16 the high nibble.
+template <>
+__device__ __forceinline__ void decode_unit<T_Q4_0>(const uint8_t* row, uint32_t u, float w[8], bool) {
+    const uint8_t* blk = row + (size_t)(u >> 2) * 18;
+    const float d = ld_f16(blk);
+    const uint32_t part = u & 3, shift = 4 * (part >> 1);
+    const uint8_t* q = blk + 2 + 8 * (part & 1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = __fmul_rn((float)((int)((ld_u8(q + i) >> shift) & 15u) - 8), d);
+}
+
+template <>
+__device__ __forceinline__ void decode_unit<T_Q4_1>(const uint8_t* row, uint32_t u, float w[8], bool) {
+    const uint8_t* blk = row + (size_t)(u >> 2) * 20;
+    const float d = ld_f16(blk), m = ld_f16(blk + 2);
+    const uint32_t part = u & 3, shift = 4 * (part >> 1);
+    const uint8_t* q = blk + 4 + 8 * (part & 1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = __fadd_rn(__fmul_rn((float)((ld_u8(q + i) >> shift) & 15u), d), m);
+}
+
+// fifth bit of value v of a Q5_0 / Q5_1 block from the 32-bit mask qh: bit v
+__device__ __forceinline__ uint32_t q5_code(const uint8_t* qs, uint32_t qh, uint32_t v) {
+    const uint32_t nib = v < 16 ? (ld_u8(qs + v) & 15u) : (ld_u8(qs + v - 16) >> 4);
+    return nib | (((qh >> v) & 1u) << 4);
+}
+
+template <>
+__device__ __forceinline__ void decode_unit<T_Q5_0>(const uint8_t* row, uint32_t u, float w[8], bool) {
+    const uint8_t* blk = row + (size_t)(u >> 2) * 22;
+    const float d = ld_f16(blk);
+    const uint32_t qh = ld_u8(blk + 2) | (ld_u8(blk + 3) << 8) | (ld_u8(blk + 4) << 16) | (ld_u8(blk + 5) << 24);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = __fmul_rn((float)((int)q5_code(blk + 6, qh, 8 * (u & 3) + i) - 16), d);
+}
+
+template <>
+__device__ __forceinline__ void decode_unit<T_Q5_1>(const uint8_t* row, uint32_t u, float w[8], bool) {
+    const uint8_t* blk = row + (size_t)(u >> 2) * 24;
+    const float d = ld_f16(blk), m = ld_f16(blk + 2);
+    const uint32_t qh = ld_u8(blk + 4) | (ld_u8(blk + 5) << 8) | (ld_u8(blk + 6) << 16) | (ld_u8(blk + 7) << 24);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = __fadd_rn(__fmul_rn((float)q5_code(blk + 8, qh, 8 * (u & 3) + i), d), m);
+}
+
+template <>
+__device__ __forceinline__ void decode_unit<T_Q8_1>(const uint8_t* row, uint32_t u, float w[8], bool) {
+    const uint8_t* blk = row + (size_t)(u >> 2) * 36;  // f16 d, f16 s (unused by the decode), 32 int8
+    const float d = ld_f16(blk);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = __fmul_rn((float)(int8_t)ld_u8(blk + 4 + 8 * (u & 3) + i), d);
+}
+
+template <>
+__device__ __forceinline__ void decode_unit<T_Q8_K>(const uint8_t* row, uint32_t u, float w[8], bool) {
+    const uint8_t* blk = row + (size_t)(u >> 5) * 292;  // f32 d, 256 int8, 16 int16 block sums (unused)
+    const float d = __uint_as_float(ld_u8(blk) | (ld_u8(blk + 1) << 8) | (ld_u8(blk + 2) << 16) | (ld_u8(blk + 3) << 24));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = __fmul_rn(d, (float)(int8_t)ld_u8(blk + 4 + 8 * (u & 31) + i));
+}
+
+// Q3_K: hmask[32] | qs[64] | scales[12] | f16 d.  Value v: half = v / 128, j = (v % 128) / 32, l = v % 32; low two
+// bits (qs[32 half + l] >> 2j) & 3, minus 4 unless bit (4 half + j) of hmask[l] is set; scale index v / 16.
+__device__ __forceinline__ int q3k_scale(const uint8_t* s, uint32_t i) {  // six-bit scale i of 16, minus 32
+    // low four bits: nibble (i / 8) of byte i % 8; high two bits: bit pair (i / 4) of byte 8 + i % 4
+    const uint32_t lo = (ld_u8(s + (i & 7)) >> (4 * (i >> 3))) & 15u;
+    const uint32_t hi = (ld_u8(s + 8 + (i & 3)) >> (2 * (i >> 2))) & 3u;
+    return (int)(lo | (hi << 4)) - 32;
+}
+
+template <>
+__device__ __forceinline__ void decode_unit<T_Q3_K>(const uint8_t* row, uint32_t u, float w[8], bool) {
+    const uint8_t* blk = row + (size_t)(u >> 5) * 110;
+    const uint32_t v0 = (u & 31) * 8, half = v0 >> 7, j = (v0 & 127) >> 5, l0 = v0 & 31;
+    const float dl = __fmul_rn(ld_f16(blk + 108), (float)q3k_scale(blk + 96, v0 >> 4));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int two = (int)((ld_u8(blk + 32 + 32 * half + l0 + i) >> (2 * j)) & 3u);
+        const int q = two - (((ld_u8(blk + l0 + i) >> (4 * half + j)) & 1u) ? 0 : 4);
+        w[i] = __fmul_rn(dl, (float)q);
+    }
+}
+
+// Q5_K: f16 d | f16 dmin | scales[12] | qh[32] | qs[128].  As Q4_K with a fifth bit: group g (32 values) takes
+// bit g of qh[l].
+template <>
+__device__ __forceinline__ void decode_unit<T_Q5_K>(const uint8_t* row, uint32_t u, float w[8], bool) {
+    const uint8_t* blk = row + (size_t)(u >> 5) * 176;
+    const uint32_t pair = (u & 31) >> 2, l0 = 8 * (u & 3);
+    uint32_t sc, mn;
+    q4k_scale_min(blk + 4, pair, &sc, &mn);
+    const float d1 = __fmul_rn(ld_f16(blk), (float)sc), m1 = __fmul_rn(ld_f16(blk + 2), (float)mn);
+    const uint8_t* q = blk + 48 + 32 * (pair >> 1) + l0;
+    const uint32_t shift = 4 * (pair & 1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t code = ((ld_u8(q + i) >> shift) & 15u) + (((ld_u8(blk + 16 + l0 + i) >> pair) & 1u) << 4);
+        w[i] = __fsub_rn(__fmul_rn(d1, (float)code), m1);
+    }
+}
+
+// Q6_K: ql[128] | qh[64] | int8 scales[16] | f16 d.  Value v: half = v / 128, part = (v % 128) / 32, l = v % 32;
+// low nibble from ql[64 half + 32 (part & 1) + l] (low for part < 2, high otherwise), two high bits
+// (qh[32 half + l] >> 2 part) & 3, minus 32; scale index v / 16.
+template <>
+__device__ __forceinline__ void decode_unit<T_Q6_K>(const uint8_t* row, uint32_t u, float w[8], bool) {
+    const uint8_t* blk = row + (size_t)(u >> 5) * 210;
+    const uint32_t v0 = (u & 31) * 8, half = v0 >> 7, part = (v0 & 127) >> 5, l0 = v0 & 31;
+    const float ds = __fmul_rn(ld_f16(blk + 208), (float)(int8_t)ld_u8(blk + 192 + (v0 >> 4)));
+    const uint8_t* ql = blk + 64 * half + 32 * (part & 1) + l0;
+    const uint8_t* qh = blk + 128 + 32 * half + l0;
+    const uint32_t nshift = 4 * (part >> 1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t code = ((ld_u8(ql + i) >> nshift) & 15u) | (((ld_u8(qh + i) >> (2 * part)) & 3u) << 4);
+        w[i] = __fmul_rn(ds, (float)((int)code - 32));
     }
 }
 

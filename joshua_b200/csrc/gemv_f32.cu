@@ -75,11 +75,10 @@ cudaError_t launch_matmul_f32(uint32_t type, const uint8_t* w, uint64_t n, uint6
     unsigned g = (unsigned)((n + WARPS_PER_CTA - 1) / WARPS_PER_CTA);
     dim3 b(WARPS_PER_CTA * 32);
     switch (type) {
-        case T_Q8_0: matmul_f32_kernel<T_Q8_0, 32, 34><<<g, b, 0, s>>>(w, n, k, lhs, m, dst); break;
-        case T_Q2_K: matmul_f32_kernel<T_Q2_K, 256, 84><<<g, b, 0, s>>>(w, n, k, lhs, m, dst); break;
-        case T_Q4_K: matmul_f32_kernel<T_Q4_K, 256, 144><<<g, b, 0, s>>>(w, n, k, lhs, m, dst); break;
-        case T_IQ2_XXS: matmul_f32_kernel<T_IQ2_XXS, 256, 66><<<g, b, 0, s>>>(w, n, k, lhs, m, dst); break;
-        case T_MXFP4: matmul_f32_kernel<T_MXFP4, 32, 17><<<g, b, 0, s>>>(w, n, k, lhs, m, dst); break;
+#define JQ_MM(T, E, B) \
+    case T: matmul_f32_kernel<T, E, B><<<g, b, 0, s>>>(w, n, k, lhs, m, dst); break;
+        JQ_FOR_EACH_TYPE(JQ_MM)
+#undef JQ_MM
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

@@ -1373,8 +1373,6 @@ cudaError_t launch_gemv_mma_fused(uint32_t type, const uint8_t* w, uint64_t n, u
                                   uint64_t m, float* dst, const float* norm_w, float eps, const float* residual,
                                   int* error_flag, cudaStream_t s) {
     if (!gemv_mma_fusable(m, k)) return cudaErrorInvalidValue;
-    if (m == 1 && gemv_dp4a_supports(type, w, n, k, 1))
-        return launch_gemv_dp4a(type, w, nullptr, n, k, lhs, dst, norm_w, eps, residual, 0.0f, error_flag, s);
     GemvArgs ga = {};
     ga.w[0] = ga.w[1] = w;
     ga.n = n;
@@ -1392,8 +1390,6 @@ cudaError_t launch_gemv_mma_fused(uint32_t type, const uint8_t* w, uint64_t n, u
 
 cudaError_t launch_gemv_mma(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
                             float* dst, void* scratch, int* error_flag, cudaStream_t s) {
-    if (m == 1 && gemv_dp4a_supports(type, w, n, k, 1))
-        return launch_gemv_dp4a(type, w, nullptr, n, k, lhs, dst, nullptr, 0.0f, nullptr, 0.0f, error_flag, s);
     GemvArgs ga = {};
     ga.w[0] = ga.w[1] = w;
     ga.n = n;
@@ -1416,8 +1412,6 @@ cudaError_t launch_gemv_mma_swiglu(uint32_t type, const uint8_t* w_gate, const u
                                    const float* lhs, uint64_t m, float* dst, float clamp, int* error_flag,
                                    cudaStream_t s, const float* norm_w, float eps) {
     if (!acts_fit_in_smem(m, k)) return cudaErrorInvalidValue;
-    if (m == 1 && gemv_dp4a_supports(type, w_gate, n, k, 1) && gemv_dp4a_supports(type, w_up, n, k, 1))
-        return launch_gemv_dp4a(type, w_gate, w_up, n, k, lhs, dst, norm_w, eps, nullptr, clamp, error_flag, s);
     GemvArgs ga = {};
     ga.w[0] = w_gate;
     ga.w[1] = w_up;
@@ -1558,10 +1552,6 @@ bool narrow_k(uint32_t type, uint64_t k) {
 }  // namespace
 
 cudaError_t launch_gemv_grouped(const GroupedLaunch& g, cudaStream_t s) {
-    // one-row jobs whose activation rows fit shared memory: the single-row kernel
-    if (g.rows_per_job == 1 && g.planes == nullptr && gemv_dp4a_supports(g.type, g.w0, g.n, g.k, g.x_rows) &&
-        (g.w1 == nullptr || gemv_dp4a_supports(g.type, g.w1, g.n, g.k, g.x_rows)))
-        return launch_gemv_dp4a_grouped(g, s);
     GemvArgs ga = {};
     ga.w[0] = g.w0;
     ga.w[1] = g.w1 ? g.w1 : g.w0;

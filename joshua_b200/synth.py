@@ -15,13 +15,20 @@ from __future__ import annotations
 import numpy as np
 
 Q8_0, Q2_K, Q4_K, IQ2_XXS, MXFP4 = 8, 10, 12, 16, 39
+# the block types of the reference's generic (decode a row, then dot) path
+Q4_0, Q4_1, Q5_0, Q5_1, Q8_1, Q3_K, Q5_K, Q6_K, Q8_K = 2, 3, 6, 7, 9, 11, 13, 14, 15
+GENERIC_TYPES = (Q4_0, Q4_1, Q5_0, Q5_1, Q8_1, Q3_K, Q5_K, Q6_K, Q8_K)
 
 # type id -> (elements per block, bytes per block)
-BLOCK = {Q8_0: (32, 34), Q2_K: (256, 84), Q4_K: (256, 144), IQ2_XXS: (256, 66), MXFP4: (32, 17)}
-NAMES = {Q8_0: "q8_0", Q2_K: "q2_k", Q4_K: "q4_k", IQ2_XXS: "iq2_xxs", MXFP4: "mxfp4"}
+BLOCK = {Q8_0: (32, 34), Q2_K: (256, 84), Q4_K: (256, 144), IQ2_XXS: (256, 66), MXFP4: (32, 17),
+         Q4_0: (32, 18), Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q8_1: (32, 36), Q3_K: (256, 110),
+         Q5_K: (256, 176), Q6_K: (256, 210), Q8_K: (256, 292)}
+NAMES = {Q8_0: "q8_0", Q2_K: "q2_k", Q4_K: "q4_k", IQ2_XXS: "iq2_xxs", MXFP4: "mxfp4", Q4_0: "q4_0", Q4_1: "q4_1",
+         Q5_0: "q5_0", Q5_1: "q5_1", Q8_1: "q8_1", Q3_K: "q3_k", Q5_K: "q5_k", Q6_K: "q6_k", Q8_K: "q8_k"}
 
-# byte offsets of the fp16 scale fields inside a block
-_F16_FIELDS = {Q8_0: (0,), Q2_K: (80, 82), Q4_K: (0, 2), IQ2_XXS: (0,), MXFP4: ()}
+# byte offsets of the fp16 scale fields inside a block (Q8_K carries one f32 scale at offset 0 instead)
+_F16_FIELDS = {Q8_0: (0,), Q2_K: (80, 82), Q4_K: (0, 2), IQ2_XXS: (0,), MXFP4: (), Q4_0: (0,), Q4_1: (0, 2),
+               Q5_0: (0,), Q5_1: (0, 2), Q8_1: (0, 2), Q3_K: (108,), Q5_K: (0, 2), Q6_K: (208,), Q8_K: ()}
 _SCALE_LO, _SCALE_HI = 1e-3, 1e-2
 _E8M0_LO, _E8M0_HI = 118, 130  # inclusive
 
@@ -46,6 +53,9 @@ def random_blocks(type_id: int, n_blocks: int, rng: np.random.Generator) -> np.n
         q[q == -128] = -127
     if type_id == MXFP4:
         raw[:, 0] = rng.integers(_E8M0_LO, _E8M0_HI + 1, size=n_blocks, dtype=np.uint8)
+    if type_id == Q8_K:
+        scale = rng.uniform(_SCALE_LO, _SCALE_HI, size=n_blocks).astype(np.float32)
+        raw[:, 0:4] = scale.view(np.uint8).reshape(n_blocks, 4)
     return raw
 
 

@@ -74,7 +74,10 @@ int fail(const std::string& msg) {
 
 // ───────────────────────────── formats ────────────────────────────────────
 
-enum : int { T_Q8_0 = 8, T_Q2_K = 10, T_Q4_K = 12, T_IQ2_XXS = 16, T_MXFP4 = 39 };
+enum : int {
+    T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q8_1 = 9, T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12,
+    T_Q5_K = 13, T_Q6_K = 14, T_Q8_K = 15, T_IQ2_XXS = 16, T_MXFP4 = 39
+};
 
 struct Fmt {
     size_t elems;
@@ -89,6 +92,16 @@ bool fmt_of(int type, Fmt* f) {
         case T_Q4_K: *f = {256, 144, "q4_k"}; return true;
         case T_IQ2_XXS: *f = {256, 66, "iq2_xxs"}; return true;
         case T_MXFP4: *f = {32, 17, "mxfp4"}; return true;
+        // the types of the reference's generic path (src/quant_matmul.rs:86-100; sizes src/gguf_ext.rs:483-512)
+        case T_Q4_0: *f = {32, 18, "q4_0"}; return true;
+        case T_Q4_1: *f = {32, 20, "q4_1"}; return true;
+        case T_Q5_0: *f = {32, 22, "q5_0"}; return true;
+        case T_Q5_1: *f = {32, 24, "q5_1"}; return true;
+        case T_Q8_1: *f = {32, 36, "q8_1"}; return true;
+        case T_Q3_K: *f = {256, 110, "q3_k"}; return true;
+        case T_Q5_K: *f = {256, 176, "q5_k"}; return true;
+        case T_Q6_K: *f = {256, 210, "q6_k"}; return true;
+        case T_Q8_K: *f = {256, 292, "q8_k"}; return true;
         default: return false;
     }
 }
@@ -267,8 +280,133 @@ void decode_mxfp4(const uint8_t* b, float* out) {
     }
 }
 
+// ── the generic path's types ──
+// The reference takes these decoders from candle's `k_quants::*::to_float` (not in its tree), which port ggml's
+// `dequantize_row_*`; the loops below restate the published ggml layouts and operation order.  "Parity
+// unpinned": the reference holds no vectors for them.
+void decode_q4_0(const uint8_t* b, float* out) {
+    float d = f16_to_f32(b);
+    for (int j = 0; j < 16; ++j) {
+        out[j] = (float)((int)(b[2 + j] & 0x0F) - 8) * d;
+        out[j + 16] = (float)((int)(b[2 + j] >> 4) - 8) * d;
+    }
+}
+void decode_q4_1(const uint8_t* b, float* out) {
+    float d = f16_to_f32(b), m = f16_to_f32(b + 2);
+    for (int j = 0; j < 16; ++j) {
+        out[j] = (float)(b[4 + j] & 0x0F) * d + m;
+        out[j + 16] = (float)(b[4 + j] >> 4) * d + m;
+    }
+}
+void decode_q5(const uint8_t* qhp, const uint8_t* qs, float d, float m, int bias, float* out) {
+    uint32_t qh;
+    std::memcpy(&qh, qhp, 4);
+    for (int j = 0; j < 16; ++j) {
+        uint32_t xh0 = ((qh >> j) << 4) & 0x10, xh1 = (qh >> (j + 12)) & 0x10;
+        out[j] = (float)((int)((qs[j] & 0x0F) | xh0) - bias) * d + m;
+        out[j + 16] = (float)((int)((qs[j] >> 4) | xh1) - bias) * d + m;
+    }
+}
+void decode_q8_1(const uint8_t* b, float* out) {
+    float d = f16_to_f32(b);
+    for (int j = 0; j < 32; ++j) out[j] = (float)(int8_t)b[4 + j] * d;
+}
+void decode_q8k(const uint8_t* b, float* out) {
+    float d;
+    std::memcpy(&d, b, 4);
+    for (int j = 0; j < 256; ++j) out[j] = d * (float)(int8_t)b[4 + j];
+}
+void decode_q3k(const uint8_t* b, float* out) {
+    const uint8_t *hm = b, *q = b + 32;
+    float d_all = f16_to_f32(b + 108);
+    uint32_t aux[4];
+    std::memcpy(aux, b + 96, 12);
+    const uint32_t kmask1 = 0x03030303u, kmask2 = 0x0f0f0f0fu;
+    uint32_t tmp = aux[2];
+    aux[2] = ((aux[0] >> 4) & kmask2) | (((tmp >> 4) & kmask1) << 4);
+    aux[3] = ((aux[1] >> 4) & kmask2) | (((tmp >> 6) & kmask1) << 4);
+    aux[0] = (aux[0] & kmask2) | (((tmp >> 0) & kmask1) << 4);
+    aux[1] = (aux[1] & kmask2) | (((tmp >> 2) & kmask1) << 4);
+    int8_t scales[16];
+    std::memcpy(scales, aux, 16);
+    int is = 0;
+    uint8_t m = 1;
+    for (int n = 0; n < 256; n += 128) {
+        int shift = 0;
+        for (int j = 0; j < 4; ++j) {
+            float dl = d_all * (float)(scales[is++] - 32);
+            for (int l = 0; l < 16; ++l)
+                *out++ = dl * (float)((int)((q[l] >> shift) & 3) - ((hm[l] & m) ? 0 : 4));
+            dl = d_all * (float)(scales[is++] - 32);
+            for (int l = 0; l < 16; ++l)
+                *out++ = dl * (float)((int)((q[l + 16] >> shift) & 3) - ((hm[l + 16] & m) ? 0 : 4));
+            shift += 2;
+            m <<= 1;
+        }
+        q += 32;
+    }
+}
+void decode_q5k(const uint8_t* b, float* out) {
+    float d = f16_to_f32(b), dmin = f16_to_f32(b + 2);
+    const uint8_t *qh = b + 16, *ql = b + 48;
+    int is = 0;
+    uint8_t u1 = 1, u2 = 2;
+    for (int j = 0; j < 256; j += 64) {
+        uint8_t sc, mn;
+        q4k_scale_min(b + 4, is + 0, &sc, &mn);
+        float d1 = d * (float)sc, m1 = dmin * (float)mn;
+        q4k_scale_min(b + 4, is + 1, &sc, &mn);
+        float d2 = d * (float)sc, m2 = dmin * (float)mn;
+        for (int l = 0; l < 32; ++l) *out++ = d1 * (float)((ql[l] & 0xF) + ((qh[l] & u1) ? 16 : 0)) - m1;
+        for (int l = 0; l < 32; ++l) *out++ = d2 * (float)((ql[l] >> 4) + ((qh[l] & u2) ? 16 : 0)) - m2;
+        ql += 32;
+        is += 2;
+        u1 <<= 2;
+        u2 <<= 2;
+    }
+}
+void decode_q6k(const uint8_t* b, float* out) {
+    const uint8_t *ql = b, *qh = b + 128;
+    const int8_t* sc = reinterpret_cast<const int8_t*>(b + 192);
+    float d = f16_to_f32(b + 208);
+    for (int n = 0; n < 256; n += 128) {
+        for (int l = 0; l < 32; ++l) {
+            int is = l / 16;
+            int q1 = (int)((ql[l] & 0xF) | (((qh[l] >> 0) & 3) << 4)) - 32;
+            int q2 = (int)((ql[l + 32] & 0xF) | (((qh[l] >> 2) & 3) << 4)) - 32;
+            int q3 = (int)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32;
+            int q4 = (int)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32;
+            out[l] = d * (float)sc[is + 0] * (float)q1;
+            out[l + 32] = d * (float)sc[is + 2] * (float)q2;
+            out[l + 64] = d * (float)sc[is + 4] * (float)q3;
+            out[l + 96] = d * (float)sc[is + 6] * (float)q4;
+        }
+        out += 128;
+        ql += 64;
+        qh += 32;
+        sc += 8;
+    }
+}
+
+inline bool is_generic_type(int type) {
+    switch (type) {
+        case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_Q8_1: case T_Q3_K: case T_Q5_K: case T_Q6_K:
+        case T_Q8_K: return true;
+        default: return false;
+    }
+}
+
 void decode_block(int type, const uint8_t* b, float* out, bool two_step) {
     switch (type) {
+        case T_Q4_0: decode_q4_0(b, out); break;
+        case T_Q4_1: decode_q4_1(b, out); break;
+        case T_Q5_0: decode_q5(b + 2, b + 6, f16_to_f32(b), 0.0f, 16, out); break;
+        case T_Q5_1: decode_q5(b + 4, b + 8, f16_to_f32(b), f16_to_f32(b + 2), 0, out); break;
+        case T_Q8_1: decode_q8_1(b, out); break;
+        case T_Q3_K: decode_q3k(b, out); break;
+        case T_Q5_K: decode_q5k(b, out); break;
+        case T_Q6_K: decode_q6k(b, out); break;
+        case T_Q8_K: decode_q8k(b, out); break;
         case T_Q8_0: decode_q8_0(b, out); break;
         case T_Q2_K: decode_q2k(b, out, two_step); break;
         case T_Q4_K: decode_q4k(b, out, two_step); break;
@@ -556,6 +694,20 @@ void row_iq2xxs_avx2(size_t m, size_t k, size_t n, const float* lhs, const uint8
     }
 }
 
+// The generic path (src/quant_matmul.rs:228-249,292-325): the weight row is decoded to f32 once, then dotted
+// with every activation row, one FMA per 8 columns in 8 lanes, `hsum256` at the end.
+void row_generic(int type, const Fmt& f, size_t m, size_t k, size_t n, const float* lhs, const uint8_t* row_blocks,
+                 size_t bpr, size_t row, float* dst) {
+    std::vector<float> wrow(k);
+    for (size_t b = 0; b < bpr; ++b) decode_block(type, row_blocks + b * f.bytes, wrow.data() + b * f.elems, true);
+    for (size_t i = 0; i < m; ++i) {
+        __m256 acc = _mm256_setzero_ps();
+        for (size_t c = 0; c + 8 <= k; c += 8)
+            acc = _mm256_fmadd_ps(_mm256_loadu_ps(lhs + i * k + c), _mm256_loadu_ps(wrow.data() + c), acc);
+        dst[i * n + row] = hsum256(acc);
+    }
+}
+
 // Scalar block-at-a-time row (src/iq2xxs.rs:241-268, src/mxfp4.rs:208-235):
 // per block acc = 0; acc += x*w (separately rounded) over the block in order;
 // dst += acc.  dst must have been zero-filled.
@@ -614,6 +766,10 @@ int matmul_t(int type, size_t m, size_t k, size_t n, const float* lhs, size_t lh
         const uint8_t* rb = w + row * row_bytes;
         if (scalar) {
             row_scalar_blocks(type, f, m, k, n, lhs, rb, bpr, row, dst);
+            return;
+        }
+        if (is_generic_type(type)) {
+            row_generic(type, f, m, k, n, lhs, rb, bpr, row, dst);
             return;
         }
         switch (type) {

@@ -34,10 +34,13 @@ def test_python_binding_covers_every_declared_symbol():
 
 def test_block_sizes_without_a_device():
     e, b = ctypes.c_uint64(), ctypes.c_uint64()
-    for t, want in {8: (32, 34), 10: (256, 84), 12: (256, 144), 16: (256, 66), 39: (32, 17)}.items():
+    from joshua_b200 import gguf, synth
+
+    for t, want in synth.BLOCK.items():       # every block type with a decoder, sizes as src/gguf_ext.rs:483-512
         assert _lib.lib().jq_block_size(t, ctypes.byref(e), ctypes.byref(b)) == 0
-        assert (e.value, b.value) == want
-    assert _lib.lib().jq_block_size(11, ctypes.byref(e), ctypes.byref(b)) == _lib.E_TYPE
+        assert (e.value, b.value) == want == gguf.TYPE_SIZES[t]
+    for t in (0, 1, 17, 26, 30, 40):          # float / integer / unknown ids are not block types of this library
+        assert _lib.lib().jq_block_size(t, ctypes.byref(e), ctypes.byref(b)) == _lib.E_TYPE
 
 
 def test_product_fails_loudly_without_a_device():

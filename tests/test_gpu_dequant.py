@@ -24,6 +24,23 @@ def test_dequant_bit_exact(type_id, two_step):
     assert np.array_equal(bits(got), bits(want))
 
 
+@pytest.mark.parametrize("type_id", synth.GENERIC_TYPES)
+def test_generic_path_types_dequant_bit_exact(type_id):
+    """Q4_0 .. Q8_K (the reference's `decode_raw_to_f32` ids 2, 3, 6, 7, 9, 11, 13, 14, 15, src/quant_matmul.rs:86-100)
+    against the oracle's scalar decoders, including the embedding gather."""
+    elems, nbytes = synth.BLOCK[type_id]
+    raw = synth.random_blocks(type_id, 1031, np.random.default_rng(type_id)).reshape(-1)
+    q = QTensor.from_bytes(type_id, raw)
+    want = oracle.dequantize(type_id, raw)
+    assert np.array_equal(bits(q.dequantize(1031 * elems)), bits(want))
+    hidden = 2 * max(elems, 128)
+    rows = 1031 * elems // hidden
+    raw = raw[: rows * (hidden // elems) * nbytes]
+    ids = np.array([rows - 1, 0, 5, 5], dtype=np.uint32)
+    got = QTensor.from_bytes(type_id, raw).embedding(ids, rows, hidden)
+    assert np.array_equal(bits(got), bits(want[: rows * hidden].reshape(rows, hidden)[ids]))
+
+
 def test_iq2xxs_golden_vectors():
     raw = (np_decode.GOLDEN / "iq2xxs_blocks.bin").read_bytes()
     want = np.array([float(x) for x in (np_decode.GOLDEN / "iq2xxs_ref.txt").read_text().split()], dtype=np.float32)

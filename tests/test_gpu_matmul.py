@@ -41,6 +41,20 @@ def test_matmul_matches_oracle(type_id, mkn):
     assert_close(got, want, what=f"{synth.NAMES[type_id]} {mkn}")
 
 
+@pytest.mark.parametrize("type_id", synth.GENERIC_TYPES)
+@pytest.mark.parametrize("mkn", [(1, 256, 40), (3, 512, 13), (8, 1024, 64), (40, 512, 24), (1, 4096, 256)])
+def test_generic_path_types_match_oracle(type_id, mkn):
+    """The block types the reference serves by decoding a row and dotting it (src/quant_matmul.rs:228-249): here
+    the exact-decode float kernel, any batch."""
+    m, k, n = mkn
+    raw = synth.random_weight(type_id, n, k, seed=n + k)
+    lhs = synth.random_activations(m, k, seed=m)
+    q = QTensor.from_bytes(type_id, raw)
+    got = q.matmul_t(mkn, lhs)
+    assert_close(got, oracle.matmul_t(type_id, mkn, lhs, raw), what=f"{synth.NAMES[type_id]} {mkn}")
+    assert np.array_equal(bits(got), bits(q.matmul_t(mkn, lhs)))      # run-to-run bit equality
+
+
 def test_iq2xxs_golden_block_fixture():
     for mkn, mult in [((3, 512, 7), 7919), ((3, 1024, 11), 7919), ((4, 1024, 23), 104729)]:
         m, k, n = mkn
