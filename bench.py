@@ -3,13 +3,16 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 Workloads
-  llama8b  (default) decode of a Llama-8B-shaped model, every linear Q4_K, batch 1
-           (--batch up to 8): the KV cache is filled with --prefill positions, then one
-           step = one greedily decoded token, the whole step on the device
-           (4.22 GB of raw Q4_K blocks read once per token).
-  qwen3moe decode of a Qwen3-MoE-shaped model (128 experts top-8, Q4_K experts, Q8_0 attention);
-           with --gpus N > 1 (under torchrun) the experts are split over the ranks and rows
-           are exchanged by NCCL all-to-all.
+  (default) the decode step of the Qwen3-MoE-shaped model at one sequence per GPU - the configuration whose expert
+           banks shard: with --gpus N > 1 (under torchrun) the experts are split over the ranks and activation
+           rows are exchanged through peer memory over NVLink (csrc/ep.cu).  The line carries `strong` (fixed
+           global batch 16) and `load` (max / mean rows per rank); at N = 1 also `dense`, the full line of the
+           llama8b workload (the configuration the decode metric is quoted on for dense models), and `kernels`,
+           the five block formats' 4096 x 4096 single-matmul GB/s.
+  qwen3moe the MoE line alone (--batch sequences per GPU).
+  llama8b  decode of a Llama-8B-shaped model, every linear Q4_K, batch 1 (--batch up to 8): the KV cache is
+           filled with --prefill positions, then one step = one greedily decoded token, the whole step on the
+           device (4.22 GB of raw Q4_K blocks read once per token).  With --gpus N: N replicas, no collective.
   moe_layer one routed-expert layer (--type, --experts, --used, --k hidden, --n expert width, --m tokens):
            the grouped expert matmuls at a given token count.
   gemv     one quantized matmul shape, rotated over a working set larger than L2
@@ -189,36 +192,28 @@ def cpu_moe_sample(cfg, seconds_budget: float = 12.0):
 
 
 def run_reference(args):
-    """`--impl reference`: the reference's CPU kernels (C++ oracle port) on this host, all cores."""
+    """`--impl reference`: the reference's CPU kernels (C++ oracle port) on this host, all cores.  The figure is
+    extrapolated: one layer's matmuls are timed and scaled to a token by bytes (`"extrapolated": true`)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     t0 = time.perf_counter()
-    if args.workload == "qwen3moe":
+    budget = max(5.0, min(60.0, 2.0 * (args.steps + args.warmup)))
+    if args.workload in ("default", "qwen3moe"):
+        from joshua_b200.bench_moe import moe_config
         from joshua_b200.moe_decoder import MoeDecoderConfig
 
         cfg = MoeDecoderConfig()
-        base = cpu_moe_sample(cfg, seconds_budget=max(5.0, min(60.0, 2.0 * (args.steps + args.warmup))))
-        line = {
-            "impl": "reference", "metric": "decode_tok_s", "value": base["value"], "unit": "tok/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": 1e3 / base["value"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"qwen3moe_decode_b{args.batch}", "layers": cfg.layers, "hidden": cfg.hidden,
-                       "n_expert": cfg.n_expert, "n_used": cfg.n_used, "moe_inter": cfg.moe_inter},
-            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
-            "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
-        }
-        print(json.dumps(line))
-        return
-    base = cpu_llama_sample(seconds_budget=max(5.0, min(60.0, 2.0 * (args.steps + args.warmup))))
+        base = cpu_moe_sample(cfg, seconds_budget=budget)
+        config = moe_config(cfg, args.batch, args.gpus)
+    else:
+        base = cpu_llama_sample(seconds_budget=budget)
+        config = {"workload": "llama8b_q4k_decode_b1", **LLAMA}
     line = {
         "impl": "reference", "metric": "decode_tok_s", "value": base["value"], "unit": "tok/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 / base["value"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "llama8b_q4k_decode_b1", **LLAMA},
+        "dtype": "f32", "data": "synthetic", "config": config, "extrapolated": True,
         "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
@@ -249,7 +244,7 @@ def cuda_time(fn, steps, warmup, barrier=None):
     return s.elapsed_time(e) * 1e-3 / steps
 
 
-def run_gemv(args):
+def run_gemv(args, emit=True):
     import torch
 
     from joshua_b200.qtensor import QTensor
@@ -285,7 +280,34 @@ def run_gemv(args):
                      "note": "time per matmul includes the activation-plane kernel that precedes it"},
         "gpu_launches": 2 * nmat * args.steps, "clocks": clocks.summary(),
     }
-    print(json.dumps(line))
+    del ws, bank
+    torch.cuda.empty_cache()
+    if emit:
+        print(json.dumps(line))
+    return line
+
+
+def run_default(args):
+    """The Qwen3-MoE decode step (the workload that shards over GPUs) as the line; on one GPU the dense Llama-8B
+    line and the per-format single-matmul figures ride along as `dense` and `kernels`."""
+    import copy
+
+    from joshua_b200 import bench_llama, bench_moe
+
+    def extra(line):
+        if line["n_gpus"] != 1:
+            return
+        line["dense"] = bench_llama.run(args, emit=False)
+        kernels = []
+        for t in ("q4_k", "q8_0", "q2_k", "iq2_xxs", "mxfp4"):
+            a = copy.copy(args)
+            a.workload, a.type, a.n, a.k, a.m, a.rotate_gb = "gemv", t, 4096, 4096, 1, 0.5
+            g = run_gemv(a, emit=False)
+            kernels.append({"type": t, "n": 4096, "k": 4096, "m": 1, "gbs": g["value"], "frac_of_hbm": g["roofline"]["frac"],
+                            "us_per_matmul": g["ms_per_step"] * 1e3})
+        line["kernels"] = kernels
+
+    return bench_moe.run(args, extra=extra)
 
 
 def run_moe_layer(args):
@@ -349,7 +371,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama8b", choices=["llama8b", "gemv", "qwen3moe", "moe_layer"])
+    ap.add_argument("--workload", default="default", choices=["default", "llama8b", "gemv", "qwen3moe", "moe_layer"])
     ap.add_argument("--type", default="q4_k", choices=sorted(TYPE_BY_NAME))
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -366,6 +388,8 @@ def main():
         return run_gemv(args)
     if args.workload == "moe_layer":
         return run_moe_layer(args)
+    if args.workload == "default":
+        return run_default(args)
     if args.workload == "qwen3moe":
         from joshua_b200 import bench_moe
 

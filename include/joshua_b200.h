@@ -341,6 +341,9 @@ int32_t jq_moe_route_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, const
                          uint32_t* ids_dev, float* wts_dev, void* stream);
 int32_t jq_moe_experts_dev(jq_moe* m, const float* x_dev, uint64_t n_rows, const uint32_t* expert_ids_dev,
                            float* out_dev, void* stream);
+/* Routing of rmsnorm(x; norm_w, eps): the block's norm folded into the router kernel (up to eight tokens). */
+int32_t jq_moe_route_norm_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, const float* norm_w_dev, float eps,
+                              const uint32_t* forced_ids_dev, uint32_t* ids_dev, float* wts_dev, void* stream);
 
 /* After synchronising: JQ_E_EXPERT_RANGE if an id was out of range under
  * oob_policy 0, JQ_E_TIMEOUT as jq_device_status, else JQ_OK. */
@@ -380,7 +383,10 @@ int32_t jq_moe_last_routing(jq_moe* m, uint64_t n_tokens, uint32_t* ids, float* 
  *   jq_ep_connect_loopback  instead of jq_ep_connect: every peer window becomes a
  *                  private allocation on this device that nobody serves.  For
  *                  single-GPU tests of the wait bound and of the addressing; the
- *                  waits on the absent peers run out and are reported. */
+ *                  waits on the absent peers run out and are reported.
+ *   jq_ep_rows_served  after synchronising the device: how many activation rows
+ *                  this rank's experts were sent in the last exchange (the load
+ *                  figure behind max / mean over ranks under skewed routing). */
 #define JQ_EP_HANDLE_BYTES 64
 typedef struct jq_ep jq_ep;
 int32_t jq_ep_create(jq_ctx* ctx, uint32_t rank, uint32_t world, uint32_t n_expert, uint32_t n_used, uint32_t hidden,
@@ -390,8 +396,14 @@ int32_t jq_ep_export(jq_ep* e, uint8_t* handle);
 int32_t jq_ep_connect(jq_ep* e, const uint8_t* handles);
 int32_t jq_ep_connect_loopback(jq_ep* e);
 int32_t jq_ep_set_poll_limit(jq_ep* e, uint32_t polls);
+int32_t jq_ep_rows_served(jq_ep* e, uint32_t* rows);
 int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float* x_dev, uint64_t n_tokens,
                           const float* residual_dev, float* y_dev, void* stream);
+/* The same with the block's RMS norm folded in: y = residual + layer(rmsnorm(x; norm_w, eps)); the router
+ * normalises inside its kernel and the rows travel normalised. */
+int32_t jq_ep_forward_norm_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float* x_dev, uint64_t n_tokens,
+                               const float* norm_w_dev, float eps, const float* residual_dev, float* y_dev,
+                               void* stream);
 
 #ifdef __cplusplus
 }

@@ -24,7 +24,8 @@ from . import synth
 from .llama import LlamaConfig, LlamaDecoder
 
 
-def run(args):
+def run(args, emit=True):
+    """Measures the workload; prints the JSON line on rank 0 (emit) and returns it (None on other ranks)."""
     import torch
     import torch.distributed as dist
 
@@ -174,6 +175,12 @@ def run(args):
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
         except Exception as exc:  # the oracle is test infrastructure; the line stands without it
             line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": 0, "kind": "port", "sample": repr(exc)}
-        print(json.dumps(line))
+        if emit:
+            print(json.dumps(line))
+    else:
+        line = None
     if world > 1:
         dist.destroy_process_group()
+    del model
+    torch.cuda.empty_cache()
+    return line

@@ -102,6 +102,7 @@ __device__ bool publish(uint32_t* done, const Window& win, uint64_t flag_off, ui
 // grid = P + world CTAs.  CTA p < P stores pair p's activation row and local expert id into its owner's
 // window; CTA P + d marks the unused slots of my block on rank d.  pair_slot[p] = owner * cap + slot.
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(Window win, Layout l, uint32_t me, const float* __restrict__ x,
+                                                          const float* __restrict__ norm_w, float eps,
                                                           const uint32_t* __restrict__ ids, uint32_t T, uint32_t K,
                                                           uint32_t* __restrict__ pair_slot, uint32_t* __restrict__ epoch,
                                                           uint32_t* __restrict__ done, uint32_t polls, int* status) {
@@ -127,7 +128,29 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(Window win, Layout l, 
             const uint64_t r = (uint64_t)me * l.cap + slot;
             float4* dst = reinterpret_cast<float4*>(win.base[d] + l.o_rows_in) + r * (l.hidden / 4);
             const float4* src = reinterpret_cast<const float4*>(x) + (uint64_t)(p / K) * (l.hidden / 4);
-            for (uint32_t c = tid; c < l.hidden / 4; c += blockDim.x) dst[c] = src[c];
+            if (norm_w == nullptr) {
+                for (uint32_t c = tid; c < l.hidden / 4; c += blockDim.x) dst[c] = src[c];
+            } else {
+                // the row travels RMS-normalised (the block's norm folded into the exchange): sum of squares per
+                // thread in column order, threads in thread order
+                float ss = 0.0f;
+                for (uint32_t c = tid; c < l.hidden / 4; c += blockDim.x) {
+                    const float4 v = src[c];
+                    ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+                }
+                for (int off = 16; off; off >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, off);
+                __syncthreads();  // s_red is free again (every thread has read the slot count)
+                if ((tid & 31) == 0) reinterpret_cast<float*>(s_red)[tid >> 5] = ss;
+                __syncthreads();
+                float tot = 0.0f;
+                for (uint32_t w = 0; w < blockDim.x / 32; ++w) tot += reinterpret_cast<float*>(s_red)[w];
+                const float rs = rsqrtf(tot / (float)l.hidden + eps);
+                const float4* g4 = reinterpret_cast<const float4*>(norm_w);
+                for (uint32_t c = tid; c < l.hidden / 4; c += blockDim.x) {
+                    const float4 v = src[c], g = g4[c];
+                    dst[c] = make_float4(v.x * rs * g.x, v.y * rs * g.y, v.z * rs * g.z, v.w * rs * g.w);
+                }
+            }
             if (tid == 0) {
                 reinterpret_cast<uint32_t*>(win.base[d] + l.o_ids_in)[r] = ids[p] - d * l.n_local;
                 pair_slot[p] = d * l.cap + slot;
@@ -326,8 +349,27 @@ int32_t jq_ep_set_poll_limit(jq_ep* e, uint32_t polls) {
     return jq::OK;
 }
 
+int32_t jq_ep_rows_served(jq_ep* e, uint32_t* rows) {
+    if (!e || !rows) return jq_fail(jq::E_INVALID, "jq_ep_rows_served: NULL argument");
+    JQ_CUDA(cudaSetDevice(e->ctx->device));
+    JQ_CUDA(cudaDeviceSynchronize());
+    const size_t n = (size_t)e->world * e->lay.cap;
+    std::vector<uint32_t> ids(n);
+    JQ_CUDA(cudaMemcpy(ids.data(), e->win.base[e->rank] + e->lay.o_ids_in, n * 4, cudaMemcpyDeviceToHost));
+    uint32_t served = 0;
+    for (uint32_t id : ids) served += id < e->n_local ? 1u : 0u;
+    *rows = served;
+    return jq::OK;
+}
+
 int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float* x_dev, uint64_t T,
                           const float* residual_dev, float* y_dev, void* stream) {
+    return jq_ep_forward_norm_dev(e, router, experts, x_dev, T, nullptr, 0.0f, residual_dev, y_dev, stream);
+}
+
+int32_t jq_ep_forward_norm_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float* x_dev, uint64_t T,
+                               const float* norm_w_dev, float eps, const float* residual_dev, float* y_dev,
+                               void* stream) {
     if (!e || !router || !experts) return jq_fail(jq::E_INVALID, "jq_ep_forward_dev: NULL handle");
     if (!e->connected) return jq_fail(jq::E_INVALID, "jq_ep_forward_dev: call jq_ep_connect first");
     if (!x_dev || !y_dev) return jq_fail(jq::E_INVALID, "jq_ep_forward_dev: NULL buffer");
@@ -344,9 +386,9 @@ int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     uint8_t* mine = e->win.base[e->rank];
     const uint32_t P = (uint32_t)T * e->n_used;
-    if (int32_t r = jq_moe_route_dev(router, x_dev, T, nullptr, e->ids, e->wts, stream)) return r;
+    if (int32_t r = jq_moe_route_norm_dev(router, x_dev, T, norm_w_dev, eps, nullptr, e->ids, e->wts, stream)) return r;
     JQ_CUDA(jq::launch_pdl(ep_dispatch_kernel, dim3(P + e->world), 256, 0, s, e->win, e->lay, e->rank, x_dev,
-                           (const uint32_t*)e->ids, (uint32_t)T, e->n_used, e->pair_slot, e->epoch, e->done,
+                           norm_w_dev, eps, (const uint32_t*)e->ids, (uint32_t)T, e->n_used, e->pair_slot, e->epoch, e->done,
                            e->polls, e->ctx->status_dev));
     if (int32_t r = jq_moe_experts_list(experts, reinterpret_cast<const float*>(mine + e->lay.o_rows_in), rows,
                                         reinterpret_cast<const uint32_t*>(mine + e->lay.o_ids_in), s))

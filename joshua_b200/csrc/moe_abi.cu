@@ -393,6 +393,12 @@ int32_t jq_moe_reserve(jq_moe* m, uint64_t n_tokens, uint64_t n_rows) {
 
 int32_t jq_moe_route_dev(jq_moe* m, const float* x_dev, uint64_t T, const uint32_t* forced_ids_dev,
                          uint32_t* ids_dev, float* wts_dev, void* stream) {
+    return jq_moe_route_norm_dev(m, x_dev, T, nullptr, 0.0f, forced_ids_dev, ids_dev, wts_dev, stream);
+}
+
+// Routing of rmsnorm(x; norm_w, eps) (norm_w NULL: of x).  Up to eight tokens fold the norm into the router kernel.
+int32_t jq_moe_route_norm_dev(jq_moe* m, const float* x_dev, uint64_t T, const float* norm_w_dev, float eps,
+                              const uint32_t* forced_ids_dev, uint32_t* ids_dev, float* wts_dev, void* stream) {
     if (!m) return jq_fail(jq::E_INVALID, "jq_moe_route_dev: NULL handle");
     if (T == 0) return jq::OK;
     if (!x_dev || !ids_dev || !wts_dev) return jq_fail(jq::E_INVALID, "jq_moe_route_dev: NULL buffer");
@@ -400,10 +406,15 @@ int32_t jq_moe_route_dev(jq_moe* m, const float* x_dev, uint64_t T, const uint32
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const jq_moe_config& c = m->cfg;
     if (T <= 8 && c.hidden % 4 == 0) {
-        JQ_CUDA(jq::launch_moe_route_fused(x_dev, nullptr, 0.0f, m->router, (uint32_t)T, c.hidden, m->logits, m->rp,
+        JQ_CUDA(jq::launch_moe_route_fused(x_dev, norm_w_dev, eps, m->router, (uint32_t)T, c.hidden, m->logits, m->rp,
                                            m->bias, forced_ids_dev, ids_dev, wts_dev, false, 1, nullptr, nullptr, nullptr,
                                            nullptr, nullptr, nullptr, m->counter, s));
         return jq::OK;
+    }
+    if (norm_w_dev) {
+        if (!m->xn) return jq_fail(jq::E_TOO_LARGE, "jq_moe_route_norm_dev: call jq_moe_reserve first");
+        JQ_CUDA(jq::launch_rmsnorm(x_dev, nullptr, norm_w_dev, eps, T, c.hidden, nullptr, m->xn, s));
+        x_dev = m->xn;
     }
     JQ_CUDA(jq::launch_moe_logits(x_dev, m->router, (uint32_t)T, c.n_expert, c.hidden, m->logits, s));
     JQ_CUDA(jq::launch_moe_route(m->logits, m->rp, (uint32_t)T, m->bias, forced_ids_dev, ids_dev, wts_dev, s));
@@ -471,15 +482,13 @@ int32_t jq_moe_forward_norm_add_dev(jq_moe* m, const float* x_dev, uint64_t T, c
     // buckets spread over eight streams.  Measured on 384 MXFP4 experts of 7168 x 2048 at 4096 tokens (85 rows per
     // expert): 61 ms this way against 126 ms for the grouped decode kernel (322 ms on a single stream, where one
     // expert's tile GEMM fills 16 of 148 SMs).
+    uint64_t thr_override = 0;  // average rows per expert from which to bucket (measurement switch)
 #ifdef JQ_PROFILING
-    static const char* thr_env = std::getenv("JQ_MOE_BUCKET_ROWS");  // average rows per expert from which to bucket
-#else
-    constexpr const char* thr_env = nullptr;
+    if (const char* thr_env = std::getenv("JQ_MOE_BUCKET_ROWS")) thr_override = std::strtoull(thr_env, nullptr, 10);
 #endif
     // small experts (Qwen3-MoE: 2048 x 768) need more rows before a bucket beats the grouped kernel: measured
     // 9.0 against 3.9 ms at 64 rows per expert, 11.5 against 14.9 ms at 256
-    const uint64_t thr = thr_env ? std::strtoull(thr_env, nullptr, 10)
-                                 : ((uint64_t)c.hidden * c.inter >= (1ull << 23) ? 64ull : 192ull);
+    const uint64_t thr = thr_override ? thr_override : ((uint64_t)c.hidden * c.inter >= (1ull << 23) ? 64ull : 192ull);
     const bool bucketed = !fused && !m->ctx->force_f32 && P >= thr * c.n_expert;
     if (bucketed) {
         if (int32_t rc = run_experts_bucketed(m, x_in, T, P, s)) return rc;

@@ -218,15 +218,26 @@ class PeerExchange:
             _lib.check(_lib.lib().jq_ep_connect(self._h, blob))
             dist.barrier(group=group)                      # nobody stores into a window that is not mapped yet
 
-    def forward_dev(self, router_layer, expert_layer, x, y, residual=None, stream=None) -> None:
-        """y = (residual +) layer(x); `residual` may be `y`."""
+    def forward_dev(self, router_layer, expert_layer, x, y, residual=None, stream=None, norm_w=None, eps=0.0) -> None:
+        """y = (residual +) layer(x), or layer(rmsnorm(x; norm_w, eps)) with `norm_w`; `residual` may be `y`."""
         from . import _lib
 
         T = x.numel() // self.hidden
         s = torch.cuda.current_stream(x.device).cuda_stream if stream is None else stream
-        _lib.check(_lib.lib().jq_ep_forward_dev(self._h, router_layer._h, expert_layer._h, x.data_ptr(), T,
-                                                residual.data_ptr() if residual is not None else None,
-                                                y.data_ptr(), s))
+        _lib.check(_lib.lib().jq_ep_forward_norm_dev(self._h, router_layer._h, expert_layer._h, x.data_ptr(), T,
+                                                     norm_w.data_ptr() if norm_w is not None else None, eps,
+                                                     residual.data_ptr() if residual is not None else None,
+                                                     y.data_ptr(), s))
+
+    def rows_served(self) -> int:
+        """Rows this rank's experts were sent in the last exchange (synchronises the device)."""
+        import ctypes
+
+        from . import _lib
+
+        n = ctypes.c_uint32()
+        _lib.check(_lib.lib().jq_ep_rows_served(self._h, ctypes.byref(n)))
+        return int(n.value)
 
     def close(self) -> None:
         from . import _lib

@@ -88,7 +88,7 @@ class MoeDecoder(LlamaDecoder):
                 rl.reserve(batch, 0)
                 el.reserve(cap, cap)
                 self.ffn_layers.append(dict(router=rl, experts=el, keep=banks))
-        self.launches_per_step = (3 + (4 if self.world == 1 else 8)) * cfg.layers + 4
+        self.launches_per_step = (3 + (4 if self.world == 1 else 7)) * cfg.layers + 4
 
     def _ffn(self, ly, s) -> None:
         """self.x += MoE(rmsnorm(self.x; ffn_norm)); the residual add rides in the combine kernel."""
@@ -98,8 +98,8 @@ class MoeDecoder(LlamaDecoder):
             _lib.check(L.jq_moe_forward_norm_add_dev(f["moe"]._h, P(self.x), B, None, P(ly["ffn_norm"]), c.eps,
                                                      P(self.x), P(self.x), s))
         else:
-            _lib.check(L.jq_rmsnorm_dev(P(self.x), None, P(ly["ffn_norm"]), c.eps, B, c.hidden, None, P(self.xn), s))
-            self.exchange.forward_dev(f["router"], f["experts"], self.xn, self.x, residual=self.x, stream=s)
+            self.exchange.forward_dev(f["router"], f["experts"], self.x, self.x, residual=self.x, stream=s,
+                                      norm_w=ly["ffn_norm"], eps=c.eps)
 
     def step(self, stream=None) -> None:
         if not hasattr(self, "_layer_index"):
