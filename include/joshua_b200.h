@@ -231,6 +231,31 @@ int32_t jq_attention_fused_dev(const float* qkv, const int32_t* pos, uint32_t ba
                                uint32_t head_dim, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,
                                float* out, void* scratch, int32_t* bad_pos_dev, void* stream);
 
+/* The same with the per-head RMS norm of q and k in front of the rotary embedding (Qwen3's `attn_q_norm` /
+ * `attn_k_norm`, [head_dim] each, src/quantized_qwen3_moe.rs:343-353).  Both NULL = jq_attention_fused_dev. */
+int32_t jq_attention_fused_qknorm_dev(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t n_q, uint32_t n_kv,
+                                      uint32_t head_dim, uint32_t max_ctx, float theta, const float* q_norm_w,
+                                      const float* k_norm_w, float qk_eps, float* cache_k, float* cache_v, float* out,
+                                      void* scratch, int32_t* bad_pos_dev, void* stream);
+
+/* Prefill: `seq` new tokens of ONE sequence at positions pos0[0] .. pos0[0] + seq - 1 (the reference's
+ * `forward(input [1, seq_len], offset)`, src/quantized_qwen3_moe.rs:297-386,793-819).
+ * jq_rope_append_prefill_dev: qkv [seq, (n_q + 2 n_kv) * head_dim] -> q_out [seq, n_q * head_dim] rotated (after the
+ * optional per-head q / k norm), k and v appended to the cache of sequence 0 ([n_kv, max_ctx, head_dim]).
+ * jq_attention_prefill_dev: out[s] = attention of token s over cache positions 0 .. pos0 + s (causal); head_dim 64
+ * or 128.  Tokens that would run past max_ctx store nothing / the whole call does nothing, and *bad_pos_dev is set. */
+int32_t jq_rope_append_prefill_dev(const float* qkv, const int32_t* pos0, uint32_t seq, uint32_t n_q, uint32_t n_kv,
+                                   uint32_t head_dim, uint32_t max_ctx, float theta, const float* q_norm_w,
+                                   const float* k_norm_w, float qk_eps, float* q_out, float* cache_k, float* cache_v,
+                                   int32_t* bad_pos_dev, void* stream);
+int32_t jq_attention_prefill_dev(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos0,
+                                 uint32_t seq, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t max_ctx,
+                                 float* out, int32_t* bad_pos_dev, void* stream);
+
+/* out = silu(min(gate, clamp)) * clamp(up) element-wise (`Mlp::forward` between its matmuls for batches the fused
+ * gate / up kernel does not take; clamp <= 0: none). */
+int32_t jq_swiglu_dev(const float* gate, const float* up, uint64_t n, float clamp, float* out, void* stream);
+
 /* Grouped-query attention of one new token per sequence over positions
  * 0..pos[b] of the cache (src/quantized_qwen3_moe.rs:366-386).  `scratch`:
  * jq_attention_scratch_bytes(...) bytes of caller device memory (per-chunk

@@ -58,6 +58,10 @@ _SIGNATURES = {
     "jq_add_dev": (i32, [vp, vp, u64, vp, vp]),
     "jq_argmax_scratch_bytes": (u64, [u64]),
     "jq_argmax_dev": (i32, [vp, u64, u64, vp, vp, vp, vp]),
+    "jq_attention_fused_qknorm_dev": (i32, [vp, vp, u32, u32, u32, u32, u32, f32, vp, vp, f32, vp, vp, vp, vp, vp, vp]),
+    "jq_rope_append_prefill_dev": (i32, [vp, vp, u32, u32, u32, u32, u32, f32, vp, vp, f32, vp, vp, vp, vp, vp]),
+    "jq_attention_prefill_dev": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp, vp, vp]),
+    "jq_swiglu_dev": (i32, [vp, vp, u64, f32, vp, vp]),
     "jq_sample_greedy_dev": (i32, [vp, u64, u64, f32, vp, vp, vp, vp, vp, vp]),
     "jq_moe_create": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, pp]),
     "jq_moe_free": (None, [vp]),

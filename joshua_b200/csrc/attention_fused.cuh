@@ -37,6 +37,11 @@ struct AttnArgs {
     float* out;            // [B, nq * hd]
     unsigned long long* trace = nullptr;  // profiling aid: item (0, 0, 0) stores the GPU timer at its phases
     int32_t* bad_pos = nullptr;  // set to 1 when a position lies outside the cache (the item then does nothing)
+    // per-head RMS norm of q and k before the rotary embedding (Qwen3: `attn_q_norm` / `attn_k_norm`, [hd] each,
+    // src/quantized_qwen3_moe.rs:343-353); NULL = none
+    const float* q_norm = nullptr;
+    const float* k_norm = nullptr;
+    float qk_eps = 0.0f;
 };
 
 // dynamic shared memory the item needs, in floats
@@ -145,6 +150,35 @@ __device__ __forceinline__ void attention_fused_item_t(const AttnArgs& a, uint32
     if (p_raw < 0 || (uint32_t)p_raw >= max_ctx) {
         if (tid == 0 && a.bad_pos) atomicExch(a.bad_pos, 1);
         return;
+    }
+    if (a.q_norm != nullptr) {
+        // per-head RMS norm: a head's HALF rotary pairs sit in HALF / 32 consecutive warps of one round, so its
+        // sum of squares is those warps' partial sums, added in warp order
+        __shared__ float s_nrm[ROT_PER][NW];
+#pragma unroll
+        for (uint32_t r = 0; r < ROT_PER; ++r) {
+            const uint32_t idx = tid + r * ATT_FUSED_THREADS;
+            float ss = idx < N_ROT ? fmaf(ra[r], ra[r], rb[r] * rb[r]) : 0.0f;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+            if (lane == 0) s_nrm[r][warp] = ss;
+        }
+        att_sync<BAR>();
+        constexpr uint32_t WPH = HALF / 32;  // warps per head
+#pragma unroll
+        for (uint32_t r = 0; r < ROT_PER; ++r) {
+            const uint32_t idx = tid + r * ATT_FUSED_THREADS;
+            if (idx < N_ROT) {
+                const uint32_t g = idx / HALF, i = idx - g * HALF, w0 = warp - warp % WPH;
+                float ss = 0.0f;
+#pragma unroll
+                for (uint32_t w = 0; w < WPH; ++w) ss += s_nrm[r][w0 + w];
+                const float sc = rsqrtf(ss / (float)HD + a.qk_eps);
+                const float* nw = g < G ? a.q_norm : a.k_norm;
+                ra[r] = ra[r] * sc * __ldg(nw + i);
+                rb[r] = rb[r] * sc * __ldg(nw + i + HALF);
+            }
+        }
     }
     const uint32_t p = (uint32_t)p_raw, n_ctx = p + 1;
     const uint32_t active = (n_ctx + ATT_FUSED_CHUNK - 1) / ATT_FUSED_CHUNK;

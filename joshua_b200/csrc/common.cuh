@@ -183,7 +183,12 @@ cudaError_t launch_rmsnorm(const float* x, const float* res, const float* w, flo
                            float* sum_out, float* out, cudaStream_t s);
 cudaError_t launch_rope_append(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
                                uint32_t hd, uint32_t max_ctx, float theta, float* q_out, float* cache_k, float* cache_v,
-                               int32_t* bad_pos, cudaStream_t s);
+                               int32_t* bad_pos, cudaStream_t s, uint32_t seq = 0, const float* q_norm = nullptr,
+                               const float* k_norm = nullptr, float qk_eps = 0.0f);
+// causal attention of `seq` new tokens of one sequence (positions pos[0] ..) over the cache; hd 64 or 128
+cudaError_t launch_attention_prefill(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,
+                                     uint32_t seq, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx, float* out,
+                                     int32_t* bad_pos, cudaStream_t s);
 // rope + cache append + attention + merge in one launch, from the fused qkv row (decoder.cu)
 struct AttnArgs;
 bool attention_fused_args(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd,
@@ -192,7 +197,8 @@ bool attention_fused_args(const float* qkv, const int32_t* pos, uint32_t batch, 
 size_t attention_fused_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx);
 cudaError_t launch_attention_fused(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
                                    uint32_t hd, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,
-                                   float* out, void* scratch, int32_t* bad_pos, cudaStream_t s);
+                                   float* out, void* scratch, int32_t* bad_pos, cudaStream_t s,
+                                   const float* q_norm = nullptr, const float* k_norm = nullptr, float qk_eps = 0.0f);
 // scratch: attention_scratch_bytes(...) bytes of per-chunk partial results
 size_t attention_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t hd, uint32_t max_ctx);
 cudaError_t launch_attention_decode(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,

@@ -97,11 +97,17 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const float* __restric
                                                           uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx,
                                                           float theta, float* __restrict__ q_out,
                                                           float* __restrict__ cache_k, float* __restrict__ cache_v,
-                                                          int32_t* __restrict__ bad_pos) {
+                                                          int32_t* __restrict__ bad_pos, uint32_t seq,
+                                                          const float* __restrict__ q_norm,
+                                                          const float* __restrict__ k_norm, float qk_eps) {
+    __shared__ float red[4];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     pdl_wait_();
+    // decode (seq == 0): blockIdx.y is the sequence, its position pos[b].  Prefill (seq > 0): one sequence,
+    // blockIdx.y is the token, its position pos[0] + token; the cache is sequence 0's.
     const uint32_t b = blockIdx.y, head = blockIdx.x;  // heads 0..nq-1: q; nq..nq+nkv-1: k; then v
-    const int32_t p_raw = pos[b];
+    const int32_t p_raw = seq ? pos[0] + (int32_t)b : pos[b];
+    const uint32_t cb = seq ? 0u : b;  // cache block
     if (p_raw < 0 || (uint32_t)p_raw >= max_ctx) {
         // the cache has no row for this position: nothing is stored, the flag says why
         if (threadIdx.x == 0 && bad_pos) atomicExch(bad_pos, 1);
@@ -112,17 +118,25 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const float* __restric
     const uint32_t half = hd / 2;
     if (head < nq + nkv) {
         float* dst = head < nq ? q_out + ((uint64_t)b * nq + head) * hd
-                               : cache_k + (((uint64_t)b * nkv + (head - nq)) * max_ctx + p) * hd;
+                               : cache_k + (((uint64_t)cb * nkv + (head - nq)) * max_ctx + p) * hd;
+        const float* nw = head < nq ? q_norm : k_norm;
+        float sc = 1.0f;
+        if (nw != nullptr) {  // per-head RMS norm in front of the rotary embedding
+            float ss = 0.0f;
+            for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+            sc = rsqrtf(block_sum(ss, red) / (float)hd + qk_eps);
+        }
         for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
             float freq = rope_freq(theta, i, hd);
             float s, c;
             sincosf((float)p * freq, &s, &c);
             float a = src[i], bb = src[i + half];
+            if (nw != nullptr) a = a * sc * nw[i], bb = bb * sc * nw[i + half];
             dst[i] = a * c - bb * s;
             dst[i + half] = a * s + bb * c;
         }
     } else {
-        float* dst = cache_v + (((uint64_t)b * nkv + (head - nq - nkv)) * max_ctx + p) * hd;
+        float* dst = cache_v + (((uint64_t)cb * nkv + (head - nq - nkv)) * max_ctx + p) * hd;
         for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = src[i];
     }
 }
@@ -221,6 +235,96 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const float* __res
             if (m != -INFINITY) acc = fmaf(expf(m - mx), src[(uint64_t)c * (hd + 2) + i], acc);
         }
         out[bh * hd + i] = acc / den;
+    }
+}
+
+// Prefill: `seq` new tokens of ONE sequence at positions pos0 .. pos0 + seq - 1, causal over the cache (which
+// already holds their k / v rows): out[s, head, :] = softmax(q_s . K[0 .. pos0 + s]^T / sqrt(hd)) V
+// (src/quantized_qwen3_moe.rs:366-386 with the causal mask of :805-812).  One CTA per (16 queries, q head); a warp owns
+// four queries; keys are taken 32 at a time - lane <-> key for the scores, lane <-> output dimensions for the
+// V sum - with the usual running maximum / sum, in position order.  f32 throughout.
+constexpr uint32_t PF_TQ = 16, PF_TK = 32;
+
+template <uint32_t HD>
+__global__ void __launch_bounds__(128) attention_prefill_kernel(const float* __restrict__ q, const float* __restrict__ cache_k,
+                                                                const float* __restrict__ cache_v,
+                                                                const int32_t* __restrict__ pos, uint32_t seq, uint32_t nq,
+                                                                uint32_t nkv, uint32_t max_ctx, float* __restrict__ out,
+                                                                int32_t* __restrict__ bad_pos) {
+    constexpr uint32_t DPL = HD / 32;  // output dimensions per lane
+    __shared__ float sq[PF_TQ][HD];
+    __shared__ float sk[PF_TK][HD + 1];
+    __shared__ float sv[PF_TK][HD];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    pdl_wait_();
+    const uint32_t head = blockIdx.y, kvh = head / (nq / nkv), s0 = blockIdx.x * PF_TQ;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int32_t p0 = pos[0];
+    if (p0 < 0 || (uint64_t)p0 + seq > max_ctx) {
+        if (threadIdx.x == 0 && bad_pos) atomicExch(bad_pos, 1);
+        return;
+    }
+    for (uint32_t i = threadIdx.x; i < PF_TQ * HD; i += blockDim.x) {
+        const uint32_t r = i / HD, c = i % HD, s = s0 + r;
+        sq[r][c] = s < seq ? q[((uint64_t)s * nq + head) * HD + c] : 0.0f;
+    }
+    const float* K = cache_k + (uint64_t)kvh * max_ctx * HD;
+    const float* V = cache_v + (uint64_t)kvh * max_ctx * HD;
+    const float scale = rsqrtf((float)HD);
+    float acc[4][DPL], mx[4], sum[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        mx[i] = -INFINITY, sum[i] = 0.0f;
+#pragma unroll
+        for (uint32_t d = 0; d < DPL; ++d) acc[i][d] = 0.0f;
+    }
+    const uint32_t last_q = min(seq, s0 + PF_TQ) - 1;          // newest query of the tile
+    const uint32_t n_keys = (uint32_t)p0 + last_q + 1;         // keys the tile can see
+    for (uint32_t t0 = 0; t0 < n_keys; t0 += PF_TK) {
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < PF_TK * HD; i += blockDim.x) {
+            const uint32_t r = i / HD, c = i % HD, t = t0 + r;
+            sk[r][c] = t < n_keys ? K[(uint64_t)t * HD + c] : 0.0f;
+            sv[r][c] = t < n_keys ? V[(uint64_t)t * HD + c] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t s = s0 + 4 * warp + i;
+            if (s >= seq) continue;                              // warp-uniform
+            const uint32_t visible = (uint32_t)p0 + s + 1;       // keys 0 .. p0 + s
+            if (t0 >= visible) continue;
+            float sc = 0.0f;
+#pragma unroll 8
+            for (uint32_t c = 0; c < HD; ++c) sc = fmaf(sq[4 * warp + i][c], sk[lane][c], sc);
+            sc = t0 + lane < visible ? sc * scale : -INFINITY;
+            float cm = sc;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xFFFFFFFFu, cm, o));
+            const float nm = fmaxf(mx[i], cm);
+            const float corr = expf(mx[i] - nm);                 // 0 on the first chunk (mx = -inf)
+            const float pr = expf(sc - nm);                      // 0 for masked keys
+            float ps = pr;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xFFFFFFFFu, ps, o);
+            sum[i] = sum[i] * corr + ps;
+            mx[i] = nm;
+#pragma unroll
+            for (uint32_t d = 0; d < DPL; ++d) acc[i][d] *= corr;
+            for (uint32_t j = 0; j < PF_TK; ++j) {
+                const float pj = __shfl_sync(0xFFFFFFFFu, pr, j);
+#pragma unroll
+                for (uint32_t d = 0; d < DPL; ++d) acc[i][d] = fmaf(pj, sv[j][lane + 32 * d], acc[i][d]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t s = s0 + 4 * warp + i;
+        if (s < seq) {
+#pragma unroll
+            for (uint32_t d = 0; d < DPL; ++d) out[((uint64_t)s * nq + head) * HD + lane + 32 * d] = acc[i][d] / sum[i];
+        }
     }
 }
 
@@ -380,9 +484,10 @@ cudaError_t launch_rmsnorm(const float* x, const float* res, const float* w, flo
 
 cudaError_t launch_rope_append(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
                                uint32_t hd, uint32_t max_ctx, float theta, float* q_out, float* cache_k, float* cache_v,
-                               int32_t* bad_pos, cudaStream_t s) {
-    cudaError_t le2__ = launch_pdl(rope_append_kernel, dim3(nq + 2 * nkv, batch), 128, 0, s, qkv, pos, nq, nkv, hd, max_ctx, theta, q_out, cache_k,
-                                                                 cache_v, bad_pos);
+                               int32_t* bad_pos, cudaStream_t s, uint32_t seq, const float* q_norm, const float* k_norm,
+                               float qk_eps) {
+    cudaError_t le2__ = launch_pdl(rope_append_kernel, dim3(nq + 2 * nkv, seq ? seq : batch), 128, 0, s, qkv, pos, nq, nkv, hd, max_ctx, theta, q_out, cache_k,
+                                                                 cache_v, bad_pos, seq, q_norm, k_norm, qk_eps);
     if (le2__ != cudaSuccess) return le2__;
     return cudaGetLastError();
 }
@@ -407,6 +512,20 @@ cudaError_t launch_attention_decode(const float* q, const float* cache_k, const 
     return cudaGetLastError();
 }
 
+cudaError_t launch_attention_prefill(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,
+                                     uint32_t seq, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx, float* out,
+                                     int32_t* bad_pos, cudaStream_t s) {
+    const dim3 grid((seq + PF_TQ - 1) / PF_TQ, nq);
+    cudaError_t e;
+    if (hd == 64)
+        e = launch_pdl(attention_prefill_kernel<64>, grid, 128, 0, s, q, cache_k, cache_v, pos, seq, nq, nkv, max_ctx, out, bad_pos);
+    else if (hd == 128)
+        e = launch_pdl(attention_prefill_kernel<128>, grid, 128, 0, s, q, cache_k, cache_v, pos, seq, nq, nkv, max_ctx, out, bad_pos);
+    else
+        return cudaErrorInvalidValue;
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
 size_t attention_fused_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx) {
     uint32_t n_chunks = (max_ctx + ATT_FUSED_CHUNK - 1) / ATT_FUSED_CHUNK;
     return (size_t)batch * nq * n_chunks * (hd + 2) * 4 + (size_t)batch * nkv * 2 * 4;  // partials + counters
@@ -416,11 +535,15 @@ size_t attention_fused_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t nkv, 
 // the first call; the kernel leaves them zero.
 cudaError_t launch_attention_fused(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
                                    uint32_t hd, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,
-                                   float* out, void* scratch, int32_t* bad_pos, cudaStream_t s) {
+                                   float* out, void* scratch, int32_t* bad_pos, cudaStream_t s, const float* q_norm,
+                                   const float* k_norm, float qk_eps) {
     AttnArgs a;
     if (!attention_fused_args(qkv, pos, batch, nq, nkv, hd, max_ctx, theta, cache_k, cache_v, out, scratch, &a))
         return cudaErrorInvalidValue;
     a.bad_pos = bad_pos;
+    a.q_norm = q_norm;
+    a.k_norm = k_norm;
+    a.qk_eps = qk_eps;
     size_t smem = (size_t)attention_fused_smem_floats(nq / a.gsplit, nkv, hd, a.n_chunks) * 4;
     cudaError_t e = launch_pdl(attention_fused_kernel, dim3(a.n_chunks, nkv * a.gsplit, batch), ATT_FUSED_THREADS, smem, s, a);
     if (e != cudaSuccess) return e;

@@ -97,14 +97,25 @@ uint64_t jq_attention_fused_scratch_bytes(uint32_t batch, uint32_t n_q, uint32_t
 int32_t jq_attention_fused_dev(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t n_q, uint32_t n_kv,
                                uint32_t head_dim, uint32_t max_ctx, float theta, float* cache_k, float* cache_v,
                                float* out, void* scratch, int32_t* bad_pos_dev, void* stream) {
+    return jq_attention_fused_qknorm_dev(qkv, pos, batch, n_q, n_kv, head_dim, max_ctx, theta, nullptr, nullptr, 0.0f,
+                                         cache_k, cache_v, out, scratch, bad_pos_dev, stream);
+}
+
+int32_t jq_attention_fused_qknorm_dev(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t n_q, uint32_t n_kv,
+                                      uint32_t head_dim, uint32_t max_ctx, float theta, const float* q_norm_w,
+                                      const float* k_norm_w, float qk_eps, float* cache_k, float* cache_v, float* out,
+                                      void* scratch, int32_t* bad_pos_dev, void* stream) {
     if (batch == 0) return jq::OK;
+    if ((q_norm_w == nullptr) != (k_norm_w == nullptr))
+        return jq_fail(jq::E_INVALID, "jq_attention_fused_qknorm_dev: q and k norm weights go together");
     if (!qkv || !pos || !cache_k || !cache_v || !out || !scratch)
         return jq_fail(jq::E_INVALID, "jq_attention_fused_dev: NULL buffer");
     if (n_kv == 0 || n_q % n_kv || !(head_dim == 64 || head_dim == 128 || head_dim == 256) ||
         !(n_q / n_kv == 1 || n_q / n_kv == 2 || n_q / n_kv == 4 || n_q / n_kv == 8))
         return jq_fail(jq::E_INVALID, "jq_attention_fused_dev: need head_dim 64, 128 or 256 and 1, 2, 4 or 8 query heads per kv head");
     JQ_CUDA(jq::launch_attention_fused(qkv, pos, batch, n_q, n_kv, head_dim, max_ctx, theta, cache_k, cache_v, out,
-                                       scratch, bad_pos_dev, static_cast<cudaStream_t>(stream)));
+                                       scratch, bad_pos_dev, static_cast<cudaStream_t>(stream), q_norm_w, k_norm_w,
+                                       qk_eps));
     return jq::OK;
 }
 
@@ -175,6 +186,39 @@ int32_t jq_argmax_dev(const float* logits, uint64_t rows, uint64_t vocab, int32_
     if (!logits || !token || !scratch || vocab == 0) return jq_fail(jq::E_INVALID, "jq_argmax_dev: bad argument");
     JQ_CUDA(jq::launch_argmax(logits, (uint32_t)rows, (uint32_t)vocab, token, pos, scratch,
                               static_cast<cudaStream_t>(stream)));
+    return jq::OK;
+}
+
+int32_t jq_rope_append_prefill_dev(const float* qkv, const int32_t* pos0, uint32_t seq, uint32_t n_q, uint32_t n_kv,
+                                   uint32_t head_dim, uint32_t max_ctx, float theta, const float* q_norm_w,
+                                   const float* k_norm_w, float qk_eps, float* q_out, float* cache_k, float* cache_v,
+                                   int32_t* bad_pos_dev, void* stream) {
+    if (seq == 0) return jq::OK;
+    if (!qkv || !pos0 || !q_out || !cache_k || !cache_v || head_dim % 2 || n_kv == 0 || n_q % n_kv ||
+        (q_norm_w == nullptr) != (k_norm_w == nullptr))
+        return jq_fail(jq::E_INVALID, "jq_rope_append_prefill_dev: bad argument");
+    JQ_CUDA(jq::launch_rope_append(qkv, pos0, 1, n_q, n_kv, head_dim, max_ctx, theta, q_out, cache_k, cache_v, bad_pos_dev,
+                                   static_cast<cudaStream_t>(stream), seq, q_norm_w, k_norm_w, qk_eps));
+    return jq::OK;
+}
+
+int32_t jq_attention_prefill_dev(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos0,
+                                 uint32_t seq, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t max_ctx,
+                                 float* out, int32_t* bad_pos_dev, void* stream) {
+    if (seq == 0) return jq::OK;
+    if (!q || !cache_k || !cache_v || !pos0 || !out || n_kv == 0 || n_q % n_kv)
+        return jq_fail(jq::E_INVALID, "jq_attention_prefill_dev: bad argument");
+    if (head_dim != 64 && head_dim != 128)
+        return jq_fail(jq::E_INVALID, "jq_attention_prefill_dev: head_dim 64 or 128");
+    JQ_CUDA(jq::launch_attention_prefill(q, cache_k, cache_v, pos0, seq, n_q, n_kv, head_dim, max_ctx, out, bad_pos_dev,
+                                         static_cast<cudaStream_t>(stream)));
+    return jq::OK;
+}
+
+int32_t jq_swiglu_dev(const float* gate, const float* up, uint64_t n, float clamp, float* out, void* stream) {
+    if (n == 0) return jq::OK;
+    if (!gate || !up || !out) return jq_fail(jq::E_INVALID, "jq_swiglu_dev: NULL buffer");
+    JQ_CUDA(jq::launch_swiglu(gate, up, n, clamp, out, static_cast<cudaStream_t>(stream)));
     return jq::OK;
 }
 

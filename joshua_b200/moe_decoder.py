@@ -34,7 +34,8 @@ class MoeDecoderConfig(LlamaConfig):
 
 class MoeDecoder(LlamaDecoder):
     def __init__(self, cfg: MoeDecoderConfig, device, batch: int = 1, max_ctx: int = 640, attn_type: int = synth.Q8_0,
-                 expert_type: int = synth.Q4_K, seed: int = 0, group=None, weights=None, expert_weights=None):
+                 expert_type: int = synth.Q4_K, seed: int = 0, group=None, weights=None, expert_weights=None,
+                 norms=None, qk_norm: bool = False, routers=None):
         """`weights(name, rows, cols, seed)` / `expert_weights(name, rows, cols, seed)` may supply the raw blocks
         of the dense linears / of this rank's slice of an expert bank (flat uint8 tensors); the defaults draw
         them on the device.  `seed` must be the same on every rank: dense weights are replicated."""
@@ -46,7 +47,8 @@ class MoeDecoder(LlamaDecoder):
         self.rank = dist.get_rank(group) if group is not None else 0
         self._expert_type = expert_type
         self._dense_ffn = False
-        super().__init__(cfg, device, batch=batch, max_ctx=max_ctx, wtype=attn_type, seed=seed, weights=weights)
+        super().__init__(cfg, device, batch=batch, max_ctx=max_ctx, wtype=attn_type, seed=seed, weights=weights,
+                         norms=norms, qk_norm=qk_norm)
         mk_expert = expert_weights or (lambda name, rows, cols, s: synth.random_weight_torch(expert_type, rows, cols, s, device))
         self.routers, self._expert_raw = [], []
         ctx = default_context(device.index or 0)
@@ -59,15 +61,22 @@ class MoeDecoder(LlamaDecoder):
             # router and banks are the same on every rank for the same layer (seeded by layer, not by rank)
             gen.manual_seed(1000 + l)
             router = (torch.randn(E, h, generator=gen, device=device, dtype=torch.float32) * 0.5).cpu().numpy()
+            if routers is not None:
+                router = np.ascontiguousarray(routers(l), dtype=np.float32)     # [n_expert, hidden]
             banks = []
             for i, (rows, cols) in enumerate([(I, h), (I, h), (h, I)]):
                 full_seed = 5000 + l * 8 + i
                 # each rank draws only its own experts' blocks; the seed folds in the first local expert
-                raw = mk_expert(f"l{l}.experts{i}", per * rows, cols, full_seed * 1000 + self.rank * per).to(device)
-                raw = torch.cat([raw, torch.zeros(16, dtype=torch.uint8, device=device)])
-                nbytes = synth.tensor_bytes(expert_type, per * rows, cols)
+                raw = mk_expert(f"l{l}.experts{i}", per * rows, cols, full_seed * 1000 + self.rank * per)
+                et = expert_type
+                if isinstance(raw, tuple):
+                    et, raw = raw
+                raw = torch.cat([raw.to(device), torch.zeros(16, dtype=torch.uint8, device=device)])
+                nbytes = synth.tensor_bytes(et, per * rows, cols)
                 self.expert_bytes += nbytes
-                banks.append((QTensor.from_device(expert_type, raw[:nbytes], ctx), raw))
+                banks.append((QTensor.from_device(et, raw[:nbytes], ctx), raw))
+                self._expert_types = getattr(self, "_expert_types", {})
+                self._expert_types[(l, i)] = et
             self.routers.append(router)
             self._expert_raw.append([b[1] for b in banks])
             if self.world == 1:
@@ -101,10 +110,26 @@ class MoeDecoder(LlamaDecoder):
             self.exchange.forward_dev(f["router"], f["experts"], self.x, self.x, residual=self.x, stream=s,
                                       norm_w=ly["ffn_norm"], eps=c.eps)
 
+    def _has_dense_ffn(self) -> bool:
+        return False
+
     def step(self, stream=None) -> None:
         if not hasattr(self, "_layer_index"):
             self._layer_index = {id(ly): i for i, ly in enumerate(self.layers)}
         super().step(stream)
+
+    def prefill(self, token_ids, stream=None) -> None:
+        if not hasattr(self, "_layer_index"):
+            self._layer_index = {id(ly): i for i, ly in enumerate(self.layers)}
+        assert self.world == 1, "prefill runs on one GPU (the exchange windows are sized for decode batches)"
+        super().prefill(token_ids, stream)
+
+    def _ffn_prefill(self, ly, x, xn, S, s) -> None:
+        """x += MoE(rmsnorm(x; ffn_norm)) over S tokens (`Moe::forward` with n_tokens = seq_len)."""
+        L, c, P = _lib.lib(), self.cfg, lambda t: t.data_ptr()
+        layer = self.ffn_layers[self._layer_index[id(ly)]]["moe"]
+        layer.reserve(S, S * c.n_used)
+        _lib.check(L.jq_moe_forward_norm_add_dev(layer._h, P(x), S, None, P(ly["ffn_norm"]), c.eps, P(x), P(x), s))
 
     def expert_bytes_per_token(self) -> int:
         """Expert-bank bytes one token touches: n_used experts x 3 matrices per layer."""
@@ -112,3 +137,40 @@ class MoeDecoder(LlamaDecoder):
         per_expert = 2 * synth.tensor_bytes(self._expert_type, c.moe_inter, c.hidden) + \
             synth.tensor_bytes(self._expert_type, c.hidden, c.moe_inter)
         return c.layers * c.n_used * per_expert
+
+
+def moe_from_gguf(path, device, batch: int = 1, max_ctx: int = 640, group=None) -> MoeDecoder:
+    """A `qwen3moe` GGUF file as a device decoder (the reference's `GGUFQWenMoE::from_gguf`,
+    src/quantized_qwen3_moe.rs:678-790): dense tensors are uploaded whole on every rank, of each expert bank
+    `blk.{i}.ffn_{gate,up,down}_exps.weight` ([n_expert, out, in], experts contiguous) a rank uploads only its own
+    run of experts; the router `ffn_gate_inp` is decoded to f32 once."""
+    import torch
+    import torch.distributed as dist
+
+    from .gguf import GgufFile
+    from .llama import _gguf_common, _gguf_providers
+
+    f = GgufFile(path)
+    arch = f.header.architecture()
+    if arch != "qwen3moe":
+        raise ValueError(f"expected a qwen3moe file, found `{arch}`")
+    md = f.header.metadata
+    hp = _gguf_common(f, arch)
+    cfg = MoeDecoderConfig(n_expert=int(md[f"{arch}.expert_count"]), n_used=int(md[f"{arch}.expert_used_count"]),
+                           moe_inter=int(md[f"{arch}.expert_feed_forward_length"]), **hp)
+    weights, norms = _gguf_providers(f, torch)
+    world = dist.get_world_size(group) if group is not None else 1
+    rank = dist.get_rank(group) if group is not None else 0
+    per = cfg.n_expert // world
+    bank_names = ["ffn_gate_exps", "ffn_up_exps", "ffn_down_exps"]
+
+    def expert_weights(name, rows, cols, seed):
+        layer, part = name.split(".")
+        gname = f"blk.{layer[1:]}.{bank_names[int(part[-1])]}.weight"
+        return f.info(gname).dtype, torch.from_numpy(f.expert_bytes(gname, rank * per, per).copy())
+
+    dec = MoeDecoder(cfg, device, batch=batch, max_ctx=max_ctx, group=group, weights=weights, norms=norms,
+                     expert_weights=expert_weights, qk_norm="blk.0.attn_q_norm.weight" in f.header.tensors,
+                     routers=lambda l: f.float_tensor(f"blk.{l}.ffn_gate_inp.weight"))
+    dec.gguf = f
+    return dec

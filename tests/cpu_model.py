@@ -33,22 +33,32 @@ class CpuDecoder:
     def __init__(self, dec):
         c = self.cfg = dec.cfg
         self.wtype = dec.wtype
+        self.types = dict(dec._types)
         self.raw = {name: t[:-16].cpu().numpy() for name, t in dec._raw.items()}
         self.norms = [(ly["attn_norm"].cpu().numpy(), ly["ffn_norm"].cpu().numpy()) for ly in dec.layers]
+        self.qk_norms = [(ly["q_norm"].cpu().numpy(), ly["k_norm"].cpu().numpy()) if dec.qk_norm else None
+                         for ly in dec.layers]
         self.out_norm = dec.out_norm.cpu().numpy()
         self.moe = None
         if hasattr(dec, "routers"):
-            self.moe = dict(routers=dec.routers, etype=dec._expert_type,
+            self.moe = dict(routers=dec.routers, etypes=[[dec._expert_types[(l, i)] for i in range(3)]
+                                                         for l in range(c.layers)],
                             banks=[[b[:-16].cpu().numpy() for b in layer] for layer in dec._expert_raw],
                             cfg=oracle.moe_cfg(gating=0, n_expert=c.n_expert, n_used=c.n_used, hidden=c.hidden,
                                                inter=c.moe_inter, norm=True, decode_path=True))
         self.K = [np.zeros((c.kv_heads, 0, c.head_dim), F) for _ in range(c.layers)]
         self.V = [np.zeros((c.kv_heads, 0, c.head_dim), F) for _ in range(c.layers)]
         self.pos = 0
-        self.row_bytes = synth.tensor_bytes(self.wtype, 1, c.hidden)
+        self.row_bytes = synth.tensor_bytes(self.types["token_embd"], 1, c.hidden)
 
     def linear(self, name, x, n, k):
-        return oracle.matmul_t(self.wtype, (1, k, n), x.reshape(1, k), self.raw[name])[0]
+        return oracle.matmul_t(self.types[name], (1, k, n), x.reshape(1, k), self.raw[name])[0]
+
+    def head_norm(self, v, w):
+        """Per-head RMS norm over head_dim (Qwen3 q / k norm, src/quantized_qwen3_moe.rs:343-353)."""
+        c = self.cfg
+        ss = np.sum(v * v, axis=-1, keepdims=True, dtype=F)
+        return (v * (F(1.0) / np.sqrt(ss / F(c.head_dim) + F(c.eps))).astype(F) * w).astype(F)
 
     def rms(self, x, w):
         c = self.cfg
@@ -68,12 +78,14 @@ class CpuDecoder:
         c, p = self.cfg, self.pos
         h, nq, nkv, hd = c.hidden, c.q_heads, c.kv_heads, c.head_dim
         row = self.raw["token_embd"][tok * self.row_bytes:(tok + 1) * self.row_bytes]
-        x = oracle.dequantize(self.wtype, row, two_step=True).astype(F)
+        x = oracle.dequantize(self.types["token_embd"], row, two_step=True).astype(F)
         for l in range(c.layers):
             an, fn = self.norms[l]
             qkv = self.linear(f"l{l}.wqkv", self.rms(x, an), c.qkv_rows, h)
-            q = self.rope(qkv[: nq * hd].reshape(nq, hd), p)
-            k = self.rope(qkv[nq * hd:(nq + nkv) * hd].reshape(nkv, hd), p)
+            q, k = qkv[: nq * hd].reshape(nq, hd), qkv[nq * hd:(nq + nkv) * hd].reshape(nkv, hd)
+            if self.qk_norms[l] is not None:
+                q, k = self.head_norm(q, self.qk_norms[l][0]), self.head_norm(k, self.qk_norms[l][1])
+            q, k = self.rope(q, p), self.rope(k, p)
             v = qkv[(nq + nkv) * hd:].reshape(nkv, hd)
             self.K[l] = np.concatenate([self.K[l], k[:, None, :]], axis=1)
             self.V[l] = np.concatenate([self.V[l], v[:, None, :]], axis=1)
@@ -94,7 +106,7 @@ class CpuDecoder:
                 m = self.moe
                 logits = oracle.moe_logits(xn.reshape(1, h), m["routers"][l])
                 ids, wts = oracle.moe_route(m["cfg"], logits)
-                y = oracle.moe_dispatch(m["cfg"], xn.reshape(1, h), ids, wts, [m["etype"]] * 3, m["banks"][l])
+                y = oracle.moe_dispatch(m["cfg"], xn.reshape(1, h), ids, wts, m["etypes"][l], m["banks"][l])
                 x = (x + y[0]).astype(F)
         self.pos += 1
         return self.linear("output", self.rms(x, self.out_norm), c.vocab, h)

@@ -101,7 +101,7 @@ def test_size_errors():
     with pytest.raises(JoshuaB200Error, match="whole number"):
         QTensor.from_bytes(synth.Q4_K, raw[:-1])
     with pytest.raises(JoshuaB200Error, match="unsupported"):
-        QTensor.from_bytes(11, raw)
+        QTensor.from_bytes(17, raw)      # IQ2_XS: no decoder here
     q = QTensor.from_bytes(synth.Q4_K, raw)
     with pytest.raises(JoshuaB200Error, match="output holds"):
         q.dequantize(256)
