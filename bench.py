@@ -15,6 +15,9 @@ Workloads
            device (4.22 GB of raw Q4_K blocks read once per token).  With --gpus N: N replicas, no collective.
   moe_layer one routed-expert layer (--type, --experts, --used, --k hidden, --n expert width, --m tokens):
            the grouped expert matmuls at a given token count.
+  mxfp4_experts  one routed-expert layer of 384 MXFP4 experts top-8 (hidden 7168, width 2048) swept over
+           1 / 16 / 256 / 4096 tokens with Zipf(1.1) expert popularity; with --gpus N the banks are split over the
+           ranks and rows cross through the peer-memory exchange (joshua_b200/bench_experts.py).
   gemv     one quantized matmul shape, rotated over a working set larger than L2
            (--type, --n, --k, --m, --rotate-gb): the kernel-level roofline probe
            and the command used for ncu captures.
@@ -388,7 +391,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="default", choices=["default", "llama8b", "gemv", "qwen3moe", "moe_layer"])
+    ap.add_argument("--workload", default="default", choices=["default", "llama8b", "gemv", "qwen3moe", "moe_layer", "mxfp4_experts"])
+    ap.add_argument("--tokens", default="1,16,256,4096", help="mxfp4_experts: global token counts of the sweep")
     ap.add_argument("--type", default="q4_k", choices=sorted(TYPE_BY_NAME))
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -407,6 +411,10 @@ def main():
         return run_moe_layer(args)
     if args.workload == "default":
         return run_default(args)
+    if args.workload == "mxfp4_experts":
+        from joshua_b200 import bench_experts
+
+        return bench_experts.run(args)
     if args.workload == "qwen3moe":
         from joshua_b200 import bench_moe
 

@@ -425,10 +425,11 @@ int32_t jq_ep_rows_served(jq_ep* e, uint32_t* rows);
 int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float* x_dev, uint64_t n_tokens,
                           const float* residual_dev, float* y_dev, void* stream);
 /* The same with the block's RMS norm folded in: y = residual + layer(rmsnorm(x; norm_w, eps)); the router
- * normalises inside its kernel and the rows travel normalised. */
+ * normalises inside its kernel and the rows travel normalised.  forced_ids_dev ([n_tokens, n_used] or NULL)
+ * replaces the top-k selection as in jq_moe_forward (hash-routed layers, src/quantized_deepseek4.rs:1375-1398). */
 int32_t jq_ep_forward_norm_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float* x_dev, uint64_t n_tokens,
-                               const float* norm_w_dev, float eps, const float* residual_dev, float* y_dev,
-                               void* stream);
+                               const float* norm_w_dev, float eps, const uint32_t* forced_ids_dev,
+                               const float* residual_dev, float* y_dev, void* stream);
 
 #ifdef __cplusplus
 }

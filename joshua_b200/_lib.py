@@ -81,7 +81,7 @@ _SIGNATURES = {
     "jq_ep_set_poll_limit": (i32, [vp, u32]),
     "jq_ep_rows_served": (i32, [vp, ctypes.POINTER(u32)]),
     "jq_ep_forward_dev": (i32, [vp, vp, vp, vp, u64, vp, vp, vp]),
-    "jq_ep_forward_norm_dev": (i32, [vp, vp, vp, vp, u64, vp, f32, vp, vp, vp]),
+    "jq_ep_forward_norm_dev": (i32, [vp, vp, vp, vp, u64, vp, f32, vp, vp, vp, vp]),
     "jq_moe_forward_add_dev": (i32, [vp, vp, u64, vp, vp, vp, vp]),
     "jq_moe_forward_norm_add_dev": (i32, [vp, vp, u64, vp, vp, f32, vp, vp, vp]),
     "jq_matmul_swiglu_norm_dev": (i32, [vp, vp, u64, u64, u64, vp, vp, f32, vp, f32, vp]),

@@ -364,12 +364,12 @@ int32_t jq_ep_rows_served(jq_ep* e, uint32_t* rows) {
 
 int32_t jq_ep_forward_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float* x_dev, uint64_t T,
                           const float* residual_dev, float* y_dev, void* stream) {
-    return jq_ep_forward_norm_dev(e, router, experts, x_dev, T, nullptr, 0.0f, residual_dev, y_dev, stream);
+    return jq_ep_forward_norm_dev(e, router, experts, x_dev, T, nullptr, 0.0f, nullptr, residual_dev, y_dev, stream);
 }
 
 int32_t jq_ep_forward_norm_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const float* x_dev, uint64_t T,
-                               const float* norm_w_dev, float eps, const float* residual_dev, float* y_dev,
-                               void* stream) {
+                               const float* norm_w_dev, float eps, const uint32_t* forced_ids_dev,
+                               const float* residual_dev, float* y_dev, void* stream) {
     if (!e || !router || !experts) return jq_fail(jq::E_INVALID, "jq_ep_forward_dev: NULL handle");
     if (!e->connected) return jq_fail(jq::E_INVALID, "jq_ep_forward_dev: call jq_ep_connect first");
     if (!x_dev || !y_dev) return jq_fail(jq::E_INVALID, "jq_ep_forward_dev: NULL buffer");
@@ -386,7 +386,7 @@ int32_t jq_ep_forward_norm_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     uint8_t* mine = e->win.base[e->rank];
     const uint32_t P = (uint32_t)T * e->n_used;
-    if (int32_t r = jq_moe_route_norm_dev(router, x_dev, T, norm_w_dev, eps, nullptr, e->ids, e->wts, stream)) return r;
+    if (int32_t r = jq_moe_route_norm_dev(router, x_dev, T, norm_w_dev, eps, forced_ids_dev, e->ids, e->wts, stream)) return r;
     JQ_CUDA(jq::launch_pdl(ep_dispatch_kernel, dim3(P + e->world), 256, 0, s, e->win, e->lay, e->rank, x_dev,
                            norm_w_dev, eps, (const uint32_t*)e->ids, (uint32_t)T, e->n_used, e->pair_slot, e->epoch, e->done,
                            e->polls, e->ctx->status_dev));

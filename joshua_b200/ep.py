@@ -218,16 +218,24 @@ class PeerExchange:
             _lib.check(_lib.lib().jq_ep_connect(self._h, blob))
             dist.barrier(group=group)                      # nobody stores into a window that is not mapped yet
 
-    def forward_dev(self, router_layer, expert_layer, x, y, residual=None, stream=None, norm_w=None, eps=0.0) -> None:
-        """y = (residual +) layer(x), or layer(rmsnorm(x; norm_w, eps)) with `norm_w`; `residual` may be `y`."""
+    def forward_dev(self, router_layer, expert_layer, x, y, residual=None, stream=None, norm_w=None, eps=0.0,
+                    forced_ids=None) -> None:
+        """y = (residual +) layer(x), or layer(rmsnorm(x; norm_w, eps)) with `norm_w`; `residual` may be `y`.
+        More tokens than the window was sized for go through it in slices of `max_tokens` (every rank must
+        then pass the same number of tokens, so that all ranks make the same number of exchanges)."""
         from . import _lib
 
         T = x.numel() // self.hidden
         s = torch.cuda.current_stream(x.device).cuda_stream if stream is None else stream
-        _lib.check(_lib.lib().jq_ep_forward_norm_dev(self._h, router_layer._h, expert_layer._h, x.data_ptr(), T,
-                                                     norm_w.data_ptr() if norm_w is not None else None, eps,
-                                                     residual.data_ptr() if residual is not None else None,
-                                                     y.data_ptr(), s))
+        x2, y2 = x.reshape(T, self.hidden), y.reshape(T, self.hidden)
+        r2 = residual.reshape(T, self.hidden) if residual is not None else None
+        for t0 in range(0, T, self.max_tokens):
+            t1 = min(T, t0 + self.max_tokens)
+            _lib.check(_lib.lib().jq_ep_forward_norm_dev(
+                self._h, router_layer._h, expert_layer._h, x2[t0:t1].data_ptr(), t1 - t0,
+                norm_w.data_ptr() if norm_w is not None else None, eps,
+                forced_ids[t0:t1].data_ptr() if forced_ids is not None else None,
+                r2[t0:t1].data_ptr() if r2 is not None else None, y2[t0:t1].data_ptr(), s))
 
     def rows_served(self) -> int:
         """Rows this rank's experts were sent in the last exchange (synchronises the device)."""
