@@ -15,6 +15,8 @@ Workloads
            device (4.22 GB of raw Q4_K blocks read once per token).  With --gpus N: N replicas, no collective.
   moe_layer one routed-expert layer (--type, --experts, --used, --k hidden, --n expert width, --m tokens):
            the grouped expert matmuls at a given token count.
+  deepseek_v3  decode of a DeepSeek-V3-shaped stack: 8 layers of multi-head latent attention + 256 IQ2_XXS experts
+           top-8 with a shared expert, the rest Q8_0 (--batch sequences per GPU; experts over --gpus N ranks).
   mxfp4_experts  one routed-expert layer of 384 MXFP4 experts top-8 (hidden 7168, width 2048) swept over
            1 / 16 / 256 / 4096 tokens with Zipf(1.1) expert popularity; with --gpus N the banks are split over the
            ranks and rows cross through the peer-memory exchange (joshua_b200/bench_experts.py).
@@ -391,7 +393,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="default", choices=["default", "llama8b", "gemv", "qwen3moe", "moe_layer", "mxfp4_experts"])
+    ap.add_argument("--workload", default="default", choices=["default", "llama8b", "gemv", "qwen3moe", "moe_layer", "mxfp4_experts", "deepseek_v3"])
     ap.add_argument("--tokens", default="1,16,256,4096", help="mxfp4_experts: global token counts of the sweep")
     ap.add_argument("--type", default="q4_k", choices=sorted(TYPE_BY_NAME))
     ap.add_argument("--n", type=int, default=4096)
@@ -411,6 +413,10 @@ def main():
         return run_moe_layer(args)
     if args.workload == "default":
         return run_default(args)
+    if args.workload == "deepseek_v3":
+        from joshua_b200 import bench_deepseek
+
+        return bench_deepseek.run(args)
     if args.workload == "mxfp4_experts":
         from joshua_b200 import bench_experts
 

@@ -252,6 +252,32 @@ int32_t jq_attention_prefill_dev(const float* q, const float* cache_k, const flo
                                  uint32_t seq, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t max_ctx,
                                  float* out, int32_t* bad_pos_dev, void* stream);
 
+/* RmsNorm over the first `hidden` columns of rows that are x_stride floats apart (the latent part of the
+ * compressed kv row, `kv_a_norm`, src/quantized_deepseek2.rs:462-466); out rows are `hidden` wide. */
+int32_t jq_rmsnorm_strided_dev(const float* x, uint64_t x_stride, const float* weight, float eps, uint64_t rows,
+                               uint64_t hidden, float* out, void* stream);
+
+/* Multi-head latent attention, one new token per sequence (`Attention::forward` of src/quantized_deepseek2.rs:422-504
+ * between its projections and its attention): interleaved rotary embedding (pairs 2i, 2i + 1; angle
+ * pos * inv_freq[i]; cos and sin times `mscale`, the YaRN table of :243-300) of the last qk_rope columns of every
+ * q head (in place) and of the shared key k_pe = comp[kv_lora ..], then the per-head rows
+ * K[pos] = [k_nope | k_pe] and V[pos] = v are appended to the caches, which hold the reconstructed per-head form
+ * as the reference's does (:389-401).  q [batch, n_head * (qk_nope + qk_rope)]; comp [batch, kv_lora + qk_rope];
+ * kv [batch, n_head * (qk_nope + v_dim)]; cache_k [batch, n_head, max_ctx, qk_nope + qk_rope]; cache_v
+ * [batch, n_head, max_ctx, v_dim]. */
+int32_t jq_mla_assemble_dev(float* q, const float* comp, const float* kv, const int32_t* pos, uint32_t batch,
+                            uint32_t n_head, uint32_t qk_nope, uint32_t qk_rope, uint32_t v_dim, uint32_t kv_lora,
+                            uint32_t max_ctx, const float* inv_freq_dev, float mscale, float* cache_k, float* cache_v,
+                            int32_t* bad_pos_dev, void* stream);
+
+/* jq_attention_decode_dev with key rows of qk_dim and value rows of v_dim floats and an explicit softmax scale
+ * (MLA: 192 / 128, scale 1 / sqrt(192) times the YaRN factor).  scratch: jq_attention_scratch_bytes(batch, n_q,
+ * v_dim, max_ctx). */
+int32_t jq_attention_decode_qkv_dev(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,
+                                    uint32_t batch, uint32_t n_q, uint32_t n_kv, uint32_t qk_dim, uint32_t v_dim,
+                                    uint32_t max_ctx, float softmax_scale, float* out, float* scratch,
+                                    int32_t* bad_pos_dev, void* stream);
+
 /* out = silu(min(gate, clamp)) * clamp(up) element-wise (`Mlp::forward` between its matmuls for batches the fused
  * gate / up kernel does not take; clamp <= 0: none). */
 int32_t jq_swiglu_dev(const float* gate, const float* up, uint64_t n, float clamp, float* out, void* stream);

@@ -62,6 +62,9 @@ _SIGNATURES = {
     "jq_rope_append_prefill_dev": (i32, [vp, vp, u32, u32, u32, u32, u32, f32, vp, vp, f32, vp, vp, vp, vp, vp]),
     "jq_attention_prefill_dev": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp, vp, vp]),
     "jq_swiglu_dev": (i32, [vp, vp, u64, f32, vp, vp]),
+    "jq_rmsnorm_strided_dev": (i32, [vp, u64, vp, f32, u64, u64, vp, vp]),
+    "jq_mla_assemble_dev": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, u32, vp, f32, vp, vp, vp, vp]),
+    "jq_attention_decode_qkv_dev": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, f32, vp, vp, vp, vp]),
     "jq_sample_greedy_dev": (i32, [vp, u64, u64, f32, vp, vp, vp, vp, vp, vp]),
     "jq_moe_create": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, pp]),
     "jq_moe_free": (None, [vp]),

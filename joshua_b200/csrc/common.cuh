@@ -180,7 +180,11 @@ cudaError_t launch_swiglu(const float* g, const float* u, uint64_t n, float clam
 
 // decoder.cu: the element-wise and attention steps around the matmuls of a decode step
 cudaError_t launch_rmsnorm(const float* x, const float* res, const float* w, float eps, uint64_t rows, uint32_t h,
-                           float* sum_out, float* out, cudaStream_t s);
+                           float* sum_out, float* out, cudaStream_t s, uint32_t x_stride = 0);
+cudaError_t launch_mla_assemble(float* q, const float* comp, const float* kv, const int32_t* pos, uint32_t batch,
+                                uint32_t nh, uint32_t nope, uint32_t rope, uint32_t vd, uint32_t kv_lora, uint32_t max_ctx,
+                                const float* inv_freq, float mscale, float* cache_k, float* cache_v, int32_t* bad_pos,
+                                cudaStream_t s);
 cudaError_t launch_rope_append(const float* qkv, const int32_t* pos, uint32_t batch, uint32_t nq, uint32_t nkv,
                                uint32_t hd, uint32_t max_ctx, float theta, float* q_out, float* cache_k, float* cache_v,
                                int32_t* bad_pos, cudaStream_t s, uint32_t seq = 0, const float* q_norm = nullptr,
@@ -203,7 +207,7 @@ cudaError_t launch_attention_fused(const float* qkv, const int32_t* pos, uint32_
 size_t attention_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t hd, uint32_t max_ctx);
 cudaError_t launch_attention_decode(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,
                                     uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx, float* out,
-                                    float* scratch, int32_t* bad_pos, cudaStream_t s);
+                                    float* scratch, int32_t* bad_pos, cudaStream_t s, uint32_t dv = 0, float scale = 0.0f);
 cudaError_t launch_add(const float* a, const float* b, uint64_t n, float* y, cudaStream_t s);
 size_t argmax_scratch_bytes(uint32_t rows);
 // greedy token per row; with a window (ids [rows, 64] + state [rows, 2]) and penalty != 1 the reference's

@@ -33,13 +33,14 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // registers between the two passes (rows up to 16384 wide; wider rows re-read).
 __global__ void __launch_bounds__(1024) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ res,
                                                        const float* __restrict__ w, float eps, uint32_t h,
-                                                       float* __restrict__ sum_out, float* __restrict__ out) {
+                                                       float* __restrict__ sum_out, float* __restrict__ out,
+                                                       uint32_t x_stride) {
     __shared__ float red[32];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     pdl_wait_();
     const uint64_t row = blockIdx.x;
     const uint32_t n4 = h / 4;
-    const float4* x4 = reinterpret_cast<const float4*>(x + row * h);
+    const float4* x4 = reinterpret_cast<const float4*>(x + row * x_stride);  // rows of x may be wider than h
     const float4* r4 = res ? reinterpret_cast<const float4*>(res + row * h) : nullptr;
     float4* s4 = sum_out ? reinterpret_cast<float4*>(sum_out + row * h) : nullptr;
     float4 keep[4];
@@ -152,7 +153,9 @@ __global__ void __launch_bounds__(128) attention_partial_kernel(const float* __r
                                                                 const float* __restrict__ cache_v,
                                                                 const int32_t* __restrict__ pos, uint32_t nq, uint32_t nkv,
                                                                 uint32_t hd, uint32_t max_ctx, uint32_t n_chunks,
-                                                                float* __restrict__ part, int32_t* __restrict__ bad_pos) {
+                                                                float* __restrict__ part, int32_t* __restrict__ bad_pos,
+                                                                uint32_t dv, float scale) {
+    // hd: width of q and K rows; dv: width of V rows and of the result (MLA: 192 / 128; otherwise the same)
     extern __shared__ float s_att[];  // hd (q) + ATT_CHUNK (scores)
     __shared__ float red[4];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -163,11 +166,11 @@ __global__ void __launch_bounds__(128) attention_partial_kernel(const float* __r
     if (!in_cache && threadIdx.x == 0 && bad_pos) atomicExch(bad_pos, 1);
     const uint32_t n_ctx = in_cache ? (uint32_t)p_raw + 1 : 0u;  // a position outside the cache attends to nothing
     const uint32_t t0 = chunk * ATT_CHUNK;
-    float* dst = part + (((uint64_t)b * nq + head) * n_chunks + chunk) * (hd + 2);
+    float* dst = part + (((uint64_t)b * nq + head) * n_chunks + chunk) * (dv + 2);
     if (t0 >= n_ctx) {
         if (threadIdx.x == 0) {
-            dst[hd] = -INFINITY;
-            dst[hd + 1] = 0.0f;
+            dst[dv] = -INFINITY;
+            dst[dv + 1] = 0.0f;
         }
         return;
     }
@@ -178,8 +181,7 @@ __global__ void __launch_bounds__(128) attention_partial_kernel(const float* __r
     for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) sq[i] = qr[i];
     __syncthreads();
     const float* K = cache_k + (((uint64_t)b * nkv + kvh) * max_ctx + t0) * hd;
-    const float* V = cache_v + (((uint64_t)b * nkv + kvh) * max_ctx + t0) * hd;
-    const float scale = rsqrtf((float)hd);
+    const float* V = cache_v + (((uint64_t)b * nkv + kvh) * max_ctx + t0) * dv;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     float mx = -INFINITY;
     for (uint32_t t = warp; t < cnt; t += nw) {
@@ -204,14 +206,14 @@ __global__ void __launch_bounds__(128) attention_partial_kernel(const float* __r
         sum += e;
     }
     sum = block_sum(sum, red);
-    for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) {
+    for (uint32_t i = threadIdx.x; i < dv; i += blockDim.x) {
         float acc = 0.0f;
-        for (uint32_t t = 0; t < cnt; ++t) acc = fmaf(sc[t], V[(uint64_t)t * hd + i], acc);
+        for (uint32_t t = 0; t < cnt; ++t) acc = fmaf(sc[t], V[(uint64_t)t * dv + i], acc);
         dst[i] = acc;
     }
     if (threadIdx.x == 0) {
-        dst[hd] = mx;
-        dst[hd + 1] = sum;
+        dst[dv] = mx;
+        dst[dv + 1] = sum;
     }
 }
 
@@ -475,9 +477,10 @@ unsigned blocks_for(uint64_t work, unsigned per_block) {
 }  // namespace
 
 cudaError_t launch_rmsnorm(const float* x, const float* res, const float* w, float eps, uint64_t rows, uint32_t h,
-                           float* sum_out, float* out, cudaStream_t s) {
-    if (h % 4) return cudaErrorInvalidValue;
-    cudaError_t le1__ = launch_pdl(rmsnorm_kernel, (unsigned)rows, 1024, 0, s, x, res, w, eps, h, sum_out, out);
+                           float* sum_out, float* out, cudaStream_t s, uint32_t x_stride) {
+    if (x_stride == 0) x_stride = h;
+    if (h % 4 || x_stride % 4) return cudaErrorInvalidValue;
+    cudaError_t le1__ = launch_pdl(rmsnorm_kernel, (unsigned)rows, 1024, 0, s, x, res, w, eps, h, sum_out, out, x_stride);
     if (le1__ != cudaSuccess) return le1__;
     return cudaGetLastError();
 }
@@ -497,17 +500,70 @@ size_t attention_scratch_bytes(uint32_t batch, uint32_t nq, uint32_t hd, uint32_
     return (size_t)batch * nq * n_chunks * (hd + 2) * 4;
 }
 
+// Multi-head latent attention (src/quantized_deepseek2.rs:422-504), the step between the projections and the
+// attention proper for one new token per sequence: the rotary embedding (interleaved pairs 2i, 2i+1, angles
+// pos * inv_freq[i], cos / sin scaled by `mscale`) of the last `rope` columns of every q head and of the shared key
+// k_pe, then K[pos] = [k_nope of the head | k_pe] and V[pos] = v of the head appended to the per-head caches.
+//   q [B, nh * (nope + rope)] in place;  comp [B, comp_stride], k_pe = comp[kv_lora ..];  kv [B, nh * (nope + vd)];
+//   cache_k [B, nh, max_ctx, nope + rope];  cache_v [B, nh, max_ctx, vd].
+__global__ void __launch_bounds__(128) mla_assemble_kernel(float* __restrict__ q, const float* __restrict__ comp,
+                                                           const float* __restrict__ kv, const int32_t* __restrict__ pos,
+                                                           uint32_t nh, uint32_t nope, uint32_t rope, uint32_t vd,
+                                                           uint32_t kv_lora, uint32_t max_ctx,
+                                                           const float* __restrict__ inv_freq, float mscale,
+                                                           float* __restrict__ cache_k, float* __restrict__ cache_v,
+                                                           int32_t* __restrict__ bad_pos) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    pdl_wait_();
+    const uint32_t head = blockIdx.x, b = blockIdx.y, qd = nope + rope;
+    const int32_t p_raw = pos[b];
+    if (p_raw < 0 || (uint32_t)p_raw >= max_ctx) {
+        if (threadIdx.x == 0 && bad_pos) atomicExch(bad_pos, 1);
+        return;
+    }
+    const uint32_t p = (uint32_t)p_raw;
+    float* qh = q + ((uint64_t)b * nh + head) * qd;
+    const float* kpe = comp + (uint64_t)b * (kv_lora + rope) + kv_lora;
+    const float* kvh = kv + ((uint64_t)b * nh + head) * (nope + vd);
+    float* K = cache_k + (((uint64_t)b * nh + head) * max_ctx + p) * qd;
+    float* V = cache_v + (((uint64_t)b * nh + head) * max_ctx + p) * vd;
+    for (uint32_t i = threadIdx.x; i < rope / 2; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)p * inv_freq[i], &sn, &cs);
+        sn *= mscale, cs *= mscale;
+        const float a = qh[nope + 2 * i], bb = qh[nope + 2 * i + 1];
+        qh[nope + 2 * i] = a * cs - bb * sn;
+        qh[nope + 2 * i + 1] = a * sn + bb * cs;
+        const float ka = kpe[2 * i], kb = kpe[2 * i + 1];
+        K[nope + 2 * i] = ka * cs - kb * sn;
+        K[nope + 2 * i + 1] = ka * sn + kb * cs;
+    }
+    for (uint32_t i = threadIdx.x; i < nope; i += blockDim.x) K[i] = kvh[i];
+    for (uint32_t i = threadIdx.x; i < vd; i += blockDim.x) V[i] = kvh[nope + i];
+}
+
+cudaError_t launch_mla_assemble(float* q, const float* comp, const float* kv, const int32_t* pos, uint32_t batch,
+                                uint32_t nh, uint32_t nope, uint32_t rope, uint32_t vd, uint32_t kv_lora, uint32_t max_ctx,
+                                const float* inv_freq, float mscale, float* cache_k, float* cache_v, int32_t* bad_pos,
+                                cudaStream_t s) {
+    cudaError_t e = launch_pdl(mla_assemble_kernel, dim3(nh, batch), 128, 0, s, q, comp, kv, pos, nh, nope, rope, vd,
+                               kv_lora, max_ctx, inv_freq, mscale, cache_k, cache_v, bad_pos);
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
 cudaError_t launch_attention_decode(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,
                                     uint32_t batch, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx, float* out,
-                                    float* scratch, int32_t* bad_pos, cudaStream_t s) {
+                                    float* scratch, int32_t* bad_pos, cudaStream_t s, uint32_t dv, float scale) {
+    if (dv == 0) dv = hd;
+    if (scale == 0.0f) scale = 1.0f / sqrtf((float)hd);
     uint32_t n_chunks = (max_ctx + ATT_CHUNK - 1) / ATT_CHUNK;
     size_t smem = (size_t)(hd + ATT_CHUNK) * 4;
     cudaError_t le3__ = launch_pdl(attention_partial_kernel, dim3(nq, n_chunks, batch), 128, smem, s, q, cache_k, cache_v, pos, nq, nkv, hd, max_ctx,
-                                                                          n_chunks, scratch, bad_pos);
+                                                                          n_chunks, scratch, bad_pos, dv, scale);
     if (le3__ != cudaSuccess) return le3__;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    cudaError_t le4__ = launch_pdl(attention_merge_kernel, batch * nq, 128, 0, s, scratch, hd, n_chunks, out);
+    cudaError_t le4__ = launch_pdl(attention_merge_kernel, batch * nq, 128, 0, s, scratch, dv, n_chunks, out);
     if (le4__ != cudaSuccess) return le4__;
     return cudaGetLastError();
 }

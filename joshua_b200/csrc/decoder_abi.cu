@@ -215,6 +215,40 @@ int32_t jq_attention_prefill_dev(const float* q, const float* cache_k, const flo
     return jq::OK;
 }
 
+int32_t jq_rmsnorm_strided_dev(const float* x, uint64_t x_stride, const float* weight, float eps, uint64_t rows,
+                               uint64_t hidden, float* out, void* stream) {
+    if (rows == 0) return jq::OK;
+    if (!x || !out || hidden == 0 || x_stride < hidden) return jq_fail(jq::E_INVALID, "jq_rmsnorm_strided_dev: bad argument");
+    JQ_CUDA(jq::launch_rmsnorm(x, nullptr, weight, eps, rows, (uint32_t)hidden, nullptr, out,
+                               static_cast<cudaStream_t>(stream), (uint32_t)x_stride));
+    return jq::OK;
+}
+
+int32_t jq_mla_assemble_dev(float* q, const float* comp, const float* kv, const int32_t* pos, uint32_t batch,
+                            uint32_t n_head, uint32_t qk_nope, uint32_t qk_rope, uint32_t v_dim, uint32_t kv_lora,
+                            uint32_t max_ctx, const float* inv_freq_dev, float mscale, float* cache_k, float* cache_v,
+                            int32_t* bad_pos_dev, void* stream) {
+    if (batch == 0) return jq::OK;
+    if (!q || !comp || !kv || !pos || !inv_freq_dev || !cache_k || !cache_v || n_head == 0 || qk_rope % 2)
+        return jq_fail(jq::E_INVALID, "jq_mla_assemble_dev: bad argument");
+    JQ_CUDA(jq::launch_mla_assemble(q, comp, kv, pos, batch, n_head, qk_nope, qk_rope, v_dim, kv_lora, max_ctx,
+                                    inv_freq_dev, mscale, cache_k, cache_v, bad_pos_dev,
+                                    static_cast<cudaStream_t>(stream)));
+    return jq::OK;
+}
+
+int32_t jq_attention_decode_qkv_dev(const float* q, const float* cache_k, const float* cache_v, const int32_t* pos,
+                                    uint32_t batch, uint32_t n_q, uint32_t n_kv, uint32_t qk_dim, uint32_t v_dim,
+                                    uint32_t max_ctx, float softmax_scale, float* out, float* scratch,
+                                    int32_t* bad_pos_dev, void* stream) {
+    if (batch == 0) return jq::OK;
+    if (!q || !cache_k || !cache_v || !pos || !out || !scratch || n_kv == 0 || n_q % n_kv || qk_dim == 0 || v_dim == 0)
+        return jq_fail(jq::E_INVALID, "jq_attention_decode_qkv_dev: bad argument");
+    JQ_CUDA(jq::launch_attention_decode(q, cache_k, cache_v, pos, batch, n_q, n_kv, qk_dim, max_ctx, out, scratch,
+                                        bad_pos_dev, static_cast<cudaStream_t>(stream), v_dim, softmax_scale));
+    return jq::OK;
+}
+
 int32_t jq_swiglu_dev(const float* gate, const float* up, uint64_t n, float clamp, float* out, void* stream) {
     if (n == 0) return jq::OK;
     if (!gate || !up || !out) return jq_fail(jq::E_INVALID, "jq_swiglu_dev: NULL buffer");

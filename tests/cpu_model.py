@@ -110,3 +110,76 @@ class CpuDecoder:
                 x = (x + y[0]).astype(F)
         self.pos += 1
         return self.linear("output", self.rms(x, self.out_norm), c.vocab, h)
+
+
+class CpuDeepseek:
+    """Mirror of `joshua_b200.deepseek.DeepseekDecoder` (one sequence, all experts on one rank): multi-head latent
+    attention as src/quantized_deepseek2.rs:422-504 (interleaved rotary embedding on the rope slices, per-head K / V
+    rebuilt for the new token and appended) and its routed experts + shared expert (:522-597)."""
+
+    def __init__(self, dec):
+        c = self.cfg = dec.cfg
+        self.wtype, self.etype = dec.wtype, dec.expert_type
+        self.raw = {name: t[:-16].cpu().numpy() for name, t in dec._raw.items()}
+        self.norms = [{k: ly[k].cpu().numpy() for k in ("attn_norm", "q_a_norm", "kv_a_norm", "ffn_norm")} for ly in dec.layers]
+        self.out_norm = dec.out_norm.cpu().numpy()
+        self.routers, self.biases = dec.routers, dec.biases
+        self.inv_freq, self.mscale, self.scale = dec.inv_freq.cpu().numpy(), dec.mscale, dec.softmax_scale
+        self.mcfg = oracle.moe_cfg(gating=1, n_expert=c.n_expert, n_used=c.n_used, hidden=c.hidden, inter=c.moe_inter,
+                                   n_group=c.n_group, topk_group=c.topk_group, norm=True, scale=c.weights_scale,
+                                   decode_path=True)
+        self.K = [np.zeros((c.n_head, 0, c.qd), F) for _ in range(c.layers)]
+        self.V = [np.zeros((c.n_head, 0, c.v_dim), F) for _ in range(c.layers)]
+        self.pos = 0
+        self.row_bytes = synth.tensor_bytes(self.wtype, 1, c.hidden)
+
+    def linear(self, name, x, n, k):
+        return oracle.matmul_t(self.wtype, (1, k, n), x.reshape(1, k), self.raw[name])[0]
+
+    @staticmethod
+    def rms(x, w, eps):
+        ss = F(np.sum(x * x, dtype=F))
+        return (x * F(1.0 / np.sqrt(ss / F(x.size) + F(eps))) * w).astype(F)
+
+    def rope_i(self, v, p):
+        """Interleaved pairs (2i, 2i + 1) of the last axis."""
+        ang = (F(p) * self.inv_freq).astype(F)
+        cs, sn = (np.cos(ang) * F(self.mscale)).astype(F), (np.sin(ang) * F(self.mscale)).astype(F)
+        a, b = v[..., 0::2], v[..., 1::2]
+        out = np.empty_like(v)
+        out[..., 0::2] = a * cs - b * sn
+        out[..., 1::2] = a * sn + b * cs
+        return out.astype(F)
+
+    def step(self, tok: int) -> np.ndarray:
+        c, p = self.cfg, self.pos
+        h, nh = c.hidden, c.n_head
+        row = self.raw["token_embd"][tok * self.row_bytes:(tok + 1) * self.row_bytes]
+        x = oracle.dequantize(self.wtype, row, two_step=True).astype(F)
+        for l in range(c.layers):
+            nm = self.norms[l]
+            xn = self.rms(x, nm["attn_norm"], c.eps)
+            qa = self.linear(f"l{l}.wq_a", xn, c.q_lora, h)
+            q = self.linear(f"l{l}.wq_b", self.rms(qa, nm["q_a_norm"], c.eps), nh * c.qd, c.q_lora).reshape(nh, c.qd).copy()
+            comp = self.linear(f"l{l}.wkv_a", xn, c.kv_lora + c.qk_rope, h)
+            kv = self.linear(f"l{l}.wkv_b", self.rms(comp[:c.kv_lora], nm["kv_a_norm"], c.eps),
+                             nh * (c.qk_nope + c.v_dim), c.kv_lora).reshape(nh, c.qk_nope + c.v_dim)
+            q[:, c.qk_nope:] = self.rope_i(q[:, c.qk_nope:], p)
+            k_pe = self.rope_i(comp[c.kv_lora:], p)
+            k_new = np.concatenate([kv[:, :c.qk_nope], np.broadcast_to(k_pe, (nh, c.qk_rope))], axis=1).astype(F)
+            self.K[l] = np.concatenate([self.K[l], k_new[:, None, :]], axis=1)
+            self.V[l] = np.concatenate([self.V[l], kv[:, None, c.qk_nope:]], axis=1)
+            att = np.einsum("hd,hcd->hc", q, self.K[l]).astype(F) * F(self.scale)
+            att = np.exp(att - att.max(axis=1, keepdims=True)).astype(F)
+            att = (att / att.sum(axis=1, keepdims=True, dtype=F)).astype(F)
+            a = np.einsum("hc,hcd->hd", att, self.V[l]).astype(F).reshape(-1)
+            x = (x + self.linear(f"l{l}.wo", a, h, nh * c.v_dim)).astype(F)
+            xn = self.rms(x, nm["ffn_norm"], c.eps).reshape(1, h)
+            logits = oracle.moe_logits(xn, self.routers[l])
+            ids, wts = oracle.moe_route(self.mcfg, logits, bias=self.biases[l])
+            y = oracle.moe_dispatch(self.mcfg, xn, ids, wts, [self.etype] * 3,
+                                    [self.raw[f"l{l}.experts{i}"] for i in range(3)], [self.wtype] * 3,
+                                    [self.raw[f"l{l}.sh_{n}"] for n in ("gate", "up", "down")])
+            x = (x + y[0]).astype(F)
+        self.pos += 1
+        return self.linear("output", self.rms(x, self.out_norm, c.eps), c.vocab, h)
