@@ -91,6 +91,31 @@ __device__ __forceinline__ uint32_t ld_u32(const uint8_t* p) {  // p 4-byte alig
 }
 __device__ __forceinline__ uint32_t ld_u16_bytes(const uint8_t* p) { return ld_u8(p) | (ld_u8(p + 1) << 8); }
 
+// Where a decoder's block bytes live: global memory (read-only path) or this CTA's shared memory.
+struct LdGlobal {
+    static __device__ __forceinline__ uint32_t u8(const uint8_t* p) { return ld_u8(p); }
+    static __device__ __forceinline__ uint32_t u16(const uint8_t* p) { return ld_u16(p); }
+    static __device__ __forceinline__ uint32_t u32(const uint8_t* p) { return ld_u32(p); }
+};
+struct LdShared {
+    static __device__ __forceinline__ uint32_t addr(const uint8_t* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+    static __device__ __forceinline__ uint32_t u8(const uint8_t* p) {
+        uint32_t v;
+        asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr(p)));
+        return v;
+    }
+    static __device__ __forceinline__ uint32_t u16(const uint8_t* p) {  // p 2-byte aligned
+        uint32_t v;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr(p)));
+        return v;
+    }
+    static __device__ __forceinline__ uint32_t u32(const uint8_t* p) {  // p 4-byte aligned
+        uint32_t v;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr(p)));
+        return v;
+    }
+};
+
 // The 8-bit sign pattern of a 7-bit IQ2_XXS sign index: bit 7 makes the
 // population count even (the reference's KSIGNS table, src/iq2xxs.rs:441-449).
 __device__ __forceinline__ uint32_t iq2_signs(uint32_t idx7) { return idx7 | ((__popc(idx7) & 1u) << 7); }
@@ -107,33 +132,33 @@ __device__ __forceinline__ float e2m1_value(uint32_t code) {
 // `row`.  `row` must be aligned to 2 bytes for Q8_0 / IQ2_XXS, 4 for Q2_K /
 // Q4_K; MXFP4 has no alignment.
 template <uint32_t TYPE>
-__device__ __forceinline__ void decode_unit(const uint8_t* row, uint32_t u, float w[8], bool two_step);
+__device__ __forceinline__ void decode_unit_generic(const uint8_t* row, uint32_t u, float w[8], bool two_step);
 
-template <>
-__device__ __forceinline__ void decode_unit<T_Q8_0>(const uint8_t* row, uint32_t u, float w[8], bool) {
+template <class LD>
+__device__ __forceinline__ void decode_q8_0(const uint8_t* row, uint32_t u, float w[8], bool) {
     const uint8_t* blk = row + (size_t)(u >> 2) * 34;
-    float d = f16_bits_to_f32(ld_u16(blk));
+    float d = f16_bits_to_f32(LD::u16(blk));
     const uint8_t* q = blk + 2 + 8 * (u & 3);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        uint32_t v = ld_u16(q + 2 * i);
+        uint32_t v = LD::u16(q + 2 * i);
         w[2 * i] = __fmul_rn((float)(int8_t)(v & 0xFF), d);
         w[2 * i + 1] = __fmul_rn((float)(int8_t)(v >> 8), d);
     }
 }
 
-template <>
-__device__ __forceinline__ void decode_unit<T_Q2_K>(const uint8_t* row, uint32_t u, float w[8], bool two_step) {
+template <class LD>
+__device__ __forceinline__ void decode_q2_k(const uint8_t* row, uint32_t u, float w[8], bool two_step) {
     const uint8_t* blk = row + (size_t)(u >> 5) * 84;
     uint32_t v0 = (u & 31) * 8;  // first value inside the block
     uint32_t sg = v0 >> 7, r = v0 & 127;
-    uint32_t sc = ld_u8(blk + sg * 8 + (r >> 4));
-    uint32_t dd = ld_u32(blk + 80);
+    uint32_t sc = LD::u8(blk + sg * 8 + (r >> 4));
+    uint32_t dd = LD::u32(blk + 80);
     float d1 = __fmul_rn(f16_bits_to_f32(dd & 0xFFFF), (float)(sc & 15));
     float m1 = __fmul_rn(f16_bits_to_f32(dd >> 16), (float)(sc >> 4));
     const uint8_t* q = blk + 16 + sg * 32 + (r & 31);
     uint32_t shift = 2 * (r >> 5);
-    uint32_t lo = ld_u32(q), hi = ld_u32(q + 4);
+    uint32_t lo = LD::u32(q), hi = LD::u32(q + 4);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         uint32_t word = i < 4 ? lo : hi;
@@ -142,29 +167,30 @@ __device__ __forceinline__ void decode_unit<T_Q2_K>(const uint8_t* row, uint32_t
     }
 }
 
+template <class LD>
 __device__ __forceinline__ void q4k_scale_min(const uint8_t* s, uint32_t j, uint32_t* sc, uint32_t* mn) {
     if (j < 4) {
-        *sc = ld_u8(s + j) & 63;
-        *mn = ld_u8(s + j + 4) & 63;
+        *sc = LD::u8(s + j) & 63;
+        *mn = LD::u8(s + j + 4) & 63;
     } else {
-        uint32_t a = ld_u8(s + j + 4), b = ld_u8(s + j - 4), c = ld_u8(s + j);
+        uint32_t a = LD::u8(s + j + 4), b = LD::u8(s + j - 4), c = LD::u8(s + j);
         *sc = (a & 0xF) | ((b >> 6) << 4);
         *mn = (a >> 4) | ((c >> 6) << 4);
     }
 }
 
-template <>
-__device__ __forceinline__ void decode_unit<T_Q4_K>(const uint8_t* row, uint32_t u, float w[8], bool two_step) {
+template <class LD>
+__device__ __forceinline__ void decode_q4_k(const uint8_t* row, uint32_t u, float w[8], bool two_step) {
     const uint8_t* blk = row + (size_t)(u >> 5) * 144;
     uint32_t pair = (u & 31) >> 2;  // 32-value group
     uint32_t sc, mn;
-    q4k_scale_min(blk + 4, pair, &sc, &mn);
-    uint32_t dd = ld_u32(blk);
+    q4k_scale_min<LD>(blk + 4, pair, &sc, &mn);
+    uint32_t dd = LD::u32(blk);
     float d1 = __fmul_rn(f16_bits_to_f32(dd & 0xFFFF), (float)sc);
     float m1 = __fmul_rn(f16_bits_to_f32(dd >> 16), (float)mn);
     const uint8_t* q = blk + 16 + 32 * (pair >> 1) + 8 * (u & 3);
     uint32_t shift = 4 * (pair & 1);
-    uint32_t lo = ld_u32(q), hi = ld_u32(q + 4);
+    uint32_t lo = LD::u32(q), hi = LD::u32(q + 4);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         uint32_t word = i < 4 ? lo : hi;
@@ -173,14 +199,14 @@ __device__ __forceinline__ void decode_unit<T_Q4_K>(const uint8_t* row, uint32_t
     }
 }
 
-template <>
-__device__ __forceinline__ void decode_unit<T_IQ2_XXS>(const uint8_t* row, uint32_t u, float w[8], bool) {
+template <class LD>
+__device__ __forceinline__ void decode_iq2_xxs(const uint8_t* row, uint32_t u, float w[8], bool) {
     const uint8_t* blk = row + (size_t)(u >> 5) * 66;
     uint32_t ib32 = (u & 31) >> 2, l = u & 3;
     const uint8_t* p = blk + 2 + ib32 * 8;
-    float d = f16_bits_to_f32(ld_u16(blk));
-    uint32_t code = ld_u8(p + l);
-    uint32_t hi = ld_u16(p + 4) | (ld_u16(p + 6) << 16);
+    float d = f16_bits_to_f32(LD::u16(blk));
+    uint32_t code = LD::u8(p + l);
+    uint32_t hi = LD::u16(p + 4) | (LD::u16(p + 6) << 16);
     float db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, (float)(hi >> 28))), 0.25f);
     uint32_t signs = iq2_signs((hi >> (7 * l)) & 127u);
     uint2 g = g_iq2xxs_grid[code];
@@ -193,17 +219,17 @@ __device__ __forceinline__ void decode_unit<T_IQ2_XXS>(const uint8_t* row, uint3
     }
 }
 
-template <>
-__device__ __forceinline__ void decode_unit<T_MXFP4>(const uint8_t* row, uint32_t u, float w[8], bool) {
+template <class LD>
+__device__ __forceinline__ void decode_mxfp4(const uint8_t* row, uint32_t u, float w[8], bool) {
     const uint8_t* blk = row + (size_t)(u >> 2) * 17;
-    uint32_t e = ld_u8(blk);
+    uint32_t e = LD::u8(blk);
     uint32_t part = u & 3;  // values 8*part .. 8*part+7 of the block
     const uint8_t* q = blk + 1 + 8 * (part & 1);
     uint32_t shift = 4 * (part >> 1);  // split-half: high nibbles hold values 16..31
     float scale = __uint_as_float(e == 0 ? 0x00400000u : e << 23);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        uint32_t code = (ld_u8(q + i) >> shift) & 15u;
+        uint32_t code = (LD::u8(q + i) >> shift) & 15u;
         w[i] = e == 0xFFu ? 0.0f : __fmul_rn(scale, e2m1_value(code));
     }
 }
@@ -216,7 +242,7 @@ __device__ __forceinline__ float ld_f16(const uint8_t* p) { return f16_bits_to_f
 
 // 32-value blocks with split halves: value j < 16 is the low nibble of byte j, value j + 16 the high nibble.
 template <>
-__device__ __forceinline__ void decode_unit<T_Q4_0>(const uint8_t* row, uint32_t u, float w[8], bool) {
+__device__ __forceinline__ void decode_unit_generic<T_Q4_0>(const uint8_t* row, uint32_t u, float w[8], bool) {
     const uint8_t* blk = row + (size_t)(u >> 2) * 18;
     const float d = ld_f16(blk);
     const uint32_t part = u & 3, shift = 4 * (part >> 1);
@@ -226,7 +252,7 @@ __device__ __forceinline__ void decode_unit<T_Q4_0>(const uint8_t* row, uint32_t
 }
 
 template <>
-__device__ __forceinline__ void decode_unit<T_Q4_1>(const uint8_t* row, uint32_t u, float w[8], bool) {
+__device__ __forceinline__ void decode_unit_generic<T_Q4_1>(const uint8_t* row, uint32_t u, float w[8], bool) {
     const uint8_t* blk = row + (size_t)(u >> 2) * 20;
     const float d = ld_f16(blk), m = ld_f16(blk + 2);
     const uint32_t part = u & 3, shift = 4 * (part >> 1);
@@ -242,7 +268,7 @@ __device__ __forceinline__ uint32_t q5_code(const uint8_t* qs, uint32_t qh, uint
 }
 
 template <>
-__device__ __forceinline__ void decode_unit<T_Q5_0>(const uint8_t* row, uint32_t u, float w[8], bool) {
+__device__ __forceinline__ void decode_unit_generic<T_Q5_0>(const uint8_t* row, uint32_t u, float w[8], bool) {
     const uint8_t* blk = row + (size_t)(u >> 2) * 22;
     const float d = ld_f16(blk);
     const uint32_t qh = ld_u8(blk + 2) | (ld_u8(blk + 3) << 8) | (ld_u8(blk + 4) << 16) | (ld_u8(blk + 5) << 24);
@@ -251,7 +277,7 @@ __device__ __forceinline__ void decode_unit<T_Q5_0>(const uint8_t* row, uint32_t
 }
 
 template <>
-__device__ __forceinline__ void decode_unit<T_Q5_1>(const uint8_t* row, uint32_t u, float w[8], bool) {
+__device__ __forceinline__ void decode_unit_generic<T_Q5_1>(const uint8_t* row, uint32_t u, float w[8], bool) {
     const uint8_t* blk = row + (size_t)(u >> 2) * 24;
     const float d = ld_f16(blk), m = ld_f16(blk + 2);
     const uint32_t qh = ld_u8(blk + 4) | (ld_u8(blk + 5) << 8) | (ld_u8(blk + 6) << 16) | (ld_u8(blk + 7) << 24);
@@ -260,7 +286,7 @@ __device__ __forceinline__ void decode_unit<T_Q5_1>(const uint8_t* row, uint32_t
 }
 
 template <>
-__device__ __forceinline__ void decode_unit<T_Q8_1>(const uint8_t* row, uint32_t u, float w[8], bool) {
+__device__ __forceinline__ void decode_unit_generic<T_Q8_1>(const uint8_t* row, uint32_t u, float w[8], bool) {
     const uint8_t* blk = row + (size_t)(u >> 2) * 36;  // f16 d, f16 s (unused by the decode), 32 int8
     const float d = ld_f16(blk);
 #pragma unroll
@@ -268,7 +294,7 @@ __device__ __forceinline__ void decode_unit<T_Q8_1>(const uint8_t* row, uint32_t
 }
 
 template <>
-__device__ __forceinline__ void decode_unit<T_Q8_K>(const uint8_t* row, uint32_t u, float w[8], bool) {
+__device__ __forceinline__ void decode_unit_generic<T_Q8_K>(const uint8_t* row, uint32_t u, float w[8], bool) {
     const uint8_t* blk = row + (size_t)(u >> 5) * 292;  // f32 d, 256 int8, 16 int16 block sums (unused)
     const float d = __uint_as_float(ld_u8(blk) | (ld_u8(blk + 1) << 8) | (ld_u8(blk + 2) << 16) | (ld_u8(blk + 3) << 24));
 #pragma unroll
@@ -285,7 +311,7 @@ __device__ __forceinline__ int q3k_scale(const uint8_t* s, uint32_t i) {  // six
 }
 
 template <>
-__device__ __forceinline__ void decode_unit<T_Q3_K>(const uint8_t* row, uint32_t u, float w[8], bool) {
+__device__ __forceinline__ void decode_unit_generic<T_Q3_K>(const uint8_t* row, uint32_t u, float w[8], bool) {
     const uint8_t* blk = row + (size_t)(u >> 5) * 110;
     const uint32_t v0 = (u & 31) * 8, half = v0 >> 7, j = (v0 & 127) >> 5, l0 = v0 & 31;
     const float dl = __fmul_rn(ld_f16(blk + 108), (float)q3k_scale(blk + 96, v0 >> 4));
@@ -300,11 +326,11 @@ __device__ __forceinline__ void decode_unit<T_Q3_K>(const uint8_t* row, uint32_t
 // Q5_K: f16 d | f16 dmin | scales[12] | qh[32] | qs[128].  As Q4_K with a fifth bit: group g (32 values) takes
 // bit g of qh[l].
 template <>
-__device__ __forceinline__ void decode_unit<T_Q5_K>(const uint8_t* row, uint32_t u, float w[8], bool) {
+__device__ __forceinline__ void decode_unit_generic<T_Q5_K>(const uint8_t* row, uint32_t u, float w[8], bool) {
     const uint8_t* blk = row + (size_t)(u >> 5) * 176;
     const uint32_t pair = (u & 31) >> 2, l0 = 8 * (u & 3);
     uint32_t sc, mn;
-    q4k_scale_min(blk + 4, pair, &sc, &mn);
+    q4k_scale_min<LdGlobal>(blk + 4, pair, &sc, &mn);
     const float d1 = __fmul_rn(ld_f16(blk), (float)sc), m1 = __fmul_rn(ld_f16(blk + 2), (float)mn);
     const uint8_t* q = blk + 48 + 32 * (pair >> 1) + l0;
     const uint32_t shift = 4 * (pair & 1);
@@ -319,7 +345,7 @@ __device__ __forceinline__ void decode_unit<T_Q5_K>(const uint8_t* row, uint32_t
 // low nibble from ql[64 half + 32 (part & 1) + l] (low for part < 2, high otherwise), two high bits
 // (qh[32 half + l] >> 2 part) & 3, minus 32; scale index v / 16.
 template <>
-__device__ __forceinline__ void decode_unit<T_Q6_K>(const uint8_t* row, uint32_t u, float w[8], bool) {
+__device__ __forceinline__ void decode_unit_generic<T_Q6_K>(const uint8_t* row, uint32_t u, float w[8], bool) {
     const uint8_t* blk = row + (size_t)(u >> 5) * 210;
     const uint32_t v0 = (u & 31) * 8, half = v0 >> 7, part = (v0 & 127) >> 5, l0 = v0 & 31;
     const float ds = __fmul_rn(ld_f16(blk + 208), (float)(int8_t)ld_u8(blk + 192 + (v0 >> 4)));
@@ -331,6 +357,17 @@ __device__ __forceinline__ void decode_unit<T_Q6_K>(const uint8_t* row, uint32_t
         const uint32_t code = ((ld_u8(ql + i) >> nshift) & 15u) | (((ld_u8(qh + i) >> (2 * part)) & 3u) << 4);
         w[i] = __fmul_rn(ds, (float)((int)code - 32));
     }
+}
+
+// One decoder per block type; LD says where the block bytes are read from.
+template <uint32_t TYPE, class LD = LdGlobal>
+__device__ __forceinline__ void decode_unit(const uint8_t* row, uint32_t u, float w[8], bool two_step) {
+    if constexpr (TYPE == T_Q8_0) decode_q8_0<LD>(row, u, w, two_step);
+    else if constexpr (TYPE == T_Q2_K) decode_q2_k<LD>(row, u, w, two_step);
+    else if constexpr (TYPE == T_Q4_K) decode_q4_k<LD>(row, u, w, two_step);
+    else if constexpr (TYPE == T_IQ2_XXS) decode_iq2_xxs<LD>(row, u, w, two_step);
+    else if constexpr (TYPE == T_MXFP4) decode_mxfp4<LD>(row, u, w, two_step);
+    else decode_unit_generic<TYPE>(row, u, w, two_step);
 }
 
 #endif  // __CUDACC__

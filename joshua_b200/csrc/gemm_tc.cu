@@ -183,7 +183,13 @@ __device__ __forceinline__ void store_split(uint8_t* hi_tile, uint8_t* lo_tile, 
     *reinterpret_cast<float4*>(lo_tile + off) = l;
 }
 
-template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE>
+// Elements of a row that one staged window of raw bytes covers: a whole number of blocks whose bytes are a
+// multiple of four (so the window moves as 32-bit words), a few K steps long.
+__host__ __device__ constexpr uint32_t window_elems(uint32_t type) {
+    return type == T_Q8_0 ? 128u : type == T_IQ2_XXS ? 512u : 256u;  // 136 / 132 / 144, 84, 136 bytes
+}
+
+template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE, bool STAGED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     gemm_tc_kernel(const uint8_t* __restrict__ w, uint64_t n, uint64_t k, const __grid_constant__ CUtensorMap map_hi,
                    const __grid_constant__ CUtensorMap map_lo, uint64_t m, float* __restrict__ dst, uint32_t n_stages,
@@ -201,20 +207,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     const uint64_t row0 = (uint64_t)blockIdx.x * TC_M;
     const uint64_t tok0 = (uint64_t)blockIdx.y * N_TILE;
     const uint32_t k_steps = (uint32_t)(k / TC_K);
-    // The converter warps can work in 1, 2 or 4 groups that take alternate K steps (more steps in flight, more
-    // units per thread).  Measured: no gain at 2 groups and a loss at 4 (m = 512: 0.30 -> 0.35 ms at 4096 x 4096,
-    // MXFP4 m = 4096: 0.91 -> 1.06 ms), because a step is bound by the converters' instruction throughput, not by
-    // the latency of one step's chain; with the weight decode switched off (JQ_DEBUG_TC_SKIP=1) a step takes
-    // 1.0 us against 2.2 us with it.  One group it is.
-    constexpr uint32_t n_groups = 1u;
     const uint32_t n_chunks = (k_steps + TC_CHUNK - 1) / TC_CHUNK;
     const uint64_t row_bytes = k / ELEMS * BYTES;
     constexpr uint32_t UPB = ELEMS / 8;
     constexpr uint32_t TMEM_COLS = 2 * N_TILE < 32 ? 32 : 2 * N_TILE;  // two accumulators; a power of two >= 32
+    // Converter mapping: warp w owns weight rows 8w .. 8w+7, lane l the unit l % 4 (8 of the step's 32 columns)
+    // of row 8w + l / 4, so a warp's loads touch 8 rows and its 16-byte stores to the swizzled tile fall on
+    // distinct banks.  Staged form: the warp copies its rows' raw bytes of one window of K (a few steps) to a
+    // private piece of shared memory as coalesced 32-bit asynchronous copies and decodes from there; only the
+    // warp itself reads what it copied, so no barrier beyond the warp is involved.  The copy of the next window
+    // starts as soon as the last step of the current one is decoded and lands while that step is stored and the
+    // accumulator drained.  Decoding straight from global memory (one L1 wavefront per row and load) remains
+    // for shapes whose rows are not word-aligned or whose k is not a whole number of windows.
+    constexpr uint32_t WIN_STEPS = window_elems(TYPE) / TC_K;              // K steps per window
+    constexpr uint32_t WIN_WORDS = window_elems(TYPE) / ELEMS * BYTES / 4;  // words per row and window
+    constexpr uint32_t WIN_STRIDE = WIN_WORDS | 1u;                         // padded row stride, words
+    constexpr uint32_t ROWS_PER_WARP = TC_M / TC_CONV_WARPS;                // 8
+    uint32_t* raw = reinterpret_cast<uint32_t*>(smem + (size_t)n_stages * STAGE);
 
     if (tid == 0) {
         for (uint32_t s = 0; s < n_stages; ++s) {
-            mbar_init(&full[s], TC_CONV_WARPS / n_groups + 1);  // a group's warps and the thread that starts the TMA copies
+            mbar_init(&full[s], TC_CONV_WARPS + 1);  // the converter warps and the thread that starts the TMA copies
             mbar_init(&empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -236,12 +249,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     const uint32_t tmem_d = tmem_base_slot;
 
     if (warp < TC_CONV_WARPS) {
-        // ── converters: per K step thread (r, unit) decodes 8 weights of row r and stores their two TF32 terms;
+        // ── converters: per K step a thread decodes 8 weights of its row and stores their two TF32 terms;
         // thread 0 also starts the TMA copies of the step's activation tiles.
         // Between chunks they read the finished accumulator back: warp w reads TMEM lanes 32 (w % 4) .. + 31
         // (its weight rows) and the quarter w / 4 of the columns (tokens). ──
-        const uint32_t tg = (TC_CONV_WARPS * 32) / n_groups;   // threads per group
-        const uint32_t sg = tid / tg, gt = tid - sg * tg;      // step group, thread inside it
+        const uint32_t r = warp * ROWS_PER_WARP + (lane >> 2), unit = lane & 3;  // this thread's row and unit
+        const uint64_t wrow = row0 + r < n ? row0 + r : n - 1;                  // rows past n repeat the last one
         const uint32_t q = warp & 3, grp = warp >> 2;
         constexpr int MY_COLS = N_TILE / 4;  // columns this thread accumulates
         float sums[MY_COLS];
@@ -279,26 +292,54 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         };
         bool ok = true;
         uint32_t drained = 0;
-        for (uint32_t ks = sg; ks < k_steps && ok; ks += n_groups) {
-            const uint32_t s = ks % n_stages, round = ks / n_stages;
-            // decode before waiting for the stage (the loads overlap the wait): the group's threads share the
-            // 128 rows x 4 units of the step, item = gt + i * tg -> (row item % 128, unit item / 128)
-            float v[4][8];
+        // copy this warp's rows of window wn: ROWS_PER_WARP x WIN_WORDS words, consecutive lanes consecutive words
+        uint32_t* my_raw = raw + warp * ROWS_PER_WARP * WIN_STRIDE;
+        auto copy_window = [&](uint32_t wn) {
+            const uint64_t gr0 = row0 + warp * ROWS_PER_WARP;
+            const uint32_t dst0 = smem_u32(my_raw) + lane * 4;
+#pragma unroll 1  // a real loop: unrolled, its eight row addresses would stay in registers across the K loop
+            for (uint32_t rr = 0; rr < ROWS_PER_WARP; ++rr) {
+                const uint64_t gr = gr0 + rr < n ? gr0 + rr : n - 1;
+                const uint8_t* src = w + gr * row_bytes + ((uint64_t)wn * WIN_WORDS + lane) * 4;
+                const uint32_t dst = dst0 + rr * (WIN_STRIDE * 4);
 #pragma unroll
-            for (uint32_t i = 0; i < 4; ++i) {
-                if (i < n_groups && !(dbg_skip & 1)) {
-                    const uint32_t item = gt + i * tg, r = item & 127, unit = item >> 7;
-                    const uint64_t wrow = row0 + r < n ? row0 + r : n - 1;
+                for (uint32_t c = 0; c < WIN_WORDS; c += 32) {
+                    if (c + lane < WIN_WORDS)
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + c * 4), "l"(src + c * 4) : "memory");
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        const uint32_t n_windows = k_steps / WIN_STEPS;
+        if constexpr (STAGED) copy_window(0);
+        for (uint32_t ks = 0; ks < k_steps && ok; ++ks) {
+            const uint32_t s = ks % n_stages, round = ks / n_stages;
+            const uint32_t wn = ks / WIN_STEPS, wj = ks - wn * WIN_STEPS;
+            // decode before waiting for the stage (the loads overlap the wait)
+            float v[8];
+            if (!(dbg_skip & 1)) {
+                if constexpr (STAGED) {
+                    if (wj == 0) {
+                        asm volatile("cp.async.wait_group 0;" ::: "memory");
+                        __syncwarp();
+                    }
+                    decode_unit<TYPE, LdShared>(reinterpret_cast<const uint8_t*>(raw + r * WIN_STRIDE), wj * 4 + unit, v,
+                                                false);
+                    if (wj == WIN_STEPS - 1 && wn + 1 < n_windows) {
+                        __syncwarp();  // every lane has its last bytes of the window in registers
+                        copy_window(wn + 1);
+                    }
+                } else {
                     const uint32_t u = ks * 4 + unit;  // 8-value unit of the row
-                    decode_unit<TYPE>(w + wrow * row_bytes + (uint64_t)(u / UPB) * BYTES, u % UPB, v[i], false);
+                    decode_unit<TYPE>(w + wrow * row_bytes + (uint64_t)(u / UPB) * BYTES, u % UPB, v, false);
                 }
             }
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(&empty[s], (round & 1) ^ 1));  // warp-uniform
             if (!ok) break;
-            const bool tr = trace != nullptr && gt == 0 && blockIdx.x == 0 && blockIdx.y == 0 && ks < 64;
+            const bool tr = trace != nullptr && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && ks < 64;
             if (tr) trace[4 * ks] = tc_now();
             uint8_t* st = smem + (size_t)s * STAGE;
-            if (gt == 0) {
+            if (tid == 0) {
                 // the stage is free: start the two activation tiles (hi, lo) of this K step on their way
                 if (dbg_skip & 2) {
                     mbar_arrive(&full[s]);
@@ -308,13 +349,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     tma_load_2d(st + 2 * PLANE_A + PLANE_B, &map_lo, ks * TC_K, (uint32_t)tok0, &full[s]);
                 }
             }
-#pragma unroll
-            for (uint32_t i = 0; i < 4; ++i) {
-                if (i < n_groups && !(dbg_skip & 1)) {
-                    const uint32_t item = gt + i * tg, r = item & 127, unit = item >> 7;
-                    store_split(st, st + PLANE_A, r, unit * 2, v[i]);
-                    store_split(st, st + PLANE_A, r, unit * 2 + 1, v[i] + 4);
-                }
+            if (!(dbg_skip & 1)) {
+                store_split(st, st + PLANE_A, r, unit * 2, v);
+                store_split(st, st + PLANE_A, r, unit * 2 + 1, v + 4);
             }
             // make the generic-proxy stores visible to the tensor core's async proxy, then hand over
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -406,13 +443,14 @@ cudaError_t tensor_map_for(const float* base, uint64_t m, uint64_t k, uint32_t n
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE>
+template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE, bool STAGED>
 cudaError_t launch_tile(const uint8_t* w, uint64_t n, uint64_t k, const float* x_hi, const float* x_lo, uint64_t m,
                         float* dst, int* error_flag, cudaStream_t s) {
     constexpr uint32_t STAGE = 2 * PLANE_A + 2 * N_TILE * 128;
-    uint32_t n_stages = std::min<uint32_t>(8, std::min<uint32_t>((uint32_t)(k / TC_K), (216 * 1024) / STAGE));
-    size_t smem = (size_t)n_stages * STAGE + 1024;
-    auto kern = gemm_tc_kernel<TYPE, ELEMS, BYTES, N_TILE>;
+    constexpr uint32_t RAW = STAGED ? TC_M * ((window_elems(TYPE) / ELEMS * BYTES / 4) | 1u) * 4 : 0;  // staged window
+    uint32_t n_stages = std::min<uint32_t>(8, std::min<uint32_t>((uint32_t)(k / TC_K), (216 * 1024 - RAW) / STAGE));
+    size_t smem = (size_t)n_stages * STAGE + RAW + 1024;
+    auto kern = gemm_tc_kernel<TYPE, ELEMS, BYTES, N_TILE, STAGED>;
     static bool configured[MAX_DEVICES] = {};
     if (cudaError_t ce = set_max_smem_once(kern, 226 * 1024, configured); ce != cudaSuccess) return ce;
     CUtensorMap map_hi, map_lo;
@@ -430,22 +468,32 @@ cudaError_t launch_tile(const uint8_t* w, uint64_t n, uint64_t k, const float* x
     return cudaGetLastError();
 }
 
-template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES>
-cudaError_t launch_type(const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m, float* dst,
-                        float* scratch, int* error_flag, cudaStream_t s) {
+template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, bool STAGED>
+cudaError_t launch_staged(const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m, float* dst,
+                          float* scratch, int* error_flag, cudaStream_t s) {
     // split the activations once: hi and lo arrays of m * k floats each
     float* x_hi = scratch;
     float* x_lo = scratch + ((m * k + 63) & ~(uint64_t)63);
     const uint64_t n4 = m * k / 4;
     split_tf32_kernel<<<(unsigned)std::min<uint64_t>((n4 + 255) / 256, 148 * 16), 256, 0, s>>>(lhs, n4, x_hi, x_lo);
     if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
-    if (m <= 32) return launch_tile<TYPE, ELEMS, BYTES, 32>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
-    if (m <= 64) return launch_tile<TYPE, ELEMS, BYTES, 64>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
-    if (m <= 128) return launch_tile<TYPE, ELEMS, BYTES, 128>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+    if (m <= 32) return launch_tile<TYPE, ELEMS, BYTES, 32, STAGED>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+    if (m <= 64) return launch_tile<TYPE, ELEMS, BYTES, 64, STAGED>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+    if (m <= 128) return launch_tile<TYPE, ELEMS, BYTES, 128, STAGED>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
     // 256-token tiles decode every weight half as often, but only pay off once they still fill the SMs
     const uint64_t ctas256 = ((n + TC_M - 1) / TC_M) * ((m + 255) / 256);
-    if (ctas256 < 148) return launch_tile<TYPE, ELEMS, BYTES, 128>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
-    return launch_tile<TYPE, ELEMS, BYTES, 256>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+    if (ctas256 < 148) return launch_tile<TYPE, ELEMS, BYTES, 128, STAGED>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+    return launch_tile<TYPE, ELEMS, BYTES, 256, STAGED>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+}
+
+// The staged form needs word-aligned rows and k a whole number of windows.
+template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES>
+cudaError_t launch_type(const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m, float* dst,
+                        float* scratch, int* error_flag, cudaStream_t s) {
+    const uint64_t row_bytes = k / ELEMS * BYTES;
+    const bool staged = reinterpret_cast<uintptr_t>(w) % 4 == 0 && row_bytes % 4 == 0 && k % window_elems(TYPE) == 0;
+    if (staged) return launch_staged<TYPE, ELEMS, BYTES, true>(w, n, k, lhs, m, dst, scratch, error_flag, s);
+    return launch_staged<TYPE, ELEMS, BYTES, false>(w, n, k, lhs, m, dst, scratch, error_flag, s);
 }
 
 }  // namespace
