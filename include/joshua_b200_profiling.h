@@ -11,9 +11,9 @@
 extern "C" {
 #endif
 
-/* Profiling aid: with a device buffer of 256 uint64, CTA (0, 0) of the tile GEMM stores four GPU nanosecond
- * timestamps per K step for its first 64 steps (stage free, stage handed over, operands complete, MMAs
- * issued); NULL = off. */
+/* Profiling aid: with a device buffer of 512 uint64, CTA (0, 0) of the tile GEMM stores eight SM-cycle stamps
+ * per K step for its first 64 steps (converter thread 0: stage free, stage handed over; issuing thread: top of
+ * the step, accumulator half free, operands complete, MMAs issued, stage commit issued, end); NULL = off. */
 int32_t jq_debug_gemm_trace(uint64_t* trace_dev);
 
 /* Profiling aid: with a device buffer of 8 uint64 the last CTA of the decode router kernel stores the GPU

@@ -54,6 +54,17 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     uint32_t addr = smem_u32(bar);
+    {  // the phase usually is complete already: the non-blocking test answers faster than a try_wait
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
     for (uint32_t it = 0; it < (1u << 24); ++it) {
         uint32_t done;
         asm volatile(
@@ -67,14 +78,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     }
     return false;
 }
+// The same wait for warps that have nothing else to do: the thread may stay suspended up to `hint_ns` per try
+// (it resumes at once when the phase completes), so a waiting warp does not compete for issue slots with the
+// warp that feeds the tensor core.  The number of tries still is bounded.
+__device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < (1u << 20); ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity), "r"(hint_ns)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
 
 __device__ __forceinline__ unsigned long long tc_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
+    return (unsigned long long)clock64();  // SM cycles: both traced threads run on the same SM
 }
-// Profiling aid (jq_debug_gemm_trace): CTA (0, 0) stores four timestamps per K step for its first 64 steps:
-// stage free (converter), stage handed over (converter), operands complete (issuer), MMAs issued (issuer).
+// Profiling aid (jq_debug_gemm_trace, a buffer of 512 values): CTA (0, 0) stores eight SM-cycle stamps per K step
+// for its first 64 steps.  Converter thread 0: [0] stage free, [1] stage handed over.  Issuer: [2] top of the
+// step, [3] accumulator half free, [4] operands complete, [5] MMAs issued, [6] stage commit issued, [7] end.
 unsigned long long* g_gemm_trace = nullptr;
 
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
@@ -130,6 +158,16 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint
         "}\n" ::"r"(tmem_d),
         "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
         : "memory");
+}
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -263,7 +301,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         // read chunk `c`'s accumulator and add it to the running sums
         auto drain = [&](uint32_t c) -> bool {
             const uint32_t buf = c & 1;
-            if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[buf], (c >> 1) & 1))) return false;
+            if (!__all_sync(0xFFFFFFFFu, (dbg_skip & 8) ? mbar_wait_idle(&acc_full[buf], (c >> 1) & 1, 20000)
+                                                         : mbar_wait(&acc_full[buf], (c >> 1) & 1)))
+                return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tmem_d + ((q * 32) << 16) + buf * N_TILE + grp * MY_COLS;
             if constexpr (MY_COLS == 8) {
@@ -334,10 +374,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     decode_unit<TYPE>(w + wrow * row_bytes + (uint64_t)(u / UPB) * BYTES, u % UPB, v, false);
                 }
             }
-            ok = __all_sync(0xFFFFFFFFu, mbar_wait(&empty[s], (round & 1) ^ 1));  // warp-uniform
+            ok = __all_sync(0xFFFFFFFFu, (dbg_skip & 8) ? mbar_wait_idle(&empty[s], (round & 1) ^ 1, 20000)
+                                                            : mbar_wait(&empty[s], (round & 1) ^ 1));  // warp-uniform
             if (!ok) break;
             const bool tr = trace != nullptr && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && ks < 64;
-            if (tr) trace[4 * ks] = tc_now();
+            if (tr) trace[8 * ks] = tc_now();
             uint8_t* st = smem + (size_t)s * STAGE;
             if (tid == 0) {
                 // the stage is free: start the two activation tiles (hi, lo) of this K step on their way
@@ -357,7 +398,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&full[s]);
-            if (tr) trace[4 * ks + 1] = tc_now();
+            if (tr) trace[8 * ks + 1] = tc_now();
             // drain every finished chunk but the newest (which is still accumulating)
             while (ok && drained + 1 < (ks + 1) / TC_CHUNK) ok = drain(drained++);
         }
@@ -372,29 +413,33 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             }
         }
     } else {
-        // ── issuer: one thread feeds the tensor core ──
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc(N_TILE);
-            const uint32_t base0 = smem_u32(smem);
-            const uint64_t d0_a_hi = umma_desc(base0), d0_a_lo = umma_desc(base0 + PLANE_A);
-            const uint64_t d0_b_hi = umma_desc(base0 + 2 * PLANE_A), d0_b_lo = umma_desc(base0 + 2 * PLANE_A + PLANE_B);
-            bool ok = true;
-            for (uint32_t ks = 0; ks < k_steps && ok; ++ks) {
-                const uint32_t s = ks % n_stages, round = ks / n_stages;
-                const uint32_t chunk = ks / TC_CHUNK, buf = chunk & 1;
-                if (ks % TC_CHUNK == 0 && chunk >= 2) {
-                    // the accumulator half must have been read back before it is overwritten
-                    ok = mbar_wait(&acc_empty[buf], ((chunk >> 1) - 1) & 1);
-                    if (!ok) break;
-                }
-                ok = mbar_wait(&full[s], round & 1);
+        // ── issuer: the whole warp walks the K steps and waits on the barriers (warp-uniform control flow); one
+        // elected lane issues the tensor-core instructions and their commits ──
+        const uint32_t idesc = umma_idesc(N_TILE);
+        const uint32_t base0 = smem_u32(smem);
+        const uint64_t d0_a_hi = umma_desc(base0), d0_a_lo = umma_desc(base0 + PLANE_A);
+        const uint64_t d0_b_hi = umma_desc(base0 + 2 * PLANE_A), d0_b_lo = umma_desc(base0 + 2 * PLANE_A + PLANE_B);
+        bool ok = true;
+        uint32_t s = 0, round = 0;  // stage and its use count, stepped without a division
+        for (uint32_t ks = 0; ks < k_steps && ok; ++ks) {
+            const uint32_t chunk = ks / TC_CHUNK, buf = chunk & 1;
+            const bool tr = trace != nullptr && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && ks < 64;
+            if (tr) trace[8 * ks + 2] = tc_now();
+            if (ks % TC_CHUNK == 0 && chunk >= 2) {
+                // the accumulator half must have been read back before it is overwritten
+                ok = __all_sync(0xFFFFFFFFu, mbar_wait(&acc_empty[buf], ((chunk >> 1) - 1) & 1));
                 if (!ok) break;
-                const bool tr = trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && ks < 64;
-                if (tr) trace[4 * ks + 2] = tc_now();
+                // orders the MMAs below after the converters' reads of this half of tensor memory; the
+                // shared-memory operands need no tensor-core fence (proxy fence + mbarrier)
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            if (tr) trace[8 * ks + 3] = tc_now();
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(&full[s], round & 1));
+            if (!ok) break;
+            if (tr) trace[8 * ks + 4] = tc_now();
+            if (elect_one()) {
                 // descriptors differ from the stage-0 ones only in the start-address field (bytes / 16, no carry
-                // out of its 14 bits below 256 KB): one add each instead of rebuilding them, the issuing thread's
-                // own instruction latency being what bounds a K step once the operands are there
+                // out of its 14 bits below 256 KB): one add each instead of rebuilding them
                 const uint64_t so = (uint64_t)s * (STAGE >> 4);
                 const uint64_t da_hi = d0_a_hi + so, da_lo = d0_a_lo + so, db_hi = d0_b_hi + so, db_lo = d0_b_lo + so;
                 const uint32_t d = tmem_d + buf * N_TILE;
@@ -403,16 +448,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     // one instruction covers K = 8 tf32 = 32 bytes of the swizzled row
                     const uint64_t adv = kk * 2;
                     umma_tf32(d, da_hi + adv, db_hi + adv, idesc, (ks % TC_CHUNK != 0) || kk != 0);
+                    if (dbg_skip & 4) continue;  // measurement only: one product of the three
                     umma_tf32(d, da_hi + adv, db_lo + adv, idesc, 1);
                     umma_tf32(d, da_lo + adv, db_hi + adv, idesc, 1);
                 }
+                if (tr) trace[8 * ks + 5] = tc_now();
                 umma_commit(&empty[s]);  // arrives when the instructions above have finished reading the stage
-                if (tr) trace[4 * ks + 3] = tc_now();
+                if (tr) trace[8 * ks + 6] = tc_now();
                 if ((ks + 1) % TC_CHUNK == 0 || ks + 1 == k_steps) umma_commit(&acc_full[buf]);
             }
-            if (!ok) abort_flag = 1;
+            __syncwarp();
+            if (tr) trace[8 * ks + 7] = tc_now();
+            if (++s == n_stages) {
+                s = 0;
+                ++round;
+            }
         }
-        __syncwarp();
+        if (!ok && lane == 0) abort_flag = 1;
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -458,7 +510,8 @@ cudaError_t launch_tile(const uint8_t* w, uint64_t n, uint64_t k, const float* x
     if (e == cudaSuccess) e = tensor_map_for(x_lo, m, k, N_TILE, &map_lo);
     if (e != cudaSuccess) return e;
     dim3 grid((unsigned)((n + TC_M - 1) / TC_M), (unsigned)((m + N_TILE - 1) / N_TILE));
-    // JQ_DEBUG_TC_SKIP (measurement only, results are wrong): bit 0 = no weight decode / stores, bit 1 = no TMA
+    // JQ_DEBUG_TC_SKIP (measurement only, results are wrong): bit 0 = no weight decode / stores, bit 1 = no TMA,
+    // bit 2 = one tensor-core product instead of three
 #ifdef JQ_PROFILING
     static const int dbg_skip = std::getenv("JQ_DEBUG_TC_SKIP") ? std::atoi(std::getenv("JQ_DEBUG_TC_SKIP")) : 0;
 #else
