@@ -1,26 +1,26 @@
 // Prefill / batched matmul (m > 8) over raw GGUF blocks on the 5th-generation tensor cores.
 //
 // dst[m, n] = lhs[m, k] . W[n, k]^T with W left in its GGUF bytes.  A CTA owns a 128-row tile of W and a tile
-// of up to 256 activation rows (the wider the tile, the fewer times a weight is decoded).  Per 32-column K step its converter warps decode the 128 x 32 weight block to
-// the exact f32 weights the reference forms (formats.cuh), split weights and activations into two TF32 terms
-// (hi = top 11 significant bits, lo = the exact remainder), and store both terms K-major in the 128-byte
-// swizzled layout the tensor core reads.  One thread issues tcgen05.mma (kind::tf32) for the three
-// significant products hi*hi + hi*lo + lo*hi into a 128 x N f32 accumulator in tensor memory; each product is
-// exact and the split carries ~2^-22 relative error per term.  The tensor core adds into its f32 accumulator
-// with truncation, an error that grows linearly with the number of accumulated instructions, so the
-// accumulator only ever holds TC_CHUNK K steps (128 columns): the converter warps read each finished chunk
-// back with tcgen05.ld and add it, round-to-nearest, to running sums in registers while the next chunk
-// accumulates in the other half of tensor memory.  The result then matches f32 accumulation
-// (src/kquant_dot.rs:268-483) to the tolerance the path is held to.
+// of up to 128 activation rows.  Per 32-column K step its converter warps decode the 128 x 32 weight block to
+// the exact f32 weights the reference forms (formats.cuh) and split them into two TF32 terms (hi = top 11
+// significant bits, lo = the exact remainder); the activations are split the same way once per launch by a
+// small kernel (two f32 arrays) and reach shared memory by TMA (`cp.async.bulk.tensor.2d`, 128-byte swizzle).
+// One thread issues tcgen05.mma (kind::tf32) for the three significant products hi*hi + hi*lo + lo*hi into a
+// 128 x N f32 accumulator in tensor memory; each product is exact and the split carries ~2^-22 relative error
+// per term.  The tensor core adds into its f32 accumulator with truncation, an error that grows linearly with
+// the number of accumulated instructions, so the accumulator only ever holds a chunk of 4 K steps (128
+// columns): the converter warps read each finished chunk back with tcgen05.ld and add it, round-to-nearest, to
+// running sums in registers while the next chunk accumulates in the other half of tensor memory.  The result
+// then matches f32 accumulation (src/kquant_dot.rs:268-483) to the tolerance the path is held to.
 //
-// The activations are split once per launch by a small kernel (two f32 arrays, hi and lo) and reach shared
-// memory by TMA (`cp.async.bulk.tensor.2d`, 128-byte swizzle) without passing through the converter warps or
-// the L1 cache, which the weight decode then has to itself.
+// Two forms.  `gemm_ts_kernel` (the usual one): raw weight bytes are staged in shared memory by asynchronous
+// copies, the weight terms go to tensor memory (tcgen05.st) and are the MMA's A operand from there, so shared
+// memory carries only the activation tiles.  `gemm_tc_kernel`: weights decoded straight from global memory into
+// swizzled shared-memory tiles; it takes the shapes the first does not (rows not word-aligned, k not a whole
+// number of staged windows).
 //
-// Pipeline: NS shared-memory stages, each guarded by a `full` mbarrier (converters -> issuer, after a
-// generic-to-async proxy fence) and an `empty` mbarrier (tcgen05.commit -> converters).  Every wait is
-// bounded; a wait that runs out raises the device status flag, and every thread still reaches the common
-// exit where tensor memory is released.
+// Every wait on an mbarrier is bounded; a wait that runs out raises the device status flag, and every thread
+// still reaches the common exit where tensor memory is released.
 //
 // Tensor-pipe bound for large m: 3 x 2*m*n*k TF32 flops per launch.  Algorithmic flops: 2*m*n*k.
 #include <algorithm>
@@ -78,25 +78,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     }
     return false;
 }
-// The same wait for warps that have nothing else to do: the thread may stay suspended up to `hint_ns` per try
-// (it resumes at once when the phase completes), so a waiting warp does not compete for issue slots with the
-// warp that feeds the tensor core.  The number of tries still is bounded.
-__device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
-    uint32_t addr = smem_u32(bar);
-    for (uint32_t it = 0; it < (1u << 20); ++it) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(addr), "r"(parity), "r"(hint_ns)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-
 __device__ __forceinline__ unsigned long long tc_now() {
     return (unsigned long long)clock64();  // SM cycles: both traced threads run on the same SM
 }
@@ -224,10 +205,10 @@ __device__ __forceinline__ void store_split(uint8_t* hi_tile, uint8_t* lo_tile, 
 // Elements of a row that one staged window of raw bytes covers: a whole number of blocks whose bytes are a
 // multiple of four (so the window moves as 32-bit words), a few K steps long.
 __host__ __device__ constexpr uint32_t window_elems(uint32_t type) {
-    return type == T_Q8_0 ? 128u : type == T_IQ2_XXS ? 512u : 256u;  // 136 / 132 / 144, 84, 136 bytes
+    return type == T_IQ2_XXS ? 512u : 256u;  // 132 bytes / 272, 144, 84, 136 bytes
 }
 
-template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE, bool STAGED>
+template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     gemm_tc_kernel(const uint8_t* __restrict__ w, uint64_t n, uint64_t k, const __grid_constant__ CUtensorMap map_hi,
                    const __grid_constant__ CUtensorMap map_lo, uint64_t m, float* __restrict__ dst, uint32_t n_stages,
@@ -250,18 +231,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     constexpr uint32_t UPB = ELEMS / 8;
     constexpr uint32_t TMEM_COLS = 2 * N_TILE < 32 ? 32 : 2 * N_TILE;  // two accumulators; a power of two >= 32
     // Converter mapping: warp w owns weight rows 8w .. 8w+7, lane l the unit l % 4 (8 of the step's 32 columns)
-    // of row 8w + l / 4, so a warp's loads touch 8 rows and its 16-byte stores to the swizzled tile fall on
-    // distinct banks.  Staged form: the warp copies its rows' raw bytes of one window of K (a few steps) to a
-    // private piece of shared memory as coalesced 32-bit asynchronous copies and decodes from there; only the
-    // warp itself reads what it copied, so no barrier beyond the warp is involved.  The copy of the next window
-    // starts as soon as the last step of the current one is decoded and lands while that step is stored and the
-    // accumulator drained.  Decoding straight from global memory (one L1 wavefront per row and load) remains
-    // for shapes whose rows are not word-aligned or whose k is not a whole number of windows.
-    constexpr uint32_t WIN_STEPS = window_elems(TYPE) / TC_K;              // K steps per window
-    constexpr uint32_t WIN_WORDS = window_elems(TYPE) / ELEMS * BYTES / 4;  // words per row and window
-    constexpr uint32_t WIN_STRIDE = WIN_WORDS | 1u;                         // padded row stride, words
+    // of row 8w + l / 4, so a warp's loads touch 8 rows (8 L1 wavefronts per load, not 32) and its 16-byte
+    // stores to the swizzled tile fall on distinct banks.  The decode reads global memory directly: this form
+    // serves the shapes the tensor-memory form below does not take (rows that are not word-aligned, k not a
+    // whole number of its windows).
     constexpr uint32_t ROWS_PER_WARP = TC_M / TC_CONV_WARPS;                // 8
-    uint32_t* raw = reinterpret_cast<uint32_t*>(smem + (size_t)n_stages * STAGE);
 
     if (tid == 0) {
         for (uint32_t s = 0; s < n_stages; ++s) {
@@ -301,9 +275,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         // read chunk `c`'s accumulator and add it to the running sums
         auto drain = [&](uint32_t c) -> bool {
             const uint32_t buf = c & 1;
-            if (!__all_sync(0xFFFFFFFFu, (dbg_skip & 8) ? mbar_wait_idle(&acc_full[buf], (c >> 1) & 1, 20000)
-                                                         : mbar_wait(&acc_full[buf], (c >> 1) & 1)))
-                return false;
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[buf], (c >> 1) & 1))) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr = tmem_d + ((q * 32) << 16) + buf * N_TILE + grp * MY_COLS;
             if constexpr (MY_COLS == 8) {
@@ -332,50 +304,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         };
         bool ok = true;
         uint32_t drained = 0;
-        // copy this warp's rows of window wn: ROWS_PER_WARP x WIN_WORDS words, consecutive lanes consecutive words
-        uint32_t* my_raw = raw + warp * ROWS_PER_WARP * WIN_STRIDE;
-        auto copy_window = [&](uint32_t wn) {
-            const uint64_t gr0 = row0 + warp * ROWS_PER_WARP;
-            const uint32_t dst0 = smem_u32(my_raw) + lane * 4;
-#pragma unroll 1  // a real loop: unrolled, its eight row addresses would stay in registers across the K loop
-            for (uint32_t rr = 0; rr < ROWS_PER_WARP; ++rr) {
-                const uint64_t gr = gr0 + rr < n ? gr0 + rr : n - 1;
-                const uint8_t* src = w + gr * row_bytes + ((uint64_t)wn * WIN_WORDS + lane) * 4;
-                const uint32_t dst = dst0 + rr * (WIN_STRIDE * 4);
-#pragma unroll
-                for (uint32_t c = 0; c < WIN_WORDS; c += 32) {
-                    if (c + lane < WIN_WORDS)
-                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + c * 4), "l"(src + c * 4) : "memory");
-                }
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        };
-        const uint32_t n_windows = k_steps / WIN_STEPS;
-        if constexpr (STAGED) copy_window(0);
         for (uint32_t ks = 0; ks < k_steps && ok; ++ks) {
             const uint32_t s = ks % n_stages, round = ks / n_stages;
-            const uint32_t wn = ks / WIN_STEPS, wj = ks - wn * WIN_STEPS;
             // decode before waiting for the stage (the loads overlap the wait)
             float v[8];
             if (!(dbg_skip & 1)) {
-                if constexpr (STAGED) {
-                    if (wj == 0) {
-                        asm volatile("cp.async.wait_group 0;" ::: "memory");
-                        __syncwarp();
-                    }
-                    decode_unit<TYPE, LdShared>(reinterpret_cast<const uint8_t*>(raw + r * WIN_STRIDE), wj * 4 + unit, v,
-                                                false);
-                    if (wj == WIN_STEPS - 1 && wn + 1 < n_windows) {
-                        __syncwarp();  // every lane has its last bytes of the window in registers
-                        copy_window(wn + 1);
-                    }
-                } else {
-                    const uint32_t u = ks * 4 + unit;  // 8-value unit of the row
-                    decode_unit<TYPE>(w + wrow * row_bytes + (uint64_t)(u / UPB) * BYTES, u % UPB, v, false);
-                }
+                const uint32_t u = ks * 4 + unit;  // 8-value unit of the row
+                decode_unit<TYPE>(w + wrow * row_bytes + (uint64_t)(u / UPB) * BYTES, u % UPB, v, false);
             }
-            ok = __all_sync(0xFFFFFFFFu, (dbg_skip & 8) ? mbar_wait_idle(&empty[s], (round & 1) ^ 1, 20000)
-                                                            : mbar_wait(&empty[s], (round & 1) ^ 1));  // warp-uniform
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(&empty[s], (round & 1) ^ 1));  // warp-uniform
             if (!ok) break;
             const bool tr = trace != nullptr && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && ks < 64;
             if (tr) trace[8 * ks] = tc_now();
@@ -474,6 +411,276 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
 }
 
+
+// ───────────────────────────── weights through tensor memory ─────────────────────────────
+//
+// Second form of the tile GEMM, the one launched whenever the staged decode applies.  The weight tile's two
+// TF32 terms do not pass through shared memory at all: the converter warps write them with tcgen05.st into
+// tensor memory and the tensor core reads its A operand from there, so that shared memory carries only the
+// activation tiles (TMA in, MMA out).  At a 128-token tile that halves the shared-memory bytes a K step moves
+// (the first form's bound: 96 KB of operand reads + 64 KB of tile writes per step against 128 bytes per clock).
+//
+// Tensor memory, 512 columns: [0, 2N) two accumulators (a chunk of TS_CHUNK steps each), then four stages of 64
+// columns: the step's 32 hi terms and 32 lo terms, weight row r in lane r.  The activation ring in shared memory
+// has the same four stages, so a step has one `full` and one `empty` barrier and the issuing thread one wait
+// and one commit per step (its own instruction latency is what a step costs once the operands keep up).
+//
+// Warps: 16 converters, warp (q = w % 4, g = w / 4) owns lanes / weight rows 32q .. 32q+31 (the lanes its
+// tcgen05.st and tcgen05.ld may touch) and the K steps ks = g (mod 4): it decodes all 32 columns of the step for
+// its rows, so four steps are in flight across the warps of a quarter.  The four warps of a quarter share one
+// staged window of raw bytes (copied 8 rows each) and hand it over through a pair of bounded mbarriers.  Warp
+// 16 issues the MMAs, warp 17 the TMA copies of the activation tiles.
+constexpr int TS_CHUNK = 4;
+constexpr int TS_PHASES = 4;
+constexpr int TS_THREADS = (TC_CONV_WARPS + 2) * 32;
+
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t r[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE>
+__global__ void __launch_bounds__(TS_THREADS, 1)
+    gemm_ts_kernel(const uint8_t* __restrict__ w, uint64_t n, uint64_t k, const __grid_constant__ CUtensorMap map_hi,
+                   const __grid_constant__ CUtensorMap map_lo, uint64_t m, float* __restrict__ dst,
+                   int* __restrict__ error_flag) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t PLANE_B = N_TILE * 128;
+    constexpr uint32_t STAGE = 2 * PLANE_B;  // activations hi | lo
+    constexpr uint32_t TS_STAGES = TS_PHASES;  // step ks uses stage ks % 4 of both rings: the stage of its warps
+    constexpr uint32_t A_COL0 = 2 * N_TILE;
+    constexpr uint32_t WIN_STEPS = window_elems(TYPE) / TC_K;
+    constexpr uint32_t WIN_WORDS = window_elems(TYPE) / ELEMS * BYTES / 4;
+    constexpr uint32_t WIN_STRIDE = WIN_WORDS | 1u;
+    constexpr int MY_COLS = N_TILE / 4;
+    static_assert(2 * N_TILE + 64 * TS_STAGES <= 512 && WIN_STEPS % TS_PHASES == 0 && MY_COLS % 8 == 0, "tile shape");
+    // full[s]: the step's four converter warps + the TMA thread (and the tiles' bytes); empty[s]: the MMAs' commit
+    __shared__ uint64_t full[TS_STAGES], empty[TS_STAGES], acc_full[2], acc_empty[2], raw_full[4], raw_empty[4];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint64_t row0 = (uint64_t)blockIdx.x * TC_M;
+    const uint64_t tok0 = (uint64_t)blockIdx.y * N_TILE;
+    const uint32_t k_steps = (uint32_t)(k / TC_K);
+    const uint32_t n_chunks = (k_steps + TS_CHUNK - 1) / TS_CHUNK;
+    const uint32_t n_windows = k_steps / WIN_STEPS;
+    const uint64_t row_bytes = k / ELEMS * BYTES;
+    uint32_t* raw = reinterpret_cast<uint32_t*>(smem + (size_t)TS_STAGES * STAGE);
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < TS_STAGES; ++s) {
+            mbar_init(&full[s], 4 + 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], TC_CONV_WARPS);
+        }
+        for (int q = 0; q < 4; ++q) {
+            mbar_init(&raw_full[q], TS_PHASES);
+            mbar_init(&raw_empty[q], TS_PHASES);
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == TC_CONV_WARPS) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = tmem_base_slot;
+
+    if (warp < TC_CONV_WARPS) {
+        const uint32_t q = warp & 3, g = warp >> 2;
+        const uint32_t lane_base = (q * 32) << 16;  // this warp's quarter of the tensor-memory lanes
+        float sums[MY_COLS];
+#pragma unroll
+        for (int c = 0; c < MY_COLS; ++c) sums[c] = 0.0f;
+        auto drain = [&](uint32_t c) -> bool {
+            const uint32_t buf = c & 1;
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[buf], (c >> 1) & 1))) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tmem_d + lane_base + buf * N_TILE + g * MY_COLS;
+            if constexpr (MY_COLS == 8) {
+                uint32_t rr[8];
+                tmem_ld8(taddr, rr);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sums[i] += __uint_as_float(rr[i]);
+            } else {
+#pragma unroll
+                for (int part = 0; part < MY_COLS / 16; ++part) {
+                    uint32_t rr[16];
+                    tmem_ld16(taddr + part * 16, rr);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) sums[part * 16 + i] += __uint_as_float(rr[i]);
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            return true;
+        };
+        // this warp's 8 of the quarter's 32 rows of window wn, consecutive lanes consecutive words
+        uint32_t* q_raw = raw + q * 32 * WIN_STRIDE;
+        auto copy_window = [&](uint32_t wn) {
+            const uint64_t gr0 = row0 + q * 32 + g * 8;
+            const uint32_t dst0 = smem_u32(q_raw + g * 8 * WIN_STRIDE) + lane * 4;
+#pragma unroll 1
+            for (uint32_t rr = 0; rr < 8; ++rr) {
+                const uint64_t gr = gr0 + rr < n ? gr0 + rr : n - 1;
+                const uint8_t* src = w + gr * row_bytes + ((uint64_t)wn * WIN_WORDS + lane) * 4;
+                const uint32_t dstp = dst0 + rr * (WIN_STRIDE * 4);
+#pragma unroll
+                for (uint32_t c = 0; c < WIN_WORDS; c += 32) {
+                    if (c + lane < WIN_WORDS)
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dstp + c * 4), "l"(src + c * 4) : "memory");
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        const uint8_t* my_row = reinterpret_cast<const uint8_t*>(q_raw + lane * WIN_STRIDE);
+        bool ok = true;
+        uint32_t drained = 0;
+        copy_window(0);
+        for (uint32_t ks = g; ks < k_steps && ok; ks += TS_PHASES) {
+            const uint32_t a = g, a_round = ks / TS_STAGES;
+            const uint32_t wn = ks / WIN_STEPS, wj = ks - wn * WIN_STEPS;
+            if (wj < TS_PHASES) {
+                // first step of mine in this window: my copies have landed; hand them over and wait for the others'
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&raw_full[q]);
+                ok = __all_sync(0xFFFFFFFFu, mbar_wait(&raw_full[q], wn & 1));
+                if (!ok) break;
+            }
+            // the stage's columns must have been read by the MMAs that used them last
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(&empty[a], (a_round & 1) ^ 1));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t acol = tmem_d + lane_base + A_COL0 + a * 64;
+#pragma unroll
+            for (uint32_t h = 0; h < 2; ++h) {  // 16 columns at a time: hi terms, then the remainders
+                float v[16];
+                decode_unit<TYPE, LdShared>(my_row, wj * 4 + 2 * h, v, false);
+                decode_unit<TYPE, LdShared>(my_row, wj * 4 + 2 * h + 1, v + 8, false);
+                uint32_t t[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(v[i]) & 0xFFFFE000u;
+                tmem_st16(acol + 16 * h, t);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(v[i] - __uint_as_float(t[i]));
+                tmem_st16(acol + 32 + 16 * h, t);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[a]);
+            if (wj + TS_PHASES >= WIN_STEPS && wn + 1 < n_windows) {
+                // my last step in this window: once the quarter's other warps are through with it too, bring in
+                // my rows of the next one
+                if (lane == 0) mbar_arrive(&raw_empty[q]);
+                ok = __all_sync(0xFFFFFFFFu, mbar_wait(&raw_empty[q], wn & 1));
+                if (!ok) break;
+                copy_window(wn + 1);
+            }
+            // drain every finished chunk but the newest
+            while (ok && drained + 1 < ks / TS_CHUNK + 1) ok = drain(drained++);
+        }
+        while (ok && drained < n_chunks) ok = drain(drained++);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (!ok) abort_flag = 1;
+        if (ok) {
+            const uint64_t out_row = row0 + q * 32 + lane;
+#pragma unroll
+            for (int c = 0; c < MY_COLS; ++c) {
+                const uint64_t tok = tok0 + g * MY_COLS + c;
+                if (tok < m && out_row < n) dst[tok * n + out_row] = sums[c];
+            }
+        }
+    } else if (warp == TC_CONV_WARPS) {
+        // ── issuer ──
+        const uint32_t idesc = umma_idesc(N_TILE);
+        const uint32_t base0 = smem_u32(smem);
+        const uint64_t d0_b_hi = umma_desc(base0), d0_b_lo = umma_desc(base0 + PLANE_B);
+        bool ok = true;
+        for (uint32_t ks = 0; ks < k_steps && ok; ++ks) {
+            const uint32_t chunk = ks / TS_CHUNK, buf = chunk & 1;
+            const uint32_t s = ks % TS_STAGES, round = ks / TS_STAGES;
+            if (s == 0 && chunk >= 2) {
+                ok = __all_sync(0xFFFFFFFFu, mbar_wait(&acc_empty[buf], ((chunk >> 1) - 1) & 1));
+                if (!ok) break;
+            }
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(&full[s], round & 1));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");  // the converters' tcgen05.st / .ld
+            if (elect_one()) {
+                const uint64_t so = (uint64_t)s * (STAGE >> 4);
+                const uint64_t db_hi = d0_b_hi + so, db_lo = d0_b_lo + so;
+                const uint32_t d = tmem_d + buf * N_TILE;
+                const uint32_t a_hi = tmem_d + A_COL0 + s * 64, a_lo = a_hi + 32;
+#pragma unroll
+                for (uint32_t kk = 0; kk < TC_K / 8; ++kk) {
+                    const uint64_t adv = kk * 2;  // 32 bytes of the swizzled activation row = 8 columns of A
+                    if (kk == 0)
+                        umma_tf32_ts(d, a_hi, db_hi, idesc, s != 0);  // a chunk's first product overwrites
+                    else
+                        umma_tf32_ts(d, a_hi + kk * 8, db_hi + adv, idesc, 1);
+                    umma_tf32_ts(d, a_hi + kk * 8, db_lo + adv, idesc, 1);
+                    umma_tf32_ts(d, a_lo + kk * 8, db_hi + adv, idesc, 1);
+                }
+                umma_commit(&empty[s]);  // both the weight columns and the activation tiles of the stage are free
+                if (s == TS_STAGES - 1 || ks + 1 == k_steps) umma_commit(&acc_full[buf]);
+            }
+            __syncwarp();
+        }
+        if (!ok && lane == 0) abort_flag = 1;
+    } else {
+        // ── activation tiles: one lane keeps the ring of TMA copies full ──
+        if (lane == 0) {
+            bool ok = true;
+            for (uint32_t ks = 0; ks < k_steps && ok; ++ks) {
+                const uint32_t s = ks % TS_STAGES, round = ks / TS_STAGES;
+                ok = mbar_wait(&empty[s], (round & 1) ^ 1);
+                if (!ok) break;
+                uint8_t* st = smem + (size_t)s * STAGE;
+                mbar_arrive_expect_tx(&full[s], 2 * PLANE_B);
+                tma_load_2d(st, &map_hi, ks * TC_K, (uint32_t)tok0, &full[s]);
+                tma_load_2d(st + PLANE_B, &map_lo, ks * TC_K, (uint32_t)tok0, &full[s]);
+            }
+            if (!ok) abort_flag = 1;
+        }
+        __syncwarp();
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (abort_flag && tid == 0) *reinterpret_cast<volatile int*>(error_flag) = 1;
+    if (warp == TC_CONV_WARPS) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(512u) : "memory");
+    }
+}
+
 PFN_cuTensorMapEncodeTiled g_encode_tiled = nullptr;
 
 cudaError_t tensor_map_for(const float* base, uint64_t m, uint64_t k, uint32_t n_tile, CUtensorMap* out) {
@@ -495,14 +702,13 @@ cudaError_t tensor_map_for(const float* base, uint64_t m, uint64_t k, uint32_t n
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE, bool STAGED>
+template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE>
 cudaError_t launch_tile(const uint8_t* w, uint64_t n, uint64_t k, const float* x_hi, const float* x_lo, uint64_t m,
                         float* dst, int* error_flag, cudaStream_t s) {
     constexpr uint32_t STAGE = 2 * PLANE_A + 2 * N_TILE * 128;
-    constexpr uint32_t RAW = STAGED ? TC_M * ((window_elems(TYPE) / ELEMS * BYTES / 4) | 1u) * 4 : 0;  // staged window
-    uint32_t n_stages = std::min<uint32_t>(8, std::min<uint32_t>((uint32_t)(k / TC_K), (216 * 1024 - RAW) / STAGE));
-    size_t smem = (size_t)n_stages * STAGE + RAW + 1024;
-    auto kern = gemm_tc_kernel<TYPE, ELEMS, BYTES, N_TILE, STAGED>;
+    uint32_t n_stages = std::min<uint32_t>(8, std::min<uint32_t>((uint32_t)(k / TC_K), (216 * 1024) / STAGE));
+    size_t smem = (size_t)n_stages * STAGE + 1024;
+    auto kern = gemm_tc_kernel<TYPE, ELEMS, BYTES, N_TILE>;
     static bool configured[MAX_DEVICES] = {};
     if (cudaError_t ce = set_max_smem_once(kern, 226 * 1024, configured); ce != cudaSuccess) return ce;
     CUtensorMap map_hi, map_lo;
@@ -521,32 +727,52 @@ cudaError_t launch_tile(const uint8_t* w, uint64_t n, uint64_t k, const float* x
     return cudaGetLastError();
 }
 
-template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, bool STAGED>
-cudaError_t launch_staged(const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m, float* dst,
-                          float* scratch, int* error_flag, cudaStream_t s) {
-    // split the activations once: hi and lo arrays of m * k floats each
+template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE>
+cudaError_t launch_ts_tile(const uint8_t* w, uint64_t n, uint64_t k, const float* x_hi, const float* x_lo, uint64_t m,
+                           float* dst, int* error_flag, cudaStream_t s) {
+    constexpr uint32_t STAGE = 2 * N_TILE * 128;
+    constexpr uint32_t RAW = TC_M * ((window_elems(TYPE) / ELEMS * BYTES / 4) | 1u) * 4;
+    size_t smem = (size_t)TS_PHASES * STAGE + RAW + 1024;  // at most 4 x 32 KB + 35 KB
+    auto kern = gemm_ts_kernel<TYPE, ELEMS, BYTES, N_TILE>;
+    static bool configured[MAX_DEVICES] = {};
+    if (cudaError_t ce = set_max_smem_once(kern, 226 * 1024, configured); ce != cudaSuccess) return ce;
+    CUtensorMap map_hi, map_lo;
+    cudaError_t e = tensor_map_for(x_hi, m, k, N_TILE, &map_hi);
+    if (e == cudaSuccess) e = tensor_map_for(x_lo, m, k, N_TILE, &map_lo);
+    if (e != cudaSuccess) return e;
+    dim3 grid((unsigned)((n + TC_M - 1) / TC_M), (unsigned)((m + N_TILE - 1) / N_TILE));
+    kern<<<grid, TS_THREADS, smem, s>>>(w, n, k, map_hi, map_lo, m, dst, error_flag);
+    return cudaGetLastError();
+}
+
+// Tile width of the tensor-memory form for m activation rows.  128 tokens is its widest tile: two accumulators
+// and four weight stages fill the 512 columns, and the four weight stages are what lets each stage belong to one
+// group of warps (with fewer, two groups would share a stage and a parity wait could run a whole use ahead).
+template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES>
+cudaError_t launch_ts(const uint8_t* w, uint64_t n, uint64_t k, const float* x_hi, const float* x_lo, uint64_t m,
+                      float* dst, int* error_flag, cudaStream_t s) {
+    if (m <= 32) return launch_ts_tile<TYPE, ELEMS, BYTES, 32>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+    if (m <= 64) return launch_ts_tile<TYPE, ELEMS, BYTES, 64>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+    if (m <= 128) return launch_ts_tile<TYPE, ELEMS, BYTES, 128>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+    return launch_ts_tile<TYPE, ELEMS, BYTES, 128>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+}
+
+// Splits the activations once (hi and lo arrays of m * k floats each), then the tensor-memory form where the
+// weight rows are word-aligned and k is a whole number of staged windows, else the shared-memory form.
+template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES>
+cudaError_t launch_type(const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m, float* dst,
+                        float* scratch, int* error_flag, cudaStream_t s) {
     float* x_hi = scratch;
     float* x_lo = scratch + ((m * k + 63) & ~(uint64_t)63);
     const uint64_t n4 = m * k / 4;
     split_tf32_kernel<<<(unsigned)std::min<uint64_t>((n4 + 255) / 256, 148 * 16), 256, 0, s>>>(lhs, n4, x_hi, x_lo);
     if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
-    if (m <= 32) return launch_tile<TYPE, ELEMS, BYTES, 32, STAGED>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
-    if (m <= 64) return launch_tile<TYPE, ELEMS, BYTES, 64, STAGED>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
-    if (m <= 128) return launch_tile<TYPE, ELEMS, BYTES, 128, STAGED>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
-    // 256-token tiles decode every weight half as often, but only pay off once they still fill the SMs
-    const uint64_t ctas256 = ((n + TC_M - 1) / TC_M) * ((m + 255) / 256);
-    if (ctas256 < 148) return launch_tile<TYPE, ELEMS, BYTES, 128, STAGED>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
-    return launch_tile<TYPE, ELEMS, BYTES, 256, STAGED>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
-}
-
-// The staged form needs word-aligned rows and k a whole number of windows.
-template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES>
-cudaError_t launch_type(const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m, float* dst,
-                        float* scratch, int* error_flag, cudaStream_t s) {
     const uint64_t row_bytes = k / ELEMS * BYTES;
-    const bool staged = reinterpret_cast<uintptr_t>(w) % 4 == 0 && row_bytes % 4 == 0 && k % window_elems(TYPE) == 0;
-    if (staged) return launch_staged<TYPE, ELEMS, BYTES, true>(w, n, k, lhs, m, dst, scratch, error_flag, s);
-    return launch_staged<TYPE, ELEMS, BYTES, false>(w, n, k, lhs, m, dst, scratch, error_flag, s);
+    if (reinterpret_cast<uintptr_t>(w) % 4 == 0 && row_bytes % 4 == 0 && k % window_elems(TYPE) == 0)
+        return launch_ts<TYPE, ELEMS, BYTES>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+    if (m <= 32) return launch_tile<TYPE, ELEMS, BYTES, 32>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+    if (m <= 64) return launch_tile<TYPE, ELEMS, BYTES, 64>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+    return launch_tile<TYPE, ELEMS, BYTES, 128>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
 }
 
 }  // namespace
