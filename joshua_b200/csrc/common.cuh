@@ -86,6 +86,24 @@ void gemm_tc_set_trace(unsigned long long* dev_buf);  // profiling aid, see gemm
 cudaError_t launch_gemm_tc(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, const float* lhs, uint64_t m,
                            float* dst, void* scratch, int* error_flag, cudaStream_t s);
 
+// Grouped form for routed experts at prefill sizes: one launch over a device list of tiles, each up to 128
+// consecutive rows of the expert-sorted activation matrix x[rows, k] against that expert's slice of a bank
+// ([n_expert][n, k] blocks, `expert_bytes` apart).  With `bank_b` / `dst_b` the same activations go through two
+// banks in one launch (gate and up).  dst[row, n] is written for the tiles' rows only.  The first `n_narrow`
+// tiles of the list must hold at most 32 rows each (they run as narrower tiles).  False from
+// gemm_tc_grouped_supports = shapes this form does not take (the caller then runs one product per expert).
+struct GemmTile {
+    uint32_t expert;
+    uint32_t row0;  // first row of the tile in x / dst
+    uint32_t cnt;   // rows, 1..128
+    uint32_t pad;
+};
+bool gemm_tc_grouped_supports(uint32_t type, const uint8_t* bank, uint64_t n, uint64_t k);
+cudaError_t launch_gemm_tc_grouped(uint32_t type, const uint8_t* bank_a, const uint8_t* bank_b, uint64_t expert_bytes,
+                                   uint64_t n, uint64_t k, const float* x, uint64_t rows, float* dst_a, float* dst_b,
+                                   const GemmTile* tiles, uint32_t n_tiles, uint32_t n_narrow, void* scratch,
+                                   int* error_flag, cudaStream_t s);
+
 // One unit of grouped (MoE) work: up to 8 consecutive positions of the expert-sorted activation list,
 // all routed to `expert`.
 struct MoeJob {

@@ -455,11 +455,52 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t r[16]) 
         : "memory");
 }
 
+
+// MXFP4 by the block (the tensor-memory form decodes all 32 values of a step in one thread).  The 17-byte block
+// sits at any byte offset of a word-aligned row in shared memory: five aligned words and a funnel shift give the
+// 16 code bytes.  The padded row stride leaves at least three readable bytes after a row's last block.
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void mxfp4_load_block(uint32_t blk_addr, uint32_t codes[4], float* half_scale) {
+    const uint32_t e = (lds32(blk_addr & ~3u) >> ((blk_addr & 3u) * 8)) & 0xFFu;
+    const uint32_t qa = blk_addr + 1, al = qa & ~3u, sh = (qa & 3u) * 8;
+    uint32_t wds[5];
+#pragma unroll
+    for (int i = 0; i < 5; ++i) wds[i] = lds32(al + 4 * i);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) codes[i] = __funnelshift_r(wds[i], wds[i + 1], sh);
+    // half of the block scale 2^(e-127) (e = 0 reads as 2^-127, src/mxfp4.rs:83-94), exact also when subnormal;
+    // a NaN scale (0xFF) decodes to zeros
+    *half_scale = e == 0xFFu ? 0.0f : __uint_as_float(e >= 2 ? (e - 1) << 23 : e == 1 ? 0x00400000u : 0x00200000u);
+}
+// Values 16h .. 16h+15 of the block: the low (h = 0) or high nibbles of the 16 code bytes.  An E2M1 code is
+// sign | magnitude index into {0, .5, 1, 1.5, 2, 3, 4, 6}; twice the magnitude comes from a byte table by
+// `prmt`, four codes at a time, and (2 * magnitude) * (scale / 2) is the exact product the reference forms.
+__device__ __forceinline__ void mxfp4_half(const uint32_t codes[4], uint32_t h, float half_scale, float v[16]) {
+#pragma unroll
+    for (int wi = 0; wi < 4; ++wi) {
+        const uint32_t c = codes[wi] >> (4 * h);
+        const uint32_t x = c & 0x07070707u, y = x | (x >> 4);
+        const uint32_t sel = (y & 0xFFu) | ((y >> 8) & 0xFF00u);
+        const uint32_t m2 = __byte_perm(0x03020100u, 0x0C080604u, sel);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const float mag = (float)((m2 >> (8 * b)) & 0xFFu);
+            const uint32_t sign = (c << (28 - 8 * b)) & 0x80000000u;
+            v[4 * wi + b] = __fmul_rn(__uint_as_float(__float_as_uint(mag) | sign), half_scale);
+        }
+    }
+}
+
 template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE>
 __global__ void __launch_bounds__(TS_THREADS, 1)
-    gemm_ts_kernel(const uint8_t* __restrict__ w, uint64_t n, uint64_t k, const __grid_constant__ CUtensorMap map_hi,
-                   const __grid_constant__ CUtensorMap map_lo, uint64_t m, float* __restrict__ dst,
-                   int* __restrict__ error_flag) {
+    gemm_ts_kernel(const uint8_t* __restrict__ w_a, uint64_t n, uint64_t k, const __grid_constant__ CUtensorMap map_hi,
+                   const __grid_constant__ CUtensorMap map_lo, uint64_t m_rows, float* __restrict__ dst_a,
+                   int* __restrict__ error_flag, const GemmTile* __restrict__ tiles, uint64_t expert_bytes,
+                   const uint8_t* __restrict__ w_b, float* __restrict__ dst_b) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t PLANE_B = N_TILE * 128;
@@ -470,6 +511,8 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
     constexpr uint32_t WIN_WORDS = window_elems(TYPE) / ELEMS * BYTES / 4;
     constexpr uint32_t WIN_STRIDE = WIN_WORDS | 1u;
     constexpr int MY_COLS = N_TILE / 4;
+    // MXFP4 weights (an E2M1 value times a power of two) are TF32 numbers already: no remainder term, two products
+    constexpr bool EXACT_TF32 = TYPE == T_MXFP4;
     static_assert(2 * N_TILE + 64 * TS_STAGES <= 512 && WIN_STEPS % TS_PHASES == 0 && MY_COLS % 8 == 0, "tile shape");
     // full[s]: the step's four converter warps + the TMA thread (and the tiles' bytes); empty[s]: the MMAs' commit
     __shared__ uint64_t full[TS_STAGES], empty[TS_STAGES], acc_full[2], acc_empty[2], raw_full[4], raw_empty[4];
@@ -478,7 +521,18 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint64_t row0 = (uint64_t)blockIdx.x * TC_M;
-    const uint64_t tok0 = (uint64_t)blockIdx.y * N_TILE;
+    // plain form: token tile blockIdx.y of lhs[m_rows, k].  Grouped form: tile blockIdx.y of the list, its
+    // expert's slice of the bank (blockIdx.z picks the bank and its destination); rows of the tile box beyond
+    // the tile's count belong to other experts, are multiplied along and never stored.
+    uint64_t tok0 = (uint64_t)blockIdx.y * N_TILE, m = m_rows;
+    const uint8_t* w = blockIdx.z ? w_b : w_a;
+    float* dst = blockIdx.z ? dst_b : dst_a;
+    if (tiles != nullptr) {
+        const GemmTile t = tiles[blockIdx.y];
+        w += (uint64_t)t.expert * expert_bytes;
+        tok0 = t.row0;
+        m = (uint64_t)t.row0 + t.cnt;
+    }
     const uint32_t k_steps = (uint32_t)(k / TC_K);
     const uint32_t n_chunks = (k_steps + TS_CHUNK - 1) / TS_CHUNK;
     const uint32_t n_windows = k_steps / WIN_STEPS;
@@ -580,18 +634,27 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acol = tmem_d + lane_base + A_COL0 + a * 64;
+            [[maybe_unused]] uint32_t fp4_codes[4];
+            [[maybe_unused]] float fp4_half_scale;
+            if constexpr (TYPE == T_MXFP4) mxfp4_load_block(smem_u32(my_row) + wj * 17, fp4_codes, &fp4_half_scale);
 #pragma unroll
             for (uint32_t h = 0; h < 2; ++h) {  // 16 columns at a time: hi terms, then the remainders
                 float v[16];
-                decode_unit<TYPE, LdShared>(my_row, wj * 4 + 2 * h, v, false);
-                decode_unit<TYPE, LdShared>(my_row, wj * 4 + 2 * h + 1, v + 8, false);
+                if constexpr (TYPE == T_MXFP4) {
+                    mxfp4_half(fp4_codes, h, fp4_half_scale, v);
+                } else {
+                    decode_unit<TYPE, LdShared>(my_row, wj * 4 + 2 * h, v, false);
+                    decode_unit<TYPE, LdShared>(my_row, wj * 4 + 2 * h + 1, v + 8, false);
+                }
                 uint32_t t[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(v[i]) & 0xFFFFE000u;
                 tmem_st16(acol + 16 * h, t);
+                if constexpr (!EXACT_TF32) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(v[i] - __uint_as_float(t[i]));
-                tmem_st16(acol + 32 + 16 * h, t);
+                    for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(v[i] - __uint_as_float(t[i]));
+                    tmem_st16(acol + 32 + 16 * h, t);
+                }
             }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -648,7 +711,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
                     else
                         umma_tf32_ts(d, a_hi + kk * 8, db_hi + adv, idesc, 1);
                     umma_tf32_ts(d, a_hi + kk * 8, db_lo + adv, idesc, 1);
-                    umma_tf32_ts(d, a_lo + kk * 8, db_hi + adv, idesc, 1);
+                    if constexpr (!EXACT_TF32) umma_tf32_ts(d, a_lo + kk * 8, db_hi + adv, idesc, 1);
                 }
                 umma_commit(&empty[s]);  // both the weight columns and the activation tiles of the stage are free
                 if (s == TS_STAGES - 1 || ks + 1 == k_steps) umma_commit(&acc_full[buf]);
@@ -741,7 +804,7 @@ cudaError_t launch_ts_tile(const uint8_t* w, uint64_t n, uint64_t k, const float
     if (e == cudaSuccess) e = tensor_map_for(x_lo, m, k, N_TILE, &map_lo);
     if (e != cudaSuccess) return e;
     dim3 grid((unsigned)((n + TC_M - 1) / TC_M), (unsigned)((m + N_TILE - 1) / N_TILE));
-    kern<<<grid, TS_THREADS, smem, s>>>(w, n, k, map_hi, map_lo, m, dst, error_flag);
+    kern<<<grid, TS_THREADS, smem, s>>>(w, n, k, map_hi, map_lo, m, dst, error_flag, nullptr, 0, nullptr, nullptr);
     return cudaGetLastError();
 }
 
@@ -755,6 +818,52 @@ cudaError_t launch_ts(const uint8_t* w, uint64_t n, uint64_t k, const float* x_h
     if (m <= 64) return launch_ts_tile<TYPE, ELEMS, BYTES, 64>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
     if (m <= 128) return launch_ts_tile<TYPE, ELEMS, BYTES, 128>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
     return launch_ts_tile<TYPE, ELEMS, BYTES, 128>(w, n, k, x_hi, x_lo, m, dst, error_flag, s);
+}
+
+template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE>
+cudaError_t launch_grouped_tiles(const uint8_t* bank_a, const uint8_t* bank_b, uint64_t expert_bytes, uint64_t n, uint64_t k,
+                                 const float* x_hi, const float* x_lo, uint64_t rows, float* dst_a, float* dst_b,
+                                 const GemmTile* tiles, uint32_t n_tiles, int* error_flag, cudaStream_t s) {
+    constexpr uint32_t STAGE = 2 * N_TILE * 128;
+    constexpr uint32_t RAW = TC_M * ((window_elems(TYPE) / ELEMS * BYTES / 4) | 1u) * 4;
+    size_t smem = (size_t)TS_PHASES * STAGE + RAW + 1024;
+    auto kern = gemm_ts_kernel<TYPE, ELEMS, BYTES, N_TILE>;
+    static bool configured[MAX_DEVICES] = {};
+    if (cudaError_t ce = set_max_smem_once(kern, 226 * 1024, configured); ce != cudaSuccess) return ce;
+    CUtensorMap map_hi, map_lo;
+    cudaError_t e = tensor_map_for(x_hi, rows, k, N_TILE, &map_hi);
+    if (e == cudaSuccess) e = tensor_map_for(x_lo, rows, k, N_TILE, &map_lo);
+    if (e != cudaSuccess) return e;
+    // the tile list is walked along grid.y (at most 65535 entries a launch)
+    for (uint32_t t0 = 0; t0 < n_tiles; t0 += 65535) {
+        dim3 grid((unsigned)((n + TC_M - 1) / TC_M), std::min<uint32_t>(65535, n_tiles - t0), bank_b ? 2 : 1);
+        kern<<<grid, TS_THREADS, smem, s>>>(bank_a, n, k, map_hi, map_lo, rows, dst_a, error_flag, tiles + t0, expert_bytes,
+                                            bank_b, dst_b);
+        if (cudaError_t le = cudaGetLastError(); le != cudaSuccess) return le;
+    }
+    return cudaSuccess;
+}
+
+// The first `n_narrow` tiles of the list hold at most 32 rows each and run as 32-token tiles (a quarter of the
+// tensor-core work and of the activation traffic of a 128-token tile), the rest as 128-token tiles.
+template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES>
+cudaError_t launch_grouped_type(const uint8_t* bank_a, const uint8_t* bank_b, uint64_t expert_bytes, uint64_t n, uint64_t k,
+                                const float* x, uint64_t rows, float* dst_a, float* dst_b, const GemmTile* tiles,
+                                uint32_t n_tiles, uint32_t n_narrow, float* scratch, int* error_flag, cudaStream_t s) {
+    float* x_hi = scratch;
+    float* x_lo = scratch + ((rows * k + 63) & ~(uint64_t)63);
+    const uint64_t n4 = rows * k / 4;
+    split_tf32_kernel<<<(unsigned)std::min<uint64_t>((n4 + 255) / 256, 148 * 16), 256, 0, s>>>(x, n4, x_hi, x_lo);
+    if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
+    if (n_narrow) {
+        cudaError_t e = launch_grouped_tiles<TYPE, ELEMS, BYTES, 32>(bank_a, bank_b, expert_bytes, n, k, x_hi, x_lo, rows, dst_a,
+                                                                      dst_b, tiles, n_narrow, error_flag, s);
+        if (e != cudaSuccess) return e;
+    }
+    if (n_tiles > n_narrow)
+        return launch_grouped_tiles<TYPE, ELEMS, BYTES, 128>(bank_a, bank_b, expert_bytes, n, k, x_hi, x_lo, rows, dst_a, dst_b,
+                                                             tiles + n_narrow, n_tiles - n_narrow, error_flag, s);
+    return cudaSuccess;
 }
 
 // Splits the activations once (hi and lo arrays of m * k floats each), then the tensor-memory form where the
@@ -791,6 +900,40 @@ bool gemm_tc_supports(uint32_t type, const uint8_t* w, uint64_t n, uint64_t k, u
         case T_IQ2_XXS: return a % 2 == 0;
         case T_MXFP4: return true;
         default: return false;
+    }
+}
+
+bool gemm_tc_grouped_supports(uint32_t type, const uint8_t* bank, uint64_t n, uint64_t k) {
+    Format f;
+    if (n == 0 || k == 0 || !format_of(type, &f) || !gemm_tc_supports(type, bank, n, k, 128)) return false;
+    const uint64_t row_bytes = k / f.elems * f.bytes;
+    // the tensor-memory form's conditions; every expert's slice starts a whole number of rows into the bank
+    return reinterpret_cast<uintptr_t>(bank) % 4 == 0 && row_bytes % 4 == 0 && k % window_elems(type) == 0;
+}
+
+cudaError_t launch_gemm_tc_grouped(uint32_t type, const uint8_t* bank_a, const uint8_t* bank_b, uint64_t expert_bytes,
+                                   uint64_t n, uint64_t k, const float* x, uint64_t rows, float* dst_a, float* dst_b,
+                                   const GemmTile* tiles, uint32_t n_tiles, uint32_t n_narrow, void* scratch_v,
+                                   int* error_flag, cudaStream_t s) {
+    float* scratch = static_cast<float*>(scratch_v);
+    if (n_tiles == 0) return cudaSuccess;
+    switch (type) {
+        case T_Q8_0:
+            return launch_grouped_type<T_Q8_0, 32, 34>(bank_a, bank_b, expert_bytes, n, k, x, rows, dst_a, dst_b, tiles, n_tiles,
+                                                       n_narrow, scratch, error_flag, s);
+        case T_Q2_K:
+            return launch_grouped_type<T_Q2_K, 256, 84>(bank_a, bank_b, expert_bytes, n, k, x, rows, dst_a, dst_b, tiles, n_tiles,
+                                                        n_narrow, scratch, error_flag, s);
+        case T_Q4_K:
+            return launch_grouped_type<T_Q4_K, 256, 144>(bank_a, bank_b, expert_bytes, n, k, x, rows, dst_a, dst_b, tiles,
+                                                         n_tiles, n_narrow, scratch, error_flag, s);
+        case T_IQ2_XXS:
+            return launch_grouped_type<T_IQ2_XXS, 256, 66>(bank_a, bank_b, expert_bytes, n, k, x, rows, dst_a, dst_b, tiles,
+                                                           n_tiles, n_narrow, scratch, error_flag, s);
+        case T_MXFP4:
+            return launch_grouped_type<T_MXFP4, 32, 17>(bank_a, bank_b, expert_bytes, n, k, x, rows, dst_a, dst_b, tiles, n_tiles,
+                                                        n_narrow, scratch, error_flag, s);
+        default: return cudaErrorInvalidValue;
     }
 }
 

@@ -1,6 +1,7 @@
 // C ABI of the MoE layer: routing on the device, grouped expert matmuls, weighted combine.
 // Declarations and the reference interfaces they replace are in include/joshua_b200.h.
 #include "handles.cuh"
+#include <algorithm>
 
 
 namespace {
@@ -121,9 +122,9 @@ int32_t run_experts(jq_moe* m, const float* x, uint64_t R, uint64_t P, uint32_t 
 // sh_out[T, hidden] = shared expert MLP over all tokens
 // The prefill form of the expert MLPs, as the reference buckets tokens per expert and runs one matmul per
 // bucket (src/quantized_qwen3_moe.rs:455-520): when an expert sees dozens of rows, its rows are gathered into
-// bucket order and every expert's gate / up / down product is one call of the batched matmul (tile GEMM on the
-// tensor cores for more than 64 rows).  The expert histogram is read back to the host once, which synchronises
-// the stream.
+// bucket order and the experts' gate / up / down products run on the tile GEMM (tensor cores), as one grouped
+// launch per phase over a list of (expert, row range) tiles.  The job list is read back to the host once to
+// cut the tiles, which synchronises the stream.
 int32_t run_experts_bucketed(jq_moe* m, const float* x, uint64_t T, uint64_t P, cudaStream_t s) {
     const jq_moe_config& c = m->cfg;
     if (P > m->bucket_pairs) {
@@ -161,7 +162,44 @@ int32_t run_experts_bucketed(jq_moe* m, const float* x, uint64_t T, uint64_t P, 
         w.owns = false;
         return w;
     };
-    // One expert's product fills only a fraction of the GPU (n / 128 CTAs), so the buckets are dealt to eight
+    // Usual form: the buckets cut into tiles of up to 128 rows, and one grouped launch of the tile GEMM per phase
+    // (gate and up together, then down) walks the tile list on the device.
+    if (jq::gemm_tc_grouped_supports(m->gate->type, m->gate->dev, c.inter, c.hidden) && m->up->type == m->gate->type &&
+        jq::gemm_tc_grouped_supports(m->down->type, m->down->dev, c.hidden, c.inter)) {
+        std::vector<jq::GemmTile> tiles;
+        uint64_t live = 0;
+        for (const Bucket& b : buckets) {
+            for (uint32_t r = 0; r < b.cnt; r += 128) tiles.push_back({b.expert, b.row0 + r, std::min<uint32_t>(128, b.cnt - r), 0});
+            live = std::max<uint64_t>(live, (uint64_t)b.row0 + b.cnt);
+        }
+        if (tiles.empty()) return jq::OK;
+        // tiles of at most 32 rows first: they run as 32-token tiles
+        const uint32_t n_narrow = (uint32_t)(std::stable_partition(tiles.begin(), tiles.end(),
+                                                                   [](const jq::GemmTile& t) { return t.cnt <= 32; }) -
+                                             tiles.begin());
+        if (tiles.size() > m->tiles_cap) {
+            if (m->tiles) cudaFree(m->tiles);
+            m->tiles = nullptr;
+            m->tiles_cap = 0;
+            JQ_CUDA(cudaMalloc(&m->tiles, tiles.size() * sizeof(jq::GemmTile)));
+            m->tiles_cap = tiles.size();
+        }
+        JQ_CUDA(cudaMemcpyAsync(m->tiles, tiles.data(), tiles.size() * sizeof(jq::GemmTile), cudaMemcpyHostToDevice, s));
+        JQ_CUDA(cudaStreamSynchronize(s));  // the list is host memory of this call
+        void* scratch = nullptr;
+        const size_t need = std::max(jq::gemm_tc_scratch_bytes(P, c.hidden), jq::gemm_tc_scratch_bytes(P, c.inter));
+        JQ_CUDA(m->ctx->scratch_for(reinterpret_cast<cudaStream_t>(reinterpret_cast<uintptr_t>(s) ^ 3), need, &scratch));
+        const uint32_t nt = (uint32_t)tiles.size();
+        JQ_CUDA(jq::launch_gemm_tc_grouped(m->gate->type, m->gate->dev, m->up->dev, m->gate_expert_bytes, c.inter, c.hidden, xs, P,
+                                           gbuf, ubuf, m->tiles, nt, n_narrow, scratch, m->ctx->status_dev, s));
+        JQ_CUDA(jq::launch_swiglu(gbuf, ubuf, live * c.inter, c.clamp, m->hidden, s));
+        JQ_CUDA(jq::launch_gemm_tc_grouped(m->down->type, m->down->dev, nullptr, m->down_expert_bytes, c.hidden, c.inter,
+                                           m->hidden, P, m->out, nullptr, m->tiles, nt, n_narrow, scratch, m->ctx->status_dev, s));
+        (void)T;
+        return jq::OK;
+    }
+    // Shapes the grouped form does not take: one batched matmul per bucket.  One expert's product fills only a
+    // fraction of the GPU (n / 128 CTAs), so the buckets are dealt to eight
     // auxiliary streams that fork from and join the caller's stream around each phase.
     constexpr int NAUX = 8;
     jq_ctx* cx = m->ctx;
@@ -378,6 +416,7 @@ void jq_moe_free(jq_moe* m) {
     cudaFree(m->bias);
     cudaFree(m->ws);
     cudaFree(m->bucket);
+    cudaFree(m->tiles);
     cudaFree(m->dense_jobs);
     cudaFree(m->one);
     if (m->bad_host) cudaFreeHost(m->bad_host);
@@ -478,17 +517,16 @@ int32_t jq_moe_forward_norm_add_dev(jq_moe* m, const float* x_dev, uint64_t T, c
         JQ_CUDA(jq::launch_moe_jobs(m->ids, (uint32_t)T, c.n_used, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
                                     m->n_jobs, m->n_list, m->bad_dev, s));
     }
-    // prefill-sized batches (64 or more rows per expert on average): one batched matmul per expert bucket, the
-    // buckets spread over eight streams.  Measured on 384 MXFP4 experts of 7168 x 2048 at 4096 tokens (85 rows per
-    // expert): 61 ms this way against 126 ms for the grouped decode kernel (322 ms on a single stream, where one
-    // expert's tile GEMM fills 16 of 148 SMs).
+    // prefill-sized batches (12 or more rows per expert on average): the experts' rows gathered into buckets and
+    // the products run as grouped launches of the tile GEMM.  Measured crossovers against the grouped decode
+    // kernel (uniform routing): 128 Q4_K experts of 2048 x 768 between 8 and 16 rows per expert (0.91 / 0.68 ms at
+    // 8, 0.95 / 1.13 ms at 16), 384 MXFP4 experts of 7168 x 2048 near 11 (20.8 / 19.2 ms), 256 IQ2_XXS experts of
+    // the same shape above 8 (13.3 / 9.2 ms).
     uint64_t thr_override = 0;  // average rows per expert from which to bucket (measurement switch)
 #ifdef JQ_PROFILING
     if (const char* thr_env = std::getenv("JQ_MOE_BUCKET_ROWS")) thr_override = std::strtoull(thr_env, nullptr, 10);
 #endif
-    // small experts (Qwen3-MoE: 2048 x 768) need more rows before a bucket beats the grouped kernel: measured
-    // 9.0 against 3.9 ms at 64 rows per expert, 11.5 against 14.9 ms at 256
-    const uint64_t thr = thr_override ? thr_override : ((uint64_t)c.hidden * c.inter >= (1ull << 23) ? 64ull : 192ull);
+    const uint64_t thr = thr_override ? thr_override : 12ull;
     const bool bucketed = !fused && !m->ctx->force_f32 && P >= thr * c.n_expert;
     if (bucketed) {
         if (int32_t rc = run_experts_bucketed(m, x_in, T, P, s)) return rc;
