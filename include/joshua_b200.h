@@ -414,7 +414,7 @@ int32_t jq_moe_last_routing(jq_moe* m, uint64_t n_tokens, uint32_t* ids, float* 
  * same values for any number of ranks.
  *
  *   jq_ep_create   on every rank (rank < world <= 8, n_expert % world == 0,
- *                  max_tokens * n_used <= 4096): allocates this rank's window
+ *                  max_tokens * n_used <= 16384): allocates this rank's window
  *   jq_ep_export   writes the JQ_EP_HANDLE_BYTES-byte handle of the window;
  *                  the host gathers the handles of all ranks, in rank order,
  *                  by whatever means it has (MPI, a store, torch.distributed)

@@ -11,8 +11,8 @@ ids (the mechanism of hash-routed layers, src/quantized_deepseek4.rs:1375-1398);
 the gate.
 
 With --gpus N the banks are split contiguously (48 experts per rank at N = 8), every rank holds `tokens / N`
-of the tokens (at least one) and rows travel through the peer-memory exchange of `csrc/ep.cu`, in slices of 512
-tokens per rank.  Reported per token count: tokens/s, algorithmic TFLOP/s (2 * tokens * 8 * 3 * 7168 * 2048),
+of the tokens (at least one) and rows travel through the peer-memory exchange of `csrc/ep.cu`, in slices of up
+to 2048 tokens per rank.  Reported per token count: tokens/s, algorithmic TFLOP/s (2 * tokens * 8 * 3 * 7168 * 2048),
 the GB/s of distinct experts' bytes read (the roofline at 1 and 16 tokens), and max / mean rows per rank.
 """
 from __future__ import annotations
@@ -64,7 +64,6 @@ def run(args):
         banks.append(QTensor.from_device(t, raw[:nbytes], ctx))
     router = (np.random.default_rng(0).standard_normal((E, H)) * 0.02).astype(np.float32)
     token_counts = [int(v) for v in str(args.tokens).split(",")]
-    cap = 512                                                        # tokens per rank and exchange
     if world == 1:
         layer = Moe(MoeConfig(gating=GATE_SOFTMAX, n_expert=E, n_used=K, hidden=H, inter=INTER, norm=True), router,
                     *banks, ctx=ctx)
@@ -76,9 +75,7 @@ def run(args):
                  None, None, ctx=ctx)
         el = Moe(MoeConfig(gating=GATE_SOFTMAX, n_expert=per, n_used=1, hidden=H, inter=INTER, oob_policy=OOB_SKIP),
                  np.zeros((per, H), np.float32), *banks, ctx=ctx)
-        exchange = PeerExchange(ctx, E, K, H, cap, group=group)
-        rl.reserve(cap, 0)
-        el.reserve(cap * K * world, cap * K * world)
+        exchange = None
     perm = np.random.default_rng(7).permutation(E)
     per_expert_bytes = 3 * synth.tensor_bytes(t, INTER, H)
     peak, which = measured_peaks()
@@ -95,6 +92,15 @@ def run(args):
         y = torch.empty(Tl, H, device=dev)
         if world == 1:
             layer.reserve(Tl, Tl * K)
+        else:
+            # the exchange is sized for this token count (its fixed-capacity blocks cost time in proportion)
+            if exchange is not None:
+                dist.barrier()
+                exchange.close()
+            cap = min(2048, Tl)                                      # tokens per rank and exchange
+            exchange = PeerExchange(ctx, E, K, H, cap, group=group)
+            rl.reserve(cap, 0)
+            el.reserve(cap * K * world, cap * K * world)
         it = [0]
 
         def step():

@@ -255,8 +255,8 @@ int32_t jq_ep_create(jq_ctx* ctx, uint32_t rank, uint32_t world, uint32_t n_expe
     if (n_expert == 0 || n_expert % world) return jq_fail(jq::E_INVALID, "jq_ep_create: experts do not split evenly over the ranks");
     if (n_used == 0 || n_used > n_expert || hidden == 0 || hidden % 4 || max_tokens == 0)
         return jq_fail(jq::E_INVALID, "jq_ep_create: bad n_used / hidden / max_tokens");
-    if ((uint64_t)max_tokens * n_used > 4096)
-        return jq_fail(jq::E_TOO_LARGE, "jq_ep_create: max_tokens * n_used above 4096 (this exchange is sized for decode batches)");
+    if ((uint64_t)max_tokens * n_used > 16384)
+        return jq_fail(jq::E_TOO_LARGE, "jq_ep_create: max_tokens * n_used above 16384 rows per exchange (send more tokens in slices)");
     JQ_CUDA(cudaSetDevice(ctx->device));
     jq_ep* e = new (std::nothrow) jq_ep();
     if (!e) return jq_fail(jq::E_NOMEM, "jq_ep_create: out of host memory");
@@ -391,7 +391,7 @@ int32_t jq_ep_forward_norm_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const 
                            norm_w_dev, eps, (const uint32_t*)e->ids, (uint32_t)T, e->n_used, e->pair_slot, e->epoch, e->done,
                            e->polls, e->ctx->status_dev));
     if (int32_t r = jq_moe_experts_list(experts, reinterpret_cast<const float*>(mine + e->lay.o_rows_in), rows,
-                                        reinterpret_cast<const uint32_t*>(mine + e->lay.o_ids_in), s))
+                                        reinterpret_cast<const uint32_t*>(mine + e->lay.o_ids_in), P, s))
         return r;
     JQ_CUDA(jq::launch_pdl(ep_return_kernel, dim3(rows), 256, 0, s, e->win, e->lay, e->rank,
                            (const float*)experts->out, (const uint32_t*)experts->inv, (const uint32_t*)e->epoch,

@@ -149,5 +149,8 @@ struct jq_moe {
     std::mutex mu;
 };
 
+// Expert MLPs over n_rows rows with given local expert ids (an id out of range marks an unused row).
+// `live_rows` is the caller's estimate of how many rows carry a valid id: from 12 per expert on, the rows run
+// in buckets on the tile GEMM (which reads the job list back and so synchronises the stream).
 int32_t jq_moe_experts_list(jq_moe* m, const float* x_dev, uint64_t n_rows, const uint32_t* expert_ids_dev,
-                            cudaStream_t s);
+                            uint64_t live_rows, cudaStream_t s);

@@ -125,6 +125,8 @@ int32_t run_experts(jq_moe* m, const float* x, uint64_t R, uint64_t P, uint32_t 
 // bucket order and the experts' gate / up / down products run on the tile GEMM (tensor cores), as one grouped
 // launch per phase over a list of (expert, row range) tiles.  The job list is read back to the host once to
 // cut the tiles, which synchronises the stream.
+constexpr uint64_t BUCKET_ROWS_PER_EXPERT = 12;  // average rows per expert from which the bucketed form is used
+
 int32_t run_experts_bucketed(jq_moe* m, const float* x, uint64_t T, uint64_t P, cudaStream_t s) {
     const jq_moe_config& c = m->cfg;
     if (P > m->bucket_pairs) {
@@ -329,11 +331,12 @@ int32_t check_bank(const char* name, const jq_weight* w, uint64_t experts, uint6
 // Expert MLPs over rows with one expert id each, left in expert-sorted list order: row r's output is
 // m->out[m->inv[r], :] (inv = 0xFFFFFFFF for an id out of range).  Arguments are checked by the callers.
 int32_t jq_moe_experts_list(jq_moe* m, const float* x_dev, uint64_t n_rows, const uint32_t* expert_ids_dev,
-                            cudaStream_t s) {
+                            uint64_t live_rows, cudaStream_t s) {
     const jq_moe_config& c = m->cfg;
     uint32_t rpj = rows_per_job_for(n_rows, n_rows == 1 ? 1 : 2, c.n_expert);
     JQ_CUDA(jq::launch_moe_jobs(expert_ids_dev, (uint32_t)n_rows, 1, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
                                 m->n_jobs, m->n_list, m->bad_dev, s));
+    if (!m->ctx->force_f32 && live_rows >= BUCKET_ROWS_PER_EXPERT * c.n_expert) return run_experts_bucketed(m, x_dev, n_rows, n_rows, s);
     return run_experts(m, x_dev, n_rows, n_rows, rpj, s);
 }
 
@@ -469,7 +472,7 @@ int32_t jq_moe_experts_dev(jq_moe* m, const float* x_dev, uint64_t n_rows, const
     if (n_rows > m->cap_tokens || n_rows > m->cap_pairs)
         return jq_fail(jq::E_TOO_LARGE, "jq_moe_experts_dev: call jq_moe_reserve for this many rows first");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (int32_t rc = jq_moe_experts_list(m, x_dev, n_rows, expert_ids_dev, s)) return rc;
+    if (int32_t rc = jq_moe_experts_list(m, x_dev, n_rows, expert_ids_dev, n_rows, s)) return rc;
     // back to row order: out[r] = out_list[inv[r]] (rows with an id out of range come back as zeros)
     JQ_CUDA(jq::launch_moe_combine(m->out, m->inv, m->ones, nullptr, (uint32_t)n_rows, 1, m->cfg.hidden, out_dev, s));
     return jq::OK;
@@ -526,7 +529,7 @@ int32_t jq_moe_forward_norm_add_dev(jq_moe* m, const float* x_dev, uint64_t T, c
 #ifdef JQ_PROFILING
     if (const char* thr_env = std::getenv("JQ_MOE_BUCKET_ROWS")) thr_override = std::strtoull(thr_env, nullptr, 10);
 #endif
-    const uint64_t thr = thr_override ? thr_override : 12ull;
+    const uint64_t thr = thr_override ? thr_override : BUCKET_ROWS_PER_EXPERT;
     const bool bucketed = !fused && !m->ctx->force_f32 && P >= thr * c.n_expert;
     if (bucketed) {
         if (int32_t rc = run_experts_bucketed(m, x_in, T, P, s)) return rc;

@@ -68,7 +68,7 @@ def test_exchange_rejects_bad_arguments():
     assert _lib.lib().jq_ep_create(ctx._h, 0, 3, 16, 4, 512, 8, ctypes.byref(h)) != 0   # 16 experts over 3 ranks
     assert b"evenly" in _lib.lib().jq_last_error()
     assert _lib.lib().jq_ep_create(ctx._h, 2, 2, 16, 4, 512, 8, ctypes.byref(h)) != 0   # rank out of range
-    assert _lib.lib().jq_ep_create(ctx._h, 0, 1, 16, 4, 512, 4096, ctypes.byref(h)) != 0  # window too large
+    assert _lib.lib().jq_ep_create(ctx._h, 0, 1, 16, 4, 512, 8192, ctypes.byref(h)) != 0  # window too large
 
 
 def test_absent_peer_times_out_and_the_context_stays_usable():
