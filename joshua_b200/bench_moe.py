@@ -56,7 +56,8 @@ def measure(args, batch: int, group, sample_load: bool = True, with_e2e: bool = 
     warmup = max(3, args.warmup)
     cfg = MoeDecoderConfig()
     prefill = min(args.prefill, 128)
-    max_ctx = prefill + 3 * (warmup + args.steps) + 24
+    prompt = args.prefill if (world == 1 and batch == 1 and with_e2e) else 0   # one timed prefill pass, one GPU only
+    max_ctx = max(prefill, prompt) + 3 * (warmup + args.steps) + 24
     # the same seed on every rank: attention, router and head weights are replicas; a rank draws only its own experts
     model = MoeDecoder(cfg, dev, batch=batch, max_ctx=max_ctx, seed=0, group=group)
     stream = torch.cuda.Stream()
@@ -102,6 +103,28 @@ def measure(args, batch: int, group, sample_load: bool = True, with_e2e: bool = 
     model.check_flags()
     out = {"dt": dt, "clocks": clocks.summary(), "load": load, "cfg": cfg, "warmup": warmup,
            "launches_per_step": model.launches_per_step, "weight_bytes": model.weight_bytes}
+    if prompt > 0:
+        # the prompt in one pass (`forward(input [1, seq_len], 0)`): batched linears and the experts' buckets on the
+        # tile GEMM, causal attention; the reference's bench feeds a repeated token (examples/bench_qwen3moe.rs:148-162)
+        with torch.cuda.stream(stream):
+            ids = ((np.arange(prompt) * 7919) % 50000 + 42).astype(np.int32)   # distinct tokens: the experts all see rows
+            model.reset(42)
+            model.prefill(ids)
+            times = []
+            for _ in range(3):
+                model.reset(42)
+                stream.synchronize()
+                s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s0.record(stream)
+                model.prefill(ids)
+                e0.record(stream)
+                stream.synchronize()
+                times.append(s0.elapsed_time(e0) * 1e-3)
+            pt = sorted(times)[1]
+        model.check_flags()
+        out["prefill"] = {"tokens": prompt, "ms": pt * 1e3, "tok_s": prompt / pt,
+                          "how": "MoeDecoder.prefill: one pass over the prompt, median of 3 (eager launches; the expert "
+                                 "buckets read the job list back once per layer)"}
     if with_e2e:
         # end to end, model level: host token ids in, host logits out, every step (every rank does its own copies)
         tok = np.full(batch, 42, np.int32)
@@ -176,7 +199,7 @@ def run(args, extra=None):
                            "over ranks"},
             "gpu_launches": m["launches_per_step"] * args.steps, "clocks": m["clocks"],
             "exchange": None if world == 1 else "peer-memory stores over NVLink (csrc/ep.cu), one CUDA graph per step",
-            "load": m["load"], "strong": strong,
+            "load": m["load"], "strong": strong, "prefill": m.get("prefill"),
         }
         if world == 1:
             try:
