@@ -392,6 +392,11 @@ int32_t jq_moe_route_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, const
                          uint32_t* ids_dev, float* wts_dev, void* stream);
 int32_t jq_moe_experts_dev(jq_moe* m, const float* x_dev, uint64_t n_rows, const uint32_t* expert_ids_dev,
                            float* out_dev, void* stream);
+/* The expert matmuls alone (gate/up with SwiGLU, then down) over the job list that the last decode-sized
+ * jq_moe_forward*_dev / jq_moe_experts_dev call on this layer left on the device, reading the rows of x_dev
+ * (shaped as in that call).  For measuring the matmul kernels without routing and combine; the layer's output
+ * buffer is overwritten, no result is returned. */
+int32_t jq_moe_experts_replay_dev(jq_moe* m, const float* x_dev, void* stream);
 /* Routing of rmsnorm(x; norm_w, eps): the block's norm folded into the router kernel (up to eight tokens). */
 int32_t jq_moe_route_norm_dev(jq_moe* m, const float* x_dev, uint64_t n_tokens, const float* norm_w_dev, float eps,
                               const uint32_t* forced_ids_dev, uint32_t* ids_dev, float* wts_dev, void* stream);

@@ -73,6 +73,7 @@ _SIGNATURES = {
     "jq_moe_forward_dev": (i32, [vp, vp, u64, vp, vp, vp]),
     "jq_moe_route_dev": (i32, [vp, vp, u64, vp, vp, vp, vp]),
     "jq_moe_experts_dev": (i32, [vp, vp, u64, vp, vp, vp]),
+    "jq_moe_experts_replay_dev": (i32, [vp, vp, vp]),
     "jq_moe_route_norm_dev": (i32, [vp, vp, u64, vp, f32, vp, vp, vp, vp]),
     "jq_moe_status": (i32, [vp]),
     "jq_moe_last_routing": (i32, [vp, u64, vp, vp]),

@@ -86,6 +86,25 @@ def measure(args, batch: int, group, sample_load: bool = True, with_e2e: bool = 
             stream.synchronize()
         barrier()
         dt = max_over_ranks(s.elapsed_time(e) * 1e-3 / args.steps)
+        # the quantized matmuls of the step alone (the dominant kernel, gemv_mma_kernel: dense Q8_0 linears, grouped
+        # Q4_K experts over the routing the last step left, head), one CUDA graph, CUDA events
+        mm_dt = None
+        if with_e2e:
+            mm_graph = torch.cuda.CUDAGraph()
+            model.matmuls_only(stream.cuda_stream)
+            stream.synchronize()
+            with torch.cuda.graph(mm_graph, stream=stream):
+                model.matmuls_only(stream.cuda_stream)
+            for _ in range(3):
+                mm_graph.replay()
+            stream.synchronize()
+            s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s2.record(stream)
+            for _ in range(args.steps):
+                mm_graph.replay()
+            e2.record(stream)
+            stream.synchronize()
+            mm_dt = max_over_ranks(s2.elapsed_time(e2) * 1e-3 / args.steps)
         # load balance: rows each rank's experts were sent in the last layer of a step, sampled over a few steps
         load = None
         if world > 1 and sample_load:
@@ -101,7 +120,7 @@ def measure(args, batch: int, group, sample_load: bool = True, with_e2e: bool = 
             load = {"max_over_mean_rows_per_rank": float((a.max(axis=1) / np.maximum(a.mean(axis=1), 1e-9)).mean()),
                     "rows_per_rank_mean": float(a.mean()), "sampled": "last layer of 8 steps"}
     model.check_flags()
-    out = {"dt": dt, "clocks": clocks.summary(), "load": load, "cfg": cfg, "warmup": warmup,
+    out = {"dt": dt, "mm_dt": mm_dt, "clocks": clocks.summary(), "load": load, "cfg": cfg, "warmup": warmup,
            "launches_per_step": model.launches_per_step, "weight_bytes": model.weight_bytes}
     if prompt > 0:
         # the prompt in one pass (`forward(input [1, seq_len], 0)`): batched linears and the experts' buckets on the
@@ -165,7 +184,7 @@ def run(args, extra=None):
         group = dist.group.WORLD
     batch = args.batch
     m = measure(args, batch, group)
-    cfg, dt, e2e_dt = m["cfg"], m["dt"], m["e2e_dt"]
+    cfg, dt, e2e_dt, mm_dt = m["cfg"], m["dt"], m["e2e_dt"], m["mm_dt"]
     # strong scaling at a fixed global batch of 16 sequences (the configuration's "batch 16"): 16 / N per GPU
     strong = None
     if getattr(args, "strong", True) and 16 % world == 0:
@@ -186,12 +205,16 @@ def run(args, extra=None):
             "scaling": "weak", "vs_baseline": None,
             "dtype": "int8 codes x int8 activation planes -> int32, f32 scales and glue", "data": "synthetic",
             "config": moe_config(cfg, batch, world),
-            "roofline": {"bound": "hbm", "achieved": alg / dt / 1e9, "peak": peak, "unit": "GB/s",
-                         "frac": alg / dt / 1e9 / peak, "traffic": None, "peak_source": which,
-                         "kernel": "gemv_mma_kernel (Q8_0 attention + grouped Q4_K experts) inside the whole step",
-                         "note": "whole step (all kernels, and at N > 1 the exchange) over the weight bytes one rank "
-                                 "must read: attention + head once, 3 matrices per distinct expert touched",
-                         "bytes_per_step": alg},
+            "roofline": {"bound": "hbm", "achieved": alg / mm_dt / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": alg / mm_dt / 1e9 / peak, "traffic": None, "peak_source": which,
+                         "kernel": "gemv_mma_kernel: the step's quantized matmuls alone (per layer the Q8_0 QKV and output "
+                                   "projections and the grouped Q4_K gate/up and down products of the routed experts, "
+                                   "then the head), one CUDA graph, CUDA events",
+                         "bytes_per_step": alg, "ms": mm_dt * 1e3,
+                         "step_frac": alg / dt / 1e9 / peak,
+                         "note": "bytes = the weight bytes one rank must read per step: attention + head once, 3 matrices "
+                                 "per distinct expert touched; step_frac = the same bytes over the whole step (all "
+                                 "kernels, and at N > 1 the exchange)"},
             "e2e": {"value": world * batch / e2e_dt, "unit": "tok/s", "h2d_bytes_per_step": 4 * batch * world,
                     "d2h_bytes_per_step": 4 * batch * cfg.vocab * world,
                     "how": "model-level call with host buffers on every rank (forward_host): token ids host->device, "

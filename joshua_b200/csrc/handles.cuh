@@ -142,6 +142,8 @@ struct jq_moe {
     float* xn = nullptr;          // normalised tokens, for the paths that cannot fold the norm in
     float* bucket = nullptr;      // prefill path: gathered rows [P, hidden] + gate and up products [2][P, inter]
     uint64_t bucket_pairs = 0;
+    uint64_t last_rows = 0, last_pairs = 0;  // shape of the job list the last decode-sized call left (replay entry)
+    uint32_t last_rpj = 0;
     jq::GemmTile* tiles = nullptr;  // prefill path: tile list of the grouped tile GEMM
     uint64_t tiles_cap = 0;
     int* bad_host = nullptr;  // pinned, device-visible: an expert id was out of range

@@ -337,6 +337,7 @@ int32_t jq_moe_experts_list(jq_moe* m, const float* x_dev, uint64_t n_rows, cons
     JQ_CUDA(jq::launch_moe_jobs(expert_ids_dev, (uint32_t)n_rows, 1, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
                                 m->n_jobs, m->n_list, m->bad_dev, s));
     if (!m->ctx->force_f32 && live_rows >= BUCKET_ROWS_PER_EXPERT * c.n_expert) return run_experts_bucketed(m, x_dev, n_rows, n_rows, s);
+    m->last_rows = m->last_pairs = n_rows, m->last_rpj = rpj;
     return run_experts(m, x_dev, n_rows, n_rows, rpj, s);
 }
 
@@ -533,8 +534,9 @@ int32_t jq_moe_forward_norm_add_dev(jq_moe* m, const float* x_dev, uint64_t T, c
     const bool bucketed = !fused && !m->ctx->force_f32 && P >= thr * c.n_expert;
     if (bucketed) {
         if (int32_t rc = run_experts_bucketed(m, x_in, T, P, s)) return rc;
-    } else if (int32_t rc = run_experts(m, x_in, T, P, rpj, s, nw, eps)) {
-        return rc;
+    } else {
+        m->last_rows = T, m->last_pairs = P, m->last_rpj = rpj;
+        if (int32_t rc = run_experts(m, x_in, T, P, rpj, s, nw, eps)) return rc;
     }
     const float* shared = nullptr;
     if (m->sh_gate) {
@@ -543,6 +545,13 @@ int32_t jq_moe_forward_norm_add_dev(jq_moe* m, const float* x_dev, uint64_t T, c
     }
     JQ_CUDA(jq::launch_moe_combine(m->out, m->inv, m->wts, shared, (uint32_t)T, c.n_used, c.hidden, y_dev, s, residual_dev));
     return jq::OK;
+}
+
+int32_t jq_moe_experts_replay_dev(jq_moe* m, const float* x_dev, void* stream) {
+    if (!m || !x_dev) return jq_fail(jq::E_INVALID, "jq_moe_experts_replay_dev: NULL argument");
+    if (!m->gate || m->last_rpj == 0)
+        return jq_fail(jq::E_INVALID, "jq_moe_experts_replay_dev: no decode-sized call has left a job list on this layer");
+    return run_experts(m, x_dev, m->last_rows, m->last_pairs, m->last_rpj, static_cast<cudaStream_t>(stream));
 }
 
 #ifdef JQ_PROFILING

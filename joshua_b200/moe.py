@@ -120,5 +120,9 @@ class Moe:
         check(_lib.lib().jq_moe_experts_dev(self._h, x_rows.data_ptr(), R, expert_ids.data_ptr(),
                                             out_rows.data_ptr(), self._stream(x_rows, stream)))
 
+    def experts_replay_dev(self, x, stream=None) -> None:
+        """The expert matmuls alone over the job list of the last decode-sized call (a measurement aid)."""
+        check(_lib.lib().jq_moe_experts_replay_dev(self._h, x.data_ptr(), self._stream(x, stream)))
+
     def status(self) -> None:
         check(_lib.lib().jq_moe_status(self._h))

@@ -113,6 +113,25 @@ class MoeDecoder(LlamaDecoder):
     def _has_dense_ffn(self) -> bool:
         return False
 
+    def matmuls_only(self, stream=None) -> None:
+        """The quantized matmuls of one step back to back, over the routing the last step left on the device: QKV and
+        output projection per layer, the grouped gate/up and down products of the routed experts, the head (the
+        kernel-level roofline probe; norms, attention, router and combine are left out)."""
+        L, c, B = _lib.lib(), self.cfg, self.batch
+        s = self.torch.cuda.current_stream(self.dev).cuda_stream if stream is None else stream
+        h, P = c.hidden, lambda t: t.data_ptr()
+        if self.world > 1 and getattr(self, "_probe_rows", None) is None:
+            self._probe_rows = self.torch.zeros(self.exchange.rows, h, dtype=self.torch.float32, device=self.dev)
+        for i, ly in enumerate(self.layers):
+            _lib.check(L.jq_matmul_t_dev(ly["wqkv"]._h, B, h, c.qkv_rows, P(self.xn), P(self.qkv), s))
+            _lib.check(L.jq_matmul_t_dev(ly["wo"]._h, B, c.q_heads * c.head_dim, h, P(self.attn), P(self.o), s))
+            f = self.ffn_layers[i]
+            if "moe" in f:
+                f["moe"].experts_replay_dev(self.x, stream=s)
+            else:
+                f["experts"].experts_replay_dev(self._probe_rows, stream=s)
+        _lib.check(L.jq_matmul_t_dev(self.output._h, B, h, c.vocab, P(self.xn), P(self.logits), s))
+
     def step(self, stream=None) -> None:
         if not hasattr(self, "_layer_index"):
             self._layer_index = {id(ly): i for i, ly in enumerate(self.layers)}
