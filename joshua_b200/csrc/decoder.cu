@@ -242,90 +242,143 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const float* __res
 
 // Prefill: `seq` new tokens of ONE sequence at positions pos0 .. pos0 + seq - 1, causal over the cache (which
 // already holds their k / v rows): out[s, head, :] = softmax(q_s . K[0 .. pos0 + s]^T / sqrt(hd)) V
-// (src/quantized_qwen3_moe.rs:366-386 with the causal mask of :805-812).  One CTA per (16 queries, q head); a warp owns
-// four queries; keys are taken 32 at a time - lane <-> key for the scores, lane <-> output dimensions for the
-// V sum - with the usual running maximum / sum, in position order.  f32 throughout.
-constexpr uint32_t PF_TQ = 16, PF_TK = 32;
+// (src/quantized_qwen3_moe.rs:366-386 with the causal mask of :805-812).  One CTA per (64 queries, q head).
+constexpr uint32_t PF_TQ = 64, PF_TK = 64, PF_THREADS = 256;
 
+// 64 queries of one head against the keys they may see, 64 keys at a time, f32 throughout.  Threads form a 16 x 16
+// grid: thread (ty, tx) holds the scores of queries 4ty .. 4ty+3 against keys tx, tx+16, tx+32, tx+48 of the tile
+// (a 4 x 4 register tile, operands read from shared memory as float4 along the head dimension; rows are padded by
+// four floats so that the eight lanes of a quarter warp hit distinct banks) and the outputs of the same four
+// queries for dimensions 4tx .. 4tx+3 (+64).  Softmax is the running (max, sum) form; the probabilities go through
+// shared memory key-major so that the P.V product reads them as one float4 per key.  K and V tiles share one
+// buffer (85 KB of shared memory in all, two CTAs per SM).
 template <uint32_t HD>
-__global__ void __launch_bounds__(128) attention_prefill_kernel(const float* __restrict__ q, const float* __restrict__ cache_k,
-                                                                const float* __restrict__ cache_v,
-                                                                const int32_t* __restrict__ pos, uint32_t seq, uint32_t nq,
-                                                                uint32_t nkv, uint32_t max_ctx, float* __restrict__ out,
-                                                                int32_t* __restrict__ bad_pos) {
-    constexpr uint32_t DPL = HD / 32;  // output dimensions per lane
-    __shared__ float sq[PF_TQ][HD];
-    __shared__ float sk[PF_TK][HD + 1];
-    __shared__ float sv[PF_TK][HD];
+__global__ void __launch_bounds__(PF_THREADS, 2)
+    attention_prefill_kernel(const float* __restrict__ q, const float* __restrict__ cache_k, const float* __restrict__ cache_v,
+                             const int32_t* __restrict__ pos, uint32_t seq, uint32_t nq, uint32_t nkv, uint32_t max_ctx,
+                             float* __restrict__ out, int32_t* __restrict__ bad_pos) {
+    constexpr uint32_t LDQ = HD + 4, LDP = PF_TQ + 4, NV4 = HD / 64;  // row strides (floats), float4 of output per thread
+    extern __shared__ __align__(16) float pf_smem[];
+    float* sq = pf_smem;                  // [PF_TQ][LDQ] queries
+    float* skv = sq + PF_TQ * LDQ;        // [PF_TK][LDQ] the key tile, then the value tile
+    float* sp = skv + PF_TK * LDQ;        // [PF_TK][LDP] probabilities, key-major
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     pdl_wait_();
     const uint32_t head = blockIdx.y, kvh = head / (nq / nkv), s0 = blockIdx.x * PF_TQ;
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int32_t p0 = pos[0];
     if (p0 < 0 || (uint64_t)p0 + seq > max_ctx) {
-        if (threadIdx.x == 0 && bad_pos) atomicExch(bad_pos, 1);
+        if (tid == 0 && bad_pos) atomicExch(bad_pos, 1);
         return;
     }
-    for (uint32_t i = threadIdx.x; i < PF_TQ * HD; i += blockDim.x) {
-        const uint32_t r = i / HD, c = i % HD, s = s0 + r;
-        sq[r][c] = s < seq ? q[((uint64_t)s * nq + head) * HD + c] : 0.0f;
+    for (uint32_t i = tid; i < PF_TQ * (HD / 4); i += PF_THREADS) {
+        const uint32_t r = i / (HD / 4), c4 = i % (HD / 4), sr = s0 + r;
+        const float4 v = sr < seq ? *reinterpret_cast<const float4*>(q + ((uint64_t)sr * nq + head) * HD + 4 * c4)
+                                  : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        *reinterpret_cast<float4*>(sq + r * LDQ + 4 * c4) = v;
     }
     const float* K = cache_k + (uint64_t)kvh * max_ctx * HD;
     const float* V = cache_v + (uint64_t)kvh * max_ctx * HD;
     const float scale = rsqrtf((float)HD);
-    float acc[4][DPL], mx[4], sum[4];
+    float o[4][4 * NV4], mx[4], sum[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         mx[i] = -INFINITY, sum[i] = 0.0f;
 #pragma unroll
-        for (uint32_t d = 0; d < DPL; ++d) acc[i][d] = 0.0f;
+        for (uint32_t d = 0; d < 4 * NV4; ++d) o[i][d] = 0.0f;
     }
-    const uint32_t last_q = min(seq, s0 + PF_TQ) - 1;          // newest query of the tile
-    const uint32_t n_keys = (uint32_t)p0 + last_q + 1;         // keys the tile can see
-    for (uint32_t t0 = 0; t0 < n_keys; t0 += PF_TK) {
-        __syncthreads();
-        for (uint32_t i = threadIdx.x; i < PF_TK * HD; i += blockDim.x) {
-            const uint32_t r = i / HD, c = i % HD, t = t0 + r;
-            sk[r][c] = t < n_keys ? K[(uint64_t)t * HD + c] : 0.0f;
-            sv[r][c] = t < n_keys ? V[(uint64_t)t * HD + c] : 0.0f;
+    const uint32_t last_q = min(seq, s0 + PF_TQ) - 1;   // newest query of the tile
+    const uint32_t n_keys = (uint32_t)p0 + last_q + 1;  // keys the tile can see
+    auto load_tile = [&](const float* src, uint32_t t0) {
+        for (uint32_t i = tid; i < PF_TK * (HD / 4); i += PF_THREADS) {
+            const uint32_t r = i / (HD / 4), c4 = i % (HD / 4), t = t0 + r;
+            const float4 v = t < n_keys ? *reinterpret_cast<const float4*>(src + (uint64_t)t * HD + 4 * c4)
+                                        : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            *reinterpret_cast<float4*>(skv + r * LDQ + 4 * c4) = v;
         }
+    };
+    for (uint32_t t0 = 0; t0 < n_keys; t0 += PF_TK) {
+        __syncthreads();  // the previous tile's P.V product has read skv and sp
+        load_tile(K, t0);
         __syncthreads();
+        float sc[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sc[i][j] = 0.0f;
+#pragma unroll 4
+        for (uint32_t c = 0; c < HD; c += 4) {
+            float4 a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(sq + (4 * ty + i) * LDQ + c);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = *reinterpret_cast<const float4*>(skv + (tx + 16 * j) * LDQ + c);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    sc[i][j] = fmaf(a[i].w, b[j].w, fmaf(a[i].z, b[j].z, fmaf(a[i].y, b[j].y, fmaf(a[i].x, b[j].x, sc[i][j]))));
+        }
+        // causal mask, running softmax; a row's 64 scores sit in the 16 threads that share its ty
+        float pr[4][4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const uint32_t s = s0 + 4 * warp + i;
-            if (s >= seq) continue;                              // warp-uniform
-            const uint32_t visible = (uint32_t)p0 + s + 1;       // keys 0 .. p0 + s
-            if (t0 >= visible) continue;
-            float sc = 0.0f;
-#pragma unroll 8
-            for (uint32_t c = 0; c < HD; ++c) sc = fmaf(sq[4 * warp + i][c], sk[lane][c], sc);
-            sc = t0 + lane < visible ? sc * scale : -INFINITY;
-            float cm = sc;
+            const uint32_t visible = (uint32_t)p0 + s0 + 4 * ty + i + 1;  // keys 0 .. p0 + s (rows past seq: never stored)
+            float cm = -INFINITY;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xFFFFFFFFu, cm, o));
-            const float nm = fmaxf(mx[i], cm);
-            const float corr = expf(mx[i] - nm);                 // 0 on the first chunk (mx = -inf)
-            const float pr = expf(sc - nm);                      // 0 for masked keys
-            float ps = pr;
+            for (int j = 0; j < 4; ++j) {
+                sc[i][j] = t0 + tx + 16 * j < visible ? sc[i][j] * scale : -INFINITY;
+                cm = fmaxf(cm, sc[i][j]);
+            }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xFFFFFFFFu, ps, o);
+            for (int off = 8; off > 0; off >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xFFFFFFFFu, cm, off));
+            const float nm = fmaxf(mx[i], cm);       // finite from the first tile on: key 0 is visible to every query
+            const float corr = expf(mx[i] - nm);     // 0 on the first tile (mx = -inf)
+            float ps = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                pr[i][j] = expf(sc[i][j] - nm);      // 0 for masked keys
+                ps += pr[i][j];
+            }
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) ps += __shfl_xor_sync(0xFFFFFFFFu, ps, off);
             sum[i] = sum[i] * corr + ps;
             mx[i] = nm;
 #pragma unroll
-            for (uint32_t d = 0; d < DPL; ++d) acc[i][d] *= corr;
-            for (uint32_t j = 0; j < PF_TK; ++j) {
-                const float pj = __shfl_sync(0xFFFFFFFFu, pr, j);
+            for (uint32_t d = 0; d < 4 * NV4; ++d) o[i][d] *= corr;
+        }
 #pragma unroll
-                for (uint32_t d = 0; d < DPL; ++d) acc[i][d] = fmaf(pj, sv[j][lane + 32 * d], acc[i][d]);
+        for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<float4*>(sp + (tx + 16 * j) * LDP + 4 * ty) = make_float4(pr[0][j], pr[1][j], pr[2][j], pr[3][j]);
+        __syncthreads();  // every score has been formed from the key tile; the probabilities are in place
+        load_tile(V, t0);
+        __syncthreads();
+#pragma unroll 4
+        for (uint32_t kk = 0; kk < PF_TK; ++kk) {
+            const float4 pv = *reinterpret_cast<const float4*>(sp + kk * LDP + 4 * ty);
+            const float pq[4] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+            for (uint32_t h = 0; h < NV4; ++h) {
+                const float4 vv = *reinterpret_cast<const float4*>(skv + kk * LDQ + 4 * tx + 64 * h);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    o[i][4 * h + 0] = fmaf(pq[i], vv.x, o[i][4 * h + 0]);
+                    o[i][4 * h + 1] = fmaf(pq[i], vv.y, o[i][4 * h + 1]);
+                    o[i][4 * h + 2] = fmaf(pq[i], vv.z, o[i][4 * h + 2]);
+                    o[i][4 * h + 3] = fmaf(pq[i], vv.w, o[i][4 * h + 3]);
+                }
             }
         }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const uint32_t s = s0 + 4 * warp + i;
-        if (s < seq) {
+        const uint32_t sr = s0 + 4 * ty + i;
+        if (sr < seq) {
+            const float inv = 1.0f / sum[i];
 #pragma unroll
-            for (uint32_t d = 0; d < DPL; ++d) out[((uint64_t)s * nq + head) * HD + lane + 32 * d] = acc[i][d] / sum[i];
+            for (uint32_t h = 0; h < NV4; ++h)
+                *reinterpret_cast<float4*>(out + ((uint64_t)sr * nq + head) * HD + 4 * tx + 64 * h) =
+                    make_float4(o[i][4 * h] * inv, o[i][4 * h + 1] * inv, o[i][4 * h + 2] * inv, o[i][4 * h + 3] * inv);
         }
     }
 }
@@ -572,13 +625,19 @@ cudaError_t launch_attention_prefill(const float* q, const float* cache_k, const
                                      uint32_t seq, uint32_t nq, uint32_t nkv, uint32_t hd, uint32_t max_ctx, float* out,
                                      int32_t* bad_pos, cudaStream_t s) {
     const dim3 grid((seq + PF_TQ - 1) / PF_TQ, nq);
+    const size_t smem = (size_t)((PF_TQ + PF_TK) * (hd + 4) + PF_TK * (PF_TQ + 4)) * 4;
     cudaError_t e;
-    if (hd == 64)
-        e = launch_pdl(attention_prefill_kernel<64>, grid, 128, 0, s, q, cache_k, cache_v, pos, seq, nq, nkv, max_ctx, out, bad_pos);
-    else if (hd == 128)
-        e = launch_pdl(attention_prefill_kernel<128>, grid, 128, 0, s, q, cache_k, cache_v, pos, seq, nq, nkv, max_ctx, out, bad_pos);
-    else
+    if (hd == 64) {
+        static bool configured[MAX_DEVICES] = {};
+        if (cudaError_t ce = set_max_smem_once(attention_prefill_kernel<64>, (int)smem, configured); ce != cudaSuccess) return ce;
+        e = launch_pdl(attention_prefill_kernel<64>, grid, PF_THREADS, smem, s, q, cache_k, cache_v, pos, seq, nq, nkv, max_ctx, out, bad_pos);
+    } else if (hd == 128) {
+        static bool configured[MAX_DEVICES] = {};
+        if (cudaError_t ce = set_max_smem_once(attention_prefill_kernel<128>, (int)smem, configured); ce != cudaSuccess) return ce;
+        e = launch_pdl(attention_prefill_kernel<128>, grid, PF_THREADS, smem, s, q, cache_k, cache_v, pos, seq, nq, nkv, max_ctx, out, bad_pos);
+    } else {
         return cudaErrorInvalidValue;
+    }
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
