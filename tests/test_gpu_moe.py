@@ -7,7 +7,7 @@ from joshua_b200 import synth
 from joshua_b200._lib import JoshuaB200Error
 from joshua_b200.moe import GATE_SIGMOID, GATE_SOFTMAX, GATE_SQRT_SOFTPLUS, OOB_SKIP, Moe, MoeConfig
 from joshua_b200.qtensor import QTensor
-from tests.gpu_util import assert_close
+from tests.gpu_util import assert_close, bits
 
 pytestmark = pytest.mark.gpu
 
@@ -172,6 +172,24 @@ def test_device_entries_and_expert_rows():
     y2 = (out.reshape(T, cfg.n_used, cfg.hidden) * wts[:, :, None]).sum(dim=1)
     torch.cuda.synchronize()
     assert_close(y2.cpu().numpy(), want)
+    # the measurement entry: the expert matmuls alone over the job list of the last call; it changes no later result
+    moe.forward_dev(xd, yd)
+    moe.experts_replay_dev(xd)
+    moe.experts_replay_dev(xd)
+    y3 = torch.empty_like(xd)
+    moe.forward_dev(xd, y3)
+    torch.cuda.synchronize()
+    moe.status()
+    assert np.array_equal(bits(y3.cpu().numpy()), bits(yd.cpu().numpy()))
+
+
+def test_replay_needs_a_previous_call():
+    cfg = MoeConfig(gating=GATE_SOFTMAX, n_expert=16, n_used=4, hidden=512, inter=256)
+    moe, *_ = build(cfg, synth.Q4_K, seed=42)
+    import torch
+
+    with pytest.raises(JoshuaB200Error, match="job list"):
+        moe.experts_replay_dev(torch.zeros(1, cfg.hidden, device="cuda"))
 
 
 def test_create_rejects_bad_banks():
