@@ -142,8 +142,7 @@ def measure(args, batch: int, group, sample_load: bool = True, with_e2e: bool = 
             pt = sorted(times)[1]
         model.check_flags()
         out["prefill"] = {"tokens": prompt, "ms": pt * 1e3, "tok_s": prompt / pt,
-                          "how": "MoeDecoder.prefill: one pass over the prompt, median of 3 (eager launches; the expert "
-                                 "buckets read the job list back once per layer)"}
+                          "how": "MoeDecoder.prefill: one pass over the prompt, median of 3 (eager launches)"}
     if with_e2e:
         # end to end, model level: host token ids in, host logits out, every step (every rank does its own copies)
         tok = np.full(batch, 42, np.int32)

@@ -89,8 +89,10 @@ cudaError_t launch_gemm_tc(uint32_t type, const uint8_t* w, uint64_t n, uint64_t
 // Grouped form for routed experts at prefill sizes: one launch over a device list of tiles, each up to 128
 // consecutive rows of the expert-sorted activation matrix x[rows, k] against that expert's slice of a bank
 // ([n_expert][n, k] blocks, `expert_bytes` apart).  With `bank_b` / `dst_b` the same activations go through two
-// banks in one launch (gate and up).  dst[row, n] is written for the tiles' rows only.  The first `n_narrow`
-// tiles of the list must hold at most 32 rows each (they run as narrower tiles).  False from
+// banks in one launch (gate and up).  dst[row, n] is written for the tiles' rows only.  Two lists on the device:
+// `narrow` (tiles of at most 32 rows, run as 32-token tiles) and `wide`, their lengths in counts[0] and counts[1]
+// (device memory, read by the kernels: the launches cover max_narrow / max_wide entries and the surplus CTAs
+// leave at once), so that no host read stands between the routing and the products.  False from
 // gemm_tc_grouped_supports = shapes this form does not take (the caller then runs one product per expert).
 struct GemmTile {
     uint32_t expert;
@@ -101,8 +103,8 @@ struct GemmTile {
 bool gemm_tc_grouped_supports(uint32_t type, const uint8_t* bank, uint64_t n, uint64_t k);
 cudaError_t launch_gemm_tc_grouped(uint32_t type, const uint8_t* bank_a, const uint8_t* bank_b, uint64_t expert_bytes,
                                    uint64_t n, uint64_t k, const float* x, uint64_t rows, float* dst_a, float* dst_b,
-                                   const GemmTile* tiles, uint32_t n_tiles, uint32_t n_narrow, void* scratch,
-                                   int* error_flag, cudaStream_t s);
+                                   const GemmTile* narrow, uint32_t max_narrow, const GemmTile* wide, uint32_t max_wide,
+                                   const uint32_t* counts, void* scratch, int* error_flag, cudaStream_t s);
 
 // One unit of grouped (MoE) work: up to 8 consecutive positions of the expert-sorted activation list,
 // all routed to `expert`.
@@ -195,6 +197,12 @@ cudaError_t launch_moe_route_fused(const float* x, const float* norm_w, float ep
 cudaError_t launch_moe_combine(const float* out, const uint32_t* inv, const float* wts, const float* shared, uint32_t T,
                                uint32_t K, uint32_t h, float* y, cudaStream_t s, const float* residual = nullptr);
 cudaError_t launch_swiglu(const float* g, const float* u, uint64_t n, float clamp, float* out, cudaStream_t s);
+// the same over the first *n_rows (at most max_rows) rows of [rows, inter]
+cudaError_t launch_swiglu_rows(const float* g, const float* u, const uint32_t* n_rows, uint32_t max_rows, uint32_t inter,
+                               float clamp, float* out, cudaStream_t s);
+// tile lists of the grouped tile GEMM from the job list: counts = {narrow tiles (<= 32 rows), wide tiles, list rows}
+cudaError_t launch_moe_tiles(const MoeJob* jobs, const uint32_t* n_jobs, const uint32_t* n_list, uint32_t E, GemmTile* narrow,
+                             GemmTile* wide, uint32_t* counts, cudaStream_t s);
 
 // decoder.cu: the element-wise and attention steps around the matmuls of a decode step
 cudaError_t launch_rmsnorm(const float* x, const float* res, const float* w, float eps, uint64_t rows, uint32_t h,

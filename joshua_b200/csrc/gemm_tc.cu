@@ -499,9 +499,10 @@ template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE>
 __global__ void __launch_bounds__(TS_THREADS, 1)
     gemm_ts_kernel(const uint8_t* __restrict__ w_a, uint64_t n, uint64_t k, const __grid_constant__ CUtensorMap map_hi,
                    const __grid_constant__ CUtensorMap map_lo, uint64_t m_rows, float* __restrict__ dst_a,
-                   int* __restrict__ error_flag, const GemmTile* __restrict__ tiles, uint64_t expert_bytes,
-                   const uint8_t* __restrict__ w_b, float* __restrict__ dst_b) {
+                   int* __restrict__ error_flag, const GemmTile* __restrict__ tiles, const uint32_t* __restrict__ n_tiles,
+                   uint64_t expert_bytes, const uint8_t* __restrict__ w_b, float* __restrict__ dst_b) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
+    if (tiles != nullptr && blockIdx.y >= *n_tiles) return;  // the launch covers the list's capacity, not its length
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t PLANE_B = N_TILE * 128;
     constexpr uint32_t STAGE = 2 * PLANE_B;  // activations hi | lo
@@ -804,7 +805,7 @@ cudaError_t launch_ts_tile(const uint8_t* w, uint64_t n, uint64_t k, const float
     if (e == cudaSuccess) e = tensor_map_for(x_lo, m, k, N_TILE, &map_lo);
     if (e != cudaSuccess) return e;
     dim3 grid((unsigned)((n + TC_M - 1) / TC_M), (unsigned)((m + N_TILE - 1) / N_TILE));
-    kern<<<grid, TS_THREADS, smem, s>>>(w, n, k, map_hi, map_lo, m, dst, error_flag, nullptr, 0, nullptr, nullptr);
+    kern<<<grid, TS_THREADS, smem, s>>>(w, n, k, map_hi, map_lo, m, dst, error_flag, nullptr, nullptr, 0, nullptr, nullptr);
     return cudaGetLastError();
 }
 
@@ -823,7 +824,8 @@ cudaError_t launch_ts(const uint8_t* w, uint64_t n, uint64_t k, const float* x_h
 template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES, int N_TILE>
 cudaError_t launch_grouped_tiles(const uint8_t* bank_a, const uint8_t* bank_b, uint64_t expert_bytes, uint64_t n, uint64_t k,
                                  const float* x_hi, const float* x_lo, uint64_t rows, float* dst_a, float* dst_b,
-                                 const GemmTile* tiles, uint32_t n_tiles, int* error_flag, cudaStream_t s) {
+                                 const GemmTile* tiles, uint32_t max_tiles, const uint32_t* n_tiles, int* error_flag,
+                                 cudaStream_t s) {
     constexpr uint32_t STAGE = 2 * N_TILE * 128;
     constexpr uint32_t RAW = TC_M * ((window_elems(TYPE) / ELEMS * BYTES / 4) | 1u) * 4;
     size_t smem = (size_t)TS_PHASES * STAGE + RAW + 1024;
@@ -834,35 +836,31 @@ cudaError_t launch_grouped_tiles(const uint8_t* bank_a, const uint8_t* bank_b, u
     cudaError_t e = tensor_map_for(x_hi, rows, k, N_TILE, &map_hi);
     if (e == cudaSuccess) e = tensor_map_for(x_lo, rows, k, N_TILE, &map_lo);
     if (e != cudaSuccess) return e;
-    // the tile list is walked along grid.y (at most 65535 entries a launch)
-    for (uint32_t t0 = 0; t0 < n_tiles; t0 += 65535) {
-        dim3 grid((unsigned)((n + TC_M - 1) / TC_M), std::min<uint32_t>(65535, n_tiles - t0), bank_b ? 2 : 1);
-        kern<<<grid, TS_THREADS, smem, s>>>(bank_a, n, k, map_hi, map_lo, rows, dst_a, error_flag, tiles + t0, expert_bytes,
-                                            bank_b, dst_b);
-        if (cudaError_t le = cudaGetLastError(); le != cudaSuccess) return le;
-    }
-    return cudaSuccess;
+    if (max_tiles > 65535) return cudaErrorInvalidValue;  // the tile list is walked along grid.y
+    dim3 grid((unsigned)((n + TC_M - 1) / TC_M), max_tiles, bank_b ? 2 : 1);
+    kern<<<grid, TS_THREADS, smem, s>>>(bank_a, n, k, map_hi, map_lo, rows, dst_a, error_flag, tiles, n_tiles, expert_bytes,
+                                        bank_b, dst_b);
+    return cudaGetLastError();
 }
 
-// The first `n_narrow` tiles of the list hold at most 32 rows each and run as 32-token tiles (a quarter of the
-// tensor-core work and of the activation traffic of a 128-token tile), the rest as 128-token tiles.
 template <uint32_t TYPE, uint32_t ELEMS, uint32_t BYTES>
 cudaError_t launch_grouped_type(const uint8_t* bank_a, const uint8_t* bank_b, uint64_t expert_bytes, uint64_t n, uint64_t k,
-                                const float* x, uint64_t rows, float* dst_a, float* dst_b, const GemmTile* tiles,
-                                uint32_t n_tiles, uint32_t n_narrow, float* scratch, int* error_flag, cudaStream_t s) {
+                                const float* x, uint64_t rows, float* dst_a, float* dst_b, const GemmTile* narrow,
+                                uint32_t max_narrow, const GemmTile* wide, uint32_t max_wide, const uint32_t* counts,
+                                float* scratch, int* error_flag, cudaStream_t s) {
     float* x_hi = scratch;
     float* x_lo = scratch + ((rows * k + 63) & ~(uint64_t)63);
     const uint64_t n4 = rows * k / 4;
     split_tf32_kernel<<<(unsigned)std::min<uint64_t>((n4 + 255) / 256, 148 * 16), 256, 0, s>>>(x, n4, x_hi, x_lo);
     if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
-    if (n_narrow) {
+    if (max_narrow) {
         cudaError_t e = launch_grouped_tiles<TYPE, ELEMS, BYTES, 32>(bank_a, bank_b, expert_bytes, n, k, x_hi, x_lo, rows, dst_a,
-                                                                      dst_b, tiles, n_narrow, error_flag, s);
+                                                                      dst_b, narrow, max_narrow, counts, error_flag, s);
         if (e != cudaSuccess) return e;
     }
-    if (n_tiles > n_narrow)
+    if (max_wide)
         return launch_grouped_tiles<TYPE, ELEMS, BYTES, 128>(bank_a, bank_b, expert_bytes, n, k, x_hi, x_lo, rows, dst_a, dst_b,
-                                                             tiles + n_narrow, n_tiles - n_narrow, error_flag, s);
+                                                             wide, max_wide, counts + 1, error_flag, s);
     return cudaSuccess;
 }
 
@@ -913,28 +911,21 @@ bool gemm_tc_grouped_supports(uint32_t type, const uint8_t* bank, uint64_t n, ui
 
 cudaError_t launch_gemm_tc_grouped(uint32_t type, const uint8_t* bank_a, const uint8_t* bank_b, uint64_t expert_bytes,
                                    uint64_t n, uint64_t k, const float* x, uint64_t rows, float* dst_a, float* dst_b,
-                                   const GemmTile* tiles, uint32_t n_tiles, uint32_t n_narrow, void* scratch_v,
-                                   int* error_flag, cudaStream_t s) {
+                                   const GemmTile* narrow, uint32_t max_narrow, const GemmTile* wide, uint32_t max_wide,
+                                   const uint32_t* counts, void* scratch_v, int* error_flag, cudaStream_t s) {
     float* scratch = static_cast<float*>(scratch_v);
-    if (n_tiles == 0) return cudaSuccess;
+#define JQ_GROUPED(T, E, B)                                                                                              \
+    return launch_grouped_type<T, E, B>(bank_a, bank_b, expert_bytes, n, k, x, rows, dst_a, dst_b, narrow, max_narrow, wide, \
+                                        max_wide, counts, scratch, error_flag, s)
     switch (type) {
-        case T_Q8_0:
-            return launch_grouped_type<T_Q8_0, 32, 34>(bank_a, bank_b, expert_bytes, n, k, x, rows, dst_a, dst_b, tiles, n_tiles,
-                                                       n_narrow, scratch, error_flag, s);
-        case T_Q2_K:
-            return launch_grouped_type<T_Q2_K, 256, 84>(bank_a, bank_b, expert_bytes, n, k, x, rows, dst_a, dst_b, tiles, n_tiles,
-                                                        n_narrow, scratch, error_flag, s);
-        case T_Q4_K:
-            return launch_grouped_type<T_Q4_K, 256, 144>(bank_a, bank_b, expert_bytes, n, k, x, rows, dst_a, dst_b, tiles,
-                                                         n_tiles, n_narrow, scratch, error_flag, s);
-        case T_IQ2_XXS:
-            return launch_grouped_type<T_IQ2_XXS, 256, 66>(bank_a, bank_b, expert_bytes, n, k, x, rows, dst_a, dst_b, tiles,
-                                                           n_tiles, n_narrow, scratch, error_flag, s);
-        case T_MXFP4:
-            return launch_grouped_type<T_MXFP4, 32, 17>(bank_a, bank_b, expert_bytes, n, k, x, rows, dst_a, dst_b, tiles, n_tiles,
-                                                        n_narrow, scratch, error_flag, s);
+        case T_Q8_0: JQ_GROUPED(T_Q8_0, 32, 34);
+        case T_Q2_K: JQ_GROUPED(T_Q2_K, 256, 84);
+        case T_Q4_K: JQ_GROUPED(T_Q4_K, 256, 144);
+        case T_IQ2_XXS: JQ_GROUPED(T_IQ2_XXS, 256, 66);
+        case T_MXFP4: JQ_GROUPED(T_MXFP4, 32, 17);
         default: return cudaErrorInvalidValue;
     }
+#undef JQ_GROUPED
 }
 
 void gemm_tc_set_trace(unsigned long long* dev_buf) { g_gemm_trace = dev_buf; }

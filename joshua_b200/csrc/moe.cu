@@ -485,6 +485,61 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const float* __restrict
     }
 }
 
+// Tile list of the grouped tile GEMM from the job list (jobs of one expert are consecutive and cover consecutive
+// rows): an expert's rows are cut into tiles of 128; a last piece of at most 32 rows goes to the narrow list,
+// anything else to the wide list.  counts = {narrow tiles, wide tiles, rows in the list}.  Which slot of a list a
+// tile takes depends on timing; the products do not (every tile is computed on its own).  One CTA.
+__global__ void __launch_bounds__(1024) moe_tiles_kernel(const MoeJob* __restrict__ jobs, const uint32_t* __restrict__ n_jobs,
+                                                         const uint32_t* __restrict__ n_list, uint32_t E,
+                                                         GemmTile* __restrict__ narrow, GemmTile* __restrict__ wide,
+                                                         uint32_t* __restrict__ counts) {
+    __shared__ uint32_t s_row0[MAX_EXPERTS], s_cnt[MAX_EXPERTS], s_n[2];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (uint32_t e = threadIdx.x; e < E; e += blockDim.x) s_row0[e] = 0xFFFFFFFFu, s_cnt[e] = 0;
+    if (threadIdx.x < 2) s_n[threadIdx.x] = 0;
+    __syncthreads();
+    const uint32_t nj = *n_jobs;
+    for (uint32_t j = threadIdx.x; j < nj; j += blockDim.x) {
+        const MoeJob jb = jobs[j];
+        if (jb.expert < E) {
+            atomicMin(&s_row0[jb.expert], jb.row0);
+            atomicAdd(&s_cnt[jb.expert], jb.cnt);
+        }
+    }
+    __syncthreads();
+    for (uint32_t e = threadIdx.x; e < E; e += blockDim.x) {
+        const uint32_t cnt = s_cnt[e], row0 = s_row0[e];
+        for (uint32_t r = 0; r < cnt; r += 128) {
+            const uint32_t c = min(128u, cnt - r);
+            GemmTile t = {e, row0 + r, c, 0};
+            if (c <= 32)
+                narrow[atomicAdd(&s_n[0], 1u)] = t;
+            else
+                wide[atomicAdd(&s_n[1], 1u)] = t;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) counts[0] = s_n[0], counts[1] = s_n[1], counts[2] = *n_list;
+}
+
+// SwiGLU over the first *n_rows rows of [rows, inter] (rows of the expert-sorted list that exist).
+__global__ void __launch_bounds__(256) swiglu_rows_kernel(const float* __restrict__ g, const float* __restrict__ u,
+                                                          const uint32_t* __restrict__ n_rows, uint32_t max_rows, uint32_t inter,
+                                                          float clamp, float* __restrict__ out) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint64_t n = (uint64_t)min(*n_rows, max_rows) * inter;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        float gv = g[i], uv = u[i];
+        if (clamp > 0.0f) {
+            gv = fminf(gv, clamp);
+            uv = fmaxf(-clamp, fminf(uv, clamp));
+        }
+        out[i] = gv / (1.0f + expf(-gv)) * uv;
+    }
+}
+
 unsigned blocks_for(uint64_t work, unsigned per_block) {
     uint64_t b = (work + per_block - 1) / per_block;
     return (unsigned)(b < 1 ? 1 : (b > 148ull * 16 ? 148ull * 16 : b));
@@ -522,6 +577,20 @@ cudaError_t launch_moe_gather(const float* x, const uint32_t* list_token, const 
                                P, h, xs);
     if (e != cudaSuccess) return e;
     return cudaGetLastError();
+}
+
+cudaError_t launch_moe_tiles(const MoeJob* jobs, const uint32_t* n_jobs, const uint32_t* n_list, uint32_t E, GemmTile* narrow,
+                             GemmTile* wide, uint32_t* counts, cudaStream_t s) {
+    if (E > MAX_EXPERTS) return cudaErrorInvalidValue;
+    cudaError_t e = launch_pdl(moe_tiles_kernel, 1, 1024, 0, s, jobs, n_jobs, n_list, E, narrow, wide, counts);
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+cudaError_t launch_swiglu_rows(const float* g, const float* u, const uint32_t* n_rows, uint32_t max_rows, uint32_t inter,
+                               float clamp, float* out, cudaStream_t s) {
+    cudaError_t e = launch_pdl(swiglu_rows_kernel, blocks_for((uint64_t)max_rows * inter, 256), 256, 0, s, g, u, n_rows, max_rows,
+                               inter, clamp, out);
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 cudaError_t moe_set_trace(unsigned long long* dev_buf) {

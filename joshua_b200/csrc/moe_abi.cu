@@ -123,8 +123,7 @@ int32_t run_experts(jq_moe* m, const float* x, uint64_t R, uint64_t P, uint32_t 
 // The prefill form of the expert MLPs, as the reference buckets tokens per expert and runs one matmul per
 // bucket (src/quantized_qwen3_moe.rs:455-520): when an expert sees dozens of rows, its rows are gathered into
 // bucket order and the experts' gate / up / down products run on the tile GEMM (tensor cores), as one grouped
-// launch per phase over a list of (expert, row range) tiles.  The job list is read back to the host once to
-// cut the tiles, which synchronises the stream.
+// launch per phase over a list of (expert, row range) tiles built on the device.
 constexpr uint64_t BUCKET_ROWS_PER_EXPERT = 12;  // average rows per expert from which the bucketed form is used
 
 int32_t run_experts_bucketed(jq_moe* m, const float* x, uint64_t T, uint64_t P, cudaStream_t s) {
@@ -139,6 +138,40 @@ int32_t run_experts_bucketed(jq_moe* m, const float* x, uint64_t T, uint64_t P, 
     float* xs = m->bucket;
     float* gbuf = xs + P * c.hidden;
     float* ubuf = gbuf + P * c.inter;
+    // Usual form: the experts' rows cut into tiles of up to 128 rows on the device (`moe_tiles_kernel`), and one
+    // grouped launch of the tile GEMM per phase (gate and up together, then down) walks the tile lists.  No host
+    // read: the launches cover the lists' capacity and the kernels read their lengths.
+    if (jq::gemm_tc_grouped_supports(m->gate->type, m->gate->dev, c.inter, c.hidden) && m->up->type == m->gate->type &&
+        jq::gemm_tc_grouped_supports(m->down->type, m->down->dev, c.hidden, c.inter) && P / 128 + c.n_expert <= 65535) {
+        // an expert has at most one tile of <= 32 rows (its last piece) and cnt / 128 + 1 others
+        const uint32_t max_narrow = c.n_expert, max_wide = (uint32_t)(P / 128) + c.n_expert;
+        const uint64_t need_tiles = (uint64_t)max_narrow + max_wide;
+        if (need_tiles > m->tiles_cap) {
+            if (m->tiles) cudaFree(m->tiles);
+            m->tiles = nullptr;
+            m->tiles_cap = 0;
+            JQ_CUDA(cudaMalloc(&m->tiles, need_tiles * sizeof(jq::GemmTile) + 16));
+            m->tiles_cap = need_tiles;
+        }
+        jq::GemmTile* narrow = m->tiles;
+        jq::GemmTile* wide = m->tiles + max_narrow;
+        uint32_t* counts = reinterpret_cast<uint32_t*>(m->tiles + need_tiles);  // {narrow, wide, list rows}
+        void* scratch = nullptr;
+        const size_t need = std::max(jq::gemm_tc_scratch_bytes(P, c.hidden), jq::gemm_tc_scratch_bytes(P, c.inter));
+        JQ_CUDA(m->ctx->scratch_for(reinterpret_cast<cudaStream_t>(reinterpret_cast<uintptr_t>(s) ^ 3), need, &scratch));
+        JQ_CUDA(jq::launch_moe_gather(x, m->list_token, m->n_list, (uint32_t)P, c.hidden, xs, s));
+        JQ_CUDA(jq::launch_moe_tiles(m->jobs, m->n_jobs, m->n_list, c.n_expert, narrow, wide, counts, s));
+        JQ_CUDA(jq::launch_gemm_tc_grouped(m->gate->type, m->gate->dev, m->up->dev, m->gate_expert_bytes, c.inter, c.hidden, xs, P,
+                                           gbuf, ubuf, narrow, max_narrow, wide, max_wide, counts, scratch, m->ctx->status_dev, s));
+        JQ_CUDA(jq::launch_swiglu_rows(gbuf, ubuf, counts + 2, (uint32_t)P, c.inter, c.clamp, m->hidden, s));
+        JQ_CUDA(jq::launch_gemm_tc_grouped(m->down->type, m->down->dev, nullptr, m->down_expert_bytes, c.hidden, c.inter,
+                                           m->hidden, P, m->out, nullptr, narrow, max_narrow, wide, max_wide, counts, scratch,
+                                           m->ctx->status_dev, s));
+        (void)T;
+        return jq::OK;
+    }
+    // Shapes the grouped form does not take: the job list is read back to the host (which synchronises the stream)
+    // and every expert's bucket is one batched matmul.
     uint32_t n_jobs = 0;
     JQ_CUDA(cudaMemcpyAsync(&n_jobs, m->n_jobs, sizeof(n_jobs), cudaMemcpyDeviceToHost, s));
     JQ_CUDA(cudaStreamSynchronize(s));
@@ -164,44 +197,7 @@ int32_t run_experts_bucketed(jq_moe* m, const float* x, uint64_t T, uint64_t P, 
         w.owns = false;
         return w;
     };
-    // Usual form: the buckets cut into tiles of up to 128 rows, and one grouped launch of the tile GEMM per phase
-    // (gate and up together, then down) walks the tile list on the device.
-    if (jq::gemm_tc_grouped_supports(m->gate->type, m->gate->dev, c.inter, c.hidden) && m->up->type == m->gate->type &&
-        jq::gemm_tc_grouped_supports(m->down->type, m->down->dev, c.hidden, c.inter)) {
-        std::vector<jq::GemmTile> tiles;
-        uint64_t live = 0;
-        for (const Bucket& b : buckets) {
-            for (uint32_t r = 0; r < b.cnt; r += 128) tiles.push_back({b.expert, b.row0 + r, std::min<uint32_t>(128, b.cnt - r), 0});
-            live = std::max<uint64_t>(live, (uint64_t)b.row0 + b.cnt);
-        }
-        if (tiles.empty()) return jq::OK;
-        // tiles of at most 32 rows first: they run as 32-token tiles
-        const uint32_t n_narrow = (uint32_t)(std::stable_partition(tiles.begin(), tiles.end(),
-                                                                   [](const jq::GemmTile& t) { return t.cnt <= 32; }) -
-                                             tiles.begin());
-        if (tiles.size() > m->tiles_cap) {
-            if (m->tiles) cudaFree(m->tiles);
-            m->tiles = nullptr;
-            m->tiles_cap = 0;
-            JQ_CUDA(cudaMalloc(&m->tiles, tiles.size() * sizeof(jq::GemmTile)));
-            m->tiles_cap = tiles.size();
-        }
-        JQ_CUDA(cudaMemcpyAsync(m->tiles, tiles.data(), tiles.size() * sizeof(jq::GemmTile), cudaMemcpyHostToDevice, s));
-        JQ_CUDA(cudaStreamSynchronize(s));  // the list is host memory of this call
-        void* scratch = nullptr;
-        const size_t need = std::max(jq::gemm_tc_scratch_bytes(P, c.hidden), jq::gemm_tc_scratch_bytes(P, c.inter));
-        JQ_CUDA(m->ctx->scratch_for(reinterpret_cast<cudaStream_t>(reinterpret_cast<uintptr_t>(s) ^ 3), need, &scratch));
-        const uint32_t nt = (uint32_t)tiles.size();
-        JQ_CUDA(jq::launch_gemm_tc_grouped(m->gate->type, m->gate->dev, m->up->dev, m->gate_expert_bytes, c.inter, c.hidden, xs, P,
-                                           gbuf, ubuf, m->tiles, nt, n_narrow, scratch, m->ctx->status_dev, s));
-        JQ_CUDA(jq::launch_swiglu(gbuf, ubuf, live * c.inter, c.clamp, m->hidden, s));
-        JQ_CUDA(jq::launch_gemm_tc_grouped(m->down->type, m->down->dev, nullptr, m->down_expert_bytes, c.hidden, c.inter,
-                                           m->hidden, P, m->out, nullptr, m->tiles, nt, n_narrow, scratch, m->ctx->status_dev, s));
-        (void)T;
-        return jq::OK;
-    }
-    // Shapes the grouped form does not take: one batched matmul per bucket.  One expert's product fills only a
-    // fraction of the GPU (n / 128 CTAs), so the buckets are dealt to eight
+    // One expert's product fills only a fraction of the GPU (n / 128 CTAs), so the buckets are dealt to eight
     // auxiliary streams that fork from and join the caller's stream around each phase.
     constexpr int NAUX = 8;
     jq_ctx* cx = m->ctx;
