@@ -9,29 +9,40 @@ namespace jq {
 
 namespace {
 
-// logits[t, e] = sum_j x[t, j] * router[e, j]: one warp per (token, expert) pair, f32.
+// logits[t, e] = sum_j x[t, j] * router[e, j], f32: one warp per (token, four consecutive experts), so that a token's
+// row is read once for four dot products; each dot product sums its lane's strided pieces in column order and
+// then across the lanes, the same order for every batch size.
 __global__ void __launch_bounds__(256) moe_logits_kernel(const float* __restrict__ x, const float* __restrict__ router,
                                                          uint32_t T, uint32_t E, uint32_t h,
                                                          float* __restrict__ logits) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t lane = threadIdx.x & 31;
-    const uint64_t total = (uint64_t)T * E;
+    const uint32_t lane = threadIdx.x & 31, E4 = (E + 3) / 4;
+    const uint64_t total = (uint64_t)T * E4;
     for (uint64_t p = blockIdx.x * 8ull + (threadIdx.x >> 5); p < total; p += gridDim.x * 8ull) {
-        const uint32_t t = (uint32_t)(p / E), e = (uint32_t)(p % E);
+        const uint32_t t = (uint32_t)(p / E4), e0 = (uint32_t)(p % E4) * 4;
         const float4* a = reinterpret_cast<const float4*>(x + (uint64_t)t * h);
-        const float4* b = reinterpret_cast<const float4*>(router + (uint64_t)e * h);
-        float acc = 0.0f;
+        const float4* b[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) b[q] = reinterpret_cast<const float4*>(router + (uint64_t)min(e0 + q, E - 1) * h);
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         for (uint32_t j = lane; j < h / 4; j += 32) {
-            float4 u = __ldg(a + j), v = __ldg(b + j);
-            acc = fmaf(u.x, v.x, acc);
-            acc = fmaf(u.y, v.y, acc);
-            acc = fmaf(u.z, v.z, acc);
-            acc = fmaf(u.w, v.w, acc);
+            const float4 u = __ldg(a + j);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 v = __ldg(b[q] + j);
+                acc[q] = fmaf(u.x, v.x, acc[q]);
+                acc[q] = fmaf(u.y, v.y, acc[q]);
+                acc[q] = fmaf(u.z, v.z, acc[q]);
+                acc[q] = fmaf(u.w, v.w, acc[q]);
+            }
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-        if (lane == 0) logits[p] = acc;
+        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc[q] += __shfl_xor_sync(0xFFFFFFFFu, acc[q], o);
+            if (lane == 0 && e0 + q < E) logits[(uint64_t)t * E + e0 + q] = acc[q];
+        }
     }
 }
 
@@ -308,16 +319,111 @@ __device__ __forceinline__ void build_jobs(const uint32_t* __restrict__ ids, uin
 }
 
 
+// The same lists for many pairs (prefill sizes).  The stable fill above lets every warp walk all pairs once per
+// expert it owns; here the pairs are cut into JOB_SLICES contiguous slices, a warp counts its slice's pairs per
+// expert, the slices' counts are prefixed per expert, and the warp walks its slice once more in order: a pair's
+// position is its expert's offset + the pairs of earlier slices + its rank among the slice's earlier pairs of the
+// same expert (`__match_any_sync` within a group of 32).  Same lists, P / JOB_SLICES steps per warp instead of
+// P * E / warps.
+constexpr uint32_t JOB_SLICES = 16;
+struct JobsSliceSmem {
+    uint32_t cnt[JOB_SLICES][MAX_EXPERTS];
+};
+
+__device__ __forceinline__ void build_jobs_sliced(const uint32_t* __restrict__ ids, uint32_t T, uint32_t K, uint32_t E,
+                                                  uint32_t rows_per_job, uint32_t* __restrict__ list_token,
+                                                  uint32_t* __restrict__ inv, MoeJob* __restrict__ jobs,
+                                                  uint32_t* __restrict__ n_jobs, uint32_t* __restrict__ n_list,
+                                                  int* __restrict__ bad_id, JobsSmem& js, JobsSliceSmem& ss, uint32_t tid,
+                                                  uint32_t nthreads) {
+    const uint32_t lane = tid & 31, warp = tid >> 5;
+    const uint32_t P = T * K;
+    const uint32_t slice = ((P + JOB_SLICES - 1) / JOB_SLICES + 31) & ~31u;  // pairs per slice, whole groups of 32
+    for (uint32_t i = tid; i < JOB_SLICES * MAX_EXPERTS; i += nthreads) (&ss.cnt[0][0])[i] = 0;
+    __syncthreads();
+    if (warp < JOB_SLICES) {
+        const uint32_t p_end = min(P, (warp + 1) * slice);
+        for (uint32_t p = warp * slice + lane; p < p_end; p += 32) {
+            const uint32_t e = ids[p];
+            if (e < E) {
+                atomicAdd(&ss.cnt[warp][e], 1u);
+            } else {
+                inv[p] = 0xFFFFFFFFu;
+                *bad_id = 1;
+            }
+        }
+    }
+    __syncthreads();
+    // per expert: the slices' counts become the count of earlier slices; the total goes to js.cnt
+    for (uint32_t e = tid; e < E; e += nthreads) {
+        uint32_t run = 0;
+#pragma unroll
+        for (uint32_t w = 0; w < JOB_SLICES; ++w) {
+            const uint32_t c = ss.cnt[w][e];
+            ss.cnt[w][e] = run;
+            run += c;
+        }
+        js.cnt[e] = run;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t off = 0, job = 0;
+        for (uint32_t e = 0; e < E; ++e) {
+            js.off[e] = off;
+            js.job[e] = job;
+            off += js.cnt[e];
+            job += (js.cnt[e] + rows_per_job - 1) / rows_per_job;
+        }
+        *n_jobs = job;
+        *n_list = off;
+    }
+    __syncthreads();
+    if (warp < JOB_SLICES) {
+        const uint32_t p_end = min(P, (warp + 1) * slice);
+        for (uint32_t p0 = warp * slice; p0 < p_end; p0 += 32) {  // warp-uniform bounds: every lane takes part
+            const uint32_t p = p0 + lane;
+            const uint32_t e = p < p_end ? ids[p] : 0xFFFFFFFFu;
+            const bool valid = e < E;
+            const uint32_t same = __match_any_sync(0xFFFFFFFFu, valid ? e : 0xFFFFFFFFu);
+            uint32_t base = 0;
+            if (valid) base = js.off[e] + ss.cnt[warp][e];
+            __syncwarp();
+            if (valid) {
+                const uint32_t pos = base + __popc(same & ((1u << lane) - 1));
+                list_token[pos] = p / K;
+                inv[p] = pos;
+                if ((same & ((1u << lane) - 1)) == 0) ss.cnt[warp][e] += __popc(same);  // the group's first lane of e
+            }
+            __syncwarp();
+        }
+    }
+    for (uint32_t e = tid; e < E; e += nthreads) {
+        const uint32_t cnt = js.cnt[e];
+        for (uint32_t j = 0; j * rows_per_job < cnt; ++j) {
+            MoeJob jd;
+            jd.expert = e;
+            jd.row0 = js.off[e] + j * rows_per_job;
+            jd.cnt = min(rows_per_job, cnt - j * rows_per_job);
+            jobs[js.job[e] + j] = jd;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(1024) moe_jobs_kernel(const uint32_t* __restrict__ ids, uint32_t T, uint32_t K,
                                                         uint32_t E, uint32_t rows_per_job,
                                                         uint32_t* __restrict__ list_token, uint32_t* __restrict__ inv,
                                                         MoeJob* __restrict__ jobs, uint32_t* __restrict__ n_jobs,
                                                         uint32_t* __restrict__ n_list, int* __restrict__ bad_id) {
     __shared__ JobsSmem js;
+    __shared__ JobsSliceSmem ss;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    build_jobs(ids, T, K, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id, js, threadIdx.x, blockDim.x,
-               [] { __syncthreads(); });
+    if (T * K > 1024)
+        build_jobs_sliced(ids, T, K, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id, js, ss, threadIdx.x,
+                          blockDim.x);
+    else
+        build_jobs(ids, T, K, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id, js, threadIdx.x, blockDim.x,
+                   [] { __syncthreads(); });
 }
 
 // Decode-sized batches (T <= 8): router logits, routing and the job list in ONE launch.  A CTA per (token,
@@ -549,7 +655,7 @@ unsigned blocks_for(uint64_t work, unsigned per_block) {
 
 cudaError_t launch_moe_logits(const float* x, const float* router, uint32_t T, uint32_t E, uint32_t h, float* logits,
                               cudaStream_t s) {
-    cudaError_t le1__ = launch_pdl(moe_logits_kernel, blocks_for((uint64_t)T * E, 8), 256, 0, s, x, router, T, E, h, logits);
+    cudaError_t le1__ = launch_pdl(moe_logits_kernel, blocks_for((uint64_t)T * ((E + 3) / 4), 8), 256, 0, s, x, router, T, E, h, logits);
     if (le1__ != cudaSuccess) return le1__;
     return cudaGetLastError();
 }
