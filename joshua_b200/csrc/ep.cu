@@ -211,16 +211,41 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const uint8_t* __restri
          i += (uint64_t)gridDim.x * blockDim.x) {
         const uint32_t t = (uint32_t)(i / h4), c = (uint32_t)(i % h4);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t s = 0; s < K; ++s) {
-            const uint32_t ps = pair_slot[(uint64_t)t * K + s];
-            if (ps == 0xFFFFFFFFu) continue;
-            const float w = wts[(uint64_t)t * K + s];
-            // rows_back is written by peers: read it through L2, never from a stale L1 line
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(back + (uint64_t)ps * l.hidden) + c);
-            acc.x += v.x * w;
-            acc.y += v.y * w;
-            acc.z += v.z * w;
-            acc.w += v.w * w;
+        // rows_back is written by peers: read it through L2, never from a stale L1 line
+        if (K <= 8) {
+            // all slots and weights requested first, then all rows, then the sum in slot order (two round trips
+            // instead of 2 K dependent ones)
+            uint32_t ps[8];
+            float w[8];
+            float4 v[8];
+#pragma unroll
+            for (uint32_t s = 0; s < 8; ++s) {
+                ps[s] = s < K ? pair_slot[(uint64_t)t * K + s] : 0xFFFFFFFFu;
+                w[s] = s < K ? wts[(uint64_t)t * K + s] : 0.0f;
+            }
+#pragma unroll
+            for (uint32_t s = 0; s < 8; ++s)
+                v[s] = ps[s] != 0xFFFFFFFFu ? __ldcg(reinterpret_cast<const float4*>(back + (uint64_t)ps[s] * l.hidden) + c)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (uint32_t s = 0; s < 8; ++s) {
+                if (ps[s] == 0xFFFFFFFFu) continue;
+                acc.x += v[s].x * w[s];
+                acc.y += v[s].y * w[s];
+                acc.z += v[s].z * w[s];
+                acc.w += v[s].w * w[s];
+            }
+        } else {
+            for (uint32_t s = 0; s < K; ++s) {
+                const uint32_t ps = pair_slot[(uint64_t)t * K + s];
+                if (ps == 0xFFFFFFFFu) continue;
+                const float w = wts[(uint64_t)t * K + s];
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(back + (uint64_t)ps * l.hidden) + c);
+                acc.x += v.x * w;
+                acc.y += v.y * w;
+                acc.z += v.z * w;
+                acc.w += v.w * w;
+            }
         }
         if (residual) {
             const float4 v = *reinterpret_cast<const float4*>(residual + (uint64_t)t * l.hidden + 4 * c);

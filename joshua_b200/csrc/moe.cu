@@ -531,15 +531,40 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
          i += (uint64_t)gridDim.x * blockDim.x) {
         const uint32_t t = (uint32_t)(i / (h / 4)), c = (uint32_t)(i % (h / 4));
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t s = 0; s < K; ++s) {
-            uint32_t pos = inv[(uint64_t)t * K + s];
-            if (pos == 0xFFFFFFFFu) continue;
-            float w = wts[(uint64_t)t * K + s];
-            float4 v = *reinterpret_cast<const float4*>(out + (uint64_t)pos * h + 4 * c);
-            acc.x += v.x * w;
-            acc.y += v.y * w;
-            acc.z += v.z * w;
-            acc.w += v.w * w;
+        if (K <= 8) {
+            // latency is all this kernel costs at decode sizes: all positions and weights are requested first, then
+            // all rows, and only then summed in slot order (a loop that loads as it goes waits out 2 K round trips)
+            uint32_t pos[8];
+            float w[8];
+            float4 v[8];
+#pragma unroll
+            for (uint32_t s = 0; s < 8; ++s) {
+                pos[s] = s < K ? inv[(uint64_t)t * K + s] : 0xFFFFFFFFu;
+                w[s] = s < K ? wts[(uint64_t)t * K + s] : 0.0f;
+            }
+#pragma unroll
+            for (uint32_t s = 0; s < 8; ++s)
+                v[s] = pos[s] != 0xFFFFFFFFu ? *reinterpret_cast<const float4*>(out + (uint64_t)pos[s] * h + 4 * c)
+                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (uint32_t s = 0; s < 8; ++s) {
+                if (pos[s] == 0xFFFFFFFFu) continue;
+                acc.x += v[s].x * w[s];
+                acc.y += v[s].y * w[s];
+                acc.z += v[s].z * w[s];
+                acc.w += v[s].w * w[s];
+            }
+        } else {
+            for (uint32_t s = 0; s < K; ++s) {
+                uint32_t pos = inv[(uint64_t)t * K + s];
+                if (pos == 0xFFFFFFFFu) continue;
+                float w = wts[(uint64_t)t * K + s];
+                float4 v = *reinterpret_cast<const float4*>(out + (uint64_t)pos * h + 4 * c);
+                acc.x += v.x * w;
+                acc.y += v.y * w;
+                acc.z += v.z * w;
+                acc.w += v.w * w;
+            }
         }
         if (shared) {
             float4 v = *reinterpret_cast<const float4*>(shared + (uint64_t)t * h + 4 * c);
