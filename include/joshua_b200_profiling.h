@@ -1,7 +1,7 @@
 /* joshua_b200 - profiling aids, exported only by builds made with -DJQ_PROFILING
  * (python -m joshua_b200.build --profiling).  Release builds do not contain these entry
  * points, nor the measurement switches read from the environment (JQ_DEBUG_TC_SKIP,
- * JQ_NO_NARROW_K, JQ_MOE_BUCKET_ROWS).  No counterpart in the reference. */
+ * JQ_NO_NARROW_K, JQ_MOE_BUCKET_TOKENS).  No counterpart in the reference. */
 #ifndef JOSHUA_B200_PROFILING_H
 #define JOSHUA_B200_PROFILING_H
 

@@ -200,9 +200,11 @@ cudaError_t launch_swiglu(const float* g, const float* u, uint64_t n, float clam
 // the same over the first *n_rows (at most max_rows) rows of [rows, inter]
 cudaError_t launch_swiglu_rows(const float* g, const float* u, const uint32_t* n_rows, uint32_t max_rows, uint32_t inter,
                                float clamp, float* out, cudaStream_t s);
-// tile lists of the grouped tile GEMM from the job list: counts = {narrow tiles (<= 32 rows), wide tiles, list rows}
-cudaError_t launch_moe_tiles(const MoeJob* jobs, const uint32_t* n_jobs, const uint32_t* n_list, uint32_t E, GemmTile* narrow,
-                             GemmTile* wide, uint32_t* counts, cudaStream_t s);
+// work lists of the prefill form from the job list: experts with >= min_rows rows as tiles of the grouped tile GEMM,
+// the other experts' jobs copied for the grouped decode kernel;
+// counts = {narrow tiles (<= 32 rows), wide tiles, list rows, small jobs}
+cudaError_t launch_moe_tiles(const MoeJob* jobs, const uint32_t* n_jobs, const uint32_t* n_list, uint32_t E, uint32_t min_rows,
+                             GemmTile* narrow, GemmTile* wide, MoeJob* small_jobs, uint32_t* counts, cudaStream_t s);
 
 // decoder.cu: the element-wise and attention steps around the matmuls of a decode step
 cudaError_t launch_rmsnorm(const float* x, const float* res, const float* w, float eps, uint64_t rows, uint32_t h,

@@ -616,19 +616,21 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const float* __restrict
     }
 }
 
-// Tile list of the grouped tile GEMM from the job list (jobs of one expert are consecutive and cover consecutive
-// rows): an expert's rows are cut into tiles of 128; a last piece of at most 32 rows goes to the narrow list,
-// anything else to the wide list.  counts = {narrow tiles, wide tiles, rows in the list}.  Which slot of a list a
-// tile takes depends on timing; the products do not (every tile is computed on its own).  One CTA.
+// Work lists of the prefill form from the job list (jobs of one expert are consecutive and cover consecutive rows).
+// An expert with at least `min_rows` rows goes to the tile GEMM: its rows are cut into tiles of 128, a last piece of
+// at most 32 rows goes to the narrow list, anything else to the wide list.  The jobs of the other experts are copied
+// to `small_jobs` for the grouped decode kernel.  counts = {narrow tiles, wide tiles, rows in the list, small jobs}.
+// Which slot of a list an entry takes depends on timing; the products do not (every entry is computed on its own).
+// One CTA.
 __global__ void __launch_bounds__(1024) moe_tiles_kernel(const MoeJob* __restrict__ jobs, const uint32_t* __restrict__ n_jobs,
-                                                         const uint32_t* __restrict__ n_list, uint32_t E,
+                                                         const uint32_t* __restrict__ n_list, uint32_t E, uint32_t min_rows,
                                                          GemmTile* __restrict__ narrow, GemmTile* __restrict__ wide,
-                                                         uint32_t* __restrict__ counts) {
-    __shared__ uint32_t s_row0[MAX_EXPERTS], s_cnt[MAX_EXPERTS], s_n[2];
+                                                         MoeJob* __restrict__ small_jobs, uint32_t* __restrict__ counts) {
+    __shared__ uint32_t s_row0[MAX_EXPERTS], s_cnt[MAX_EXPERTS], s_n[3];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint32_t e = threadIdx.x; e < E; e += blockDim.x) s_row0[e] = 0xFFFFFFFFu, s_cnt[e] = 0;
-    if (threadIdx.x < 2) s_n[threadIdx.x] = 0;
+    if (threadIdx.x < 3) s_n[threadIdx.x] = 0;
     __syncthreads();
     const uint32_t nj = *n_jobs;
     for (uint32_t j = threadIdx.x; j < nj; j += blockDim.x) {
@@ -641,6 +643,7 @@ __global__ void __launch_bounds__(1024) moe_tiles_kernel(const MoeJob* __restric
     __syncthreads();
     for (uint32_t e = threadIdx.x; e < E; e += blockDim.x) {
         const uint32_t cnt = s_cnt[e], row0 = s_row0[e];
+        if (cnt < min_rows) continue;
         for (uint32_t r = 0; r < cnt; r += 128) {
             const uint32_t c = min(128u, cnt - r);
             GemmTile t = {e, row0 + r, c, 0};
@@ -650,8 +653,12 @@ __global__ void __launch_bounds__(1024) moe_tiles_kernel(const MoeJob* __restric
                 wide[atomicAdd(&s_n[1], 1u)] = t;
         }
     }
+    for (uint32_t j = threadIdx.x; j < nj; j += blockDim.x) {
+        const MoeJob jb = jobs[j];
+        if (jb.expert < E && s_cnt[jb.expert] < min_rows) small_jobs[atomicAdd(&s_n[2], 1u)] = jb;
+    }
     __syncthreads();
-    if (threadIdx.x == 0) counts[0] = s_n[0], counts[1] = s_n[1], counts[2] = *n_list;
+    if (threadIdx.x == 0) counts[0] = s_n[0], counts[1] = s_n[1], counts[2] = *n_list, counts[3] = s_n[2];
 }
 
 // SwiGLU over the first *n_rows rows of [rows, inter] (rows of the expert-sorted list that exist).
@@ -710,10 +717,11 @@ cudaError_t launch_moe_gather(const float* x, const uint32_t* list_token, const 
     return cudaGetLastError();
 }
 
-cudaError_t launch_moe_tiles(const MoeJob* jobs, const uint32_t* n_jobs, const uint32_t* n_list, uint32_t E, GemmTile* narrow,
-                             GemmTile* wide, uint32_t* counts, cudaStream_t s) {
+cudaError_t launch_moe_tiles(const MoeJob* jobs, const uint32_t* n_jobs, const uint32_t* n_list, uint32_t E, uint32_t min_rows,
+                             GemmTile* narrow, GemmTile* wide, MoeJob* small_jobs, uint32_t* counts, cudaStream_t s) {
     if (E > MAX_EXPERTS) return cudaErrorInvalidValue;
-    cudaError_t e = launch_pdl(moe_tiles_kernel, 1, 1024, 0, s, jobs, n_jobs, n_list, E, narrow, wide, counts);
+    cudaError_t e = launch_pdl(moe_tiles_kernel, 1, 1024, 0, s, jobs, n_jobs, n_list, E, min_rows, narrow, wide, small_jobs,
+                               counts);
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 

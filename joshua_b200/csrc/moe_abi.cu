@@ -64,12 +64,14 @@ bool fits_smem(uint64_t rows, uint64_t k) { return jq::gemv_mma_scratch_bytes(ro
 
 // out_list[pos, :] = MLP_expert(pos)(x[list_token[pos], :]) for the list built by the jobs kernel.
 // R activation rows, P list positions at most.
+// `jobs` / `n_jobs` (device) default to the layer's whole job list; `phases` bit 0 = gate/up, bit 1 = down.
 int32_t run_experts(jq_moe* m, const float* x, uint64_t R, uint64_t P, uint32_t rows_per_job, cudaStream_t s,
-                    const float* norm_w = nullptr, float eps = 0.0f) {
+                    const float* norm_w = nullptr, float eps = 0.0f, const jq::MoeJob* jobs = nullptr,
+                    const uint32_t* n_jobs = nullptr, int phases = 3) {
     const jq_moe_config& c = m->cfg;
     jq::GroupedLaunch g = {};
-    g.jobs = m->jobs;
-    g.n_jobs = m->n_jobs;
+    g.jobs = jobs ? jobs : m->jobs;
+    g.n_jobs = n_jobs ? n_jobs : m->n_jobs;
     // a job holds at most rows_per_job positions of one expert
     g.max_jobs = (uint32_t)std::min<uint64_t>(P, P / rows_per_job + c.n_expert);
     g.rows_per_job = rows_per_job;
@@ -86,16 +88,19 @@ int32_t run_experts(jq_moe* m, const float* x, uint64_t R, uint64_t P, uint32_t 
     g.x_rows = (uint32_t)R;
     g.act_rows = m->list_token;
     g.dst = m->hidden;
-    if (fits_smem(R, c.hidden)) {
-        g.planes = nullptr;
-        g.norm_w = norm_w;
-        g.norm_eps = eps;
-    } else {
-        if (norm_w) return jq_fail(jq::E_INVALID, "moe: internal: norm requested for rows that do not fit shared memory");
-        JQ_CUDA(jq::launch_quantize_acts(g.type, x, R, c.hidden, m->planes_x, s));
-        g.planes = m->planes_x;
+    if (phases & 1) {
+        if (fits_smem(R, c.hidden)) {
+            g.planes = nullptr;
+            g.norm_w = norm_w;
+            g.norm_eps = eps;
+        } else {
+            if (norm_w) return jq_fail(jq::E_INVALID, "moe: internal: norm requested for rows that do not fit shared memory");
+            JQ_CUDA(jq::launch_quantize_acts(g.type, x, R, c.hidden, m->planes_x, s));
+            g.planes = m->planes_x;
+        }
+        JQ_CUDA(jq::launch_gemv_grouped(g, s));
     }
-    JQ_CUDA(jq::launch_gemv_grouped(g, s));
+    if (!(phases & 2)) return jq::OK;
     // down: out[pos, hidden]; activation row = list position
     g.type = m->down->type;
     g.w0 = m->down->dev;
@@ -124,9 +129,10 @@ int32_t run_experts(jq_moe* m, const float* x, uint64_t R, uint64_t P, uint32_t 
 // bucket (src/quantized_qwen3_moe.rs:455-520): when an expert sees dozens of rows, its rows are gathered into
 // bucket order and the experts' gate / up / down products run on the tile GEMM (tensor cores), as one grouped
 // launch per phase over a list of (expert, row range) tiles built on the device.
-constexpr uint64_t BUCKET_ROWS_PER_EXPERT = 12;  // average rows per expert from which the bucketed form is used
+constexpr uint64_t BUCKET_ROWS_PER_EXPERT = 12;  // rows from which an expert runs on the tile GEMM
+constexpr uint64_t BUCKET_MIN_TOKENS = 128;      // tokens from which the prefill form (tile GEMM + decode kernel) is used
 
-int32_t run_experts_bucketed(jq_moe* m, const float* x, uint64_t T, uint64_t P, cudaStream_t s) {
+int32_t run_experts_bucketed(jq_moe* m, const float* x, uint64_t T, uint64_t P, uint32_t rows_per_job, cudaStream_t s) {
     const jq_moe_config& c = m->cfg;
     if (P > m->bucket_pairs) {
         if (m->bucket) cudaFree(m->bucket);
@@ -138,37 +144,50 @@ int32_t run_experts_bucketed(jq_moe* m, const float* x, uint64_t T, uint64_t P, 
     float* xs = m->bucket;
     float* gbuf = xs + P * c.hidden;
     float* ubuf = gbuf + P * c.inter;
-    // Usual form: the experts' rows cut into tiles of up to 128 rows on the device (`moe_tiles_kernel`), and one
-    // grouped launch of the tile GEMM per phase (gate and up together, then down) walks the tile lists.  No host
-    // read: the launches cover the lists' capacity and the kernels read their lengths.
+    // Usual form, all on the device (`moe_tiles_kernel`): an expert with at least BUCKET_ROWS_PER_EXPERT rows has
+    // them cut into tiles of up to 128 rows and runs on the tile GEMM, one grouped launch per phase and tile class
+    // (gate and up together, then down); the other experts' jobs run on the grouped decode kernel in the same pass.
+    // No host read: the launches cover the lists' capacity and the kernels read their lengths.
     if (jq::gemm_tc_grouped_supports(m->gate->type, m->gate->dev, c.inter, c.hidden) && m->up->type == m->gate->type &&
-        jq::gemm_tc_grouped_supports(m->down->type, m->down->dev, c.hidden, c.inter) && P / 128 + c.n_expert <= 65535) {
-        // an expert has at most one tile of <= 32 rows (its last piece) and cnt / 128 + 1 others
-        const uint32_t max_narrow = c.n_expert, max_wide = (uint32_t)(P / 128) + c.n_expert;
-        const uint64_t need_tiles = (uint64_t)max_narrow + max_wide;
-        if (need_tiles > m->tiles_cap) {
+        jq::gemm_tc_grouped_supports(m->down->type, m->down->dev, c.hidden, c.inter) && P / 33 + 1 <= 65535) {
+        // a narrow tile (<= 32 rows) is an expert's only tile (>= min rows) or the last piece behind full tiles; a wide
+        // tile holds more than 32 rows
+        // With 24 or more rows per expert on average hardly an expert is small: every expert then takes the tile
+        // form (an expert with a few rows is one narrow tile) and the decode kernel's passes are left out.
+        const bool all_tiles = P >= 24ull * c.n_expert;
+        const uint32_t min_rows = all_tiles ? 1u : (uint32_t)BUCKET_ROWS_PER_EXPERT;
+        const uint32_t max_narrow = (uint32_t)std::min<uint64_t>(c.n_expert, P / min_rows + 1);
+        const uint32_t max_wide = (uint32_t)(P / 33 + 1);
+        const uint32_t max_small = (uint32_t)std::min<uint64_t>(P, P / rows_per_job + c.n_expert);
+        const uint64_t need_bytes = ((uint64_t)max_narrow + max_wide) * sizeof(jq::GemmTile) + (uint64_t)max_small * sizeof(jq::MoeJob) + 32;
+        if (need_bytes > m->tiles_cap) {
             if (m->tiles) cudaFree(m->tiles);
             m->tiles = nullptr;
             m->tiles_cap = 0;
-            JQ_CUDA(cudaMalloc(&m->tiles, need_tiles * sizeof(jq::GemmTile) + 16));
-            m->tiles_cap = need_tiles;
+            JQ_CUDA(cudaMalloc(&m->tiles, need_bytes));
+            m->tiles_cap = need_bytes;
         }
         jq::GemmTile* narrow = m->tiles;
-        jq::GemmTile* wide = m->tiles + max_narrow;
-        uint32_t* counts = reinterpret_cast<uint32_t*>(m->tiles + need_tiles);  // {narrow, wide, list rows}
+        jq::GemmTile* wide = narrow + max_narrow;
+        jq::MoeJob* small_jobs = reinterpret_cast<jq::MoeJob*>(wide + max_wide);
+        // {narrow tiles, wide tiles, list rows, small jobs}, 16-byte aligned behind the lists
+        uint32_t* counts = reinterpret_cast<uint32_t*>(
+            (reinterpret_cast<uintptr_t>(small_jobs + max_small) + 15) & ~(uintptr_t)15);
         void* scratch = nullptr;
         const size_t need = std::max(jq::gemm_tc_scratch_bytes(P, c.hidden), jq::gemm_tc_scratch_bytes(P, c.inter));
         JQ_CUDA(m->ctx->scratch_for(reinterpret_cast<cudaStream_t>(reinterpret_cast<uintptr_t>(s) ^ 3), need, &scratch));
         JQ_CUDA(jq::launch_moe_gather(x, m->list_token, m->n_list, (uint32_t)P, c.hidden, xs, s));
-        JQ_CUDA(jq::launch_moe_tiles(m->jobs, m->n_jobs, m->n_list, c.n_expert, narrow, wide, counts, s));
+        JQ_CUDA(jq::launch_moe_tiles(m->jobs, m->n_jobs, m->n_list, c.n_expert, min_rows, narrow, wide, small_jobs, counts, s));
         JQ_CUDA(jq::launch_gemm_tc_grouped(m->gate->type, m->gate->dev, m->up->dev, m->gate_expert_bytes, c.inter, c.hidden, xs, P,
                                            gbuf, ubuf, narrow, max_narrow, wide, max_wide, counts, scratch, m->ctx->status_dev, s));
+        // SwiGLU over every list row (rows of the small experts hold nothing yet; the decode kernel writes them next)
         JQ_CUDA(jq::launch_swiglu_rows(gbuf, ubuf, counts + 2, (uint32_t)P, c.inter, c.clamp, m->hidden, s));
+        if (!all_tiles)
+            if (int32_t rc = run_experts(m, x, T, P, rows_per_job, s, nullptr, 0.0f, small_jobs, counts + 3, 1)) return rc;
         JQ_CUDA(jq::launch_gemm_tc_grouped(m->down->type, m->down->dev, nullptr, m->down_expert_bytes, c.hidden, c.inter,
                                            m->hidden, P, m->out, nullptr, narrow, max_narrow, wide, max_wide, counts, scratch,
                                            m->ctx->status_dev, s));
-        (void)T;
-        return jq::OK;
+        return all_tiles ? jq::OK : run_experts(m, x, T, P, rows_per_job, s, nullptr, 0.0f, small_jobs, counts + 3, 2);
     }
     // Shapes the grouped form does not take: the job list is read back to the host (which synchronises the stream)
     // and every expert's bucket is one batched matmul.
@@ -332,7 +351,7 @@ int32_t jq_moe_experts_list(jq_moe* m, const float* x_dev, uint64_t n_rows, cons
     uint32_t rpj = rows_per_job_for(n_rows, n_rows == 1 ? 1 : 2, c.n_expert);
     JQ_CUDA(jq::launch_moe_jobs(expert_ids_dev, (uint32_t)n_rows, 1, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
                                 m->n_jobs, m->n_list, m->bad_dev, s));
-    if (!m->ctx->force_f32 && live_rows >= BUCKET_ROWS_PER_EXPERT * c.n_expert) return run_experts_bucketed(m, x_dev, n_rows, n_rows, s);
+    if (!m->ctx->force_f32 && live_rows >= BUCKET_MIN_TOKENS) return run_experts_bucketed(m, x_dev, n_rows, n_rows, rpj, s);
     m->last_rows = m->last_pairs = n_rows, m->last_rpj = rpj;
     return run_experts(m, x_dev, n_rows, n_rows, rpj, s);
 }
@@ -517,19 +536,18 @@ int32_t jq_moe_forward_norm_add_dev(jq_moe* m, const float* x_dev, uint64_t T, c
         JQ_CUDA(jq::launch_moe_jobs(m->ids, (uint32_t)T, c.n_used, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
                                     m->n_jobs, m->n_list, m->bad_dev, s));
     }
-    // prefill-sized batches (12 or more rows per expert on average): the experts' rows gathered into buckets and
-    // the products run as grouped launches of the tile GEMM.  Measured crossovers against the grouped decode
-    // kernel (uniform routing): 128 Q4_K experts of 2048 x 768 between 8 and 16 rows per expert (0.91 / 0.68 ms at
-    // 8, 0.95 / 1.13 ms at 16), 384 MXFP4 experts of 7168 x 2048 near 11 (20.8 / 19.2 ms), 256 IQ2_XXS experts of
-    // the same shape above 8 (13.3 / 9.2 ms).
-    uint64_t thr_override = 0;  // average rows per expert from which to bucket (measurement switch)
+    // From BUCKET_MIN_TOKENS tokens on, the prefill form: experts with at least BUCKET_ROWS_PER_EXPERT rows on the
+    // tile GEMM, the others on the grouped decode kernel, decided per expert on the device.  Measured crossovers of
+    // the two kernels (uniform routing): 128 Q4_K experts of 2048 x 768 between 8 and 16 rows per expert (tile GEMM /
+    // decode kernel 0.91 / 0.68 ms at 8, 0.78 / 1.13 ms at 16), 384 MXFP4 experts of 7168 x 2048 near 11
+    // (20.8 / 19.2 ms), 256 IQ2_XXS experts of the same shape above 8 (13.3 / 9.2 ms).
+    uint64_t min_tokens = BUCKET_MIN_TOKENS;
 #ifdef JQ_PROFILING
-    if (const char* thr_env = std::getenv("JQ_MOE_BUCKET_ROWS")) thr_override = std::strtoull(thr_env, nullptr, 10);
+    if (const char* thr_env = std::getenv("JQ_MOE_BUCKET_TOKENS")) min_tokens = std::strtoull(thr_env, nullptr, 10);  // measurement switch
 #endif
-    const uint64_t thr = thr_override ? thr_override : BUCKET_ROWS_PER_EXPERT;
-    const bool bucketed = !fused && !m->ctx->force_f32 && P >= thr * c.n_expert;
+    const bool bucketed = !fused && !m->ctx->force_f32 && T >= min_tokens;
     if (bucketed) {
-        if (int32_t rc = run_experts_bucketed(m, x_in, T, P, s)) return rc;
+        if (int32_t rc = run_experts_bucketed(m, x_in, T, P, rpj, s)) return rc;
     } else {
         m->last_rows = T, m->last_pairs = P, m->last_rpj = rpj;
         if (int32_t rc = run_experts(m, x_in, T, P, rpj, s, nw, eps)) return rc;
