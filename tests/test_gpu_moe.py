@@ -110,6 +110,41 @@ def test_deepseek4_style_sqrt_softplus_clamp_and_hash_routing(T):
     assert_close(got2, want2, what="deepseek4 hash routing")
 
 
+@pytest.mark.parametrize("type_id,n_expert", [(synth.Q4_K, 32), (synth.MXFP4, 32), (synth.Q4_K, 16)])
+def test_prefill_form_per_expert_row_counts(type_id, n_expert):
+    """From 128 tokens on every expert is placed on the device by its row count: none, below 12 (decode kernel), 12
+    and 32 (one narrow tile), 33 and 128 (one wide tile), 129 (a full tile and a narrow rest), 161 (a full tile and a
+    wide rest).  Forced ids (the hash-routing mechanism) fix the counts; n_used = 2 so that a token's experts differ.
+    With 32 experts the average is below 24 rows (tile GEMM and decode kernel side by side), with 16 above it (every
+    expert as tiles)."""
+    cfg = MoeConfig(gating=GATE_SOFTMAX, n_expert=n_expert, n_used=2, hidden=512, inter=256, norm=True,
+                    oob_policy=OOB_SKIP)
+    moe, router, banks, types, _ = build(cfg, type_id, seed=77)
+    counts = [0, 1, 11, 12, 32, 33, 128, 129, 161, 5, 7, 40, 13, 31, 2, 3]          # rows per expert, sum even
+    total = sum(counts)
+    assert total % 2 == 0
+    counts = counts + [0] * (n_expert - 16)
+    flat = np.repeat(np.arange(n_expert, dtype=np.uint32), counts)
+    # pair position i with position i + total / 2: the list is sorted, so a pair never holds one expert twice unless
+    # an expert has more than half of all rows (none does)
+    forced = np.stack([flat[:total // 2], flat[total // 2:]], axis=1)
+    assert (forced[:, 0] != forced[:, 1]).all()
+    T = forced.shape[0]
+    assert T >= 128
+    x = tokens(T, cfg.hidden, 5)
+    if type_id == synth.MXFP4:
+        # the synthetic MXFP4 scales reach 2^3: keep the outputs O(1), where the bound |a - b| <= 1e-3 max(|b|, 1) is
+        # a relative one (sums of terms of size 100 that cancel to less than 1 are beyond any f32 path)
+        x = (x * 0.03).astype(np.float32)
+    _, w, want = oracle_forward(cfg, x, router, banks, types, forced=forced)
+    got = moe.forward(x, forced_ids=forced)
+    gids, gw = moe.last_routing(T)
+    assert np.array_equal(gids, forced) and np.allclose(gw, w, rtol=1e-5)
+    assert float(np.abs(want).max()) > 0.05   # not a comparison of zeros
+    assert_close(got, want, what="prefill form, mixed row counts")
+    assert np.array_equal(bits(got), bits(moe.forward(x, forced_ids=forced)))   # run-to-run identical
+
+
 def test_out_of_range_expert_ids():
     base = dict(gating=GATE_SQRT_SOFTPLUS, n_expert=8, n_used=2, hidden=256, inter=256)
     x = tokens(3, 256, 1)
