@@ -30,6 +30,7 @@
 #include <cstring>
 
 #include "handles.cuh"
+#include "moe_jobs.cuh"
 
 namespace {
 
@@ -80,15 +81,18 @@ __device__ void wait_flag(const uint32_t* flag, uint32_t target, uint32_t polls,
     *status = 1;
 }
 
-// The last CTA of the grid to arrive publishes `epoch` in slot `me` of the given flag array of every peer.
+// The last of `n_ctas` CTAs to arrive publishes `epoch` in slot `me` of the given flag array of every peer.
 // All data stores of the grid are ordered before the flag stores.  Returns true in thread 0 of that last CTA.
 __device__ bool publish(uint32_t* done, const Window& win, uint64_t flag_off, uint32_t world, uint32_t me,
-                        uint32_t epoch) {
-    __threadfence_system();
+                        uint32_t epoch, uint32_t n_ctas) {
+    // The CTA's stores are ordered before thread 0's count by the barrier and a device-scope fence; the one thread
+    // that sees the last count issues the single system-scope fence (cumulative over everything the counted CTAs
+    // stored) and then the flag stores.  A system-scope fence in every thread of every CTA costs several
+    // microseconds a launch and adds nothing to that order.
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();
-        if (atomicAdd(done, 1u) == gridDim.x - 1) {
+        __threadfence();
+        if (atomicAdd(done, 1u) == n_ctas - 1) {
             *done = 0;
             __threadfence_system();
             for (uint32_t d = 0; d < world; ++d)
@@ -99,14 +103,28 @@ __device__ bool publish(uint32_t* done, const Window& win, uint64_t flag_off, ui
     return false;
 }
 
+// Where the dispatch kernel's last CTA leaves the local expert layer's job list (jobs == NULL: it does not build it).
+struct JobsOut {
+    uint32_t* list_token;
+    uint32_t* inv;
+    jq::MoeJob* jobs;
+    uint32_t* n_jobs;
+    uint32_t* n_list;
+    int* bad_id;
+    uint32_t rows_per_job;
+};
+
 // grid = P + world CTAs.  CTA p < P stores pair p's activation row and local expert id into its owner's
 // window; CTA P + d marks the unused slots of my block on rank d.  pair_slot[p] = owner * cap + slot.
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(Window win, Layout l, uint32_t me, const float* __restrict__ x,
                                                           const float* __restrict__ norm_w, float eps,
                                                           const uint32_t* __restrict__ ids, uint32_t T, uint32_t K,
                                                           uint32_t* __restrict__ pair_slot, uint32_t* __restrict__ epoch,
-                                                          uint32_t* __restrict__ done, uint32_t polls, int* status) {
+                                                          uint32_t* __restrict__ done, uint32_t polls, int* status,
+                                                          JobsOut jo) {
     __shared__ uint32_t s_red[8];
+    __shared__ jq::JobsSmem s_jobs;
+    __shared__ int s_last;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t P = T * K, tid = threadIdx.x;
     const uint32_t next_epoch = *epoch + 1;
@@ -162,53 +180,64 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(Window win, Layout l, 
         uint32_t* idd = reinterpret_cast<uint32_t*>(win.base[d] + l.o_ids_in) + (uint64_t)me * l.cap;
         for (uint32_t sl = cnt + tid; sl < l.cap; sl += blockDim.x) idd[sl] = l.n_local;
     }
-    if (publish(done, win, l.o_flag_in, l.world, me, next_epoch)) {
-        // The publishing thread also waits (bounded) for every rank's dispatch of this epoch and then advances
-        // the local epoch counter: the kernels behind this one in the stream read rows_in / ids_in and the new
-        // epoch, so the kernel must not end before the rows are there.  Every CTA of this grid read the old
-        // epoch before it counted itself in.
-        for (uint32_t r = 0; r < l.world; ++r)
-            wait_flag(reinterpret_cast<const uint32_t*>(win.base[me] + l.o_flag_in) + r, next_epoch, polls, status);
-        *epoch = next_epoch;
+    const bool last = publish(done, win, l.o_flag_in, l.world, me, next_epoch, gridDim.x);
+    if (tid == 0) s_last = last ? 1 : 0;
+    __syncthreads();
+    if (s_last) {
+        // The last CTA also waits (bounded, one thread per rank) for every rank's dispatch of this epoch and then
+        // advances the local epoch counter: the kernels behind this one in the stream read rows_in / ids_in and
+        // the new epoch, so the kernel must not end before the rows are there.  Every CTA of this grid read the
+        // old epoch before it counted itself in.
+        if (tid < l.world)
+            wait_flag(reinterpret_cast<const uint32_t*>(win.base[me] + l.o_flag_in) + tid, next_epoch, polls, status);
+        __syncthreads();
+        if (tid == 0) *epoch = next_epoch;
+        // ... and builds the job list of the local expert layer over the ids that have just arrived (one id per
+        // row, an id out of range marks an unused slot), which saves the launch that would do it.
+        if (jo.jobs != nullptr)
+            jq::build_jobs<true>(reinterpret_cast<const uint32_t*>(win.base[me] + l.o_ids_in), l.world * l.cap, 1u, l.n_local,
+                                 jo.rows_per_job, jo.list_token, jo.inv, jo.jobs, jo.n_jobs, jo.n_list, jo.bad_id, s_jobs, tid,
+                                 blockDim.x, [] { __syncthreads(); });
     }
 }
 
-// grid = world * cap CTAs: row r of my rows_in (source rank r / cap, its slot r % cap).  A valid row's output,
-// out_list[inv[r], :], is stored into the source's rows_back block `me`.
-__global__ void __launch_bounds__(256) ep_return_kernel(Window win, Layout l, uint32_t me,
-                                                        const float* __restrict__ out_list,
-                                                        const uint32_t* __restrict__ inv,
-                                                        const uint32_t* __restrict__ epoch, uint32_t* __restrict__ done) {
+// Return and combine in one launch.  CTAs 0 .. n_rows-1 (n_rows = world * cap): row r of my rows_in (source rank
+// r / cap, its slot r % cap); a valid row's output, out_list[inv[r], :], is stored into the source's rows_back block
+// `me`, and the last of them publishes the return flag.  The CTAs behind them form
+//     y[t, :] = sum over slots (in slot order) of w[t, s] * rows_back[pair_slot[t*K+s], :] (+ residual)
+// after every owner's return of this epoch has arrived.  The return CTAs wait for nothing and come first in the
+// grid, so the combine CTAs' (bounded) wait never keeps them from running, whatever the grid's size.
+__global__ void __launch_bounds__(256) ep_return_combine_kernel(Window win, Layout l, uint32_t me, uint32_t n_rows,
+                                                                const float* __restrict__ out_list,
+                                                                const uint32_t* __restrict__ inv,
+                                                                const uint32_t* __restrict__ pair_slot,
+                                                                const float* __restrict__ wts, uint32_t T, uint32_t K,
+                                                                const uint32_t* __restrict__ epoch, uint32_t* __restrict__ done,
+                                                                const float* residual, float* y, uint32_t polls, int* status) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t r = blockIdx.x, src_rank = r / l.cap, slot = r % l.cap;
-    const uint32_t id = reinterpret_cast<const uint32_t*>(win.base[me] + l.o_ids_in)[r];
-    if (id < l.n_local) {
-        const uint32_t pos = inv[r];
-        float4* dst = reinterpret_cast<float4*>(win.base[src_rank] + l.o_rows_back) +
-                      ((uint64_t)me * l.cap + slot) * (l.hidden / 4);
-        const float4* src = reinterpret_cast<const float4*>(out_list) + (uint64_t)pos * (l.hidden / 4);
-        for (uint32_t c = threadIdx.x; c < l.hidden / 4; c += blockDim.x) dst[c] = src[c];
+    if (blockIdx.x < n_rows) {
+        const uint32_t r = blockIdx.x, src_rank = r / l.cap, slot = r % l.cap;
+        const uint32_t id = reinterpret_cast<const uint32_t*>(win.base[me] + l.o_ids_in)[r];
+        if (id < l.n_local) {
+            const uint32_t pos = inv[r];
+            float4* dst = reinterpret_cast<float4*>(win.base[src_rank] + l.o_rows_back) +
+                          ((uint64_t)me * l.cap + slot) * (l.hidden / 4);
+            const float4* src = reinterpret_cast<const float4*>(out_list) + (uint64_t)pos * (l.hidden / 4);
+            for (uint32_t c = threadIdx.x; c < l.hidden / 4; c += blockDim.x) dst[c] = src[c];
+        }
+        publish(done, win, l.o_flag_back, l.world, me, *epoch, n_rows);
+        return;
     }
-    publish(done, win, l.o_flag_back, l.world, me, *epoch);
-}
-
-// y[t, :] = sum over slots (in slot order) of w[t, s] * rows_back[pair_slot[t*K+s], :], after every owner's
-// return of this epoch has arrived.
-__global__ void __launch_bounds__(256) ep_combine_kernel(const uint8_t* __restrict__ my_window, Layout l,
-                                                         const uint32_t* __restrict__ pair_slot,
-                                                         const float* __restrict__ wts, uint32_t T, uint32_t K,
-                                                         const uint32_t* __restrict__ epoch, const float* residual,
-                                                         float* y, uint32_t polls, int* status) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint8_t* my_window = win.base[me];
     if (threadIdx.x < l.world)
         wait_flag(reinterpret_cast<const uint32_t*>(my_window + l.o_flag_back) + threadIdx.x, *epoch, polls, status);
     __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const float* back = reinterpret_cast<const float*>(my_window + l.o_rows_back);
-    const uint32_t h4 = l.hidden / 4;
+    const uint32_t h4 = l.hidden / 4, n_comb = gridDim.x - n_rows;
     const uint64_t total = (uint64_t)T * h4;
-    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total;
-         i += (uint64_t)gridDim.x * blockDim.x) {
+    for (uint64_t i = (blockIdx.x - n_rows) * (uint64_t)blockDim.x + threadIdx.x; i < total;
+         i += (uint64_t)n_comb * blockDim.x) {
         const uint32_t t = (uint32_t)(i / h4), c = (uint32_t)(i % h4);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         // rows_back is written by peers: read it through L2, never from a stale L1 line
@@ -412,19 +441,23 @@ int32_t jq_ep_forward_norm_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const 
     uint8_t* mine = e->win.base[e->rank];
     const uint32_t P = (uint32_t)T * e->n_used;
     if (int32_t r = jq_moe_route_norm_dev(router, x_dev, T, norm_w_dev, eps, forced_ids_dev, e->ids, e->wts, stream)) return r;
+    // at decode sizes the dispatch kernel's last CTA also builds the expert layer's job list (one launch fewer)
+    const bool jobs_in_dispatch = rows <= 1024 && ec.n_expert <= jq::MAX_EXPERTS;
+    JobsOut jo = {};
+    if (jobs_in_dispatch)
+        jo = JobsOut{experts->list_token, experts->inv, experts->jobs, experts->n_jobs, experts->n_list, experts->bad_dev,
+                     jq_moe_rows_per_job(P, ec.n_expert)};
     JQ_CUDA(jq::launch_pdl(ep_dispatch_kernel, dim3(P + e->world), 256, 0, s, e->win, e->lay, e->rank, x_dev,
                            norm_w_dev, eps, (const uint32_t*)e->ids, (uint32_t)T, e->n_used, e->pair_slot, e->epoch, e->done,
-                           e->polls, e->ctx->status_dev));
+                           e->polls, e->ctx->status_dev, jo));
     if (int32_t r = jq_moe_experts_list(experts, reinterpret_cast<const float*>(mine + e->lay.o_rows_in), rows,
-                                        reinterpret_cast<const uint32_t*>(mine + e->lay.o_ids_in), P, s))
+                                        reinterpret_cast<const uint32_t*>(mine + e->lay.o_ids_in), P, s, jobs_in_dispatch))
         return r;
-    JQ_CUDA(jq::launch_pdl(ep_return_kernel, dim3(rows), 256, 0, s, e->win, e->lay, e->rank,
-                           (const float*)experts->out, (const uint32_t*)experts->inv, (const uint32_t*)e->epoch,
-                           e->done + 1));
     const unsigned cblocks = (unsigned)std::min<uint64_t>(((uint64_t)T * (e->hidden / 4) + 255) / 256, 148 * 4);
-    JQ_CUDA(jq::launch_pdl(ep_combine_kernel, dim3(cblocks), 256, 0, s, (const uint8_t*)mine, e->lay,
-                           (const uint32_t*)e->pair_slot, (const float*)e->wts, (uint32_t)T, e->n_used,
-                           (const uint32_t*)e->epoch, residual_dev, y_dev, e->polls, e->ctx->status_dev));
+    JQ_CUDA(jq::launch_pdl(ep_return_combine_kernel, dim3(rows + cblocks), 256, 0, s, e->win, e->lay, e->rank, rows,
+                           (const float*)experts->out, (const uint32_t*)experts->inv, (const uint32_t*)e->pair_slot,
+                           (const float*)e->wts, (uint32_t)T, e->n_used, (const uint32_t*)e->epoch, e->done + 1, residual_dev,
+                           y_dev, e->polls, e->ctx->status_dev));
     return jq::OK;
 }
 

@@ -345,12 +345,19 @@ int32_t check_bank(const char* name, const jq_weight* w, uint64_t experts, uint6
 
 // Expert MLPs over rows with one expert id each, left in expert-sorted list order: row r's output is
 // m->out[m->inv[r], :] (inv = 0xFFFFFFFF for an id out of range).  Arguments are checked by the callers.
+uint32_t jq_moe_rows_per_job(uint64_t live_rows, uint32_t n_expert) {
+    // up to 16 rows (one or two sequences per rank of an expert-parallel step) few rows share an expert, and the
+    // one-row form of the decode kernel is the faster one (a shared expert then is two jobs)
+    return rows_per_job_for(live_rows, live_rows <= 16 ? 1 : 2, n_expert);
+}
+
 int32_t jq_moe_experts_list(jq_moe* m, const float* x_dev, uint64_t n_rows, const uint32_t* expert_ids_dev,
-                            uint64_t live_rows, cudaStream_t s) {
+                            uint64_t live_rows, cudaStream_t s, bool jobs_prebuilt) {
     const jq_moe_config& c = m->cfg;
-    uint32_t rpj = rows_per_job_for(n_rows, n_rows == 1 ? 1 : 2, c.n_expert);
-    JQ_CUDA(jq::launch_moe_jobs(expert_ids_dev, (uint32_t)n_rows, 1, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
-                                m->n_jobs, m->n_list, m->bad_dev, s));
+    uint32_t rpj = jq_moe_rows_per_job(live_rows, c.n_expert);
+    if (!jobs_prebuilt)
+        JQ_CUDA(jq::launch_moe_jobs(expert_ids_dev, (uint32_t)n_rows, 1, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
+                                    m->n_jobs, m->n_list, m->bad_dev, s));
     if (!m->ctx->force_f32 && live_rows >= BUCKET_MIN_TOKENS) return run_experts_bucketed(m, x_dev, n_rows, n_rows, rpj, s);
     m->last_rows = m->last_pairs = n_rows, m->last_rpj = rpj;
     return run_experts(m, x_dev, n_rows, n_rows, rpj, s);
