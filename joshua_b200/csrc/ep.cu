@@ -30,7 +30,6 @@
 #include <cstring>
 
 #include "handles.cuh"
-#include "moe_jobs.cuh"
 
 namespace {
 
@@ -103,27 +102,14 @@ __device__ bool publish(uint32_t* done, const Window& win, uint64_t flag_off, ui
     return false;
 }
 
-// Where the dispatch kernel's last CTA leaves the local expert layer's job list (jobs == NULL: it does not build it).
-struct JobsOut {
-    uint32_t* list_token;
-    uint32_t* inv;
-    jq::MoeJob* jobs;
-    uint32_t* n_jobs;
-    uint32_t* n_list;
-    int* bad_id;
-    uint32_t rows_per_job;
-};
-
 // grid = P + world CTAs.  CTA p < P stores pair p's activation row and local expert id into its owner's
 // window; CTA P + d marks the unused slots of my block on rank d.  pair_slot[p] = owner * cap + slot.
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(Window win, Layout l, uint32_t me, const float* __restrict__ x,
                                                           const float* __restrict__ norm_w, float eps,
                                                           const uint32_t* __restrict__ ids, uint32_t T, uint32_t K,
                                                           uint32_t* __restrict__ pair_slot, uint32_t* __restrict__ epoch,
-                                                          uint32_t* __restrict__ done, uint32_t polls, int* status,
-                                                          JobsOut jo) {
+                                                          uint32_t* __restrict__ done, uint32_t polls, int* status) {
     __shared__ uint32_t s_red[8];
-    __shared__ jq::JobsSmem s_jobs;
     __shared__ int s_last;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t P = T * K, tid = threadIdx.x;
@@ -192,12 +178,6 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(Window win, Layout l, 
             wait_flag(reinterpret_cast<const uint32_t*>(win.base[me] + l.o_flag_in) + tid, next_epoch, polls, status);
         __syncthreads();
         if (tid == 0) *epoch = next_epoch;
-        // ... and builds the job list of the local expert layer over the ids that have just arrived (one id per
-        // row, an id out of range marks an unused slot), which saves the launch that would do it.
-        if (jo.jobs != nullptr)
-            jq::build_jobs<true>(reinterpret_cast<const uint32_t*>(win.base[me] + l.o_ids_in), l.world * l.cap, 1u, l.n_local,
-                                 jo.rows_per_job, jo.list_token, jo.inv, jo.jobs, jo.n_jobs, jo.n_list, jo.bad_id, s_jobs, tid,
-                                 blockDim.x, [] { __syncthreads(); });
     }
 }
 
@@ -441,17 +421,13 @@ int32_t jq_ep_forward_norm_dev(jq_ep* e, jq_moe* router, jq_moe* experts, const 
     uint8_t* mine = e->win.base[e->rank];
     const uint32_t P = (uint32_t)T * e->n_used;
     if (int32_t r = jq_moe_route_norm_dev(router, x_dev, T, norm_w_dev, eps, forced_ids_dev, e->ids, e->wts, stream)) return r;
-    // at decode sizes the dispatch kernel's last CTA also builds the expert layer's job list (one launch fewer)
-    const bool jobs_in_dispatch = rows <= 1024 && ec.n_expert <= jq::MAX_EXPERTS;
-    JobsOut jo = {};
-    if (jobs_in_dispatch)
-        jo = JobsOut{experts->list_token, experts->inv, experts->jobs, experts->n_jobs, experts->n_list, experts->bad_dev,
-                     jq_moe_rows_per_job(P, ec.n_expert)};
     JQ_CUDA(jq::launch_pdl(ep_dispatch_kernel, dim3(P + e->world), 256, 0, s, e->win, e->lay, e->rank, x_dev,
                            norm_w_dev, eps, (const uint32_t*)e->ids, (uint32_t)T, e->n_used, e->pair_slot, e->epoch, e->done,
-                           e->polls, e->ctx->status_dev, jo));
+                           e->polls, e->ctx->status_dev));
+    // (building the expert layer's job list in the dispatch kernel's last CTA instead of a launch of its own was
+    // measured slower: 256 threads behind the wait against 1024 threads that are resident before it ends)
     if (int32_t r = jq_moe_experts_list(experts, reinterpret_cast<const float*>(mine + e->lay.o_rows_in), rows,
-                                        reinterpret_cast<const uint32_t*>(mine + e->lay.o_ids_in), P, s, jobs_in_dispatch))
+                                        reinterpret_cast<const uint32_t*>(mine + e->lay.o_ids_in), P, s))
         return r;
     const unsigned cblocks = (unsigned)std::min<uint64_t>(((uint64_t)T * (e->hidden / 4) + 255) / 256, 148 * 4);
     JQ_CUDA(jq::launch_pdl(ep_return_combine_kernel, dim3(rows + cblocks), 256, 0, s, e->win, e->lay, e->rank, rows,

@@ -154,10 +154,8 @@ struct jq_moe {
 // Expert MLPs over n_rows rows with given local expert ids (an id out of range marks an unused row).
 // `live_rows` is the caller's estimate of how many rows carry a valid id: from 12 per expert on, the rows run
 // in buckets on the tile GEMM (which reads the job list back and so synchronises the stream).
-// With `jobs_prebuilt` the caller's own kernel has already left the job list of these ids in the layer's buffers
-// (built with jq_moe_rows_per_job(live_rows, n_expert) rows per job).
 int32_t jq_moe_experts_list(jq_moe* m, const float* x_dev, uint64_t n_rows, const uint32_t* expert_ids_dev,
-                            uint64_t live_rows, cudaStream_t s, bool jobs_prebuilt = false);
+                            uint64_t live_rows, cudaStream_t s);
 // Rows per job for about `live_rows` rows with valid ids: one while two rows rarely share an expert (the decode
 // kernel's one-row form), else as for a batch of tokens.
 uint32_t jq_moe_rows_per_job(uint64_t live_rows, uint32_t n_expert);

@@ -352,12 +352,11 @@ uint32_t jq_moe_rows_per_job(uint64_t live_rows, uint32_t n_expert) {
 }
 
 int32_t jq_moe_experts_list(jq_moe* m, const float* x_dev, uint64_t n_rows, const uint32_t* expert_ids_dev,
-                            uint64_t live_rows, cudaStream_t s, bool jobs_prebuilt) {
+                            uint64_t live_rows, cudaStream_t s) {
     const jq_moe_config& c = m->cfg;
     uint32_t rpj = jq_moe_rows_per_job(live_rows, c.n_expert);
-    if (!jobs_prebuilt)
-        JQ_CUDA(jq::launch_moe_jobs(expert_ids_dev, (uint32_t)n_rows, 1, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
-                                    m->n_jobs, m->n_list, m->bad_dev, s));
+    JQ_CUDA(jq::launch_moe_jobs(expert_ids_dev, (uint32_t)n_rows, 1, c.n_expert, rpj, m->list_token, m->inv, m->jobs,
+                                m->n_jobs, m->n_list, m->bad_dev, s));
     if (!m->ctx->force_f32 && live_rows >= BUCKET_MIN_TOKENS) return run_experts_bucketed(m, x_dev, n_rows, n_rows, rpj, s);
     m->last_rows = m->last_pairs = n_rows, m->last_rpj = rpj;
     return run_experts(m, x_dev, n_rows, n_rows, rpj, s);

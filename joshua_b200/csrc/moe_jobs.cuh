@@ -1,5 +1,4 @@
-// The job list of the grouped expert matmuls, built by one CTA: shared between the MoE layer's kernels (moe.cu) and
-// the expert-parallel dispatch kernel (ep.cu), whose last CTA builds the list right behind the exchange.
+// The job list of the grouped expert matmuls, built by one CTA (the MoE layer's kernels in moe.cu).
 #pragma once
 
 #include <cstdint>
@@ -19,9 +18,8 @@ struct JobsSmem {
     uint32_t cnt[MAX_EXPERTS], off[MAX_EXPERTS], job[MAX_EXPERTS];
 };
 
-// Body of the job builder for the `nthreads` threads of one CTA (tid = 0 .. nthreads - 1, whole warps).  With
-// THROUGH_L2 the ids are read with ld.global.cg: they were stored by other devices while this kernel ran.
-template <bool THROUGH_L2 = false, class Sync>
+// Body of the job builder for the `nthreads` threads of one CTA (tid = 0 .. nthreads - 1, whole warps).
+template <class Sync>
 __device__ __forceinline__ void build_jobs(const uint32_t* __restrict__ ids, uint32_t T, uint32_t K, uint32_t E,
                                            uint32_t rows_per_job, uint32_t* __restrict__ list_token,
                                            uint32_t* __restrict__ inv, MoeJob* __restrict__ jobs,
@@ -36,7 +34,7 @@ __device__ __forceinline__ void build_jobs(const uint32_t* __restrict__ ids, uin
     for (uint32_t e = tid; e < E; e += nthreads) s_cnt[e] = 0;
     cta_sync();
     for (uint32_t p = tid; p < P; p += nthreads) {
-        uint32_t e = THROUGH_L2 ? __ldcg(ids + p) : ids[p];
+        uint32_t e = ids[p];
         if (e < E)
             atomicAdd(&s_cnt[e], 1u);
         else {
@@ -64,7 +62,7 @@ __device__ __forceinline__ void build_jobs(const uint32_t* __restrict__ ids, uin
         uint32_t base = s_off[e];
         for (uint32_t p0 = 0; p0 < P; p0 += 32) {
             uint32_t p = p0 + lane;
-            bool hit = p < P && (THROUGH_L2 ? __ldcg(ids + p) : ids[p]) == e;
+            bool hit = p < P && ids[p] == e;
             uint32_t ballot = __ballot_sync(0xFFFFFFFFu, hit);
             if (hit) {
                 uint32_t pos = base + __popc(ballot & ((1u << lane) - 1));
