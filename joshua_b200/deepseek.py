@@ -182,7 +182,7 @@ class DeepseekDecoder:
         self.logits = torch.empty(B, c.vocab, **f32)
         self.att_scratch = torch.empty(L.jq_attention_scratch_bytes(B, nh, c.v_dim, max_ctx) // 4 + 1, **f32)
         self.argmax_scratch = torch.empty(L.jq_argmax_scratch_bytes(B) // 4 + 1, **f32)
-        self.launches_per_step = (10 + (5 if self.world == 1 else 10)) * c.layers + 4
+        self.launches_per_step = (10 + (5 if self.world == 1 else 9)) * c.layers + 4
 
     def step(self, stream=None) -> None:
         """One token per sequence: reads self.token / self.pos, writes self.logits and the next self.token."""

@@ -97,7 +97,7 @@ class MoeDecoder(LlamaDecoder):
                 rl.reserve(batch, 0)
                 el.reserve(cap, cap)
                 self.ffn_layers.append(dict(router=rl, experts=el, keep=banks))
-        self.launches_per_step = (3 + (4 if self.world == 1 else 7)) * cfg.layers + 4
+        self.launches_per_step = (3 + (4 if self.world == 1 else 6)) * cfg.layers + 4
 
     def _ffn(self, ly, s) -> None:
         """self.x += MoE(rmsnorm(self.x; ffn_norm)); the residual add rides in the combine kernel."""
