@@ -345,7 +345,11 @@ __global__ void __launch_bounds__(1024) moe_jobs_kernel(const uint32_t* __restri
     __shared__ JobsSliceSmem ss;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (T * K > 1024)
+    if (T * K <= JOBS_SMALL_PAIRS) {
+        __shared__ JobsSmallSmem jsm;
+        build_jobs_small(ids, T, K, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id, js, jsm, threadIdx.x,
+                         blockDim.x, [] { __syncthreads(); });
+    } else if (T * K > 1024)
         build_jobs_sliced(ids, T, K, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id, js, ss, threadIdx.x,
                           blockDim.x);
     else
@@ -367,6 +371,7 @@ __global__ void __launch_bounds__(128) moe_route_fused_kernel(
     uint32_t* __restrict__ counter) {
     __shared__ RouteSmem sm;
     __shared__ JobsSmem js;
+    __shared__ JobsSmallSmem jsm;
     __shared__ uint32_t s_last;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -437,8 +442,12 @@ __global__ void __launch_bounds__(128) moe_route_fused_kernel(
     if (do_jobs) {
         __threadfence_block();
         __syncthreads();
-        build_jobs(ids, T, rp.n_used, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id, js, threadIdx.x,
-                   128u, [] { __syncthreads(); });
+        if (T * rp.n_used <= JOBS_SMALL_PAIRS)
+            build_jobs_small(ids, T, rp.n_used, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id, js, jsm,
+                             threadIdx.x, 128u, [] { __syncthreads(); });
+        else
+            build_jobs(ids, T, rp.n_used, E, rows_per_job, list_token, inv, jobs, n_jobs, n_list, bad_id, js, threadIdx.x,
+                       128u, [] { __syncthreads(); });
     }
     if (trace && threadIdx.x == 0) {
         trace[0] = t_start, trace[1] = t_logits, trace[2] = t_counted, trace[3] = t_routed, trace[4] = moe_now();

@@ -81,4 +81,87 @@ __device__ __forceinline__ void build_jobs(const uint32_t* __restrict__ ids, uin
     }
 }
 
+// The same lists for at most JOBS_SMALL_PAIRS pairs (decode batches), written for latency: one trip to memory for
+// the ids, everything else out of shared memory, a parallel scan over the experts instead of one thread walking
+// them.  Same lists as build_jobs.  `rows_per_job` is 1, 2, 4 or 8.
+constexpr uint32_t JOBS_SMALL_PAIRS = 64;
+struct JobsSmallSmem {
+    uint32_t ids[JOBS_SMALL_PAIRS];
+    uint32_t warp_rows[32], warp_jobs[32];
+};
+
+template <class Sync>
+__device__ __forceinline__ void build_jobs_small(const uint32_t* __restrict__ ids, uint32_t T, uint32_t K, uint32_t E,
+                                                 uint32_t rows_per_job, uint32_t* __restrict__ list_token,
+                                                 uint32_t* __restrict__ inv, MoeJob* __restrict__ jobs,
+                                                 uint32_t* __restrict__ n_jobs, uint32_t* __restrict__ n_list,
+                                                 int* __restrict__ bad_id, JobsSmem& js, JobsSmallSmem& sm, uint32_t tid,
+                                                 uint32_t nthreads, Sync cta_sync) {
+    const uint32_t P = T * K, lane = tid & 31, warp = tid >> 5, nwarp = nthreads >> 5;
+    const uint32_t shift = 31u - __clz(rows_per_job);
+    if (tid < P) {
+        const uint32_t e = ids[tid];
+        sm.ids[tid] = e;
+        if (e >= E) {
+            inv[tid] = 0xFFFFFFFFu;
+            *bad_id = 1;
+        }
+    }
+    cta_sync();
+    // thread t owns the experts [t * per, (t + 1) * per): counts, then an exclusive scan of rows and jobs
+    const uint32_t per = (E + nthreads - 1) / nthreads;
+    uint32_t rows = 0, njob = 0;
+    for (uint32_t i = 0; i < per; ++i) {
+        const uint32_t e = tid * per + i;
+        if (e >= E) break;
+        uint32_t c = 0;
+        for (uint32_t p = 0; p < P; ++p) c += sm.ids[p] == e ? 1u : 0u;
+        js.cnt[e] = c;
+        rows += c;
+        njob += (c + rows_per_job - 1) >> shift;
+    }
+    uint32_t sr = rows, sj = njob;  // inclusive scans over the warp
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t ur = __shfl_up_sync(0xFFFFFFFFu, sr, off), uj = __shfl_up_sync(0xFFFFFFFFu, sj, off);
+        if ((int)lane >= off) sr += ur, sj += uj;
+    }
+    if (lane == 31) sm.warp_rows[warp] = sr, sm.warp_jobs[warp] = sj;
+    cta_sync();
+    uint32_t base_r = 0, base_j = 0;
+    for (uint32_t w = 0; w < warp; ++w) base_r += sm.warp_rows[w], base_j += sm.warp_jobs[w];
+    uint32_t off_r = base_r + sr - rows, off_j = base_j + sj - njob;  // exclusive
+    for (uint32_t i = 0; i < per; ++i) {
+        const uint32_t e = tid * per + i;
+        if (e >= E) break;
+        const uint32_t c = js.cnt[e];
+        js.off[e] = off_r;
+        for (uint32_t j = 0; j * rows_per_job < c; ++j) {
+            MoeJob jd;
+            jd.expert = e;
+            jd.row0 = off_r + j * rows_per_job;
+            jd.cnt = min(rows_per_job, c - j * rows_per_job);
+            jobs[off_j + j] = jd;
+        }
+        off_r += c;
+        off_j += (c + rows_per_job - 1) >> shift;
+    }
+    if (tid == nthreads - 1) {
+        *n_jobs = off_j;
+        *n_list = off_r;
+    }
+    cta_sync();
+    // a pair's position: its expert's offset + the earlier pairs of the same expert
+    if (tid < P) {
+        const uint32_t e = sm.ids[tid];
+        if (e < E) {
+            uint32_t rank = 0;
+            for (uint32_t q = 0; q < tid; ++q) rank += sm.ids[q] == e ? 1u : 0u;
+            const uint32_t pos = js.off[e] + rank;
+            list_token[pos] = tid / K;
+            inv[tid] = pos;
+        }
+    }
+}
+
 }  // namespace jq
