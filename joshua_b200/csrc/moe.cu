@@ -235,6 +235,126 @@ __device__ __forceinline__ void route_tokens(const float* __restrict__ logits, c
     }
 }
 
+// The same routing with a token's scores held in registers (lane l holds experts l, l + 32, ...: EPL of them),
+// for layers without a group limit: no trips through shared memory between the steps, loops of the token's real
+// width.  Same operations in the same order as route_tokens, hence the same ids and weights.
+template <int EPL>
+__device__ __forceinline__ void route_tokens_regs(const float* __restrict__ logits, const MoeRouteParams& rp, uint32_t T,
+                                                  const float* __restrict__ bias, const uint32_t* __restrict__ forced_ids,
+                                                  uint32_t* __restrict__ ids, float* __restrict__ wts, RouteSmem& sm,
+                                                  uint32_t first, uint32_t stride, uint32_t wq, uint32_t lane) {
+    const uint32_t E = rp.n_expert, K = rp.n_used;
+    float* prob = sm.prob[wq];
+    uint32_t* chosen = sm.chosen[wq];
+    for (uint32_t t = first + wq; t < T; t += stride) {
+        float lg[EPL], pv[EPL];
+        bool in[EPL];
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            const uint32_t e = lane + 32 * i;
+            in[i] = e < E;
+            lg[i] = in[i] ? __ldcg(logits + (uint64_t)t * E + e) : -INFINITY;  // written by other CTAs: through L2
+        }
+        if (rp.gating == MOE_GATE_SOFTMAX) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i)
+                if (in[i]) mx = fmaxf(mx, lg[i]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+            float sum = 0.0f;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                pv[i] = in[i] ? expf(lg[i] - mx) : 0.0f;
+                if (in[i]) sum += pv[i];
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) pv[i] = pv[i] / sum;
+        } else if (rp.gating == MOE_GATE_SIGMOID) {
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) pv[i] = 1.0f / (1.0f + expf(-lg[i]));
+        } else {  // sqrt(softplus), softplus(x) = max(x, 0) + log(1 + exp(-|x|))
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) pv[i] = sqrtf(fmaxf(lg[i], 0.0f) + logf(expf(-fabsf(lg[i])) + 1.0f));
+        }
+#pragma unroll
+        for (int i = 0; i < EPL; ++i)
+            if (in[i]) prob[lane + 32 * i] = pv[i];
+        uint32_t* id = ids + (uint64_t)t * K;
+        float* w = wts + (uint64_t)t * K;
+        if (forced_ids) {
+            // hash-routed layers: ids come from a token-id table, weights from the gate scores
+            for (uint32_t s = lane; s < K; s += 32) {
+                chosen[s] = forced_ids[(uint64_t)t * K + s];
+                id[s] = chosen[s];
+            }
+        } else {
+            // top-k: every round is a local scan, one warp-wide maximum of the order-preserving integer image of
+            // the value, and one warp-wide minimum of the candidates' indices (ties go to the lower index)
+            float val[EPL];
+            uint32_t live = 0;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                val[i] = in[i] ? (bias ? pv[i] + bias[lane + 32 * i] : pv[i]) : -INFINITY;
+                if (in[i]) live |= 1u << i;
+            }
+            for (uint32_t s = 0; s < K; ++s) {
+                float best = -INFINITY;
+                int bi = -1;
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) {
+                    if (((live >> i) & 1u) && (bi < 0 || val[i] > best)) {
+                        best = val[i];
+                        bi = i;
+                    }
+                }
+                const uint32_t bits = __float_as_uint(best);
+                const uint32_t key = bi < 0 ? 0u : (bits ^ ((bits >> 31) ? 0xFFFFFFFFu : 0x80000000u));
+                const uint32_t mx = __reduce_max_sync(0xFFFFFFFFu, key);
+                const uint32_t cand = (bi >= 0 && key == mx) ? lane + 32u * (uint32_t)bi : 0xFFFFFFFFu;
+                const uint32_t e = __reduce_min_sync(0xFFFFFFFFu, cand);
+                if (e != 0xFFFFFFFFu && (e & 31u) == lane) live &= ~(1u << (e >> 5));
+                if (lane == 0) {
+                    chosen[s] = e;
+                    id[s] = e;
+                }
+            }
+        }
+        __syncwarp();
+        // weights from the unbiased scores of the chosen experts: the sum runs in slot order, then every
+        // weight is written once
+        float sum = 0.0f;
+        for (uint32_t s = 0; s < K; ++s) {
+            const uint32_t e = chosen[s];
+            sum += e < E ? prob[e] : 0.0f;
+        }
+        const float denom = rp.renorm_plus_eps ? sum + 1e-20f : fmaxf(sum, 6.1035156e-5f);
+        for (uint32_t s = lane; s < K; s += 32) {
+            const uint32_t e = chosen[s];
+            float p = e < E ? prob[e] : 0.0f;
+            if (rp.norm) p = p / denom;
+            if (rp.scale != 0.0f && rp.scale != 1.0f) p = p * rp.scale;
+            w[s] = p;
+        }
+        __syncwarp();
+    }
+}
+
+// Routing of tokens first + wq, ... by warp wq: the register form where it applies, else the general one.
+__device__ __forceinline__ void route_dispatch(const float* __restrict__ logits, const MoeRouteParams& rp, uint32_t T,
+                                               const float* __restrict__ bias, const uint32_t* __restrict__ forced_ids,
+                                               uint32_t* __restrict__ ids, float* __restrict__ wts, RouteSmem& sm,
+                                               uint32_t first, uint32_t stride, uint32_t wq, uint32_t lane) {
+    if (rp.n_group <= 1 && rp.n_expert <= 128)
+        route_tokens_regs<4>(logits, rp, T, bias, forced_ids, ids, wts, sm, first, stride, wq, lane);
+    else if (rp.n_group <= 1 && rp.n_expert <= 256)
+        route_tokens_regs<8>(logits, rp, T, bias, forced_ids, ids, wts, sm, first, stride, wq, lane);
+    else
+        route_tokens(logits, rp, T, bias, forced_ids, ids, wts, sm, first, stride, wq, lane);
+}
+
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, MoeRouteParams rp, uint32_t T,
                                                         const float* __restrict__ bias,
                                                         const uint32_t* __restrict__ forced_ids,
@@ -242,8 +362,8 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     __shared__ RouteSmem sm;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    route_tokens(logits, rp, T, bias, forced_ids, ids, wts, sm, blockIdx.x * 4, gridDim.x * 4, threadIdx.x >> 5,
-                 threadIdx.x & 31);
+    route_dispatch(logits, rp, T, bias, forced_ids, ids, wts, sm, blockIdx.x * 4, gridDim.x * 4, threadIdx.x >> 5,
+                   threadIdx.x & 31);
 }
 
 // The same lists for many pairs (prefill sizes).  The stable fill above lets every warp walk all pairs once per
@@ -436,7 +556,7 @@ __global__ void __launch_bounds__(128) moe_route_fused_kernel(
     }
     __syncthreads();
     if (!s_last) return;
-    route_tokens(logits, rp, T, bias, forced_ids, ids, wts, sm, 0, 4, wq, lane);
+    route_dispatch(logits, rp, T, bias, forced_ids, ids, wts, sm, 0, 4, wq, lane);
     unsigned long long t_routed = 0;
     if (trace && threadIdx.x == 0) t_routed = moe_now();
     if (do_jobs) {
