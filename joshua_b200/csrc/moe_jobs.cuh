@@ -81,10 +81,10 @@ __device__ __forceinline__ void build_jobs(const uint32_t* __restrict__ ids, uin
     }
 }
 
-// The same lists for at most JOBS_SMALL_PAIRS pairs (decode batches), written for latency: one trip to memory for
+// The same lists for at most JOBS_SMALL_PAIRS pairs (decode batches of up to 32 tokens x 8), written for latency: one trip to memory for
 // the ids, everything else out of shared memory, a parallel scan over the experts instead of one thread walking
 // them.  Same lists as build_jobs.  `rows_per_job` is 1, 2, 4 or 8.
-constexpr uint32_t JOBS_SMALL_PAIRS = 64;
+constexpr uint32_t JOBS_SMALL_PAIRS = 256;
 struct JobsSmallSmem {
     uint32_t ids[JOBS_SMALL_PAIRS];
     uint32_t warp_rows[32], warp_jobs[32];
