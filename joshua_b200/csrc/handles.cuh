@@ -144,8 +144,8 @@ struct jq_moe {
     uint64_t bucket_pairs = 0;
     uint64_t last_rows = 0, last_pairs = 0;  // shape of the job list the last decode-sized call left (replay entry)
     uint32_t last_rpj = 0;
-    jq::GemmTile* tiles = nullptr;  // prefill path: tile list of the grouped tile GEMM
-    uint64_t tiles_cap = 0;
+    jq::GemmTile* tiles = nullptr;  // prefill path: narrow and wide tile lists, the small experts' job list, 4 counts
+    uint64_t tiles_cap = 0;         // bytes allocated behind `tiles`
     int* bad_host = nullptr;  // pinned, device-visible: an expert id was out of range
     int* bad_dev = nullptr;
     std::mutex mu;
